@@ -1,0 +1,110 @@
+// Hardware self-test of the tensor-core building blocks in common/sm100.cuh: one CTA stages two
+// bf16 tiles in the swizzled panel layout, issues tcgen05.mma over them in the requested
+// operand-major combination, and dumps the whole 128-lane TMEM accumulator so the host can check
+// both the arithmetic and the accumulator's lane mapping (M = 128: row r -> lane r;
+// M = 64: row r -> lane (r % 16) + 32 * (r / 16) + lane offset).
+#include "common/sm100.cuh"
+#include "fla_b200_internal.h"
+
+namespace fla {
+
+struct SelftestParams {
+  const __nv_bfloat16* a;  // a_mn == 0: [M][K] row-major, else [K][M]
+  const __nv_bfloat16* b;  // b_mn == 0: [N][K] row-major, else [K][N]
+  float* d;                // [128][N] TMEM dump
+  int M, N, K, a_mn, b_mn, d_lane_off, prefill;
+  int* err;
+};
+
+// Copy a row-major [rows][cols] bf16 matrix (cols % 64 == 0) into panels at `dst`.
+__device__ void stage_panels(uint8_t* dst, const __nv_bfloat16* src, int rows, int cols) {
+  const int chunks_per_row = cols / 8;
+  const int total = rows * chunks_per_row;
+  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    const int r = idx / chunks_per_row, ch = idx % chunks_per_row;
+    const uint4 val = *reinterpret_cast<const uint4*>(src + size_t(r) * cols + ch * 8);
+    const int panel = ch / 8, c = ch % 8;
+    *reinterpret_cast<uint4*>(dst + size_t(panel) * rows * 128 + panel_chunk_off(r, c)) = val;
+  }
+}
+
+__global__ void __launch_bounds__(128) selftest_mma_kernel(SelftestParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int a_rows = p.a_mn ? p.K : p.M, a_cols = p.a_mn ? p.M : p.K;
+  const int b_rows = p.b_mn ? p.K : p.N, b_cols = p.b_mn ? p.N : p.K;
+  uint8_t* sa = smem;
+  uint8_t* sb = smem + 32768;
+
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  stage_panels(sa, p.a, a_rows, a_cols);
+  stage_panels(sb, p.b, b_rows, b_cols);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+
+  if (p.prefill) {  // D starts as lane*4 + col/64 pattern written with tcgen05.st, MMA accumulates on top
+    for (int c0 = 0; c0 < p.N; c0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = float(warp * 32 + lane) + float(c0 + i) * 0.001f;
+      tmem_st16(tmem_addr(tbase, warp * 32, c0), v);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
+
+  if (threadIdx.x == 0) {
+    Operand A{smem_u32(sa), uint32_t(a_rows) * 128u, p.a_mn};
+    Operand B{smem_u32(sb), uint32_t(b_rows) * 128u, p.b_mn};
+    mma_tile(tmem_addr(tbase, p.d_lane_off, 0), A, B, p.M, p.N, p.K / 16, p.prefill != 0);
+    mma_commit(&bar);
+  }
+  const bool ok = mbar_wait(&bar, 0, p.err, 1);
+  tc_fence_after();
+  if (ok) {
+    for (int c0 = 0; c0 < p.N; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem_addr(tbase, warp * 32, c0), v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) p.d[size_t(warp * 32 + lane) * p.N + c0 + i] = v[i];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+}  // namespace fla
+
+extern "C" FLA_API int fla_b200_selftest_mma(const void* a, const void* b, float* d, int M, int N, int K, int a_mn, int b_mn,
+                                     int d_lane_off, int prefill, int* err_flag, void* stream) {
+  using namespace fla;
+  if (!a || !b || !d || !err_flag) return FLA_ERR_NULL;
+  if (!(M == 64 || M == 128) || N % 16 || N < 16 || N > 256 || K % 16 || K < 16 || K > 128) return FLA_ERR_SHAPE;
+  if ((a_mn ? M : K) % 64 || (b_mn ? N : K) % 64) return FLA_ERR_SHAPE;
+  if (M * K * 2 > 32768 || N * K * 2 > 32768) return FLA_ERR_SHAPE;
+  SelftestParams p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, M, N, K,
+                   a_mn, b_mn, d_lane_off, prefill, err_flag};
+  const int smem = 65536 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(selftest_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return FLA_ERR_CUDA;
+  selftest_mma_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
