@@ -1,0 +1,58 @@
+"""KDA oracle (test infrastructure only).
+
+`naive_recurrent_kda` follows the reference's per-token loop
+(tests/atk/recurrent_kda/executor_recurrent_kda.py:63-83), vectorised over batch and heads and
+with the state kept K-first ([B,HV,K,V]) like the chunk operators' initial/final state:
+    S <- diag(exp(g_t)) S;  d = beta_t (v_t - S^T k_t);  S <- S + k_t d^T;  o_t = S^T (scale q_t)
+The reference has no KDA backward of its own (it defers to a third-party Triton package that is
+not part of its tree), so gradients are pinned by autograd through this recurrence.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def naive_recurrent_kda(q, k, v, g, beta, *, scale, initial_state=None, dtype=torch.float32):
+    """q,k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] (log decay per channel); beta [B,T,H]; H = HV."""
+    q, k, v, g, beta = [x.to(dtype) for x in (q, k, v, g, beta)]
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    state = q.new_zeros(B, H, K, V) if initial_state is None else initial_state.to(dtype)
+    outs = []
+    for t in range(T):
+        state = state * g[:, t].exp()[..., None]
+        k_t = k[:, t]
+        delta = beta[:, t][..., None] * (v[:, t] - torch.einsum("bhkv,bhk->bhv", state, k_t))
+        state = state + k_t[..., None] * delta[..., None, :]
+        outs.append(torch.einsum("bhkv,bhk->bhv", state, q[:, t] * scale))
+    return torch.stack(outs, dim=1), state
+
+
+def kda_reference_fwd_bwd(q, k, v, g, beta, *, scale=None, initial_state=None, do=None, dht=None,
+                          use_qk_l2norm=False, dtype=torch.float32):
+    """Forward (+ autograd backward) through the naive KDA recurrence; GVA by repeat_interleave."""
+    HK, HV = q.shape[2], v.shape[2]
+    rep = HV // HK
+    K = q.shape[-1]
+    scale = K ** -0.5 if scale is None else scale
+    need_grad = do is not None
+    leaves = {}
+    for name, t in (("q", q), ("k", k), ("v", v), ("g", g), ("beta", beta), ("h0", initial_state)):
+        leaves[name] = None if t is None else t.detach().to(dtype).clone().requires_grad_(need_grad)
+    q_i, k_i = leaves["q"], leaves["k"]
+    if use_qk_l2norm:
+        q_i, k_i = F.normalize(q_i, p=2, dim=-1), F.normalize(k_i, p=2, dim=-1)
+    if rep != 1:
+        q_i, k_i = q_i.repeat_interleave(rep, dim=2), k_i.repeat_interleave(rep, dim=2)
+    o, ht = naive_recurrent_kda(q_i, k_i, leaves["v"], leaves["g"], leaves["beta"], scale=scale,
+                                initial_state=leaves["h0"], dtype=dtype)
+    res = {"o": o.detach(), "ht": ht.detach()}
+    if need_grad:
+        loss = (o * do.to(dtype)).sum()
+        if dht is not None:
+            loss = loss + (ht * dht.to(dtype)).sum()
+        loss.backward()
+        res.update(dq=leaves["q"].grad, dk=leaves["k"].grad, dv=leaves["v"].grad, dg=leaves["g"].grad,
+                   dbeta=leaves["beta"].grad, dh0=None if leaves["h0"] is None else leaves["h0"].grad)
+    return res

@@ -1,0 +1,138 @@
+"""Generate the committed golden fixtures by running the REFERENCE's own CPU functions.
+
+Run once in a container that has the reference checkout (path in $FLA_REFERENCE_ROOT, default
+/root/reference):  python tests/golden/make_golden.py
+The reference modules import Ascend-only packages at module level, so the needed pure-torch
+functions are extracted from the source text with `ast` and executed on their own.  The outputs
+(inputs + reference results, float32/int32 numpy arrays) are written next to this script as .npz;
+tests/test_oracle_golden.py replays them against oracle/ without needing the reference.
+"""
+from __future__ import annotations
+
+import ast
+import math
+import os
+import sys
+from pathlib import Path
+from typing import Optional, Tuple  # noqa: F401  (used by exec'd reference code)
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = Path(__file__).resolve().parent
+REF = Path(os.environ.get("FLA_REFERENCE_ROOT", "/root/reference"))
+sys.path.insert(0, str(HERE.parent.parent))
+
+
+def extract(path: Path, names):
+    src = path.read_text()
+    tree = ast.parse(src)
+    ns = {"torch": torch, "F": F, "math": math, "Optional": Optional, "Tuple": Tuple}
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            exec(compile(ast.Module([node], []), str(path), "exec"), ns)
+    missing = [n for n in names if n not in ns]
+    assert not missing, missing
+    return ns
+
+
+def f32(t):
+    return t.detach().float().numpy()
+
+
+def gdn_fixture():
+    ns = extract(REF / "examples/flash_gated_delta_rule.py", ["_naive_recurrent_gated_delta_rule_cpu"])
+    naive = ns["_naive_recurrent_gated_delta_rule_cpu"]
+    g_ = torch.Generator().manual_seed(11)
+    B, T, H, K, V = 2, 96, 3, 16, 24
+    q = F.normalize(torch.randn(B, T, H, K, generator=g_), dim=-1)
+    k = F.normalize(torch.randn(B, T, H, K, generator=g_), dim=-1)
+    v = torch.randn(B, T, H, V, generator=g_)
+    g = F.logsigmoid(torch.randn(B, T, H, generator=g_))
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=g_))
+    do = torch.randn(B, T, H, V, generator=g_)
+    leaves = [x.clone().requires_grad_(True) for x in (q, k, v, beta, g)]
+    o = naive(*leaves, scale=K ** -0.5)
+    (o * do).sum().backward()
+    np.savez_compressed(HERE / "gdn_naive.npz", q=f32(q), k=f32(k), v=f32(v), g=f32(g), beta=f32(beta), do=f32(do),
+                        o=f32(o), dq=f32(leaves[0].grad), dk=f32(leaves[1].grad), dv=f32(leaves[2].grad),
+                        dbeta=f32(leaves[3].grad), dg=f32(leaves[4].grad))
+
+
+def decode_fixture():
+    gold_dir = REF / "fla/ops/ascendc/gdn/recurrent_gdn/recurrent_gated_delta_rule/tests/pta"
+    ns = extract(gold_dir / "golden.py", ["recurrent_gated_delta_rule_golden"])
+    golden = ns["recurrent_gated_delta_rule_golden"]
+    torch.manual_seed(42)
+    bs, mtp, nk, nv, dk, dv = 3, 2, 2, 4, 16, 8
+    asl = torch.cat([torch.tensor([1], dtype=torch.int32), torch.full((bs,), mtp, dtype=torch.int32)])
+    t = int(asl.sum())
+    state = torch.rand((t, nv, dv, dk)).bfloat16()
+    query = F.normalize(torch.rand((t, nk, dk)), p=2, dim=-1).bfloat16()
+    key = F.normalize(torch.rand((t, nk, dk)), p=2, dim=-1).bfloat16()
+    value = torch.rand((t, nv, dv)).bfloat16()
+    beta = torch.rand((t, nv)).bfloat16()
+    g = -torch.rand((t, nv))
+    ssm = torch.randperm(t).to(torch.int32)
+    acc = torch.tensor([1, 2, 1], dtype=torch.int32)
+    out, fs = golden(query, key, value, state, beta, dk ** -0.5, asl, ssm, num_accepted_tokens=acc, g=g)
+    out2, fs2 = golden(query, key, value, state, beta, dk ** -0.5, asl, ssm, num_accepted_tokens=None, g=g)
+    np.savez_compressed(HERE / "decode_golden.npz", query=f32(query), key=f32(key), value=f32(value),
+                        state=f32(state), beta=f32(beta), g=f32(g), actual_seq_lengths=asl.numpy(),
+                        ssm_state_indices=ssm.numpy(), num_accepted_tokens=acc.numpy(), scale=np.float32(dk ** -0.5),
+                        out_acc=f32(out), state_acc=f32(fs), out=f32(out2), state_out=f32(fs2))
+
+
+def conv_fixture():
+    ns = extract(REF / "torch_custom/fla_npu/test/test_npu_causal_conv1d.py",
+                 ["causal_conv1d_ref", "causal_conv1d_update_ref", "causal_conv1d_update_spec_ref"])
+
+    def make_tensor(shape, start=1.0):  # the reference tests' arange/128 known-answer inputs
+        n = int(np.prod(shape))
+        return (torch.arange(start, start + n, dtype=torch.float32).reshape(shape) / 128.0)
+
+    x = make_tensor((2, 16, 6), 1.0)             # (batch, dim, seqlen)
+    w = make_tensor((16, 4), 101.0) / 64.0
+    b = make_tensor((16,), 201.0) / 64.0
+    init = make_tensor((2, 16, 3), 301.0) / 64.0
+    y0, fs0 = ns["causal_conv1d_ref"](x, w, b, None, True, None, "silu")
+    y1, fs1 = ns["causal_conv1d_ref"](x, w, None, init, True, None, None)
+    xs = make_tensor((2, 16, 2), 1.0)            # short sequence: final state is left-padded
+    y2, fs2 = ns["causal_conv1d_ref"](xs, w, b, None, True, None, "silu")
+    st = init.clone()
+    xu = make_tensor((2, 16), 7.0)
+    yu = ns["causal_conv1d_update_ref"](xu, st, w, b, "silu")
+    st_spec = make_tensor((2, 16, 5), 401.0) / 64.0
+    st_spec_after = st_spec.clone()
+    xsp = make_tensor((2, 16, 3), 9.0)
+    ysp = ns["causal_conv1d_update_spec_ref"](xsp, st_spec_after, w, b, [1, 3], "silu")
+    np.savez_compressed(HERE / "conv_golden.npz", x=f32(x), w=f32(w), b=f32(b), init=f32(init), y0=f32(y0), fs0=f32(fs0),
+                        y1=f32(y1), fs1=f32(fs1), xs=f32(xs), y2=f32(y2), fs2=f32(fs2), xu=f32(xu), yu=f32(yu),
+                        st_after=f32(st), st_spec=f32(st_spec), st_spec_after=f32(st_spec_after), xsp=f32(xsp),
+                        ysp=f32(ysp), accepted=np.array([1, 3], dtype=np.int32))
+
+
+def kda_fixture():
+    ns = extract(REF / "tests/atk/recurrent_kda/executor_recurrent_kda.py", ["_recurrent_kda_ref"])
+    ref = ns["_recurrent_kda_ref"]
+    g_ = torch.Generator().manual_seed(13)
+    B, T, H, HV, K, V = 1, 40, 2, 4, 16, 8
+    q = F.normalize(torch.randn(B, T, H, K, generator=g_), dim=-1)
+    k = F.normalize(torch.randn(B, T, H, K, generator=g_), dim=-1)
+    v = torch.randn(B, T, HV, V, generator=g_)
+    g = F.logsigmoid(torch.randn(B, T, HV, K, generator=g_)) / 4
+    beta = torch.sigmoid(torch.randn(B, T, HV, generator=g_))
+    h0 = 0.1 * torch.randn(B, HV, V, K, generator=g_)       # reference state is V-first
+    out, st = ref(dict(q=q, k=k, v=v, g=g, beta=beta, initial_state=h0, scale=K ** -0.5))
+    np.savez_compressed(HERE / "kda_naive.npz", q=f32(q), k=f32(k), v=f32(v), g=f32(g), beta=f32(beta), h0=f32(h0),
+                        o=f32(out), ht=f32(st))
+
+
+if __name__ == "__main__":
+    gdn_fixture()
+    decode_fixture()
+    conv_fixture()
+    kda_fixture()
+    for p in sorted(HERE.glob("*.npz")):
+        print(p.name, p.stat().st_size)

@@ -1,0 +1,88 @@
+"""Pins the CPU oracle to the reference: replays fixtures produced by the reference's own CPU
+functions (tests/golden/make_golden.py) through oracle/ and requires agreement to fp32 round-off."""
+from pathlib import Path
+
+import numpy as np
+import torch
+
+import oracle
+
+G = Path(__file__).resolve().parent / "golden"
+
+
+def _load(name):
+    return {k: torch.from_numpy(v) for k, v in np.load(G / name).items()}
+
+
+def _close(a, b, tol=2e-5):
+    assert a.shape == b.shape, (a.shape, b.shape)
+    err = (a.double() - b.double()).abs().max().item()
+    assert err <= tol * max(1.0, b.abs().max().item()), err
+
+
+def test_gdn_naive_forward_and_autograd_match_reference():
+    f = _load("gdn_naive.npz")
+    r = oracle.gdn_reference_fwd_bwd(f["q"], f["k"], f["v"], f["g"], f["beta"], do=f["do"], dtype=torch.float32)
+    for name in ("o", "dq", "dk", "dv", "dg", "dbeta"):
+        _close(r[name], f[name])
+    # zero initial state == the reference's implicit start
+    h0 = torch.zeros(f["q"].shape[0], f["q"].shape[2], f["q"].shape[3], f["v"].shape[3])
+    r0 = oracle.gdn_reference_fwd_bwd(f["q"], f["k"], f["v"], f["g"], f["beta"], initial_state=h0)
+    _close(r0["o"], f["o"])
+
+
+def test_gdn_chunked_restatement_matches_reference():
+    f = _load("gdn_naive.npz")
+    for C in (64, 32):
+        c = oracle.chunk_gated_delta_rule_restated(f["q"], f["k"], f["v"], f["g"], f["beta"], chunk_size=C)
+        _close(c["o"].float(), f["o"])
+
+
+def test_gdn_final_state_consistent_with_split_sequence():
+    # the extension (initial_state / final state) is pinned by composition: running [0,T1) then
+    # [T1,T) from the returned state must equal the reference's single pass.
+    f = _load("gdn_naive.npz")
+    T1 = 37
+    a = oracle.gdn_reference_fwd_bwd(f["q"][:, :T1], f["k"][:, :T1], f["v"][:, :T1], f["g"][:, :T1], f["beta"][:, :T1])
+    b = oracle.gdn_reference_fwd_bwd(f["q"][:, T1:], f["k"][:, T1:], f["v"][:, T1:], f["g"][:, T1:], f["beta"][:, T1:],
+                                     initial_state=a["ht"])
+    _close(torch.cat([a["o"], b["o"]], 1), f["o"])
+
+
+def test_decode_golden_matches_reference():
+    f = _load("decode_golden.npz")
+    args = [f["query"].bfloat16(), f["key"].bfloat16(), f["value"].bfloat16(), f["state"].bfloat16(),
+            f["beta"].bfloat16(), float(f["scale"]), f["actual_seq_lengths"], f["ssm_state_indices"]]
+    out, st = oracle.recurrent_gated_delta_rule_golden(*args, num_accepted_tokens=f["num_accepted_tokens"], g=f["g"])
+    _close(out.float(), f["out_acc"], 1e-6)
+    _close(st.float(), f["state_acc"], 1e-6)
+    out, st = oracle.recurrent_gated_delta_rule_golden(*args, g=f["g"])
+    _close(out.float(), f["out"], 1e-6)
+    _close(st.float(), f["state_out"], 1e-6)
+
+
+def test_conv_goldens_match_reference():
+    f = _load("conv_golden.npz")
+    y0, fs0 = oracle.causal_conv1d_ref(f["x"], f["w"], f["b"], None, True, "silu")
+    _close(y0, f["y0"]); _close(fs0, f["fs0"])
+    y1, fs1 = oracle.causal_conv1d_ref(f["x"], f["w"], None, f["init"], True, None)
+    _close(y1, f["y1"]); _close(fs1, f["fs1"])
+    y2, fs2 = oracle.causal_conv1d_ref(f["xs"], f["w"], f["b"], None, True, "silu")
+    _close(y2, f["y2"]); _close(fs2, f["fs2"])
+    st = f["init"].clone()
+    yu = oracle.causal_conv1d_update_ref(f["xu"], st, f["w"], f["b"], "silu")
+    _close(yu, f["yu"]); _close(st, f["st_after"])
+    st = f["st_spec"].clone()
+    ysp = oracle.causal_conv1d_update_spec_ref(f["xsp"], st, f["w"], f["b"], f["accepted"], "silu")
+    _close(ysp, f["ysp"]); _close(st, f["st_spec_after"])
+
+
+def test_kda_naive_matches_reference():
+    f = _load("kda_naive.npz")
+    rep = f["v"].shape[2] // f["q"].shape[2]
+    q = f["q"].repeat_interleave(rep, dim=2)
+    k = f["k"].repeat_interleave(rep, dim=2)
+    o, ht = oracle.naive_recurrent_kda(q, k, f["v"], f["g"], f["beta"], scale=q.shape[-1] ** -0.5,
+                                       initial_state=f["h0"].transpose(-1, -2))
+    _close(o, f["o"])
+    _close(ht.transpose(-1, -2), f["ht"])
