@@ -1,0 +1,22 @@
+"""ctypes twins of the argument structs declared in include/fla_b200.h (field order must match)."""
+import ctypes
+
+from .._runtime import TensorDesc
+
+
+class RecurrentGdnArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "g", "beta", "state_in", "state_out", "out",
+                                           "cu_seqlens", "state_indices", "num_accepted_tokens")] + [
+        ("scale", ctypes.c_float), ("tokens_per_seq", ctypes.c_int32), ("state_v_first", ctypes.c_int32),
+        ("use_qk_l2norm", ctypes.c_int32)]
+
+
+class CausalConv1dFwdArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("x", "weight", "bias", "residual", "initial_state", "y", "final_state",
+                                           "cu_seqlens")] + [("activation_silu", ctypes.c_int32)]
+
+
+class CausalConv1dUpdateArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("x", "weight", "bias", "residual", "conv_state", "y", "cache_indices",
+                                           "num_accepted_tokens")] + [
+        ("activation_silu", ctypes.c_int32), ("pad_slot_id", ctypes.c_int32)]

@@ -1,0 +1,122 @@
+"""causal_conv1d forward / decode update.
+
+`causal_conv1d` and `causal_conv1d_update` use the `[B,T,D]` surface the reference's composed entry
+exposes (examples/flash_gated_delta_rule.py:422-443: x, weight `[D,W]`, bias, residual, initial_state,
+activation, cu_seqlens, output_final_state).  States are `[N,D,W-1]` (the last W-1 inputs);
+`npu_causal_conv1d` below keeps the reference low-level operator's signature and its
+`[W,D]` weight / `[N,W-1,D]` state layouts (…/ops/ascendc/_aclnn_ctypes.py:951-985).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _runtime as rt
+from ._structs import CausalConv1dFwdArgs, CausalConv1dUpdateArgs
+
+
+def _act(activation) -> int:
+    if activation in (None, 0, False):
+        return 0
+    if activation in ("silu", "swish", 1, True):
+        return 1
+    raise NotImplementedError(f"activation must be None, 'silu' or 'swish', got {activation!r}")
+
+
+def causal_conv1d(x, weight=None, bias=None, residual=None, initial_state=None, output_final_state=False,
+                  activation=None, cu_seqlens=None):
+    """x `[B,T,D]` bf16; weight `[D,W]`; initial_state / final_state `[N,D,W-1]`.
+    Returns ``(y [B,T,D], final_state | None)``."""
+    op = "causal_conv1d"
+    if x.dim() != 3:
+        raise RuntimeError(f"{op}: x must be [B,T,D], got {tuple(x.shape)}")
+    if weight is None:
+        raise RuntimeError(f"{op}: weight is required")
+    B, T, D = x.shape
+    W = weight.shape[1]
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    cu = None
+    N = B
+    if cu_seqlens is not None:
+        cu = cu_seqlens.to(device=x.device, dtype=torch.int32)
+        N = cu.numel() - 1
+    y = torch.empty_like(x)
+    final = torch.empty((N, D, W - 1), dtype=x.dtype, device=x.device) if output_final_state else None
+    a = CausalConv1dFwdArgs()
+    a.x, a.weight, a.bias, a.residual = rt.desc(x), rt.desc(weight), rt.desc(bias), rt.desc(residual)
+    a.initial_state, a.y, a.final_state, a.cu_seqlens = rt.desc(initial_state), rt.desc(y), rt.desc(final), rt.desc(cu)
+    a.activation_silu = _act(activation)
+    rt.call("causal_conv1d_fwd", a, [x, weight, bias, residual, initial_state, y, final, cu])
+    return y, final
+
+
+def causal_conv1d_update(x, cache, residual=None, weight=None, bias=None, activation=None, cache_indices=None,
+                         num_accepted_tokens=None, pad_slot_id=-1):
+    """Decode step.  x `[N,D]` or `[N,T,D]`; cache `[slots,D,S]` (S >= W-1), updated in place.
+    Returns y with the shape of x."""
+    op = "causal_conv1d_update"
+    if weight is None:
+        raise RuntimeError(f"{op}: weight is required")
+    rt.reject_requires_grad(op, cache=cache)
+    squeeze = x.dim() == 2
+    x3 = x.unsqueeze(1) if squeeze else x
+    r3 = None if residual is None else (residual.unsqueeze(1) if squeeze else residual)
+    y3 = torch.empty_like(x3)
+    a = CausalConv1dUpdateArgs()
+    a.x, a.weight, a.bias, a.residual = rt.desc(x3), rt.desc(weight), rt.desc(bias), rt.desc(r3)
+    a.conv_state, a.y = rt.desc(cache), rt.desc(y3)
+    a.cache_indices, a.num_accepted_tokens = rt.desc(cache_indices), rt.desc(num_accepted_tokens)
+    a.activation_silu, a.pad_slot_id = _act(activation), int(pad_slot_id)
+    rt.call("causal_conv1d_update", a, [x3, weight, bias, r3, cache, y3, cache_indices, num_accepted_tokens])
+    rt.mark_mutated(cache)
+    return y3.squeeze(1) if squeeze else y3
+
+
+def npu_causal_conv1d(x, weight, bias=None, conv_states=None, *, query_start_loc=None, cache_indices=None,
+                      initial_state_mode=None, num_accepted_tokens=None, activation_mode=0, pad_slot_id=-1,
+                      run_mode=0, head_num=0):
+    """Reference low-level signature.  x `[B,T,D]` / `[T,D]` (varlen with query_start_loc) for run_mode 0,
+    `[N,D]` / `[N,T,D]` for run_mode 1; weight `[W,D]`; conv_states `[slots,S,D]` updated in place."""
+    op = "npu_causal_conv1d"
+    if head_num:
+        raise NotImplementedError(f"{op}: head_num output re-layout is not provided; outputs keep the layout of x")
+    w_dw = weight.transpose(0, 1)                                   # [D,W] view of the [W,D] tensor
+    st = None if conv_states is None else conv_states.transpose(1, 2)  # [slots,D,S] view
+    dev = x.device
+
+    def as_i32(v):
+        if v is None:
+            return None
+        return v.to(device=dev, dtype=torch.int32) if isinstance(v, torch.Tensor) else torch.tensor(
+            list(v), dtype=torch.int32, device=dev)
+
+    if int(run_mode) == 1:
+        return causal_conv1d_update(x, st, weight=w_dw, bias=bias, activation=int(activation_mode),
+                                    cache_indices=as_i32(cache_indices),
+                                    num_accepted_tokens=as_i32(num_accepted_tokens), pad_slot_id=pad_slot_id)
+    W = weight.shape[0]
+    varlen = x.dim() == 2
+    x3 = x.unsqueeze(0) if varlen else x
+    cu = as_i32(query_start_loc) if varlen else None
+    N = (cu.numel() - 1) if varlen else x3.shape[0]
+    init = None
+    idx = as_i32(cache_indices)
+    if st is not None:
+        rt.reject_requires_grad(op, conv_states=conv_states)
+        if st.shape[2] != W - 1:
+            raise RuntimeError(f"{op}: prefill expects conv_states with state_len == W-1")
+        if initial_state_mode is not None:
+            sel = st if idx is None else st[idx.long()]
+            mode = as_i32(initial_state_mode).bool()
+            init = torch.where(mode[:, None, None], sel, torch.zeros_like(sel))
+    y, final = causal_conv1d(x3, w_dw, bias, None, init, st is not None, int(activation_mode), cu)
+    if st is not None:
+        if idx is None:
+            st[:N].copy_(final)
+        else:
+            keep = idx != pad_slot_id
+            st[idx[keep].long()] = final[keep]
+        rt.mark_mutated(conv_states)
+    return y.squeeze(0) if varlen else y

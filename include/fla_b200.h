@@ -62,6 +62,77 @@ FLA_API int fla_b200_version(void);
 FLA_API int fla_b200_selftest_mma(const void* a, const void* b, float* d, int M, int N, int K, int a_mn, int b_mn,
                           int d_lane_off, int prefill, int* err_flag, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Fused-recurrent gated delta rule (decode step), in-place over a state pool.
+ * Replaces aclnnRecurrentGatedDeltaRule as bound by npu_recurrent_gated_delta_rule
+ * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:654-846; kernel
+ * fla/ops/ascendc/gdn/recurrent_gdn/recurrent_gated_delta_rule/op_kernel/recurrent_gated_delta_rule.h:159-199).
+ * Per token: S <- exp(g) S; d = beta (v - S^T k); S <- S + k d^T; o = S^T (scale q).
+ *   q, k   [T, HK, K] bf16          v   [T, HV, V] bf16        (HV % HK == 0, head hv reads q/k head hv / (HV/HK))
+ *   g      [T, HV] f32|bf16, optional (absent: no decay)        beta [T, HV] f32|bf16, optional (absent: 1)
+ *   state_in / state_out [blocks, HV, K, V] (state_v_first = 0) or [blocks, HV, V, K] (= 1), f32|bf16,
+ *          innermost two dims dense; the two may be the same tensor (in-place update)
+ *   out    [T, HV, V] bf16|f32
+ *   cu_seqlens          int32 [N+1] device, token offsets of the N sequences; absent: every sequence has
+ *                       `tokens_per_seq` tokens
+ *   state_indices       int32 [T] device: the state after token t is written to block state_indices[t], and a
+ *                       sequence starts from block state_indices[first token (+ accepted - 1)]; a negative
+ *                       start index skips the sequence.  Absent: sequence n reads block n of state_in and its
+ *                       final state is written to block n of state_out.
+ *   num_accepted_tokens int32 [N] device, optional (needs state_indices)
+ * K, V in {64, 128}.  No workspace. */
+typedef struct fla_recurrent_gdn_args {
+  fla_tensor_t q, k, v, g, beta, state_in, state_out, out;
+  fla_tensor_t cu_seqlens, state_indices, num_accepted_tokens;
+  float scale;
+  int32_t tokens_per_seq;
+  int32_t state_v_first;
+  int32_t use_qk_l2norm; /* normalise q and k rows as x * rsqrt(sum x^2 + 1e-6) first */
+} fla_recurrent_gdn_args;
+FLA_API int fla_b200_recurrent_gdn_workspace_size(const fla_recurrent_gdn_args* args, uint64_t* bytes);
+FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* args, void* workspace, uint64_t workspace_bytes,
+                                   void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * causal_conv1d forward over whole sequences (prefill).
+ * Replaces aclnnCausalConv1d with run_mode = 0 as bound by npu_causal_conv1d
+ * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:951-985) and the composed entry
+ * causal_conv1d_ascendc (examples/flash_gated_delta_rule.py:422-443).
+ *   y[t, d] = act(bias[d] + sum_{j<W} weight[d, j] * x[t - (W-1) + j, d]) (+ residual[t, d])
+ *   x, y, residual [B, T, D] bf16, D contiguous and a multiple of 8
+ *   weight [D, W] bf16 (any strides: pass the reference's [W, D] tensor as a transposed view), W in {2,3,4}
+ *   bias [D] bf16, optional
+ *   initial_state / final_state [N, D, W-1] bf16 (any strides), optional: the last W-1 inputs before /
+ *          after each sequence (zero-padded on the left when a sequence is shorter)
+ *   cu_seqlens int32 [N+1] device, optional: packed variable-length sequences, requires B == 1
+ *   activation_silu: 0 = none, 1 = SiLU.   No workspace. */
+typedef struct fla_causal_conv1d_fwd_args {
+  fla_tensor_t x, weight, bias, residual, initial_state, y, final_state, cu_seqlens;
+  int32_t activation_silu;
+} fla_causal_conv1d_fwd_args;
+FLA_API int fla_b200_causal_conv1d_fwd_workspace_size(const fla_causal_conv1d_fwd_args* args, uint64_t* bytes);
+FLA_API int fla_b200_causal_conv1d_fwd(const fla_causal_conv1d_fwd_args* args, void* workspace,
+                                       uint64_t workspace_bytes, void* stream);
+
+/* causal_conv1d decode update: consumes T new tokens per sequence and shifts conv_state in place.
+ * Replaces aclnnCausalConv1d with run_mode = 1 (same binding as above; kernel
+ * fla/ops/ascendc/gdn/gdn_preprocess/causal_conv1d/op_kernel/causal_conv1d_update.h).
+ *   x, y, residual [N, T, D] bf16 (T <= 16);  weight [D, W];  bias [D]
+ *   conv_state [slots, D, S] bf16, any strides, S >= W-1, updated in place.  Fast paths: T == 1, S == W-1 and
+ *          either channels contiguous ([slots, S, D] memory) or taps contiguous ([slots, D, S] memory).
+ *   cache_indices int32 [N] device, optional: slot of each sequence; entries equal to pad_slot_id are skipped
+ *   num_accepted_tokens int32 [N] device, optional: speculative decoding; history window starts at
+ *          accepted-1 and S >= (W-1) + (T-1)
+ * No workspace. */
+typedef struct fla_causal_conv1d_update_args {
+  fla_tensor_t x, weight, bias, residual, conv_state, y, cache_indices, num_accepted_tokens;
+  int32_t activation_silu;
+  int32_t pad_slot_id;
+} fla_causal_conv1d_update_args;
+FLA_API int fla_b200_causal_conv1d_update_workspace_size(const fla_causal_conv1d_update_args* args, uint64_t* bytes);
+FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* args, void* workspace,
+                                          uint64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
