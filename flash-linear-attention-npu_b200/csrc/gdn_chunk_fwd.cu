@@ -1,0 +1,578 @@
+// Chunked gated-delta-rule forward (chunk = 64 tokens, K = V = 128) as two kernels:
+//
+//  gdn_prep_kernel   (parallel over chunks): gam = chunk-local cumsum(g);
+//                    A[i,j] = beta_i exp(gam_i - gam_j) k_i.k_j (j < i);  X = (I + A)^-1
+//                    KK^T on tcgen05 (shared by the value heads of a GVA group), the unit-lower
+//                    triangular inverse by fp32 forward substitution on CUDA cores.
+//                    Replaces chunk_local_cumsum + chunk_scaled_dot_kkt + solve_tri of the reference
+//                    (examples/flash_gated_delta_rule.py:811-838).
+//  gdn_fwd_kernel    (sequential over chunks, one CTA per (sequence, value head, 64-column block of V)):
+//                    v_new = X (beta * (V - exp(gam) * (K S)))
+//                    o     = scale (exp(gam) * (Q S) + tril(Q K^T * exp(gam_i - gam_j)) v_new)
+//                    S    <- exp(gam_L) S + K^T (exp(gam_L - gam) * v_new)
+//                    which is recompute_w_u + chunk_gated_delta_rule_fwd_h + chunk_fwd_o of the reference
+//                    (examples/flash_gated_delta_rule.py:840-880) with the WY factors w, u folded away so
+//                    that no per-chunk intermediate (A, w, u, h, v_new) round-trips through HBM.
+//
+// The fp32 state lives in TMEM for the whole sequence.  Tensor-core operands that the result is
+// sensitive to (the state copy, beta*(V - ...), v_new, the decayed score tile) are split into a bf16
+// "hi" part and a bf16 residual and multiplied in two or three passes; q, k, v enter as the exact
+// bf16 inputs.  All matrix products run as tcgen05.mma with M = 128 (unused accumulator rows are
+// ignored) so that TMEM lane == accumulator row for every tile.
+#include "gdn_common.cuh"
+#include "fla_b200_internal.h"
+
+namespace fla {
+
+struct GdnFwdParams {
+  const bf16* q; const bf16* k; const bf16* v;
+  const void* g; const void* beta;
+  float* gam;          // [tokens, HV]      chunk-local cumulative log decay (saved for backward)
+  bf16* X;             // [tokens, HV, 64]  row i of the chunk's (I + A)^-1 (saved for backward)
+  const float* h0;     // [N, HV, K, V] or null
+  float* ht;           // [N, HV, K, V] or null
+  void* o;             // [tokens, HV, V]
+  bf16* s_hi; bf16* s_lo;    // [chunks, HV, K, V] state at chunk start, split (optional, for backward)
+  bf16* vn_hi; bf16* vn_lo;  // [tokens, HV, V] v_new, split (optional, for backward)
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int64_t q_st, q_sh, k_st, k_sh, v_st, v_sh, o_st, o_sh, g_st, beta_st;
+  int N, T, HK, HV, g_is_f32, beta_is_f32, o_is_f32;
+  float scale;
+  int* status;
+};
+
+// --------------------------------------------------------------------------------------------- prep
+constexpr int kAStride = 68;  // fp32 row stride of the 64x64 score tiles in shared memory
+
+__global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k_pan = smem;                                        // 2 panels x 64 rows
+  float* kk_s = reinterpret_cast<float*>(smem + 16384);          // [64][68]
+  float* a_s = kk_s + kC * kAStride;                             // [2][64][68]
+  float* g_s = a_s + 2 * kC * kAStride;                          // [2][64] raw g, then gam
+  float* b_s = g_s + 2 * kC;                                     // [2][64]
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int hk = blockIdx.y, n = blockIdx.z;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const int t0 = blockIdx.x * kC;
+  if (t0 >= sq.len) return;
+  const int rows = min(kC, sq.len - t0);
+  const int64_t tok0 = int64_t(sq.bos) + t0;
+
+  for (int idx = tid; idx < kC * 16; idx += 128) {
+    const int r = idx / 16, ch = idx % 16;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r < rows) val = *reinterpret_cast<const uint4*>(p.k + (tok0 + r) * p.k_st + hk * p.k_sh + ch * 8);
+    *reinterpret_cast<uint4*>(k_pan + (ch / 8) * 8192 + panel_chunk_off(r, ch % 8)) = val;
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 64);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  if (tid == 0) {
+    const Operand kop{smem_u32(k_pan), 8192u, 0};
+    mma_tile(tbase, kop, kop, 64, 64, kK / 16, false);  // K K^T, M = 64: row r -> lane (r % 16) + 32 (r / 16)
+    mma_commit(&bar);
+  }
+  const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
+  tc_fence_after();
+  if (ok) {
+#pragma unroll
+    for (int c0 = 0; c0 < kC; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem_addr(tbase, warp * 32, c0), v);
+      tmem_ld_wait();
+      if (lane < 16) {
+        float* dst = kk_s + (warp * 16 + lane) * kAStride + c0;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 64);
+  if (!ok) return;
+
+  const int G = p.HV / p.HK;
+  const int hsel = tid / 64, c = tid % 64;
+  float* A = a_s + hsel * kC * kAStride;
+  float* gs = g_s + hsel * kC;
+  float* bs = b_s + hsel * kC;
+  for (int h0 = 0; h0 < G; h0 += 2) {
+    const int h = h0 + hsel;
+    const bool active = h < G;
+    const int hv = hk * G + h;
+    if (active) {
+      gs[c] = c < rows ? ld_scalar(p.g, (tok0 + c) * p.g_st + hv, p.g_is_f32) : 0.f;
+      bs[c] = c < rows ? ld_scalar(p.beta, (tok0 + c) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    }
+    __syncthreads();
+    float gam = 0.f;
+    if (active) {
+      for (int j = 0; j <= c; ++j) gam += gs[j];
+    }
+    __syncthreads();
+    if (active) {
+      gs[c] = gam;
+      if (c < rows) p.gam[(tok0 + c) * p.HV + hv] = gam;
+    }
+    __syncthreads();
+    if (active) {
+      // column c of A (rows below the diagonal)
+      for (int i = c + 1; i < kC; ++i) A[i * kAStride + c] = bs[i] * __expf(gs[i] - gam) * kk_s[i * kAStride + c];
+    }
+    __syncthreads();
+    if (active) {
+      // thread c solves column c of X = (I + A)^-1 by forward substitution: x_i = [i == c] - sum_{j<i} A_ij x_j
+      float x[kC];
+#pragma unroll
+      for (int i = 0; i < kC; ++i) {
+        float acc = (i == c) ? 1.f : 0.f;
+#pragma unroll
+        for (int j4 = 0; j4 < i; j4 += 4) {
+          const float4 a4 = *reinterpret_cast<const float4*>(A + i * kAStride + j4);
+          acc -= a4.x * x[j4];
+          if (j4 + 1 < i) acc -= a4.y * x[j4 + 1];
+          if (j4 + 2 < i) acc -= a4.z * x[j4 + 2];
+          if (j4 + 3 < i) acc -= a4.w * x[j4 + 3];
+        }
+        x[i] = acc;
+      }
+      bf16* xg = p.X + ((tok0 * p.HV + hv) * kC) + c;
+#pragma unroll
+      for (int i = 0; i < kC; ++i)
+        if (i < rows) xg[int64_t(i) * p.HV * kC] = __float2bfloat16_rn(x[i]);
+    }
+    __syncthreads();
+  }
+}
+
+// --------------------------------------------------------------------------------------------- forward
+// Shared-memory map of gdn_fwd_kernel (offsets from a 1024-byte aligned base).
+constexpr uint32_t kOffQK = 0;                    // 2 panels x 128 rows: rows 0-63 q, rows 64-127 k
+constexpr uint32_t kQKPanel = 16384;
+constexpr uint32_t kOffSH = 32768, kOffSL = 49152;            // state copy hi / lo: 128 rows x 64 cols
+constexpr uint32_t kOffZH = 65536, kOffZL = 73728;            // beta*(V - ..) hi / lo, then v_new hi / lo
+constexpr uint32_t kOffVH = 81920, kOffVL = 90112;            // decayed v_new hi / lo
+constexpr uint32_t kOffX = 98304;                             // X panel (64 rows); the 64 rows before it are VL
+constexpr uint32_t kFwdSmem = 106496;
+constexpr uint32_t kColS = 0, kColRQ = 64, kColQK = 128, kColVN = 192;  // TMEM column map (256 columns)
+
+struct FwdPrefetch {
+  uint4 qk[16];
+  uint4 x[4];
+  uint4 v[8];
+  float gb;
+};
+
+__global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ float gam_s[2][kC], beta_s[2][kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+
+  const int tid = threadIdx.x, warp = tid / 32;
+  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
+  const int hk = hv / (p.HV / p.HK);
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const bool kwarp = warp >= 2;          // warps 2,3 own the k-side rows (TMEM lanes 64..127)
+  const int row = tid;                   // TMEM lane == accumulator row
+  const int tok = tid & 63;              // token row inside the chunk for both halves
+
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  uint32_t phase = 0;
+  const uint32_t sb = smem_u32(smem);
+
+  FwdPrefetch pf;
+  auto prefetch_load = [&](int c) {
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = tid + i * 128;            // 0..2047: [q rows | k rows] x 16 chunks
+      const int r = (idx / 16) & 63, ch = idx % 16;
+      const bool isk = idx >= 1024;
+      pf.qk[i] = make_uint4(0, 0, 0, 0);
+      if (r < rows) {
+        const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
+        pf.qk[i] = *reinterpret_cast<const uint4*>(src + ch * 8);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 128, r = idx / 8, ch = idx % 8;
+      pf.x[i] = make_uint4(0, 0, 0, 0);
+      if (r < rows) pf.x[i] = *reinterpret_cast<const uint4*>(p.X + ((tok0 + r) * p.HV + hv) * kC + ch * 8);
+    }
+    if (kwarp) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        pf.v[i] = make_uint4(0, 0, 0, 0);
+        if (tok < rows) pf.v[i] = *reinterpret_cast<const uint4*>(p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + i * 8);
+      }
+      pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    } else {
+      // rows past the end of the sequence carry the last valid cumulative decay so every exponent stays finite
+      pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
+    }
+  };
+  uint4 vcur[8];
+  auto prefetch_store = [&](int c) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = tid + i * 128;
+      const int r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
+      *reinterpret_cast<uint4*>(smem + kOffQK + (ch / 8) * kQKPanel + panel_chunk_off(r, ch % 8)) = pf.qk[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 128;
+      *reinterpret_cast<uint4*>(smem + kOffX + panel_chunk_off(idx / 8, idx % 8)) = pf.x[i];
+    }
+    if (kwarp) {
+      beta_s[c & 1][tok] = pf.gb;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vcur[i] = pf.v[i];
+    } else {
+      gam_s[c & 1][tok] = pf.gb;
+    }
+  };
+
+  // operands (shared addresses)
+  const Operand opQK{sb + kOffQK, kQKPanel, 0};                 // [q; k]  M = 128, reduction over K
+  const Operand opKb{sb + kOffQK + 8192, kQKPanel, 0};          // k as B (N = 64 tokens), reduction over K
+  const Operand opKT{sb + kOffQK + 8192, kQKPanel, 1};          // k^T     M = 128 (K dims), reduction over tokens
+  const Operand opSH{sb + kOffSH, 16384, 1}, opSL{sb + kOffSL, 16384, 1};
+  const Operand opZH{sb + kOffZH, 8192, 1}, opZL{sb + kOffZL, 8192, 1};
+  const Operand opVH{sb + kOffVH, 8192, 1}, opVL{sb + kOffVL, 8192, 1};
+  const Operand opX{sb + kOffX - 8192, 16384, 0};               // rows 64..127 of this tile are X
+  const Operand opPH{sb + kOffQK, kQKPanel, 0}, opPL{sb + kOffQK + kQKPanel, kQKPanel, 0};  // alias the q rows
+
+  bool ok = true;
+  float srow[kBV];
+
+  // ---- prologue: chunk 0 operands and the initial state
+  prefetch_load(0);
+  prefetch_store(0);
+  if (p.h0) {
+    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+#pragma unroll
+    for (int i = 0; i < kBV; i += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(src + i);
+      srow[i] = t.x; srow[i + 1] = t.y; srow[i + 2] = t.z; srow[i + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kBV; ++i) srow[i] = 0.f;
+  }
+  __syncthreads();  // gam_s[0] visible
+
+  for (int c = 0; c < sq.nt; ++c) {
+    const int cur = c & 1;
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+    const float gam_last = gam_s[cur][rows - 1];
+
+    // ---- stage 0: publish the state at chunk start (split copy for the MMAs, pre-decayed master in TMEM)
+    row64_to_hilo(smem + kOffSH, smem + kOffSL, row, srow);
+    if (p.s_hi) {
+      const int64_t off = (((int64_t(sq.cbase) + c) * p.HV + hv) * kK + row) * kV + vb * kBV;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 hi, lo;
+        split8(srow + ch * 8, hi, lo);
+        *reinterpret_cast<uint4*>(p.s_hi + off + ch * 8) = hi;
+        *reinterpret_cast<uint4*>(p.s_lo + off + ch * 8) = lo;
+      }
+    }
+    {
+      const float dl = __expf(gam_last);
+#pragma unroll
+      for (int i = 0; i < kBV; ++i) srow[i] *= dl;
+      tmem_st_row64(trow + kColS, srow);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 1: [Q;K] S (split state) and [Q;K] K^T
+    if (tid == 0) {
+      mma_tile(tbase + kColRQ, opQK, opSH, 128, 64, 8, false);
+      mma_tile(tbase + kColRQ, opQK, opSL, 128, 64, 8, true);
+      mma_tile(tbase + kColQK, opQK, opKb, 128, 64, 8, false);
+      mma_commit(&bar);
+    }
+    if (c + 1 < sq.nt) prefetch_load(c + 1);
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- stage 2: K-side rows build Z = beta (V - exp(gam) K S); Q-side rows build P = tril(QK^T * decay)
+    float acc[kBV];
+    const float gam_i = gam_s[cur][tok];
+    if (kwarp) {
+      tmem_ld_row64(trow + kColRQ, acc);
+      const float eg = __expf(gam_i), bi = beta_s[cur][tok];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float vv[8];
+        unpack_bf16x8(vcur[i], vv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i * 8 + j] = bi * (vv[j] - eg * acc[i * 8 + j]);
+      }
+      row64_to_hilo(smem + kOffZH, smem + kOffZL, tok, acc);
+    } else {
+      tmem_ld_row64(trow + kColQK, acc);
+#pragma unroll
+      for (int j = 0; j < kC; ++j) acc[j] = (j <= tok) ? acc[j] * __expf(gam_i - gam_s[cur][j]) : 0.f;
+      row64_to_hilo(smem + kOffQK, smem + kOffQK + kQKPanel, tok, acc);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 3: v_new = X Z  (rows 64..127 of the accumulator)
+    if (tid == 0) {
+      mma_tile(tbase + kColVN, opX, opZH, 128, 64, 4, false);
+      mma_tile(tbase + kColVN, opX, opZL, 128, 64, 4, true);
+      mma_commit(&bar);
+    }
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- stage 4: K-side rows publish v_new and its decayed copy
+    if (kwarp) {
+      tmem_ld_row64(trow + kColVN, acc);
+      row64_to_hilo(smem + kOffZH, smem + kOffZL, tok, acc);
+      if (p.vn_hi && tok < rows) {
+        const int64_t off = ((tok0 + tok) * p.HV + hv) * kV + vb * kBV;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4 hi, lo;
+          split8(acc + ch * 8, hi, lo);
+          *reinterpret_cast<uint4*>(p.vn_hi + off + ch * 8) = hi;
+          *reinterpret_cast<uint4*>(p.vn_lo + off + ch * 8) = lo;
+        }
+      }
+      const float dk = __expf(gam_last - gam_i);
+#pragma unroll
+      for (int i = 0; i < kBV; ++i) acc[i] *= dk;
+      row64_to_hilo(smem + kOffVH, smem + kOffVL, tok, acc);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 5: P v_new (three passes) and the state update S += K^T vhat
+    if (tid == 0) {
+      mma_tile(tbase + kColQK, opPH, opZH, 128, 64, 4, false);
+      mma_tile(tbase + kColQK, opPH, opZL, 128, 64, 4, true);
+      mma_tile(tbase + kColQK, opPL, opZH, 128, 64, 4, true);
+      mma_tile(tbase + kColS, opKT, opVH, 128, 64, 4, true);
+      mma_tile(tbase + kColS, opKT, opVL, 128, 64, 4, true);
+      mma_commit(&bar);
+    }
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- stage 6: output rows, next state, next chunk's operands
+    if (!kwarp) {
+      const float eg = __expf(gam_i) * p.scale;
+      const int64_t off = (tok0 + tok) * p.o_st + hv * p.o_sh + vb * kBV;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float qs[32], pv[32];
+        tmem_ld32(trow + kColRQ + half * 32, qs);
+        tmem_ld32(trow + kColQK + half * 32, pv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pv[i] = eg * qs[i] + p.scale * pv[i];
+        if (tok < rows) {
+          if (p.o_is_f32) {
+            float* dst = static_cast<float*>(p.o) + off + half * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(pv[i], pv[i + 1], pv[i + 2], pv[i + 3]);
+          } else {
+            bf16* dst = static_cast<bf16*>(p.o) + off + half * 32;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(pv + ch * 8);
+          }
+        }
+      }
+    }
+    tmem_ld_row64(trow + kColS, srow);
+    if (c + 1 < sq.nt) prefetch_store(c + 1);
+    tc_fence_before();
+    __syncthreads();  // next chunk's gam_s / beta_s visible; all TMEM reads of this chunk retired
+  }
+
+  if (ok && p.ht) {
+    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+#pragma unroll
+    for (int i = 0; i < kBV; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+}  // namespace fla
+
+using namespace fla;
+
+static int check_token_tensor(const fla_tensor_t& t, int64_t heads, int64_t dim, int dtype_a, int dtype_b) {
+  // [B, T, H, D] with D contiguous, rows 16-byte aligned, and batch rows laid out back to back
+  if (!t.data) return FLA_ERR_NULL;
+  if (t.ndim != 4 || t.shape[2] != heads || t.shape[3] != dim) return FLA_ERR_SHAPE;
+  if (t.dtype != dtype_a && t.dtype != dtype_b) return FLA_ERR_DTYPE;
+  const int64_t esz = t.dtype == FLA_F32 ? 4 : 2;
+  if (t.stride[3] != 1 || (t.stride[2] * esz) % 16 || (t.stride[1] * esz) % 16 || !aligned16(t.data)) return FLA_ERR_LAYOUT;
+  if (t.shape[0] > 1 && t.stride[0] != t.shape[1] * t.stride[1]) return FLA_ERR_LAYOUT;
+  return FLA_OK;
+}
+static int check_gate_tensor(const fla_tensor_t& t, int64_t B, int64_t T, int64_t heads) {
+  if (!t.data) return FLA_ERR_NULL;
+  if (t.ndim != 3 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != heads) return FLA_ERR_SHAPE;
+  if (t.dtype != FLA_F32 && t.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (t.stride[2] != 1 || (B > 1 && t.stride[0] != T * t.stride[1])) return FLA_ERR_LAYOUT;
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_gdn_chunk_fwd_workspace_size(const fla_gdn_chunk_fwd_args* a, uint64_t* bytes) {
+  if (!a || !bytes) return FLA_ERR_NULL;
+  *bytes = 256;  // device status word
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, void* workspace, uint64_t workspace_bytes,
+                                              void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  if (!workspace || workspace_bytes < 256) return FLA_ERR_WORKSPACE;
+  const fla_tensor_t &q = a->q, &k = a->k, &v = a->v, &o = a->o;
+  if (!q.data || !k.data || !v.data || !o.data) return FLA_ERR_NULL;
+  if (q.ndim != 4 || v.ndim != 4) return FLA_ERR_SHAPE;
+  const int64_t B = q.shape[0], T = q.shape[1], HK = q.shape[2], HV = v.shape[2];
+  if (B <= 0 || T <= 0 || HK <= 0 || HV <= 0 || HV % HK || v.shape[0] != B || v.shape[1] != T) return FLA_ERR_SHAPE;
+  int st;
+  if ((st = check_token_tensor(q, HK, kK, FLA_BF16, FLA_BF16))) return st;
+  if ((st = check_token_tensor(k, HK, kK, FLA_BF16, FLA_BF16))) return st;
+  if ((st = check_token_tensor(v, HV, kV, FLA_BF16, FLA_BF16))) return st;
+  if ((st = check_token_tensor(o, HV, kV, FLA_BF16, FLA_F32))) return st;
+  if (k.shape[0] != B || k.shape[1] != T || o.shape[0] != B || o.shape[1] != T) return FLA_ERR_SHAPE;
+  if ((st = check_gate_tensor(a->g, B, T, HV))) return st;
+  if ((st = check_gate_tensor(a->beta, B, T, HV))) return st;
+  if (a->chunk_size != kC) return FLA_ERR_VALUE;
+  if (!(a->scale == a->scale)) return FLA_ERR_VALUE;
+
+  int N = int(B);
+  int64_t total_chunks = B * ((T + kC - 1) / kC);
+  int max_len = int(T);
+  if (a->cu_seqlens.data) {
+    if (B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    N = int(a->cu_seqlens.shape[0] - 1);
+    if (!a->chunk_offsets.data || a->chunk_offsets.dtype != FLA_I32 || a->chunk_offsets.shape[0] != N + 1) return FLA_ERR_SHAPE;
+    if (a->max_seqlen <= 0 || a->max_seqlen > T || a->total_chunks <= 0) return FLA_ERR_VALUE;
+    max_len = a->max_seqlen;
+    total_chunks = a->total_chunks;
+  }
+  const fla_tensor_t &gam = a->gam, &X = a->x_inv;
+  if (!gam.data || !X.data) return FLA_ERR_NULL;
+  if (gam.dtype != FLA_F32 || gam.ndim != 3 || gam.shape[0] != B || gam.shape[1] != T || gam.shape[2] != HV ||
+      gam.stride[2] != 1 || gam.stride[1] != HV || (B > 1 && gam.stride[0] != T * HV))
+    return FLA_ERR_SHAPE;
+  if (X.dtype != FLA_BF16 || X.ndim != 4 || X.shape[0] != B || X.shape[1] != T || X.shape[2] != HV || X.shape[3] != kC ||
+      X.stride[3] != 1 || X.stride[2] != kC || X.stride[1] != HV * kC || !aligned16(X.data))
+    return FLA_ERR_SHAPE;
+  for (const fla_tensor_t* s : {&a->initial_state, &a->final_state}) {
+    if (!s->data) continue;
+    if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
+    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != HV * kK * kV || !aligned16(s->data))
+      return FLA_ERR_LAYOUT;
+  }
+  GdnFwdParams p{};
+  p.q = static_cast<const bf16*>(q.data); p.k = static_cast<const bf16*>(k.data); p.v = static_cast<const bf16*>(v.data);
+  p.g = a->g.data; p.beta = a->beta.data;
+  p.gam = static_cast<float*>(gam.data); p.X = static_cast<bf16*>(X.data);
+  p.h0 = static_cast<const float*>(a->initial_state.data); p.ht = static_cast<float*>(a->final_state.data);
+  p.o = o.data;
+  if (a->s_hi.data || a->s_lo.data || a->vn_hi.data || a->vn_lo.data) {
+    const fla_tensor_t &sh = a->s_hi, &sl = a->s_lo, &vh = a->vn_hi, &vl = a->vn_lo;
+    if (!sh.data || !sl.data || !vh.data || !vl.data) return FLA_ERR_NULL;
+    for (const fla_tensor_t* s : {&sh, &sl}) {
+      if (s->dtype != FLA_BF16 || s->ndim != 4 || s->shape[0] != total_chunks || s->shape[1] != HV || s->shape[2] != kK ||
+          s->shape[3] != kV || s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV ||
+          s->stride[0] != HV * kK * kV || !aligned16(s->data))
+        return FLA_ERR_SHAPE;
+    }
+    for (const fla_tensor_t* s : {&vh, &vl}) {
+      if (s->dtype != FLA_BF16 || s->ndim != 4 || s->shape[0] != B || s->shape[1] != T || s->shape[2] != HV ||
+          s->shape[3] != kV || s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != HV * kV || !aligned16(s->data))
+        return FLA_ERR_SHAPE;
+    }
+    p.s_hi = static_cast<bf16*>(sh.data); p.s_lo = static_cast<bf16*>(sl.data);
+    p.vn_hi = static_cast<bf16*>(vh.data); p.vn_lo = static_cast<bf16*>(vl.data);
+  }
+  p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+  p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
+  p.q_st = q.stride[1]; p.q_sh = q.stride[2]; p.k_st = k.stride[1]; p.k_sh = k.stride[2];
+  p.v_st = v.stride[1]; p.v_sh = v.stride[2]; p.o_st = o.stride[1]; p.o_sh = o.stride[2];
+  p.g_st = a->g.stride[1]; p.beta_st = a->beta.stride[1];
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV);
+  p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = a->beta.dtype == FLA_F32; p.o_is_f32 = o.dtype == FLA_F32;
+  p.scale = a->scale;
+  p.status = static_cast<int*>(workspace);
+
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
+  const int prep_smem = 16384 + (3 * kC * kAStride + 4 * kC) * 4 + 1024;
+  static bool attr_done_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  bool& attr_done = attr_done_dev[dev];
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prep_smem) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(gdn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    attr_done = true;
+  }
+  const int nt_max = (max_len + kC - 1) / kC;
+  gdn_prep_kernel<<<dim3(nt_max, unsigned(HK), N), 128, prep_smem, cs>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), 128, kFwdSmem + 1024, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}

@@ -1,0 +1,81 @@
+// Shared pieces of the chunked GDN kernels: parameter block, sequence/chunk geometry and small
+// row-wise helpers for moving fp32 accumulator rows between TMEM, registers and operand panels.
+#pragma once
+#include "common/sm100.cuh"
+
+namespace fla {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int kC = 64;     // chunk length (tokens)
+constexpr int kK = 128;    // key head dim
+constexpr int kV = 128;    // value head dim
+constexpr int kBV = 64;    // value columns owned by one CTA of the sequential kernels
+
+struct SeqInfo {
+  int bos;   // first token (flat index) of the sequence
+  int len;   // tokens in the sequence
+  int nt;    // chunks in the sequence
+  int cbase; // flat index of the sequence's first chunk (for per-chunk saved tensors)
+};
+
+// cu_seqlens == nullptr: sequence n is batch row n with T tokens.
+__device__ __forceinline__ SeqInfo seq_info(const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n, int T) {
+  SeqInfo s;
+  if (cu_seqlens) {
+    s.bos = cu_seqlens[n];
+    s.len = cu_seqlens[n + 1] - s.bos;
+    s.cbase = chunk_offsets[n];
+  } else {
+    s.bos = n * T;
+    s.len = T;
+    s.cbase = n * ((T + kC - 1) / kC);
+  }
+  s.nt = (s.len + kC - 1) / kC;
+  return s;
+}
+
+__device__ __forceinline__ float ld_scalar(const void* p, int64_t idx, int is_f32) {
+  return is_f32 ? static_cast<const float*>(p)[idx] : __bfloat162float(static_cast<const bf16*>(p)[idx]);
+}
+
+// Load 64 consecutive fp32 accumulator columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld_row64(uint32_t taddr, float* v) {
+  tmem_ld32(taddr, v);
+  tmem_ld32(taddr + 32, v + 32);
+  tmem_ld_wait();
+}
+__device__ __forceinline__ void tmem_st_row64(uint32_t taddr, const float* v) {
+  tmem_st16(taddr, v);
+  tmem_st16(taddr + 16, v + 16);
+  tmem_st16(taddr + 32, v + 32);
+  tmem_st16(taddr + 48, v + 48);
+  tmem_st_wait();
+}
+
+// Write a 64-wide fp32 row as bf16 hi / lo residual rows of two panels.
+__device__ __forceinline__ void row64_to_hilo(uint8_t* pan_hi, uint8_t* pan_lo, int row, const float* x) {
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    uint4 hi, lo;
+    split8(x + ch * 8, hi, lo);
+    const uint32_t off = panel_chunk_off(row, ch);
+    *reinterpret_cast<uint4*>(pan_hi + off) = hi;
+    *reinterpret_cast<uint4*>(pan_lo + off) = lo;
+  }
+}
+__device__ __forceinline__ void row64_to_bf16(uint8_t* pan, int row, const float* x) {
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(pan + panel_chunk_off(row, ch)) = pack8(x + ch * 8);
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __low2float(h[i]);
+    f[2 * i + 1] = __high2float(h[i]);
+  }
+}
+
+}  // namespace fla

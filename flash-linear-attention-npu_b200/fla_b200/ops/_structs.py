@@ -20,3 +20,11 @@ class CausalConv1dUpdateArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("x", "weight", "bias", "residual", "conv_state", "y", "cache_indices",
                                            "num_accepted_tokens")] + [
         ("activation_silu", ctypes.c_int32), ("pad_slot_id", ctypes.c_int32)]
+
+
+class GdnChunkFwdArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "g", "beta", "initial_state", "o", "final_state", "gam",
+                                           "x_inv", "s_hi", "s_lo", "vn_hi", "vn_lo", "cu_seqlens",
+                                           "chunk_offsets")] + [
+        ("scale", ctypes.c_float), ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32),
+        ("total_chunks", ctypes.c_int32)]

@@ -133,6 +133,36 @@ FLA_API int fla_b200_causal_conv1d_update_workspace_size(const fla_causal_conv1d
 FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* args, void* workspace,
                                           uint64_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Chunked gated delta rule, forward (chunk = 64, K = V = 128).
+ * Replaces the reference's forward chain chunk_local_cumsum -> chunk_scaled_dot_kkt -> solve_tri ->
+ * recompute_w_u_fwd -> chunk_gated_delta_rule_fwd_h -> chunk_fwd_o as composed by
+ * flash_chunk_gated_delta_rule_fwd (examples/flash_gated_delta_rule.py:796-881; per-op bindings
+ * torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:875-936, 1786-1800, 618-651, 552-615, 517-549).
+ *   q, k [B, T, HK, 128] bf16;  v [B, T, HV, 128] bf16;  g, beta [B, T, HV] f32|bf16 (g = log decay per token)
+ *   o [B, T, HV, 128] bf16|f32
+ *   initial_state / final_state [N, HV, 128(K), 128(V)] f32, optional
+ *   gam   [B, T, HV] f32      out: chunk-local cumulative sum of g      (saved for backward)
+ *   x_inv [B, T, HV, 64] bf16 out: rows of (I + strict_tril(beta_i exp(gam_i-gam_j) k_i.k_j))^-1 per chunk
+ *   s_hi, s_lo  [chunks, HV, 128, 128] bf16, optional out: state at each chunk start as hi + lo (for backward)
+ *   vn_hi, vn_lo [B, T, HV, 128] bf16, optional out: v_new as hi + lo (for backward)
+ *   cu_seqlens int32 [N+1] device (requires B == 1) with chunk_offsets int32 [N+1] device (prefix sum of
+ *   ceil(len/64)), max_seqlen and total_chunks given by the host.  All four are ignored for dense batches.
+ * Token tensors need a contiguous last dim, 16-byte aligned rows and batch rows laid out back to back.
+ * Workspace: a 256-byte status block (first int32 becomes FLA_ERR_TIMEOUT if a device-side wait ran out). */
+typedef struct fla_gdn_chunk_fwd_args {
+  fla_tensor_t q, k, v, g, beta, initial_state;
+  fla_tensor_t o, final_state, gam, x_inv, s_hi, s_lo, vn_hi, vn_lo;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  float scale;
+  int32_t chunk_size;
+  int32_t max_seqlen;
+  int32_t total_chunks;
+} fla_gdn_chunk_fwd_args;
+FLA_API int fla_b200_gdn_chunk_fwd_workspace_size(const fla_gdn_chunk_fwd_args* args, uint64_t* bytes);
+FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* args, void* workspace, uint64_t workspace_bytes,
+                                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,63 @@
+"""Parity of the chunked GDN forward with the naive fp32/fp64 recurrent oracle (through the C ABI).
+
+Bar: max-abs-err / RMS(ref) <= 5e-3 for o (checked on fp32 output; the bf16 output additionally gets
+the half-ulp allowance of its final rounding) and for the fp32 final state.
+"""
+import pytest
+import torch
+
+import oracle
+from _util import assert_close, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 5e-3
+
+
+def _run(B, T, HK, HV, seed, h0=True, cu=None, out_dtype=torch.float32):
+    from fla_b200.ops import chunk_gated_delta_rule
+    inp = oracle.make_gdn_inputs(B, T, HK, HV, seed=seed, h0_scale=0.1 if h0 else 0.0, with_grad=False)
+    N = B if cu is None else len(cu) - 1
+    if h0 and cu is not None:
+        inp["h0"] = (0.1 * torch.randn(N, HV, 128, 128, generator=torch.Generator().manual_seed(seed))).float()
+    ref = oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"],
+                                       dtype=torch.float64, cu_seqlens=cu)
+    d = {n: (t.cuda() if t is not None else None) for n, t in inp.items()}
+    o, ht = chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
+                                   output_final_state=True, output_dtype=out_dtype,
+                                   cu_seqlens=None if cu is None else torch.tensor(cu, dtype=torch.int32))
+    torch.cuda.synchronize()
+    return o, ht, ref
+
+
+@pytest.mark.parametrize("B,T,HK,HV", [(1, 64, 1, 1), (1, 128, 1, 2), (2, 256, 2, 4), (1, 1024, 2, 2)])
+def test_forward_fp32_output(B, T, HK, HV):
+    o, ht, ref = _run(B, T, HK, HV, seed=1000 + T)
+    assert_close("o", o, ref["o"], TOL)
+    assert_close("final_state", ht, ref["ht"], TOL)
+
+
+@pytest.mark.parametrize("T", [1, 15, 63, 65, 127, 200])
+def test_forward_ragged_lengths(T):
+    o, ht, ref = _run(1, T, 1, 2, seed=7 + T)
+    assert_close("o", o, ref["o"], TOL)
+    assert_close("final_state", ht, ref["ht"], TOL)
+
+
+def test_forward_bf16_output_and_zero_state():
+    o, ht, ref = _run(2, 192, 2, 4, seed=5, h0=False, out_dtype=torch.bfloat16)
+    assert o.dtype == torch.bfloat16
+    assert_close("o", o, ref["o"], TOL, stored_bf16=True)
+    assert_close("final_state", ht, ref["ht"], TOL)
+
+
+def test_forward_varlen_packed():
+    cu = [0, 70, 71, 199, 263, 300]
+    o, ht, ref = _run(1, 300, 2, 4, seed=11, cu=cu)
+    assert_close("o", o, ref["o"], TOL)
+    assert_close("final_state", ht, ref["ht"], TOL)
+
+
+def test_forward_is_deterministic():
+    o1, h1, _ = _run(1, 256, 2, 4, seed=3)
+    o2, h2, _ = _run(1, 256, 2, 4, seed=3)
+    assert torch.equal(o1, o2) and torch.equal(h1, h2)
