@@ -8,6 +8,7 @@
 // (fla/ops/ascendc/gdn/gdn_preprocess/causal_conv1d/op_kernel/causal_conv1d.h, causal_conv1d_update.h).
 #include <cuda_bf16.h>
 #include "fla_b200_internal.h"
+#include "kernel_timer.h"
 
 namespace fla {
 
@@ -58,8 +59,8 @@ constexpr int kConvTile = 64;     // tokens per CTA tile
 constexpr int kConvGroup = 8;     // tokens loaded together (independent 16-byte loads in flight)
 constexpr int kConvThreads = 128;
 
-template <int W>
-__global__ void __launch_bounds__(kConvThreads) conv_fwd_kernel(ConvFwdParams p) {
+template <int W, bool HAS_RES>
+__global__ void __launch_bounds__(kConvThreads, 4) conv_fwd_kernel(ConvFwdParams p) {
   const int d0 = (blockIdx.x * kConvThreads + threadIdx.x) * 8;
   if (d0 >= p.D) return;
   const int b = blockIdx.z;
@@ -90,79 +91,77 @@ __global__ void __launch_bounds__(kConvThreads) conv_fwd_kernel(ConvFwdParams p)
 
   const bf16* xb = p.x + b * p.x_sb + d0;
   bf16* yb = p.y + b * p.y_sb + d0;
-  const bf16* rb = p.residual ? p.residual + b * p.r_sb + d0 : nullptr;
+  const bf16* rb = HAS_RES ? p.residual + b * p.r_sb + d0 : nullptr;
 
   // hist[j-1] = input at (t - j), j = 1..W-1
   float hist[W - 1][8];
-  auto load_hist = [&](int t, int sq, int sq_begin) {
+  int t = t_begin;
+  while (t < t_end) {
+    if (p.cu_seqlens) {
+      while (seq_end <= t) {  // step over sequences that end at or before t (also skips empty ones)
+        ++seq;
+        seq_begin = seq_end;
+        seq_end = p.cu_seqlens[seq + 1];
+      }
+    }
+    const int seg_end = min(t_end, seq_end);
 #pragma unroll
     for (int j = 1; j < W; ++j) {
       const int pos = t - j;
-      if (pos >= sq_begin) {
+      if (pos >= seq_begin) {
         unpack8(*reinterpret_cast<const uint4*>(xb + pos * p.x_st), hist[j - 1]);
       } else {
-        const int si = (W - 1) + (pos - sq_begin);  // index into the W-1 stored inputs
+        const int si = (W - 1) + (pos - seq_begin);  // index into the W-1 stored inputs
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-          hist[j - 1][c] = (p.init && si >= 0)
-                               ? __bfloat162float(p.init[sq * p.i_sn + (d0 + c) * p.i_sd + si * p.i_sw])
-                               : 0.f;
+          hist[j - 1][c] = (p.init && si >= 0) ? __bfloat162float(p.init[seq * p.i_sn + (d0 + c) * p.i_sd + si * p.i_sw]) : 0.f;
       }
     }
-  };
-  load_hist(t_begin, seq, seq_begin);
-
-  for (int tg = t_begin; tg < t_end; tg += kConvGroup) {
-    uint4 xin[kConvGroup], rin[kConvGroup];
+    for (int tg = t; tg < seg_end; tg += kConvGroup) {
+      uint4 xin[kConvGroup], rin[HAS_RES ? kConvGroup : 1];
 #pragma unroll
-    for (int i = 0; i < kConvGroup; ++i) {
-      const int t = tg + i;
-      xin[i] = (t < t_end) ? *reinterpret_cast<const uint4*>(xb + t * p.x_st) : make_uint4(0, 0, 0, 0);
-      if (rb) rin[i] = (t < t_end) ? *reinterpret_cast<const uint4*>(rb + t * p.r_st) : make_uint4(0, 0, 0, 0);
-    }
+      for (int i = 0; i < kConvGroup; ++i) {
+        const int tt = tg + i;
+        xin[i] = (tt < seg_end) ? *reinterpret_cast<const uint4*>(xb + tt * p.x_st) : make_uint4(0, 0, 0, 0);
+        if constexpr (HAS_RES) rin[i] = (tt < seg_end) ? *reinterpret_cast<const uint4*>(rb + tt * p.r_st) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-    for (int i = 0; i < kConvGroup; ++i) {
-      const int t = tg + i;
-      if (t >= t_end) break;
-      if (p.cu_seqlens && t >= seq_end) {  // crossed into the next sequence: restart its history
-        while (t >= seq_end) {
-          ++seq;
-          seq_begin = seq_end;
-          seq_end = p.cu_seqlens[seq + 1];
+      for (int i = 0; i < kConvGroup; ++i) {
+        const int tt = tg + i;
+        if (tt < seg_end) {
+          float xv[8], acc[8];
+          unpack8(xin[i], xv);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float a = bias[c] + w[W - 1][c] * xv[c];
+#pragma unroll
+            for (int j = 1; j < W; ++j) a += w[W - 1 - j][c] * hist[j - 1][c];
+            acc[c] = p.silu ? silu(a) : a;
+          }
+          if constexpr (HAS_RES) {
+            float rv[8];
+            unpack8(rin[i], rv);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[c] += rv[c];
+          }
+          *reinterpret_cast<uint4*>(yb + tt * p.y_st) = pack8f(acc);
+#pragma unroll
+          for (int j = W - 1; j > 1; --j)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) hist[j - 1][c] = hist[j - 2][c];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) hist[0][c] = xv[c];
         }
-        load_hist(t, seq, seq_begin);
-      }
-      float xv[8], acc[8];
-      unpack8(xin[i], xv);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float a = bias[c] + w[W - 1][c] * xv[c];
-#pragma unroll
-        for (int j = 1; j < W; ++j) a += w[W - 1 - j][c] * hist[j - 1][c];
-        acc[c] = p.silu ? silu(a) : a;
-      }
-      if (rb) {
-        float rv[8];
-        unpack8(rin[i], rv);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) acc[c] += rv[c];
-      }
-      *reinterpret_cast<uint4*>(yb + t * p.y_st) = pack8f(acc);
-      // shift history
-#pragma unroll
-      for (int j = W - 1; j > 1; --j)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) hist[j - 1][c] = hist[j - 2][c];
-#pragma unroll
-      for (int c = 0; c < 8; ++c) hist[0][c] = xv[c];
-      if (p.final_state && t == seq_end - 1) {  // last token of a sequence: its last W-1 inputs are the state
-#pragma unroll
-        for (int j = 1; j < W; ++j)
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            p.final_state[seq * p.f_sn + (d0 + c) * p.f_sd + (W - 1 - j) * p.f_sw] = __float2bfloat16_rn(hist[j - 1][c]);
       }
     }
+    if (p.final_state && seg_end == seq_end) {  // the sequence ended in this tile: its last W-1 inputs are the state
+#pragma unroll
+      for (int j = 1; j < W; ++j)
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          p.final_state[seq * p.f_sn + (d0 + c) * p.f_sd + (W - 1 - j) * p.f_sw] = __float2bfloat16_rn(hist[j - 1][c]);
+    }
+    t = seg_end;
   }
 }
 
@@ -347,9 +346,12 @@ extern "C" FLA_API int fla_b200_causal_conv1d_fwd(const fla_causal_conv1d_fwd_ar
   if (T == 0) return FLA_OK;
   const dim3 grid(unsigned((D / 8 + kConvThreads - 1) / kConvThreads), unsigned((T + kConvTile - 1) / kConvTile), unsigned(B));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (W == 4) conv_fwd_kernel<4><<<grid, kConvThreads, 0, st>>>(p);
-  else if (W == 3) conv_fwd_kernel<3><<<grid, kConvThreads, 0, st>>>(p);
-  else conv_fwd_kernel<2><<<grid, kConvThreads, 0, st>>>(p);
+  KernelTimer kt("causal_conv1d_fwd", st);
+#define FLA_LAUNCH_FWD(WW)                                                        \
+  if (p.residual) conv_fwd_kernel<WW, true><<<grid, kConvThreads, 0, st>>>(p);  \
+  else conv_fwd_kernel<WW, false><<<grid, kConvThreads, 0, st>>>(p);
+  if (W == 4) { FLA_LAUNCH_FWD(4) } else if (W == 3) { FLA_LAUNCH_FWD(3) } else { FLA_LAUNCH_FWD(2) }
+#undef FLA_LAUNCH_FWD
   return cuda_status(cudaGetLastError());
 }
 
@@ -405,6 +407,7 @@ extern "C" FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_upd
   p.silu = a->activation_silu; p.pad_slot_id = a->pad_slot_id;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
+  KernelTimer kt("causal_conv1d_update", st);
   const bool w_ok = w.stride[0] != 1 || (aligned16(w.data) && w.stride[1] % 8 == 0);
   const bool dmajor = s.stride[1] == 1 && s.stride[2] % 8 == 0 && s.stride[0] % 8 == 0 && aligned16(s.data);
   const bool smajor = s.stride[2] == 1 && s.stride[1] == S && s.stride[0] % 8 == 0 && aligned16(s.data);

@@ -21,6 +21,7 @@
 // ignored) so that TMEM lane == accumulator row for every tile.
 #include "gdn_common.cuh"
 #include "fla_b200_internal.h"
+#include "kernel_timer.h"
 
 namespace fla {
 
@@ -47,10 +48,12 @@ constexpr int kAStride = 68;  // fp32 row stride of the 64x64 score tiles in sha
 __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* k_pan = smem;                                        // 2 panels x 64 rows
-  float* kk_s = reinterpret_cast<float*>(smem + 16384);          // [64][68]
-  float* a_s = kk_s + kC * kAStride;                             // [2][64][68]
-  float* g_s = a_s + 2 * kC * kAStride;                          // [2][64] raw g, then gam
+  constexpr int kTile = kC * kAStride * 4;                       // bytes of one fp32 64x64 tile (padded rows)
+  uint8_t* k_pan = smem;                                        // 2 panels x 64 rows; dead after the MMA
+  float* at1 = reinterpret_cast<float*>(smem);                   // A^T of the second head (reuses the k panels)
+  float* kk_s = reinterpret_cast<float*>(smem + kTile);          // [64][68]  K K^T
+  float* at0 = reinterpret_cast<float*>(smem + 2 * kTile);       // A^T of the first head
+  float* g_s = reinterpret_cast<float*>(smem + 3 * kTile);       // [2][64] raw g, then gam
   float* b_s = g_s + 2 * kC;                                     // [2][64]
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t bar;
@@ -109,7 +112,7 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
 
   const int G = p.HV / p.HK;
   const int hsel = tid / 64, c = tid % 64;
-  float* A = a_s + hsel * kC * kAStride;
+  float* AT = hsel ? at1 : at0;                                  // AT[j][i] = A[i][j]
   float* gs = g_s + hsel * kC;
   float* bs = b_s + hsel * kC;
   for (int h0 = 0; h0 < G; h0 += 2) {
@@ -132,25 +135,33 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
     }
     __syncthreads();
     if (active) {
-      // column c of A (rows below the diagonal)
-      for (int i = c + 1; i < kC; ++i) A[i * kAStride + c] = bs[i] * __expf(gs[i] - gam) * kk_s[i * kAStride + c];
+      // row c of A^T, i.e. column c of A below the diagonal: A[i][c] = beta_i exp(gam_i - gam_c) (k_i . k_c)
+      for (int i = c + 1; i < kC; ++i) AT[c * kAStride + i] = bs[i] * __expf(gs[i] - gam) * kk_s[i * kAStride + c];
     }
     __syncthreads();
     if (active) {
-      // thread c solves column c of X = (I + A)^-1 by forward substitution: x_i = [i == c] - sum_{j<i} A_ij x_j
+      // Thread c solves column c of X = (I + A)^-1 by right-looking forward substitution:
+      //   r = e_c;  for j: x_j = r_j;  r_i -= A[i][j] x_j  (i > j).
+      // The updates of one step are independent, so the FMA pipeline stays full.  Entries above the
+      // column's diagonal are zero, so a warp skips the steps before its first column.
       float x[kC];
 #pragma unroll
-      for (int i = 0; i < kC; ++i) {
-        float acc = (i == c) ? 1.f : 0.f;
+      for (int i = 0; i < kC; ++i) x[i] = (i == c) ? 1.f : 0.f;
+      const int jmin = c & ~31;  // warp-uniform
 #pragma unroll
-        for (int j4 = 0; j4 < i; j4 += 4) {
-          const float4 a4 = *reinterpret_cast<const float4*>(A + i * kAStride + j4);
-          acc -= a4.x * x[j4];
-          if (j4 + 1 < i) acc -= a4.y * x[j4 + 1];
-          if (j4 + 2 < i) acc -= a4.z * x[j4 + 2];
-          if (j4 + 3 < i) acc -= a4.w * x[j4 + 3];
+      for (int j = 0; j < kC - 1; ++j) {
+        if (j >= jmin) {
+          const float xj = x[j];
+          const float* col = AT + j * kAStride;
+#pragma unroll
+          for (int i4 = (j + 1) & ~3; i4 < kC; i4 += 4) {
+            const float4 a4 = *reinterpret_cast<const float4*>(col + i4);
+            if (i4 > j) x[i4] -= a4.x * xj;
+            if (i4 + 1 > j) x[i4 + 1] -= a4.y * xj;
+            if (i4 + 2 > j) x[i4 + 2] -= a4.z * xj;
+            if (i4 + 3 > j) x[i4 + 3] -= a4.w * xj;
+          }
         }
-        x[i] = acc;
       }
       bf16* xg = p.X + ((tok0 * p.HV + hv) * kC) + c;
 #pragma unroll
@@ -560,7 +571,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
-  const int prep_smem = 16384 + (3 * kC * kAStride + 4 * kC) * 4 + 1024;
+  const int prep_smem = (3 * kC * kAStride + 4 * kC) * 4 + 1024;
   static bool attr_done_dev[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
@@ -571,8 +582,14 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
     attr_done = true;
   }
   const int nt_max = (max_len + kC - 1) / kC;
-  gdn_prep_kernel<<<dim3(nt_max, unsigned(HK), N), 128, prep_smem, cs>>>(p);
+  {
+    KernelTimer kt("gdn_prep", cs);
+    gdn_prep_kernel<<<dim3(nt_max, unsigned(HK), N), 128, prep_smem, cs>>>(p);
+  }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
-  gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), 128, kFwdSmem + 1024, cs>>>(p);
+  {
+    KernelTimer kt("gdn_fwd", cs);
+    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), 128, kFwdSmem + 1024, cs>>>(p);
+  }
   return cuda_status(cudaGetLastError());
 }

@@ -9,6 +9,7 @@
 // (fla/ops/ascendc/gdn/recurrent_gdn/recurrent_gated_delta_rule/op_kernel/recurrent_gated_delta_rule.h:159-199,364-402,445-513).
 #include <cuda_bf16.h>
 #include "fla_b200_internal.h"
+#include "kernel_timer.h"
 
 namespace fla {
 
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
 template <int K, int V>
 int launch_recurrent(const RecurrentParams& p, int nseq, bool state_f32, bool vfirst, cudaStream_t st) {
   const dim3 grid(nseq * p.HV), block(kRecThreads);
+  KernelTimer kt("recurrent_gdn", st);
   if (state_f32) {
     if (vfirst) recurrent_gdn_kernel<K, V, float, true><<<grid, block, 0, st>>>(p);
     else recurrent_gdn_kernel<K, V, float, false><<<grid, block, 0, st>>>(p);

@@ -55,6 +55,15 @@ typedef struct fla_tensor {
 /* Library version (major * 10000 + minor * 100 + patch). */
 FLA_API int fla_b200_version(void);
 
+/* Optional per-kernel device timing (no reference counterpart; the reference relies on an external
+ * profiler).  While enabled, every kernel launch of the library is bracketed by CUDA events on the
+ * launching stream.  Enabling or disabling clears earlier records.  kernel_timing_read synchronises the
+ * recorded events and returns the summed duration and the number of launches of `kernel_name`
+ * (names: "gdn_prep", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par", "recurrent_gdn", "causal_conv1d_fwd",
+ * "causal_conv1d_update"). */
+FLA_API int fla_b200_kernel_timing_enable(int enable);
+FLA_API int fla_b200_kernel_timing_read(const char* kernel_name, float* total_ms, int* launches);
+
 /* Hardware self-test of the tcgen05 tile-GEMM building block (no reference counterpart; it exists
  * because the kernels below stage every tensor-core operand through the same descriptors).
  * Computes D[M x N] (+)= A * B^T-or-B with bf16 operands read from row-major device buffers and
