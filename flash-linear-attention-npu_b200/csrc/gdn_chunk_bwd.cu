@@ -1,0 +1,811 @@
+// Chunked gated-delta-rule backward (chunk = 64, K = V = 128) as two kernels.
+//
+// With per chunk  gam = cumsum(g),  P = tril(Q K^T * e^{gam_i-gam_j}),  X = (I + strict_tril(beta_i e^{gam_i-gam_j} k_i.k_j))^-1,
+// S = state at chunk start, Vn = v_new (both saved by the forward as split bf16 panel images) and dS' the state
+// gradient entering the chunk from the right:
+//
+//  gdn_bwd_dhu_kernel  (reverse-sequential over chunks, one CTA per (sequence, value head, 64-column block of V)):
+//      dVn = scale P^T dO + e^{gam_L-gam} * (K dS')          dZ = X^T dVn          dV = beta * dZ
+//      dS  = e^{gam_L} dS' + (scale e^{gam} * Q)^T dO - K^T (beta e^{gam} * dZ)     dh0 = dS after the first chunk
+//      saves dS' and [dO; dZ] as panel images and the partial row sums  sum_v dZ*V  for the second kernel.
+//      Replaces chunk_bwd_dv_local + chunk_gated_delta_rule_bwd_dhu of the reference
+//      (examples/flash_gated_delta_rule.py:930-960) and the dv / du parts of prepare_wy_repr_bwd_*.
+//  gdn_bwd_par_kernel  (parallel over chunks, one CTA per (chunk, q/k head), looping over the value heads of the group):
+//      dP  = scale tril(dO Vn^T * e^{gam_i-gam_j})            dA = -strict_tril(dZ Vn^T)       dAt = dA * beta_i e^{gam_i-gam_j}
+//      dq  = scale e^{gam} * (dO S^T) + dP K
+//      dk  = dP^T Q + dAt^T K + dAt K + e^{gam_L-gam} * (Vn dS'^T) - beta e^{gam} * (dZ S^T)
+//      dbeta = sum_v dZ*V - e^{gam} k.(dZ S^T) + sum_j dA_ij e^{gam_i-gam_j} k_i.k_j
+//      dgam  = q.dq - k.dk + 2 beta (sum_j dA_ij e^{..} k_i.k_j) - 2 beta e^{gam} k.(dZ S^T);
+//      dgam_L += e^{gam_L} <S, dS'> + sum_i e^{gam_L-gam_i} k_i.(Vn dS'^T)_i;   dg = reverse chunk-local cumsum(dgam)
+//      with dq, dk summed over the value heads of a GVA group in registers (deterministic, no atomics).
+//      Replaces chunk_bwd_dqkwg + prepare_wy_repr_bwd_da + prepare_wy_repr_bwd_full + the reverse cumsum
+//      (examples/flash_gated_delta_rule.py:962-1021).
+//
+// Operands the gradients are sensitive to travel as bf16 hi + bf16 residual and are multiplied in two or three
+// tcgen05.mma passes; q, k, dO enter as the exact bf16 inputs; accumulation is fp32 in TMEM.
+#include "gdn_common.cuh"
+#include "fla_b200_internal.h"
+#include "kernel_timer.h"
+
+namespace fla {
+
+struct GdnBwdParams {
+  const bf16* q; const bf16* k; const bf16* v; const bf16* dO;
+  const void* beta;
+  const float* gam; const bf16* X;
+  const bf16* s_img; const bf16* vn_img;
+  bf16* ds_img;        // [chunks, HV, 2, 2, 128x64]  state gradient entering each chunk (hi, lo)
+  bf16* dz_img;        // [chunks, HV, 2, {128x64 hi: rows 0-63 dO, rows 64-127 dZ_hi ; 64x64 dZ_lo}]
+  float* bz;           // [2, tokens, HV] partial sums over a V block of dZ * V
+  const float* dht; float* dh0;
+  void* dq; void* dk; void* dv; void* dg; void* dbeta;
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int64_t q_st, q_sh, k_st, k_sh, v_st, v_sh, do_st, do_sh, beta_st;
+  int64_t dq_st, dq_sh, dk_st, dk_sh, dv_st, dv_sh;
+  int64_t total_tokens;
+  int N, T, HK, HV, beta_is_f32, grads_f32;
+  float scale;
+  int* status;
+};
+
+constexpr int64_t kSImg = 32768;   // bf16 elements of the state images per (chunk, head): 2 blocks x (hi, lo) x 128x64
+constexpr int64_t kVnImg = 16384;  // v_new images per (chunk, head): 2 x (hi, lo) x 64x64
+constexpr int64_t kDzImg = 24576;  // per (chunk, head): 2 x (128x64 hi + 64x64 lo)
+
+// ============================================================================================= dhu
+constexpr uint32_t hOffQK = 0, hQKPanel = 16384;
+constexpr uint32_t hOffDSH = 32768, hOffDSL = 49152;      // dS' hi / lo, later rows 0-63 scale e^gam dO, rows 64-127 -beta e^gam dZ
+constexpr uint32_t hOffDO = 65536;                         // raw dO rows of this V block
+constexpr uint32_t hOffPH = 73728, hOffPL = 81920;         // P, then dVn, then dZ (hi / lo)
+constexpr uint32_t hOffX = 90112;
+constexpr uint32_t kDhuSmem = 98304;
+constexpr uint32_t hColDS = 0, hColW1 = 64, hColQK = 128, hColU1 = 192;
+
+struct DhuPrefetch {
+  uint4 qk[16];
+  uint4 x[4];
+  uint4 row[8];   // q-side threads: dO row; k-side threads: v row
+  float gb;
+};
+
+__global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ float gam_s[2][kC], beta_s[2][kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+
+  const int tid = threadIdx.x, warp = tid / 32;
+  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
+  const int hk = hv / (p.HV / p.HK);
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const bool kwarp = warp >= 2;
+  const int row = tid, tok = tid & 63;
+
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  uint32_t phase = 0;
+  const uint32_t sb = smem_u32(smem);
+
+  DhuPrefetch pf;
+  auto prefetch_load = [&](int c) {
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = tid + i * 128;
+      const int r = (idx / 16) & 63, ch = idx % 16;
+      const bool isk = idx >= 1024;
+      pf.qk[i] = make_uint4(0, 0, 0, 0);
+      if (r < rows) {
+        const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
+        pf.qk[i] = *reinterpret_cast<const uint4*>(src + ch * 8);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 128, r = idx / 8, ch = idx % 8;
+      pf.x[i] = make_uint4(0, 0, 0, 0);
+      if (r < rows) pf.x[i] = *reinterpret_cast<const uint4*>(p.X + ((tok0 + r) * p.HV + hv) * kC + ch * 8);
+    }
+    const bf16* rsrc = kwarp ? p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV
+                             : p.dO + (tok0 + tok) * p.do_st + hv * p.do_sh + vb * kBV;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      pf.row[i] = make_uint4(0, 0, 0, 0);
+      if (tok < rows) pf.row[i] = *reinterpret_cast<const uint4*>(rsrc + i * 8);
+    }
+    if (kwarp) pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    else pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
+  };
+  uint4 rcur[8];
+  auto prefetch_store = [&](int c) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = tid + i * 128;
+      const int r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
+      *reinterpret_cast<uint4*>(smem + hOffQK + (ch / 8) * hQKPanel + panel_chunk_off(r, ch % 8)) = pf.qk[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 128;
+      *reinterpret_cast<uint4*>(smem + hOffX + panel_chunk_off(idx / 8, idx % 8)) = pf.x[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) rcur[i] = pf.row[i];
+    if (kwarp) {
+      beta_s[c & 1][tok] = pf.gb;
+    } else {
+      gam_s[c & 1][tok] = pf.gb;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(smem + hOffDO + panel_chunk_off(tok, i)) = pf.row[i];
+    }
+  };
+
+  const Operand opQK{sb + hOffQK, hQKPanel, 0};
+  const Operand opKb{sb + hOffQK + 8192, hQKPanel, 0};
+  const Operand opQKT{sb + hOffQK, hQKPanel, 1};               // [q^T | k^T]: M = 128 key dims, reduction over 128 rows
+  const Operand opDSH{sb + hOffDSH, 16384, 1}, opDSL{sb + hOffDSL, 16384, 1};
+  const Operand opPTh{sb + hOffPH - 8192, 8192, 1}, opPTl{sb + hOffPL - 8192, 8192, 1};  // P^T, valid rows 64..127
+  const Operand opDO{sb + hOffDO, 8192, 1};
+  const Operand opXT{sb + hOffX - 8192, 8192, 1};              // X^T, valid rows 64..127
+  const Operand opDVh{sb + hOffPH, 8192, 1}, opDVl{sb + hOffPL, 8192, 1};
+
+  bool ok = true;
+  float srow[kBV];
+  const int c_last = sq.nt - 1;
+  prefetch_load(c_last);
+  prefetch_store(c_last);
+  if (p.dht) {
+    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+#pragma unroll
+    for (int i = 0; i < kBV; i += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(src + i);
+      srow[i] = t.x; srow[i + 1] = t.y; srow[i + 2] = t.z; srow[i + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kBV; ++i) srow[i] = 0.f;
+  }
+  __syncthreads();
+
+  for (int c = c_last; c >= 0; --c) {
+    const int cur = c & 1;
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+    const float gam_last = gam_s[cur][rows - 1];
+    const float gam_i = gam_s[cur][tok];
+    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+
+    // ---- stage 0: publish dS' (split copy for the MMAs and for the second kernel), pre-decayed master in TMEM
+    row64_to_hilo(smem + hOffDSH, smem + hOffDSL, row, srow);
+    {
+      const float dl = __expf(gam_last);
+#pragma unroll
+      for (int i = 0; i < kBV; ++i) srow[i] *= dl;
+      tmem_st_row64(trow + hColDS, srow);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 1: [Q;K] dS' and [Q;K] K^T
+    if (tid == 0) {
+      bf16* dst = p.ds_img + (cidx * 2 + vb) * (2 * 8192);
+      bulk_store(dst, sb + hOffDSH, 16384);
+      bulk_store(dst + 8192, sb + hOffDSL, 16384);
+      bulk_commit();
+      mma_tile(tbase + hColW1, opQK, opDSH, 128, 64, 8, false);
+      mma_tile(tbase + hColW1, opQK, opDSL, 128, 64, 8, true);
+      mma_tile(tbase + hColQK, opQK, opKb, 128, 64, 8, false);
+      mma_commit(&bar);
+    }
+    if (c > 0) prefetch_load(c - 1);
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- stage 2: q-side rows build P = tril(Q K^T * decay)
+    float acc[kBV];
+    if (!kwarp) {
+      tmem_ld_row64(trow + hColQK, acc);
+#pragma unroll
+      for (int j = 0; j < kC; ++j) acc[j] = (j <= tok) ? acc[j] * __expf(gam_i - gam_s[cur][j]) : 0.f;
+      row64_to_hilo(smem + hOffPH, smem + hOffPL, tok, acc);
+    }
+    if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 3: U1 = P^T dO  (valid accumulator rows 64..127)
+    if (tid == 0) {
+      mma_tile(tbase + hColU1, opPTh, opDO, 128, 64, 4, false);
+      mma_tile(tbase + hColU1, opPTl, opDO, 128, 64, 4, true);
+      mma_commit(&bar);
+    }
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- stage 4: k-side rows: dVn = scale U1 + e^{gam_L - gam} (K dS')
+    if (kwarp) {
+      float w1[kBV];
+      tmem_ld_row64(trow + hColW1, w1);
+      tmem_ld_row64(trow + hColU1, acc);
+      const float dk = __expf(gam_last - gam_i);
+#pragma unroll
+      for (int i = 0; i < kBV; ++i) acc[i] = p.scale * acc[i] + dk * w1[i];
+      row64_to_hilo(smem + hOffPH, smem + hOffPL, tok, acc);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 5: dZ = X^T dVn  (valid accumulator rows 64..127)
+    if (tid == 0) {
+      mma_tile(tbase + hColQK, opXT, opDVh, 128, 64, 4, false);
+      mma_tile(tbase + hColQK, opXT, opDVl, 128, 64, 4, true);
+      mma_commit(&bar);
+    }
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- stage 6: k-side rows: dV, sum_v dZ*V, dZ images, -beta e^gam dZ;  q-side rows: scale e^gam dO
+    if (kwarp) {
+      tmem_ld_row64(trow + hColQK, acc);
+      const float bi = beta_s[cur][tok];
+      float bzsum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float vv[8];
+        unpack_bf16x8(rcur[i], vv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bzsum += acc[i * 8 + j] * vv[j];
+      }
+      row64_to_hilo(smem + hOffPH, smem + hOffPL, tok, acc);
+      if (tok < rows) {
+        p.bz[(int64_t(vb) * p.total_tokens + tok0 + tok) * p.HV + hv] = bzsum;
+        const int64_t off = (tok0 + tok) * p.dv_st + hv * p.dv_sh + vb * kBV;
+        if (p.grads_f32) {
+          float* dst = static_cast<float*>(p.dv) + off;
+#pragma unroll
+          for (int i = 0; i < kBV; i += 4)
+            *reinterpret_cast<float4*>(dst + i) = make_float4(bi * acc[i], bi * acc[i + 1], bi * acc[i + 2], bi * acc[i + 3]);
+        } else {
+          bf16* dst = static_cast<bf16*>(p.dv) + off;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = bi * acc[ch * 8 + j];
+            *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(t);
+          }
+        }
+      }
+      const float f = -bi * __expf(gam_i);
+#pragma unroll
+      for (int i = 0; i < kBV; ++i) acc[i] *= f;
+      row64_to_hilo(smem + hOffDSH, smem + hOffDSL, 64 + tok, acc);
+    } else {
+      const float f = p.scale * __expf(gam_i);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float vv[8];
+        unpack_bf16x8(rcur[i], vv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i * 8 + j] = f * vv[j];
+      }
+      row64_to_hilo(smem + hOffDSH, smem + hOffDSL, tok, acc);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 7: dS += [Q^T | K^T] [scale e^gam dO ; -beta e^gam dZ]
+    if (tid == 0) {
+      bf16* dst = p.dz_img + (cidx * 2 + vb) * 12288;
+      bulk_store(dst, sb + hOffDO, 8192);            // rows 0..63 of the hi image: dO
+      bulk_store(dst + 4096, sb + hOffPH, 8192);     // rows 64..127: dZ hi
+      bulk_store(dst + 8192, sb + hOffPL, 8192);     // dZ lo
+      bulk_commit();
+      mma_tile(tbase + hColDS, opQKT, opDSH, 128, 64, 8, true);
+      mma_tile(tbase + hColDS, opQKT, opDSL, 128, 64, 8, true);
+      mma_commit(&bar);
+    }
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- stage 8: new dS to registers; next chunk's operands
+    tmem_ld_row64(trow + hColDS, srow);
+    if (tid == 0) bulk_wait_read();
+    tc_fence_before();
+    __syncthreads();
+    if (c > 0) {
+      prefetch_store(c - 1);
+      __syncthreads();
+    }
+  }
+
+  if (ok && p.dh0) {
+    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+#pragma unroll
+    for (int i = 0; i < kBV; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+  }
+  if (tid == 0) bulk_wait_all();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+// ============================================================================================= par
+constexpr uint32_t rOffQK = 0, rQKPanel = 16384;
+constexpr uint32_t rOffAH = 32768;             // [dO ; dZ_hi] rows of one V block (128 rows)
+constexpr uint32_t rOffAL = 49152;             // rows 0-63 zero, rows 64-127 dZ_lo
+constexpr uint32_t rOffVNH = 65536, rOffVNL = 73728;
+constexpr uint32_t rOffSH = 81920, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 131072;
+constexpr uint32_t rOffPAH = 147456, rOffPAL = 163840;   // [dP ; dAt] hi / lo (128 rows x 64)
+constexpr uint32_t kParSmem = 180224;
+constexpr uint32_t rColQK = 0, rColDV = 64, rColTA = 128, rColTB = 256;
+constexpr uint32_t kStepBytes = 16384 + 8192 + 16384 + 32768 + 32768;
+
+__device__ __forceinline__ void row_dot64(const uint8_t* pan0, uint32_t panel_stride, int row, int col0, const float* x,
+                                          float& acc) {
+  // acc += sum_c bf16_panel[row][col0 + c] * x[c], c in [0, 64); col0 is 0 or 64 (one panel)
+  const uint8_t* pan = pan0 + (col0 / 64) * panel_stride;
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    float f[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(pan + panel_chunk_off(row, ch)), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += f[j] * x[ch * 8 + j];
+  }
+}
+
+__global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ float gam_s[kC], beta_s[kC];
+  __shared__ float red[5][2][kC];      // qdq, kdk, rkG, rkB, ma : [half][row]
+  __shared__ float sds_s[8];
+  __shared__ float dgam_s[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar;
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int hk = blockIdx.y, n = blockIdx.z;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const int c = blockIdx.x;
+  if (c >= sq.nt) return;
+  const int t0 = c * kC;
+  const int rows = min(kC, sq.len - t0);
+  const int64_t tok0 = int64_t(sq.bos) + t0;
+  const int G = p.HV / p.HK;
+  const int quad = warp & 3, half = warp >> 2;
+  const int row = quad * 32 + lane;           // accumulator row == TMEM lane
+  const bool kside = quad >= 2;
+  const int tok = row & 63;
+
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init(&load_bar, 1);
+    mbar_init_fence();
+  }
+  // q, k rows of the chunk (shared by the value heads of the group) and the static zero rows of the lo operand
+  for (int idx = tid; idx < 2048; idx += 256) {
+    const int r = (idx / 16) & 63, ch = idx % 16;
+    const bool isk = idx >= 1024;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r < rows) {
+      const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
+      val = *reinterpret_cast<const uint4*>(src + ch * 8);
+    }
+    *reinterpret_cast<uint4*>(smem + rOffQK + (ch / 8) * rQKPanel + panel_chunk_off(r + (isk ? 64 : 0), ch % 8)) = val;
+  }
+  for (int idx = tid; idx < 512; idx += 256) *reinterpret_cast<uint4*>(smem + rOffAL + idx * 16) = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, quad * 32, 0);
+  const uint32_t sb = smem_u32(smem);
+  uint32_t mphase = 0, lphase = 0;
+  bool ok = true;
+
+  auto issue_loads = [&](int hv, int vb) {  // one thread: operands of one (value head, V block) step
+    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+    mbar_arrive_expect_tx(&load_bar, kStepBytes);
+    const bf16* dz = p.dz_img + (cidx * 2 + vb) * 12288;
+    bulk_load(sb + rOffAH, dz, 16384, &load_bar);
+    bulk_load(sb + rOffAL + 8192, dz + 8192, 8192, &load_bar);
+    bulk_load(sb + rOffVNH, p.vn_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + rOffSH, p.s_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + rOffDSH, p.ds_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
+  };
+  if (tid == 0) issue_loads(hk * G, 0);
+
+  const Operand opQK{sb + rOffQK, rQKPanel, 0};                      // [q; k], reduction over key dims
+  const Operand opKb{sb + rOffQK + 8192, rQKPanel, 0};               // k as B, N = 64 tokens
+  const Operand opKn{sb + rOffQK + 8192, rQKPanel, 1};               // k as B, N = 128 key dims, reduction over tokens
+  const Operand opQKn{sb + rOffQK, rQKPanel, 1};                     // [q; k] as B, N = 128 key dims, reduction over 128 rows
+  const Operand opAH{sb + rOffAH, 16384, 0}, opAL{sb + rOffAL, 16384, 0};
+  const Operand opVNbH{sb + rOffVNH, 8192, 0}, opVNbL{sb + rOffVNL, 8192, 0};            // Vn as B (N = 64 tokens)
+  const Operand opVNaH{sb + rOffVNH - 8192, 8192, 0}, opVNaL{sb + rOffVNL - 8192, 8192, 0};  // Vn as A, valid rows 64..127
+  const Operand opSH{sb + rOffSH, 16384, 0}, opSL{sb + rOffSL, 16384, 0};                // S block as B (N = 128 key dims)
+  const Operand opDSH{sb + rOffDSH, 16384, 0}, opDSL{sb + rOffDSL, 16384, 0};
+  const Operand opPAH{sb + rOffPAH, 16384, 0}, opPAL{sb + rOffPAL, 16384, 0};            // [dP; dAt], reduction over j
+  const Operand opPATh{sb + rOffPAH - 8192, 8192, 1}, opPATl{sb + rOffPAL - 8192, 8192, 1};  // its transpose, valid rows 64..127
+
+  float acc_out[64];  // running dq (q-side rows) or dk (k-side rows), this thread's 64 key-dim columns
+#pragma unroll
+  for (int i = 0; i < 64; ++i) acc_out[i] = 0.f;
+
+  for (int h = 0; h < G && ok; ++h) {
+    const int hv = hk * G + h;
+    if (tid < kC) {
+      gam_s[tid] = p.gam[(tok0 + min(tid, rows - 1)) * p.HV + hv];
+      beta_s[tid] = tid < rows ? ld_scalar(p.beta, (tok0 + tid) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    }
+    float sds = 0.f;
+    for (int vb = 0; vb < 2; ++vb) {
+      ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT);
+      lphase ^= 1;
+      if (!__syncthreads_and(ok)) break;
+      if (tid == 0) {
+        tc_fence_after();
+        if (h == 0 && vb == 0) mma_tile(tbase + rColQK, opQK, opKb, 128, 64, 8, false);
+        const bool accf = vb > 0;
+        mma_tile(tbase + rColDV, opAH, opVNbH, 128, 64, 4, accf);
+        mma_tile(tbase + rColDV, opAH, opVNbL, 128, 64, 4, true);
+        mma_tile(tbase + rColDV, opAL, opVNbH, 128, 64, 4, true);
+        mma_tile(tbase + rColTA, opAH, opSH, 128, 128, 4, accf);
+        mma_tile(tbase + rColTA, opAH, opSL, 128, 128, 4, true);
+        mma_tile(tbase + rColTA, opAL, opSH, 128, 128, 4, true);
+        mma_tile(tbase + rColTB, opVNaH, opDSH, 128, 128, 4, accf);
+        mma_tile(tbase + rColTB, opVNaH, opDSL, 128, 128, 4, true);
+        mma_tile(tbase + rColTB, opVNaL, opDSH, 128, 128, 4, true);
+        mma_commit(&mma_bar);
+      }
+      // <S, dS'> over this V block while the MMAs run (elementwise on the raw panel images)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t off = (tid + i * 256) * 16;
+        float s1[8], s2[8], d1[8], d2[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + rOffSH + off), s1);
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + rOffSL + off), s2);
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + rOffDSH + off), d1);
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + rOffDSL + off), d2);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sds += (s1[j] + s2[j]) * (d1[j] + d2[j]);
+      }
+      ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+      mphase ^= 1;
+      if (!__syncthreads_and(ok)) break;   // also: every thread is done reading the step's buffers
+      tc_fence_after();
+      if (tid == 0) {
+        if (vb == 0) issue_loads(hv, 1);
+        else if (h + 1 < G) issue_loads(hv + 1, 0);
+      }
+    }
+    if (!ok) break;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sds += __shfl_xor_sync(0xffffffffu, sds, o);
+    if (lane == 0) sds_s[warp] = sds;
+
+    // ---- epilogue 1: score-tile gradients -> [dP; dAt] operand, first parts of this head's dq / dk rows
+    const float gam_i = gam_s[tok], beta_i = beta_s[tok], gam_last = gam_s[rows - 1];
+    const float eg = __expf(gam_i);
+    float ma_part = 0.f;
+    {
+      float sc[32], dvv[32];
+      tmem_ld32(trow + rColQK + half * 32, sc);
+      tmem_ld32(trow + rColDV + half * 32, dvv);
+      tmem_ld_wait();
+      if (!kside) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int j = half * 32 + jj;
+          dvv[jj] = (j <= tok) ? p.scale * dvv[jj] * __expf(gam_i - gam_s[j]) : 0.f;
+        }
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int j = half * 32 + jj;
+          const float dec = (j < tok) ? __expf(gam_i - gam_s[j]) : 0.f;
+          const float dA = -dvv[jj] * dec;
+          ma_part += dA * sc[jj];
+          dvv[jj] = dA * beta_i;
+        }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint4 hi, lo;
+        split8(dvv + ch * 8, hi, lo);
+        const uint32_t off = panel_chunk_off(row, half * 4 + ch);
+        *reinterpret_cast<uint4*>(smem + rOffPAH + off) = hi;
+        *reinterpret_cast<uint4*>(smem + rOffPAL + off) = lo;
+      }
+    }
+    float part[64];   // this head's contribution to my dq / dk row (64 key-dim columns)
+    float rkG = 0.f, rkB = 0.f;
+    tmem_ld_row64(trow + rColTA + half * 64, part);
+    if (!kside) {
+      const float f = p.scale * eg;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) part[i] *= f;
+    } else {
+      row_dot64(smem + rOffQK, rQKPanel, 64 + tok, half * 64, part, rkG);
+      float bk[64];
+      tmem_ld_row64(trow + rColTB + half * 64, bk);
+      row_dot64(smem + rOffQK, rQKPanel, 64 + tok, half * 64, bk, rkB);
+      const float f1 = -beta_i * eg, f2 = __expf(gam_last - gam_i);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) part[i] = f1 * part[i] + f2 * bk[i];
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- [dP; dAt] K  and  [dP^T | dAt^T] [Q; K]
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase + rColTA, opPAH, opKn, 128, 128, 4, false);
+      mma_tile(tbase + rColTA, opPAL, opKn, 128, 128, 4, true);
+      mma_tile(tbase + rColTB, opPATh, opQKn, 128, 128, 8, false);
+      mma_tile(tbase + rColTB, opPATl, opQKn, 128, 128, 8, true);
+      mma_commit(&mma_bar);
+    }
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    mphase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after();
+
+    // ---- epilogue 2: finish the rows, row dots for dg / dbeta
+    {
+      float t[64];
+      tmem_ld_row64(trow + rColTA + half * 64, t);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) part[i] += t[i];
+      if (kside) {
+        tmem_ld_row64(trow + rColTB + half * 64, t);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) part[i] += t[i];
+      }
+    }
+    float xdx = 0.f;  // q.dq (q-side) or k.dk (k-side) over my columns
+    row_dot64(smem + rOffQK, rQKPanel, row, half * 64, part, xdx);
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc_out[i] += part[i];
+    if (!kside) {
+      red[0][half][tok] = xdx;
+    } else {
+      red[1][half][tok] = xdx;
+      red[2][half][tok] = rkG;
+      red[3][half][tok] = rkB;
+      red[4][half][tok] = ma_part;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid < kC) {
+      const int i = tid;
+      const float qdq = red[0][0][i] + red[0][1][i], kdk = red[1][0][i] + red[1][1][i];
+      const float g_ = red[2][0][i] + red[2][1][i], b_ = red[3][0][i] + red[3][1][i], ma = red[4][0][i] + red[4][1][i];
+      const float gi = gam_s[i], bi = beta_s[i], egi = __expf(gi), el = __expf(gam_s[rows - 1] - gi);
+      float dgam = qdq - kdk + 2.f * bi * ma - 2.f * bi * egi * g_;
+      red[3][0][i] = (i < rows) ? el * b_ : 0.f;   // e^{gam_L - gam_i} k_i.(Vn dS'^T)_i, summed below for the last row
+      dgam_s[i] = (i < rows) ? dgam : 0.f;
+      if (i < rows) {
+        const int64_t gidx = (tok0 + i) * p.HV + hv;
+        const float bz = p.bz[gidx] + p.bz[p.total_tokens * p.HV + gidx];
+        const float db = bz - egi * g_ + ma;
+        if (p.grads_f32) static_cast<float*>(p.dbeta)[gidx] = db;
+        else static_cast<bf16*>(p.dbeta)[gidx] = __float2bfloat16_rn(db);
+      }
+    }
+    __syncthreads();
+    if (tid < rows) {
+      // dg = reverse chunk-local cumulative sum of dgam; the last row additionally carries
+      // e^{gam_L} <S, dS'> + sum_i e^{gam_L - gam_i} k_i.(Vn dS'^T)_i, which therefore reaches every row.
+      float tot = 0.f;
+      for (int w = 0; w < 8; ++w) tot += sds_s[w];
+      float dgv = __expf(gam_s[rows - 1]) * tot;
+      for (int j = 0; j < rows; ++j) dgv += red[3][0][j];
+      for (int j = tid; j < rows; ++j) dgv += dgam_s[j];
+      const int64_t gidx = (tok0 + tid) * p.HV + hv;
+      if (p.grads_f32) static_cast<float*>(p.dg)[gidx] = dgv;
+      else static_cast<bf16*>(p.dg)[gidx] = __float2bfloat16_rn(dgv);
+    }
+    __syncthreads();
+  }
+
+  if (ok && tok < rows) {
+    void* base = kside ? p.dk : p.dq;
+    const int64_t off = kside ? (tok0 + tok) * p.dk_st + hk * p.dk_sh + half * 64 : (tok0 + tok) * p.dq_st + hk * p.dq_sh + half * 64;
+    if (p.grads_f32) {
+      float* dst = static_cast<float*>(base) + off;
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(acc_out[i], acc_out[i + 1], acc_out[i + 2], acc_out[i + 3]);
+    } else {
+      bf16* dst = static_cast<bf16*>(base) + off;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(acc_out + ch * 8);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
+}  // namespace fla
+
+using namespace fla;
+
+static uint64_t bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t tokens, uint64_t* off_ds, uint64_t* off_dz,
+                              uint64_t* off_bz) {
+  uint64_t o = 256;  // status block
+  *off_ds = o; o += align_up(uint64_t(total_chunks) * HV * kSImg * 2, 256);
+  *off_dz = o; o += align_up(uint64_t(total_chunks) * HV * kDzImg * 2, 256);
+  *off_bz = o; o += align_up(uint64_t(2) * tokens * HV * 4, 256);
+  return o;
+}
+
+static int bwd_geometry(const fla_gdn_chunk_bwd_args* a, int64_t* total_chunks, int* N, int* max_len) {
+  const fla_tensor_t& q = a->q;
+  if (!q.data || q.ndim != 4 || !a->v.data || a->v.ndim != 4) return FLA_ERR_SHAPE;
+  const int64_t B = q.shape[0], T = q.shape[1];
+  *N = int(B);
+  *total_chunks = B * ((T + kC - 1) / kC);
+  *max_len = int(T);
+  if (a->cu_seqlens.data) {
+    if (B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    *N = int(a->cu_seqlens.shape[0] - 1);
+    if (!a->chunk_offsets.data || a->chunk_offsets.dtype != FLA_I32 || a->chunk_offsets.shape[0] != *N + 1) return FLA_ERR_SHAPE;
+    if (a->max_seqlen <= 0 || a->max_seqlen > T || a->total_chunks <= 0) return FLA_ERR_VALUE;
+    *max_len = a->max_seqlen;
+    *total_chunks = a->total_chunks;
+  }
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_gdn_chunk_bwd_workspace_size(const fla_gdn_chunk_bwd_args* a, uint64_t* bytes) {
+  if (!a || !bytes) return FLA_ERR_NULL;
+  int64_t total_chunks; int N, max_len;
+  int st = bwd_geometry(a, &total_chunks, &N, &max_len);
+  if (st) return st;
+  uint64_t o1, o2, o3;
+  *bytes = bwd_ws_layout(total_chunks, a->v.shape[2], a->q.shape[0] * a->q.shape[1], &o1, &o2, &o3);
+  return FLA_OK;
+}
+
+static int check_tok4(const fla_tensor_t& t, int64_t B, int64_t T, int64_t heads, int64_t dim, bool allow_f32) {
+  if (!t.data) return FLA_ERR_NULL;
+  if (t.ndim != 4 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != heads || t.shape[3] != dim) return FLA_ERR_SHAPE;
+  if (t.dtype != FLA_BF16 && !(allow_f32 && t.dtype == FLA_F32)) return FLA_ERR_DTYPE;
+  const int64_t esz = t.dtype == FLA_F32 ? 4 : 2;
+  if (t.stride[3] != 1 || (t.stride[2] * esz) % 16 || (t.stride[1] * esz) % 16 || !aligned16(t.data)) return FLA_ERR_LAYOUT;
+  if (B > 1 && t.stride[0] != T * t.stride[1]) return FLA_ERR_LAYOUT;
+  return FLA_OK;
+}
+static int check_tok3(const fla_tensor_t& t, int64_t B, int64_t T, int64_t heads, bool dense) {
+  if (!t.data) return FLA_ERR_NULL;
+  if (t.ndim != 3 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != heads) return FLA_ERR_SHAPE;
+  if (t.dtype != FLA_BF16 && t.dtype != FLA_F32) return FLA_ERR_DTYPE;
+  if (t.stride[2] != 1 || (B > 1 && t.stride[0] != T * t.stride[1])) return FLA_ERR_LAYOUT;
+  if (dense && t.stride[1] != heads) return FLA_ERR_LAYOUT;
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, void* workspace, uint64_t workspace_bytes,
+                                              void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  int64_t total_chunks; int N, max_len;
+  int st = bwd_geometry(a, &total_chunks, &N, &max_len);
+  if (st) return st;
+  const int64_t B = a->q.shape[0], T = a->q.shape[1], HK = a->q.shape[2], HV = a->v.shape[2];
+  if (HK <= 0 || HV <= 0 || HV % HK) return FLA_ERR_SHAPE;
+  if ((st = check_tok4(a->q, B, T, HK, kK, false))) return st;
+  if ((st = check_tok4(a->k, B, T, HK, kK, false))) return st;
+  if ((st = check_tok4(a->v, B, T, HV, kV, false))) return st;
+  if ((st = check_tok4(a->d_o, B, T, HV, kV, false))) return st;
+  if ((st = check_tok4(a->dq, B, T, HK, kK, true))) return st;
+  if ((st = check_tok4(a->dk, B, T, HK, kK, true))) return st;
+  if ((st = check_tok4(a->dv, B, T, HV, kV, true))) return st;
+  if ((st = check_tok3(a->beta, B, T, HV, false))) return st;
+  if ((st = check_tok3(a->dg, B, T, HV, true))) return st;
+  if ((st = check_tok3(a->dbeta, B, T, HV, true))) return st;
+  const int gdt = a->dq.dtype;
+  if (a->dk.dtype != gdt || a->dv.dtype != gdt || a->dg.dtype != gdt || a->dbeta.dtype != gdt) return FLA_ERR_DTYPE;
+  const fla_tensor_t &gam = a->gam, &X = a->x_inv;
+  if (!gam.data || !X.data || !a->s_img.data || !a->vn_img.data) return FLA_ERR_NULL;
+  if (gam.dtype != FLA_F32 || gam.ndim != 3 || gam.shape[0] != B || gam.shape[1] != T || gam.shape[2] != HV ||
+      gam.stride[2] != 1 || gam.stride[1] != HV || (B > 1 && gam.stride[0] != T * HV))
+    return FLA_ERR_SHAPE;
+  if (X.dtype != FLA_BF16 || X.ndim != 4 || X.shape[0] != B || X.shape[1] != T || X.shape[2] != HV || X.shape[3] != kC ||
+      X.stride[3] != 1 || X.stride[2] != kC || X.stride[1] != HV * kC || !aligned16(X.data))
+    return FLA_ERR_SHAPE;
+  if (a->s_img.dtype != FLA_BF16 || a->s_img.ndim != 1 || a->s_img.shape[0] != total_chunks * HV * kSImg || !aligned16(a->s_img.data))
+    return FLA_ERR_SHAPE;
+  if (a->vn_img.dtype != FLA_BF16 || a->vn_img.ndim != 1 || a->vn_img.shape[0] != total_chunks * HV * kVnImg || !aligned16(a->vn_img.data))
+    return FLA_ERR_SHAPE;
+  for (const fla_tensor_t* s : {&a->dht, &a->dh0}) {
+    if (!s->data) continue;
+    if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
+    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != HV * kK * kV || !aligned16(s->data))
+      return FLA_ERR_LAYOUT;
+  }
+  if (a->chunk_size != kC) return FLA_ERR_VALUE;
+  uint64_t off_ds, off_dz, off_bz;
+  const uint64_t need = bwd_ws_layout(total_chunks, HV, B * T, &off_ds, &off_dz, &off_bz);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
+
+  GdnBwdParams p{};
+  p.q = static_cast<const bf16*>(a->q.data); p.k = static_cast<const bf16*>(a->k.data);
+  p.v = static_cast<const bf16*>(a->v.data); p.dO = static_cast<const bf16*>(a->d_o.data);
+  p.beta = a->beta.data; p.gam = static_cast<const float*>(gam.data); p.X = static_cast<const bf16*>(X.data);
+  p.s_img = static_cast<const bf16*>(a->s_img.data); p.vn_img = static_cast<const bf16*>(a->vn_img.data);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.ds_img = reinterpret_cast<bf16*>(ws + off_ds);
+  p.dz_img = reinterpret_cast<bf16*>(ws + off_dz);
+  p.bz = reinterpret_cast<float*>(ws + off_bz);
+  p.dht = static_cast<const float*>(a->dht.data); p.dh0 = static_cast<float*>(a->dh0.data);
+  p.dq = a->dq.data; p.dk = a->dk.data; p.dv = a->dv.data; p.dg = a->dg.data; p.dbeta = a->dbeta.data;
+  p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+  p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
+  p.q_st = a->q.stride[1]; p.q_sh = a->q.stride[2]; p.k_st = a->k.stride[1]; p.k_sh = a->k.stride[2];
+  p.v_st = a->v.stride[1]; p.v_sh = a->v.stride[2]; p.do_st = a->d_o.stride[1]; p.do_sh = a->d_o.stride[2];
+  p.beta_st = a->beta.stride[1];
+  p.dq_st = a->dq.stride[1]; p.dq_sh = a->dq.stride[2]; p.dk_st = a->dk.stride[1]; p.dk_sh = a->dk.stride[2];
+  p.dv_st = a->dv.stride[1]; p.dv_sh = a->dv.stride[2];
+  p.total_tokens = B * T;
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV);
+  p.beta_is_f32 = a->beta.dtype == FLA_F32; p.grads_f32 = gdt == FLA_F32;
+  p.scale = a->scale;
+
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
+  static bool attr_done_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (!attr_done_dev[dev]) {
+    if (cudaFuncSetAttribute(gdn_bwd_dhu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDhuSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(gdn_bwd_par_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    attr_done_dev[dev] = true;
+  }
+  {
+    KernelTimer kt("gdn_bwd_dhu", cs);
+    gdn_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), 128, kDhuSmem + 1024, cs>>>(p);
+  }
+  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  const int nt_max = (max_len + kC - 1) / kC;
+  {
+    KernelTimer kt("gdn_bwd_par", cs);
+    gdn_bwd_par_kernel<<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p);
+  }
+  return cuda_status(cudaGetLastError());
+}

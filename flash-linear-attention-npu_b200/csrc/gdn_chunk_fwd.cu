@@ -33,8 +33,8 @@ struct GdnFwdParams {
   const float* h0;     // [N, HV, K, V] or null
   float* ht;           // [N, HV, K, V] or null
   void* o;             // [tokens, HV, V]
-  bf16* s_hi; bf16* s_lo;    // [chunks, HV, K, V] state at chunk start, split (optional, for backward)
-  bf16* vn_hi; bf16* vn_lo;  // [tokens, HV, V] v_new, split (optional, for backward)
+  bf16* s_img;         // [chunks, HV, 2, 2, 128x64] panel images of the state at chunk start (hi, lo), optional
+  bf16* vn_img;        // [chunks, HV, 2, 2, 64x64]  panel images of v_new (hi, lo), optional
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int64_t q_st, q_sh, k_st, k_sh, v_st, v_sh, o_st, o_sh, g_st, beta_st;
   int N, T, HK, HV, g_is_f32, beta_is_f32, o_is_f32;
@@ -313,16 +313,6 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
 
     // ---- stage 0: publish the state at chunk start (split copy for the MMAs, pre-decayed master in TMEM)
     row64_to_hilo(smem + kOffSH, smem + kOffSL, row, srow);
-    if (p.s_hi) {
-      const int64_t off = (((int64_t(sq.cbase) + c) * p.HV + hv) * kK + row) * kV + vb * kBV;
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint4 hi, lo;
-        split8(srow + ch * 8, hi, lo);
-        *reinterpret_cast<uint4*>(p.s_hi + off + ch * 8) = hi;
-        *reinterpret_cast<uint4*>(p.s_lo + off + ch * 8) = lo;
-      }
-    }
     {
       const float dl = __expf(gam_last);
 #pragma unroll
@@ -336,6 +326,12 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
 
     // ---- stage 1: [Q;K] S (split state) and [Q;K] K^T
     if (tid == 0) {
+      if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format
+        bf16* dst = p.s_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 8192);
+        bulk_store(dst, sb + kOffSH, 16384);
+        bulk_store(dst + 8192, sb + kOffSL, 16384);
+        bulk_commit();
+      }
       mma_tile(tbase + kColRQ, opQK, opSH, 128, 64, 8, false);
       mma_tile(tbase + kColRQ, opQK, opSL, 128, 64, 8, true);
       mma_tile(tbase + kColQK, opQK, opKb, 128, 64, 8, false);
@@ -387,16 +383,6 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
     if (kwarp) {
       tmem_ld_row64(trow + kColVN, acc);
       row64_to_hilo(smem + kOffZH, smem + kOffZL, tok, acc);
-      if (p.vn_hi && tok < rows) {
-        const int64_t off = ((tok0 + tok) * p.HV + hv) * kV + vb * kBV;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint4 hi, lo;
-          split8(acc + ch * 8, hi, lo);
-          *reinterpret_cast<uint4*>(p.vn_hi + off + ch * 8) = hi;
-          *reinterpret_cast<uint4*>(p.vn_lo + off + ch * 8) = lo;
-        }
-      }
       const float dk = __expf(gam_last - gam_i);
 #pragma unroll
       for (int i = 0; i < kBV; ++i) acc[i] *= dk;
@@ -409,6 +395,12 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
 
     // ---- stage 5: P v_new (three passes) and the state update S += K^T vhat
     if (tid == 0) {
+      if (p.vn_img) {
+        bf16* dst = p.vn_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 4096);
+        bulk_store(dst, sb + kOffZH, 8192);
+        bulk_store(dst + 4096, sb + kOffZL, 8192);
+        bulk_commit();
+      }
       mma_tile(tbase + kColQK, opPH, opZH, 128, 64, 4, false);
       mma_tile(tbase + kColQK, opPH, opZL, 128, 64, 4, true);
       mma_tile(tbase + kColQK, opPL, opZH, 128, 64, 4, true);
@@ -448,6 +440,7 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
     }
     tmem_ld_row64(trow + kColS, srow);
     if (c + 1 < sq.nt) prefetch_store(c + 1);
+    if (tid == 0 && p.s_img) bulk_wait_read();  // saved images have left shared memory before it is reused
     tc_fence_before();
     __syncthreads();  // next chunk's gam_s / beta_s visible; all TMEM reads of this chunk retired
   }
@@ -457,6 +450,7 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
 #pragma unroll
     for (int i = 0; i < kBV; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
+  if (tid == 0 && p.s_img) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 256);
@@ -542,22 +536,13 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   p.gam = static_cast<float*>(gam.data); p.X = static_cast<bf16*>(X.data);
   p.h0 = static_cast<const float*>(a->initial_state.data); p.ht = static_cast<float*>(a->final_state.data);
   p.o = o.data;
-  if (a->s_hi.data || a->s_lo.data || a->vn_hi.data || a->vn_lo.data) {
-    const fla_tensor_t &sh = a->s_hi, &sl = a->s_lo, &vh = a->vn_hi, &vl = a->vn_lo;
-    if (!sh.data || !sl.data || !vh.data || !vl.data) return FLA_ERR_NULL;
-    for (const fla_tensor_t* s : {&sh, &sl}) {
-      if (s->dtype != FLA_BF16 || s->ndim != 4 || s->shape[0] != total_chunks || s->shape[1] != HV || s->shape[2] != kK ||
-          s->shape[3] != kV || s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV ||
-          s->stride[0] != HV * kK * kV || !aligned16(s->data))
-        return FLA_ERR_SHAPE;
-    }
-    for (const fla_tensor_t* s : {&vh, &vl}) {
-      if (s->dtype != FLA_BF16 || s->ndim != 4 || s->shape[0] != B || s->shape[1] != T || s->shape[2] != HV ||
-          s->shape[3] != kV || s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != HV * kV || !aligned16(s->data))
-        return FLA_ERR_SHAPE;
-    }
-    p.s_hi = static_cast<bf16*>(sh.data); p.s_lo = static_cast<bf16*>(sl.data);
-    p.vn_hi = static_cast<bf16*>(vh.data); p.vn_lo = static_cast<bf16*>(vl.data);
+  if (a->s_img.data || a->vn_img.data) {
+    const fla_tensor_t &si = a->s_img, &vi = a->vn_img;
+    if (!si.data || !vi.data) return FLA_ERR_NULL;
+    if (si.dtype != FLA_BF16 || si.ndim != 1 || si.shape[0] != total_chunks * HV * 32768 || !aligned16(si.data)) return FLA_ERR_SHAPE;
+    if (vi.dtype != FLA_BF16 || vi.ndim != 1 || vi.shape[0] != total_chunks * HV * 16384 || !aligned16(vi.data)) return FLA_ERR_SHAPE;
+    p.s_img = static_cast<bf16*>(si.data);
+    p.vn_img = static_cast<bf16*>(vi.data);
   }
   p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
   p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);

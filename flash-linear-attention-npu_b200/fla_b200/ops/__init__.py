@@ -1,7 +1,8 @@
 """Operator surface.  Every function launches hand-written sm_100a kernels through the C ABI;
 nothing here computes on the CPU or through PyTorch math."""
 from .conv import causal_conv1d, causal_conv1d_update, npu_causal_conv1d  # noqa: F401
-from .gdn import chunk_gated_delta_rule  # noqa: F401
+from .gdn import (chunk_gated_delta_rule, chunk_gated_delta_rule_bwd, chunk_gated_delta_rule_fwd_bwd,  # noqa: F401
+                  ChunkGatedDeltaRuleFunction)
 from .recurrent import fused_recurrent_gated_delta_rule, recurrent_gated_delta_rule  # noqa: F401
 
 npu_recurrent_gated_delta_rule = recurrent_gated_delta_rule

@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from .. import _runtime as rt
-from ._structs import GdnChunkFwdArgs
+from ._structs import GdnChunkBwdArgs, GdnChunkFwdArgs
 
 CHUNK = 64
 
@@ -77,29 +77,110 @@ def gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     ht = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if output_final_state else None
     gam = torch.empty((B, T, HV), dtype=torch.float32, device=dev)
     x_inv = torch.empty((B, T, HV, CHUNK), dtype=torch.bfloat16, device=dev)
-    s_hi = s_lo = vn_hi = vn_lo = None
+    s_img = vn_img = None
     if save_for_backward:
-        s_hi = torch.empty((total_chunks, HV, K, V), dtype=torch.bfloat16, device=dev)
-        s_lo = torch.empty_like(s_hi)
-        vn_hi = torch.empty((B, T, HV, V), dtype=torch.bfloat16, device=dev)
-        vn_lo = torch.empty_like(vn_hi)
+        s_img = torch.empty(total_chunks * HV * 32768, dtype=torch.bfloat16, device=dev)
+        vn_img = torch.empty(total_chunks * HV * 16384, dtype=torch.bfloat16, device=dev)
     a = GdnChunkFwdArgs()
     a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)
     a.initial_state, a.o, a.final_state = rt.desc(initial_state), rt.desc(o), rt.desc(ht)
     a.gam, a.x_inv = rt.desc(gam), rt.desc(x_inv)
-    a.s_hi, a.s_lo, a.vn_hi, a.vn_lo = rt.desc(s_hi), rt.desc(s_lo), rt.desc(vn_hi), rt.desc(vn_lo)
+    a.s_img, a.vn_img = rt.desc(s_img), rt.desc(vn_img)
     a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
     a.scale, a.chunk_size, a.max_seqlen, a.total_chunks = float(scale), CHUNK, int(max_len), int(total_chunks)
-    rt.call("gdn_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gam, x_inv, s_hi, s_lo, vn_hi, vn_lo, cu, co])
-    saved = dict(gam=gam, x_inv=x_inv, s_hi=s_hi, s_lo=s_lo, vn_hi=vn_hi, vn_lo=vn_lo, cu=cu, co=co,
+    rt.call("gdn_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gam, x_inv, s_img, vn_img, cu, co])
+    saved = dict(gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img, cu=cu, co=co,
                  max_len=max_len, total_chunks=total_chunks, N=N)
     return o, ht, saved
+
+
+def gdn_chunk_bwd(q, k, v, beta, saved, do, dht, scale, want_dh0, grad_dtype=None):
+    """Launch the backward kernels on the tensors the forward saved.
+    Returns (dq, dk, dv, dg, dbeta, dh0 | None); gradients are bf16 unless `grad_dtype` says fp32."""
+    op = "chunk_gated_delta_rule_bwd"
+    B, T, HK, K = q.shape
+    HV, V = v.shape[2], v.shape[3]
+    dev = q.device
+    if do.dtype != torch.bfloat16:
+        do = do.to(torch.bfloat16)
+    do = _as_rows(do)
+    if tuple(do.shape) != (B, T, HV, V):
+        raise RuntimeError(f"{op}: do must be {(B, T, HV, V)}, got {tuple(do.shape)}")
+    if saved["s_img"] is None:
+        raise RuntimeError(f"{op}: the forward was not run with save_for_backward=True")
+    N = saved["N"]
+    if dht is not None:
+        if tuple(dht.shape) != (N, HV, K, V):
+            raise RuntimeError(f"{op}: dht must be {(N, HV, K, V)}, got {tuple(dht.shape)}")
+        dht = dht.float().contiguous()
+    gdt = grad_dtype or torch.bfloat16
+    dq = torch.empty((B, T, HK, K), dtype=gdt, device=dev)
+    dk = torch.empty_like(dq)
+    dv = torch.empty((B, T, HV, V), dtype=gdt, device=dev)
+    dg = torch.empty((B, T, HV), dtype=gdt, device=dev)
+    dbeta = torch.empty_like(dg)
+    dh0 = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if want_dh0 else None
+    a = GdnChunkBwdArgs()
+    a.q, a.k, a.v, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(beta)
+    a.gam, a.x_inv, a.s_img, a.vn_img = (rt.desc(saved[n]) for n in ("gam", "x_inv", "s_img", "vn_img"))
+    a.d_o, a.dht = rt.desc(do), rt.desc(dht)
+    a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = (rt.desc(x) for x in (dq, dk, dv, dg, dbeta, dh0))
+    a.cu_seqlens, a.chunk_offsets = rt.desc(saved["cu"]), rt.desc(saved["co"])
+    a.scale, a.chunk_size = float(scale), CHUNK
+    a.max_seqlen, a.total_chunks = int(saved["max_len"]), int(saved["total_chunks"])
+    rt.call("gdn_chunk_bwd", a, [q, k, v, beta, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"], do, dht,
+                                 dq, dk, dv, dg, dbeta, dh0, saved["cu"], saved["co"]])
+    return dq, dk, dv, dg, dbeta, dh0
+
+
+class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
+    """Autograd binding (the reference's ChunkGatedDeltaRuleFunction, examples/flash_gated_delta_rule.py:1026-1122).
+    Saves q, k, v, beta, gam, X and the split per-chunk states / v_new instead of recomputing them."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, output_dtype):
+        need_grad = any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+        q_, k_, v_, g_, b_ = (_as_rows(x.detach()) for x in (q, k, v, g, beta))
+        o, ht, saved = gdn_chunk_fwd(q_, k_, v_, g_, b_, scale, None if initial_state is None else initial_state.detach(),
+                                     output_final_state, cu_seqlens, save_for_backward=need_grad,
+                                     output_dtype=output_dtype)
+        if need_grad:
+            ctx.save_for_backward(q_, k_, v_, b_, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"])
+            ctx.meta = {kk: saved[kk] for kk in ("cu", "co", "max_len", "total_chunks", "N")}
+            ctx.scale = scale
+            ctx.has_h0 = initial_state is not None
+            ctx.in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        q, k, v, beta, gam, x_inv, s_img, vn_img = ctx.saved_tensors
+        saved = dict(ctx.meta, gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img)
+        dq, dk, dv, dg, dbeta, dh0 = gdn_chunk_bwd(q, k, v, beta, saved, do.contiguous(), dht, ctx.scale, ctx.has_h0,
+                                                   grad_dtype=torch.float32 if ctx.in_dtypes[3] == torch.float32 else None)
+        dts = ctx.in_dtypes
+        return (dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]), dg.to(dts[3]), dbeta.to(dts[4]), None, dh0, None, None, None)
+
+
+def chunk_gated_delta_rule_fwd_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, cu_seqlens=None,
+                                   output_dtype=None, grad_dtype=None):
+    """Forward and backward in one call without the autograd graph (what a training step costs).
+    Returns (o, final_state, (dq, dk, dv, dg, dbeta, dh0))."""
+    scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
+    q, k, v, g, beta = (_as_rows(x) for x in (q, k, v, g, beta))
+    o, ht, saved = gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, True, cu_seqlens, save_for_backward=True,
+                                 output_dtype=output_dtype)
+    grads = gdn_chunk_bwd(q, k, v, beta, saved, do, dht, scale, initial_state is not None, grad_dtype=grad_dtype)
+    return o, ht, grads
+
+
+chunk_gated_delta_rule_bwd = gdn_chunk_bwd
 
 
 def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
                            use_qk_l2norm_in_kernel=False, cu_seqlens=None, chunk_size=64, head_first=False,
                            output_dtype=None):
-    """Returns ``(o [B,T,HV,V], final_state [N,HV,K,V] | None)``."""
+    """Returns ``(o [B,T,HV,V], final_state [N,HV,K,V] | None)``; differentiable w.r.t. q, k, v, g, beta, initial_state."""
     op = "chunk_gated_delta_rule"
     if head_first:
         raise NotImplementedError(f"{op}: head_first layouts are not provided; pass [B,T,H,D] tensors")
@@ -108,6 +189,5 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     if use_qk_l2norm_in_kernel:
         raise NotImplementedError(f"{op}: use_qk_l2norm_in_kernel is not available yet")
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
-    o, ht, _ = gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
-                             save_for_backward=False, output_dtype=output_dtype)
-    return o, ht
+    return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
+                                             output_dtype)

@@ -1,0 +1,89 @@
+"""Parity of the chunked GDN backward with fp64 autograd through the naive recurrent oracle.
+
+Bar: max-abs-err / RMS(ref) <= 5e-3 per gradient tensor (fp32 gradient outputs; bf16 gradient outputs get the
+half-ulp allowance of their final rounding on top).
+"""
+import pytest
+import torch
+
+import oracle
+from _util import assert_close, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 5e-3
+NAMES = ("dq", "dk", "dv", "dg", "dbeta")
+
+
+def _ref_and_inputs(B, T, HK, HV, seed, cu=None, h0=True):
+    inp = oracle.make_gdn_inputs(B, T, HK, HV, seed=seed, h0_scale=0.1 if h0 else 0.0)
+    N = B if cu is None else len(cu) - 1
+    if cu is not None:
+        gen = torch.Generator().manual_seed(seed + 1)
+        inp["h0"] = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float() if h0 else None
+        inp["dht"] = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float()
+    ref = oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"],
+                                       do=inp["do"], dht=inp["dht"], dtype=torch.float64, cu_seqlens=cu)
+    d = {n: (t.cuda() if t is not None else None) for n, t in inp.items()}
+    return ref, d
+
+
+@pytest.mark.parametrize("B,T,HK,HV", [(1, 64, 1, 1), (1, 128, 1, 2), (2, 256, 2, 4), (1, 512, 2, 2)])
+def test_backward_fp32_grads(B, T, HK, HV):
+    from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
+    ref, d = _ref_and_inputs(B, T, HK, HV, seed=2000 + T)
+    o, ht, grads = chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
+                                                  dht=d["dht"], output_dtype=torch.float32, grad_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert_close("o", o, ref["o"], TOL)
+    assert_close("ht", ht, ref["ht"], TOL)
+    for name, got in zip(NAMES + ("dh0",), grads):
+        assert_close(name, got, ref[name], TOL)
+
+
+@pytest.mark.parametrize("T", [1, 17, 63, 65, 130])
+def test_backward_ragged_lengths(T):
+    from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
+    ref, d = _ref_and_inputs(1, T, 1, 2, seed=31 + T)
+    _, _, grads = chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
+                                                 dht=d["dht"], grad_dtype=torch.float32)
+    for name, got in zip(NAMES + ("dh0",), grads):
+        assert_close(name, got, ref[name], TOL)
+
+
+def test_backward_varlen_packed_no_initial_state():
+    from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
+    cu = [0, 70, 71, 199, 263, 300]
+    ref, d = _ref_and_inputs(1, 300, 2, 4, seed=77, cu=cu, h0=False)
+    _, _, grads = chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], dht=d["dht"],
+                                                 cu_seqlens=torch.tensor(cu, dtype=torch.int32), grad_dtype=torch.float32)
+    for name, got in zip(NAMES, grads[:5]):
+        assert_close(name, got, ref[name], TOL)
+    assert grads[5] is None
+
+
+def test_autograd_function_bf16_grads_and_determinism():
+    from fla_b200.ops import chunk_gated_delta_rule
+    ref, d = _ref_and_inputs(2, 192, 2, 4, seed=5)
+    outs = []
+    for _ in range(2):
+        leaves = {n: d[n].clone().requires_grad_(True) for n in ("q", "k", "v", "g", "beta", "h0")}
+        o, ht = chunk_gated_delta_rule(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"],
+                                       initial_state=leaves["h0"], output_final_state=True)
+        ((o.float() * d["do"].float()).sum() + (ht * d["dht"]).sum()).backward()
+        outs.append({n: leaves[n].grad for n in leaves})
+    g1, g2 = outs
+    for n, r in (("q", "dq"), ("k", "dk"), ("v", "dv"), ("g", "dg"), ("beta", "dbeta")):
+        assert g1[n].dtype == torch.bfloat16
+        assert_close(r, g1[n], ref[r], TOL, stored_bf16=True)
+        assert torch.equal(g1[n], g2[n]), f"{r} differs between identical runs"
+    assert_close("dh0", g1["h0"], ref["dh0"], TOL)
+
+
+def test_forward_only_call_saves_nothing_and_matches():
+    from fla_b200.ops import chunk_gated_delta_rule
+    ref, d = _ref_and_inputs(1, 128, 1, 2, seed=9)
+    with torch.no_grad():
+        o, ht = chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
+                                       output_final_state=True, output_dtype=torch.float32)
+    assert not o.requires_grad
+    assert_close("o", o, ref["o"], TOL)
