@@ -37,7 +37,14 @@ sys.path.insert(0, str(REPO))
 CFG = dict(B=8, T=4096, HK=16, HV=32, K=128, V=128, D=8192, W=4)
 FWD_FLOP_PER_TOKEN_HEAD = 182955.0      # KK^T, inverse, w/u, state, output (dense 64x64 tiles, no causal credit)
 BWD_FLOP_PER_TOKEN_HEAD = 524288.0
-FWD_KERNEL_FLOP_PER_TOKEN_HEAD = 182955.0 - 16384.0 - 2731.0   # the sequential kernel: everything but KK^T + inverse
+# Algorithmic FLOPs per token per value head of each kernel (dense 64x64 tiles; split-precision passes not counted):
+KERNEL_FLOP_PER_TOKEN_HEAD = {
+    "gdn_fwd": 182955.0 - 16384.0 - 2731.0,        # [Q;K]S, QK^T, X Z, P v_new, K^T vhat  (all but KK^T + inverse)
+    "gdn_bwd_dhu": 147456.0,                        # K dS', QK^T, P^T dO, X^T dVn, [Q^T|K^T][dO~; dR]
+    "gdn_bwd_par": 212992.0,                        # [dO;dZ]Vn^T, [dO;dZ]S^T, Vn dS'^T, [dP;dA]K, [dP^T|dA^T][Q;K], [Q;K]K^T / G
+}
+KERNEL_NAMES = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel"}
+DEFAULT_WORKLOAD = "gdn_fwd_bwd"
 
 
 def _peaks():
@@ -115,11 +122,6 @@ def make_inputs(device, seed):
     return d
 
 
-def have_backward():
-    import fla_b200.ops as ops
-    return hasattr(ops, "chunk_gated_delta_rule_bwd")
-
-
 def step_device(d, workload):
     """One pass of the hot path with device-resident inputs.  Returns the outputs of the step."""
     import fla_b200.ops as ops
@@ -134,7 +136,7 @@ def step_device(d, workload):
 
 
 def launches_per_step(workload):
-    return 3 if workload == "gdn_fwd_conv" else 5
+    return 3 if workload == "gdn_fwd_conv" else 4      # conv + prep + fwd  |  prep + fwd + bwd_dhu + bwd_par
 
 
 def kernel_time(lib, name):
@@ -200,7 +202,7 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        run_reference(args, args.workload or "gdn_fwd_conv")
+        run_reference(args, args.workload or DEFAULT_WORKLOAD)
         return
 
     import torch.distributed as dist
@@ -216,7 +218,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = fla_b200.load_library()
-    workload = args.workload or ("gdn_fwd_bwd" if have_backward() else "gdn_fwd_conv")
+    workload = args.workload or DEFAULT_WORKLOAD
     K, W = args.steps, max(args.warmup, 3)
 
     d = make_inputs(dev, 1001 + rank)
@@ -297,15 +299,18 @@ def main():
     if rank == 0:
         peaks = _peaks()
         token_heads = CFG["B"] * CFG["T"] * CFG["HV"]
-        dom = "gdn_fwd" if "gdn_fwd" in ktimes else None
+        cands = [k for k in ktimes if k in KERNEL_FLOP_PER_TOKEN_HEAD]
+        dom = max(cands, key=lambda k: ktimes[k]["ms_per_launch"]) if cands else None
         roofline = None
         if dom:
-            flops = FWD_KERNEL_FLOP_PER_TOKEN_HEAD * token_heads
+            flops = KERNEL_FLOP_PER_TOKEN_HEAD[dom] * token_heads
             achieved = flops / (ktimes[dom]["ms_per_launch"] * 1e-3) / 1e12
-            roofline = {"kernel": "gdn_fwd_kernel", "bound": "tensor", "achieved": achieved,
+            roofline = {"kernel": KERNEL_NAMES[dom], "bound": "tensor", "achieved": achieved,
                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                         "traffic": None, "peak_source": peaks["source"] + " (burst)",
                         "ms_per_launch": ktimes[dom]["ms_per_launch"]}
+        step_flops = (FWD_FLOP_PER_TOKEN_HEAD + (BWD_FLOP_PER_TOKEN_HEAD if workload == "gdn_fwd_bwd" else 0.0)) * token_heads
+        step_tflops = step_flops / (ms_per_step * 1e-3) / 1e12
         cpu_baseline = None
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
@@ -318,7 +323,9 @@ def main():
             "config": {"workload": workload, **CFG, "global_batch": CFG["B"] * world,
                        "parallelism": f"replicated per GPU x{world}, sharded by batch, no collective",
                        "l2": "inputs per step exceed the 126 MB L2"},
-            "roofline": roofline, "kernels": ktimes, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "kernels": ktimes,
+            "step_roofline": {"algorithmic_tflops": step_tflops, "frac_of_bf16_peak": step_tflops / peaks["bf16_tflops"]},
+            "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_step(workload) * K, "clocks": clocks,
         }

@@ -18,7 +18,7 @@ def declared_symbols():
 
 def test_header_declares_entry_points():
     syms = declared_symbols()
-    for must in ("fla_b200_gdn_chunk_fwd", "fla_b200_recurrent_gdn", "fla_b200_causal_conv1d_fwd",
+    for must in ("fla_b200_gdn_chunk_fwd", "fla_b200_gdn_chunk_bwd", "fla_b200_recurrent_gdn", "fla_b200_causal_conv1d_fwd",
                  "fla_b200_causal_conv1d_update", "fla_b200_version"):
         assert must in syms
 
@@ -53,7 +53,8 @@ def _c_struct_fields(name):
 @pytest.mark.parametrize("cname,pyname", [("fla_recurrent_gdn_args", "RecurrentGdnArgs"),
                                           ("fla_causal_conv1d_fwd_args", "CausalConv1dFwdArgs"),
                                           ("fla_causal_conv1d_update_args", "CausalConv1dUpdateArgs"),
-                                          ("fla_gdn_chunk_fwd_args", "GdnChunkFwdArgs")])
+                                          ("fla_gdn_chunk_fwd_args", "GdnChunkFwdArgs"),
+                                          ("fla_gdn_chunk_bwd_args", "GdnChunkBwdArgs")])
 def test_arg_structs_match_header_field_order(cname, pyname):
     from fla_b200.ops import _structs
     from fla_b200._runtime import TensorDesc
