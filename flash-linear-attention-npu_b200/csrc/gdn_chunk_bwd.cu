@@ -809,3 +809,51 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   }
   return cuda_status(cudaGetLastError());
 }
+
+// ----------------------------------------------------------------------------- allocation-free variant
+// Some hosts of this library may not allocate device memory at the point where they call the backward:
+// an inference / training runtime that sized one device arena at start-up and forbids any later
+// cudaMalloc (an allocation can synchronise the whole device and stall the other streams of a serving
+// process), a plugin running inside another framework's callback that owns the allocator, or a
+// real-time loop with a fixed memory budget.  For them the scratch that fla_b200_gdn_chunk_bwd normally
+// receives from the caller lives here instead, in one fixed array that is part of the library image:
+// every GPU whose context loads libfla_b200.so carries these 32 MiB until the process exits.
+constexpr uint64_t kStaticScratchBytes = 32ull << 20;
+static __device__ __align__(256) unsigned char g_bwd_static_scratch[kStaticScratchBytes];
+
+#include <mutex>
+namespace {
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {};   // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" FLA_API int fla_b200_gdn_chunk_bwd_static_scratch_bytes(uint64_t* bytes) {
+  if (!bytes) return FLA_ERR_NULL;
+  *bytes = kStaticScratchBytes;
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_args* a, void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  uint64_t need = 0;
+  const int st = fla_b200_gdn_chunk_bwd_workspace_size(a, &need);
+  if (st != FLA_OK) return st;
+  if (need > kStaticScratchBytes) return FLA_ERR_TOO_LARGE;   // the problem does not fit the built-in scratch
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+      // In host code the array's name is only a handle; the address the kernels can use has to be asked for,
+      // once per device, while that device is current.
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_bwd_static_scratch) != cudaSuccess || !ptr) return FLA_ERR_CUDA;
+      g_static_ptr[dev] = ptr;
+    }
+    scratch = g_static_ptr[dev];
+  }
+  // The regular entry point clears the status block at the head of the scratch on `stream` and overwrites
+  // every other byte it later reads, so nothing else of the previous call's contents matters.
+  return fla_b200_gdn_chunk_bwd(a, scratch, kStaticScratchBytes, stream);
+}

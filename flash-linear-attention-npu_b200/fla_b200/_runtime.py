@@ -34,6 +34,7 @@ _STATUS_NAMES = {
     6: "FLA_ERR_CUDA (CUDA runtime error)",
     7: "FLA_ERR_VALUE (scalar argument out of range)",
     8: "FLA_ERR_TIMEOUT (device-side wait ran out)",
+    9: "FLA_ERR_TOO_LARGE (problem exceeds the built-in scratch of an allocation-free entry point)",
 }
 
 

@@ -37,7 +37,8 @@ enum fla_status {
   FLA_ERR_WORKSPACE = 5, /* workspace missing or too small */
   FLA_ERR_CUDA = 6,      /* a CUDA runtime call failed */
   FLA_ERR_VALUE = 7,     /* scalar argument out of range */
-  FLA_ERR_TIMEOUT = 8    /* a bounded device-side wait ran out (read back from a kernel status word) */
+  FLA_ERR_TIMEOUT = 8,   /* a bounded device-side wait ran out (read back from a kernel status word) */
+  FLA_ERR_TOO_LARGE = 9  /* the problem needs more scratch than an allocation-free entry point owns */
 };
 
 enum fla_dtype { FLA_F32 = 0, FLA_BF16 = 1, FLA_F16 = 2, FLA_I32 = 3, FLA_I64 = 4 };
@@ -198,6 +199,25 @@ typedef struct fla_gdn_chunk_bwd_args {
 FLA_API int fla_b200_gdn_chunk_bwd_workspace_size(const fla_gdn_chunk_bwd_args* args, uint64_t* bytes);
 FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* args, void* workspace, uint64_t workspace_bytes,
                                    void* stream);
+
+/* Allocation-free backward (no counterpart in the reference, whose Python runtime always allocates the
+ * workspace itself).  Same arguments and results as fla_b200_gdn_chunk_bwd, but the scratch is a fixed
+ * 32 MiB array inside the library instead of a caller-provided workspace, and the call performs no
+ * cudaMalloc / cudaFree and calls no allocating routine.  It is meant for callers that must not allocate
+ * when they reach this call: runtimes that carved up one device arena at start-up and forbid later
+ * allocations (a cudaMalloc can synchronise the device and stall the other streams of a serving process),
+ * plugins that run inside another framework's callback and do not own its allocator, fixed-budget
+ * real-time loops.
+ *   - Limit: the scratch fla_b200_gdn_chunk_bwd_workspace_size reports for the arguments must not exceed
+ *     fla_b200_gdn_chunk_bwd_static_scratch_bytes (32 MiB, about 290 (chunk, value-head) pairs, e.g. T = 512
+ *     with HV = 32 or T = 1024 with HV = 16 for one sequence); larger problems return FLA_ERR_TOO_LARGE.
+ *   - Every GPU whose context loads the library holds the 32 MiB until the process exits.
+ *   - The first call on a device looks up the array's device address (with that device current); make
+ *     that first call before starting any stream capture.
+ *   - All calls on one device share the array: two calls whose kernels can overlap on the GPU (different
+ *     streams, or a second process thread) race on it.  Serialise them, or use the workspace entry point. */
+FLA_API int fla_b200_gdn_chunk_bwd_static_scratch_bytes(uint64_t* bytes);
+FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_args* args, void* stream);
 
 #ifdef __cplusplus
 }
