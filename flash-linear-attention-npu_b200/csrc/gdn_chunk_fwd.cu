@@ -182,28 +182,31 @@ constexpr uint32_t kOffVH = 81920, kOffVL = 90112;            // decayed v_new h
 constexpr uint32_t kOffX = 98304;                             // X panel (64 rows); the 64 rows before it are VL
 constexpr uint32_t kFwdSmem = 106496;
 constexpr uint32_t kColS = 0, kColRQ = 64, kColQK = 128, kColVN = 192;  // TMEM column map (256 columns)
+constexpr int kFwdThreads = 256;
 
 struct FwdPrefetch {
-  uint4 qk[16];
-  uint4 x[4];
-  uint4 v[8];
+  uint4 qk[8];
+  uint4 x[2];
+  uint4 v[4];
   float gb;
 };
 
-__global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
+__global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t bar;
 
-  const int tid = threadIdx.x, warp = tid / 32;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
   const int hk = hv / (p.HV / p.HK);
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
-  const bool kwarp = warp >= 2;          // warps 2,3 own the k-side rows (TMEM lanes 64..127)
-  const int row = tid;                   // TMEM lane == accumulator row
-  const int tok = tid & 63;              // token row inside the chunk for both halves
+  const int quad = warp & 3, half = warp >> 2;   // TMEM lane quadrant; which 32 of the tile's 64 columns
+  const bool kside = quad >= 2;                  // rows 64..127 hold the k-side results
+  const int row = quad * 32 + lane;              // TMEM lane == accumulator row
+  const int tok = row & 63;                      // token row inside the chunk
+  const int c0 = half * 32;
 
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 256);
@@ -215,8 +218,9 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
   uint32_t phase = 0;
+  bool dead = false;
   const uint32_t sb = smem_u32(smem);
 
   FwdPrefetch pf;
@@ -225,8 +229,8 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int idx = tid + i * 128;            // 0..2047: [q rows | k rows] x 16 chunks
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * kFwdThreads;            // 0..2047: [q rows | k rows] x 16 chunks
       const int r = (idx / 16) & 63, ch = idx % 16;
       const bool isk = idx >= 1024;
       pf.qk[i] = make_uint4(0, 0, 0, 0);
@@ -236,16 +240,16 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
       }
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int idx = tid + i * 128, r = idx / 8, ch = idx % 8;
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * kFwdThreads, r = idx / 8, ch = idx % 8;
       pf.x[i] = make_uint4(0, 0, 0, 0);
       if (r < rows) pf.x[i] = *reinterpret_cast<const uint4*>(p.X + ((tok0 + r) * p.HV + hv) * kC + ch * 8);
     }
-    if (kwarp) {
+    if (kside) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         pf.v[i] = make_uint4(0, 0, 0, 0);
-        if (tok < rows) pf.v[i] = *reinterpret_cast<const uint4*>(p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + i * 8);
+        if (tok < rows) pf.v[i] = *reinterpret_cast<const uint4*>(p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + c0 + i * 8);
       }
       pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
     } else {
@@ -253,26 +257,27 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
       pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
     }
   };
-  uint4 vcur[8];
-  auto prefetch_store = [&](int c) {
+  uint4 vcur[4];
+  auto store_scalars = [&](int c) {   // double-buffered by chunk parity: may be written while chunk c-1 is in flight
+    if (half == 0) {
+      if (kside) beta_s[c & 1][tok] = pf.gb;
+      else gam_s[c & 1][tok] = pf.gb;
+    }
+  };
+  auto store_panels = [&]() {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int idx = tid + i * 128;
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * kFwdThreads;
       const int r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
       *reinterpret_cast<uint4*>(smem + kOffQK + (ch / 8) * kQKPanel + panel_chunk_off(r, ch % 8)) = pf.qk[i];
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int idx = tid + i * 128;
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * kFwdThreads;
       *reinterpret_cast<uint4*>(smem + kOffX + panel_chunk_off(idx / 8, idx % 8)) = pf.x[i];
     }
-    if (kwarp) {
-      beta_s[c & 1][tok] = pf.gb;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) vcur[i] = pf.v[i];
-    } else {
-      gam_s[c & 1][tok] = pf.gb;
-    }
+    for (int i = 0; i < 4; ++i) vcur[i] = pf.v[i];
   };
 
   // operands (shared addresses)
@@ -285,22 +290,22 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
   const Operand opX{sb + kOffX - 8192, 16384, 0};               // rows 64..127 of this tile are X
   const Operand opPH{sb + kOffQK, kQKPanel, 0}, opPL{sb + kOffQK + kQKPanel, kQKPanel, 0};  // alias the q rows
 
-  bool ok = true;
-  float srow[kBV];
+  float srow[32];   // this thread's 32 columns of the fp32 state row
 
   // ---- prologue: chunk 0 operands and the initial state
   prefetch_load(0);
-  prefetch_store(0);
+  store_scalars(0);
+  store_panels();
   if (p.h0) {
-    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
 #pragma unroll
-    for (int i = 0; i < kBV; i += 4) {
+    for (int i = 0; i < 32; i += 4) {
       const float4 t = *reinterpret_cast<const float4*>(src + i);
       srow[i] = t.x; srow[i + 1] = t.y; srow[i + 2] = t.z; srow[i + 3] = t.w;
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < kBV; ++i) srow[i] = 0.f;
+    for (int i = 0; i < 32; ++i) srow[i] = 0.f;
   }
   __syncthreads();  // gam_s[0] visible
 
@@ -310,15 +315,17 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
     const float gam_last = gam_s[cur][rows - 1];
+    const float gam_i = gam_s[cur][tok];
 
     // ---- stage 0: publish the state at chunk start (split copy for the MMAs, pre-decayed master in TMEM)
-    row64_to_hilo(smem + kOffSH, smem + kOffSL, row, srow);
+    row32_to_hilo(smem + kOffSH, smem + kOffSL, row, half, srow);
     {
       const float dl = __expf(gam_last);
 #pragma unroll
-      for (int i = 0; i < kBV; ++i) srow[i] *= dl;
-      tmem_st_row64(trow + kColS, srow);
+      for (int i = 0; i < 32; ++i) srow[i] *= dl;
+      tmem_st_row32(trow + kColS, srow);
     }
+    if (tid == 0 && p.s_img) bulk_wait_read();  // the previous chunk's v_new images have left shared memory
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -337,31 +344,34 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
       mma_tile(tbase + kColQK, opQK, opKb, 128, 64, 8, false);
       mma_commit(&bar);
     }
-    if (c + 1 < sq.nt) prefetch_load(c + 1);
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
+    if (c + 1 < sq.nt) {
+      prefetch_load(c + 1);
+      store_scalars(c + 1);
+    }
+    wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
-    // ---- stage 2: K-side rows build Z = beta (V - exp(gam) K S); Q-side rows build P = tril(QK^T * decay)
-    float acc[kBV];
-    const float gam_i = gam_s[cur][tok];
-    if (kwarp) {
-      tmem_ld_row64(trow + kColRQ, acc);
+    // ---- stage 2: k-side rows build Z = beta (V - exp(gam) K S); q-side rows build P = tril(QK^T * decay)
+    float acc[32];
+    if (kside) {
+      tmem_ld_row32(trow + kColRQ, acc);
       const float eg = __expf(gam_i), bi = beta_s[cur][tok];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         float vv[8];
         unpack_bf16x8(vcur[i], vv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i * 8 + j] = bi * (vv[j] - eg * acc[i * 8 + j]);
       }
-      row64_to_hilo(smem + kOffZH, smem + kOffZL, tok, acc);
+      row32_to_hilo(smem + kOffZH, smem + kOffZL, tok, half, acc);
     } else {
-      tmem_ld_row64(trow + kColQK, acc);
+      tmem_ld_row32(trow + kColQK, acc);
 #pragma unroll
-      for (int j = 0; j < kC; ++j) acc[j] = (j <= tok) ? acc[j] * __expf(gam_i - gam_s[cur][j]) : 0.f;
-      row64_to_hilo(smem + kOffQK, smem + kOffQK + kQKPanel, tok, acc);
+      for (int jj = 0; jj < 32; ++jj) {
+        const int j = c0 + jj;
+        acc[jj] = (j <= tok) ? acc[jj] * __expf(gam_i - gam_s[cur][j]) : 0.f;
+      }
+      row32_to_hilo(smem + kOffQK, smem + kOffQK + kQKPanel, tok, half, acc);
     }
     fence_async_smem();
     tc_fence_before();
@@ -374,20 +384,19 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
       mma_tile(tbase + kColVN, opX, opZL, 128, 64, 4, true);
       mma_commit(&bar);
     }
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
+    wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
-    // ---- stage 4: K-side rows publish v_new and its decayed copy
-    if (kwarp) {
-      tmem_ld_row64(trow + kColVN, acc);
-      row64_to_hilo(smem + kOffZH, smem + kOffZL, tok, acc);
+    // ---- stage 4: k-side rows publish v_new and its decayed copy
+    if (kside) {
+      tmem_ld_row32(trow + kColVN, acc);
+      row32_to_hilo(smem + kOffZH, smem + kOffZL, tok, half, acc);
       const float dk = __expf(gam_last - gam_i);
 #pragma unroll
-      for (int i = 0; i < kBV; ++i) acc[i] *= dk;
-      row64_to_hilo(smem + kOffVH, smem + kOffVL, tok, acc);
+      for (int i = 0; i < 32; ++i) acc[i] *= dk;
+      row32_to_hilo(smem + kOffVH, smem + kOffVL, tok, half, acc);
     }
+    if (tid == 0 && p.s_img) bulk_wait_read();  // this chunk's state images have left shared memory
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -408,47 +417,41 @@ __global__ void __launch_bounds__(128, 2) gdn_fwd_kernel(GdnFwdParams p) {
       mma_tile(tbase + kColS, opKT, opVL, 128, 64, 4, true);
       mma_commit(&bar);
     }
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
+    wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
-    // ---- stage 6: output rows, next state, next chunk's operands
-    if (!kwarp) {
+    // ---- stage 6: output rows, next state, next chunk's operand panels
+    if (!kside) {
+      float qs[32];
+      tmem_ld32(trow + kColRQ, qs);
+      tmem_ld32(trow + kColQK, acc);
+      tmem_ld_wait();
       const float eg = __expf(gam_i) * p.scale;
-      const int64_t off = (tok0 + tok) * p.o_st + hv * p.o_sh + vb * kBV;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float qs[32], pv[32];
-        tmem_ld32(trow + kColRQ + half * 32, qs);
-        tmem_ld32(trow + kColQK + half * 32, pv);
-        tmem_ld_wait();
+      for (int i = 0; i < 32; ++i) acc[i] = eg * qs[i] + p.scale * acc[i];
+      if (tok < rows) {
+        const int64_t off = (tok0 + tok) * p.o_st + hv * p.o_sh + vb * kBV + c0;
+        if (p.o_is_f32) {
+          float* dst = static_cast<float*>(p.o) + off;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) pv[i] = eg * qs[i] + p.scale * pv[i];
-        if (tok < rows) {
-          if (p.o_is_f32) {
-            float* dst = static_cast<float*>(p.o) + off + half * 32;
+          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+        } else {
+          bf16* dst = static_cast<bf16*>(p.o) + off;
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(pv[i], pv[i + 1], pv[i + 2], pv[i + 3]);
-          } else {
-            bf16* dst = static_cast<bf16*>(p.o) + off + half * 32;
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(pv + ch * 8);
-          }
+          for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(acc + ch * 8);
         }
       }
     }
-    tmem_ld_row64(trow + kColS, srow);
-    if (c + 1 < sq.nt) prefetch_store(c + 1);
-    if (tid == 0 && p.s_img) bulk_wait_read();  // saved images have left shared memory before it is reused
-    tc_fence_before();
-    __syncthreads();  // next chunk's gam_s / beta_s visible; all TMEM reads of this chunk retired
+    tmem_ld_row32(trow + kColS, srow);
+    // The only readers of the q/k/X panels were this chunk's MMAs, which have completed; no barrier is needed
+    // before the next iteration (its first barrier orders everything else).
+    if (c + 1 < sq.nt) store_panels();
   }
 
-  if (ok && p.ht) {
-    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+  if (!dead && p.ht) {
+    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
 #pragma unroll
-    for (int i = 0; i < kBV; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
   if (tid == 0 && p.s_img) bulk_wait_all();
   tc_fence_before();
@@ -574,7 +577,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_fwd", cs);
-    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), 128, kFwdSmem + 1024, cs>>>(p);
+    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p);
   }
   return cuda_status(cudaGetLastError());
 }

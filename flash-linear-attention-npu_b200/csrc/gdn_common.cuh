@@ -78,4 +78,35 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* f) {
   }
 }
 
+// 32 consecutive fp32 accumulator columns of this thread's TMEM lane <-> registers / split bf16 panels.
+__device__ __forceinline__ void tmem_ld_row32(uint32_t taddr, float* v) {
+  tmem_ld32(taddr, v);
+  tmem_ld_wait();
+}
+__device__ __forceinline__ void tmem_st_row32(uint32_t taddr, const float* v) {
+  tmem_st16(taddr, v);
+  tmem_st16(taddr + 16, v + 16);
+  tmem_st_wait();
+}
+// columns [32*half, 32*half + 32) of `row`
+__device__ __forceinline__ void row32_to_hilo(uint8_t* pan_hi, uint8_t* pan_lo, int row, int half, const float* x) {
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint4 hi, lo;
+    split8(x + ch * 8, hi, lo);
+    const uint32_t off = panel_chunk_off(row, half * 4 + ch);
+    *reinterpret_cast<uint4*>(pan_hi + off) = hi;
+    *reinterpret_cast<uint4*>(pan_lo + off) = lo;
+  }
+}
+
+
+// A wait that gives up records the timeout once; afterwards the thread stops waiting so that the kernel
+// still terminates quickly (its results are then invalid, which the status word tells the host).
+__device__ __forceinline__ void wait_or_mark(uint64_t* bar, uint32_t& phase, bool& dead, int* status) {
+  if (!dead && !mbar_wait(bar, phase, status, 8 /* FLA_ERR_TIMEOUT */)) dead = true;
+  phase ^= 1;
+}
+
+
 }  // namespace fla

@@ -1,0 +1,633 @@
+// Chunked Kimi-Delta-Attention forward (per-channel log gate g[t, h, :], chunk = 64, K = V = 128).
+//
+//   gk = chunk-local cumsum(gate(g));   with a per-channel anchor a = gk at the middle token of the chunk:
+//   Qp = Q * e^{gk - a}   Kp = K * e^{gk - a}   Kn = K * e^{a - gk}        (all finite for any realistic decay)
+//   Aqk = tril(Qp Kn^T)   Akk = strict_tril(beta_i Kp Kn^T)   X = (I + Akk)^-1
+//   per chunk, Sa = diag(e^a) S:   v_new = X (beta * (V - Kp Sa))
+//                                  o     = scale (Qp Sa + Aqk v_new)
+//                                  S    <- diag(e^{gk_L - a}) (Sa + Kn^T v_new)
+// which equals the reference's chunk_kda_fwd stages (gate cumsum -> Prepare -> Post-WU -> FwdH -> Finalize,
+// fla/ops/ascendc/kda/chunk_kda_fwd/docs/design.md:11-78; golden tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:402-530)
+// with w, u folded away.  The decay sits inside the K reduction, so the scaled operands cannot be the exact
+// bf16 inputs: kda_prep_kernel (parallel over chunks) builds them once as bf16 hi + residual operand panels,
+// computes both score tiles on tcgen05 and the inverse on CUDA cores, and stores everything as ready-to-load
+// panel images; kda_fwd_kernel (sequential over chunks, fp32 state in TMEM) only bulk-loads them.
+#include "gdn_common.cuh"
+#include "fla_b200_internal.h"
+#include "kernel_timer.h"
+
+namespace fla {
+
+struct KdaParams {
+  const bf16* q; const bf16* k; const bf16* v;
+  const void* g; const void* beta;
+  const float* a_log; const float* dt_bias;   // optional gate parameters: [HV], [HV, K]
+  float* gk_out;        // [tokens, HV, K] cumulative gate (optional)
+  bf16* qk_img;         // [chunks, HV, {hi, lo}, 2 panels x 128 rows]  rows 0-63 Qp, rows 64-127 Kp
+  bf16* kn_img;         // [chunks, HV, {hi, lo}, 2 panels x 64 rows]
+  bf16* p_img;          // [chunks, HV, {hi, lo}, 64 x 64]   tril(Qp Kn^T)
+  bf16* x_img;          // [chunks, HV, 64 x 64]             (I + Akk)^-1
+  float* vec;           // [chunks, HV, 2, K]  e^a, e^{gk_L - a}
+  const float* h0; float* ht;
+  void* o;
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int64_t q_st, q_sh, k_st, k_sh, v_st, v_sh, o_st, o_sh, g_st, g_sh, beta_st;
+  int N, T, HK, HV, g_is_f32, beta_is_f32, o_is_f32, gate_mode;
+  float scale, lower_bound;
+  int* status;
+};
+
+constexpr int64_t kKdaQkImg = 32768, kKdaKnImg = 16384, kKdaPImg = 8192, kKdaXImg = 4096;
+
+// --------------------------------------------------------------------------------------------- prep
+constexpr uint32_t pOffQKH = 0, pOffQKL = 32768, pOffKNH = 65536, pOffKNL = 81920;
+constexpr uint32_t pOffGK = 98304;                 // fp32 [64][129] cumulative gates; later the score tile / P / X panels
+constexpr int kGkStride = 129;
+constexpr int kAStrideKda = 68;
+constexpr uint32_t kKdaPrepSmem = 98304 + 34816;   // operand panels + max(gate tile, P panels + A^T)
+
+__device__ __forceinline__ float kda_gate(float g, int mode, float eig, float bias, float lower_bound) {
+  if (mode == 0) return g;
+  const float raw = g + bias;
+  if (mode == 1) {  // -exp(A_log) * softplus(g + dt_bias)
+    const float sp = raw > 20.f ? raw : log1pf(__expf(raw));
+    return -eig * sp;
+  }
+  return lower_bound / (1.f + __expf(-eig * raw));  // lower_bound * sigmoid(exp(A_log) (g + dt_bias))
+}
+
+__global__ void __launch_bounds__(256, 1) kda_prep_kernel(KdaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* gk_s = reinterpret_cast<float*>(smem + pOffGK);
+  __shared__ float anchor_s[kK], beta_s[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int hv = blockIdx.y, n = blockIdx.z;
+  const int hk = hv / (p.HV / p.HK);
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const int c = blockIdx.x;
+  if (c >= sq.nt) return;
+  const int t0 = c * kC;
+  const int rows = min(kC, sq.len - t0);
+  const int64_t tok0 = int64_t(sq.bos) + t0;
+  const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 64);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  // 1. gate tile -> shared (activated), zero past the end of the sequence
+  {
+    const float eig = (p.gate_mode && p.a_log) ? __expf(p.a_log[hv]) : 1.f;
+    for (int idx = tid; idx < kC * kK; idx += 256) {
+      const int t = idx / kK, r = idx % kK;
+      float gv = 0.f;
+      if (t < rows) {
+        const float raw = ld_scalar(p.g, (tok0 + t) * p.g_st + hv * p.g_sh + r, p.g_is_f32);
+        const float bias = (p.gate_mode && p.dt_bias) ? p.dt_bias[hv * kK + r] : 0.f;
+        gv = kda_gate(raw, p.gate_mode, eig, bias, p.lower_bound);
+      }
+      gk_s[t * kGkStride + r] = gv;
+    }
+    if (tid < kC) beta_s[tid] = tid < rows ? ld_scalar(p.beta, (tok0 + tid) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+  }
+  __syncthreads();
+  // 2. per-channel prefix sum over the chunk's tokens; anchor and boundary factors
+  if (tid < kK) {
+    float acc = 0.f;
+    for (int t = 0; t < kC; ++t) {
+      acc += gk_s[t * kGkStride + tid];       // zero gates past the end keep the last valid value
+      gk_s[t * kGkStride + tid] = acc;
+    }
+    const float a = gk_s[min(kC / 2 - 1, rows - 1) * kGkStride + tid];
+    const float gl = gk_s[(rows - 1) * kGkStride + tid];
+    anchor_s[tid] = a;
+    p.vec[cidx * 2 * kK + tid] = __expf(a);
+    p.vec[cidx * 2 * kK + kK + tid] = __expf(gl - a);
+  }
+  __syncthreads();
+  // 3. scaled operands as split bf16 panels
+  for (int idx = tid; idx < kC * 16; idx += 256) {
+    const int t = idx / 16, ch = idx % 16;
+    float qv[8], kv[8], qp[8], kp[8], kn[8];
+    uint4 qraw = make_uint4(0, 0, 0, 0), kraw = qraw;
+    if (t < rows) {
+      qraw = *reinterpret_cast<const uint4*>(p.q + (tok0 + t) * p.q_st + hk * p.q_sh + ch * 8);
+      kraw = *reinterpret_cast<const uint4*>(p.k + (tok0 + t) * p.k_st + hk * p.k_sh + ch * 8);
+    }
+    unpack_bf16x8(qraw, qv);
+    unpack_bf16x8(kraw, kv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = ch * 8 + j;
+      const float d = gk_s[t * kGkStride + r] - anchor_s[r];
+      const float e1 = __expf(d), e2 = __expf(-d);
+      qp[j] = qv[j] * e1; kp[j] = kv[j] * e1; kn[j] = kv[j] * e2;
+    }
+    if (p.gk_out && t < rows) {
+      float* dst = p.gk_out + ((tok0 + t) * p.HV + hv) * kK + ch * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[j] = gk_s[t * kGkStride + ch * 8 + j];
+    }
+    uint4 hi, lo;
+    const uint32_t pan = (ch / 8) * 16384, pan64 = (ch / 8) * 8192;
+    split8(qp, hi, lo);
+    *reinterpret_cast<uint4*>(smem + pOffQKH + pan + panel_chunk_off(t, ch % 8)) = hi;
+    *reinterpret_cast<uint4*>(smem + pOffQKL + pan + panel_chunk_off(t, ch % 8)) = lo;
+    split8(kp, hi, lo);
+    *reinterpret_cast<uint4*>(smem + pOffQKH + pan + panel_chunk_off(64 + t, ch % 8)) = hi;
+    *reinterpret_cast<uint4*>(smem + pOffQKL + pan + panel_chunk_off(64 + t, ch % 8)) = lo;
+    split8(kn, hi, lo);
+    *reinterpret_cast<uint4*>(smem + pOffKNH + pan64 + panel_chunk_off(t, ch % 8)) = hi;
+    *reinterpret_cast<uint4*>(smem + pOffKNL + pan64 + panel_chunk_off(t, ch % 8)) = lo;
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t sb = smem_u32(smem);
+  // 4. save the operand images; both score tiles in one M = 128 product: rows 0-63 Qp Kn^T, rows 64-127 Kp Kn^T
+  if (tid == 0) {
+    bulk_store(p.qk_img + cidx * kKdaQkImg, sb + pOffQKH, 65536);
+    bulk_store(p.kn_img + cidx * kKdaKnImg, sb + pOffKNH, 32768);
+    bulk_commit();
+    const Operand aH{sb + pOffQKH, 16384, 0}, aL{sb + pOffQKL, 16384, 0};
+    const Operand bH{sb + pOffKNH, 8192, 0}, bL{sb + pOffKNL, 8192, 0};
+    mma_tile(tbase, aH, bH, 128, 64, 8, false);
+    mma_tile(tbase, aH, bL, 128, 64, 8, true);
+    mma_tile(tbase, aL, bH, 128, 64, 8, true);
+    mma_commit(&bar);
+  }
+  const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
+  tc_fence_after();
+  // 5. q-side rows: P = tril(Aqk) as split panels; k-side rows: A^T for the triangular solve.
+  //    Both reuse the gate tile's memory (all readers of gk_s are past the barrier above).
+  uint8_t* p_hi = smem + pOffGK;             // 8 KB
+  uint8_t* p_lo = smem + pOffGK + 8192;      // 8 KB
+  float* AT = reinterpret_cast<float*>(smem + pOffGK + 16384);   // [64][68] fp32, AT[j][i] = A[i][j]
+  const int quad = warp & 3, half = warp >> 2, row = quad * 32 + lane, tok = row & 63;
+  if (ok) {
+    float sc[32];
+    tmem_ld32(tmem_addr(tbase, quad * 32, half * 32), sc);
+    tmem_ld_wait();
+    if (quad < 2) {
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) sc[jj] = (half * 32 + jj <= tok) ? sc[jj] : 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint4 hi, lo;
+        split8(sc + ch * 8, hi, lo);
+        const uint32_t off = panel_chunk_off(tok, half * 4 + ch);
+        *reinterpret_cast<uint4*>(p_hi + off) = hi;
+        *reinterpret_cast<uint4*>(p_lo + off) = lo;
+      }
+    } else {
+      const float bi = beta_s[tok];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        const int j = half * 32 + jj;
+        if (j < tok) AT[j * kAStrideKda + tok] = bi * sc[jj];
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 64);
+  if (!ok) return;
+  if (tid == 0) {
+    bulk_store(p.p_img + cidx * kKdaPImg, smem_u32(p_hi), 16384);
+    bulk_commit();
+  }
+  // 6. X = (I + A)^-1, column c per thread (right-looking forward substitution), written as a 64x64 bf16 panel
+  uint8_t* x_pan = smem + pOffQKH;   // the operand panels have been handed to the bulk store engine: wait before reuse
+  if (tid == 0) bulk_wait_read();
+  __syncthreads();
+  if (tid < kC) {
+    const int cc = tid;
+    float x[kC];
+#pragma unroll
+    for (int i = 0; i < kC; ++i) x[i] = (i == cc) ? 1.f : 0.f;
+    const int jmin = cc & ~31;
+#pragma unroll
+    for (int j = 0; j < kC - 1; ++j) {
+      if (j >= jmin) {
+        const float xj = x[j];
+        const float* col = AT + j * kAStrideKda;
+#pragma unroll
+        for (int i4 = (j + 1) & ~3; i4 < kC; i4 += 4) {
+          const float4 a4 = *reinterpret_cast<const float4*>(col + i4);
+          if (i4 > j) x[i4] -= a4.x * xj;
+          if (i4 + 1 > j) x[i4 + 1] -= a4.y * xj;
+          if (i4 + 2 > j) x[i4 + 2] -= a4.z * xj;
+          if (i4 + 3 > j) x[i4 + 3] -= a4.w * xj;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kC; ++i)
+      *reinterpret_cast<bf16*>(x_pan + panel_off(i, cc)) = __float2bfloat16_rn(i < rows ? x[i] : 0.f);
+  }
+  fence_async_smem();
+  __syncthreads();
+  if (tid == 0) {
+    bulk_store(p.x_img + cidx * kKdaXImg, smem_u32(x_pan), 8192);
+    bulk_commit();
+    bulk_wait_all();
+  }
+}
+
+// --------------------------------------------------------------------------------------------- forward
+constexpr uint32_t fOffQKH = 0, fOffQKL = 32768, fOffKNH = 65536, fOffKNL = 81920;
+constexpr uint32_t fOffPH = 98304, fOffPL = 106496, fOffX = 114688;
+constexpr uint32_t fOffSH = 122880, fOffSL = 139264, fOffZH = 155648, fOffZL = 163840;
+constexpr uint32_t kKdaFwdSmem = 172032;
+constexpr uint32_t fColS = 0, fColRQ = 64, fColPV = 128, fColVN = 192;
+
+__global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ float vec_s[2][2][kK];     // [chunk parity][e^a | e^{gk_L - a}][channel]
+  __shared__ float beta_s[2][kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar, load1_bar, load2_bar;
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const int quad = warp & 3, half = warp >> 2;
+  const bool kside = quad >= 2;
+  const int row = quad * 32 + lane, tok = row & 63, c0 = half * 32;
+
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init(&load1_bar, 1);
+    mbar_init(&load2_bar, 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
+  const uint32_t sb = smem_u32(smem);
+  uint32_t mphase = 0, l1phase = 0, l2phase = 0;
+  bool dead = false;
+
+  auto issue_load1 = [&](int c) {   // [Qp; Kp] hi + lo
+    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+    mbar_arrive_expect_tx(&load1_bar, 65536);
+    bulk_load(sb + fOffQKH, p.qk_img + cidx * kKdaQkImg, 65536, &load1_bar);
+  };
+  auto issue_load2 = [&](int c) {   // Kn hi + lo, P hi + lo, X
+    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+    mbar_arrive_expect_tx(&load2_bar, 32768 + 16384 + 8192);
+    bulk_load(sb + fOffKNH, p.kn_img + cidx * kKdaKnImg, 32768, &load2_bar);
+    bulk_load(sb + fOffPH, p.p_img + cidx * kKdaPImg, 16384, &load2_bar);
+    bulk_load(sb + fOffX, p.x_img + cidx * kKdaXImg, 8192, &load2_bar);
+  };
+  if (tid == 0) {
+    issue_load1(0);
+    issue_load2(0);
+  }
+
+  const Operand opQKH{sb + fOffQKH, 16384, 0}, opQKL{sb + fOffQKL, 16384, 0};
+  const Operand opKNTh{sb + fOffKNH, 8192, 1}, opKNTl{sb + fOffKNL, 8192, 1};   // Kn^T: M = 128 key dims
+  const Operand opSH{sb + fOffSH, 16384, 1}, opSL{sb + fOffSL, 16384, 1};
+  const Operand opZH{sb + fOffZH, 8192, 1}, opZL{sb + fOffZL, 8192, 1};
+  const Operand opX{sb + fOffX - 8192, 16384, 0};               // rows 64..127 of this tile are X
+  const Operand opPH{sb + fOffPH, 16384, 0}, opPL{sb + fOffPL, 16384, 0};       // rows 0..63 are P
+
+  // per-chunk scalars / vectors / value rows are staged through registers one chunk ahead
+  float pf_vec = 0.f, pf_beta = 0.f;
+  uint4 pf_v[4], vcur[4];
+  auto prefetch_load = [&](int c) {
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+    pf_vec = p.vec[cidx * 2 * kK + tid];                       // 256 threads: e^a then e^{gk_L - a}
+    if (kside) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        pf_v[i] = make_uint4(0, 0, 0, 0);
+        if (tok < rows) pf_v[i] = *reinterpret_cast<const uint4*>(p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + c0 + i * 8);
+      }
+      pf_beta = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    }
+  };
+  auto store_scalars = [&](int c) {   // double-buffered by chunk parity: safe to write while chunk c-1 is in flight
+    vec_s[c & 1][tid / kK][tid % kK] = pf_vec;
+    if (kside && half == 0) beta_s[c & 1][tok] = pf_beta;
+  };
+  auto take_values = [&]() {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) vcur[i] = pf_v[i];
+  };
+
+  float srow[32];
+  prefetch_load(0);
+  store_scalars(0);
+  take_values();
+  if (p.h0) {
+    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(src + i);
+      srow[i] = t.x; srow[i + 1] = t.y; srow[i + 2] = t.z; srow[i + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) srow[i] = 0.f;
+  }
+  __syncthreads();
+
+  for (int c = 0; c < sq.nt; ++c) {
+    const int cur = c & 1;
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+
+    // ---- stage 0: Sa = diag(e^a) S as split copy and as the fp32 master in TMEM
+    {
+      const float ea = vec_s[cur][0][row];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) srow[i] *= ea;
+      row32_to_hilo(smem + fOffSH, smem + fOffSL, row, half, srow);
+      tmem_st16(trow + fColS, srow);
+      tmem_st16(trow + fColS + 16, srow + 16);
+      tmem_st_wait();
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 1: [Qp; Kp] Sa
+    if (!dead && !mbar_wait(&load1_bar, l1phase, p.status, FLA_ERR_TIMEOUT)) dead = true;
+    l1phase ^= 1;
+    if (tid == 0) {
+      mma_tile(tbase + fColRQ, opQKH, opSH, 128, 64, 8, false);
+      mma_tile(tbase + fColRQ, opQKH, opSL, 128, 64, 8, true);
+      mma_tile(tbase + fColRQ, opQKL, opSH, 128, 64, 8, true);
+      mma_commit(&mma_bar);
+    }
+    if (c + 1 < sq.nt) {
+      prefetch_load(c + 1);
+      store_scalars(c + 1);
+    }
+    if (!dead && !mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT)) dead = true;
+    mphase ^= 1;
+    tc_fence_after();
+    if (tid == 0 && c + 1 < sq.nt) issue_load1(c + 1);   // the [Qp; Kp] buffers are free again
+
+    // ---- stage 2: k-side rows: Z = beta (V - Kp Sa)
+    float acc[32];
+    if (kside) {
+      tmem_ld32(trow + fColRQ, acc);
+      tmem_ld_wait();
+      const float bi = beta_s[cur][tok];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float vv[8];
+        unpack_bf16x8(vcur[i], vv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i * 8 + j] = bi * (vv[j] - acc[i * 8 + j]);
+      }
+      row32_to_hilo(smem + fOffZH, smem + fOffZL, tok, half, acc);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 3: v_new = X Z
+    if (!dead && !mbar_wait(&load2_bar, l2phase, p.status, FLA_ERR_TIMEOUT)) dead = true;
+    l2phase ^= 1;
+    if (tid == 0) {
+      mma_tile(tbase + fColVN, opX, opZH, 128, 64, 4, false);
+      mma_tile(tbase + fColVN, opX, opZL, 128, 64, 4, true);
+      mma_commit(&mma_bar);
+    }
+    if (!dead && !mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT)) dead = true;
+    mphase ^= 1;
+    tc_fence_after();
+
+    // ---- stage 4: k-side rows publish v_new
+    if (kside) {
+      tmem_ld32(trow + fColVN, acc);
+      tmem_ld_wait();
+      row32_to_hilo(smem + fOffZH, smem + fOffZL, tok, half, acc);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- stage 5: Aqk v_new and the state update Sa += Kn^T v_new
+    if (tid == 0) {
+      mma_tile(tbase + fColPV, opPH, opZH, 128, 64, 4, false);
+      mma_tile(tbase + fColPV, opPH, opZL, 128, 64, 4, true);
+      mma_tile(tbase + fColPV, opPL, opZH, 128, 64, 4, true);
+      mma_tile(tbase + fColS, opKNTh, opZH, 128, 64, 4, true);
+      mma_tile(tbase + fColS, opKNTh, opZL, 128, 64, 4, true);
+      mma_tile(tbase + fColS, opKNTl, opZH, 128, 64, 4, true);
+      mma_commit(&mma_bar);
+    }
+    if (!dead && !mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT)) dead = true;
+    mphase ^= 1;
+    tc_fence_after();
+    if (tid == 0 && c + 1 < sq.nt) issue_load2(c + 1);
+
+    // ---- stage 6: output rows; next state S = diag(e^{gk_L - a}) (Sa + Kn^T v_new)
+    if (!kside) {
+      float qs[32];
+      tmem_ld32(trow + fColRQ, qs);
+      tmem_ld32(trow + fColPV, acc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = p.scale * (qs[i] + acc[i]);
+      if (tok < rows) {
+        const int64_t off = (tok0 + tok) * p.o_st + hv * p.o_sh + vb * kBV + c0;
+        if (p.o_is_f32) {
+          float* dst = static_cast<float*>(p.o) + off;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+        } else {
+          bf16* dst = static_cast<bf16*>(p.o) + off;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(acc + ch * 8);
+        }
+      }
+    }
+    tmem_ld32(trow + fColS, srow);
+    tmem_ld_wait();
+    {
+      const float el = vec_s[cur][1][row];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) srow[i] *= el;
+    }
+    if (c + 1 < sq.nt) take_values();
+  }
+
+  if (!dead && p.ht) {
+    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+}  // namespace fla
+
+using namespace fla;
+
+static uint64_t kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[5]) {
+  uint64_t o = 256;
+  const uint64_t per = uint64_t(total_chunks) * HV;
+  off[0] = o; o += align_up(per * kKdaQkImg * 2, 256);
+  off[1] = o; o += align_up(per * kKdaKnImg * 2, 256);
+  off[2] = o; o += align_up(per * kKdaPImg * 2, 256);
+  off[3] = o; o += align_up(per * kKdaXImg * 2, 256);
+  off[4] = o; o += align_up(per * 2 * kK * 4, 256);
+  return o;
+}
+
+static int kda_geometry(const fla_kda_chunk_fwd_args* a, int64_t* total_chunks, int* N, int* max_len) {
+  const fla_tensor_t& q = a->q;
+  if (!q.data || q.ndim != 4 || !a->v.data || a->v.ndim != 4) return FLA_ERR_SHAPE;
+  const int64_t B = q.shape[0], T = q.shape[1];
+  *N = int(B);
+  *total_chunks = B * ((T + kC - 1) / kC);
+  *max_len = int(T);
+  if (a->cu_seqlens.data) {
+    if (B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    *N = int(a->cu_seqlens.shape[0] - 1);
+    if (!a->chunk_offsets.data || a->chunk_offsets.dtype != FLA_I32 || a->chunk_offsets.shape[0] != *N + 1) return FLA_ERR_SHAPE;
+    if (a->max_seqlen <= 0 || a->max_seqlen > T || a->total_chunks <= 0) return FLA_ERR_VALUE;
+    *max_len = a->max_seqlen;
+    *total_chunks = a->total_chunks;
+  }
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_kda_chunk_fwd_workspace_size(const fla_kda_chunk_fwd_args* a, uint64_t* bytes) {
+  if (!a || !bytes) return FLA_ERR_NULL;
+  int64_t total_chunks; int N, max_len;
+  const int st = kda_geometry(a, &total_chunks, &N, &max_len);
+  if (st) return st;
+  uint64_t off[5];
+  *bytes = kda_ws_layout(total_chunks, a->v.shape[2], off);
+  return FLA_OK;
+}
+
+static int kda_check_tok(const fla_tensor_t& t, int64_t B, int64_t T, int64_t heads, int64_t dim, bool allow_f32) {
+  if (!t.data) return FLA_ERR_NULL;
+  if (t.ndim != 4 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != heads || t.shape[3] != dim) return FLA_ERR_SHAPE;
+  if (t.dtype != FLA_BF16 && !(allow_f32 && t.dtype == FLA_F32)) return FLA_ERR_DTYPE;
+  const int64_t esz = t.dtype == FLA_F32 ? 4 : 2;
+  if (t.stride[3] != 1 || (t.stride[2] * esz) % 16 || (t.stride[1] * esz) % 16 || !aligned16(t.data)) return FLA_ERR_LAYOUT;
+  if (B > 1 && t.stride[0] != T * t.stride[1]) return FLA_ERR_LAYOUT;
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, void* workspace, uint64_t workspace_bytes,
+                                              void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  int64_t total_chunks; int N, max_len;
+  int st = kda_geometry(a, &total_chunks, &N, &max_len);
+  if (st) return st;
+  const int64_t B = a->q.shape[0], T = a->q.shape[1], HK = a->q.shape[2], HV = a->v.shape[2];
+  if (HK <= 0 || HV <= 0 || HV % HK) return FLA_ERR_SHAPE;
+  if ((st = kda_check_tok(a->q, B, T, HK, kK, false))) return st;
+  if ((st = kda_check_tok(a->k, B, T, HK, kK, false))) return st;
+  if ((st = kda_check_tok(a->v, B, T, HV, kV, false))) return st;
+  if ((st = kda_check_tok(a->g, B, T, HV, kK, true))) return st;
+  if ((st = kda_check_tok(a->o, B, T, HV, kV, true))) return st;
+  const fla_tensor_t& be = a->beta;
+  if (!be.data) return FLA_ERR_NULL;
+  if (be.ndim != 3 || be.shape[0] != B || be.shape[1] != T || be.shape[2] != HV || be.stride[2] != 1 ||
+      (B > 1 && be.stride[0] != T * be.stride[1]))
+    return FLA_ERR_SHAPE;
+  if (be.dtype != FLA_F32 && be.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  for (const fla_tensor_t* s : {&a->initial_state, &a->final_state}) {
+    if (!s->data) continue;
+    if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
+    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != HV * kK * kV || !aligned16(s->data))
+      return FLA_ERR_LAYOUT;
+  }
+  if (a->gate_mode < 0 || a->gate_mode > 2) return FLA_ERR_VALUE;
+  if (a->gate_mode) {
+    if (!a->a_log.data || a->a_log.dtype != FLA_F32 || a->a_log.ndim != 1 || a->a_log.shape[0] != HV || a->a_log.stride[0] != 1)
+      return FLA_ERR_SHAPE;
+    if (a->dt_bias.data && (a->dt_bias.dtype != FLA_F32 || a->dt_bias.ndim != 2 || a->dt_bias.shape[0] != HV ||
+                            a->dt_bias.shape[1] != kK || a->dt_bias.stride[1] != 1 || a->dt_bias.stride[0] != kK))
+      return FLA_ERR_SHAPE;
+  }
+  if (a->gk.data) {
+    const fla_tensor_t& gk = a->gk;
+    if (gk.dtype != FLA_F32 || gk.ndim != 4 || gk.shape[0] != B || gk.shape[1] != T || gk.shape[2] != HV || gk.shape[3] != kK ||
+        gk.stride[3] != 1 || gk.stride[2] != kK || gk.stride[1] != HV * kK || (B > 1 && gk.stride[0] != T * HV * kK))
+      return FLA_ERR_SHAPE;
+  }
+  if (a->chunk_size != kC) return FLA_ERR_VALUE;
+  uint64_t off[5];
+  const uint64_t need = kda_ws_layout(total_chunks, HV, off);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
+
+  KdaParams p{};
+  p.q = static_cast<const bf16*>(a->q.data); p.k = static_cast<const bf16*>(a->k.data); p.v = static_cast<const bf16*>(a->v.data);
+  p.g = a->g.data; p.beta = be.data;
+  p.a_log = static_cast<const float*>(a->a_log.data); p.dt_bias = static_cast<const float*>(a->dt_bias.data);
+  p.gk_out = static_cast<float*>(a->gk.data);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.qk_img = reinterpret_cast<bf16*>(ws + off[0]); p.kn_img = reinterpret_cast<bf16*>(ws + off[1]);
+  p.p_img = reinterpret_cast<bf16*>(ws + off[2]); p.x_img = reinterpret_cast<bf16*>(ws + off[3]);
+  p.vec = reinterpret_cast<float*>(ws + off[4]);
+  p.h0 = static_cast<const float*>(a->initial_state.data); p.ht = static_cast<float*>(a->final_state.data);
+  p.o = a->o.data;
+  p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+  p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
+  p.q_st = a->q.stride[1]; p.q_sh = a->q.stride[2]; p.k_st = a->k.stride[1]; p.k_sh = a->k.stride[2];
+  p.v_st = a->v.stride[1]; p.v_sh = a->v.stride[2]; p.o_st = a->o.stride[1]; p.o_sh = a->o.stride[2];
+  p.g_st = a->g.stride[1]; p.g_sh = a->g.stride[2]; p.beta_st = be.stride[1];
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV);
+  p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = be.dtype == FLA_F32; p.o_is_f32 = a->o.dtype == FLA_F32;
+  p.gate_mode = a->gate_mode; p.scale = a->scale; p.lower_bound = a->lower_bound;
+
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
+  static bool attr_done_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (!attr_done_dev[dev]) {
+    if (cudaFuncSetAttribute(kda_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaPrepSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(kda_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    attr_done_dev[dev] = true;
+  }
+  const int nt_max = (max_len + kC - 1) / kC;
+  {
+    KernelTimer kt("kda_prep", cs);
+    kda_prep_kernel<<<dim3(nt_max, unsigned(HV), N), 256, kKdaPrepSmem + 1024, cs>>>(p);
+  }
+  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  {
+    KernelTimer kt("kda_fwd", cs);
+    kda_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), 256, kKdaFwdSmem + 1024, cs>>>(p);
+  }
+  return cuda_status(cudaGetLastError());
+}

@@ -219,6 +219,33 @@ FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* args, void* wor
 FLA_API int fla_b200_gdn_chunk_bwd_static_scratch_bytes(uint64_t* bytes);
 FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_args* args, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Chunked Kimi Delta Attention, forward (per-channel log gate, chunk = 64, K = V = 128).
+ * Replaces aclnnKdaGateCumsum + aclnnChunkKdaFwd as bound by npu_kda_gate_cumsum / npu_chunk_kda_fwd
+ * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1268-1296, 1066-1265; stages in
+ * fla/ops/ascendc/kda/chunk_kda_fwd/docs/design.md:11-78).
+ *   q, k [B, T, HK, 128] bf16;  v [B, T, HV, 128] bf16;  g [B, T, HV, 128] f32|bf16;  beta [B, T, HV] f32|bf16
+ *   gate_mode 0: g is the log decay;  1: -exp(a_log[h]) * softplus(g + dt_bias[h, :]);
+ *             2: lower_bound * sigmoid(exp(a_log[h]) * (g + dt_bias[h, :]))   (a_log [HV] f32, dt_bias [HV, 128] f32 optional)
+ *   o [B, T, HV, 128] bf16|f32;  initial_state / final_state [N, HV, 128(K), 128(V)] f32, optional
+ *   gk [B, T, HV, 128] f32, optional out: chunk-local cumulative sum of the activated gate (natural log units)
+ *   cu_seqlens / chunk_offsets / max_seqlen / total_chunks: as in fla_gdn_chunk_fwd_args
+ * Workspace: status block + per (chunk, head) operand images (about 121 KB each). */
+typedef struct fla_kda_chunk_fwd_args {
+  fla_tensor_t q, k, v, g, beta, a_log, dt_bias, initial_state;
+  fla_tensor_t o, final_state, gk;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  float scale;
+  float lower_bound;
+  int32_t gate_mode;
+  int32_t chunk_size;
+  int32_t max_seqlen;
+  int32_t total_chunks;
+} fla_kda_chunk_fwd_args;
+FLA_API int fla_b200_kda_chunk_fwd_workspace_size(const fla_kda_chunk_fwd_args* args, uint64_t* bytes);
+FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* args, void* workspace, uint64_t workspace_bytes,
+                                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif
