@@ -1,19 +1,22 @@
 #!/usr/bin/env python
-"""Benchmark of the GDN hot path on B200.
+"""Benchmark of the GDN / KDA hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--shape B,T]
 
-One "step" is one pass of the hot path over one batch of seeded synthetic input of the shapes in
-BASELINE.json.  Workloads:
-  gdn_fwd_conv   config 1: causal_conv1d (W=4, SiLU) over x[8,4096,8192] bf16, then chunked GDN forward,
-                 B=8 T=4096 HQK=16 HV=32 K=V=128, nonzero fp32 h0
-  gdn_fwd_bwd    config 2: the same shapes, forward + backward (when the backward kernels are present)
-With N > 1 every rank (one process per GPU, launched by torch.distributed.run) processes its own
-batch of that shape (weak scaling, no collective on the data path); NCCL is used only for the
-barrier and the max-over-ranks reduction of the measured time.  Rank 0 prints ONE JSON line.
+One "step" is one pass of the hot path over one batch of seeded synthetic input with the shapes and value
+distributions of BASELINE.json.  Workloads (the default is the one the headline metric is quoted on):
+  gdn_fwd_bwd    config 2: chunked GDN forward + backward, B=8 T=4096 HQK=16 HV=32 K=V=128, nonzero fp32 h0, dO, dht
+  gdn_fwd_conv   config 1: causal_conv1d (W=4, SiLU) over x[8,4096,8192] bf16, then the chunked GDN forward
+  kda_fwd        config 3 (forward half): chunked KDA, B=4 T=8192 H=32 K=V=128, g = logsigmoid/16 per channel
+  decode         config 4: causal_conv1d_update + fused-recurrent GDN, 256 sequences x 1 token, fp32 state pool,
+                 one CUDA graph replay per step
+  conv_prefill   the conv half of config 1 alone
+With N > 1 every rank (one process per GPU, launched by torch.distributed.run) processes its own batch of that
+shape (weak scaling; the path has no exchange step, so there is no collective on the data path); NCCL carries only
+the barrier and the max-over-ranks reduction of the measured time.  Rank 0 prints ONE JSON line.
 
-`--impl reference` times the reference's CPU algorithm (the oracle port of its naive fp32 torch
-recurrence) on the host cores for the same metric, on a bounded sample of the workload.
+`--impl reference` times the reference's CPU algorithm (the oracle port of its naive fp32 torch goldens) on the
+host cores for the same metric, each step a bounded sample of the workload.
 """
 from __future__ import annotations
 
@@ -34,17 +37,25 @@ REPO = Path(__file__).resolve().parent
 sys.path.insert(0, str(REPO / "flash-linear-attention-npu_b200"))
 sys.path.insert(0, str(REPO))
 
-CFG = dict(B=8, T=4096, HK=16, HV=32, K=128, V=128, D=8192, W=4)
+DEFAULT_WORKLOAD = "gdn_fwd_bwd"
+WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "decode", "conv_prefill"]
 FWD_FLOP_PER_TOKEN_HEAD = 182955.0      # KK^T, inverse, w/u, state, output (dense 64x64 tiles, no causal credit)
 BWD_FLOP_PER_TOKEN_HEAD = 524288.0
-# Algorithmic FLOPs per token per value head of each kernel (dense 64x64 tiles; split-precision passes not counted):
-KERNEL_FLOP_PER_TOKEN_HEAD = {
-    "gdn_fwd": 182955.0 - 16384.0 - 2731.0,        # [Q;K]S, QK^T, X Z, P v_new, K^T vhat  (all but KK^T + inverse)
-    "gdn_bwd_dhu": 147456.0,                        # K dS', QK^T, P^T dO, X^T dVn, [Q^T|K^T][dO~; dR]
-    "gdn_bwd_par": 212992.0,                        # [dO;dZ]Vn^T, [dO;dZ]S^T, Vn dS'^T, [dP;dA]K, [dP^T|dA^T][Q;K], [Q;K]K^T / G
+
+# Algorithmic work of each kernel per token per value head (FLOPs; dense 64x64 tiles; split-precision passes
+# are overhead and not counted).
+KERNEL_FLOPS = {
+    "gdn_fwd": 163840.0,       # [Q;K]S, QK^T, X Z, P v_new, K^T vhat
+    "gdn_bwd_dhu": 147456.0,   # K dS', QK^T, P^T dO, X^T dVn, [Q^T|K^T][dO~; dR]
+    "gdn_bwd_par": 212992.0,   # [dO;dZ]Vn^T, [dO;dZ]S^T, Vn dS'^T, [dP;dA]K, [dP^T|dA^T][Q;K], [Q;K]K^T / G
+    "kda_fwd": 131072.0,       # [Qp;Kp]Sa, X Z, Aqk v_new, Kn^T v_new
+    "kda_prep": 32768.0,       # [Qp;Kp]Kn^T (+ the CUDA-core inverse)
+    "gdn_prep": 16384.0,
 }
-KERNEL_NAMES = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel"}
-DEFAULT_WORKLOAD = "gdn_fwd_bwd"
+KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
+                 "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "gdn_prep": "gdn_prep_kernel",
+                 "recurrent_gdn": "recurrent_gdn_kernel", "causal_conv1d_fwd": "conv_fwd_kernel",
+                 "causal_conv1d_update": "conv_update1_kernel"}
 
 
 def _peaks():
@@ -101,42 +112,208 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def make_inputs(device, seed):
-    """Config-1 tensors (BASELINE.json): q,k ~ N(0,1) L2-normalised; v ~ N(0,1); g = logsigmoid(N(0,1));
-    beta = sigmoid(N(0,1)); h0 ~ 0.1 N(0,1) fp32; conv input x ~ N(0,1) with weights ~ N(0, 1/4)."""
-    c = CFG
-    g_ = torch.Generator(device=device).manual_seed(seed)
-    rn = lambda *s: torch.randn(*s, device=device, generator=g_)  # noqa: E731
-    d = {}
-    d["q"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
-    d["k"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
-    d["v"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
-    d["g"] = F.logsigmoid(rn(c["B"], c["T"], c["HV"])).bfloat16()
-    d["beta"] = torch.sigmoid(rn(c["B"], c["T"], c["HV"])).bfloat16()
-    d["h0"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
-    d["x"] = rn(c["B"], c["T"], c["D"]).bfloat16()
-    d["w"] = (0.5 * rn(c["D"], c["W"])).bfloat16()
-    d["bias"] = torch.zeros(c["D"], device=device, dtype=torch.bfloat16)
-    d["do"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
-    d["dht"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
-    return d
+# ----------------------------------------------------------------------------------------------- workloads
+class Workload:
+    """name, shapes, synthetic inputs, one step through the public API, and the work one step represents."""
+
+    def __init__(self, name, shape):
+        self.name = name
+        self.graph = None
+        if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill"):
+            self.cfg = dict(B=8, T=4096, HK=16, HV=32, K=128, V=128, D=8192, W=4)
+        elif name == "kda_fwd":
+            self.cfg = dict(B=4, T=8192, HK=32, HV=32, K=128, V=128)
+        else:
+            self.cfg = dict(N=256, T=1, HK=16, HV=32, K=128, V=128, D=8192, W=4)
+        if shape:
+            b, t = (int(x) for x in shape.split(","))
+            if name == "decode":
+                self.cfg["N"] = b
+            else:
+                self.cfg["B"], self.cfg["T"] = b, t
+        c = self.cfg
+        self.tokens_per_step = c["N"] if name == "decode" else c["B"] * c["T"]
+        self.token_heads = self.tokens_per_step * c["HV"]
+
+    # -- inputs (BASELINE.json distributions): q,k ~ N(0,1) L2-normalised; v ~ N(0,1); g = logsigmoid(N(0,1))
+    #    (/16 per channel for KDA); beta = sigmoid(N(0,1)); states ~ 0.1 N(0,1) fp32; conv weights ~ N(0, 1/4).
+    def make_inputs(self, device, seed):
+        c = self.cfg
+        g_ = torch.Generator(device=device).manual_seed(seed)
+        rn = lambda *s: torch.randn(*s, device=device, generator=g_)  # noqa: E731
+        d = {}
+        if self.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd"):
+            d["q"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
+            d["k"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
+            d["v"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
+            d["beta"] = torch.sigmoid(rn(c["B"], c["T"], c["HV"])).bfloat16()
+            if self.name == "kda_fwd":
+                d["g"] = (F.logsigmoid(rn(c["B"], c["T"], c["HV"], c["K"])) / 16).bfloat16()
+            else:
+                d["g"] = F.logsigmoid(rn(c["B"], c["T"], c["HV"])).bfloat16()
+                d["h0"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
+        if self.name == "gdn_fwd_bwd":
+            d["do"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
+            d["dht"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
+        if self.name in ("gdn_fwd_conv", "conv_prefill"):
+            d["x"] = rn(c["B"], c["T"], c["D"]).bfloat16()
+        if self.name == "decode":
+            d["q"] = F.normalize(rn(c["N"], 1, c["HK"], c["K"]), dim=-1).bfloat16()
+            d["k"] = F.normalize(rn(c["N"], 1, c["HK"], c["K"]), dim=-1).bfloat16()
+            d["v"] = rn(c["N"], 1, c["HV"], c["V"]).bfloat16()
+            d["g"] = F.logsigmoid(rn(c["N"], 1, c["HV"])).bfloat16()
+            d["beta"] = torch.sigmoid(rn(c["N"], 1, c["HV"])).bfloat16()
+            d["state"] = 0.1 * rn(c["N"], c["HV"], c["K"], c["V"])
+            d["conv_state"] = rn(c["N"], c["D"], c["W"] - 1).bfloat16()
+            d["x"] = rn(c["N"], c["D"]).bfloat16()
+        if "D" in c:
+            d["w"] = (0.5 * rn(c["D"], c["W"])).bfloat16()
+            d["bias"] = torch.zeros(c["D"], device=device, dtype=torch.bfloat16)
+        return d
+
+    def host_input_names(self):
+        return {"gdn_fwd_bwd": ["q", "k", "v", "g", "beta", "h0", "do", "dht"],
+                "gdn_fwd_conv": ["q", "k", "v", "g", "beta", "h0", "x"],
+                "kda_fwd": ["q", "k", "v", "g", "beta"],
+                "decode": ["q", "k", "v", "g", "beta", "x"],
+                "conv_prefill": ["x"]}[self.name]
+
+    def step(self, d):
+        """One pass through the public Python API.  Returns the tensors a caller reads back."""
+        import fla_b200.ops as ops
+        n = self.name
+        if n == "gdn_fwd_bwd":
+            o, ht, grads = ops.chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"],
+                                                              initial_state=d["h0"], dht=d["dht"])
+            return (o, ht) + tuple(grads)
+        if n == "gdn_fwd_conv":
+            ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")
+            with torch.no_grad():
+                return ops.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
+                                                  output_final_state=True)
+        if n == "kda_fwd":
+            with torch.no_grad():
+                return ops.chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True)
+        if n == "conv_prefill":
+            return ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")[:1]
+        y = ops.causal_conv1d_update(d["x"], d["conv_state"], weight=d["w"], bias=d["bias"], activation="silu")
+        o, _ = ops.fused_recurrent_gated_delta_rule(d["q"], d["k"], d["v"], g=d["g"], beta=d["beta"],
+                                                    initial_state=d["state"], inplace_final_state=True)
+        return y, o
+
+    def step_fast(self, d):
+        """Device-resident step as timed for `value`: the decode step is replayed as one CUDA graph."""
+        if self.name != "decode":
+            return self.step(d)
+        if self.graph is None:
+            self.step(d)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.graph_out = self.step(d)
+        self.graph.replay()
+        return self.graph_out
+
+    def launches_per_step(self):
+        return {"gdn_fwd_bwd": 4, "gdn_fwd_conv": 3, "kda_fwd": 2, "decode": 2, "conv_prefill": 1}[self.name]
+
+    def kernel_names(self):
+        return {"gdn_fwd_bwd": ["gdn_prep", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
+                "gdn_fwd_conv": ["causal_conv1d_fwd", "gdn_prep", "gdn_fwd"],
+                "kda_fwd": ["kda_prep", "kda_fwd"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
+                "conv_prefill": ["causal_conv1d_fwd"]}[self.name]
+
+    def kernel_work(self, kname):
+        """(bound, algorithmic work per launch, unit) of one kernel at this workload's shape."""
+        c = self.cfg
+        if kname in KERNEL_FLOPS:
+            return "tensor", KERNEL_FLOPS[kname] * self.token_heads, "TFLOP/s"
+        if kname == "recurrent_gdn":      # state read + write, plus q,k,v,g,beta,o
+            n = c["N"]
+            act = n * (2 * c["HK"] * c["K"] + 2 * c["HV"] * c["V"] + 4 * c["HV"]) * 2
+            return "hbm", 2.0 * n * c["HV"] * c["K"] * c["V"] * 4 + act, "GB/s"
+        if kname == "causal_conv1d_fwd":  # x read + y write
+            return "hbm", 2.0 * c["B"] * c["T"] * c["D"] * 2, "GB/s"
+        if kname == "causal_conv1d_update":  # state read + write, x read, y write
+            return "hbm", (2.0 * c["N"] * c["D"] * (c["W"] - 1) + 2.0 * c["N"] * c["D"]) * 2, "GB/s"
+        raise KeyError(kname)
+
+    def step_flops(self):
+        if self.name == "gdn_fwd_bwd":
+            return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads
+        if self.name in ("gdn_fwd_conv", "kda_fwd"):
+            return FWD_FLOP_PER_TOKEN_HEAD * self.token_heads
+        return None
 
 
-def step_device(d, workload):
-    """One pass of the hot path with device-resident inputs.  Returns the outputs of the step."""
-    import fla_b200.ops as ops
-    if workload == "gdn_fwd_conv":
-        y, _ = ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")
-        o, ht = ops.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
-                                           output_final_state=True)
-        return y, o, ht
-    o, ht, grads = ops.chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"],
-                                                      initial_state=d["h0"], dht=d["dht"])
-    return (o, ht) + tuple(grads)
+def cpu_reference(wl: Workload, threads: int, steps: int = 1, warmup: int = 0):
+    """The reference's CPU algorithm for one step on a bounded sample of the workload.
+    Returns (tokens/s, description of the sample)."""
+    import oracle
+    torch.set_num_threads(threads)
+    c = wl.cfg
+    if wl.name in ("gdn_fwd_bwd", "gdn_fwd_conv"):
+        Ts = 1024
+        inp = oracle.make_gdn_inputs(1, Ts, c["HK"], c["HV"], seed=1001)
+        xs, w = torch.randn(1, c["D"], Ts), 0.5 * torch.randn(c["D"], c["W"])
+        desc = f"B=1 T={Ts} HQK={c['HK']} HV={c['HV']} K=V=128 fp32 naive recurrence"
+        if wl.name == "gdn_fwd_bwd":
+            fn = lambda: oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"],  # noqa: E731
+                                                      initial_state=inp["h0"], do=inp["do"], dht=inp["dht"])
+            desc += " + autograd"
+        else:
+            def fn():
+                oracle.causal_conv1d_ref(xs, w, None, None, False, "silu")
+                oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"])
+            desc += " + conv1d"
+        tokens = Ts
+    elif wl.name == "kda_fwd":
+        Ts = 512
+        inp = oracle.make_kda_inputs(1, Ts, c["HK"], c["HV"], seed=1003, with_grad=False)
+        fn = lambda: oracle.kda_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"])  # noqa: E731
+        tokens, desc = Ts, f"B=1 T={Ts} H={c['HV']} K=V=128 fp32 naive KDA recurrence"
+    elif wl.name == "conv_prefill":
+        Ts = 4096
+        xs, w = torch.randn(1, c["D"], Ts), 0.5 * torch.randn(c["D"], c["W"])
+        fn = lambda: oracle.causal_conv1d_ref(xs, w, None, None, False, "silu")  # noqa: E731
+        tokens, desc = Ts, f"B=1 T={Ts} D={c['D']} W=4 F.conv1d golden"
+    else:
+        Ns = 32
+        dec = oracle.make_decode_inputs(Ns, c["HK"], c["HV"], seed=1004)
+        asl = torch.tensor([0] + [1] * Ns, dtype=torch.int32)
+        idx = torch.arange(Ns, dtype=torch.int32)
+        st = dec["state"].transpose(-1, -2).contiguous()
+        cs, xu, w = torch.randn(Ns, c["D"], 3), torch.randn(Ns, c["D"]), 0.5 * torch.randn(c["D"], 4)
+
+        def fn():
+            oracle.causal_conv1d_update_ref(xu, cs, w, None, "silu")
+            oracle.recurrent_gated_delta_rule_golden(dec["q"], dec["k"], dec["v"], st, dec["beta"], 128 ** -0.5, asl, idx,
+                                                     g=dec["g"].float(), state_out_dtype=torch.float32)
+        tokens, desc = Ns, f"{Ns} sequences x 1 token, HV={c['HV']}, fp32 state golden + conv update golden"
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    return tokens / dt, f"{desc}, {threads} threads"
 
 
-def launches_per_step(workload):
-    return 3 if workload == "gdn_fwd_conv" else 4      # conv + prep + fwd  |  prep + fwd + bwd_dhu + bwd_par
+def run_reference(args, wl: Workload):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    threads = os.cpu_count() or 1
+    tps, sample = cpu_reference(wl, threads, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": f"GDN/KDA tokens/s ({wl.name})", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl.name, **wl.cfg, "sample": sample},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
 
 
 def kernel_time(lib, name):
@@ -145,64 +322,21 @@ def kernel_time(lib, name):
     return ms.value, n.value
 
 
-def cpu_reference_tokens_per_s(workload, threads, steps=1, warmup=0):
-    """The reference's CPU algorithm for the same step on a bounded sample: B=1, T=1024 at full head
-    count (the naive recurrence costs the same per token at any T), plus the conv reference over the
-    same tokens for the conv workload.  Returns (tokens/s, description)."""
-    import oracle
-    torch.set_num_threads(threads)
-    c = CFG
-    Ts = 1024
-    inp = oracle.make_gdn_inputs(1, Ts, c["HK"], c["HV"], c["K"], c["V"], seed=1001)
-    xs = torch.randn(1, c["D"], Ts)
-    w = 0.5 * torch.randn(c["D"], c["W"])
-
-    def one():
-        if workload == "gdn_fwd_conv":
-            oracle.causal_conv1d_ref(xs, w, None, None, False, "silu")
-            oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"])
-        else:
-            oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"],
-                                         do=inp["do"], dht=inp["dht"])
-    for _ in range(warmup):
-        one()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        one()
-    dt = (time.perf_counter() - t0) / steps
-    return Ts / dt, f"B=1 T={Ts} HQK={c['HK']} HV={c['HV']} K=V=128 fp32 naive recurrence, {threads} threads"
-
-
-def run_reference(args, workload):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    threads = os.cpu_count() or 1
-    tps, sample = cpu_reference_tokens_per_s(workload, threads, steps=max(1, args.steps), warmup=min(args.warmup, 1))
-    line = {
-        "impl": "reference", "metric": "GDN chunk tokens/s (%s)" % workload, "value": tps, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * 1024 / tps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload, **CFG, "sample": sample},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line), flush=True)
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "gdn_fwd_conv", "gdn_fwd_bwd"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=WORKLOADS)
+    ap.add_argument("--shape", default=None, help="B,T override (N,1 for decode) for small profiling cases")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
+    wl = Workload(args.workload, args.shape)
 
     if args.impl == "reference":
-        run_reference(args, args.workload or DEFAULT_WORKLOAD)
+        run_reference(args, wl)
         return
 
     import torch.distributed as dist
@@ -218,11 +352,8 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = fla_b200.load_library()
-    workload = args.workload or DEFAULT_WORKLOAD
     K, W = args.steps, max(args.warmup, 3)
-
-    d = make_inputs(dev, 1001 + rank)
-    tokens_per_step = CFG["B"] * CFG["T"]
+    d = wl.make_inputs(dev, 1001 + rank)
 
     def barrier():
         if world > 1:
@@ -231,7 +362,7 @@ def main():
 
     # ---- device-resident timing: W warm-up steps, then exactly K timed steps
     for _ in range(W):
-        step_device(d, workload)
+        wl.step_fast(d)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -240,7 +371,7 @@ def main():
     barrier()
     e0.record()
     for _ in range(K):
-        step_device(d, workload)
+        wl.step_fast(d)
     e1.record()
     barrier()
     elapsed_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -248,86 +379,94 @@ def main():
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = elapsed_ms.item() / K
-    value = world * tokens_per_step / (ms_per_step * 1e-3)
+    value = world * wl.tokens_per_step / (ms_per_step * 1e-3)
 
     # ---- per-kernel durations of the same step (CUDA events around each launch, on the launching stream)
     lib.fla_b200_kernel_timing_enable(1)
-    for _ in range(K):
-        step_device(d, workload)
+    for _ in range(min(K, 10)):
+        wl.step(d)
     torch.cuda.synchronize()
     ktimes = {}
-    for nm in ("gdn_prep", "gdn_fwd", "causal_conv1d_fwd", "gdn_bwd_dhu", "gdn_bwd_par"):
+    for nm in wl.kernel_names():
         ms, n = kernel_time(lib, nm)
         if n:
             ktimes[nm] = {"ms_per_launch": ms / n, "launches": n}
     lib.fla_b200_kernel_timing_enable(0)
 
     # ---- end to end through the public API with host buffers: pinned H2D of the step's inputs, D2H of its outputs
-    names = ["q", "k", "v", "g", "beta", "h0"] + (["x"] if workload == "gdn_fwd_conv" else ["do", "dht"])
-    host = {n: d[n].cpu().pin_memory() for n in names}
-    stage = {n: torch.empty_like(d[n]) for n in names}
-    h2d = sum(host[n].numel() * host[n].element_size() for n in names)
-    outs = step_device(d, workload)
-    outs = outs[1:] if workload == "gdn_fwd_conv" else outs          # conv output feeds the device side only
-    host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-    d2h = sum(o.numel() * o.element_size() for o in host_out)
+    e2e = None
+    if not args.no_e2e:
+        names = wl.host_input_names()
+        host = {n: d[n].cpu().pin_memory() for n in names}
+        stage = {n: torch.empty_like(d[n]) for n in names}
+        h2d = sum(host[n].numel() * host[n].element_size() for n in names)
+        outs = [o for o in wl.step(d) if o is not None]
+        host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        d2h = sum(o.numel() * o.element_size() for o in host_out)
 
-    def step_e2e():
-        for n in names:
-            stage[n].copy_(host[n], non_blocking=True)
-        dd = dict(d)
-        dd.update(stage)
-        res = step_device(dd, workload)
-        res = res[1:] if workload == "gdn_fwd_conv" else res
-        for h, o in zip(host_out, res):
-            h.copy_(o, non_blocking=True)
+        def step_e2e():
+            for n in names:
+                stage[n].copy_(host[n], non_blocking=True)
+            dd = dict(d)
+            dd.update(stage)
+            res = [o for o in wl.step(dd) if o is not None]
+            for h, o in zip(host_out, res):
+                h.copy_(o, non_blocking=True)
 
-    for _ in range(2):
-        step_e2e()
-    barrier()
-    Ke = max(3, K // 4)
-    e0.record()
-    for _ in range(Ke):
-        step_e2e()
-    e1.record()
-    barrier()
-    e2e_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    e2e_value = world * tokens_per_step / (e2e_ms.item() / Ke * 1e-3)
+        for _ in range(2):
+            step_e2e()
+        barrier()
+        Ke = max(3, K // 4)
+        e0.record()
+        for _ in range(Ke):
+            step_e2e()
+        e1.record()
+        barrier()
+        e2e_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        e2e = {"value": world * wl.tokens_per_step / (e2e_ms.item() / Ke * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
     if rank == 0:
         peaks = _peaks()
-        token_heads = CFG["B"] * CFG["T"] * CFG["HV"]
-        cands = [k for k in ktimes if k in KERNEL_FLOP_PER_TOKEN_HEAD]
-        dom = max(cands, key=lambda k: ktimes[k]["ms_per_launch"]) if cands else None
         roofline = None
-        if dom:
-            flops = KERNEL_FLOP_PER_TOKEN_HEAD[dom] * token_heads
-            achieved = flops / (ktimes[dom]["ms_per_launch"] * 1e-3) / 1e12
-            roofline = {"kernel": KERNEL_NAMES[dom], "bound": "tensor", "achieved": achieved,
-                        "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                        "traffic": None, "peak_source": peaks["source"] + " (burst)",
+        if ktimes:
+            dom = max(ktimes, key=lambda k: ktimes[k]["ms_per_launch"])
+            bound, work, unit = wl.kernel_work(dom)
+            sec = ktimes[dom]["ms_per_launch"] * 1e-3
+            achieved = work / sec / (1e12 if bound == "tensor" else 1e9)
+            peak = peaks["bf16_tflops"] if bound == "tensor" else peaks["hbm_gbs"]
+            roofline = {"kernel": KERNEL_SYMBOL[dom], "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                        "frac": achieved / peak, "traffic": None,
+                        "peak_source": peaks["source"] + (" (burst)" if bound == "tensor" else ""),
                         "ms_per_launch": ktimes[dom]["ms_per_launch"]}
-        step_flops = (FWD_FLOP_PER_TOKEN_HEAD + (BWD_FLOP_PER_TOKEN_HEAD if workload == "gdn_fwd_bwd" else 0.0)) * token_heads
-        step_tflops = step_flops / (ms_per_step * 1e-3) / 1e12
+            for k in ktimes:
+                b, wk, _ = wl.kernel_work(k)
+                s = ktimes[k]["ms_per_launch"] * 1e-3
+                denom = 1e12 * peaks["bf16_tflops"] if b == "tensor" else 1e9 * peaks["hbm_gbs"]
+                ktimes[k]["frac_of_peak"] = wk / s / denom
+                ktimes[k]["bound"] = b
+        step_roofline = None
+        if wl.step_flops():
+            tf = wl.step_flops() / (ms_per_step * 1e-3) / 1e12
+            step_roofline = {"algorithmic_tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
         cpu_baseline = None
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            tps, sample = cpu_reference_tokens_per_s(workload, threads)
+            tps, sample = cpu_reference(wl, threads)
             cpu_baseline = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
         line = {
-            "metric": "GDN chunk tokens/s (%s)" % workload, "value": value, "unit": "tokens/s", "n_gpus": world,
+            "metric": f"GDN/KDA tokens/s ({wl.name})", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload, **CFG, "global_batch": CFG["B"] * world,
-                       "parallelism": f"replicated per GPU x{world}, sharded by batch, no collective",
-                       "l2": "inputs per step exceed the 126 MB L2"},
-            "roofline": roofline, "kernels": ktimes,
-            "step_roofline": {"algorithmic_tflops": step_tflops, "frac_of_bf16_peak": step_tflops / peaks["bf16_tflops"]},
-            "cpu_baseline": cpu_baseline,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches_per_step(workload) * K, "clocks": clocks,
+            "config": {"workload": wl.name, **wl.cfg, "global_batch": wl.cfg.get("B", wl.cfg.get("N")) * world,
+                       "parallelism": f"one replica of the batch per GPU x{world}, no collective",
+                       "l2": "inputs per step exceed the 126 MB L2" if wl.name != "decode" else
+                             "the 1.07 GB state pool streamed every step exceeds the 126 MB L2",
+                       "cuda_graph": wl.name == "decode"},
+            "roofline": roofline, "kernels": ktimes, "step_roofline": step_roofline, "cpu_baseline": cpu_baseline,
+            "e2e": e2e, "gpu_launches": wl.launches_per_step() * K, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
