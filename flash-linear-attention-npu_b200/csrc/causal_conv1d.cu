@@ -29,7 +29,14 @@ __device__ __forceinline__ uint4 pack8f(const float* f) {
   for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
   return raw;
 }
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+// SiLU as 0.5 x (1 + tanh(0.5 x)): one MUFU op and two FP32 ops.  tanh.approx is accurate to about 2^-11
+// relative, far below the rounding of the bf16 result.
+__device__ __forceinline__ float silu(float x) {
+  const float h = 0.5f * x;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+  return fmaf(h, t, h);
+}
 
 // weight element (d, j) at w[d * wsd + j * wsw]; returns taps for 8 channels starting at d0.
 template <int W>
@@ -37,6 +44,15 @@ __device__ __forceinline__ void load_weights(const bf16* w, int64_t wsd, int64_t
   if (wsd == 1) {  // [W, D]: channels contiguous
 #pragma unroll
     for (int j = 0; j < W; ++j) unpack8(*reinterpret_cast<const uint4*>(w + j * wsw + d0), out[j]);
+  } else if (wsw == 1 && wsd == W && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    // [D, W] dense: the 8 channels' taps are 8 * W contiguous elements = W 16-byte vectors
+    float flat[W * 8];
+#pragma unroll
+    for (int j = 0; j < W; ++j) unpack8(*reinterpret_cast<const uint4*>(w + int64_t(d0) * W + j * 8), flat + j * 8);
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+      for (int j = 0; j < W; ++j) out[j][c] = flat[c * W + j];
   } else {
 #pragma unroll
     for (int j = 0; j < W; ++j)
@@ -56,11 +72,12 @@ struct ConvFwdParams {
 };
 
 constexpr int kConvTile = 64;     // tokens per CTA tile
-constexpr int kConvGroup = 8;     // tokens loaded together (independent 16-byte loads in flight)
+constexpr int kConvGroup = 8;     // tokens processed per inner step (independent 16-byte loads in flight)
 constexpr int kConvThreads = 128;
 
-template <int W, bool HAS_RES>
-__global__ void __launch_bounds__(kConvThreads, 4) conv_fwd_kernel(ConvFwdParams p) {
+template <int W, bool HAS_RES, bool SILU>
+__global__ void __launch_bounds__(kConvThreads, 3) conv_fwd_kernel(ConvFwdParams p) {
+  constexpr int G = kConvGroup;
   const int d0 = (blockIdx.x * kConvThreads + threadIdx.x) * 8;
   if (d0 >= p.D) return;
   const int b = blockIdx.z;
@@ -93,8 +110,8 @@ __global__ void __launch_bounds__(kConvThreads, 4) conv_fwd_kernel(ConvFwdParams
   bf16* yb = p.y + b * p.y_sb + d0;
   const bf16* rb = HAS_RES ? p.residual + b * p.r_sb + d0 : nullptr;
 
-  // hist[j-1] = input at (t - j), j = 1..W-1
-  float hist[W - 1][8];
+  // win[0 .. W-2] = the W-1 inputs before the group, win[W-1 + i] = input i of the group
+  float win[W - 1 + G][8];
   int t = t_begin;
   while (t < t_end) {
     if (p.cu_seqlens) {
@@ -109,57 +126,75 @@ __global__ void __launch_bounds__(kConvThreads, 4) conv_fwd_kernel(ConvFwdParams
     for (int j = 1; j < W; ++j) {
       const int pos = t - j;
       if (pos >= seq_begin) {
-        unpack8(*reinterpret_cast<const uint4*>(xb + pos * p.x_st), hist[j - 1]);
+        unpack8(*reinterpret_cast<const uint4*>(xb + pos * p.x_st), win[W - 1 - j]);
       } else {
         const int si = (W - 1) + (pos - seq_begin);  // index into the W-1 stored inputs
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-          hist[j - 1][c] = (p.init && si >= 0) ? __bfloat162float(p.init[seq * p.i_sn + (d0 + c) * p.i_sd + si * p.i_sw]) : 0.f;
+          win[W - 1 - j][c] = (p.init && si >= 0) ? __bfloat162float(p.init[seq * p.i_sn + (d0 + c) * p.i_sd + si * p.i_sw]) : 0.f;
       }
     }
-    for (int tg = t; tg < seg_end; tg += kConvGroup) {
-      uint4 xin[kConvGroup], rin[HAS_RES ? kConvGroup : 1];
+    uint4 xin[G], rin[HAS_RES ? G : 1];
+    auto issue = [&](int tg) {
 #pragma unroll
-      for (int i = 0; i < kConvGroup; ++i) {
+      for (int i = 0; i < G; ++i) {
         const int tt = tg + i;
         xin[i] = (tt < seg_end) ? *reinterpret_cast<const uint4*>(xb + tt * p.x_st) : make_uint4(0, 0, 0, 0);
         if constexpr (HAS_RES) rin[i] = (tt < seg_end) ? *reinterpret_cast<const uint4*>(rb + tt * p.r_st) : make_uint4(0, 0, 0, 0);
       }
+    };
+    issue(t);
+    int nvalid = 0;
+    for (int tg = t; tg < seg_end; tg += G) {
 #pragma unroll
-      for (int i = 0; i < kConvGroup; ++i) {
-        const int tt = tg + i;
-        if (tt < seg_end) {
-          float xv[8], acc[8];
-          unpack8(xin[i], xv);
+      for (int i = 0; i < G; ++i) unpack8(xin[i], win[W - 1 + i]);
+      float res[HAS_RES ? G : 1][8];
+      if constexpr (HAS_RES) {
+#pragma unroll
+        for (int i = 0; i < G; ++i) unpack8(rin[i], res[i]);
+      }
+      if (tg + G < seg_end) issue(tg + G);   // next group's loads fly while this one is computed
+      nvalid = min(G, seg_end - tg);
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        if (i < nvalid) {
+          float acc[8];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            float a = bias[c] + w[W - 1][c] * xv[c];
+            float a = bias[c];
 #pragma unroll
-            for (int j = 1; j < W; ++j) a += w[W - 1 - j][c] * hist[j - 1][c];
-            acc[c] = p.silu ? silu(a) : a;
+            for (int j = 0; j < W; ++j) a = fmaf(w[j][c], win[i + j][c], a);
+            if constexpr (SILU) a = silu(a);
+            if constexpr (HAS_RES) a += res[i][c];
+            acc[c] = a;
           }
-          if constexpr (HAS_RES) {
-            float rv[8];
-            unpack8(rin[i], rv);
+          *reinterpret_cast<uint4*>(yb + (tg + i) * p.y_st) = pack8f(acc);
+        }
+      }
+      if (nvalid == G) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) acc[c] += rv[c];
-          }
-          *reinterpret_cast<uint4*>(yb + tt * p.y_st) = pack8f(acc);
+        for (int j = 0; j < W - 1; ++j)
 #pragma unroll
-          for (int j = W - 1; j > 1; --j)
+          for (int c = 0; c < 8; ++c) win[j][c] = win[G + j][c];
+      }
+    }
+    if (nvalid != G) {  // partial last group: the W-1 newest inputs sit at win[nvalid .. nvalid + W-2]
 #pragma unroll
-            for (int c = 0; c < 8; ++c) hist[j - 1][c] = hist[j - 2][c];
+      for (int i = 0; i < G; ++i) {
+        if (i == nvalid) {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) hist[0][c] = xv[c];
+          for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) win[j][c] = win[i + j][c];
         }
       }
     }
     if (p.final_state && seg_end == seq_end) {  // the sequence ended in this tile: its last W-1 inputs are the state
 #pragma unroll
-      for (int j = 1; j < W; ++j)
+      for (int j = 0; j < W - 1; ++j)
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-          p.final_state[seq * p.f_sn + (d0 + c) * p.f_sd + (W - 1 - j) * p.f_sw] = __float2bfloat16_rn(hist[j - 1][c]);
+          p.final_state[seq * p.f_sn + (d0 + c) * p.f_sd + j * p.f_sw] = __float2bfloat16_rn(win[j][c]);
     }
     t = seg_end;
   }
@@ -347,9 +382,14 @@ extern "C" FLA_API int fla_b200_causal_conv1d_fwd(const fla_causal_conv1d_fwd_ar
   const dim3 grid(unsigned((D / 8 + kConvThreads - 1) / kConvThreads), unsigned((T + kConvTile - 1) / kConvTile), unsigned(B));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   KernelTimer kt("causal_conv1d_fwd", st);
-#define FLA_LAUNCH_FWD(WW)                                                        \
-  if (p.residual) conv_fwd_kernel<WW, true><<<grid, kConvThreads, 0, st>>>(p);  \
-  else conv_fwd_kernel<WW, false><<<grid, kConvThreads, 0, st>>>(p);
+#define FLA_LAUNCH_FWD(WW)                                                                           \
+  if (p.residual) {                                                                                  \
+    if (p.silu) conv_fwd_kernel<WW, true, true><<<grid, kConvThreads, 0, st>>>(p);                   \
+    else conv_fwd_kernel<WW, true, false><<<grid, kConvThreads, 0, st>>>(p);                         \
+  } else {                                                                                           \
+    if (p.silu) conv_fwd_kernel<WW, false, true><<<grid, kConvThreads, 0, st>>>(p);                  \
+    else conv_fwd_kernel<WW, false, false><<<grid, kConvThreads, 0, st>>>(p);                        \
+  }
   if (W == 4) { FLA_LAUNCH_FWD(4) } else if (W == 3) { FLA_LAUNCH_FWD(3) } else { FLA_LAUNCH_FWD(2) }
 #undef FLA_LAUNCH_FWD
   return cuda_status(cudaGetLastError());
