@@ -51,9 +51,10 @@ KERNEL_FLOPS = {
     "kda_fwd": 131072.0,       # [Qp;Kp]Sa, X Z, Aqk v_new, Kn^T v_new
     "kda_prep": 32768.0,       # [Qp;Kp]Kn^T (+ the CUDA-core inverse)
     "gdn_prep": 16384.0,
+    "tri_inverse": 8192.0,     # 2 * 64^2 FLOP per token-head of the triangular solve (CUDA cores; shown against the tensor peak)
 }
 KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
-                 "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "gdn_prep": "gdn_prep_kernel",
+                 "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "gdn_prep": "gdn_prep_kernel", "tri_inverse": "tri_inverse_kernel",
                  "recurrent_gdn": "recurrent_gdn_kernel", "causal_conv1d_fwd": "conv_fwd_kernel",
                  "causal_conv1d_update": "conv_update1_kernel"}
 
@@ -215,12 +216,12 @@ class Workload:
         return self.graph_out
 
     def launches_per_step(self):
-        return {"gdn_fwd_bwd": 4, "gdn_fwd_conv": 3, "kda_fwd": 2, "decode": 2, "conv_prefill": 1}[self.name]
+        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "decode": 2, "conv_prefill": 1}[self.name]
 
     def kernel_names(self):
-        return {"gdn_fwd_bwd": ["gdn_prep", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
-                "gdn_fwd_conv": ["causal_conv1d_fwd", "gdn_prep", "gdn_fwd"],
-                "kda_fwd": ["kda_prep", "kda_fwd"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
+        return {"gdn_fwd_bwd": ["gdn_prep", "tri_inverse", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
+                "gdn_fwd_conv": ["causal_conv1d_fwd", "gdn_prep", "tri_inverse", "gdn_fwd"],
+                "kda_fwd": ["kda_prep", "tri_inverse", "kda_fwd"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
                 "conv_prefill": ["causal_conv1d_fwd"]}[self.name]
 
     def kernel_work(self, kname):

@@ -2,8 +2,8 @@
 //
 //  gdn_prep_kernel   (parallel over chunks): gam = chunk-local cumsum(g);
 //                    A[i,j] = beta_i exp(gam_i - gam_j) k_i.k_j (j < i);  X = (I + A)^-1
-//                    KK^T on tcgen05 (shared by the value heads of a GVA group), the unit-lower
-//                    triangular inverse by fp32 forward substitution on CUDA cores.
+//                    KK^T on tcgen05 (shared by the value heads of a GVA group); the unit-lower
+//                    triangular inverse runs in tri_inverse_kernel (fp32 forward substitution on CUDA cores).
 //                    Replaces chunk_local_cumsum + chunk_scaled_dot_kkt + solve_tri of the reference
 //                    (examples/flash_gated_delta_rule.py:811-838).
 //  gdn_fwd_kernel    (sequential over chunks, one CTA per (sequence, value head, 64-column block of V)):
@@ -22,6 +22,7 @@
 #include "gdn_common.cuh"
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
+#include "tri_inverse.h"
 
 namespace fla {
 
@@ -30,6 +31,7 @@ struct GdnFwdParams {
   const void* g; const void* beta;
   float* gam;          // [tokens, HV]      chunk-local cumulative log decay (saved for backward)
   bf16* X;             // [tokens, HV, 64]  row i of the chunk's (I + A)^-1 (saved for backward)
+  float* at;           // [chunks, HV, 64, 64] scratch: A^T handed to the triangular-inverse kernel
   const float* h0;     // [N, HV, K, V] or null
   float* ht;           // [N, HV, K, V] or null
   void* o;             // [tokens, HV, V]
@@ -140,33 +142,12 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
     }
     __syncthreads();
     if (active) {
-      // Thread c solves column c of X = (I + A)^-1 by right-looking forward substitution:
-      //   r = e_c;  for j: x_j = r_j;  r_i -= A[i][j] x_j  (i > j).
-      // The updates of one step are independent, so the FMA pipeline stays full.  Entries above the
-      // column's diagonal are zero, so a warp skips the steps before its first column.
-      float x[kC];
-#pragma unroll
-      for (int i = 0; i < kC; ++i) x[i] = (i == c) ? 1.f : 0.f;
-      const int jmin = c & ~31;  // warp-uniform
-#pragma unroll
-      for (int j = 0; j < kC - 1; ++j) {
-        if (j >= jmin) {
-          const float xj = x[j];
-          const float* col = AT + j * kAStride;
-#pragma unroll
-          for (int i4 = (j + 1) & ~3; i4 < kC; i4 += 4) {
-            const float4 a4 = *reinterpret_cast<const float4*>(col + i4);
-            if (i4 > j) x[i4] -= a4.x * xj;
-            if (i4 + 1 > j) x[i4 + 1] -= a4.y * xj;
-            if (i4 + 2 > j) x[i4 + 2] -= a4.z * xj;
-            if (i4 + 3 > j) x[i4 + 3] -= a4.w * xj;
-          }
-        }
+      // hand A^T to the inverse kernel (coalesced rows; entries on and above the diagonal are never read)
+      float* dst = p.at + ((int64_t(sq.cbase) + blockIdx.x) * p.HV + hv) * (kC * kC);
+      for (int idx = c; idx < kC * 16; idx += 64) {
+        const int j = idx / 16, q4 = idx % 16;
+        *reinterpret_cast<float4*>(dst + j * kC + q4 * 4) = *reinterpret_cast<const float4*>(AT + j * kAStride + q4 * 4);
       }
-      bf16* xg = p.X + ((tok0 * p.HV + hv) * kC) + c;
-#pragma unroll
-      for (int i = 0; i < kC; ++i)
-        if (i < rows) xg[int64_t(i) * p.HV * kC] = __float2bfloat16_rn(x[i]);
     }
     __syncthreads();
   }
@@ -483,14 +464,18 @@ static int check_gate_tensor(const fla_tensor_t& t, int64_t B, int64_t T, int64_
 
 extern "C" FLA_API int fla_b200_gdn_chunk_fwd_workspace_size(const fla_gdn_chunk_fwd_args* a, uint64_t* bytes) {
   if (!a || !bytes) return FLA_ERR_NULL;
-  *bytes = 256;  // device status word
+  if (!a->q.data || a->q.ndim != 4 || !a->v.data || a->v.ndim != 4) return FLA_ERR_SHAPE;
+  int64_t chunks = a->q.shape[0] * ((a->q.shape[1] + kC - 1) / kC);
+  if (a->cu_seqlens.data) chunks = a->total_chunks;
+  if (chunks <= 0) return FLA_ERR_VALUE;
+  *bytes = 256 + uint64_t(chunks) * a->v.shape[2] * kC * kC * 4;  // status block + A^T scratch for the inverse
   return FLA_OK;
 }
 
 extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, void* workspace, uint64_t workspace_bytes,
                                               void* stream) {
   if (!a) return FLA_ERR_NULL;
-  if (!workspace || workspace_bytes < 256) return FLA_ERR_WORKSPACE;
+  if (!workspace || workspace_bytes < 256 || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
   const fla_tensor_t &q = a->q, &k = a->k, &v = a->v, &o = a->o;
   if (!q.data || !k.data || !v.data || !o.data) return FLA_ERR_NULL;
   if (q.ndim != 4 || v.ndim != 4) return FLA_ERR_SHAPE;
@@ -556,6 +541,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = a->beta.dtype == FLA_F32; p.o_is_f32 = o.dtype == FLA_F32;
   p.scale = a->scale;
   p.status = static_cast<int*>(workspace);
+  if (workspace_bytes < 256 + uint64_t(total_chunks) * HV * kC * kC * 4) return FLA_ERR_WORKSPACE;
+  p.at = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
@@ -575,6 +562,11 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
     gdn_prep_kernel<<<dim3(nt_max, unsigned(HK), N), 128, prep_smem, cs>>>(p);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  {
+    KernelTimer kt("tri_inverse", cs);
+    TriInverseParams tp{p.at, p.X, nullptr, p.cu_seqlens, p.chunk_offsets, p.T, p.HV};
+    if (launch_tri_inverse(tp, nt_max, N, cs)) return FLA_ERR_CUDA;
+  }
   {
     KernelTimer kt("gdn_fwd", cs);
     gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p);

@@ -15,6 +15,7 @@
 #include "gdn_common.cuh"
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
+#include "tri_inverse.h"
 
 namespace fla {
 
@@ -26,7 +27,8 @@ struct KdaParams {
   bf16* qk_img;         // [chunks, HV, {hi, lo}, 2 panels x 128 rows]  rows 0-63 Qp, rows 64-127 Kp
   bf16* kn_img;         // [chunks, HV, {hi, lo}, 2 panels x 64 rows]
   bf16* p_img;          // [chunks, HV, {hi, lo}, 64 x 64]   tril(Qp Kn^T)
-  bf16* x_img;          // [chunks, HV, 64 x 64]             (I + Akk)^-1
+  bf16* x_img;          // [chunks, HV, 64 x 64]             (I + Akk)^-1 (written by the inverse kernel)
+  float* at;            // [chunks, HV, 64, 64] scratch: Akk^T for the inverse kernel
   float* vec;           // [chunks, HV, 2, K]  e^a, e^{gk_L - a}
   const float* h0; float* ht;
   void* o;
@@ -41,10 +43,7 @@ constexpr int64_t kKdaQkImg = 32768, kKdaKnImg = 16384, kKdaPImg = 8192, kKdaXIm
 
 // --------------------------------------------------------------------------------------------- prep
 constexpr uint32_t pOffQKH = 0, pOffQKL = 32768, pOffKNH = 65536, pOffKNL = 81920;
-constexpr uint32_t pOffGK = 98304;                 // fp32 [64][129] cumulative gates; later the score tile / P / X panels
-constexpr int kGkStride = 129;
-constexpr int kAStrideKda = 68;
-constexpr uint32_t kKdaPrepSmem = 98304 + 34816;   // operand panels + max(gate tile, P panels + A^T)
+constexpr uint32_t kKdaPrepSmem = 98304;           // operand panels only
 
 __device__ __forceinline__ float kda_gate(float g, int mode, float eig, float bias, float lower_bound) {
   if (mode == 0) return g;
@@ -56,11 +55,12 @@ __device__ __forceinline__ float kda_gate(float g, int mode, float eig, float bi
   return lower_bound / (1.f + __expf(-eig * raw));  // lower_bound * sigmoid(exp(A_log) (g + dt_bias))
 }
 
-__global__ void __launch_bounds__(256, 1) kda_prep_kernel(KdaParams p) {
+// Thread layout of the elementwise phases: 16 channel groups (8 channels each) x 16 token segments (4 tokens each).
+__global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* gk_s = reinterpret_cast<float*>(smem + pOffGK);
-  __shared__ float anchor_s[kK], beta_s[kC];
+  __shared__ float tot_s[16][kK];          // gate sum of each token segment, per channel
+  __shared__ float anchor_s[kK], last_s[kK];
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t bar;
 
@@ -74,6 +74,7 @@ __global__ void __launch_bounds__(256, 1) kda_prep_kernel(KdaParams p) {
   const int rows = min(kC, sq.len - t0);
   const int64_t tok0 = int64_t(sq.bos) + t0;
   const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+  const int cg = tid & 15, seg = tid >> 4, r0 = cg * 8;
 
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 64);
@@ -83,70 +84,112 @@ __global__ void __launch_bounds__(256, 1) kda_prep_kernel(KdaParams p) {
     mbar_init(&bar, 1);
     mbar_init_fence();
   }
-  // 1. gate tile -> shared (activated), zero past the end of the sequence
+  // 1. activated gates of my 4 tokens x 8 channels, prefix-summed inside the segment (zero past the sequence end)
+  float gk[4][8];
   {
     const float eig = (p.gate_mode && p.a_log) ? __expf(p.a_log[hv]) : 1.f;
-    for (int idx = tid; idx < kC * kK; idx += 256) {
-      const int t = idx / kK, r = idx % kK;
-      float gv = 0.f;
+    float bias[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bias[j] = (p.gate_mode && p.dt_bias) ? p.dt_bias[hv * kK + r0 + j] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = seg * 4 + i;
+      float raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) raw[j] = 0.f;
       if (t < rows) {
-        const float raw = ld_scalar(p.g, (tok0 + t) * p.g_st + hv * p.g_sh + r, p.g_is_f32);
-        const float bias = (p.gate_mode && p.dt_bias) ? p.dt_bias[hv * kK + r] : 0.f;
-        gv = kda_gate(raw, p.gate_mode, eig, bias, p.lower_bound);
+        const int64_t off = (tok0 + t) * p.g_st + hv * p.g_sh + r0;
+        if (p.g_is_f32) {
+          const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(p.g) + off);
+          const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(p.g) + off + 4);
+          raw[0] = a.x; raw[1] = a.y; raw[2] = a.z; raw[3] = a.w; raw[4] = b.x; raw[5] = b.y; raw[6] = b.z; raw[7] = b.w;
+        } else {
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.g) + off), raw);
+        }
       }
-      gk_s[t * kGkStride + r] = gv;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gv = t < rows ? kda_gate(raw[j], p.gate_mode, eig, bias[j], p.lower_bound) : 0.f;
+        gk[i][j] = gv + (i ? gk[i - 1][j] : 0.f);
+      }
     }
-    if (tid < kC) beta_s[tid] = tid < rows ? ld_scalar(p.beta, (tok0 + tid) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tot_s[seg][r0 + j] = gk[3][j];
   }
   __syncthreads();
-  // 2. per-channel prefix sum over the chunk's tokens; anchor and boundary factors
+  // 2. add the totals of the earlier segments; publish the anchor row (middle token) and the last valid row
+  {
+    float off[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) off[j] = 0.f;
+    for (int sgm = 0; sgm < seg; ++sgm) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) off[j] += tot_s[sgm][r0 + j];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gk[i][j] += off[j];
+    const int ta = min(kC / 2 - 1, rows - 1), tl = rows - 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = seg * 4 + i;
+      if (t == ta) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) anchor_s[r0 + j] = gk[i][j];
+      }
+      if (t == tl) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) last_s[r0 + j] = gk[i][j];
+      }
+    }
+  }
+  __syncthreads();
   if (tid < kK) {
-    float acc = 0.f;
-    for (int t = 0; t < kC; ++t) {
-      acc += gk_s[t * kGkStride + tid];       // zero gates past the end keep the last valid value
-      gk_s[t * kGkStride + tid] = acc;
-    }
-    const float a = gk_s[min(kC / 2 - 1, rows - 1) * kGkStride + tid];
-    const float gl = gk_s[(rows - 1) * kGkStride + tid];
-    anchor_s[tid] = a;
+    const float a = anchor_s[tid];
     p.vec[cidx * 2 * kK + tid] = __expf(a);
-    p.vec[cidx * 2 * kK + kK + tid] = __expf(gl - a);
+    p.vec[cidx * 2 * kK + kK + tid] = __expf(last_s[tid] - a);
   }
-  __syncthreads();
   // 3. scaled operands as split bf16 panels
-  for (int idx = tid; idx < kC * 16; idx += 256) {
-    const int t = idx / 16, ch = idx % 16;
-    float qv[8], kv[8], qp[8], kp[8], kn[8];
-    uint4 qraw = make_uint4(0, 0, 0, 0), kraw = qraw;
-    if (t < rows) {
-      qraw = *reinterpret_cast<const uint4*>(p.q + (tok0 + t) * p.q_st + hk * p.q_sh + ch * 8);
-      kraw = *reinterpret_cast<const uint4*>(p.k + (tok0 + t) * p.k_st + hk * p.k_sh + ch * 8);
-    }
-    unpack_bf16x8(qraw, qv);
-    unpack_bf16x8(kraw, kv);
+  {
+    float an[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int r = ch * 8 + j;
-      const float d = gk_s[t * kGkStride + r] - anchor_s[r];
-      const float e1 = __expf(d), e2 = __expf(-d);
-      qp[j] = qv[j] * e1; kp[j] = kv[j] * e1; kn[j] = kv[j] * e2;
-    }
-    if (p.gk_out && t < rows) {
-      float* dst = p.gk_out + ((tok0 + t) * p.HV + hv) * kK + ch * 8;
+    for (int j = 0; j < 8; ++j) an[j] = anchor_s[r0 + j];
+    const uint32_t pan = (cg / 8) * 16384, pan64 = (cg / 8) * 8192;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dst[j] = gk_s[t * kGkStride + ch * 8 + j];
+    for (int i = 0; i < 4; ++i) {
+      const int t = seg * 4 + i;
+      float qv[8], kv[8], qp[8], kp[8], kn[8];
+      uint4 qraw = make_uint4(0, 0, 0, 0), kraw = qraw;
+      if (t < rows) {
+        qraw = *reinterpret_cast<const uint4*>(p.q + (tok0 + t) * p.q_st + hk * p.q_sh + r0);
+        kraw = *reinterpret_cast<const uint4*>(p.k + (tok0 + t) * p.k_st + hk * p.k_sh + r0);
+      }
+      unpack_bf16x8(qraw, qv);
+      unpack_bf16x8(kraw, kv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = gk[i][j] - an[j];
+        const float e1 = __expf(d), e2 = __expf(-d);
+        qp[j] = qv[j] * e1; kp[j] = kv[j] * e1; kn[j] = kv[j] * e2;
+      }
+      if (p.gk_out && t < rows) {
+        float* dst = p.gk_out + ((tok0 + t) * p.HV + hv) * kK + r0;
+        *reinterpret_cast<float4*>(dst) = make_float4(gk[i][0], gk[i][1], gk[i][2], gk[i][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(gk[i][4], gk[i][5], gk[i][6], gk[i][7]);
+      }
+      uint4 hi, lo;
+      const uint32_t o1 = panel_chunk_off(t, cg % 8), o2 = panel_chunk_off(64 + t, cg % 8);
+      split8(qp, hi, lo);
+      *reinterpret_cast<uint4*>(smem + pOffQKH + pan + o1) = hi;
+      *reinterpret_cast<uint4*>(smem + pOffQKL + pan + o1) = lo;
+      split8(kp, hi, lo);
+      *reinterpret_cast<uint4*>(smem + pOffQKH + pan + o2) = hi;
+      *reinterpret_cast<uint4*>(smem + pOffQKL + pan + o2) = lo;
+      split8(kn, hi, lo);
+      *reinterpret_cast<uint4*>(smem + pOffKNH + pan64 + o1) = hi;
+      *reinterpret_cast<uint4*>(smem + pOffKNL + pan64 + o1) = lo;
     }
-    uint4 hi, lo;
-    const uint32_t pan = (ch / 8) * 16384, pan64 = (ch / 8) * 8192;
-    split8(qp, hi, lo);
-    *reinterpret_cast<uint4*>(smem + pOffQKH + pan + panel_chunk_off(t, ch % 8)) = hi;
-    *reinterpret_cast<uint4*>(smem + pOffQKL + pan + panel_chunk_off(t, ch % 8)) = lo;
-    split8(kp, hi, lo);
-    *reinterpret_cast<uint4*>(smem + pOffQKH + pan + panel_chunk_off(64 + t, ch % 8)) = hi;
-    *reinterpret_cast<uint4*>(smem + pOffQKL + pan + panel_chunk_off(64 + t, ch % 8)) = lo;
-    split8(kn, hi, lo);
-    *reinterpret_cast<uint4*>(smem + pOffKNH + pan64 + panel_chunk_off(t, ch % 8)) = hi;
-    *reinterpret_cast<uint4*>(smem + pOffKNL + pan64 + panel_chunk_off(t, ch % 8)) = lo;
   }
   fence_async_smem();
   tc_fence_before();
@@ -168,11 +211,8 @@ __global__ void __launch_bounds__(256, 1) kda_prep_kernel(KdaParams p) {
   }
   const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
   tc_fence_after();
-  // 5. q-side rows: P = tril(Aqk) as split panels; k-side rows: A^T for the triangular solve.
-  //    Both reuse the gate tile's memory (all readers of gk_s are past the barrier above).
-  uint8_t* p_hi = smem + pOffGK;             // 8 KB
-  uint8_t* p_lo = smem + pOffGK + 8192;      // 8 KB
-  float* AT = reinterpret_cast<float*>(smem + pOffGK + 16384);   // [64][68] fp32, AT[j][i] = A[i][j]
+  // 5. q-side rows: P = tril(Aqk) written straight into its split panel image;
+  //    k-side rows: Akk^T = (beta_i Kp Kn^T)^T for the inverse kernel (coalesced along i)
   const int quad = warp & 3, half = warp >> 2, row = quad * 32 + lane, tok = row & 63;
   if (ok) {
     float sc[32];
@@ -181,68 +221,29 @@ __global__ void __launch_bounds__(256, 1) kda_prep_kernel(KdaParams p) {
     if (quad < 2) {
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) sc[jj] = (half * 32 + jj <= tok) ? sc[jj] : 0.f;
+      uint8_t* img = reinterpret_cast<uint8_t*>(p.p_img + cidx * kKdaPImg);
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         uint4 hi, lo;
         split8(sc + ch * 8, hi, lo);
         const uint32_t off = panel_chunk_off(tok, half * 4 + ch);
-        *reinterpret_cast<uint4*>(p_hi + off) = hi;
-        *reinterpret_cast<uint4*>(p_lo + off) = lo;
+        *reinterpret_cast<uint4*>(img + off) = hi;
+        *reinterpret_cast<uint4*>(img + 8192 + off) = lo;
       }
     } else {
-      const float bi = beta_s[tok];
+      const float bi = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+      float* at = p.at + cidx * (kC * kC);
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) {
         const int j = half * 32 + jj;
-        if (j < tok) AT[j * kAStrideKda + tok] = bi * sc[jj];
+        if (j < tok) at[j * kC + tok] = bi * sc[jj];
       }
     }
   }
-  fence_async_smem();
+  if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 64);
-  if (!ok) return;
-  if (tid == 0) {
-    bulk_store(p.p_img + cidx * kKdaPImg, smem_u32(p_hi), 16384);
-    bulk_commit();
-  }
-  // 6. X = (I + A)^-1, column c per thread (right-looking forward substitution), written as a 64x64 bf16 panel
-  uint8_t* x_pan = smem + pOffQKH;   // the operand panels have been handed to the bulk store engine: wait before reuse
-  if (tid == 0) bulk_wait_read();
-  __syncthreads();
-  if (tid < kC) {
-    const int cc = tid;
-    float x[kC];
-#pragma unroll
-    for (int i = 0; i < kC; ++i) x[i] = (i == cc) ? 1.f : 0.f;
-    const int jmin = cc & ~31;
-#pragma unroll
-    for (int j = 0; j < kC - 1; ++j) {
-      if (j >= jmin) {
-        const float xj = x[j];
-        const float* col = AT + j * kAStrideKda;
-#pragma unroll
-        for (int i4 = (j + 1) & ~3; i4 < kC; i4 += 4) {
-          const float4 a4 = *reinterpret_cast<const float4*>(col + i4);
-          if (i4 > j) x[i4] -= a4.x * xj;
-          if (i4 + 1 > j) x[i4 + 1] -= a4.y * xj;
-          if (i4 + 2 > j) x[i4 + 2] -= a4.z * xj;
-          if (i4 + 3 > j) x[i4 + 3] -= a4.w * xj;
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < kC; ++i)
-      *reinterpret_cast<bf16*>(x_pan + panel_off(i, cc)) = __float2bfloat16_rn(i < rows ? x[i] : 0.f);
-  }
-  fence_async_smem();
-  __syncthreads();
-  if (tid == 0) {
-    bulk_store(p.x_img + cidx * kKdaXImg, smem_u32(x_pan), 8192);
-    bulk_commit();
-    bulk_wait_all();
-  }
 }
 
 // --------------------------------------------------------------------------------------------- forward
@@ -494,7 +495,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
 
 using namespace fla;
 
-static uint64_t kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[5]) {
+static uint64_t kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[6]) {
   uint64_t o = 256;
   const uint64_t per = uint64_t(total_chunks) * HV;
   off[0] = o; o += align_up(per * kKdaQkImg * 2, 256);
@@ -502,6 +503,7 @@ static uint64_t kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[5])
   off[2] = o; o += align_up(per * kKdaPImg * 2, 256);
   off[3] = o; o += align_up(per * kKdaXImg * 2, 256);
   off[4] = o; o += align_up(per * 2 * kK * 4, 256);
+  off[5] = o; o += align_up(per * kC * kC * 4, 256);
   return o;
 }
 
@@ -528,7 +530,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd_workspace_size(const fla_kda_chunk
   int64_t total_chunks; int N, max_len;
   const int st = kda_geometry(a, &total_chunks, &N, &max_len);
   if (st) return st;
-  uint64_t off[5];
+  uint64_t off[6];
   *bytes = kda_ws_layout(total_chunks, a->v.shape[2], off);
   return FLA_OK;
 }
@@ -584,7 +586,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
       return FLA_ERR_SHAPE;
   }
   if (a->chunk_size != kC) return FLA_ERR_VALUE;
-  uint64_t off[5];
+  uint64_t off[6];
   const uint64_t need = kda_ws_layout(total_chunks, HV, off);
   if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
 
@@ -598,6 +600,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   p.qk_img = reinterpret_cast<bf16*>(ws + off[0]); p.kn_img = reinterpret_cast<bf16*>(ws + off[1]);
   p.p_img = reinterpret_cast<bf16*>(ws + off[2]); p.x_img = reinterpret_cast<bf16*>(ws + off[3]);
   p.vec = reinterpret_cast<float*>(ws + off[4]);
+  p.at = reinterpret_cast<float*>(ws + off[5]);
   p.h0 = static_cast<const float*>(a->initial_state.data); p.ht = static_cast<float*>(a->final_state.data);
   p.o = a->o.data;
   p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
@@ -625,6 +628,11 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
     kda_prep_kernel<<<dim3(nt_max, unsigned(HV), N), 256, kKdaPrepSmem + 1024, cs>>>(p);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  {
+    KernelTimer kt("tri_inverse", cs);
+    TriInverseParams tp{p.at, nullptr, p.x_img, p.cu_seqlens, p.chunk_offsets, p.T, p.HV};
+    if (launch_tri_inverse(tp, nt_max, N, cs)) return FLA_ERR_CUDA;
+  }
   {
     KernelTimer kt("kda_fwd", cs);
     kda_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), 256, kKdaFwdSmem + 1024, cs>>>(p);

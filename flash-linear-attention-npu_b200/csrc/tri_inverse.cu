@@ -1,0 +1,81 @@
+// Inverse of 64x64 unit lower-triangular matrices  X = (I + A)^-1,  A strictly lower triangular, fp32.
+// Shared by the GDN and KDA chunk kernels (the reference's solve_tri operator,
+// fla/ops/ascendc/gdn/chunk_gdn_fwd/solve_tri/README.md:9-13, which inverts in bf16 on the matrix unit;
+// here the inverse is built in fp32 and rounded to bf16 once at the end).
+// One CTA handles four matrices (64 threads each).  Thread c solves column c by right-looking forward
+// substitution:  r = e_c;  for j: x_j = r_j;  r_i -= A[i][j] x_j (i > j).  The updates of one step are
+// independent, so the FMA pipeline stays full, and a warp skips the steps before its first column
+// because the entries above a column's diagonal are zero.
+#include "gdn_common.cuh"
+#include "tri_inverse.h"
+
+namespace fla {
+
+constexpr int kTriStride = 68;   // fp32 row stride of A^T in shared memory (16-byte aligned rows, spread banks)
+
+__global__ void __launch_bounds__(256) tri_inverse_kernel(TriInverseParams p) {
+  extern __shared__ float tri_smem[];
+  const int tid = threadIdx.x, grp = tid / 64, c = tid % 64;
+  const int n = blockIdx.z;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const int chunk = blockIdx.x;
+  if (chunk >= sq.nt) return;
+  const int hv = blockIdx.y * 4 + grp;
+  const bool active = hv < p.HV;
+  const int rows = min(kC, sq.len - chunk * kC);
+  const int64_t tok0 = int64_t(sq.bos) + chunk * kC;
+  const int64_t cidx = (int64_t(sq.cbase) + chunk) * p.HV + hv;
+  float* AT = tri_smem + grp * kC * kTriStride;
+  if (active) {
+    const float* src = p.at + cidx * (kC * kC);     // A^T row-major: src[j * 64 + i] = A[i][j]
+#pragma unroll 8
+    for (int j = 0; j < kC; ++j) AT[j * kTriStride + c] = src[j * kC + c];
+  }
+  __syncthreads();
+  if (!active) return;
+  float x[kC];
+#pragma unroll
+  for (int i = 0; i < kC; ++i) x[i] = (i == c) ? 1.f : 0.f;
+  const int jmin = c & ~31;  // warp-uniform
+#pragma unroll
+  for (int j = 0; j < kC - 1; ++j) {
+    if (j >= jmin) {
+      const float xj = x[j];
+      const float* col = AT + j * kTriStride;
+#pragma unroll
+      for (int i4 = (j + 1) & ~3; i4 < kC; i4 += 4) {
+        const float4 a4 = *reinterpret_cast<const float4*>(col + i4);
+        if (i4 > j) x[i4] -= a4.x * xj;
+        if (i4 + 1 > j) x[i4 + 1] -= a4.y * xj;
+        if (i4 + 2 > j) x[i4 + 2] -= a4.z * xj;
+        if (i4 + 3 > j) x[i4 + 3] -= a4.w * xj;
+      }
+    }
+  }
+  if (p.x_rows) {            // token-major rows: X[(tok0 + i), hv, c]
+    bf16* xg = p.x_rows + ((tok0 * p.HV + hv) * kC) + c;
+#pragma unroll
+    for (int i = 0; i < kC; ++i)
+      if (i < rows) xg[int64_t(i) * p.HV * kC] = __float2bfloat16_rn(x[i]);
+  }
+  if (p.x_img) {             // swizzled 64x64 operand panel per (chunk, head); rows past the sequence end are zero
+    uint8_t* img = reinterpret_cast<uint8_t*>(p.x_img + cidx * (kC * kC));
+#pragma unroll
+    for (int i = 0; i < kC; ++i) *reinterpret_cast<bf16*>(img + panel_off(i, c)) = __float2bfloat16_rn(i < rows ? x[i] : 0.f);
+  }
+}
+
+int launch_tri_inverse(const TriInverseParams& p, int nt_max, int N, cudaStream_t stream) {
+  const int smem = 4 * kC * kTriStride * 4;
+  static bool attr_done_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 6;
+  if (!attr_done_dev[dev]) {
+    if (cudaFuncSetAttribute(tri_inverse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 6;
+    attr_done_dev[dev] = true;
+  }
+  tri_inverse_kernel<<<dim3(nt_max, (p.HV + 3) / 4, N), 256, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 6;
+}
+
+}  // namespace fla

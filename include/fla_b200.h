@@ -60,7 +60,7 @@ FLA_API int fla_b200_version(void);
  * profiler).  While enabled, every kernel launch of the library is bracketed by CUDA events on the
  * launching stream.  Enabling or disabling clears earlier records.  kernel_timing_read synchronises the
  * recorded events and returns the summed duration and the number of launches of `kernel_name`
- * (names: "gdn_prep", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par", "recurrent_gdn", "causal_conv1d_fwd",
+ * (names: "gdn_prep", "tri_inverse", "kda_prep", "kda_fwd", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par", "recurrent_gdn", "causal_conv1d_fwd",
  * "causal_conv1d_update"). */
 FLA_API int fla_b200_kernel_timing_enable(int enable);
 FLA_API int fla_b200_kernel_timing_read(const char* kernel_name, float* total_ms, int* launches);
@@ -161,7 +161,8 @@ FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* a
  *   cu_seqlens int32 [N+1] device (requires B == 1) with chunk_offsets int32 [N+1] device (prefix sum of
  *   ceil(len/64)), max_seqlen and total_chunks given by the host.  All four are ignored for dense batches.
  * Token tensors need a contiguous last dim, 16-byte aligned rows and batch rows laid out back to back.
- * Workspace: a 256-byte status block (first int32 becomes FLA_ERR_TIMEOUT if a device-side wait ran out). */
+ * Workspace: a 256-byte status block (first int32 becomes FLA_ERR_TIMEOUT if a device-side wait ran out)
+ * followed by a 16 KB fp32 scratch tile per (chunk, value head) for the triangular inverse. */
 typedef struct fla_gdn_chunk_fwd_args {
   fla_tensor_t q, k, v, g, beta, initial_state;
   fla_tensor_t o, final_state, gam, x_inv, s_img, vn_img;
