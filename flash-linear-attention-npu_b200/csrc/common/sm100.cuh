@@ -206,12 +206,27 @@ __device__ __forceinline__ uint64_t operand_desc(const Operand& o, int kstep) {
   if (o.mn_major) return desc_mnmajor(o.saddr + kstep * 2048, o.panel_stride);
   return desc_kmajor(o.saddr + (kstep >> 2) * o.panel_stride + (kstep & 3) * 32);
 }
-// D (+)= A * B over `ksteps` MMAs of K = 16 each.  Single-thread call.
+// Upper 32 bits of every descriptor used here: stride byte offset 1024, descriptor version 1, SWIZZLE_128B.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+// Lower 32 bits at k-step 0: start address, and the leading byte offset (panel stride) of MN-major views.
+__device__ __forceinline__ uint32_t operand_desc_lo(const Operand& o) {
+  return ((o.saddr >> 4) & 0x3FFFu) | (o.mn_major ? ((o.panel_stride >> 4) & 0x3FFFu) << 16 : (1u << 16));
+}
+// D (+)= A * B over `ksteps` MMAs of K = 16 each.  Single-thread call; call with a literal `ksteps` so the
+// loop unrolls.  Issue cost matters (one thread feeds the tensor core): per k-step only the start-address
+// field of each descriptor changes, by a constant, so each MMA costs two integer adds.
 __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N,
                                          int ksteps, bool accumulate) {
   const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major, b.mn_major);
+  const uint32_t alo = operand_desc_lo(a), blo = operand_desc_lo(b);
+  const uint32_t aps = a.panel_stride >> 4, bps = b.panel_stride >> 4;
+#pragma unroll
   for (int ks = 0; ks < ksteps; ++ks) {
-    mma_ss(d_tmem, operand_desc(a, ks), operand_desc(b, ks), idesc, (accumulate || ks > 0) ? 1u : 0u);
+    const uint32_t ao = a.mn_major ? uint32_t(ks) * 128u : uint32_t(ks >> 2) * aps + uint32_t(ks & 3) * 2u;
+    const uint32_t bo = b.mn_major ? uint32_t(ks) * 128u : uint32_t(ks >> 2) * bps + uint32_t(ks & 3) * 2u;
+    const uint64_t ad = (uint64_t(kDescHi) << 32) | uint64_t(alo + ao);
+    const uint64_t bd = (uint64_t(kDescHi) << 32) | uint64_t(blo + bo);
+    mma_ss(d_tmem, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 

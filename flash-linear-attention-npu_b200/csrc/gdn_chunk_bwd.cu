@@ -417,15 +417,24 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     mbar_init_fence();
   }
   // q, k rows of the chunk (shared by the value heads of the group) and the static zero rows of the lo operand
-  for (int idx = tid; idx < 2048; idx += 256) {
-    const int r = (idx / 16) & 63, ch = idx % 16;
-    const bool isk = idx >= 1024;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (r < rows) {
-      const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
-      val = *reinterpret_cast<const uint4*>(src + ch * 8);
+  {
+    uint4 val[8];   // all loads in flight before the first one is consumed
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * 256, r = (idx / 16) & 63, ch = idx % 16;
+      const bool isk = idx >= 1024;
+      val[i] = make_uint4(0, 0, 0, 0);
+      if (r < rows) {
+        const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
+        val[i] = *reinterpret_cast<const uint4*>(src + ch * 8);
+      }
     }
-    *reinterpret_cast<uint4*>(smem + rOffQK + (ch / 8) * rQKPanel + panel_chunk_off(r + (isk ? 64 : 0), ch % 8)) = val;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * 256, r = (idx / 16) & 63, ch = idx % 16;
+      const bool isk = idx >= 1024;
+      *reinterpret_cast<uint4*>(smem + rOffQK + (ch / 8) * rQKPanel + panel_chunk_off(r + (isk ? 64 : 0), ch % 8)) = val[i];
+    }
   }
   for (int idx = tid; idx < 512; idx += 256) *reinterpret_cast<uint4*>(smem + rOffAL + idx * 16) = make_uint4(0, 0, 0, 0);
   fence_async_smem();

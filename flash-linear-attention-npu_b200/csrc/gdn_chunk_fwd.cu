@@ -45,18 +45,15 @@ struct GdnFwdParams {
 };
 
 // --------------------------------------------------------------------------------------------- prep
-constexpr int kAStride = 68;  // fp32 row stride of the 64x64 score tiles in shared memory
-
+// One CTA per (chunk, q/k head).  The k rows are staged twice ([k; k], 128 rows) so that one M = 128 product
+// leaves K K^T in TMEM lanes 0..63 and again in lanes 64..127: two value heads of the GVA group are then
+// processed at once, each thread holding one row of K K^T for its head in registers.
 __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int kTile = kC * kAStride * 4;                       // bytes of one fp32 64x64 tile (padded rows)
-  uint8_t* k_pan = smem;                                        // 2 panels x 64 rows; dead after the MMA
-  float* at1 = reinterpret_cast<float*>(smem);                   // A^T of the second head (reuses the k panels)
-  float* kk_s = reinterpret_cast<float*>(smem + kTile);          // [64][68]  K K^T
-  float* at0 = reinterpret_cast<float*>(smem + 2 * kTile);       // A^T of the first head
-  float* g_s = reinterpret_cast<float*>(smem + 3 * kTile);       // [2][64] raw g, then gam
-  float* b_s = g_s + 2 * kC;                                     // [2][64]
+  uint8_t* k_pan = smem;                         // 2 panels x 128 rows (rows r and r + 64 hold the same token)
+  __shared__ float gam_s[2][kC];
+  __shared__ float wsum_s[4];
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t bar;
 
@@ -68,11 +65,21 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   const int rows = min(kC, sq.len - t0);
   const int64_t tok0 = int64_t(sq.bos) + t0;
 
-  for (int idx = tid; idx < kC * 16; idx += 128) {
-    const int r = idx / 16, ch = idx % 16;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (r < rows) val = *reinterpret_cast<const uint4*>(p.k + (tok0 + r) * p.k_st + hk * p.k_sh + ch * 8);
-    *reinterpret_cast<uint4*>(k_pan + (ch / 8) * 8192 + panel_chunk_off(r, ch % 8)) = val;
+  {
+    uint4 val[8];   // all eight loads in flight before the first one is consumed
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * 128, r = idx / 16, ch = idx % 16;
+      val[i] = make_uint4(0, 0, 0, 0);
+      if (r < rows) val[i] = *reinterpret_cast<const uint4*>(p.k + (tok0 + r) * p.k_st + hk * p.k_sh + ch * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * 128, r = idx / 16, ch = idx % 16;
+      uint8_t* pan = k_pan + (ch / 8) * 16384;
+      *reinterpret_cast<uint4*>(pan + panel_chunk_off(r, ch % 8)) = val[i];
+      *reinterpret_cast<uint4*>(pan + panel_chunk_off(r + 64, ch % 8)) = val[i];
+    }
   }
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 64);
@@ -88,66 +95,46 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   tc_fence_after();
   const uint32_t tbase = tmem_base_s;
   if (tid == 0) {
-    const Operand kop{smem_u32(k_pan), 8192u, 0};
-    mma_tile(tbase, kop, kop, 64, 64, kK / 16, false);  // K K^T, M = 64: row r -> lane (r % 16) + 32 (r / 16)
+    const Operand a{smem_u32(k_pan), 16384u, 0};
+    const Operand b{smem_u32(k_pan), 16384u, 0};           // N = 64: rows 0..63
+    mma_tile(tbase, a, b, 128, 64, 8, false);
     mma_commit(&bar);
   }
+  const int G = p.HV / p.HK;
+  const int hsel = tid / 64, tok = tid % 64;
   const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
   tc_fence_after();
-  if (ok) {
-#pragma unroll
-    for (int c0 = 0; c0 < kC; c0 += 16) {
-      float v[16];
-      tmem_ld16(tmem_addr(tbase, warp * 32, c0), v);
-      tmem_ld_wait();
-      if (lane < 16) {
-        float* dst = kk_s + (warp * 16 + lane) * kAStride + c0;
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-      }
-    }
-  }
+  float kk[kC];
+  if (ok) tmem_ld_row64(tmem_addr(tbase, warp * 32, 0), kk);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 64);
   if (!ok) return;
 
-  const int G = p.HV / p.HK;
-  const int hsel = tid / 64, c = tid % 64;
-  float* AT = hsel ? at1 : at0;                                  // AT[j][i] = A[i][j]
-  float* gs = g_s + hsel * kC;
-  float* bs = b_s + hsel * kC;
   for (int h0 = 0; h0 < G; h0 += 2) {
     const int h = h0 + hsel;
     const bool active = h < G;
-    const int hv = hk * G + h;
-    if (active) {
-      gs[c] = c < rows ? ld_scalar(p.g, (tok0 + c) * p.g_st + hv, p.g_is_f32) : 0.f;
-      bs[c] = c < rows ? ld_scalar(p.beta, (tok0 + c) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    const int hv = hk * G + min(h, G - 1);
+    // chunk-local cumulative sum of g over the 64 tokens of this head (two warps)
+    float gv = (active && tok < rows) ? ld_scalar(p.g, (tok0 + tok) * p.g_st + hv, p.g_is_f32) : 0.f;
+    const float bi = (active && tok < rows) ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, gv, o);
+      if (lane >= o) gv += up;
     }
+    if (lane == 31) wsum_s[warp] = gv;
     __syncthreads();
-    float gam = 0.f;
-    if (active) {
-      for (int j = 0; j <= c; ++j) gam += gs[j];
-    }
-    __syncthreads();
-    if (active) {
-      gs[c] = gam;
-      if (c < rows) p.gam[(tok0 + c) * p.HV + hv] = gam;
-    }
-    __syncthreads();
-    if (active) {
-      // row c of A^T, i.e. column c of A below the diagonal: A[i][c] = beta_i exp(gam_i - gam_c) (k_i . k_c)
-      for (int i = c + 1; i < kC; ++i) AT[c * kAStride + i] = bs[i] * __expf(gs[i] - gam) * kk_s[i * kAStride + c];
-    }
+    if (warp & 1) gv += wsum_s[warp - 1];
+    gam_s[hsel][tok] = gv;
+    if (active && tok < rows) p.gam[(tok0 + tok) * p.HV + hv] = gv;
     __syncthreads();
     if (active) {
-      // hand A^T to the inverse kernel (coalesced rows; entries on and above the diagonal are never read)
-      float* dst = p.at + ((int64_t(sq.cbase) + blockIdx.x) * p.HV + hv) * (kC * kC);
-      for (int idx = c; idx < kC * 16; idx += 64) {
-        const int j = idx / 16, q4 = idx % 16;
-        *reinterpret_cast<float4*>(dst + j * kC + q4 * 4) = *reinterpret_cast<const float4*>(AT + j * kAStride + q4 * 4);
-      }
+      // A^T[j][i] = beta_i exp(gam_i - gam_j) (k_i . k_j) for j < i, written coalesced along i
+      float* at = p.at + ((int64_t(sq.cbase) + blockIdx.x) * p.HV + hv) * (kC * kC);
+#pragma unroll
+      for (int j = 0; j < kC - 1; ++j)
+        if (j < tok) at[j * kC + tok] = bi * __expf(gv - gam_s[hsel][j]) * kk[j];
     }
     __syncthreads();
   }
@@ -546,7 +533,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
-  const int prep_smem = (3 * kC * kAStride + 4 * kC) * 4 + 1024;
+  const int prep_smem = 32768 + 1024;
   static bool attr_done_dev[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
