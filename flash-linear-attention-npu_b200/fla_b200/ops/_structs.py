@@ -42,3 +42,7 @@ class KdaChunkFwdArgs(ctypes.Structure):
                                            "final_state", "gk", "cu_seqlens", "chunk_offsets")] + [
         ("scale", ctypes.c_float), ("lower_bound", ctypes.c_float), ("gate_mode", ctypes.c_int32),
         ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32), ("total_chunks", ctypes.c_int32)]
+
+
+class L2NormArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("x", "y", "rstd", "dy", "dx")] + [("eps", ctypes.c_float)]

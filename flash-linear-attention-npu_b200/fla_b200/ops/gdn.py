@@ -138,14 +138,22 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     Saves q, k, v, beta, gam, X and the split per-chunk states / v_new instead of recomputing them."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, output_dtype):
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, output_dtype, qk_l2norm):
         need_grad = any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
         q_, k_, v_, g_, b_ = (_as_rows(x.detach()) for x in (q, k, v, g, beta))
+        ctx.qk_l2norm = qk_l2norm
+        if qk_l2norm:
+            # q, k <- x * rsqrt(sum x^2 + 1e-6), stored in the input dtype like the reference's l2norm_fwd
+            # (examples/flash_gated_delta_rule.py:1046-1050); rstd is kept for the backward
+            from .l2norm import l2norm_fwd
+            q_, q_rstd = l2norm_fwd(q_)
+            k_, k_rstd = l2norm_fwd(k_)
         o, ht, saved = gdn_chunk_fwd(q_, k_, v_, g_, b_, scale, None if initial_state is None else initial_state.detach(),
                                      output_final_state, cu_seqlens, save_for_backward=need_grad,
                                      output_dtype=output_dtype)
         if need_grad:
-            ctx.save_for_backward(q_, k_, v_, b_, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"])
+            extra = (q_rstd, k_rstd) if qk_l2norm else ()
+            ctx.save_for_backward(q_, k_, v_, b_, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"], *extra)
             ctx.meta = {kk: saved[kk] for kk in ("cu", "co", "max_len", "total_chunks", "N")}
             ctx.scale = scale
             ctx.has_h0 = initial_state is not None
@@ -154,12 +162,18 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, beta, gam, x_inv, s_img, vn_img = ctx.saved_tensors
+        q, k, v, beta, gam, x_inv, s_img, vn_img = ctx.saved_tensors[:8]
         saved = dict(ctx.meta, gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img)
         dq, dk, dv, dg, dbeta, dh0 = gdn_chunk_bwd(q, k, v, beta, saved, do.contiguous(), dht, ctx.scale, ctx.has_h0,
-                                                   grad_dtype=torch.float32 if ctx.in_dtypes[3] == torch.float32 else None)
+                                                   grad_dtype=torch.float32 if (ctx.in_dtypes[3] == torch.float32 or ctx.qk_l2norm) else None)
+        if ctx.qk_l2norm:
+            from .l2norm import l2norm_bwd
+            q_rstd, k_rstd = ctx.saved_tensors[8:10]
+            dq = l2norm_bwd(q, q_rstd, dq)
+            dk = l2norm_bwd(k, k_rstd, dk)
         dts = ctx.in_dtypes
-        return (dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]), dg.to(dts[3]), dbeta.to(dts[4]), None, dh0, None, None, None)
+        return (dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]), dg.to(dts[3]), dbeta.to(dts[4]), None, dh0, None, None, None,
+                None)
 
 
 def chunk_gated_delta_rule_fwd_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, cu_seqlens=None,
@@ -186,8 +200,6 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
         raise NotImplementedError(f"{op}: head_first layouts are not provided; pass [B,T,H,D] tensors")
     if chunk_size != CHUNK:
         raise NotImplementedError(f"{op}: chunk_size must be {CHUNK}")
-    if use_qk_l2norm_in_kernel:
-        raise NotImplementedError(f"{op}: use_qk_l2norm_in_kernel is not available yet")
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
-                                             output_dtype)
+                                             output_dtype, bool(use_qk_l2norm_in_kernel))

@@ -247,6 +247,20 @@ FLA_API int fla_b200_kda_chunk_fwd_workspace_size(const fla_kda_chunk_fwd_args* 
 FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* args, void* workspace, uint64_t workspace_bytes,
                                    void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Row-wise L2 normalisation (the q/k normalisation behind use_qk_l2norm_in_kernel).
+ * Replaces the reference's Triton l2norm_fwd / l2norm_bwd (fla/ops/triton/triton_core/l2norm.py:131-234).
+ *   fwd: x [rows, D] -> y [rows, D] = x * rstd, rstd [rows] f32 = rsqrt(sum x^2 + eps)
+ *   bwd: y, rstd, dy -> dx = dy * rstd - (sum dy * y) * y * rstd
+ * x, y, dy, dx bf16|f32 with contiguous columns and 16-byte aligned rows; D % 8 == 0, D <= 1024.
+ * Single-phase (no workspace). */
+typedef struct fla_l2norm_args {
+  fla_tensor_t x, y, rstd, dy, dx;
+  float eps;
+} fla_l2norm_args;
+FLA_API int fla_b200_l2norm_fwd(const fla_l2norm_args* args, void* stream);
+FLA_API int fla_b200_l2norm_bwd(const fla_l2norm_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
