@@ -223,7 +223,10 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     if (!kwarp) {
       tmem_ld_row64(trow + hColQK, acc);
 #pragma unroll
-      for (int j = 0; j < kC; ++j) acc[j] = (j <= tok) ? acc[j] * __expf(gam_i - gam_s[cur][j]) : 0.f;
+      for (int j = 0; j < kC; ++j) {  // branch-free: clamped exponent, arithmetic mask
+        const float e = __expf(fminf(gam_i - gam_s[cur][j], 0.f));
+        acc[j] *= (j <= tok) ? e : 0.f;
+      }
       row64_to_hilo(smem + hOffPH, smem + hOffPL, tok, acc);
     }
     if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
@@ -538,13 +541,15 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           const int j = half * 32 + jj;
-          dvv[jj] = (j <= tok) ? p.scale * dvv[jj] * __expf(gam_i - gam_s[j]) : 0.f;
+          const float e = p.scale * __expf(fminf(gam_i - gam_s[j], 0.f));
+          dvv[jj] *= (j <= tok) ? e : 0.f;
         }
       } else {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           const int j = half * 32 + jj;
-          const float dec = (j < tok) ? __expf(gam_i - gam_s[j]) : 0.f;
+          const float e = __expf(fminf(gam_i - gam_s[j], 0.f));
+          const float dec = (j < tok) ? e : 0.f;
           const float dA = -dvv[jj] * dec;
           ma_part += dA * sc[jj];
           dvv[jj] = dA * beta_i;

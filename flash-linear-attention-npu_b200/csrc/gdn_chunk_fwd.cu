@@ -159,7 +159,19 @@ struct FwdPrefetch {
   float gb;
 };
 
+#ifdef FLA_STAGE_CLOCKS
+__device__ long long g_stage_clocks[16];
+#define STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { long long now_ = clock64(); g_stage_clocks[i] += now_ - last_; last_ = now_; } } while (0)
+#define STAMPK(i) do { if (threadIdx.x == 63 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { long long now_ = clock64(); g_stage_clocks[i] += now_ - lastk_; lastk_ = now_; } } while (0)
+#else
+#define STAMP(i)
+#define STAMPK(i)
+#endif
+
 __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p) {
+#ifdef FLA_STAGE_CLOCKS
+  long long last_ = clock64(), lastk_ = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
@@ -285,6 +297,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     const float gam_last = gam_s[cur][rows - 1];
     const float gam_i = gam_s[cur][tok];
 
+    STAMP(9);
     // ---- stage 0: publish the state at chunk start (split copy for the MMAs, pre-decayed master in TMEM)
     row32_to_hilo(smem + kOffSH, smem + kOffSL, row, half, srow);
     {
@@ -299,6 +312,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     __syncthreads();
     tc_fence_after();
 
+    STAMP(0);
     // ---- stage 1: [Q;K] S (split state) and [Q;K] K^T
     if (tid == 0) {
       if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format
@@ -319,10 +333,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
+    STAMP(1);
     // ---- stage 2: k-side rows build Z = beta (V - exp(gam) K S); q-side rows build P = tril(QK^T * decay)
     float acc[32];
+    STAMPK(10);
     if (kside) {
       tmem_ld_row32(trow + kColRQ, acc);
+      STAMPK(11);
       const float eg = __expf(gam_i), bi = beta_s[cur][tok];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -331,21 +348,31 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i * 8 + j] = bi * (vv[j] - eg * acc[i * 8 + j]);
       }
+      STAMPK(12);
       row32_to_hilo(smem + kOffZH, smem + kOffZL, tok, half, acc);
+      STAMPK(13);
     } else {
       tmem_ld_row32(trow + kColQK, acc);
+      STAMPK(11);
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) {
         const int j = c0 + jj;
-        acc[jj] = (j <= tok) ? acc[jj] * __expf(gam_i - gam_s[cur][j]) : 0.f;
+        // branch-free: the exponent is clamped so that masked entries cannot produce inf * 0
+        const float e = __expf(fminf(gam_i - gam_s[cur][j], 0.f));
+        acc[jj] *= (j <= tok) ? e : 0.f;
       }
+      STAMPK(12);
       row32_to_hilo(smem + kOffQK, smem + kOffQK + kQKPanel, tok, half, acc);
+      STAMPK(13);
     }
     fence_async_smem();
+    STAMPK(14);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    STAMPK(15);
 
+    STAMP(2);
     // ---- stage 3: v_new = X Z  (rows 64..127 of the accumulator)
     if (tid == 0) {
       mma_tile(tbase + kColVN, opX, opZH, 128, 64, 4, false);
@@ -355,6 +382,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
+    STAMP(3);
     // ---- stage 4: k-side rows publish v_new and its decayed copy
     if (kside) {
       tmem_ld_row32(trow + kColVN, acc);
@@ -370,6 +398,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     __syncthreads();
     tc_fence_after();
 
+    STAMP(4);
     // ---- stage 5: P v_new (three passes) and the state update S += K^T vhat
     if (tid == 0) {
       if (p.vn_img) {
@@ -388,6 +417,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
+    STAMP(5);
     // ---- stage 6: output rows, next state, next chunk's operand panels
     if (!kside) {
       float qs[32];
@@ -414,6 +444,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     // The only readers of the q/k/X panels were this chunk's MMAs, which have completed; no barrier is needed
     // before the next iteration (its first barrier orders everything else).
     if (c + 1 < sq.nt) store_panels();
+    STAMP(6);
   }
 
   if (!dead && p.ht) {
@@ -560,3 +591,9 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   }
   return cuda_status(cudaGetLastError());
 }
+
+#ifdef FLA_STAGE_CLOCKS
+extern "C" FLA_API int fla_b200_debug_stage_clocks(long long* out16) {
+  return cudaMemcpyFromSymbol(out16, fla::g_stage_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
+}
+#endif

@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p) {
     tmem_ld_wait();
     if (quad < 2) {
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) sc[jj] = (half * 32 + jj <= tok) ? sc[jj] : 0.f;
+      for (int jj = 0; jj < 32; ++jj) sc[jj] = (half * 32 + jj <= tok) ? sc[jj] : 0.f;   // select: masked entries may be inf
       uint8_t* img = reinterpret_cast<uint8_t*>(p.p_img + cidx * kKdaPImg);
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
