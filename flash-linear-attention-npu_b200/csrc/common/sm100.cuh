@@ -155,7 +155,8 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 
 // ----------------------------------------------------------------------------- descriptors
 // Instruction descriptor for tcgen05.mma.kind::f16 with fp32 accumulate.
-// a_mn / b_mn: 0 = operand is K-major, 1 = MN-major.  a_fmt / b_fmt: 1 = bf16, 0 = fp16 (may differ).
+// a_mn / b_mn: 0 = operand is K-major, 1 = MN-major.  fmt: 1 = bf16, 0 = fp16; A and B must use the SAME
+// format (a bf16 x fp16 mix is rejected by the hardware as an illegal instruction).
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_mn, int b_mn, int a_fmt, int b_fmt) {
   return (1u << 4)                       // D format: f32
          | (uint32_t(a_fmt) << 7)        // A format
@@ -204,7 +205,6 @@ struct Operand {
   uint32_t saddr;         // shared address of panel 0
   uint32_t panel_stride;  // bytes between panels (rows * 128)
   int mn_major;           // 0: rows are M/N, columns are the reduction dim; 1: the transpose view
-  int fp16 = 0;           // element format: 0 = bf16, 1 = fp16
 };
 __device__ __forceinline__ uint64_t operand_desc(const Operand& o, int kstep) {
   if (o.mn_major) return desc_mnmajor(o.saddr + kstep * 2048, o.panel_stride);
@@ -221,7 +221,7 @@ __device__ __forceinline__ uint32_t operand_desc_lo(const Operand& o) {
 // field of each descriptor changes, by a constant, so each MMA costs two integer adds.
 __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N,
                                          int ksteps, bool accumulate) {
-  const uint32_t idesc = make_idesc(M, N, a.mn_major, b.mn_major, a.fp16 ? 0 : 1, b.fp16 ? 0 : 1);
+  const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major, b.mn_major);
   const uint32_t alo = operand_desc_lo(a), blo = operand_desc_lo(b);
   const uint32_t aps = a.panel_stride >> 4, bps = b.panel_stride >> 4;
 #pragma unroll

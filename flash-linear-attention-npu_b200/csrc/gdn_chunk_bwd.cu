@@ -33,7 +33,7 @@ struct GdnBwdParams {
   const bf16* q; const bf16* k; const bf16* v; const bf16* dO;
   const void* beta;
   const float* gam; const bf16* X;
-  const bf16* s_img; const bf16* vn_img;
+  const bf16* s_img; const bf16* vn_img; const bf16* p_img;
   bf16* ds_img;        // [chunks, HV, 2, 2, 128x64]  state gradient entering each chunk (hi, lo)
   bf16* dz_img;        // [chunks, HV, 2, {128x64 hi: rows 0-63 dO, rows 64-127 dZ_hi ; 64x64 dZ_lo}]
   float* bz;           // [2, tokens, HV] partial sums over a V block of dZ * V
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar;
+  __shared__ __align__(8) uint64_t bar, pbar;
 
   const int tid = threadIdx.x, warp = tid / 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -88,13 +88,19 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
   }
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&pbar, 1);
     mbar_init_fence();
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
-  uint32_t phase = 0;
+  uint32_t phase = 0, pphase = 0;
   const uint32_t sb = smem_u32(smem);
+  auto issue_p_load = [&](int c) {   // P = tril(Q K^T * decay) of chunk c, built by the forward's prep kernel
+    const bf16* src = p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192;
+    mbar_arrive_expect_tx(&pbar, 16384);
+    bulk_load(sb + hOffPH, src, 16384, &pbar);
+  };
 
   DhuPrefetch pf;
   auto prefetch_load = [&](int c) {
@@ -128,6 +134,21 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     if (kwarp) pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
     else pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
   };
+  // Touch the next chunk's rows early so that the register loads issued late in the iteration hit L2.
+  auto prefetch_l2 = [&](int c) {
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+    const int r = tid & 63;
+    if (r < rows) {
+      const bf16* src = tid >= 64 ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 64));
+      const bf16* s2 = tid >= 64 ? p.v + (tok0 + r) * p.v_st + hv * p.v_sh + vb * kBV : p.dO + (tok0 + r) * p.do_st + hv * p.do_sh + vb * kBV;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(s2));
+      if (tid < 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.X + ((tok0 + r) * p.HV + hv) * kC));
+    }
+  };
   uint4 rcur[8];
   auto prefetch_store = [&](int c) {
 #pragma unroll
@@ -153,7 +174,6 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
   };
 
   const Operand opQK{sb + hOffQK, hQKPanel, 0};
-  const Operand opKb{sb + hOffQK + 8192, hQKPanel, 0};
   const Operand opQKT{sb + hOffQK, hQKPanel, 1};               // [q^T | k^T]: M = 128 key dims, reduction over 128 rows
   const Operand opDSH{sb + hOffDSH, 16384, 1}, opDSL{sb + hOffDSL, 16384, 1};
   const Operand opPTh{sb + hOffPH - 8192, 8192, 1}, opPTl{sb + hOffPL - 8192, 8192, 1};  // P^T, valid rows 64..127
@@ -166,6 +186,7 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
   const int c_last = sq.nt - 1;
   prefetch_load(c_last);
   prefetch_store(c_last);
+  if (tid == 0) issue_p_load(c_last);
   if (p.dht) {
     const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
 #pragma unroll
@@ -201,7 +222,7 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     __syncthreads();
     tc_fence_after();
 
-    // ---- stage 1: [Q;K] dS' and [Q;K] K^T
+    // ---- stage 1: [Q;K] dS'  and  U1 = P^T dO (valid accumulator rows 64..127)
     if (tid == 0) {
       bf16* dst = p.ds_img + (cidx * 2 + vb) * (2 * 8192);
       bulk_store(dst, sb + hOffDSH, 16384);
@@ -209,44 +230,21 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
       bulk_commit();
       mma_tile(tbase + hColW1, opQK, opDSH, 128, 64, 8, false);
       mma_tile(tbase + hColW1, opQK, opDSL, 128, 64, 8, true);
-      mma_tile(tbase + hColQK, opQK, opKb, 128, 64, 8, false);
-      mma_commit(&bar);
-    }
-    if (c > 0) prefetch_load(c - 1);
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
-    tc_fence_after();
-
-    // ---- stage 2: q-side rows build P = tril(Q K^T * decay)
-    float acc[kBV];
-    if (!kwarp) {
-      tmem_ld_row64(trow + hColQK, acc);
-#pragma unroll
-      for (int j = 0; j < kC; ++j) {  // branch-free: clamped exponent, arithmetic mask
-        const float e = __expf(fminf(gam_i - gam_s[cur][j], 0.f));
-        acc[j] *= (j <= tok) ? e : 0.f;
-      }
-      row64_to_hilo(smem + hOffPH, smem + hOffPL, tok, acc);
-    }
-    if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- stage 3: U1 = P^T dO  (valid accumulator rows 64..127)
-    if (tid == 0) {
+      ok = mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT) && ok;   // P panels have landed
       mma_tile(tbase + hColU1, opPTh, opDO, 128, 64, 4, false);
       mma_tile(tbase + hColU1, opPTl, opDO, 128, 64, 4, true);
       mma_commit(&bar);
     }
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
+    pphase ^= 1;
+    if (c > 0) prefetch_l2(c - 1);
+    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT) && ok;
     phase ^= 1;
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
+    if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
 
     // ---- stage 4: k-side rows: dVn = scale U1 + e^{gam_L - gam} (K dS')
+    float acc[kBV];
     if (kwarp) {
       float w1[kBV];
       tmem_ld_row64(trow + hColW1, w1);
@@ -335,6 +333,7 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
       mma_tile(tbase + hColDS, opQKT, opDSL, 128, 64, 8, true);
       mma_commit(&bar);
     }
+    if (c > 0) prefetch_load(c - 1);   // L2-resident by now; travels while the MMAs run
     ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
     phase ^= 1;
     if (!__syncthreads_and(ok)) break;
@@ -342,7 +341,10 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
 
     // ---- stage 8: new dS to registers; next chunk's operands
     tmem_ld_row64(trow + hColDS, srow);
-    if (tid == 0) bulk_wait_read();
+    if (tid == 0) {
+      bulk_wait_read();                  // the dZ images have left the P / dVn / dZ panels
+      if (c > 0) issue_p_load(c - 1);    // ... which now receive the next chunk's P
+    }
     tc_fence_before();
     __syncthreads();
     if (c > 0) {
@@ -754,12 +756,14 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   const int gdt = a->dq.dtype;
   if (a->dk.dtype != gdt || a->dv.dtype != gdt || a->dg.dtype != gdt || a->dbeta.dtype != gdt) return FLA_ERR_DTYPE;
   const fla_tensor_t &gam = a->gam, &X = a->x_inv;
-  if (!gam.data || !X.data || !a->s_img.data || !a->vn_img.data) return FLA_ERR_NULL;
+  if (!gam.data || !X.data || !a->s_img.data || !a->vn_img.data || !a->p_img.data) return FLA_ERR_NULL;
   if (gam.dtype != FLA_F32 || gam.ndim != 3 || gam.shape[0] != B || gam.shape[1] != T || gam.shape[2] != HV ||
       gam.stride[2] != 1 || gam.stride[1] != HV || (B > 1 && gam.stride[0] != T * HV))
     return FLA_ERR_SHAPE;
   if (X.dtype != FLA_BF16 || X.ndim != 4 || X.shape[0] != B || X.shape[1] != T || X.shape[2] != HV || X.shape[3] != kC ||
       X.stride[3] != 1 || X.stride[2] != kC || X.stride[1] != HV * kC || !aligned16(X.data))
+    return FLA_ERR_SHAPE;
+  if (a->p_img.dtype != FLA_BF16 || a->p_img.ndim != 1 || a->p_img.shape[0] != total_chunks * HV * 8192 || !aligned16(a->p_img.data))
     return FLA_ERR_SHAPE;
   if (a->s_img.dtype != FLA_BF16 || a->s_img.ndim != 1 || a->s_img.shape[0] != total_chunks * HV * kSImg || !aligned16(a->s_img.data))
     return FLA_ERR_SHAPE;
@@ -782,6 +786,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   p.v = static_cast<const bf16*>(a->v.data); p.dO = static_cast<const bf16*>(a->d_o.data);
   p.beta = a->beta.data; p.gam = static_cast<const float*>(gam.data); p.X = static_cast<const bf16*>(X.data);
   p.s_img = static_cast<const bf16*>(a->s_img.data); p.vn_img = static_cast<const bf16*>(a->vn_img.data);
+  p.p_img = static_cast<const bf16*>(a->p_img.data);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.status = reinterpret_cast<int*>(ws);
   p.ds_img = reinterpret_cast<bf16*>(ws + off_ds);

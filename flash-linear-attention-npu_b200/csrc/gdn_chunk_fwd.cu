@@ -32,6 +32,7 @@ struct GdnFwdParams {
   float* gam;          // [tokens, HV]      chunk-local cumulative log decay (saved for backward)
   bf16* X;             // [tokens, HV, 64]  row i of the chunk's (I + A)^-1 (saved for backward)
   float* at;           // [chunks, HV, 64, 64] scratch: A^T handed to the triangular-inverse kernel
+  bf16* p_img;         // [chunks, HV, 2, 64x64] tril(Q K^T * decay) as hi / lo operand panels (scratch, reused by backward)
   const float* h0;     // [N, HV, K, V] or null
   float* ht;           // [N, HV, K, V] or null
   void* o;             // [tokens, HV, V]
@@ -45,15 +46,15 @@ struct GdnFwdParams {
 };
 
 // --------------------------------------------------------------------------------------------- prep
-// One CTA per (chunk, q/k head).  The k rows are staged twice ([k; k], 128 rows) so that one M = 128 product
-// leaves K K^T in TMEM lanes 0..63 and again in lanes 64..127: two value heads of the GVA group are then
-// processed at once, each thread holding one row of K K^T for its head in registers.
+// One CTA per (chunk, q/k head).  One M = 128 product [q; k] k^T leaves Q K^T in TMEM lanes 0..63 and K K^T in
+// lanes 64..127; each thread keeps its row in registers and, per value head of the GVA group, the q-side
+// threads emit P = tril(Q K^T * e^{gam_i - gam_j}) as split operand panels and the k-side threads emit A^T.
 __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* k_pan = smem;                         // 2 panels x 128 rows (rows r and r + 64 hold the same token)
-  __shared__ float gam_s[2][kC];
-  __shared__ float wsum_s[4];
+  uint8_t* qk_pan = smem;                        // 2 panels x 128 rows: rows 0..63 q, rows 64..127 k
+  __shared__ float gam_s[kC];
+  __shared__ float wsum_s[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t bar;
 
@@ -64,21 +65,22 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   if (t0 >= sq.len) return;
   const int rows = min(kC, sq.len - t0);
   const int64_t tok0 = int64_t(sq.bos) + t0;
-
   {
-    uint4 val[8];   // all eight loads in flight before the first one is consumed
+    uint4 val[16];   // all loads in flight before the first one is consumed
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * 128, r = idx / 16, ch = idx % 16;
+    for (int i = 0; i < 16; ++i) {
+      const int idx = tid + i * 128, r = (idx / 16) & 63, ch = idx % 16;
+      const bool isk = idx >= 1024;
       val[i] = make_uint4(0, 0, 0, 0);
-      if (r < rows) val[i] = *reinterpret_cast<const uint4*>(p.k + (tok0 + r) * p.k_st + hk * p.k_sh + ch * 8);
+      if (r < rows) {
+        const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
+        val[i] = *reinterpret_cast<const uint4*>(src + ch * 8);
+      }
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * 128, r = idx / 16, ch = idx % 16;
-      uint8_t* pan = k_pan + (ch / 8) * 16384;
-      *reinterpret_cast<uint4*>(pan + panel_chunk_off(r, ch % 8)) = val[i];
-      *reinterpret_cast<uint4*>(pan + panel_chunk_off(r + 64, ch % 8)) = val[i];
+    for (int i = 0; i < 16; ++i) {
+      const int idx = tid + i * 128, r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
+      *reinterpret_cast<uint4*>(qk_pan + (ch / 8) * 16384 + panel_chunk_off(r, ch % 8)) = val[i];
     }
   }
   if (warp == 0) {
@@ -95,46 +97,70 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   tc_fence_after();
   const uint32_t tbase = tmem_base_s;
   if (tid == 0) {
-    const Operand a{smem_u32(k_pan), 16384u, 0};
-    const Operand b{smem_u32(k_pan), 16384u, 0};           // N = 64: rows 0..63
+    const Operand a{smem_u32(qk_pan), 16384u, 0};
+    const Operand b{smem_u32(qk_pan) + 8192u, 16384u, 0};   // k rows as B (N = 64 tokens)
     mma_tile(tbase, a, b, 128, 64, 8, false);
     mma_commit(&bar);
   }
   const int G = p.HV / p.HK;
-  const int hsel = tid / 64, tok = tid % 64;
+  const bool kside = tid >= 64;
+  const int tok = tid & 63;
   const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
   tc_fence_after();
-  float kk[kC];
-  if (ok) tmem_ld_row64(tmem_addr(tbase, warp * 32, 0), kk);
+  float sc[kC];   // my row of Q K^T (q side) or K K^T (k side)
+  if (ok) tmem_ld_row64(tmem_addr(tbase, warp * 32, 0), sc);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 64);
   if (!ok) return;
 
-  for (int h0 = 0; h0 < G; h0 += 2) {
-    const int h = h0 + hsel;
-    const bool active = h < G;
-    const int hv = hk * G + min(h, G - 1);
-    // chunk-local cumulative sum of g over the 64 tokens of this head (two warps)
-    float gv = (active && tok < rows) ? ld_scalar(p.g, (tok0 + tok) * p.g_st + hv, p.g_is_f32) : 0.f;
-    const float bi = (active && tok < rows) ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+  for (int h = 0; h < G; ++h) {
+    const int hv = hk * G + h;
+    const int64_t cidx = (int64_t(sq.cbase) + blockIdx.x) * p.HV + hv;
+    // chunk-local cumulative sum of g (threads 0..63, two warps)
+    float gv = 0.f;
+    if (!kside) {
+      gv = tok < rows ? ld_scalar(p.g, (tok0 + tok) * p.g_st + hv, p.g_is_f32) : 0.f;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float up = __shfl_up_sync(0xffffffffu, gv, o);
-      if (lane >= o) gv += up;
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, gv, o);
+        if (lane >= o) gv += up;
+      }
+      if (lane == 31) wsum_s[warp] = gv;
     }
-    if (lane == 31) wsum_s[warp] = gv;
+    const float bi = (kside && tok < rows) ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
     __syncthreads();
-    if (warp & 1) gv += wsum_s[warp - 1];
-    gam_s[hsel][tok] = gv;
-    if (active && tok < rows) p.gam[(tok0 + tok) * p.HV + hv] = gv;
+    if (!kside) {
+      if (warp == 1) gv += wsum_s[0];
+      gam_s[tok] = gv;
+      if (tok < rows) p.gam[(tok0 + tok) * p.HV + hv] = gv;
+    }
     __syncthreads();
-    if (active) {
+    const float gam_i = gam_s[tok];
+    if (!kside) {
+      // P row as split bf16, written straight into the (swizzled) panel images
+      uint8_t* img = reinterpret_cast<uint8_t*>(p.p_img + cidx * 8192);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        float t[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int j = ch * 8 + jj;
+          const float e = __expf(fminf(gam_i - gam_s[j], 0.f));
+          t[jj] = sc[j] * ((j <= tok) ? e : 0.f);
+        }
+        uint4 hi, lo;
+        split8(t, hi, lo);
+        const uint32_t off = panel_chunk_off(tok, ch);
+        *reinterpret_cast<uint4*>(img + off) = hi;
+        *reinterpret_cast<uint4*>(img + 8192 + off) = lo;
+      }
+    } else {
       // A^T[j][i] = beta_i exp(gam_i - gam_j) (k_i . k_j) for j < i, written coalesced along i
-      float* at = p.at + ((int64_t(sq.cbase) + blockIdx.x) * p.HV + hv) * (kC * kC);
+      float* at = p.at + cidx * (kC * kC);
 #pragma unroll
       for (int j = 0; j < kC - 1; ++j)
-        if (j < tok) at[j * kC + tok] = bi * __expf(gv - gam_s[hsel][j]) * kk[j];
+        if (j < tok) at[j * kC + tok] = bi * __expf(gam_i - gam_s[j]) * sc[j];
     }
     __syncthreads();
   }
@@ -162,21 +188,19 @@ struct FwdPrefetch {
 #ifdef FLA_STAGE_CLOCKS
 __device__ long long g_stage_clocks[16];
 #define STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { long long now_ = clock64(); g_stage_clocks[i] += now_ - last_; last_ = now_; } } while (0)
-#define STAMPK(i) do { if (threadIdx.x == 63 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { long long now_ = clock64(); g_stage_clocks[i] += now_ - lastk_; lastk_ = now_; } } while (0)
 #else
 #define STAMP(i)
-#define STAMPK(i)
 #endif
 
 __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p) {
 #ifdef FLA_STAGE_CLOCKS
-  long long last_ = clock64(), lastk_ = clock64();
+  long long last_ = clock64();
 #endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar;
+  __shared__ __align__(8) uint64_t bar, pbar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -194,12 +218,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
   }
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&pbar, 1);
     mbar_init_fence();
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
-  uint32_t phase = 0;
+  uint32_t phase = 0, pphase = 0;
   bool dead = false;
   const uint32_t sb = smem_u32(smem);
 
@@ -231,10 +256,39 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
         pf.v[i] = make_uint4(0, 0, 0, 0);
         if (tok < rows) pf.v[i] = *reinterpret_cast<const uint4*>(p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + c0 + i * 8);
       }
+    }
+  };
+  // The per-token scalars travel separately and early: they are published to shared memory well before the
+  // barriers that precede their first use in the next iteration.
+  auto prefetch_scalars = [&](int c) {
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+    if (kside) {
       pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
     } else {
       // rows past the end of the sequence carry the last valid cumulative decay so every exponent stays finite
       pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
+    }
+  };
+  // Touch the next chunk's rows early so that the register loads issued late in the iteration hit L2.
+  auto prefetch_l2 = [&](int c) {
+    const int t0 = c * kC;
+    const int rows = min(kC, sq.len - t0);
+    const int64_t tok0 = int64_t(sq.bos) + t0;
+    if (tid < 128) {
+      const int r = tid & 63;
+      if (r < rows) {
+        const bf16* src = tid >= 64 ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 64));
+      }
+    } else if (tid < 192) {
+      const int r = tid - 128;
+      if (r < rows) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.X + ((tok0 + r) * p.HV + hv) * kC));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.v + (tok0 + r) * p.v_st + hv * p.v_sh + vb * kBV));
+      }
     }
   };
   uint4 vcur[4];
@@ -262,7 +316,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
 
   // operands (shared addresses)
   const Operand opQK{sb + kOffQK, kQKPanel, 0};                 // [q; k]  M = 128, reduction over K
-  const Operand opKb{sb + kOffQK + 8192, kQKPanel, 0};          // k as B (N = 64 tokens), reduction over K
   const Operand opKT{sb + kOffQK + 8192, kQKPanel, 1};          // k^T     M = 128 (K dims), reduction over tokens
   const Operand opSH{sb + kOffSH, 16384, 1}, opSL{sb + kOffSL, 16384, 1};
   const Operand opZH{sb + kOffZH, 8192, 1}, opZL{sb + kOffZL, 8192, 1};
@@ -274,6 +327,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
 
   // ---- prologue: chunk 0 operands and the initial state
   prefetch_load(0);
+  prefetch_scalars(0);
   store_scalars(0);
   store_panels();
   if (p.h0) {
@@ -313,33 +367,36 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     tc_fence_after();
 
     STAMP(0);
-    // ---- stage 1: [Q;K] S (split state) and [Q;K] K^T
+    // ---- stage 1: [Q;K] S  (split state: two passes)
     if (tid == 0) {
       if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format
         bf16* dst = p.s_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 8192);
-        bulk_store(dst, sb + kOffSH, 16384);
-        bulk_store(dst + 8192, sb + kOffSL, 16384);
+        bulk_store(dst, sb + kOffSH, 32768);
         bulk_commit();
       }
       mma_tile(tbase + kColRQ, opQK, opSH, 128, 64, 8, false);
       mma_tile(tbase + kColRQ, opQK, opSL, 128, 64, 8, true);
-      mma_tile(tbase + kColQK, opQK, opKb, 128, 64, 8, false);
       mma_commit(&bar);
     }
     if (c + 1 < sq.nt) {
-      prefetch_load(c + 1);
+      prefetch_l2(c + 1);
+      prefetch_scalars(c + 1);
       store_scalars(c + 1);
     }
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
-
+    if (tid == 0) {  // the q rows are consumed: the chunk's P panels (from the prep kernel) take their place
+      const bf16* src = p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192;
+      mbar_arrive_expect_tx(&pbar, 16384);
+      bulk_load(sb + kOffQK, src, 8192, &pbar);
+      bulk_load(sb + kOffQK + kQKPanel, src + 4096, 8192, &pbar);
+    }
     STAMP(1);
-    // ---- stage 2: k-side rows build Z = beta (V - exp(gam) K S); q-side rows build P = tril(QK^T * decay)
+
+    // ---- stage 2: k-side rows build Z = beta (V - exp(gam) K S)
     float acc[32];
-    STAMPK(10);
     if (kside) {
       tmem_ld_row32(trow + kColRQ, acc);
-      STAMPK(11);
       const float eg = __expf(gam_i), bi = beta_s[cur][tok];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -348,29 +405,12 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i * 8 + j] = bi * (vv[j] - eg * acc[i * 8 + j]);
       }
-      STAMPK(12);
       row32_to_hilo(smem + kOffZH, smem + kOffZL, tok, half, acc);
-      STAMPK(13);
-    } else {
-      tmem_ld_row32(trow + kColQK, acc);
-      STAMPK(11);
-#pragma unroll
-      for (int jj = 0; jj < 32; ++jj) {
-        const int j = c0 + jj;
-        // branch-free: the exponent is clamped so that masked entries cannot produce inf * 0
-        const float e = __expf(fminf(gam_i - gam_s[cur][j], 0.f));
-        acc[jj] *= (j <= tok) ? e : 0.f;
-      }
-      STAMPK(12);
-      row32_to_hilo(smem + kOffQK, smem + kOffQK + kQKPanel, tok, half, acc);
-      STAMPK(13);
     }
     fence_async_smem();
-    STAMPK(14);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    STAMPK(15);
 
     STAMP(2);
     // ---- stage 3: v_new = X Z  (rows 64..127 of the accumulator)
@@ -407,13 +447,16 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
         bulk_store(dst + 4096, sb + kOffZL, 8192);
         bulk_commit();
       }
+      mma_tile(tbase + kColS, opKT, opVH, 128, 64, 4, true);
+      mma_tile(tbase + kColS, opKT, opVL, 128, 64, 4, true);
+      if (!mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // P panels have landed
       mma_tile(tbase + kColQK, opPH, opZH, 128, 64, 4, false);
       mma_tile(tbase + kColQK, opPH, opZL, 128, 64, 4, true);
       mma_tile(tbase + kColQK, opPL, opZH, 128, 64, 4, true);
-      mma_tile(tbase + kColS, opKT, opVH, 128, 64, 4, true);
-      mma_tile(tbase + kColS, opKT, opVL, 128, 64, 4, true);
       mma_commit(&bar);
     }
+    pphase ^= 1;
+    if (c + 1 < sq.nt) prefetch_load(c + 1);   // the next chunk's rows (L2-resident by now) travel while the MMAs run
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
@@ -486,7 +529,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd_workspace_size(const fla_gdn_chunk
   int64_t chunks = a->q.shape[0] * ((a->q.shape[1] + kC - 1) / kC);
   if (a->cu_seqlens.data) chunks = a->total_chunks;
   if (chunks <= 0) return FLA_ERR_VALUE;
-  *bytes = 256 + uint64_t(chunks) * a->v.shape[2] * kC * kC * 4;  // status block + A^T scratch for the inverse
+  // status block + A^T scratch for the inverse + P panels (unless the caller keeps them for the backward)
+  *bytes = 256 + uint64_t(chunks) * a->v.shape[2] * (kC * kC * 4 + (a->p_img.data ? 0 : 8192 * 2));
   return FLA_OK;
 }
 
@@ -559,8 +603,18 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = a->beta.dtype == FLA_F32; p.o_is_f32 = o.dtype == FLA_F32;
   p.scale = a->scale;
   p.status = static_cast<int*>(workspace);
-  if (workspace_bytes < 256 + uint64_t(total_chunks) * HV * kC * kC * 4) return FLA_ERR_WORKSPACE;
-  p.at = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+  {
+    const uint64_t per = uint64_t(total_chunks) * HV;
+    if (workspace_bytes < 256 + per * (kC * kC * 4 + (a->p_img.data ? 0 : 8192 * 2))) return FLA_ERR_WORKSPACE;
+    p.at = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+    if (a->p_img.data) {
+      const fla_tensor_t& pi = a->p_img;
+      if (pi.dtype != FLA_BF16 || pi.ndim != 1 || pi.shape[0] != int64_t(per) * 8192 || !aligned16(pi.data)) return FLA_ERR_SHAPE;
+      p.p_img = static_cast<bf16*>(pi.data);
+    } else {
+      p.p_img = reinterpret_cast<bf16*>(static_cast<uint8_t*>(workspace) + 256 + per * kC * kC * 4);
+    }
+  }
 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;

@@ -1,6 +1,7 @@
 // Shared pieces of the chunked GDN kernels: parameter block, sequence/chunk geometry and small
 // row-wise helpers for moving fp32 accumulator rows between TMEM, registers and operand panels.
 #pragma once
+#include <cuda_fp16.h>
 #include "common/sm100.cuh"
 
 namespace fla {
@@ -100,6 +101,27 @@ __device__ __forceinline__ void row32_to_hilo(uint8_t* pan_hi, uint8_t* pan_lo, 
   }
 }
 
+
+// columns [32*half, 32*half + 32) of `row` as fp16 (11-bit significand: enough for the state copy in one pass)
+__device__ __forceinline__ void row32_to_f16(uint8_t* pan, int row, int half, const float* x) {
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint4 v;
+    __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(x[ch * 8 + 2 * i], x[ch * 8 + 2 * i + 1]);
+    *reinterpret_cast<uint4*>(pan + panel_chunk_off(row, half * 4 + ch)) = v;
+  }
+}
+__device__ __forceinline__ void unpack_f16x8(const uint4& raw, float* f) {
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
 
 // A wait that gives up records the timeout once; afterwards the thread stops waiting so that the kernel
 // still terminates quickly (its results are then invalid, which the status word tells the host).

@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(128) selftest_mma_kernel(SelftestParams p) {
   tc_fence_after();
   const uint32_t tbase = tmem_base_s;
 
-  if (p.prefill & 1) {  // D starts as lane*4 + col/64 pattern written with tcgen05.st, MMA accumulates on top
+  if (p.prefill) {  // D starts as lane*4 + col/64 pattern written with tcgen05.st, MMA accumulates on top
     for (int c0 = 0; c0 < p.N; c0 += 16) {
       float v[16];
 #pragma unroll
@@ -71,8 +71,8 @@ __global__ void __launch_bounds__(128) selftest_mma_kernel(SelftestParams p) {
 
   if (threadIdx.x == 0) {
     Operand A{smem_u32(sa), uint32_t(a_rows) * 128u, p.a_mn};
-    Operand B{smem_u32(sb), uint32_t(b_rows) * 128u, p.b_mn, (p.prefill >> 1) & 1};   // bit 1 of `prefill`: B holds fp16
-    mma_tile(tmem_addr(tbase, p.d_lane_off, 0), A, B, p.M, p.N, p.K / 16, (p.prefill & 1) != 0);
+    Operand B{smem_u32(sb), uint32_t(b_rows) * 128u, p.b_mn};
+    mma_tile(tmem_addr(tbase, p.d_lane_off, 0), A, B, p.M, p.N, p.K / 16, p.prefill != 0);
     mma_commit(&bar);
   }
   const bool ok = mbar_wait(&bar, 0, p.err, 1);

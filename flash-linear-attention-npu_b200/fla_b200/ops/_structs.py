@@ -24,14 +24,14 @@ class CausalConv1dUpdateArgs(ctypes.Structure):
 
 class GdnChunkFwdArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "g", "beta", "initial_state", "o", "final_state", "gam",
-                                           "x_inv", "s_img", "vn_img", "cu_seqlens",
+                                           "x_inv", "s_img", "vn_img", "p_img", "cu_seqlens",
                                            "chunk_offsets")] + [
         ("scale", ctypes.c_float), ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32),
         ("total_chunks", ctypes.c_int32)]
 
 
 class GdnChunkBwdArgs(ctypes.Structure):
-    _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "beta", "gam", "x_inv", "s_img", "vn_img", "d_o", "dht",
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "beta", "gam", "x_inv", "s_img", "vn_img", "p_img", "d_o", "dht",
                                            "dq", "dk", "dv", "dg", "dbeta", "dh0", "cu_seqlens", "chunk_offsets")] + [
         ("scale", ctypes.c_float), ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32),
         ("total_chunks", ctypes.c_int32)]

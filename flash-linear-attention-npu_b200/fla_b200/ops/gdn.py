@@ -77,19 +77,20 @@ def gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     ht = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if output_final_state else None
     gam = torch.empty((B, T, HV), dtype=torch.float32, device=dev)
     x_inv = torch.empty((B, T, HV, CHUNK), dtype=torch.bfloat16, device=dev)
-    s_img = vn_img = None
+    s_img = vn_img = p_img = None
     if save_for_backward:
         s_img = torch.empty(total_chunks * HV * 32768, dtype=torch.bfloat16, device=dev)
         vn_img = torch.empty(total_chunks * HV * 16384, dtype=torch.bfloat16, device=dev)
+        p_img = torch.empty(total_chunks * HV * 8192, dtype=torch.bfloat16, device=dev)
     a = GdnChunkFwdArgs()
     a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)
     a.initial_state, a.o, a.final_state = rt.desc(initial_state), rt.desc(o), rt.desc(ht)
     a.gam, a.x_inv = rt.desc(gam), rt.desc(x_inv)
-    a.s_img, a.vn_img = rt.desc(s_img), rt.desc(vn_img)
+    a.s_img, a.vn_img, a.p_img = rt.desc(s_img), rt.desc(vn_img), rt.desc(p_img)
     a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
     a.scale, a.chunk_size, a.max_seqlen, a.total_chunks = float(scale), CHUNK, int(max_len), int(total_chunks)
-    rt.call("gdn_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gam, x_inv, s_img, vn_img, cu, co])
-    saved = dict(gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img, cu=cu, co=co,
+    rt.call("gdn_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gam, x_inv, s_img, vn_img, p_img, cu, co])
+    saved = dict(gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img, p_img=p_img, cu=cu, co=co,
                  max_len=max_len, total_chunks=total_chunks, N=N)
     return o, ht, saved
 
@@ -122,13 +123,13 @@ def gdn_chunk_bwd(q, k, v, beta, saved, do, dht, scale, want_dh0, grad_dtype=Non
     dh0 = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if want_dh0 else None
     a = GdnChunkBwdArgs()
     a.q, a.k, a.v, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(beta)
-    a.gam, a.x_inv, a.s_img, a.vn_img = (rt.desc(saved[n]) for n in ("gam", "x_inv", "s_img", "vn_img"))
+    a.gam, a.x_inv, a.s_img, a.vn_img, a.p_img = (rt.desc(saved[n]) for n in ("gam", "x_inv", "s_img", "vn_img", "p_img"))
     a.d_o, a.dht = rt.desc(do), rt.desc(dht)
     a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = (rt.desc(x) for x in (dq, dk, dv, dg, dbeta, dh0))
     a.cu_seqlens, a.chunk_offsets = rt.desc(saved["cu"]), rt.desc(saved["co"])
     a.scale, a.chunk_size = float(scale), CHUNK
     a.max_seqlen, a.total_chunks = int(saved["max_len"]), int(saved["total_chunks"])
-    rt.call("gdn_chunk_bwd", a, [q, k, v, beta, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"], do, dht,
+    rt.call("gdn_chunk_bwd", a, [q, k, v, beta, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"], saved["p_img"], do, dht,
                                  dq, dk, dv, dg, dbeta, dh0, saved["cu"], saved["co"]])
     return dq, dk, dv, dg, dbeta, dh0
 
@@ -153,7 +154,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                                      output_dtype=output_dtype)
         if need_grad:
             extra = (q_rstd, k_rstd) if qk_l2norm else ()
-            ctx.save_for_backward(q_, k_, v_, b_, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"], *extra)
+            ctx.save_for_backward(q_, k_, v_, b_, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"],
+                                  saved["p_img"], *extra)
             ctx.meta = {kk: saved[kk] for kk in ("cu", "co", "max_len", "total_chunks", "N")}
             ctx.scale = scale
             ctx.has_h0 = initial_state is not None
@@ -162,13 +164,13 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, beta, gam, x_inv, s_img, vn_img = ctx.saved_tensors[:8]
-        saved = dict(ctx.meta, gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img)
+        q, k, v, beta, gam, x_inv, s_img, vn_img, p_img = ctx.saved_tensors[:9]
+        saved = dict(ctx.meta, gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img, p_img=p_img)
         dq, dk, dv, dg, dbeta, dh0 = gdn_chunk_bwd(q, k, v, beta, saved, do.contiguous(), dht, ctx.scale, ctx.has_h0,
                                                    grad_dtype=torch.float32 if (ctx.in_dtypes[3] == torch.float32 or ctx.qk_l2norm) else None)
         if ctx.qk_l2norm:
             from .l2norm import l2norm_bwd
-            q_rstd, k_rstd = ctx.saved_tensors[8:10]
+            q_rstd, k_rstd = ctx.saved_tensors[9:11]
             dq = l2norm_bwd(q, q_rstd, dq)
             dk = l2norm_bwd(k, k_rstd, dk)
         dts = ctx.in_dtypes

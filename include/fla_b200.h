@@ -156,16 +156,19 @@ FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* a
  *   x_inv [B, T, HV, 64] bf16 out: rows of (I + strict_tril(beta_i exp(gam_i-gam_j) k_i.k_j))^-1 per chunk
  *   s_img  [chunks * HV * 32768] bf16, optional out (for backward): per (chunk, head) the state at chunk start as
  *          2 (64-column blocks of V) x 2 (hi, lo = bf16 residual) swizzled 128x64 operand panels
- *   vn_img [chunks * HV * 16384] bf16, optional out (for backward): v_new, 2 x 2 (hi, lo) 64x64 panels
- *          (s_img and vn_img are opaque to the caller: they are produced here and consumed by fla_b200_gdn_chunk_bwd)
+ *   vn_img [chunks * HV * 16384] bf16, optional out (for backward): v_new, 2 x 2 (hi, lo = bf16 residual) 64x64 panels
+ *   p_img  [chunks * HV * 8192] bf16, optional out (for backward): tril(Q K^T * decay), 2 (hi, lo) 64x64 panels;
+ *          when absent the forward keeps these panels in its workspace
+ *          (s_img, vn_img, p_img are opaque to the caller: produced here, consumed by fla_b200_gdn_chunk_bwd)
  *   cu_seqlens int32 [N+1] device (requires B == 1) with chunk_offsets int32 [N+1] device (prefix sum of
  *   ceil(len/64)), max_seqlen and total_chunks given by the host.  All four are ignored for dense batches.
  * Token tensors need a contiguous last dim, 16-byte aligned rows and batch rows laid out back to back.
  * Workspace: a 256-byte status block (first int32 becomes FLA_ERR_TIMEOUT if a device-side wait ran out)
- * followed by a 16 KB fp32 scratch tile per (chunk, value head) for the triangular inverse. */
+ * followed by a 16 KB fp32 scratch tile per (chunk, value head) for the triangular inverse and, when p_img is
+ * absent, 16 KB per (chunk, value head) for the score panels. */
 typedef struct fla_gdn_chunk_fwd_args {
   fla_tensor_t q, k, v, g, beta, initial_state;
-  fla_tensor_t o, final_state, gam, x_inv, s_img, vn_img;
+  fla_tensor_t o, final_state, gam, x_inv, s_img, vn_img, p_img;
   fla_tensor_t cu_seqlens, chunk_offsets;
   float scale;
   int32_t chunk_size;
@@ -183,13 +186,13 @@ FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* args, void* wor
  * flash_chunk_gated_delta_rule_bwd (examples/flash_gated_delta_rule.py:884-1023; per-op bindings
  * torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:397-427, 324-394, 463-514, 430-460, 242-281).
  * Unlike the reference's composition it also consumes the final-state cotangent dht and produces dh0.
- *   q, k, v, beta, gam, x_inv, s_img, vn_img: the forward's inputs and saved outputs (same shapes as there)
+ *   q, k, v, beta, gam, x_inv, s_img, vn_img, p_img: the forward's inputs and saved outputs (same shapes as there)
  *   d_o [B, T, HV, 128] bf16;   dht [N, HV, 128, 128] f32, optional
  *   dq, dk [B, T, HK, 128], dv [B, T, HV, 128], dg, dbeta [B, T, HV]: all bf16 or all f32;  dh0 [N, HV, 128, 128] f32, optional
  *   dq / dk are summed over the value heads of each GVA group inside the kernel (deterministic).
  * Workspace (size from the _workspace_size call): status block + state-gradient images + [dO; dZ] images + row sums. */
 typedef struct fla_gdn_chunk_bwd_args {
-  fla_tensor_t q, k, v, beta, gam, x_inv, s_img, vn_img, d_o, dht;
+  fla_tensor_t q, k, v, beta, gam, x_inv, s_img, vn_img, p_img, d_o, dht;
   fla_tensor_t dq, dk, dv, dg, dbeta, dh0;
   fla_tensor_t cu_seqlens, chunk_offsets;
   float scale;

@@ -27,7 +27,7 @@ def _bwd_args(d, saved, scale, outs):
     from fla_b200.ops._structs import GdnChunkBwdArgs
     a = GdnChunkBwdArgs()
     a.q, a.k, a.v, a.beta = rt.desc(d["q"]), rt.desc(d["k"]), rt.desc(d["v"]), rt.desc(d["beta"])
-    a.gam, a.x_inv, a.s_img, a.vn_img = (rt.desc(saved[n]) for n in ("gam", "x_inv", "s_img", "vn_img"))
+    a.gam, a.x_inv, a.s_img, a.vn_img, a.p_img = (rt.desc(saved[n]) for n in ("gam", "x_inv", "s_img", "vn_img", "p_img"))
     a.d_o, a.dht = rt.desc(d["do"]), rt.desc(d["dht"])
     a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = (rt.desc(t) for t in outs)
     a.scale, a.chunk_size, a.max_seqlen, a.total_chunks = scale, 64, saved["max_len"], saved["total_chunks"]
