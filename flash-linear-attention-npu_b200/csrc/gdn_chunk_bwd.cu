@@ -36,7 +36,7 @@ struct GdnBwdParams {
   const bf16* s_img; const bf16* vn_img; const bf16* p_img;
   bf16* ds_img;        // [chunks, HV, 2, 2, 128x64]  state gradient entering each chunk (hi, lo)
   bf16* dz_img;        // [chunks, HV, 2, {128x64 hi: rows 0-63 dO, rows 64-127 dZ_hi ; 64x64 dZ_lo}]
-  float* bz;           // [2, tokens, HV] partial sums over a V block of dZ * V
+  float* bz;           // [4, tokens, HV] partial sums of dZ * V over the four 32-column slices of V
   const float* dht; float* dh0;
   void* dq; void* dk; void* dv; void* dg; void* dbeta;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
@@ -62,25 +62,27 @@ constexpr uint32_t kDhuSmem = 98304;
 constexpr uint32_t hColDS = 0, hColW1 = 64, hColQK = 128, hColU1 = 192;
 
 struct DhuPrefetch {
-  uint4 qk[16];
-  uint4 x[4];
-  uint4 row[8];   // q-side threads: dO row; k-side threads: v row
+  uint4 qk[8];
+  uint4 x[2];
+  uint4 row[4];   // q-side threads: my 32 columns of the dO row; k-side threads: of the v row
   float gb;
 };
+constexpr int kDhuThreads = 256;
 
-__global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
+__global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t bar, pbar;
 
-  const int tid = threadIdx.x, warp = tid / 32;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
   const int hk = hv / (p.HV / p.HK);
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
-  const bool kwarp = warp >= 2;
-  const int row = tid, tok = tid & 63;
+  const int quad = warp & 3, half = warp >> 2;   // TMEM lane quadrant; which 32 of the tile's 64 columns
+  const bool kside = quad >= 2;
+  const int row = quad * 32 + lane, tok = row & 63, c0 = half * 32;
 
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 256);
@@ -93,8 +95,9 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
   uint32_t phase = 0, pphase = 0;
+  bool dead = false;
   const uint32_t sb = smem_u32(smem);
   auto issue_p_load = [&](int c) {   // P = tril(Q K^T * decay) of chunk c, built by the forward's prep kernel
     const bf16* src = p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192;
@@ -108,8 +111,8 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int idx = tid + i * 128;
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * kDhuThreads;
       const int r = (idx / 16) & 63, ch = idx % 16;
       const bool isk = idx >= 1024;
       pf.qk[i] = make_uint4(0, 0, 0, 0);
@@ -119,19 +122,19 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
       }
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int idx = tid + i * 128, r = idx / 8, ch = idx % 8;
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * kDhuThreads, r = idx / 8, ch = idx % 8;
       pf.x[i] = make_uint4(0, 0, 0, 0);
       if (r < rows) pf.x[i] = *reinterpret_cast<const uint4*>(p.X + ((tok0 + r) * p.HV + hv) * kC + ch * 8);
     }
-    const bf16* rsrc = kwarp ? p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV
-                             : p.dO + (tok0 + tok) * p.do_st + hv * p.do_sh + vb * kBV;
+    const bf16* rsrc = kside ? p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + c0
+                             : p.dO + (tok0 + tok) * p.do_st + hv * p.do_sh + vb * kBV + c0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       pf.row[i] = make_uint4(0, 0, 0, 0);
       if (tok < rows) pf.row[i] = *reinterpret_cast<const uint4*>(rsrc + i * 8);
     }
-    if (kwarp) pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    if (kside) pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
     else pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
   };
   // Touch the next chunk's rows early so that the register loads issued late in the iteration hit L2.
@@ -140,36 +143,37 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
     const int r = tid & 63;
-    if (r < rows) {
+    if (tid < 128 && r < rows) {
       const bf16* src = tid >= 64 ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
       asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 64));
-      const bf16* s2 = tid >= 64 ? p.v + (tok0 + r) * p.v_st + hv * p.v_sh + vb * kBV : p.dO + (tok0 + r) * p.do_st + hv * p.do_sh + vb * kBV;
+    } else if (tid >= 128 && r < rows) {
+      const bf16* s2 = tid >= 192 ? p.v + (tok0 + r) * p.v_st + hv * p.v_sh + vb * kBV : p.dO + (tok0 + r) * p.do_st + hv * p.do_sh + vb * kBV;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(s2));
-      if (tid < 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.X + ((tok0 + r) * p.HV + hv) * kC));
+      if (tid < 192) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.X + ((tok0 + r) * p.HV + hv) * kC));
     }
   };
-  uint4 rcur[8];
+  uint4 rcur[4];
   auto prefetch_store = [&](int c) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int idx = tid + i * 128;
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * kDhuThreads;
       const int r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
       *reinterpret_cast<uint4*>(smem + hOffQK + (ch / 8) * hQKPanel + panel_chunk_off(r, ch % 8)) = pf.qk[i];
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int idx = tid + i * 128;
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * kDhuThreads;
       *reinterpret_cast<uint4*>(smem + hOffX + panel_chunk_off(idx / 8, idx % 8)) = pf.x[i];
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) rcur[i] = pf.row[i];
-    if (kwarp) {
-      beta_s[c & 1][tok] = pf.gb;
+    for (int i = 0; i < 4; ++i) rcur[i] = pf.row[i];
+    if (kside) {
+      if (half == 0) beta_s[c & 1][tok] = pf.gb;
     } else {
-      gam_s[c & 1][tok] = pf.gb;
+      if (half == 0) gam_s[c & 1][tok] = pf.gb;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(smem + hOffDO + panel_chunk_off(tok, i)) = pf.row[i];
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(smem + hOffDO + panel_chunk_off(tok, half * 4 + i)) = pf.row[i];
     }
   };
 
@@ -181,22 +185,21 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
   const Operand opXT{sb + hOffX - 8192, 8192, 1};              // X^T, valid rows 64..127
   const Operand opDVh{sb + hOffPH, 8192, 1}, opDVl{sb + hOffPL, 8192, 1};
 
-  bool ok = true;
-  float srow[kBV];
+  float srow[32];   // this thread's 32 columns of the fp32 state-gradient row
   const int c_last = sq.nt - 1;
   prefetch_load(c_last);
   prefetch_store(c_last);
   if (tid == 0) issue_p_load(c_last);
   if (p.dht) {
-    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
 #pragma unroll
-    for (int i = 0; i < kBV; i += 4) {
+    for (int i = 0; i < 32; i += 4) {
       const float4 t = *reinterpret_cast<const float4*>(src + i);
       srow[i] = t.x; srow[i + 1] = t.y; srow[i + 2] = t.z; srow[i + 3] = t.w;
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < kBV; ++i) srow[i] = 0.f;
+    for (int i = 0; i < 32; ++i) srow[i] = 0.f;
   }
   __syncthreads();
 
@@ -210,12 +213,12 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
 
     // ---- stage 0: publish dS' (split copy for the MMAs and for the second kernel), pre-decayed master in TMEM
-    row64_to_hilo(smem + hOffDSH, smem + hOffDSL, row, srow);
+    row32_to_hilo(smem + hOffDSH, smem + hOffDSL, row, half, srow);
     {
       const float dl = __expf(gam_last);
 #pragma unroll
-      for (int i = 0; i < kBV; ++i) srow[i] *= dl;
-      tmem_st_row64(trow + hColDS, srow);
+      for (int i = 0; i < 32; ++i) srow[i] *= dl;
+      tmem_st_row32(trow + hColDS, srow);
     }
     fence_async_smem();
     tc_fence_before();
@@ -225,35 +228,33 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     // ---- stage 1: [Q;K] dS'  and  U1 = P^T dO (valid accumulator rows 64..127)
     if (tid == 0) {
       bf16* dst = p.ds_img + (cidx * 2 + vb) * (2 * 8192);
-      bulk_store(dst, sb + hOffDSH, 16384);
-      bulk_store(dst + 8192, sb + hOffDSL, 16384);
+      bulk_store(dst, sb + hOffDSH, 32768);
       bulk_commit();
       mma_tile(tbase + hColW1, opQK, opDSH, 128, 64, 8, false);
       mma_tile(tbase + hColW1, opQK, opDSL, 128, 64, 8, true);
-      ok = mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT) && ok;   // P panels have landed
+      if (!mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // P panels have landed
       mma_tile(tbase + hColU1, opPTh, opDO, 128, 64, 4, false);
       mma_tile(tbase + hColU1, opPTl, opDO, 128, 64, 4, true);
       mma_commit(&bar);
     }
     pphase ^= 1;
     if (c > 0) prefetch_l2(c - 1);
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT) && ok;
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
+    wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
-    if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
 
     // ---- stage 4: k-side rows: dVn = scale U1 + e^{gam_L - gam} (K dS')
-    float acc[kBV];
-    if (kwarp) {
-      float w1[kBV];
-      tmem_ld_row64(trow + hColW1, w1);
-      tmem_ld_row64(trow + hColU1, acc);
+    float acc[32];
+    if (kside) {
+      float w1[32];
+      tmem_ld32(trow + hColW1, w1);
+      tmem_ld32(trow + hColU1, acc);
+      tmem_ld_wait();
       const float dk = __expf(gam_last - gam_i);
 #pragma unroll
-      for (int i = 0; i < kBV; ++i) acc[i] = p.scale * acc[i] + dk * w1[i];
-      row64_to_hilo(smem + hOffPH, smem + hOffPL, tok, acc);
+      for (int i = 0; i < 32; ++i) acc[i] = p.scale * acc[i] + dk * w1[i];
+      row32_to_hilo(smem + hOffPH, smem + hOffPL, tok, half, acc);
     }
+    if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -265,36 +266,34 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
       mma_tile(tbase + hColQK, opXT, opDVl, 128, 64, 4, true);
       mma_commit(&bar);
     }
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
+    wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
     // ---- stage 6: k-side rows: dV, sum_v dZ*V, dZ images, -beta e^gam dZ;  q-side rows: scale e^gam dO
-    if (kwarp) {
-      tmem_ld_row64(trow + hColQK, acc);
+    if (kside) {
+      tmem_ld_row32(trow + hColQK, acc);
       const float bi = beta_s[cur][tok];
       float bzsum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         float vv[8];
         unpack_bf16x8(rcur[i], vv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) bzsum += acc[i * 8 + j] * vv[j];
       }
-      row64_to_hilo(smem + hOffPH, smem + hOffPL, tok, acc);
+      row32_to_hilo(smem + hOffPH, smem + hOffPL, tok, half, acc);
       if (tok < rows) {
-        p.bz[(int64_t(vb) * p.total_tokens + tok0 + tok) * p.HV + hv] = bzsum;
-        const int64_t off = (tok0 + tok) * p.dv_st + hv * p.dv_sh + vb * kBV;
+        p.bz[(int64_t(vb * 2 + half) * p.total_tokens + tok0 + tok) * p.HV + hv] = bzsum;
+        const int64_t off = (tok0 + tok) * p.dv_st + hv * p.dv_sh + vb * kBV + c0;
         if (p.grads_f32) {
           float* dst = static_cast<float*>(p.dv) + off;
 #pragma unroll
-          for (int i = 0; i < kBV; i += 4)
+          for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<float4*>(dst + i) = make_float4(bi * acc[i], bi * acc[i + 1], bi * acc[i + 2], bi * acc[i + 3]);
         } else {
           bf16* dst = static_cast<bf16*>(p.dv) + off;
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
+          for (int ch = 0; ch < 4; ++ch) {
             float t[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) t[j] = bi * acc[ch * 8 + j];
@@ -304,18 +303,18 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
       }
       const float f = -bi * __expf(gam_i);
 #pragma unroll
-      for (int i = 0; i < kBV; ++i) acc[i] *= f;
-      row64_to_hilo(smem + hOffDSH, smem + hOffDSL, 64 + tok, acc);
+      for (int i = 0; i < 32; ++i) acc[i] *= f;
+      row32_to_hilo(smem + hOffDSH, smem + hOffDSL, 64 + tok, half, acc);
     } else {
       const float f = p.scale * __expf(gam_i);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         float vv[8];
         unpack_bf16x8(rcur[i], vv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i * 8 + j] = f * vv[j];
       }
-      row64_to_hilo(smem + hOffDSH, smem + hOffDSL, tok, acc);
+      row32_to_hilo(smem + hOffDSH, smem + hOffDSL, tok, half, acc);
     }
     fence_async_smem();
     tc_fence_before();
@@ -326,21 +325,18 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     if (tid == 0) {
       bf16* dst = p.dz_img + (cidx * 2 + vb) * 12288;
       bulk_store(dst, sb + hOffDO, 8192);            // rows 0..63 of the hi image: dO
-      bulk_store(dst + 4096, sb + hOffPH, 8192);     // rows 64..127: dZ hi
-      bulk_store(dst + 8192, sb + hOffPL, 8192);     // dZ lo
+      bulk_store(dst + 4096, sb + hOffPH, 16384);    // rows 64..127: dZ hi, then the dZ lo image
       bulk_commit();
       mma_tile(tbase + hColDS, opQKT, opDSH, 128, 64, 8, true);
       mma_tile(tbase + hColDS, opQKT, opDSL, 128, 64, 8, true);
       mma_commit(&bar);
     }
     if (c > 0) prefetch_load(c - 1);   // L2-resident by now; travels while the MMAs run
-    ok = mbar_wait(&bar, phase, p.status, FLA_ERR_TIMEOUT);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
+    wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
     // ---- stage 8: new dS to registers; next chunk's operands
-    tmem_ld_row64(trow + hColDS, srow);
+    tmem_ld_row32(trow + hColDS, srow);
     if (tid == 0) {
       bulk_wait_read();                  // the dZ images have left the P / dVn / dZ panels
       if (c > 0) issue_p_load(c - 1);    // ... which now receive the next chunk's P
@@ -353,10 +349,10 @@ __global__ void __launch_bounds__(128, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
     }
   }
 
-  if (ok && p.dh0) {
-    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV;
+  if (!dead && p.dh0) {
+    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
 #pragma unroll
-    for (int i = 0; i < kBV; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
   if (tid == 0) bulk_wait_all();
   tc_fence_before();
@@ -636,7 +632,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
       dgam_s[i] = (i < rows) ? dgam : 0.f;
       if (i < rows) {
         const int64_t gidx = (tok0 + i) * p.HV + hv;
-        const float bz = p.bz[gidx] + p.bz[p.total_tokens * p.HV + gidx];
+        const int64_t bzs = p.total_tokens * p.HV;
+        const float bz = (p.bz[gidx] + p.bz[bzs + gidx]) + (p.bz[2 * bzs + gidx] + p.bz[3 * bzs + gidx]);
         const float db = bz - egi * g_ + ma;
         if (p.grads_f32) static_cast<float*>(p.dbeta)[gidx] = db;
         else static_cast<bf16*>(p.dbeta)[gidx] = __float2bfloat16_rn(db);
@@ -685,7 +682,7 @@ static uint64_t bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t tokens, 
   uint64_t o = 256;  // status block
   *off_ds = o; o += align_up(uint64_t(total_chunks) * HV * kSImg * 2, 256);
   *off_dz = o; o += align_up(uint64_t(total_chunks) * HV * kDzImg * 2, 256);
-  *off_bz = o; o += align_up(uint64_t(2) * tokens * HV * 4, 256);
+  *off_bz = o; o += align_up(uint64_t(4) * tokens * HV * 4, 256);
   return o;
 }
 
@@ -818,7 +815,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   }
   {
     KernelTimer kt("gdn_bwd_dhu", cs);
-    gdn_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), 128, kDhuSmem + 1024, cs>>>(p);
+    gdn_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), kDhuThreads, kDhuSmem + 1024, cs>>>(p);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   const int nt_max = (max_len + kC - 1) / kC;
