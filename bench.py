@@ -239,6 +239,19 @@ class Workload:
             return "hbm", (2.0 * c["N"] * c["D"] * (c["W"] - 1) + 2.0 * c["N"] * c["D"]) * 2, "GB/s"
         raise KeyError(kname)
 
+    def kernel_traffic(self, kname):
+        """DRAM bytes (read + write) of one launch: the per-unit figure of one ncu capture of a small case of the
+        same kernel (profiles/), scaled by the units this launch processes; None where no capture exists."""
+        c = self.cfg
+        per_chunk_head = {"gdn_fwd": 313.04e6 / 2048, "gdn_bwd_dhu": 384.72e6 / 2048, "gdn_bwd_par": 505.20e6 / 2048}
+        if kname in per_chunk_head and "T" in c:
+            return per_chunk_head[kname] * c["B"] * ((c["T"] + 63) // 64) * c["HV"]
+        if kname == "recurrent_gdn":       # 212.33 MB for 64 sequences x 32 heads
+            return 212.33e6 / 64 * c["N"] * c["HV"] / 32
+        if kname == "causal_conv1d_fwd":   # 227.88 MB for 2 x 4096 x 8192 elements
+            return 227.88e6 / (2 * 4096 * 8192) * c["B"] * c["T"] * c["D"]
+        return None
+
     def step_flops(self):
         if self.name == "gdn_fwd_bwd":
             return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads
@@ -439,7 +452,7 @@ def main():
             achieved = work / sec / (1e12 if bound == "tensor" else 1e9)
             peak = peaks["bf16_tflops"] if bound == "tensor" else peaks["hbm_gbs"]
             roofline = {"kernel": KERNEL_SYMBOL[dom], "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                        "frac": achieved / peak, "traffic": None,
+                        "frac": achieved / peak, "traffic": wl.kernel_traffic(dom),
                         "peak_source": peaks["source"] + (" (burst)" if bound == "tensor" else ""),
                         "ms_per_launch": ktimes[dom]["ms_per_launch"]}
             for k in ktimes:
