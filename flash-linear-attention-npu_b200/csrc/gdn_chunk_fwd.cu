@@ -636,7 +636,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {
     KernelTimer kt("tri_inverse", cs);
-    TriInverseParams tp{p.at, p.X, nullptr, p.cu_seqlens, p.chunk_offsets, p.T, p.HV};
+    TriInverseParams tp{p.at, p.X, nullptr, nullptr, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, 0};
     if (launch_tri_inverse(tp, nt_max, N, cs)) return FLA_ERR_CUDA;
   }
   {

@@ -16,30 +16,9 @@
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
 #include "tri_inverse.h"
+#include "kda_common.cuh"
 
 namespace fla {
-
-struct KdaParams {
-  const bf16* q; const bf16* k; const bf16* v;
-  const void* g; const void* beta;
-  const float* a_log; const float* dt_bias;   // optional gate parameters: [HV], [HV, K]
-  float* gk_out;        // [tokens, HV, K] cumulative gate (optional)
-  bf16* qk_img;         // [chunks, HV, {hi, lo}, 2 panels x 128 rows]  rows 0-63 Qp, rows 64-127 Kp
-  bf16* kn_img;         // [chunks, HV, {hi, lo}, 2 panels x 64 rows]
-  bf16* p_img;          // [chunks, HV, {hi, lo}, 64 x 64]   tril(Qp Kn^T)
-  bf16* x_img;          // [chunks, HV, 64 x 64]             (I + Akk)^-1 (written by the inverse kernel)
-  float* at;            // [chunks, HV, 64, 64] scratch: Akk^T for the inverse kernel
-  float* vec;           // [chunks, HV, 2, K]  e^a, e^{gk_L - a}
-  const float* h0; float* ht;
-  void* o;
-  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
-  int64_t q_st, q_sh, k_st, k_sh, v_st, v_sh, o_st, o_sh, g_st, g_sh, beta_st;
-  int N, T, HK, HV, g_is_f32, beta_is_f32, o_is_f32, gate_mode;
-  float scale, lower_bound;
-  int* status;
-};
-
-constexpr int64_t kKdaQkImg = 32768, kKdaKnImg = 16384, kKdaPImg = 8192, kKdaXImg = 4096;
 
 // --------------------------------------------------------------------------------------------- prep
 constexpr uint32_t pOffQKH = 0, pOffQKL = 32768, pOffKNH = 65536, pOffKNL = 81920;
@@ -147,8 +126,9 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p) {
   __syncthreads();
   if (tid < kK) {
     const float a = anchor_s[tid];
-    p.vec[cidx * 2 * kK + tid] = __expf(a);
-    p.vec[cidx * 2 * kK + kK + tid] = __expf(last_s[tid] - a);
+    p.vec[cidx * kKdaVecs * kK + tid] = __expf(a);
+    p.vec[cidx * kKdaVecs * kK + kK + tid] = __expf(last_s[tid] - a);
+    p.vec[cidx * kKdaVecs * kK + 2 * kK + tid] = a;
   }
   // 3. scaled operands as split bf16 panels
   {
@@ -248,9 +228,9 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p) {
 
 // --------------------------------------------------------------------------------------------- forward
 constexpr uint32_t fOffQKH = 0, fOffQKL = 32768, fOffKNH = 65536, fOffKNL = 81920;
-constexpr uint32_t fOffPH = 98304, fOffPL = 106496, fOffX = 114688;
-constexpr uint32_t fOffSH = 122880, fOffSL = 139264, fOffZH = 155648, fOffZL = 163840;
-constexpr uint32_t kKdaFwdSmem = 172032;
+constexpr uint32_t fOffPH = 98304, fOffPL = 106496, fOffX = 114688, fOffXL = 122880;
+constexpr uint32_t fOffSH = 131072, fOffSL = 147456, fOffZH = 163840, fOffZL = 172032;
+constexpr uint32_t kKdaFwdSmem = 180224;
 constexpr uint32_t fColS = 0, fColRQ = 64, fColPV = 128, fColVN = 192;
 
 __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
@@ -292,10 +272,10 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
   };
   auto issue_load2 = [&](int c) {   // Kn hi + lo, P hi + lo, X
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
-    mbar_arrive_expect_tx(&load2_bar, 32768 + 16384 + 8192);
+    mbar_arrive_expect_tx(&load2_bar, 32768 + 16384 + 16384);
     bulk_load(sb + fOffKNH, p.kn_img + cidx * kKdaKnImg, 32768, &load2_bar);
     bulk_load(sb + fOffPH, p.p_img + cidx * kKdaPImg, 16384, &load2_bar);
-    bulk_load(sb + fOffX, p.x_img + cidx * kKdaXImg, 8192, &load2_bar);
+    bulk_load(sb + fOffX, p.x_img + cidx * kKdaXImg, 16384, &load2_bar);
   };
   if (tid == 0) {
     issue_load1(0);
@@ -307,6 +287,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
   const Operand opSH{sb + fOffSH, 16384, 1}, opSL{sb + fOffSL, 16384, 1};
   const Operand opZH{sb + fOffZH, 8192, 1}, opZL{sb + fOffZL, 8192, 1};
   const Operand opX{sb + fOffX - 8192, 16384, 0};               // rows 64..127 of this tile are X
+  const Operand opXL{sb + fOffXL - 8192, 16384, 0};             // ... and of this one its bf16 residual
   const Operand opPH{sb + fOffPH, 16384, 0}, opPL{sb + fOffPL, 16384, 0};       // rows 0..63 are P
 
   // per-chunk scalars / vectors / value rows are staged through registers one chunk ahead
@@ -317,7 +298,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
-    pf_vec = p.vec[cidx * 2 * kK + tid];                       // 256 threads: e^a then e^{gk_L - a}
+    pf_vec = p.vec[cidx * kKdaVecs * kK + tid];                       // 256 threads: e^a then e^{gk_L - a}
     if (kside) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -378,6 +359,11 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
     if (!dead && !mbar_wait(&load1_bar, l1phase, p.status, FLA_ERR_TIMEOUT)) dead = true;
     l1phase ^= 1;
     if (tid == 0) {
+      if (p.s_img) {
+        const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+        bulk_store(p.s_img + (cidx * 2 + vb) * 16384, sb + fOffSH, 32768);
+        bulk_commit();
+      }
       mma_tile(tbase + fColRQ, opQKH, opSH, 128, 64, 8, false);
       mma_tile(tbase + fColRQ, opQKH, opSL, 128, 64, 8, true);
       mma_tile(tbase + fColRQ, opQKL, opSH, 128, 64, 8, true);
@@ -418,6 +404,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
     if (tid == 0) {
       mma_tile(tbase + fColVN, opX, opZH, 128, 64, 4, false);
       mma_tile(tbase + fColVN, opX, opZL, 128, 64, 4, true);
+      mma_tile(tbase + fColVN, opXL, opZH, 128, 64, 4, true);
       mma_commit(&mma_bar);
     }
     if (!dead && !mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT)) dead = true;
@@ -437,6 +424,11 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
 
     // ---- stage 5: Aqk v_new and the state update Sa += Kn^T v_new
     if (tid == 0) {
+      if (p.vn_img) {
+        const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+        bulk_store(p.vn_img + (cidx * 2 + vb) * 8192, sb + fOffZH, 16384);
+        bulk_commit();
+      }
       mma_tile(tbase + fColPV, opPH, opZH, 128, 64, 4, false);
       mma_tile(tbase + fColPV, opPH, opZL, 128, 64, 4, true);
       mma_tile(tbase + fColPV, opPL, opZH, 128, 64, 4, true);
@@ -449,6 +441,10 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
     mphase ^= 1;
     tc_fence_after();
     if (tid == 0 && c + 1 < sq.nt) issue_load2(c + 1);
+    if (p.s_img || p.vn_img) {   // the saved images must have left the S / v_new panels before they are rewritten
+      if (tid == 0) bulk_wait_read();
+      __syncthreads();
+    }
 
     // ---- stage 6: output rows; next state S = diag(e^{gk_L - a}) (Sa + Kn^T v_new)
     if (!kside) {
@@ -458,7 +454,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 32; ++i) acc[i] = p.scale * (qs[i] + acc[i]);
-      if (tok < rows) {
+      if (tok < rows && p.o) {
         const int64_t off = (tok0 + tok) * p.o_st + hv * p.o_sh + vb * kBV + c0;
         if (p.o_is_f32) {
           float* dst = static_cast<float*>(p.o) + off;
@@ -486,6 +482,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
 #pragma unroll
     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
+  if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 256);
@@ -495,14 +492,14 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
 
 using namespace fla;
 
-static uint64_t kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[6]) {
+uint64_t fla::kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[6]) {
   uint64_t o = 256;
   const uint64_t per = uint64_t(total_chunks) * HV;
   off[0] = o; o += align_up(per * kKdaQkImg * 2, 256);
   off[1] = o; o += align_up(per * kKdaKnImg * 2, 256);
   off[2] = o; o += align_up(per * kKdaPImg * 2, 256);
   off[3] = o; o += align_up(per * kKdaXImg * 2, 256);
-  off[4] = o; o += align_up(per * 2 * kK * 4, 256);
+  off[4] = o; o += align_up(per * kKdaVecs * kK * 4, 256);
   off[5] = o; o += align_up(per * kC * kC * 4, 256);
   return o;
 }
@@ -614,6 +611,10 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
+  return kda_launch_forward(p, (max_len + kC - 1) / kC, cs);
+}
+
+int fla::kda_launch_forward(const KdaParams& p, int nt_max, cudaStream_t cs) {
   static bool attr_done_dev[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
@@ -622,20 +623,19 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
     if (cudaFuncSetAttribute(kda_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
-  const int nt_max = (max_len + kC - 1) / kC;
   {
     KernelTimer kt("kda_prep", cs);
-    kda_prep_kernel<<<dim3(nt_max, unsigned(HV), N), 256, kKdaPrepSmem + 1024, cs>>>(p);
+    kda_prep_kernel<<<dim3(nt_max, unsigned(p.HV), p.N), 256, kKdaPrepSmem + 1024, cs>>>(p);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {
     KernelTimer kt("tri_inverse", cs);
-    TriInverseParams tp{p.at, nullptr, p.x_img, p.cu_seqlens, p.chunk_offsets, p.T, p.HV};
-    if (launch_tri_inverse(tp, nt_max, N, cs)) return FLA_ERR_CUDA;
+    TriInverseParams tp{p.at, nullptr, p.x_img, p.x_img + kC * kC, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, int(kKdaXImg)};
+    if (launch_tri_inverse(tp, nt_max, p.N, cs)) return FLA_ERR_CUDA;
   }
   {
     KernelTimer kt("kda_fwd", cs);
-    kda_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), 256, kKdaFwdSmem + 1024, cs>>>(p);
+    kda_fwd_kernel<<<dim3(kV / kBV, unsigned(p.HV), p.N), 256, kKdaFwdSmem + 1024, cs>>>(p);
   }
   return cuda_status(cudaGetLastError());
 }

@@ -59,9 +59,16 @@ __global__ void __launch_bounds__(256) tri_inverse_kernel(TriInverseParams p) {
       if (i < rows) xg[int64_t(i) * p.HV * kC] = __float2bfloat16_rn(x[i]);
   }
   if (p.x_img) {             // swizzled 64x64 operand panel per (chunk, head); rows past the sequence end are zero
-    uint8_t* img = reinterpret_cast<uint8_t*>(p.x_img + cidx * (kC * kC));
+    const int64_t stride = p.img_stride ? p.img_stride : kC * kC;
+    uint8_t* img = reinterpret_cast<uint8_t*>(p.x_img + cidx * stride);
+    uint8_t* img_lo = p.x_img_lo ? reinterpret_cast<uint8_t*>(p.x_img_lo + cidx * stride) : nullptr;
 #pragma unroll
-    for (int i = 0; i < kC; ++i) *reinterpret_cast<bf16*>(img + panel_off(i, c)) = __float2bfloat16_rn(i < rows ? x[i] : 0.f);
+    for (int i = 0; i < kC; ++i) {
+      const float xv = i < rows ? x[i] : 0.f;
+      const bf16 hi = __float2bfloat16_rn(xv);
+      *reinterpret_cast<bf16*>(img + panel_off(i, c)) = hi;
+      if (img_lo) *reinterpret_cast<bf16*>(img_lo + panel_off(i, c)) = __float2bfloat16_rn(xv - __bfloat162float(hi));
+    }
   }
 }
 

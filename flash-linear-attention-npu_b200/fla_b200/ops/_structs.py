@@ -44,5 +44,12 @@ class KdaChunkFwdArgs(ctypes.Structure):
         ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32), ("total_chunks", ctypes.c_int32)]
 
 
+class KdaChunkBwdArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "g", "beta", "initial_state", "d_o", "dht", "dq", "dk", "dv",
+                                           "dg", "dbeta", "dh0", "cu_seqlens", "chunk_offsets")] + [
+        ("scale", ctypes.c_float), ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32),
+        ("total_chunks", ctypes.c_int32)]
+
+
 class L2NormArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("x", "y", "rstd", "dy", "dx")] + [("eps", ctypes.c_float)]

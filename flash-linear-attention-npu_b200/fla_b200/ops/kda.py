@@ -4,17 +4,99 @@
 torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1066-1265, BSND layout): q,k `[B,T,HK,K]`,
 v `[B,T,HV,V]`, per-channel gate g `[B,T,HV,K]`, beta `[B,T,HV]`, optional in-kernel gate activation
 (`use_gate_in_kernel` with `A_log`, `dt_bias`, `safe_gate` / `lower_bound`), `initial_state` / final state
-`[N,HV,K,V]` fp32.  Forward only: the reference itself ships no KDA backward (it defers to a third-party
-package), and this build has none yet, so tensors that require grad are refused instead of silently
-producing a graph-less result.
+`[N,HV,K,V]` fp32.  The operator is differentiable in q, k, v, g, beta and initial_state: the reference ships
+only the intra-chunk piece of the KDA backward (npu_chunk_kda_bwd_intra, `_aclnn_ctypes.py:1534-1783`) and defers the
+rest to a third-party package; here `fla_b200_kda_chunk_bwd` returns the complete gradient of the recurrence in one
+call, recomputing the forward from the inputs.  With `use_gate_in_kernel` and gradients enabled the gate activation
+runs in PyTorch (so autograd differentiates it) and the kernels receive the activated log decay.
 """
 from __future__ import annotations
 
 import torch
 
 from .. import _runtime as rt
-from ._structs import KdaChunkFwdArgs
+from ._structs import KdaChunkBwdArgs, KdaChunkFwdArgs
 from .gdn import CHUNK, _as_rows, _varlen_meta
+
+
+def _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias, lower_bound,
+                 meta, return_gate_cumsum, output_dtype):
+    B, T, HK, K = q.shape
+    HV, V = v.shape[2], v.shape[3]
+    cu, co, N, max_len, total_chunks = meta
+    dev = q.device
+    o = torch.empty((B, T, HV, V), dtype=output_dtype or q.dtype, device=dev)
+    ht = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if output_final_state else None
+    gk = torch.empty((B, T, HV, K), dtype=torch.float32, device=dev) if return_gate_cumsum else None
+    a = KdaChunkFwdArgs()
+    a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)
+    a.a_log, a.dt_bias = rt.desc(A_log if gate_mode else None), rt.desc(dt_bias if gate_mode else None)
+    a.initial_state, a.o, a.final_state, a.gk = rt.desc(initial_state), rt.desc(o), rt.desc(ht), rt.desc(gk)
+    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    a.scale, a.lower_bound, a.gate_mode = scale, float(lower_bound or 0.0), gate_mode
+    a.chunk_size, a.max_seqlen, a.total_chunks = CHUNK, int(max_len), int(total_chunks)
+    rt.call("kda_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gk, cu, co])
+    return o, ht, gk
+
+
+def kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dtype=None):
+    """Complete KDA chunk backward (g = per-channel log decay).  Returns dq, dk, dv, dg, dbeta, dh0."""
+    B, T, HK, K = q.shape
+    HV, V = v.shape[2], v.shape[3]
+    cu, co, N, max_len, total_chunks = meta
+    dev = q.device
+    gdt = grad_dtype or torch.float32
+    dq = torch.empty((B, T, HK, K), dtype=gdt, device=dev)
+    dk = torch.empty_like(dq)
+    dv = torch.empty((B, T, HV, V), dtype=gdt, device=dev)
+    dg = torch.empty((B, T, HV, K), dtype=gdt, device=dev)
+    dbeta = torch.empty((B, T, HV), dtype=gdt, device=dev)
+    dh0 = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if initial_state is not None else None
+    do = _as_rows(do if do.dtype == torch.bfloat16 else do.to(torch.bfloat16))
+    if dht is not None:
+        dht = dht.float().contiguous()
+    a = KdaChunkBwdArgs()
+    a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)
+    a.initial_state, a.d_o, a.dht = rt.desc(initial_state), rt.desc(do), rt.desc(dht)
+    a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = (rt.desc(x) for x in (dq, dk, dv, dg, dbeta, dh0))
+    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    a.scale = scale
+    a.chunk_size, a.max_seqlen, a.total_chunks = CHUNK, int(max_len), int(total_chunks)
+    rt.call("kda_chunk_bwd", a, [q, k, v, g, beta, initial_state, do, dht, dq, dk, dv, dg, dbeta, dh0, cu, co])
+    return dq, dk, dv, dg, dbeta, dh0
+
+
+class ChunkKdaFunction(torch.autograd.Function):
+    """Autograd glue of `chunk_kda` (gate already activated): saves only the inputs, the backward recomputes."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype):
+        o, ht, _ = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, 0, None, None, None, meta,
+                                False, output_dtype)
+        ctx.save_for_backward(q, k, v, g, beta, initial_state)
+        ctx.scale, ctx.meta = scale, meta
+        ctx.in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        q, k, v, g, beta, h0 = ctx.saved_tensors
+        dq, dk, dv, dg, dbeta, dh0 = kda_chunk_bwd(q, k, v, g, beta, ctx.scale, h0, do.contiguous(), dht, ctx.meta)
+        dts = ctx.in_dtypes
+        return (dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]), dg.to(dts[3]), dbeta.to(dts[4]), dh0,
+                None, None, None, None)
+
+
+def _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound):
+    """The in-kernel gate activations in PyTorch (kda/chunk_kda_fwd/docs/api.md:103-115), for the differentiable path."""
+    HV, K = g.shape[2], g.shape[3]
+    raw = g.float()
+    if dt_bias is not None:
+        raw = raw + dt_bias.float().reshape(HV, K)
+    eig = A_log.float().exp().reshape(1, 1, HV, 1)
+    if safe_gate:
+        return float(lower_bound) * torch.sigmoid(eig * raw)
+    return -eig * torch.nn.functional.softplus(raw)
 
 
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
@@ -26,8 +108,6 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     op = "chunk_kda"
     if use_qk_l2norm_in_kernel or use_beta_sigmoid_in_kernel:
         raise NotImplementedError(f"{op}: in-kernel q/k L2 norm and beta sigmoid are not available yet")
-    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state)):
-        raise NotImplementedError(f"{op}: backward is not implemented; call under torch.no_grad() or detach the inputs")
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != torch.bfloat16:
             raise TypeError(f"{op}: {name} must be bfloat16, got {t.dtype}")
@@ -42,15 +122,20 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     if tuple(g.shape) != (B, T, HV, K) or tuple(beta.shape) != (B, T, HV):
         raise RuntimeError(f"{op}: g must be {(B, T, HV, K)} and beta {(B, T, HV)}")
     scale = K ** -0.5 if scale is None else float(scale)
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state, A_log, dt_bias))
     gate_mode = 0
     if use_gate_in_kernel:
         if A_log is None:
             raise RuntimeError(f"{op}: use_gate_in_kernel needs A_log")
-        gate_mode = 2 if safe_gate else 1
         if safe_gate and lower_bound is None:
             raise RuntimeError(f"{op}: safe_gate needs lower_bound")
-        A_log = A_log.float().contiguous()
-        dt_bias = None if dt_bias is None else dt_bias.float().reshape(HV, K).contiguous()
+        if needs_grad:
+            g = _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound)
+        else:
+            gate_mode = 2 if safe_gate else 1
+            A_log = A_log.float().contiguous()
+            dt_bias = None if dt_bias is None else dt_bias.float().reshape(HV, K).contiguous()
     q, k, v, g, beta = (_as_rows(x) for x in (q, k, v, g, beta))
     dev = q.device
     cu = co = None
@@ -65,17 +150,14 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         if tuple(initial_state.shape) != (N, HV, K, V):
             raise RuntimeError(f"{op}: initial_state must be {(N, HV, K, V)}, got {tuple(initial_state.shape)}")
         initial_state = initial_state.float().contiguous()
-    o = torch.empty((B, T, HV, V), dtype=output_dtype or q.dtype, device=dev)
-    ht = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if output_final_state else None
-    gk = torch.empty((B, T, HV, K), dtype=torch.float32, device=dev) if return_gate_cumsum else None
-    a = KdaChunkFwdArgs()
-    a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)
-    a.a_log, a.dt_bias = rt.desc(A_log if gate_mode else None), rt.desc(dt_bias if gate_mode else None)
-    a.initial_state, a.o, a.final_state, a.gk = rt.desc(initial_state), rt.desc(o), rt.desc(ht), rt.desc(gk)
-    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
-    a.scale, a.lower_bound, a.gate_mode = scale, float(lower_bound or 0.0), gate_mode
-    a.chunk_size, a.max_seqlen, a.total_chunks = CHUNK, int(max_len), int(total_chunks)
-    rt.call("kda_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gk, cu, co])
+    meta = (cu, co, N, max_len, total_chunks)
+    if needs_grad:
+        if return_gate_cumsum:
+            raise NotImplementedError(f"{op}: return_gate_cumsum is not available on the differentiable path")
+        o, ht = ChunkKdaFunction.apply(q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype)
+        return o, ht
+    o, ht, gk = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias,
+                             lower_bound, meta, return_gate_cumsum, output_dtype)
     if return_gate_cumsum:
         return o, ht, gk
     return o, ht

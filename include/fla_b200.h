@@ -251,6 +251,31 @@ FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* args, void* wor
                                    void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Chunked Kimi Delta Attention, backward (gate_mode 0: g is the per-channel log decay).
+ * The reference has only the intra-chunk piece (aclnnChunkKdaBwdIntra as bound by npu_chunk_kda_bwd_intra,
+ * torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1534-1783) and defers the inter-chunk backward to a
+ * third-party package; this entry computes the complete gradient of fla_b200_kda_chunk_fwd in one call.
+ * It recomputes the forward internally (nothing has to be saved except the inputs).
+ *   q, k, v, g, beta, initial_state, cu_seqlens ...: the forward's inputs;  d_o [B, T, HV, 128] bf16;
+ *   dht [N, HV, 128, 128] f32 optional (gradient of the final state);
+ *   dq, dk [B, T, HK, 128] (summed over the value heads of a group), dv [B, T, HV, 128], dg [B, T, HV, 128],
+ *   dbeta [B, T, HV]: all bf16 or all f32;  dh0 [N, HV, 128, 128] f32 optional.
+ * Workspace: the forward's workspace plus about 250 KB per (chunk, value head). */
+typedef struct fla_kda_chunk_bwd_args {
+  fla_tensor_t q, k, v, g, beta, initial_state;
+  fla_tensor_t d_o, dht;
+  fla_tensor_t dq, dk, dv, dg, dbeta, dh0;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  float scale;
+  int32_t chunk_size;
+  int32_t max_seqlen;
+  int32_t total_chunks;
+} fla_kda_chunk_bwd_args;
+FLA_API int fla_b200_kda_chunk_bwd_workspace_size(const fla_kda_chunk_bwd_args* args, uint64_t* bytes);
+FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* args, void* workspace, uint64_t workspace_bytes,
+                                   void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Row-wise L2 normalisation (the q/k normalisation behind use_qk_l2norm_in_kernel).
  * Replaces the reference's Triton l2norm_fwd / l2norm_bwd (fla/ops/triton/triton_core/l2norm.py:131-234).
  *   fwd: x [rows, D] -> y [rows, D] = x * rstd, rstd [rows] f32 = rsqrt(sum x^2 + eps)

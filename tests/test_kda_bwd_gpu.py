@@ -1,0 +1,139 @@
+"""Parity of the chunked KDA backward with fp64 autograd through the naive per-channel-gate recurrence
+(oracle/kda.py).  The reference has no complete KDA backward of its own, so autograd through its recurrence
+(tests/atk/recurrent_kda/executor_recurrent_kda.py:63-83) is the pin."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from _util import assert_close
+
+pytestmark = pytest.mark.gpu
+TOL = 5e-3
+GRADS = ("dq", "dk", "dv", "dg", "dbeta")
+
+
+def _reference(inp, cu, dht):
+    if cu is None:
+        return oracle.kda_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"],
+                                            do=inp["do"], dht=dht, dtype=torch.float64)
+    parts = []
+    for i in range(len(cu) - 1):
+        sl = slice(cu[i], cu[i + 1])
+        parts.append(oracle.kda_reference_fwd_bwd(
+            inp["q"][:, sl], inp["k"][:, sl], inp["v"][:, sl], inp["g"][:, sl], inp["beta"][:, sl],
+            initial_state=None if inp["h0"] is None else inp["h0"][i:i + 1], do=inp["do"][:, sl],
+            dht=None if dht is None else dht[i:i + 1], dtype=torch.float64))
+    ref = {n: torch.cat([p[n] for p in parts], 1) for n in ("o",) + GRADS}
+    ref["ht"] = torch.cat([p["ht"] for p in parts], 0)
+    ref["dh0"] = None if inp["h0"] is None else torch.cat([p["dh0"] for p in parts], 0)
+    return ref
+
+
+def _run(B, T, HK, HV, seed, h0=True, with_dht=True, cu=None, gate_scale=1.0):
+    from fla_b200.ops import chunk_kda
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=seed)
+    inp["g"] = (inp["g"].float() * gate_scale).bfloat16()
+    N = B if cu is None else len(cu) - 1
+    gen = torch.Generator().manual_seed(seed + 1)
+    if h0:
+        inp["h0"] = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float()
+    dht = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float() if with_dht else None
+    ref = _reference(inp, cu, dht)
+    leaves = {n: inp[n].cuda().requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
+    h0_d = inp["h0"].cuda().requires_grad_(True) if h0 else None
+    o, ht = chunk_kda(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], initial_state=h0_d,
+                      output_final_state=True, output_dtype=torch.float32,
+                      cu_seqlens=None if cu is None else torch.tensor(cu, dtype=torch.int32))
+    loss = (o * inp["do"].cuda().float()).sum()
+    if with_dht:
+        loss = loss + (ht * dht.cuda()).sum()
+    loss.backward()
+    torch.cuda.synchronize()
+    got = {"o": o, "ht": ht, "dq": leaves["q"].grad, "dk": leaves["k"].grad, "dv": leaves["v"].grad,
+           "dg": leaves["g"].grad, "dbeta": leaves["beta"].grad, "dh0": None if h0_d is None else h0_d.grad}
+    return got, ref
+
+
+def _check(got, ref, stored_bf16=True):
+    assert_close("o", got["o"], ref["o"], TOL)
+    assert_close("ht", got["ht"], ref["ht"], TOL)
+    for n in GRADS:   # gradients come back in the dtype of their bf16 leaves
+        assert_close(n, got[n], ref[n], TOL, stored_bf16=stored_bf16)
+    if ref.get("dh0") is not None:
+        assert_close("dh0", got["dh0"], ref["dh0"], TOL)
+
+
+@pytest.mark.parametrize("B,T,HK,HV", [(1, 64, 1, 1), (1, 128, 1, 1), (2, 256, 2, 2), (1, 512, 1, 2)])
+def test_kda_backward_matches_autograd(B, T, HK, HV):
+    got, ref = _run(B, T, HK, HV, seed=4000 + T)
+    _check(got, ref)
+
+
+def test_kda_backward_fp32_gradients_through_the_c_abi():
+    # the low-level entry with fp32 gradient buffers is held to the plain bar (no bf16 store allowance)
+    from fla_b200.ops.kda import kda_chunk_bwd
+    B, T, HK, HV = 1, 256, 2, 2
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=4100)
+    gen = torch.Generator().manual_seed(4101)
+    inp["h0"] = (0.1 * torch.randn(B, HV, 128, 128, generator=gen)).float()
+    dht = (0.1 * torch.randn(B, HV, 128, 128, generator=gen)).float()
+    ref = _reference(inp, None, dht)
+    d = {n: t.cuda() for n, t in inp.items()}
+    meta = (None, None, B, T, B * (T // 64))
+    dq, dk, dv, dg, dbeta, dh0 = kda_chunk_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], 128 ** -0.5, d["h0"], d["do"],
+                                               dht.cuda(), meta, grad_dtype=torch.float32)
+    torch.cuda.synchronize()
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv), ("dg", dg), ("dbeta", dbeta), ("dh0", dh0)):
+        assert_close(n, t, ref[n], TOL)
+
+
+@pytest.mark.parametrize("T", [1, 31, 65, 100])
+def test_kda_backward_ragged_lengths(T):
+    got, ref = _run(1, T, 1, 1, seed=60 + T)
+    _check(got, ref)
+
+
+def test_kda_backward_without_states():
+    got, ref = _run(1, 192, 1, 1, seed=71, h0=False, with_dht=False)
+    _check(got, ref)
+
+
+def test_kda_backward_strong_gates():
+    got, ref = _run(1, 256, 1, 2, seed=19, gate_scale=16.0)
+    _check(got, ref)
+
+
+def test_kda_backward_varlen_packed():
+    cu = [0, 70, 71, 199, 263, 300]
+    got, ref = _run(1, 300, 2, 2, seed=13, cu=cu)
+    _check(got, ref)
+
+
+def test_kda_backward_through_the_gate_activation():
+    from fla_b200.ops import chunk_kda
+    B, T, HK, HV = 1, 128, 1, 2
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=78)
+    gen = torch.Generator().manual_seed(6)
+    raw = torch.randn(B, T, HV, 128, generator=gen).bfloat16()
+    A_log = torch.randn(HV, generator=gen) * 0.3 - 2.0
+    dt_bias = torch.randn(HV, 128, generator=gen) * 0.1
+    # oracle: activation + recurrence in fp64 autograd
+    raw64 = raw.double().requires_grad_(True)
+    A64, b64 = A_log.double().requires_grad_(True), dt_bias.double().requires_grad_(True)
+    gate = -torch.exp(A64)[None, None, :, None] * F.softplus(raw64 + b64[None, None])
+    q64, k64 = inp["q"].double().repeat_interleave(HV // HK, 2), inp["k"].double().repeat_interleave(HV // HK, 2)
+    o_ref, _ = oracle.naive_recurrent_kda(q64, k64, inp["v"].double(), gate, inp["beta"].double(), scale=128 ** -0.5,
+                                          dtype=torch.float64)
+    (o_ref * inp["do"].double()).sum().backward()
+    d = {n: t.cuda() for n, t in inp.items() if t is not None}
+    raw_d = raw.cuda().requires_grad_(True)
+    A_d, b_d = A_log.cuda().requires_grad_(True), dt_bias.cuda().requires_grad_(True)
+    o, _ = chunk_kda(d["q"], d["k"], d["v"], raw_d, d["beta"], use_gate_in_kernel=True, A_log=A_d, dt_bias=b_d,
+                     output_dtype=torch.float32)
+    (o * d["do"].float()).sum().backward()
+    torch.cuda.synchronize()
+    assert_close("o", o, o_ref, TOL)
+    assert_close("d_raw_gate", raw_d.grad, raw64.grad, TOL, stored_bf16=True)
+    assert_close("dA_log", A_d.grad, A64.grad, TOL)
+    assert_close("d_dt_bias", b_d.grad, b64.grad, TOL)

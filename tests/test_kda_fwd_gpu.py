@@ -94,12 +94,3 @@ def test_kda_gate_in_kernel_and_cumsum_output():
         o2, _ = chunk_kda(d["q"], d["k"], d["v"], raw.cuda(), d["beta"], use_gate_in_kernel=True, safe_gate=True,
                           lower_bound=lb, A_log=A_log.cuda(), dt_bias=dt_bias.cuda(), output_dtype=torch.float32)
     assert_close("o_safe_gate", o2, ref2["o"], TOL)
-
-
-def test_kda_refuses_autograd_inputs():
-    from fla_b200.ops import chunk_kda
-    q = torch.zeros(1, 64, 1, 128, dtype=torch.bfloat16, device="cuda", requires_grad=True)
-    g = torch.zeros(1, 64, 1, 128, dtype=torch.bfloat16, device="cuda")
-    b = torch.zeros(1, 64, 1, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(NotImplementedError):
-        chunk_kda(q, q, q, g, b)
