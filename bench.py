@@ -8,6 +8,7 @@ distributions of BASELINE.json.  Workloads (the default is the one the headline 
   gdn_fwd_bwd    config 2: chunked GDN forward + backward, B=8 T=4096 HQK=16 HV=32 K=V=128, nonzero fp32 h0, dO, dht
   gdn_fwd_conv   config 1: causal_conv1d (W=4, SiLU) over x[8,4096,8192] bf16, then the chunked GDN forward
   kda_fwd        config 3 (forward half): chunked KDA, B=4 T=8192 H=32 K=V=128, g = logsigmoid/16 per channel
+  kda_fwd_bwd    config 3: chunked KDA forward + backward (the backward recomputes the forward), dO ~ N(0,1)
   decode         config 4: causal_conv1d_update + fused-recurrent GDN, 256 sequences x 1 token, fp32 state pool,
                  one CUDA graph replay per step
   conv_prefill   the conv half of config 1 alone
@@ -38,7 +39,7 @@ sys.path.insert(0, str(REPO / "flash-linear-attention-npu_b200"))
 sys.path.insert(0, str(REPO))
 
 DEFAULT_WORKLOAD = "gdn_fwd_bwd"
-WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "decode", "conv_prefill"]
+WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "decode", "conv_prefill"]
 FWD_FLOP_PER_TOKEN_HEAD = 182955.0      # KK^T, inverse, w/u, state, output (dense 64x64 tiles, no causal credit)
 BWD_FLOP_PER_TOKEN_HEAD = 524288.0
 
@@ -50,11 +51,13 @@ KERNEL_FLOPS = {
     "gdn_bwd_par": 212992.0,   # [dO;dZ]Vn^T, [dO;dZ]S^T, Vn dS'^T, [dP;dA]K, [dP^T|dA^T][Q;K], [Q;K]K^T / G
     "kda_fwd": 131072.0,       # [Qp;Kp]Sa, X Z, Aqk v_new, Kn^T v_new
     "kda_prep": 32768.0,       # [Qp;Kp]Kn^T (+ the CUDA-core inverse)
+    "kda_bwd_dhu": 131072.0,   # Kn dS'a, P^T dO, X^T dVn, [Qp^T|Kp^T][dO~; dR]
+    "kda_bwd_par": 229376.0,   # [Qp;Kp]Kn^T, [dO;dZ]Vn^T, [dO;dZ]Sa^T, Vn dS'a^T, [dP;dM]Kn, [dP^T|dM^T][Qp;Kp]
     "gdn_prep": 16384.0,
     "tri_inverse": 8192.0,     # 2 * 64^2 FLOP per token-head of the triangular solve (CUDA cores; shown against the tensor peak)
 }
 KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
-                 "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "gdn_prep": "gdn_prep_kernel", "tri_inverse": "tri_inverse_kernel",
+                 "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "kda_bwd_dhu": "kda_bwd_dhu_kernel", "kda_bwd_par": "kda_bwd_par_kernel", "gdn_prep": "gdn_prep_kernel", "tri_inverse": "tri_inverse_kernel",
                  "recurrent_gdn": "recurrent_gdn_kernel", "causal_conv1d_fwd": "conv_fwd_kernel",
                  "causal_conv1d_update": "conv_update1_kernel"}
 
@@ -122,7 +125,7 @@ class Workload:
         self.graph = None
         if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill"):
             self.cfg = dict(B=8, T=4096, HK=16, HV=32, K=128, V=128, D=8192, W=4)
-        elif name == "kda_fwd":
+        elif name in ("kda_fwd", "kda_fwd_bwd"):
             self.cfg = dict(B=4, T=8192, HK=32, HV=32, K=128, V=128)
         else:
             self.cfg = dict(N=256, T=1, HK=16, HV=32, K=128, V=128, D=8192, W=4)
@@ -143,12 +146,12 @@ class Workload:
         g_ = torch.Generator(device=device).manual_seed(seed)
         rn = lambda *s: torch.randn(*s, device=device, generator=g_)  # noqa: E731
         d = {}
-        if self.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd"):
+        if self.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd"):
             d["q"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
             d["k"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
             d["v"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
             d["beta"] = torch.sigmoid(rn(c["B"], c["T"], c["HV"])).bfloat16()
-            if self.name == "kda_fwd":
+            if self.name in ("kda_fwd", "kda_fwd_bwd"):
                 d["g"] = (F.logsigmoid(rn(c["B"], c["T"], c["HV"], c["K"])) / 16).bfloat16()
             else:
                 d["g"] = F.logsigmoid(rn(c["B"], c["T"], c["HV"])).bfloat16()
@@ -156,6 +159,8 @@ class Workload:
         if self.name == "gdn_fwd_bwd":
             d["do"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
             d["dht"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
+        if self.name == "kda_fwd_bwd":
+            d["do"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
         if self.name in ("gdn_fwd_conv", "conv_prefill"):
             d["x"] = rn(c["B"], c["T"], c["D"]).bfloat16()
         if self.name == "decode":
@@ -176,6 +181,7 @@ class Workload:
         return {"gdn_fwd_bwd": ["q", "k", "v", "g", "beta", "h0", "do", "dht"],
                 "gdn_fwd_conv": ["q", "k", "v", "g", "beta", "h0", "x"],
                 "kda_fwd": ["q", "k", "v", "g", "beta"],
+                "kda_fwd_bwd": ["q", "k", "v", "g", "beta", "do"],
                 "decode": ["q", "k", "v", "g", "beta", "x"],
                 "conv_prefill": ["x"]}[self.name]
 
@@ -195,6 +201,10 @@ class Workload:
         if n == "kda_fwd":
             with torch.no_grad():
                 return ops.chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True)
+        if n == "kda_fwd_bwd":
+            o, ht, grads = ops.chunk_kda_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"],
+                                                 grad_dtype=torch.bfloat16)
+            return (o, ht) + tuple(x for x in grads if x is not None)
         if n == "conv_prefill":
             return ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")[:1]
         y = ops.causal_conv1d_update(d["x"], d["conv_state"], weight=d["w"], bias=d["bias"], activation="silu")
@@ -216,12 +226,13 @@ class Workload:
         return self.graph_out
 
     def launches_per_step(self):
-        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "decode": 2, "conv_prefill": 1}[self.name]
+        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 8, "decode": 2, "conv_prefill": 1}[self.name]
 
     def kernel_names(self):
         return {"gdn_fwd_bwd": ["gdn_prep", "tri_inverse", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
                 "gdn_fwd_conv": ["causal_conv1d_fwd", "gdn_prep", "tri_inverse", "gdn_fwd"],
-                "kda_fwd": ["kda_prep", "tri_inverse", "kda_fwd"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
+                "kda_fwd": ["kda_prep", "tri_inverse", "kda_fwd"],
+                "kda_fwd_bwd": ["kda_prep", "tri_inverse", "kda_fwd", "kda_bwd_dhu", "kda_bwd_par"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
                 "conv_prefill": ["causal_conv1d_fwd"]}[self.name]
 
     def kernel_work(self, kname):
@@ -255,6 +266,8 @@ class Workload:
     def step_flops(self):
         if self.name == "gdn_fwd_bwd":
             return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads
+        if self.name == "kda_fwd_bwd":
+            return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads
         if self.name in ("gdn_fwd_conv", "kda_fwd"):
             return FWD_FLOP_PER_TOKEN_HEAD * self.token_heads
         return None
@@ -281,11 +294,13 @@ def cpu_reference(wl: Workload, threads: int, steps: int = 1, warmup: int = 0):
                 oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"])
             desc += " + conv1d"
         tokens = Ts
-    elif wl.name == "kda_fwd":
+    elif wl.name in ("kda_fwd", "kda_fwd_bwd"):
         Ts = 512
-        inp = oracle.make_kda_inputs(1, Ts, c["HK"], c["HV"], seed=1003, with_grad=False)
-        fn = lambda: oracle.kda_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"])  # noqa: E731
-        tokens, desc = Ts, f"B=1 T={Ts} H={c['HV']} K=V=128 fp32 naive KDA recurrence"
+        inp = oracle.make_kda_inputs(1, Ts, c["HK"], c["HV"], seed=1003, with_grad=wl.name == "kda_fwd_bwd")
+        fn = lambda: oracle.kda_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"],  # noqa: E731
+                                                  do=inp.get("do"))
+        tokens, desc = Ts, f"B=1 T={Ts} H={c['HV']} K=V=128 fp32 naive KDA recurrence" + (
+            " + autograd" if wl.name == "kda_fwd_bwd" else "")
     elif wl.name == "conv_prefill":
         Ts = 4096
         xs, w = torch.randn(1, c["D"], Ts), 0.5 * torch.randn(c["D"], c["W"])

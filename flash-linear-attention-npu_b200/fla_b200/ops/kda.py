@@ -87,6 +87,18 @@ class ChunkKdaFunction(torch.autograd.Function):
                 None, None, None, None)
 
 
+def chunk_kda_fwd_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, output_dtype=None, grad_dtype=None):
+    """Forward and backward in one call without the autograd graph (what a training step costs); g is the log decay.
+    Returns (o, final_state, (dq, dk, dv, dg, dbeta, dh0))."""
+    B, T = q.shape[:2]
+    scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
+    q, k, v, g, beta = (_as_rows(x) for x in (q, k, v, g, beta))
+    meta = (None, None, B, T, B * ((T + CHUNK - 1) // CHUNK))
+    o, ht, _ = _kda_forward(q, k, v, g, beta, scale, initial_state, True, 0, None, None, None, meta, False, output_dtype)
+    grads = kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dtype=grad_dtype)
+    return o, ht, grads
+
+
 def _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound):
     """The in-kernel gate activations in PyTorch (kda/chunk_kda_fwd/docs/api.md:103-115), for the differentiable path."""
     HV, K = g.shape[2], g.shape[3]
