@@ -8,7 +8,7 @@ distributions of BASELINE.json.  Workloads (the default is the one the headline 
   gdn_fwd_bwd    config 2: chunked GDN forward + backward, B=8 T=4096 HQK=16 HV=32 K=V=128, nonzero fp32 h0, dO, dht
   gdn_fwd_conv   config 1: causal_conv1d (W=4, SiLU) over x[8,4096,8192] bf16, then the chunked GDN forward
   kda_fwd        config 3 (forward half): chunked KDA, B=4 T=8192 H=32 K=V=128, g = logsigmoid/16 per channel
-  kda_fwd_bwd    config 3: chunked KDA forward + backward (the backward recomputes the forward), dO ~ N(0,1)
+  kda_fwd_bwd    config 3: chunked KDA forward + backward (forward intermediates kept: disable_recompute), dO ~ N(0,1)
   decode         config 4: causal_conv1d_update + fused-recurrent GDN, 256 sequences x 1 token, fp32 state pool,
                  one CUDA graph replay per step
   conv_prefill   the conv half of config 1 alone
@@ -203,7 +203,7 @@ class Workload:
                 return ops.chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True)
         if n == "kda_fwd_bwd":
             o, ht, grads = ops.chunk_kda_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"],
-                                                 grad_dtype=torch.bfloat16)
+                                                 grad_dtype=torch.bfloat16, disable_recompute=True)
             return (o, ht) + tuple(x for x in grads if x is not None)
         if n == "conv_prefill":
             return ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")[:1]
@@ -226,7 +226,7 @@ class Workload:
         return self.graph_out
 
     def launches_per_step(self):
-        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 8, "decode": 2, "conv_prefill": 1}[self.name]
+        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1}[self.name]
 
     def kernel_names(self):
         return {"gdn_fwd_bwd": ["gdn_prep", "tri_inverse", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],

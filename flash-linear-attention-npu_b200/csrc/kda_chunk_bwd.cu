@@ -673,18 +673,16 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
 
 using namespace fla;
 
-// Workspace: status | forward workspace | gk | s_img | vn_img | ds_img | dz_img | bz
-static uint64_t kda_bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t tokens, uint64_t off[7]) {
-  uint64_t fo[6];
+// Workspace: status | [forward workspace | gk | s_img | vn_img unless the caller passes the forward's saved buffer] | ds_img | dz_img | bz
+static uint64_t kda_bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t tokens, bool have_saved, uint64_t* off_saved,
+                                  uint64_t off[3]) {
   const uint64_t per = uint64_t(total_chunks) * HV;
-  uint64_t o = 256;
-  off[0] = o; o += align_up(kda_ws_layout(total_chunks, HV, fo), 256);
-  off[1] = o; o += align_up(uint64_t(tokens) * HV * kK * 4, 256);
-  off[2] = o; o += align_up(per * kKdaSImg * 2, 256);
-  off[3] = o; o += align_up(per * kKdaVnImg * 2, 256);
-  off[4] = o; o += align_up(per * kKdaDsImg * 2, 256);
-  off[5] = o; o += align_up(per * kKdaDzImg * 2, 256);
-  off[6] = o; o += align_up(uint64_t(4) * tokens * HV * 4, 256);
+  uint64_t o = 256, so[4];
+  *off_saved = o;
+  if (!have_saved) o += align_up(kda_saved_layout(total_chunks, HV, tokens, so), 256);
+  off[0] = o; o += align_up(per * kKdaDsImg * 2, 256);
+  off[1] = o; o += align_up(per * kKdaDzImg * 2, 256);
+  off[2] = o; o += align_up(uint64_t(4) * tokens * HV * 4, 256);
   return o;
 }
 
@@ -711,8 +709,8 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd_workspace_size(const fla_kda_chunk
   int64_t total_chunks; int N, max_len;
   const int st = kda_bwd_geometry(a, &total_chunks, &N, &max_len);
   if (st) return st;
-  uint64_t off[7];
-  *bytes = kda_bwd_ws_layout(total_chunks, a->v.shape[2], a->q.shape[0] * a->q.shape[1], off);
+  uint64_t off[3], off_saved;
+  *bytes = kda_bwd_ws_layout(total_chunks, a->v.shape[2], a->q.shape[0] * a->q.shape[1], a->saved.data != nullptr, &off_saved, off);
   return FLA_OK;
 }
 
@@ -763,22 +761,28 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
       return FLA_ERR_LAYOUT;
   }
   if (a->chunk_size != kC) return FLA_ERR_VALUE;
-  uint64_t off[7], fo[6];
-  const uint64_t need = kda_bwd_ws_layout(total_chunks, HV, B * T, off);
+  uint64_t off[3], off_saved, so[4], fo[6];
+  const bool have_saved = a->saved.data != nullptr;
+  const uint64_t need = kda_bwd_ws_layout(total_chunks, HV, B * T, have_saved, &off_saved, off);
   if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
+  const uint64_t sbytes = kda_saved_layout(total_chunks, HV, B * T, so);
+  if (have_saved && (a->saved.dtype != FLA_BF16 || a->saved.ndim != 1 || uint64_t(a->saved.shape[0]) * 2 < sbytes ||
+                     !aligned16(a->saved.data)))
+    return FLA_ERR_SHAPE;
   kda_ws_layout(total_chunks, HV, fo);
 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  uint8_t* fws = ws + off[0];
+  uint8_t* sv = have_saved ? static_cast<uint8_t*>(a->saved.data) : ws + off_saved;
+  uint8_t* fws = sv + so[0];
   KdaParams f{};
   f.q = static_cast<const bf16*>(a->q.data); f.k = static_cast<const bf16*>(a->k.data); f.v = static_cast<const bf16*>(a->v.data);
   f.g = a->g.data; f.beta = a->beta.data;
-  f.gk_out = reinterpret_cast<float*>(ws + off[1]);
+  f.gk_out = reinterpret_cast<float*>(sv + so[1]);
   f.status = reinterpret_cast<int*>(ws);
   f.qk_img = reinterpret_cast<bf16*>(fws + fo[0]); f.kn_img = reinterpret_cast<bf16*>(fws + fo[1]);
   f.p_img = reinterpret_cast<bf16*>(fws + fo[2]); f.x_img = reinterpret_cast<bf16*>(fws + fo[3]);
   f.vec = reinterpret_cast<float*>(fws + fo[4]); f.at = reinterpret_cast<float*>(fws + fo[5]);
-  f.s_img = reinterpret_cast<bf16*>(ws + off[2]); f.vn_img = reinterpret_cast<bf16*>(ws + off[3]);
+  f.s_img = reinterpret_cast<bf16*>(sv + so[2]); f.vn_img = reinterpret_cast<bf16*>(sv + so[3]);
   f.h0 = static_cast<const float*>(a->initial_state.data);
   f.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
   f.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
@@ -793,8 +797,8 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   p.v = f.v; p.dO = static_cast<const bf16*>(a->d_o.data); p.beta = a->beta.data;
   p.qk_img = f.qk_img; p.kn_img = f.kn_img; p.p_img = f.p_img; p.x_img = f.x_img; p.vec = f.vec; p.gk = f.gk_out;
   p.s_img = f.s_img; p.vn_img = f.vn_img;
-  p.ds_img = reinterpret_cast<bf16*>(ws + off[4]); p.dz_img = reinterpret_cast<bf16*>(ws + off[5]);
-  p.bz = reinterpret_cast<float*>(ws + off[6]);
+  p.ds_img = reinterpret_cast<bf16*>(ws + off[0]); p.dz_img = reinterpret_cast<bf16*>(ws + off[1]);
+  p.bz = reinterpret_cast<float*>(ws + off[2]);
   p.dht = static_cast<const float*>(a->dht.data); p.dh0 = static_cast<float*>(a->dh0.data);
   p.dq = a->dq.data; p.dk = a->dk.data; p.dv = a->dv.data; p.dg = a->dg.data; p.dbeta = a->dbeta.data;
   p.cu_seqlens = f.cu_seqlens; p.chunk_offsets = f.chunk_offsets;
@@ -810,7 +814,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
   const int nt_max = (max_len + kC - 1) / kC;
-  if ((st = kda_launch_forward(f, nt_max, cs))) return st;
+  if (!have_saved && (st = kda_launch_forward(f, nt_max, cs))) return st;
   static bool attr_done_dev[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;

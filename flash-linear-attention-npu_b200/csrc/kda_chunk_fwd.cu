@@ -504,6 +504,17 @@ uint64_t fla::kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[6]) {
   return o;
 }
 
+uint64_t fla::kda_saved_layout(int64_t total_chunks, int64_t HV, int64_t tokens, uint64_t off[4]) {
+  uint64_t fo[6];
+  const uint64_t per = uint64_t(total_chunks) * HV;
+  uint64_t o = 0;
+  off[0] = o; o += align_up(kda_ws_layout(total_chunks, HV, fo), 256);
+  off[1] = o; o += align_up(uint64_t(tokens) * HV * kK * 4, 256);
+  off[2] = o; o += align_up(per * kKdaSImg * 2, 256);
+  off[3] = o; o += align_up(per * kKdaVnImg * 2, 256);
+  return o;
+}
+
 static int kda_geometry(const fla_kda_chunk_fwd_args* a, int64_t* total_chunks, int* N, int* max_len) {
   const fla_tensor_t& q = a->q;
   if (!q.data || q.ndim != 4 || !a->v.data || a->v.ndim != 4) return FLA_ERR_SHAPE;
@@ -528,7 +539,17 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd_workspace_size(const fla_kda_chunk
   const int st = kda_geometry(a, &total_chunks, &N, &max_len);
   if (st) return st;
   uint64_t off[6];
-  *bytes = kda_ws_layout(total_chunks, a->v.shape[2], off);
+  *bytes = a->saved.data ? 256 : kda_ws_layout(total_chunks, a->v.shape[2], off);
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_kda_chunk_saved_size(const fla_kda_chunk_fwd_args* a, uint64_t* bytes) {
+  if (!a || !bytes) return FLA_ERR_NULL;
+  int64_t total_chunks; int N, max_len;
+  const int st = kda_geometry(a, &total_chunks, &N, &max_len);
+  if (st) return st;
+  uint64_t off[4];
+  *bytes = kda_saved_layout(total_chunks, a->v.shape[2], a->q.shape[0] * a->q.shape[1], off);
   return FLA_OK;
 }
 
@@ -584,7 +605,17 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   }
   if (a->chunk_size != kC) return FLA_ERR_VALUE;
   uint64_t off[6];
-  const uint64_t need = kda_ws_layout(total_chunks, HV, off);
+  uint64_t need = kda_ws_layout(total_chunks, HV, off);
+  uint8_t* images = static_cast<uint8_t*>(workspace);   // where the operand images go
+  uint64_t soff[4] = {0, 0, 0, 0};
+  if (a->saved.data) {
+    const uint64_t sbytes = kda_saved_layout(total_chunks, HV, B * T, soff);
+    if (a->saved.dtype != FLA_BF16 || a->saved.ndim != 1 || uint64_t(a->saved.shape[0]) * 2 < sbytes || !aligned16(a->saved.data))
+      return FLA_ERR_SHAPE;
+    if (a->gate_mode != 0 || a->gk.data) return FLA_ERR_VALUE;
+    images = static_cast<uint8_t*>(a->saved.data) + soff[0];
+    need = 256;
+  }
   if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
 
   KdaParams p{};
@@ -592,8 +623,14 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   p.g = a->g.data; p.beta = be.data;
   p.a_log = static_cast<const float*>(a->a_log.data); p.dt_bias = static_cast<const float*>(a->dt_bias.data);
   p.gk_out = static_cast<float*>(a->gk.data);
-  uint8_t* ws = static_cast<uint8_t*>(workspace);
-  p.status = reinterpret_cast<int*>(ws);
+  uint8_t* ws = images;
+  p.status = reinterpret_cast<int*>(workspace);
+  if (a->saved.data) {
+    uint8_t* sv = static_cast<uint8_t*>(a->saved.data);
+    p.gk_out = reinterpret_cast<float*>(sv + soff[1]);
+    p.s_img = reinterpret_cast<bf16*>(sv + soff[2]);
+    p.vn_img = reinterpret_cast<bf16*>(sv + soff[3]);
+  }
   p.qk_img = reinterpret_cast<bf16*>(ws + off[0]); p.kn_img = reinterpret_cast<bf16*>(ws + off[1]);
   p.p_img = reinterpret_cast<bf16*>(ws + off[2]); p.x_img = reinterpret_cast<bf16*>(ws + off[3]);
   p.vec = reinterpret_cast<float*>(ws + off[4]);

@@ -32,6 +32,9 @@ constexpr int kKdaVecs = 3;
 
 // Workspace layout of the forward (offsets of qk_img, kn_img, p_img, x_img, vec, at); returns the total size.
 uint64_t kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[6]);
+// Layout of the buffer a training forward leaves for the backward: the forward workspace (operand images), gk, the
+// Sa images and the v_new images; returns the total size.
+uint64_t kda_saved_layout(int64_t total_chunks, int64_t HV, int64_t tokens, uint64_t off[4]);
 // prep -> inverse -> forward scan on `stream`; 0 or an FLA_ERR_* status.
 int kda_launch_forward(const KdaParams& p, int nt_max, cudaStream_t stream);
 

@@ -12,15 +12,18 @@ runs in PyTorch (so autograd differentiates it) and the kernels receive the acti
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .. import _runtime as rt
+from .. import load_library
 from ._structs import KdaChunkBwdArgs, KdaChunkFwdArgs
 from .gdn import CHUNK, _as_rows, _varlen_meta
 
 
 def _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias, lower_bound,
-                 meta, return_gate_cumsum, output_dtype):
+                 meta, return_gate_cumsum, output_dtype, keep_for_backward=False):
     B, T, HK, K = q.shape
     HV, V = v.shape[2], v.shape[3]
     cu, co, N, max_len, total_chunks = meta
@@ -35,12 +38,23 @@ def _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gat
     a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
     a.scale, a.lower_bound, a.gate_mode = scale, float(lower_bound or 0.0), gate_mode
     a.chunk_size, a.max_seqlen, a.total_chunks = CHUNK, int(max_len), int(total_chunks)
-    rt.call("kda_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gk, cu, co])
+    saved = None
+    if keep_for_backward:   # the reference's disable_recompute=True: keep the intermediates instead of recomputing them
+        nbytes = ctypes.c_uint64(0)
+        status = load_library().fla_b200_kda_chunk_saved_size(ctypes.byref(a), ctypes.byref(nbytes))
+        if status:
+            raise RuntimeError(f"kda_chunk_saved_size failed with status={status}")
+        saved = torch.empty((nbytes.value + 1) // 2, dtype=torch.bfloat16, device=dev)
+        a.saved = rt.desc(saved)
+    rt.call("kda_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gk, cu, co, saved])
+    if keep_for_backward:
+        return o, ht, saved
     return o, ht, gk
 
 
-def kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dtype=None):
-    """Complete KDA chunk backward (g = per-channel log decay).  Returns dq, dk, dv, dg, dbeta, dh0."""
+def kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dtype=None, saved=None):
+    """Complete KDA chunk backward (g = per-channel log decay).  Returns dq, dk, dv, dg, dbeta, dh0.
+    `saved` is the buffer a forward with ``keep_for_backward`` returned; without it the forward is recomputed."""
     B, T, HK, K = q.shape
     HV, V = v.shape[2], v.shape[3]
     cu, co, N, max_len, total_chunks = meta
@@ -59,10 +73,10 @@ def kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dt
     a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)
     a.initial_state, a.d_o, a.dht = rt.desc(initial_state), rt.desc(do), rt.desc(dht)
     a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = (rt.desc(x) for x in (dq, dk, dv, dg, dbeta, dh0))
-    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    a.cu_seqlens, a.chunk_offsets, a.saved = rt.desc(cu), rt.desc(co), rt.desc(saved)
     a.scale = scale
     a.chunk_size, a.max_seqlen, a.total_chunks = CHUNK, int(max_len), int(total_chunks)
-    rt.call("kda_chunk_bwd", a, [q, k, v, g, beta, initial_state, do, dht, dq, dk, dv, dg, dbeta, dh0, cu, co])
+    rt.call("kda_chunk_bwd", a, [q, k, v, g, beta, initial_state, do, dht, dq, dk, dv, dg, dbeta, dh0, cu, co, saved])
     return dq, dk, dv, dg, dbeta, dh0
 
 
@@ -70,32 +84,37 @@ class ChunkKdaFunction(torch.autograd.Function):
     """Autograd glue of `chunk_kda` (gate already activated): saves only the inputs, the backward recomputes."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype):
-        o, ht, _ = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, 0, None, None, None, meta,
-                                False, output_dtype)
-        ctx.save_for_backward(q, k, v, g, beta, initial_state)
+    def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype, disable_recompute):
+        o, ht, saved = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, 0, None, None, None, meta,
+                                    False, output_dtype, keep_for_backward=disable_recompute)
+        ctx.save_for_backward(q, k, v, g, beta, initial_state, saved if disable_recompute else None)
         ctx.scale, ctx.meta = scale, meta
         ctx.in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, g, beta, h0 = ctx.saved_tensors
-        dq, dk, dv, dg, dbeta, dh0 = kda_chunk_bwd(q, k, v, g, beta, ctx.scale, h0, do.contiguous(), dht, ctx.meta)
+        q, k, v, g, beta, h0, saved = ctx.saved_tensors
+        dq, dk, dv, dg, dbeta, dh0 = kda_chunk_bwd(q, k, v, g, beta, ctx.scale, h0, do.contiguous(), dht, ctx.meta,
+                                                   saved=saved)
         dts = ctx.in_dtypes
         return (dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]), dg.to(dts[3]), dbeta.to(dts[4]), dh0,
-                None, None, None, None)
+                None, None, None, None, None)
 
 
-def chunk_kda_fwd_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, output_dtype=None, grad_dtype=None):
+def chunk_kda_fwd_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, output_dtype=None, grad_dtype=None,
+                      disable_recompute=False):
     """Forward and backward in one call without the autograd graph (what a training step costs); g is the log decay.
+    With ``disable_recompute`` the forward keeps its intermediates (about 265 KB per (chunk, head)) for the backward.
     Returns (o, final_state, (dq, dk, dv, dg, dbeta, dh0))."""
     B, T = q.shape[:2]
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
     q, k, v, g, beta = (_as_rows(x) for x in (q, k, v, g, beta))
     meta = (None, None, B, T, B * ((T + CHUNK - 1) // CHUNK))
-    o, ht, _ = _kda_forward(q, k, v, g, beta, scale, initial_state, True, 0, None, None, None, meta, False, output_dtype)
-    grads = kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dtype=grad_dtype)
+    o, ht, saved = _kda_forward(q, k, v, g, beta, scale, initial_state, True, 0, None, None, None, meta, False, output_dtype,
+                                keep_for_backward=disable_recompute)
+    grads = kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dtype=grad_dtype,
+                          saved=saved if disable_recompute else None)
     return o, ht, grads
 
 
@@ -114,7 +133,7 @@ def _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound):
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
               use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
               cu_seqlens=None, safe_gate=False, lower_bound=None, A_log=None, dt_bias=None,
-              return_gate_cumsum=False, output_dtype=None):
+              return_gate_cumsum=False, output_dtype=None, disable_recompute=False):
     """Returns ``(o [B,T,HV,V], final_state [N,HV,K,V] | None)`` (plus the cumulative gate `[B,T,HV,K]` fp32
     when ``return_gate_cumsum``)."""
     op = "chunk_kda"
@@ -166,7 +185,8 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     if needs_grad:
         if return_gate_cumsum:
             raise NotImplementedError(f"{op}: return_gate_cumsum is not available on the differentiable path")
-        o, ht = ChunkKdaFunction.apply(q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype)
+        o, ht = ChunkKdaFunction.apply(q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype,
+                                       bool(disable_recompute))
         return o, ht
     o, ht, gk = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias,
                              lower_bound, meta, return_gate_cumsum, output_dtype)

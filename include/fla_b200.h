@@ -239,6 +239,7 @@ typedef struct fla_kda_chunk_fwd_args {
   fla_tensor_t q, k, v, g, beta, a_log, dt_bias, initial_state;
   fla_tensor_t o, final_state, gk;
   fla_tensor_t cu_seqlens, chunk_offsets;
+  fla_tensor_t saved;   /* optional out, 1-D bf16 of fla_b200_kda_chunk_saved_size bytes: what the backward otherwise recomputes */
   float scale;
   float lower_bound;
   int32_t gate_mode;
@@ -247,6 +248,9 @@ typedef struct fla_kda_chunk_fwd_args {
   int32_t total_chunks;
 } fla_kda_chunk_fwd_args;
 FLA_API int fla_b200_kda_chunk_fwd_workspace_size(const fla_kda_chunk_fwd_args* args, uint64_t* bytes);
+/* Size of the `saved` buffer (the reference's disable_recompute=True mode of npu_chunk_kda_fwd, _aclnn_ctypes.py:1085,
+ * keeps the forward's intermediates for the backward instead of recomputing them); gate_mode must be 0 with it. */
+FLA_API int fla_b200_kda_chunk_saved_size(const fla_kda_chunk_fwd_args* args, uint64_t* bytes);
 FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* args, void* workspace, uint64_t workspace_bytes,
                                    void* stream);
 
@@ -255,7 +259,7 @@ FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* args, void* wor
  * The reference has only the intra-chunk piece (aclnnChunkKdaBwdIntra as bound by npu_chunk_kda_bwd_intra,
  * torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1534-1783) and defers the inter-chunk backward to a
  * third-party package; this entry computes the complete gradient of fla_b200_kda_chunk_fwd in one call.
- * It recomputes the forward internally (nothing has to be saved except the inputs).
+ * It recomputes the forward internally (nothing has to be saved except the inputs) unless `saved` is given.
  *   q, k, v, g, beta, initial_state, cu_seqlens ...: the forward's inputs;  d_o [B, T, HV, 128] bf16;
  *   dht [N, HV, 128, 128] f32 optional (gradient of the final state);
  *   dq, dk [B, T, HK, 128] (summed over the value heads of a group), dv [B, T, HV, 128], dg [B, T, HV, 128],
@@ -266,6 +270,7 @@ typedef struct fla_kda_chunk_bwd_args {
   fla_tensor_t d_o, dht;
   fla_tensor_t dq, dk, dv, dg, dbeta, dh0;
   fla_tensor_t cu_seqlens, chunk_offsets;
+  fla_tensor_t saved;   /* optional in: the buffer the forward filled; skips the internal recomputation */
   float scale;
   int32_t chunk_size;
   int32_t max_seqlen;

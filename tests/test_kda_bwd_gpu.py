@@ -30,7 +30,7 @@ def _reference(inp, cu, dht):
     return ref
 
 
-def _run(B, T, HK, HV, seed, h0=True, with_dht=True, cu=None, gate_scale=1.0):
+def _run(B, T, HK, HV, seed, h0=True, with_dht=True, cu=None, gate_scale=1.0, **kw):
     from fla_b200.ops import chunk_kda
     inp = oracle.make_kda_inputs(B, T, HK, HV, seed=seed)
     inp["g"] = (inp["g"].float() * gate_scale).bfloat16()
@@ -44,7 +44,7 @@ def _run(B, T, HK, HV, seed, h0=True, with_dht=True, cu=None, gate_scale=1.0):
     h0_d = inp["h0"].cuda().requires_grad_(True) if h0 else None
     o, ht = chunk_kda(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], initial_state=h0_d,
                       output_final_state=True, output_dtype=torch.float32,
-                      cu_seqlens=None if cu is None else torch.tensor(cu, dtype=torch.int32))
+                      cu_seqlens=None if cu is None else torch.tensor(cu, dtype=torch.int32), **kw)
     loss = (o * inp["do"].cuda().float()).sum()
     if with_dht:
         loss = loss + (ht * dht.cuda()).sum()
@@ -91,6 +91,15 @@ def test_kda_backward_fp32_gradients_through_the_c_abi():
 @pytest.mark.parametrize("T", [1, 31, 65, 100])
 def test_kda_backward_ragged_lengths(T):
     got, ref = _run(1, T, 1, 1, seed=60 + T)
+    _check(got, ref)
+
+
+def test_kda_backward_from_saved_intermediates():
+    # disable_recompute=True: the forward keeps its operand images and the backward skips the recomputation
+    got, ref = _run(2, 200, 2, 2, seed=88, disable_recompute=True)
+    _check(got, ref)
+    cu = [0, 70, 71, 199, 263, 300]
+    got, ref = _run(1, 300, 2, 2, seed=14, cu=cu, disable_recompute=True)
     _check(got, ref)
 
 
