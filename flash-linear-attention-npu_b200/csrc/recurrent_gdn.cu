@@ -2,11 +2,14 @@
 //
 // One CTA owns one (sequence, value-head) state matrix, streams it from HBM once with 16-byte
 // loads, applies up to a few tokens of
-//     S <- exp(g) S ;  d = beta (v - S^T k) ;  S <- S + k d^T ;  o = S^T (scale q)
+//     S <- exp(g) S  (scalar g per head and / or a per-key-channel gate gk: S <- diag(exp(gk)) S) ;
+//     d = beta (v - S^T k) ;  S <- S + k d^T ;  o = S^T (scale q)
 // entirely in registers (fp32), and streams it back.  The kernel is HBM-bound: per (seq, head) it
 // moves K*V*sizeof(state) bytes in and out and a few hundred bytes of activations; no tensor cores.
-// Replaces the reference operator recurrent_gated_delta_rule
-// (fla/ops/ascendc/gdn/recurrent_gdn/recurrent_gated_delta_rule/op_kernel/recurrent_gated_delta_rule.h:159-199,364-402,445-513).
+// Replaces the reference operators recurrent_gated_delta_rule
+// (fla/ops/ascendc/gdn/recurrent_gdn/recurrent_gated_delta_rule/op_kernel/recurrent_gated_delta_rule.h:159-199,364-402,445-513)
+// and recurrent_kda (fla/ops/ascendc/kda/recurrent_kda/docs/design.md:44-70: per-channel gate with optional in-kernel
+// gate activation and beta sigmoid).
 #include <cuda_bf16.h>
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
@@ -19,6 +22,9 @@ struct RecurrentParams {
   const __nv_bfloat16* v;  // [T, HV, V]
   const void* g;           // [T, HV] or null
   const void* beta;        // [T, HV] or null
+  const void* gk;          // [T, HV, K] per-channel log gate (raw when gate_mode != 0) or null
+  const float* a_log;      // [HV] or null
+  const float* dt_bias;    // [HV, K] or null
   const void* state_in;    // [blocks, HV, K, V] (or [.., V, K] when v-first)
   void* state_out;         // may alias state_in
   void* out;               // [T, HV, V]
@@ -29,8 +35,9 @@ struct RecurrentParams {
   int64_t g_stride_t, beta_stride_t, out_stride_t, out_stride_h;
   int64_t state_in_stride_b, state_in_stride_h, state_out_stride_b, state_out_stride_h;
   int HK, HV, tokens_per_seq, nblocks_in, nblocks_out;
-  int g_is_f32, beta_is_f32, out_is_f32, l2norm;
-  float scale;
+  int64_t gk_stride_t, gk_stride_h;
+  int g_is_f32, beta_is_f32, out_is_f32, l2norm, gk_is_f32, gate_mode, beta_mode;
+  float scale, lower_bound;
 };
 
 template <typename T>
@@ -77,7 +84,7 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
   constexpr int R = ROWS / RG;               // rows per thread
   static_assert(ROWS % RG == 0 && TPR <= 32, "unsupported head dims");
 
-  __shared__ float k_s[K], q_s[K];
+  __shared__ float k_s[K], q_s[K], dk_s[K];
   __shared__ __align__(16) float red[VFIRST ? 1 : RG][VFIRST ? 4 : COLS];
   __shared__ float norm_s[2];
 
@@ -117,8 +124,19 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
     } else if (tid < 2 * K) {
       q_s[tid - K] = __bfloat162float(p.q[t * p.q_stride_t + hk * p.q_stride_h + (tid - K)]);
     }
+    if (p.gk && tid < K) {   // per-channel decay of this token: exp(gate(gk))
+      float gate = load_scalar(p.gk, t * p.gk_stride_t + hv * p.gk_stride_h + tid, p.gk_is_f32);
+      if (p.gate_mode) {
+        const float eig = p.a_log ? __expf(p.a_log[hv]) : 1.f;
+        const float raw = gate + (p.dt_bias ? p.dt_bias[hv * K + tid] : 0.f);
+        if (p.gate_mode == 1) gate = -eig * (raw > 20.f ? raw : log1pf(__expf(raw)));
+        else gate = p.lower_bound / (1.f + __expf(-eig * raw));
+      }
+      dk_s[tid] = __expf(gate);
+    }
     const float decay = p.g ? expf(load_scalar(p.g, t * p.g_stride_t + hv, p.g_is_f32)) : 1.f;
-    const float beta = p.beta ? load_scalar(p.beta, t * p.beta_stride_t + hv, p.beta_is_f32) : 1.f;
+    float beta = p.beta ? load_scalar(p.beta, t * p.beta_stride_t + hv, p.beta_is_f32) : 1.f;
+    if (p.beta_mode) beta = float(p.beta_mode) / (1.f + __expf(-beta));
     __syncthreads();
     float kscale = 1.f, qscale = p.scale;
     if (p.l2norm) {
@@ -135,6 +153,19 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
       qscale = p.scale * norm_s[1];
     }
 
+    if (p.gk) {   // S <- diag(exp(gate)) S
+      if constexpr (!VFIRST) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const float d = dk_s[rg + i * RG];
+          s[i].x *= d; s[i].y *= d; s[i].z *= d; s[i].w *= d;
+        }
+      } else {
+        const float4 d = make_float4(dk_s[c0], dk_s[c0 + 1], dk_s[c0 + 2], dk_s[c0 + 3]);
+#pragma unroll
+        for (int i = 0; i < R; ++i) { s[i].x *= d.x; s[i].y *= d.y; s[i].z *= d.z; s[i].w *= d.w; }
+      }
+    }
     if constexpr (!VFIRST) {
       // rows are k, my 4 columns are v.  dot[v] = sum_k S[k][v] k[k]
       float4 part = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -282,6 +313,21 @@ extern "C" FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* a, v
     if (s->dtype != FLA_F32 && s->dtype != FLA_BF16) return FLA_ERR_DTYPE;
   }
   if (!(a->scale == a->scale) || a->scale > 3.0e38f || a->scale < -3.0e38f) return FLA_ERR_VALUE;
+  if (a->gate_mode < 0 || a->gate_mode > 2 || a->beta_mode < 0 || a->beta_mode > 2) return FLA_ERR_VALUE;
+  if (a->gk.data) {
+    const fla_tensor_t& gk = a->gk;
+    if (gk.ndim != 3 || gk.shape[0] != T || gk.shape[1] != HV || gk.shape[2] != K || gk.stride[2] != 1) return FLA_ERR_SHAPE;
+    if (gk.dtype != FLA_F32 && gk.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+    if (a->gate_mode) {
+      if (!a->a_log.data || a->a_log.dtype != FLA_F32 || a->a_log.ndim != 1 || a->a_log.shape[0] != HV || a->a_log.stride[0] != 1)
+        return FLA_ERR_SHAPE;
+      if (a->dt_bias.data && (a->dt_bias.dtype != FLA_F32 || a->dt_bias.ndim != 2 || a->dt_bias.shape[0] != HV ||
+                              a->dt_bias.shape[1] != K || a->dt_bias.stride[1] != 1 || a->dt_bias.stride[0] != K))
+        return FLA_ERR_SHAPE;
+    }
+  } else if (a->gate_mode) {
+    return FLA_ERR_VALUE;
+  }
 
   RecurrentParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q.data);
@@ -304,6 +350,9 @@ extern "C" FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* a, v
   p.nblocks_in = int(si.shape[0]); p.nblocks_out = int(so.shape[0]);
   p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = a->beta.dtype == FLA_F32; p.out_is_f32 = o.dtype == FLA_F32;
   p.l2norm = a->use_qk_l2norm; p.scale = a->scale;
+  p.gk = a->gk.data; p.a_log = static_cast<const float*>(a->a_log.data); p.dt_bias = static_cast<const float*>(a->dt_bias.data);
+  p.gk_stride_t = a->gk.data ? a->gk.stride[0] : 0; p.gk_stride_h = a->gk.data ? a->gk.stride[1] : 0;
+  p.gk_is_f32 = a->gk.dtype == FLA_F32; p.gate_mode = a->gate_mode; p.beta_mode = a->beta_mode; p.lower_bound = a->lower_bound;
   if (!a->state_indices.data && nseq > p.nblocks_in) return FLA_ERR_SHAPE;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -5,6 +5,7 @@ from .gdn import (chunk_gated_delta_rule, chunk_gated_delta_rule_bwd, chunk_gate
                   ChunkGatedDeltaRuleFunction)
 from .kda import chunk_kda, chunk_kda_fwd_bwd, kda_chunk_bwd  # noqa: F401
 from .l2norm import l2norm_bwd, l2norm_fwd  # noqa: F401
-from .recurrent import fused_recurrent_gated_delta_rule, recurrent_gated_delta_rule  # noqa: F401
+from .recurrent import fused_recurrent_gated_delta_rule, recurrent_gated_delta_rule, recurrent_kda  # noqa: F401
 
 npu_recurrent_gated_delta_rule = recurrent_gated_delta_rule
+npu_recurrent_kda = recurrent_kda

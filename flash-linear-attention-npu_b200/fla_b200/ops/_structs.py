@@ -6,9 +6,11 @@ from .._runtime import TensorDesc
 
 class RecurrentGdnArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "g", "beta", "state_in", "state_out", "out",
-                                           "cu_seqlens", "state_indices", "num_accepted_tokens")] + [
-        ("scale", ctypes.c_float), ("tokens_per_seq", ctypes.c_int32), ("state_v_first", ctypes.c_int32),
-        ("use_qk_l2norm", ctypes.c_int32)]
+                                           "cu_seqlens", "state_indices", "num_accepted_tokens", "gk", "a_log",
+                                           "dt_bias")] + [
+        ("scale", ctypes.c_float), ("lower_bound", ctypes.c_float), ("tokens_per_seq", ctypes.c_int32),
+        ("state_v_first", ctypes.c_int32), ("use_qk_l2norm", ctypes.c_int32), ("gate_mode", ctypes.c_int32),
+        ("beta_mode", ctypes.c_int32)]
 
 
 class CausalConv1dFwdArgs(ctypes.Structure):

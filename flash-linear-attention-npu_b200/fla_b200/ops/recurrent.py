@@ -25,9 +25,10 @@ def _activation_ok(name, t):
 
 def fused_recurrent_gated_delta_rule(q, k, v, g=None, beta=None, scale=None, initial_state=None,
                                      output_final_state=False, use_qk_l2norm_in_kernel=False, cu_seqlens=None,
-                                     transpose_state_layout=False, inplace_final_state=False):
-    """q,k `[B,T,HK,K]`, v `[B,T,HV,V]` bf16; g, beta `[B,T,HV]`; initial_state `[N,HV,K,V]` fp32|bf16
-    (`[N,HV,V,K]` with ``transpose_state_layout``).  Returns ``(o [B,T,HV,V], final_state | None)``.
+                                     transpose_state_layout=False, inplace_final_state=False, gk=None):
+    """q,k `[B,T,HK,K]`, v `[B,T,HV,V]` bf16; g, beta `[B,T,HV]`; gk `[B,T,HV,K]` (per-key-channel log decay, optional);
+    initial_state `[N,HV,K,V]` fp32|bf16 (`[N,HV,V,K]` with ``transpose_state_layout``).
+    Returns ``(o [B,T,HV,V], final_state | None)``.
 
     With ``inplace_final_state`` the final state overwrites ``initial_state`` (serving pools) and that
     same tensor is returned.  With ``cu_seqlens`` (int32/int64 `[N+1]`) B must be 1.
@@ -69,13 +70,18 @@ def fused_recurrent_gated_delta_rule(q, k, v, g=None, beta=None, scale=None, ini
     q3, k3, v3, o3 = (x.reshape(B * T, x.shape[2], x.shape[3]) for x in (q, k, v, out))
     g2 = None if g is None else g.reshape(B * T, HV)
     b2 = None if beta is None else beta.reshape(B * T, HV)
+    gk3 = None
+    if gk is not None:
+        if tuple(gk.shape) != (B, T, HV, K):
+            raise RuntimeError(f"{op}: gk must be {(B, T, HV, K)}, got {tuple(gk.shape)}")
+        gk3 = gk.reshape(B * T, HV, K)
     a = RecurrentGdnArgs()
     a.q, a.k, a.v, a.g, a.beta = rt.desc(q3), rt.desc(k3), rt.desc(v3), rt.desc(g2), rt.desc(b2)
     a.state_in, a.state_out, a.out = rt.desc(state_in), rt.desc(state_out), rt.desc(o3)
-    a.cu_seqlens = rt.desc(cu)
+    a.cu_seqlens, a.gk = rt.desc(cu), rt.desc(gk3)
     a.scale, a.tokens_per_seq = scale, T
     a.state_v_first, a.use_qk_l2norm = int(transpose_state_layout), int(use_qk_l2norm_in_kernel)
-    rt.call(_OP, a, [q3, k3, v3, g2, b2, state_in, state_out, o3, cu])
+    rt.call(_OP, a, [q3, k3, v3, g2, b2, state_in, state_out, o3, cu, gk3])
     if inplace_final_state and initial_state is not None:
         rt.mark_mutated(state_out)
     return out, (state_out if (output_final_state or inplace_final_state) else None)
@@ -128,3 +134,121 @@ def recurrent_gated_delta_rule(query, key, value, state, *, beta, scale=1.0, act
     rt.call(_OP, a, [query, key, value, g, beta, state, out, cu, ssm_state_indices, num_accepted_tokens])
     rt.mark_mutated(state)
     return out
+
+
+def recurrent_kda(q, k, v, g, beta, initial_state=None, *, cu_seqlens=None, ssm_state_indices=None, A_log=None,
+                  dt_bias=None, num_accepted_tokens=None, layout="BSND", scale=None, output_final_state=False,
+                  inplace_final_state=True, use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False,
+                  use_beta_sigmoid_in_kernel=False, allow_neg_eigval=False, safe_gate=False, lower_bound=None,
+                  state_v_first=False):
+    """Recurrent KDA step over a state pool, with the reference operator's argument names
+    (npu_recurrent_kda, torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1298-1503).
+
+    BSND: q,k `[B,T,H,K]`, v `[B,T,HV,V]`, g `[B,T,HV,K]`, beta `[B,T,HV]`; TND: the same without the batch dim.
+    ``initial_state`` `[state_capacity,HV,K,V]` (`[..,V,K]` with ``state_v_first``) fp32|bf16, updated in place when
+    ``inplace_final_state``.  ``ssm_state_indices``: packed `[T]` (state after token t goes to block indices[t]) or
+    speculative `[seq_num,max_step]` (token s of sequence n goes to block indices[n,s]); a sequence starts from the
+    block of its first token, or of token ``num_accepted_tokens[n] - 1``.  Returns ``(out, final_state | None)``.
+    """
+    op = "recurrent_kda"
+    if layout not in ("BSND", "TND"):
+        raise RuntimeError(f"{op}: layout must be BSND or TND.")
+    tnd = layout == "TND"
+    rank = 3 if tnd else 4
+    if any(x.dim() != rank for x in (q, k, v, g)) or beta.dim() != rank - 1:
+        raise RuntimeError(f"{op}: layout/rank mismatch. TND expects q/k [T,H,K], v [T,HV,V], g [T,HV,K], beta [T,HV]; "
+                           "BSND expects q/k [B,T,H,K], v [B,T,HV,V], g [B,T,HV,K], beta [B,T,HV].")
+    if q.shape != k.shape:
+        raise RuntimeError(f"{op}: q and k must have identical shape.")
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _activation_ok(f"{op}: {n}", t)
+    if tnd:
+        q, k, v, g, beta = (x.unsqueeze(0) for x in (q, k, v, g, beta))
+    B, T, H, K = q.shape
+    HV, V = v.shape[2], v.shape[3]
+    if tuple(g.shape) != (B, T, HV, K) or tuple(beta.shape) != (B, T, HV) or tuple(v.shape[:2]) != (B, T):
+        raise RuntimeError(f"{op}: v/g/beta shape mismatch.")
+    if HV % H:
+        raise RuntimeError(f"{op}: HV must be divisible by H.")
+    if g.dtype not in (torch.bfloat16, torch.float32) or beta.dtype not in (torch.bfloat16, torch.float32):
+        raise RuntimeError(f"{op}: g and beta must use BF16 or FP32.")
+    dev = q.device
+    total = B * T
+    if cu_seqlens is None:
+        seq_num = B
+        cu = None if not tnd else torch.tensor([0, T], dtype=torch.int32, device=dev)
+    else:
+        if not isinstance(cu_seqlens, torch.Tensor) or cu_seqlens.dim() != 1 or cu_seqlens.numel() < 2:
+            raise RuntimeError(f"{op}: cu_seqlens must be a 1D INT32 or INT64 tensor.")
+        cu = cu_seqlens.to(device=dev, dtype=torch.int32)
+        seq_num = cu.numel() - 1
+    tail = (HV, V, K) if state_v_first else (HV, K, V)
+    if initial_state is None:
+        if inplace_final_state:
+            raise RuntimeError(f"{op}: inplace_final_state=True requires initial_state.")
+        state_in = torch.zeros((seq_num, *tail), dtype=torch.float32, device=dev)
+    else:
+        if initial_state.dtype not in (torch.float32, torch.bfloat16):
+            raise RuntimeError(f"{op}: initial_state must use FP32 or BF16.")
+        if initial_state.dim() != 4 or tuple(initial_state.shape[1:]) != tail:
+            raise RuntimeError(f"{op}: initial_state must be [state_capacity,{','.join(map(str, tail))}].")
+        state_in = initial_state if initial_state.is_contiguous() else initial_state.contiguous()
+    idx = None
+    if ssm_state_indices is not None:
+        if ssm_state_indices.dim() == 1 and ssm_state_indices.shape[0] >= total:
+            idx = ssm_state_indices[:total].to(device=dev, dtype=torch.int32).contiguous()
+        elif ssm_state_indices.dim() == 2 and ssm_state_indices.shape[0] == seq_num and ssm_state_indices.shape[1] > 0:
+            # speculative [seq_num, max_step]: token s of sequence n -> indices[n, s]
+            bounds = cu if cu is not None else torch.arange(0, total + 1, T, dtype=torch.int32, device=dev)
+            tok = torch.arange(total, device=dev)
+            seq_of = torch.bucketize(tok, bounds[1:].long(), right=True).clamp_(max=seq_num - 1)
+            step = (tok - bounds[:-1].long()[seq_of]).clamp_(0, ssm_state_indices.shape[1] - 1)
+            idx = ssm_state_indices.to(dev)[seq_of, step].to(torch.int32).contiguous()
+        else:
+            raise RuntimeError(f"{op}: ssm_state_indices must be INT32/INT64 packed [T] or speculative [seq_num,max_step].")
+    elif state_in.shape[0] != seq_num:
+        raise RuntimeError(f"{op}: without ssm_state_indices, state_capacity must equal seq_num.")
+    if num_accepted_tokens is not None:
+        if idx is None:
+            raise RuntimeError(f"{op}: num_accepted_tokens requires ssm_state_indices.")
+        if tuple(num_accepted_tokens.shape) != (seq_num,):
+            raise RuntimeError(f"{op}: num_accepted_tokens must be INT32/INT64 [seq_num].")
+        num_accepted_tokens = num_accepted_tokens.to(device=dev, dtype=torch.int32)
+    gate_mode = 0
+    lower = -5.0 if lower_bound is None else float(lower_bound)
+    if use_gate_in_kernel:
+        if A_log is None or A_log.dtype != torch.float32 or tuple(A_log.shape) != (HV,):
+            raise RuntimeError(f"{op}: A_log must be FP32 [HV] when use_gate_in_kernel=True.")
+        if safe_gate and not -5.0 <= lower < 0.0:
+            raise RuntimeError(f"{op}: lower_bound must be in [-5,0) when safe_gate=True.")
+        if dt_bias is not None:
+            if dt_bias.dtype != torch.float32 or tuple(dt_bias.shape) not in ((HV * K,), (HV, K)):
+                raise RuntimeError(f"{op}: dt_bias must be FP32 [HV*K] or [HV,K].")
+            dt_bias = dt_bias.reshape(HV, K).contiguous()
+        gate_mode = 2 if safe_gate else 1
+    elif safe_gate or A_log is not None or dt_bias is not None:
+        raise RuntimeError(f"{op}: A_log, dt_bias and safe_gate require use_gate_in_kernel=True.")
+    scale = K ** -0.5 if scale is None else float(scale)
+    if inplace_final_state:
+        rt.reject_requires_grad(op, initial_state=initial_state)
+        state_out = state_in
+    else:
+        state_out = torch.empty_like(state_in)
+    out = torch.empty_like(v)
+    q3, k3, v3, o3 = (x.reshape(total, x.shape[2], x.shape[3]) for x in (q, k, v, out))
+    gk3, b2 = g.reshape(total, HV, K), beta.reshape(total, HV)
+    a = RecurrentGdnArgs()
+    a.q, a.k, a.v, a.beta, a.gk = rt.desc(q3), rt.desc(k3), rt.desc(v3), rt.desc(b2), rt.desc(gk3)
+    a.a_log, a.dt_bias = rt.desc(A_log if gate_mode else None), rt.desc(dt_bias if gate_mode else None)
+    a.state_in, a.state_out, a.out = rt.desc(state_in), rt.desc(state_out), rt.desc(o3)
+    a.cu_seqlens, a.state_indices, a.num_accepted_tokens = rt.desc(cu), rt.desc(idx), rt.desc(num_accepted_tokens)
+    a.scale, a.lower_bound, a.tokens_per_seq = scale, lower, T
+    a.state_v_first, a.use_qk_l2norm, a.gate_mode = int(state_v_first), int(use_qk_l2norm_in_kernel), gate_mode
+    a.beta_mode = (2 if allow_neg_eigval else 1) if use_beta_sigmoid_in_kernel else 0
+    rt.call(_OP, a, [q3, k3, v3, b2, gk3, A_log if gate_mode else None, dt_bias if gate_mode else None, state_in, state_out,
+                     o3, cu, idx, num_accepted_tokens])
+    if inplace_final_state and initial_state is not None:
+        rt.mark_mutated(state_out)
+    if tnd:
+        out = out.squeeze(0)
+    return out, (state_out if output_final_state else None)

@@ -90,14 +90,24 @@ FLA_API int fla_b200_selftest_mma(const void* a, const void* b, float* d, int M,
  *                       start index skips the sequence.  Absent: sequence n reads block n of state_in and its
  *                       final state is written to block n of state_out.
  *   num_accepted_tokens int32 [N] device, optional (needs state_indices)
+ * Per-channel gate (the reference's recurrent KDA step, aclnnRecurrentKda as bound by npu_recurrent_kda,
+ * _aclnn_ctypes.py:1298-1503; semantics fla/ops/ascendc/kda/recurrent_kda/docs/design.md:44-70):
+ *   gk     [T, HV, K] f32|bf16, optional: S <- diag(exp(gate(gk))) S before the update, where gate is the identity
+ *          (gate_mode 0), -exp(a_log[h]) softplus(gk + dt_bias[h, :]) (1) or lower_bound sigmoid(exp(a_log[h]) (gk + dt_bias)) (2)
+ *   a_log  [HV] f32, dt_bias [HV, K] f32 (optional): gate parameters for gate_mode 1 / 2
+ *   beta_mode 0: beta as given; 1: sigmoid(beta); 2: 2 sigmoid(beta)
  * K, V in {64, 128}.  No workspace. */
 typedef struct fla_recurrent_gdn_args {
   fla_tensor_t q, k, v, g, beta, state_in, state_out, out;
   fla_tensor_t cu_seqlens, state_indices, num_accepted_tokens;
+  fla_tensor_t gk, a_log, dt_bias;
   float scale;
+  float lower_bound;
   int32_t tokens_per_seq;
   int32_t state_v_first;
   int32_t use_qk_l2norm; /* normalise q and k rows as x * rsqrt(sum x^2 + 1e-6) first */
+  int32_t gate_mode;
+  int32_t beta_mode;
 } fla_recurrent_gdn_args;
 FLA_API int fla_b200_recurrent_gdn_workspace_size(const fla_recurrent_gdn_args* args, uint64_t* bytes);
 FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* args, void* workspace, uint64_t workspace_bytes,
