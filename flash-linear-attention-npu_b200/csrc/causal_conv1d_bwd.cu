@@ -1,0 +1,348 @@
+// Backward of the depthwise causal conv1d (prefill form):
+//   p[t] = bias + sum_j w[j] x[t-(W-1)+j]        y[t] = act(p[t])        gr[t] = dy[t] * act'(p[t])
+//   dx[s]  = sum_j w[j] gr[s+(W-1)-j]  (+ dht: the last W-1 inputs of a sequence are its final state)
+//   dw[j]  = sum_t gr[t] x[t-(W-1)+j]      db = sum_t gr[t]      dh0[i] = sum_{t<=i} gr[t] w[i-t]
+// Replaces the reference operator causal_conv1d_bwd (aclnnCausalConv1dBwd as bound by npu_causal_conv1d_bwd,
+// torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:988-1037; golden
+// torch_custom/fla_npu/test/test_npu_causal_conv1d_bwd.py:33-127).
+// HBM streaming like the forward: a thread owns 8 adjacent channels, walks a tile of tokens once with the input
+// and gradient windows in registers, recomputes the pre-activation (or reads it when the caller kept it) and
+// leaves its dw / db partial sums in a workspace that a second, tiny kernel reduces in a fixed order.
+#include <cuda_bf16.h>
+#include "fla_b200_internal.h"
+#include "kernel_timer.h"
+
+namespace fla {
+
+using bf16 = __nv_bfloat16;
+
+namespace {
+
+__device__ __forceinline__ void unpack8b(const uint4& raw, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __low2float(h[i]);
+    f[2 * i + 1] = __high2float(h[i]);
+  }
+}
+__device__ __forceinline__ uint4 pack8b(const float* f) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return raw;
+}
+
+struct ConvBwdParams {
+  const bf16* x; const bf16* dy; const bf16* ypre; bf16* dx;
+  const bf16* weight; const bf16* bias;
+  const bf16* init; const bf16* dht;
+  void* dh0;
+  float* part;                 // [tiles][W + 1][D] partial dw (W rows) and db (1 row)
+  const int32_t* cu_seqlens;
+  int64_t x_sb, x_st, dy_sb, dy_st, yp_sb, yp_st, dx_sb, dx_st, w_sd, w_sw;
+  int64_t i_sn, i_sd, i_sw, t_sn, t_sd, t_sw, h_sn, h_sd, h_sw;
+  int B, T, D, nseq, dh0_is_f32, tiles_per_row;
+};
+
+constexpr int kBwdTile = 256;    // tokens per CTA tile
+constexpr int kBwdThreads = 128;
+
+// derivative of SiLU at pre-activation p: s (1 + p (1 - s)), s = sigmoid(p)
+__device__ __forceinline__ float dsilu(float p) {
+  const float s = 1.f / (1.f + __expf(-p));
+  return s * (1.f + p * (1.f - s));
+}
+
+template <int W, bool SILU>
+__global__ void __launch_bounds__(kBwdThreads) conv_bwd_kernel(ConvBwdParams p) {
+  const int d0 = (blockIdx.x * kBwdThreads + threadIdx.x) * 8;
+  if (d0 >= p.D) return;
+  const int b = blockIdx.z;
+  const int s0 = blockIdx.y * kBwdTile;
+  const int s1 = min(p.T, s0 + kBwdTile);
+
+  float w[W][8], bias[8];
+#pragma unroll
+  for (int j = 0; j < W; ++j)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) w[j][c] = __bfloat162float(p.weight[(d0 + c) * p.w_sd + j * p.w_sw]);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) bias[c] = p.bias ? __bfloat162float(p.bias[d0 + c]) : 0.f;
+
+  float dw[W][8], db[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    db[c] = 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) dw[j][c] = 0.f;
+  }
+
+  int seq = b, seq_begin = 0, seq_end = p.T;
+  if (p.cu_seqlens) {
+    int lo = 0, hi = p.nseq - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.cu_seqlens[mid] <= s0) lo = mid; else hi = mid - 1;
+    }
+    seq = lo;
+    seq_begin = p.cu_seqlens[seq];
+    seq_end = p.cu_seqlens[seq + 1];
+  }
+  const bf16* xb = p.x + b * p.x_sb + d0;
+  const bf16* gb = p.dy + b * p.dy_sb + d0;
+  const bf16* yb = p.ypre ? p.ypre + b * p.yp_sb + d0 : nullptr;
+  bf16* dxb = p.dx + b * p.dx_sb + d0;
+
+  int t = s0;
+  while (t < s1) {
+    if (p.cu_seqlens) {
+      while (seq_end <= t) {
+        ++seq;
+        seq_begin = seq_end;
+        seq_end = p.cu_seqlens[seq + 1];
+      }
+    }
+    const int seg_end = min(s1, seq_end);
+    // xw[j] = x[u - (W-1) + j] while token u is processed; gw[i] = gr[u - (W-1) + i]
+    float xw[W][8], gw[W][8];
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) gw[j][c] = 0.f;
+#pragma unroll
+    for (int j = 1; j < W; ++j) {   // the W-1 inputs before token t go to xw[1 .. W-1] (shifted down at each step)
+      const int pos = t - (W - j);
+      if (pos >= seq_begin) {
+        unpack8b(*reinterpret_cast<const uint4*>(xb + pos * p.x_st), xw[j]);
+      } else {
+        const int si = (W - 1) + (pos - seq_begin);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          xw[j][c] = (p.init && si >= 0) ? __bfloat162float(p.init[seq * p.i_sn + (d0 + c) * p.i_sd + si * p.i_sw]) : 0.f;
+      }
+    }
+    float dh[W - 1][8];
+    const bool owns_start = (t == seq_begin) && p.dh0;
+#pragma unroll
+    for (int i = 0; i < W - 1; ++i)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) dh[i][c] = 0.f;
+
+    // tokens u = t .. u_stop-1 are real (their gradient is needed by the outputs of this segment);
+    // W-1 flush steps with zero gradient follow when the sequence ends inside the reach of the window
+    const int u_real_end = min(seg_end + (W - 1), seq_end);
+    const int u_stop = seg_end + (W - 1);
+    for (int u = t; u < u_stop; ++u) {
+#pragma unroll
+      for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          xw[j][c] = xw[j + 1][c];
+          gw[j][c] = gw[j + 1][c];
+        }
+      if (u < u_real_end) {
+        float g8[8];
+        unpack8b(*reinterpret_cast<const uint4*>(xb + u * p.x_st), xw[W - 1]);
+        unpack8b(*reinterpret_cast<const uint4*>(gb + u * p.dy_st), g8);
+        if constexpr (SILU) {
+          float pre[8];
+          if (yb) {
+            unpack8b(*reinterpret_cast<const uint4*>(yb + u * p.yp_st), pre);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float a = bias[c];
+#pragma unroll
+              for (int j = 0; j < W; ++j) a = fmaf(w[j][c], xw[j][c], a);
+              pre[c] = a;
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) g8[c] *= dsilu(pre[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) gw[W - 1][c] = g8[c];
+        if (u < seg_end) {   // tokens of this segment own their dw / db contributions
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            db[c] += g8[c];
+#pragma unroll
+            for (int j = 0; j < W; ++j) dw[j][c] = fmaf(g8[c], xw[j][c], dw[j][c]);
+          }
+          if (owns_start) {
+            const int rel = u - seq_begin;   // dh0[i] += gr[rel] w[i - rel], i >= rel
+#pragma unroll
+            for (int i = 0; i < W - 1; ++i)
+              if (rel <= i) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                  float wv = 0.f;
+#pragma unroll
+                  for (int j = 0; j < W - 1; ++j) wv = (j == i - rel) ? w[j][c] : wv;
+                  dh[i][c] = fmaf(g8[c], wv, dh[i][c]);
+                }
+              }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) gw[W - 1][c] = 0.f;
+      }
+      const int s = u - (W - 1);   // dx[s] = sum_i w[W-1-i] gr[s+i] is complete now
+      if (s >= t && s < seg_end) {
+        float o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float a = 0.f;
+#pragma unroll
+          for (int i = 0; i < W; ++i) a = fmaf(w[W - 1 - i][c], gw[i][c], a);
+          o[c] = a;
+        }
+        const int ti = s - (seq_end - (W - 1));   // index into the final state when s is one of the last W-1 inputs
+        if (p.dht && ti >= 0) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) o[c] += __bfloat162float(p.dht[seq * p.t_sn + (d0 + c) * p.t_sd + ti * p.t_sw]);
+        }
+        *reinterpret_cast<uint4*>(dxb + s * p.dx_st) = pack8b(o);
+      }
+    }
+    if (owns_start) {
+      const int len = seq_end - seq_begin;
+#pragma unroll
+      for (int i = 0; i < W - 1; ++i) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float v = dh[i][c];
+          // a sequence shorter than W-1 hands part of its initial state on to the final state
+          const int ti = i - len;
+          if (p.dht && len < W - 1 && ti >= 0) v += __bfloat162float(p.dht[seq * p.t_sn + (d0 + c) * p.t_sd + ti * p.t_sw]);
+          const int64_t off = seq * p.h_sn + (d0 + c) * p.h_sd + i * p.h_sw;
+          if (p.dh0_is_f32) static_cast<float*>(p.dh0)[off] = v;
+          else static_cast<bf16*>(p.dh0)[off] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+    t = seg_end;
+  }
+
+  float* dst = p.part + (int64_t(b) * p.tiles_per_row + blockIdx.y) * (W + 1) * p.D + d0;
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    *reinterpret_cast<float4*>(dst + j * p.D) = make_float4(dw[j][0], dw[j][1], dw[j][2], dw[j][3]);
+    *reinterpret_cast<float4*>(dst + j * p.D + 4) = make_float4(dw[j][4], dw[j][5], dw[j][6], dw[j][7]);
+  }
+  *reinterpret_cast<float4*>(dst + W * p.D) = make_float4(db[0], db[1], db[2], db[3]);
+  *reinterpret_cast<float4*>(dst + W * p.D + 4) = make_float4(db[4], db[5], db[6], db[7]);
+}
+
+struct ConvBwdReduceParams {
+  const float* part; float* dw; float* db;
+  int64_t dw_sd, dw_sw;
+  int tiles, W, D;
+};
+
+__global__ void conv_bwd_reduce_kernel(ConvBwdReduceParams p) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  const int j = blockIdx.y;   // 0 .. W-1: dw tap, W: db
+  if (d >= p.D) return;
+  float acc = 0.f;
+  for (int t = 0; t < p.tiles; ++t) acc += p.part[(int64_t(t) * (p.W + 1) + j) * p.D + d];
+  if (j < p.W) p.dw[d * p.dw_sd + j * p.dw_sw] = acc;
+  else if (p.db) p.db[d] = acc;
+}
+
+inline bool vec_ok3(const fla_tensor_t& t) {
+  return t.stride[2] == 1 && aligned16(t.data) && t.stride[1] % 8 == 0 && t.stride[0] % 8 == 0;
+}
+
+int bwd_tiles(const fla_causal_conv1d_bwd_args* a) {
+  return int((a->x.shape[1] + kBwdTile - 1) / kBwdTile);
+}
+
+}  // namespace
+}  // namespace fla
+
+using namespace fla;
+
+extern "C" FLA_API int fla_b200_causal_conv1d_bwd_workspace_size(const fla_causal_conv1d_bwd_args* a, uint64_t* bytes) {
+  if (!a || !bytes) return FLA_ERR_NULL;
+  if (!a->x.data || a->x.ndim != 3 || !a->weight.data || a->weight.ndim != 2) return FLA_ERR_SHAPE;
+  const int64_t B = a->x.shape[0], D = a->x.shape[2], W = a->weight.shape[1];
+  *bytes = uint64_t(B) * bwd_tiles(a) * (W + 1) * D * 4;
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_causal_conv1d_bwd(const fla_causal_conv1d_bwd_args* a, void* workspace,
+                                                  uint64_t workspace_bytes, void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  const fla_tensor_t &x = a->x, &dy = a->dy, &dx = a->dx, &w = a->weight, &dw = a->dw;
+  if (!x.data || !dy.data || !dx.data || !w.data || !dw.data) return FLA_ERR_NULL;
+  if (x.ndim != 3 || dy.ndim != 3 || dx.ndim != 3 || w.ndim != 2 || dw.ndim != 2) return FLA_ERR_SHAPE;
+  if (x.dtype != FLA_BF16 || dy.dtype != FLA_BF16 || dx.dtype != FLA_BF16 || w.dtype != FLA_BF16 || dw.dtype != FLA_F32)
+    return FLA_ERR_DTYPE;
+  const int64_t B = x.shape[0], T = x.shape[1], D = x.shape[2], W = w.shape[1];
+  if (w.shape[0] != D || dw.shape[0] != D || dw.shape[1] != W || W < 2 || W > 4 || D % 8 || B <= 0 || T <= 0) return FLA_ERR_SHAPE;
+  for (int i = 0; i < 3; ++i)
+    if (dy.shape[i] != x.shape[i] || dx.shape[i] != x.shape[i]) return FLA_ERR_SHAPE;
+  if (!vec_ok3(x) || !vec_ok3(dy) || !vec_ok3(dx)) return FLA_ERR_LAYOUT;
+  int nseq = int(B);
+  if (a->cu_seqlens.data) {
+    if (B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    nseq = int(a->cu_seqlens.shape[0] - 1);
+  }
+  ConvBwdParams p{};
+  p.x = static_cast<const bf16*>(x.data); p.dy = static_cast<const bf16*>(dy.data); p.dx = static_cast<bf16*>(dx.data);
+  p.weight = static_cast<const bf16*>(w.data);
+  p.x_sb = x.stride[0]; p.x_st = x.stride[1]; p.dy_sb = dy.stride[0]; p.dy_st = dy.stride[1];
+  p.dx_sb = dx.stride[0]; p.dx_st = dx.stride[1]; p.w_sd = w.stride[0]; p.w_sw = w.stride[1];
+  if (a->y_pre.data) {
+    const fla_tensor_t& y = a->y_pre;
+    if (y.ndim != 3 || y.dtype != FLA_BF16 || !vec_ok3(y)) return FLA_ERR_LAYOUT;
+    for (int i = 0; i < 3; ++i)
+      if (y.shape[i] != x.shape[i]) return FLA_ERR_SHAPE;
+    p.ypre = static_cast<const bf16*>(y.data); p.yp_sb = y.stride[0]; p.yp_st = y.stride[1];
+  }
+  if (a->bias.data) {
+    if (a->bias.ndim != 1 || a->bias.shape[0] != D || a->bias.dtype != FLA_BF16 || a->bias.stride[0] != 1) return FLA_ERR_SHAPE;
+    p.bias = static_cast<const bf16*>(a->bias.data);
+  }
+  float* db = nullptr;
+  if (a->db.data) {
+    if (a->db.ndim != 1 || a->db.shape[0] != D || a->db.dtype != FLA_F32 || a->db.stride[0] != 1) return FLA_ERR_SHAPE;
+    db = static_cast<float*>(a->db.data);
+  }
+  for (int which = 0; which < 3; ++which) {
+    const fla_tensor_t& s = which == 0 ? a->initial_state : which == 1 ? a->dht : a->dh0;
+    if (!s.data) continue;
+    if (s.ndim != 3 || s.shape[0] != nseq || s.shape[1] != D || s.shape[2] != W - 1) return FLA_ERR_SHAPE;
+    if (which < 2 && s.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+    if (which == 2 && s.dtype != FLA_BF16 && s.dtype != FLA_F32) return FLA_ERR_DTYPE;
+    if (which == 0) { p.init = static_cast<const bf16*>(s.data); p.i_sn = s.stride[0]; p.i_sd = s.stride[1]; p.i_sw = s.stride[2]; }
+    else if (which == 1) { p.dht = static_cast<const bf16*>(s.data); p.t_sn = s.stride[0]; p.t_sd = s.stride[1]; p.t_sw = s.stride[2]; }
+    else { p.dh0 = s.data; p.h_sn = s.stride[0]; p.h_sd = s.stride[1]; p.h_sw = s.stride[2]; p.dh0_is_f32 = s.dtype == FLA_F32; }
+  }
+  p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+  const int tiles = bwd_tiles(a);
+  p.B = int(B); p.T = int(T); p.D = int(D); p.nseq = nseq; p.tiles_per_row = tiles;
+  const uint64_t need = uint64_t(B) * tiles * (W + 1) * D * 4;
+  if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
+  p.part = static_cast<float*>(workspace);
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid(unsigned((D / 8 + kBwdThreads - 1) / kBwdThreads), unsigned(tiles), unsigned(B));
+  {
+    KernelTimer kt("causal_conv1d_bwd", st);
+    const bool silu = a->activation_silu != 0;
+#define FLA_LAUNCH_BWD(WW)                                                        \
+  if (silu) conv_bwd_kernel<WW, true><<<grid, kBwdThreads, 0, st>>>(p);           \
+  else conv_bwd_kernel<WW, false><<<grid, kBwdThreads, 0, st>>>(p);
+    if (W == 4) { FLA_LAUNCH_BWD(4) } else if (W == 3) { FLA_LAUNCH_BWD(3) } else { FLA_LAUNCH_BWD(2) }
+#undef FLA_LAUNCH_BWD
+  }
+  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  ConvBwdReduceParams r{p.part, static_cast<float*>(dw.data), db, dw.stride[0], dw.stride[1], int(B) * tiles, int(W), int(D)};
+  conv_bwd_reduce_kernel<<<dim3(unsigned((D + 255) / 256), unsigned(W + 1)), 256, 0, st>>>(r);
+  return cuda_status(cudaGetLastError());
+}

@@ -1,6 +1,7 @@
 """Operator surface.  Every function launches hand-written sm_100a kernels through the C ABI;
 nothing here computes on the CPU or through PyTorch math."""
-from .conv import causal_conv1d, causal_conv1d_update, npu_causal_conv1d  # noqa: F401
+from .conv import (causal_conv1d, causal_conv1d_bwd, causal_conv1d_update, npu_causal_conv1d,  # noqa: F401
+                   npu_causal_conv1d_bwd)
 from .gdn import (chunk_gated_delta_rule, chunk_gated_delta_rule_bwd, chunk_gated_delta_rule_fwd_bwd,  # noqa: F401
                   ChunkGatedDeltaRuleFunction)
 from .kda import chunk_kda, chunk_kda_fwd_bwd, kda_chunk_bwd  # noqa: F401

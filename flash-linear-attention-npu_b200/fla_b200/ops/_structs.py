@@ -18,6 +18,11 @@ class CausalConv1dFwdArgs(ctypes.Structure):
                                            "cu_seqlens")] + [("activation_silu", ctypes.c_int32)]
 
 
+class CausalConv1dBwdArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("x", "weight", "bias", "dy", "y_pre", "initial_state", "dht", "dx", "dw", "db",
+                                           "dh0", "cu_seqlens")] + [("activation_silu", ctypes.c_int32)]
+
+
 class CausalConv1dUpdateArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("x", "weight", "bias", "residual", "conv_state", "y", "cache_indices",
                                            "num_accepted_tokens")] + [

@@ -134,6 +134,24 @@ FLA_API int fla_b200_causal_conv1d_fwd_workspace_size(const fla_causal_conv1d_fw
 FLA_API int fla_b200_causal_conv1d_fwd(const fla_causal_conv1d_fwd_args* args, void* workspace,
                                        uint64_t workspace_bytes, void* stream);
 
+/* causal_conv1d backward (prefill form).
+ * Replaces aclnnCausalConv1dBwd as bound by npu_causal_conv1d_bwd
+ * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:988-1037; golden
+ * torch_custom/fla_npu/test/test_npu_causal_conv1d_bwd.py:33-127).
+ *   x, dy, dx [B, T, D] bf16;  weight [D, W] bf16 (any strides);  bias [D] bf16 optional (enters the recomputed
+ *   pre-activation);  y_pre [B, T, D] bf16 optional: the forward's pre-activation, read instead of recomputed;
+ *   initial_state, dht [N, D, W-1] bf16 optional (gradient of the final state);  dw [D, W] f32 (any strides);
+ *   db [D] f32 optional;  dh0 [N, D, W-1] bf16|f32 optional;  cu_seqlens as in the forward.
+ * Workspace: per-tile partial sums of dw / db (reduced in a fixed order: results are deterministic). */
+typedef struct fla_causal_conv1d_bwd_args {
+  fla_tensor_t x, weight, bias, dy, y_pre, initial_state, dht;
+  fla_tensor_t dx, dw, db, dh0, cu_seqlens;
+  int32_t activation_silu;
+} fla_causal_conv1d_bwd_args;
+FLA_API int fla_b200_causal_conv1d_bwd_workspace_size(const fla_causal_conv1d_bwd_args* args, uint64_t* bytes);
+FLA_API int fla_b200_causal_conv1d_bwd(const fla_causal_conv1d_bwd_args* args, void* workspace,
+                                       uint64_t workspace_bytes, void* stream);
+
 /* causal_conv1d decode update: consumes T new tokens per sequence and shifts conv_state in place.
  * Replaces aclnnCausalConv1d with run_mode = 1 (same binding as above; kernel
  * fla/ops/ascendc/gdn/gdn_preprocess/causal_conv1d/op_kernel/causal_conv1d_update.h).

@@ -12,5 +12,6 @@ committed fixtures under tests/golden/, and tests/test_oracle_golden.py replays 
 from .gdn import naive_recurrent_gated_delta_rule, gdn_reference_fwd_bwd, chunk_gated_delta_rule_restated  # noqa: F401
 from .kda import naive_recurrent_kda, kda_reference_fwd_bwd  # noqa: F401
 from .recurrent import recurrent_gated_delta_rule_golden  # noqa: F401
-from .conv import causal_conv1d_ref, causal_conv1d_update_ref, causal_conv1d_update_spec_ref  # noqa: F401
+from .conv import (causal_conv1d_bwd_ref, causal_conv1d_ref, causal_conv1d_update_ref,  # noqa: F401
+                   causal_conv1d_update_spec_ref)
 from .inputs import make_gdn_inputs, make_kda_inputs, make_decode_inputs, make_conv_inputs  # noqa: F401

@@ -66,3 +66,24 @@ def causal_conv1d_update_spec_ref(x, conv_state, weight, bias=None, num_accepted
         conv_state_f[s, :, keep:keep + seqlen] = x[s]
     conv_state.copy_(conv_state_f.to(conv_state.dtype))
     return out.to(dtype=dtype_in)
+
+
+def causal_conv1d_bwd_ref(x, weight, dy, bias=None, initial_state=None, dht=None, activation=0, dtype=torch.float64):
+    """Gradients of the prefill conv by autograd through its definition, in the reference operator's layouts
+    (golden torch_custom/fla_npu/test/test_npu_causal_conv1d_bwd.py:33-127, which writes the same sums out by hand):
+    x, dy `[B,T,D]`; weight `[W,D]`; initial_state / dht `[B,W,D]` whose rows 1..W-1 are the W-1 stored inputs.
+    Returns dx `[B,T,D]`, dw `[W,D]`, db `[D]`, dh0 `[B,W,D]` (row 0 zero) in `dtype`."""
+    B, T, D = x.shape
+    W = weight.shape[0]
+    xf = x.to(dtype).clone().requires_grad_(True)
+    wf = weight.to(dtype).clone().requires_grad_(True)
+    bf = (torch.zeros(D) if bias is None else bias).to(dtype).clone().requires_grad_(True)
+    init = (torch.zeros(B, W, D) if initial_state is None else initial_state).to(dtype).clone().requires_grad_(True)
+    xe = torch.cat([init[:, 1:, :], xf], dim=1)                       # [B, W-1+T, D]
+    pre = bf + sum(wf[j] * xe[:, j:j + T, :] for j in range(W))
+    out = F.silu(pre) if activation else pre
+    loss = (out * dy.to(dtype)).sum()
+    if dht is not None:
+        loss = loss + (xe[:, T:, :] * dht.to(dtype)[:, 1:, :]).sum()   # final state = the last W-1 inputs
+    loss.backward()
+    return xf.grad, wf.grad, bf.grad, init.grad

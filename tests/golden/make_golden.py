@@ -84,6 +84,24 @@ def decode_fixture():
                         out_acc=f32(out), state_acc=f32(fs), out=f32(out2), state_out=f32(fs2))
 
 
+def conv_bwd_fixture():
+    ns = extract(REF / "torch_custom/fla_npu/test/test_npu_causal_conv1d_bwd.py",
+                 ["causal_conv1d_preactivation_ref", "causal_conv1d_bwd_ref"])
+    g_ = torch.Generator().manual_seed(23)
+    B, T, D, W = 2, 19, 24, 4
+    x = torch.randn(B, T, D, generator=g_)
+    w = 0.5 * torch.randn(W, D, generator=g_)
+    dy = torch.randn(B, T, D, generator=g_)
+    init = torch.randn(B, W, D, generator=g_)
+    dht = torch.randn(B, W, D, generator=g_)
+    out = {}
+    for name, act, i0, dh in (("plain", 0, None, None), ("silu_state", 1, init, dht)):
+        pre = ns["causal_conv1d_preactivation_ref"](x, w, i0)
+        dx, dw, db, dh0 = ns["causal_conv1d_bwd_ref"](x, pre, w, dy, i0, dh, act, cast_reduction_outputs=False)
+        out.update({f"{name}_dx": f32(dx), f"{name}_dw": f32(dw), f"{name}_db": f32(db), f"{name}_dh0": f32(dh0)})
+    np.savez_compressed(HERE / "conv_bwd_golden.npz", x=f32(x), w=f32(w), dy=f32(dy), init=f32(init), dht=f32(dht), **out)
+
+
 def conv_fixture():
     ns = extract(REF / "torch_custom/fla_npu/test/test_npu_causal_conv1d.py",
                  ["causal_conv1d_ref", "causal_conv1d_update_ref", "causal_conv1d_update_spec_ref"])
@@ -133,6 +151,7 @@ if __name__ == "__main__":
     gdn_fixture()
     decode_fixture()
     conv_fixture()
+    conv_bwd_fixture()
     kda_fixture()
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)

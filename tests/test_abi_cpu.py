@@ -53,6 +53,7 @@ def _c_struct_fields(name):
 @pytest.mark.parametrize("cname,pyname", [("fla_recurrent_gdn_args", "RecurrentGdnArgs"),
                                           ("fla_causal_conv1d_fwd_args", "CausalConv1dFwdArgs"),
                                           ("fla_causal_conv1d_update_args", "CausalConv1dUpdateArgs"),
+                                          ("fla_causal_conv1d_bwd_args", "CausalConv1dBwdArgs"),
                                           ("fla_gdn_chunk_fwd_args", "GdnChunkFwdArgs"),
                                           ("fla_gdn_chunk_bwd_args", "GdnChunkBwdArgs"),
                                           ("fla_kda_chunk_fwd_args", "KdaChunkFwdArgs"),

@@ -86,3 +86,13 @@ def test_kda_naive_matches_reference():
                                        initial_state=f["h0"].transpose(-1, -2))
     _close(o, f["o"])
     _close(ht.transpose(-1, -2), f["ht"])
+
+
+def test_conv_backward_golden_matches_reference():
+    f = _load("conv_bwd_golden.npz")
+    for name, act, init, dht in (("plain", 0, None, None), ("silu_state", 1, f["init"], f["dht"])):
+        dx, dw, db, dh0 = oracle.causal_conv1d_bwd_ref(f["x"], f["w"], f["dy"], None, init, dht, act)
+        for n, got in (("dx", dx), ("dw", dw), ("db", db)):
+            torch.testing.assert_close(got.float(), f[f"{name}_{n}"], rtol=2e-5, atol=2e-5)
+        if init is not None:
+            torch.testing.assert_close(dh0.float(), f[f"{name}_dh0"], rtol=2e-5, atol=2e-5)
