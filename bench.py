@@ -12,6 +12,7 @@ distributions of BASELINE.json.  Workloads (the default is the one the headline 
   decode         config 4: causal_conv1d_update + fused-recurrent GDN, 256 sequences x 1 token, fp32 state pool,
                  one CUDA graph replay per step
   conv_prefill   the conv half of config 1 alone
+  conv_bwd       backward of that conv (dx, dw, db from x, dy; SiLU pre-activation recomputed)
 With N > 1 every rank (one process per GPU, launched by torch.distributed.run) processes its own batch of that
 shape (weak scaling; the path has no exchange step, so there is no collective on the data path); NCCL carries only
 the barrier and the max-over-ranks reduction of the measured time.  Rank 0 prints ONE JSON line.
@@ -39,7 +40,7 @@ sys.path.insert(0, str(REPO / "flash-linear-attention-npu_b200"))
 sys.path.insert(0, str(REPO))
 
 DEFAULT_WORKLOAD = "gdn_fwd_bwd"
-WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "decode", "conv_prefill"]
+WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "decode", "conv_prefill", "conv_bwd"]
 FWD_FLOP_PER_TOKEN_HEAD = 182955.0      # KK^T, inverse, w/u, state, output (dense 64x64 tiles, no causal credit)
 BWD_FLOP_PER_TOKEN_HEAD = 524288.0
 
@@ -59,7 +60,7 @@ KERNEL_FLOPS = {
 KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
                  "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "kda_bwd_dhu": "kda_bwd_dhu_kernel", "kda_bwd_par": "kda_bwd_par_kernel", "gdn_prep": "gdn_prep_kernel", "tri_inverse": "tri_inverse_kernel",
                  "recurrent_gdn": "recurrent_gdn_kernel", "causal_conv1d_fwd": "conv_fwd_kernel",
-                 "causal_conv1d_update": "conv_update1_kernel"}
+                 "causal_conv1d_update": "conv_update1_kernel", "causal_conv1d_bwd": "conv_bwd_kernel"}
 
 
 def _peaks():
@@ -123,7 +124,7 @@ class Workload:
     def __init__(self, name, shape):
         self.name = name
         self.graph = None
-        if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill"):
+        if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill", "conv_bwd"):
             self.cfg = dict(B=8, T=4096, HK=16, HV=32, K=128, V=128, D=8192, W=4)
         elif name in ("kda_fwd", "kda_fwd_bwd"):
             self.cfg = dict(B=4, T=8192, HK=32, HV=32, K=128, V=128)
@@ -161,8 +162,10 @@ class Workload:
             d["dht"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
         if self.name == "kda_fwd_bwd":
             d["do"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
-        if self.name in ("gdn_fwd_conv", "conv_prefill"):
+        if self.name in ("gdn_fwd_conv", "conv_prefill", "conv_bwd"):
             d["x"] = rn(c["B"], c["T"], c["D"]).bfloat16()
+        if self.name == "conv_bwd":
+            d["dy"] = rn(c["B"], c["T"], c["D"]).bfloat16()
         if self.name == "decode":
             d["q"] = F.normalize(rn(c["N"], 1, c["HK"], c["K"]), dim=-1).bfloat16()
             d["k"] = F.normalize(rn(c["N"], 1, c["HK"], c["K"]), dim=-1).bfloat16()
@@ -183,7 +186,7 @@ class Workload:
                 "kda_fwd": ["q", "k", "v", "g", "beta"],
                 "kda_fwd_bwd": ["q", "k", "v", "g", "beta", "do"],
                 "decode": ["q", "k", "v", "g", "beta", "x"],
-                "conv_prefill": ["x"]}[self.name]
+                "conv_prefill": ["x"], "conv_bwd": ["x", "dy"]}[self.name]
 
     def step(self, d):
         """One pass through the public Python API.  Returns the tensors a caller reads back."""
@@ -207,6 +210,8 @@ class Workload:
             return (o, ht) + tuple(x for x in grads if x is not None)
         if n == "conv_prefill":
             return ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")[:1]
+        if n == "conv_bwd":
+            return ops.causal_conv1d_bwd(d["x"], d["w"], d["dy"], d["bias"], activation="silu")[:3]
         y = ops.causal_conv1d_update(d["x"], d["conv_state"], weight=d["w"], bias=d["bias"], activation="silu")
         o, _ = ops.fused_recurrent_gated_delta_rule(d["q"], d["k"], d["v"], g=d["g"], beta=d["beta"],
                                                     initial_state=d["state"], inplace_final_state=True)
@@ -226,14 +231,14 @@ class Workload:
         return self.graph_out
 
     def launches_per_step(self):
-        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1}[self.name]
+        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1, "conv_bwd": 2}[self.name]
 
     def kernel_names(self):
         return {"gdn_fwd_bwd": ["gdn_prep", "tri_inverse", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
                 "gdn_fwd_conv": ["causal_conv1d_fwd", "gdn_prep", "tri_inverse", "gdn_fwd"],
                 "kda_fwd": ["kda_prep", "tri_inverse", "kda_fwd"],
                 "kda_fwd_bwd": ["kda_prep", "tri_inverse", "kda_fwd", "kda_bwd_dhu", "kda_bwd_par"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
-                "conv_prefill": ["causal_conv1d_fwd"]}[self.name]
+                "conv_prefill": ["causal_conv1d_fwd"], "conv_bwd": ["causal_conv1d_bwd"]}[self.name]
 
     def kernel_work(self, kname):
         """(bound, algorithmic work per launch, unit) of one kernel at this workload's shape."""
@@ -246,6 +251,8 @@ class Workload:
             return "hbm", 2.0 * n * c["HV"] * c["K"] * c["V"] * 4 + act, "GB/s"
         if kname == "causal_conv1d_fwd":  # x read + y write
             return "hbm", 2.0 * c["B"] * c["T"] * c["D"] * 2, "GB/s"
+        if kname == "causal_conv1d_bwd":  # x, dy read + dx write
+            return "hbm", 3.0 * c["B"] * c["T"] * c["D"] * 2, "GB/s"
         if kname == "causal_conv1d_update":  # state read + write, x read, y write
             return "hbm", (2.0 * c["N"] * c["D"] * (c["W"] - 1) + 2.0 * c["N"] * c["D"]) * 2, "GB/s"
         raise KeyError(kname)
@@ -301,6 +308,12 @@ def cpu_reference(wl: Workload, threads: int, steps: int = 1, warmup: int = 0):
                                                   do=inp.get("do"))
         tokens, desc = Ts, f"B=1 T={Ts} H={c['HV']} K=V=128 fp32 naive KDA recurrence" + (
             " + autograd" if wl.name == "kda_fwd_bwd" else "")
+    elif wl.name == "conv_bwd":
+        Ts = 2048
+        xs, w = torch.randn(1, Ts, c["D"]), 0.5 * torch.randn(c["W"], c["D"])
+        dys = torch.randn(1, Ts, c["D"])
+        fn = lambda: oracle.causal_conv1d_bwd_ref(xs, w, dys, None, None, None, 1, dtype=torch.float32)  # noqa: E731
+        tokens, desc = Ts, f"B=1 T={Ts} D={c['D']} W=4 autograd through the conv definition"
     elif wl.name == "conv_prefill":
         Ts = 4096
         xs, w = torch.randn(1, c["D"], Ts), 0.5 * torch.randn(c["D"], c["W"])

@@ -46,17 +46,44 @@ struct ConvBwdParams {
   int B, T, D, nseq, dh0_is_f32, tiles_per_row;
 };
 
-constexpr int kBwdTile = 256;    // tokens per CTA tile
+constexpr int kBwdTile = 128;    // tokens per CTA tile
 constexpr int kBwdThreads = 128;
 
 // derivative of SiLU at pre-activation p: s (1 + p (1 - s)), s = sigmoid(p)
 __device__ __forceinline__ float dsilu(float p) {
-  const float s = 1.f / (1.f + __expf(-p));
-  return s * (1.f + p * (1.f - s));
+  float t;   // sigmoid(p) = 0.5 (1 + tanh(p / 2)): one MUFU op
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * p));
+  const float s = fmaf(0.5f, t, 0.5f);
+  return s * fmaf(p, 1.f - s, 1.f);
+}
+
+constexpr int kBwdGroup = 4;     // tokens per inner step: their loads are issued together
+
+// weight element (d, j) at w[d * wsd + j * wsw]; taps of 8 channels starting at d0
+template <int W>
+__device__ __forceinline__ void load_taps(const bf16* w, int64_t wsd, int64_t wsw, int d0, float (&out)[W][8]) {
+  if (wsd == 1 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && wsw % 8 == 0) {  // [W, D]: channels contiguous
+#pragma unroll
+    for (int j = 0; j < W; ++j) unpack8b(*reinterpret_cast<const uint4*>(w + j * wsw + d0), out[j]);
+  } else if (wsw == 1 && wsd == W && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    float flat[W * 8];   // [D, W] dense: the 8 channels' taps are W consecutive 16-byte vectors
+#pragma unroll
+    for (int j = 0; j < W; ++j) unpack8b(*reinterpret_cast<const uint4*>(w + int64_t(d0) * W + j * 8), flat + j * 8);
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+      for (int j = 0; j < W; ++j) out[j][c] = flat[c * W + j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) out[j][c] = __bfloat162float(w[(d0 + c) * wsd + j * wsw]);
+  }
 }
 
 template <int W, bool SILU>
-__global__ void __launch_bounds__(kBwdThreads) conv_bwd_kernel(ConvBwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams p) {
+  constexpr int G = kBwdGroup;
   const int d0 = (blockIdx.x * kBwdThreads + threadIdx.x) * 8;
   if (d0 >= p.D) return;
   const int b = blockIdx.z;
@@ -64,12 +91,12 @@ __global__ void __launch_bounds__(kBwdThreads) conv_bwd_kernel(ConvBwdParams p) 
   const int s1 = min(p.T, s0 + kBwdTile);
 
   float w[W][8], bias[8];
+  load_taps<W>(p.weight, p.w_sd, p.w_sw, d0, w);
+  if (p.bias) unpack8b(*reinterpret_cast<const uint4*>(p.bias + d0), bias);
+  else {
 #pragma unroll
-  for (int j = 0; j < W; ++j)
-#pragma unroll
-    for (int c = 0; c < 8; ++c) w[j][c] = __bfloat162float(p.weight[(d0 + c) * p.w_sd + j * p.w_sw]);
-#pragma unroll
-  for (int c = 0; c < 8; ++c) bias[c] = p.bias ? __bfloat162float(p.bias[d0 + c]) : 0.f;
+    for (int c = 0; c < 8; ++c) bias[c] = 0.f;
+  }
 
   float dw[W][8], db[8];
 #pragma unroll
@@ -95,6 +122,18 @@ __global__ void __launch_bounds__(kBwdThreads) conv_bwd_kernel(ConvBwdParams p) 
   const bf16* yb = p.ypre ? p.ypre + b * p.yp_sb + d0 : nullptr;
   bf16* dxb = p.dx + b * p.dx_sb + d0;
 
+  // input at position pos of the current sequence (initial state or zero before its first token)
+  auto input_at = [&](int pos, float* out) {
+    if (pos >= seq_begin) {
+      unpack8b(*reinterpret_cast<const uint4*>(xb + pos * p.x_st), out);
+    } else {
+      const int si = (W - 1) + (pos - seq_begin);
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        out[c] = (p.init && si >= 0) ? __bfloat162float(p.init[seq * p.i_sn + (d0 + c) * p.i_sd + si * p.i_sw]) : 0.f;
+    }
+  };
+
   int t = s0;
   while (t < s1) {
     if (p.cu_seqlens) {
@@ -105,111 +144,123 @@ __global__ void __launch_bounds__(kBwdThreads) conv_bwd_kernel(ConvBwdParams p) 
       }
     }
     const int seg_end = min(s1, seq_end);
-    // xw[j] = x[u - (W-1) + j] while token u is processed; gw[i] = gr[u - (W-1) + i]
-    float xw[W][8], gw[W][8];
-#pragma unroll
-    for (int j = 0; j < W; ++j)
-#pragma unroll
-      for (int c = 0; c < 8; ++c) gw[j][c] = 0.f;
-#pragma unroll
-    for (int j = 1; j < W; ++j) {   // the W-1 inputs before token t go to xw[1 .. W-1] (shifted down at each step)
-      const int pos = t - (W - j);
-      if (pos >= seq_begin) {
-        unpack8b(*reinterpret_cast<const uint4*>(xb + pos * p.x_st), xw[j]);
-      } else {
-        const int si = (W - 1) + (pos - seq_begin);
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          xw[j][c] = (p.init && si >= 0) ? __bfloat162float(p.init[seq * p.i_sn + (d0 + c) * p.i_sd + si * p.i_sw]) : 0.f;
-      }
-    }
-    float dh[W - 1][8];
-    const bool owns_start = (t == seq_begin) && p.dh0;
-#pragma unroll
-    for (int i = 0; i < W - 1; ++i)
-#pragma unroll
-      for (int c = 0; c < 8; ++c) dh[i][c] = 0.f;
-
-    // tokens u = t .. u_stop-1 are real (their gradient is needed by the outputs of this segment);
-    // W-1 flush steps with zero gradient follow when the sequence ends inside the reach of the window
+    // Tokens u = t .. u_real_end-1 are read (the outputs of this segment need the gradients of the W-1 tokens after
+    // it); steps up to u_stop-1 flush the window with zero gradient when the sequence ends first.
     const int u_real_end = min(seg_end + (W - 1), seq_end);
     const int u_stop = seg_end + (W - 1);
-    for (int u = t; u < u_stop; ++u) {
+    // xs[i + j] = x[u - (W-1) + j] and gs[i + k] = gr[u - (W-1) + k] while token u = ug + i is processed
+    float xs[W - 1 + G][8], gs[W - 1 + G][8];
 #pragma unroll
-      for (int j = 0; j < W - 1; ++j)
+    for (int j = 0; j < W - 1; ++j) {
+      input_at(t - (W - 1) + j, xs[j]);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          xw[j][c] = xw[j + 1][c];
-          gw[j][c] = gw[j + 1][c];
-        }
-      if (u < u_real_end) {
+      for (int c = 0; c < 8; ++c) gs[j][c] = 0.f;
+    }
+    for (int ug = t; ug < u_stop; ug += G) {
+      uint4 xin[G], gin[G], yin[G];
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const bool valid = ug + i < u_real_end;
+        xin[i] = valid ? *reinterpret_cast<const uint4*>(xb + (ug + i) * p.x_st) : make_uint4(0, 0, 0, 0);
+        gin[i] = valid ? *reinterpret_cast<const uint4*>(gb + (ug + i) * p.dy_st) : make_uint4(0, 0, 0, 0);
+        if (SILU && yb) yin[i] = valid ? *reinterpret_cast<const uint4*>(yb + (ug + i) * p.yp_st) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const int u = ug + i;
         float g8[8];
-        unpack8b(*reinterpret_cast<const uint4*>(xb + u * p.x_st), xw[W - 1]);
-        unpack8b(*reinterpret_cast<const uint4*>(gb + u * p.dy_st), g8);
+        unpack8b(xin[i], xs[W - 1 + i]);
+        unpack8b(gin[i], g8);
         if constexpr (SILU) {
           float pre[8];
           if (yb) {
-            unpack8b(*reinterpret_cast<const uint4*>(yb + u * p.yp_st), pre);
+            unpack8b(yin[i], pre);
           } else {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
               float a = bias[c];
 #pragma unroll
-              for (int j = 0; j < W; ++j) a = fmaf(w[j][c], xw[j][c], a);
+              for (int j = 0; j < W; ++j) a = fmaf(w[j][c], xs[i + j][c], a);
               pre[c] = a;
             }
           }
 #pragma unroll
-          for (int c = 0; c < 8; ++c) g8[c] *= dsilu(pre[c]);
+          for (int c = 0; c < 8; ++c) g8[c] *= dsilu(pre[c]);   // zero beyond the last real token: its dy was read as 0
         }
 #pragma unroll
-        for (int c = 0; c < 8; ++c) gw[W - 1][c] = g8[c];
+        for (int c = 0; c < 8; ++c) gs[W - 1 + i][c] = g8[c];
         if (u < seg_end) {   // tokens of this segment own their dw / db contributions
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             db[c] += g8[c];
 #pragma unroll
-            for (int j = 0; j < W; ++j) dw[j][c] = fmaf(g8[c], xw[j][c], dw[j][c]);
-          }
-          if (owns_start) {
-            const int rel = u - seq_begin;   // dh0[i] += gr[rel] w[i - rel], i >= rel
-#pragma unroll
-            for (int i = 0; i < W - 1; ++i)
-              if (rel <= i) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                  float wv = 0.f;
-#pragma unroll
-                  for (int j = 0; j < W - 1; ++j) wv = (j == i - rel) ? w[j][c] : wv;
-                  dh[i][c] = fmaf(g8[c], wv, dh[i][c]);
-                }
-              }
+            for (int j = 0; j < W; ++j) dw[j][c] = fmaf(g8[c], xs[i + j][c], dw[j][c]);
           }
         }
-      } else {
+        const int s = u - (W - 1);   // dx[s] = sum_k w[W-1-k] gr[s+k] is complete now
+        if (s >= t && s < seg_end) {
+          float o[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) gw[W - 1][c] = 0.f;
+          for (int c = 0; c < 8; ++c) {
+            float a = 0.f;
+#pragma unroll
+            for (int k = 0; k < W; ++k) a = fmaf(w[W - 1 - k][c], gs[i + k][c], a);
+            o[c] = a;
+          }
+          const int ti = s - (seq_end - (W - 1));   // index into the final state when s is one of the last W-1 inputs
+          if (p.dht && ti >= 0) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) o[c] += __bfloat162float(p.dht[seq * p.t_sn + (d0 + c) * p.t_sd + ti * p.t_sw]);
+          }
+          *reinterpret_cast<uint4*>(dxb + s * p.dx_st) = pack8b(o);
+        }
       }
-      const int s = u - (W - 1);   // dx[s] = sum_i w[W-1-i] gr[s+i] is complete now
-      if (s >= t && s < seg_end) {
-        float o[8];
+#pragma unroll
+      for (int j = 0; j < W - 1; ++j)
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          float a = 0.f;
-#pragma unroll
-          for (int i = 0; i < W; ++i) a = fmaf(w[W - 1 - i][c], gw[i][c], a);
-          o[c] = a;
+          xs[j][c] = xs[G + j][c];
+          gs[j][c] = gs[G + j][c];
         }
-        const int ti = s - (seq_end - (W - 1));   // index into the final state when s is one of the last W-1 inputs
-        if (p.dht && ti >= 0) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) o[c] += __bfloat162float(p.dht[seq * p.t_sn + (d0 + c) * p.t_sd + ti * p.t_sw]);
-        }
-        *reinterpret_cast<uint4*>(dxb + s * p.dx_st) = pack8b(o);
-      }
     }
-    if (owns_start) {
+    if (t == seq_begin && p.dh0) {
+      // dh0[i] = sum_{rel <= i} gr[rel] w[i - rel]: the first W-1 tokens of the sequence, recomputed on their own
       const int len = seq_end - seq_begin;
+      float dh[W - 1][8];
+#pragma unroll
+      for (int i = 0; i < W - 1; ++i)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) dh[i][c] = 0.f;
+#pragma unroll
+      for (int rel = 0; rel < W - 1; ++rel) {
+        if (rel < len) {
+          const int u = seq_begin + rel;
+          float g8[8];
+          unpack8b(*reinterpret_cast<const uint4*>(gb + u * p.dy_st), g8);
+          if constexpr (SILU) {
+            float pre[8];
+            if (yb) {
+              unpack8b(*reinterpret_cast<const uint4*>(yb + u * p.yp_st), pre);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) pre[c] = bias[c];
+#pragma unroll
+              for (int j = 0; j < W; ++j) {
+                float xv[8];
+                input_at(u - (W - 1) + j, xv);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) pre[c] = fmaf(w[j][c], xv[c], pre[c]);
+              }
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) g8[c] *= dsilu(pre[c]);
+          }
+#pragma unroll
+          for (int i = rel; i < W - 1; ++i)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) dh[i][c] = fmaf(g8[c], w[i - rel][c], dh[i][c]);
+        }
+      }
 #pragma unroll
       for (int i = 0; i < W - 1; ++i) {
 #pragma unroll
@@ -305,7 +356,7 @@ extern "C" FLA_API int fla_b200_causal_conv1d_bwd(const fla_causal_conv1d_bwd_ar
     p.ypre = static_cast<const bf16*>(y.data); p.yp_sb = y.stride[0]; p.yp_st = y.stride[1];
   }
   if (a->bias.data) {
-    if (a->bias.ndim != 1 || a->bias.shape[0] != D || a->bias.dtype != FLA_BF16 || a->bias.stride[0] != 1) return FLA_ERR_SHAPE;
+    if (a->bias.ndim != 1 || a->bias.shape[0] != D || a->bias.dtype != FLA_BF16 || a->bias.stride[0] != 1 || !aligned16(a->bias.data)) return FLA_ERR_SHAPE;
     p.bias = static_cast<const bf16*>(a->bias.data);
   }
   float* db = nullptr;
