@@ -249,15 +249,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 // Split eight fp32 values into a bf16 "hi" vector and a bf16 "lo" residual vector (x ~= hi + lo).
+// Per pair: one packed convert, the two hi values recovered by shift / mask, two subtractions, one packed convert.
 __device__ __forceinline__ void split8(const float* x, uint4& hi, uint4& lo) {
-  float h[8], l[8];
+  uint32_t h[4], l[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    h[i] = __bfloat162float(__float2bfloat16_rn(x[i]));
-    l[i] = x[i] - h[i];
+  for (int i = 0; i < 4; ++i) {
+    h[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+    const float h0 = __uint_as_float(h[i] << 16), h1 = __uint_as_float(h[i] & 0xffff0000u);
+    l[i] = pack_bf16(x[2 * i] - h0, x[2 * i + 1] - h1);
   }
-  hi = make_uint4(pack_bf16(h[0], h[1]), pack_bf16(h[2], h[3]), pack_bf16(h[4], h[5]), pack_bf16(h[6], h[7]));
-  lo = make_uint4(pack_bf16(l[0], l[1]), pack_bf16(l[2], l[3]), pack_bf16(l[4], l[5]), pack_bf16(l[6], l[7]));
+  hi = make_uint4(h[0], h[1], h[2], h[3]);
+  lo = make_uint4(l[0], l[1], l[2], l[3]);
 }
 __device__ __forceinline__ uint4 pack8(const float* x) {
   return make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
