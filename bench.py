@@ -261,7 +261,11 @@ class Workload:
         """DRAM bytes (read + write) of one launch: the per-unit figure of one ncu capture of a small case of the
         same kernel (profiles/), scaled by the units this launch processes; None where no capture exists."""
         c = self.cfg
-        per_chunk_head = {"gdn_fwd": 313.04e6 / 2048, "gdn_bwd_dhu": 384.72e6 / 2048, "gdn_bwd_par": 505.20e6 / 2048}
+        per_chunk_head = {"gdn_fwd": 313.04e6 / 2048, "gdn_bwd_dhu": 384.72e6 / 2048, "gdn_bwd_par": 505.20e6 / 2048,
+                          "kda_prep": 158.75e6 / 512, "kda_fwd": 233.31e6 / 512, "kda_bwd_dhu": 266.09e6 / 512,
+                          "kda_bwd_par": 396.03e6 / 512}
+        if kname == "gdn_fwd" and self.name == "gdn_fwd_conv":
+            return None     # the capture is of the training forward (it also writes the saved images)
         if kname in per_chunk_head and "T" in c:
             return per_chunk_head[kname] * c["B"] * ((c["T"] + 63) // 64) * c["HV"]
         if kname == "recurrent_gdn":       # 212.33 MB for 64 sequences x 32 heads
@@ -489,6 +493,10 @@ def main():
                 denom = 1e12 * peaks["bf16_tflops"] if b == "tensor" else 1e9 * peaks["hbm_gbs"]
                 ktimes[k]["frac_of_peak"] = wk / s / denom
                 ktimes[k]["bound"] = b
+                tr = wl.kernel_traffic(k)
+                if tr is not None:   # DRAM bytes of the ncu capture scaled to this launch, as a share of the copy bandwidth
+                    ktimes[k]["dram_gb"] = tr / 1e9
+                    ktimes[k]["dram_frac_of_hbm_peak"] = tr / s / (1e9 * peaks["hbm_gbs"])
         step_roofline = None
         if wl.step_flops():
             tf = wl.step_flops() / (ms_per_step * 1e-3) / 1e12
