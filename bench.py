@@ -262,8 +262,8 @@ class Workload:
         same kernel (profiles/), scaled by the units this launch processes; None where no capture exists."""
         c = self.cfg
         per_chunk_head = {"gdn_fwd": 313.04e6 / 2048, "gdn_bwd_dhu": 384.72e6 / 2048, "gdn_bwd_par": 505.20e6 / 2048,
-                          "kda_prep": 158.75e6 / 512, "kda_fwd": 233.31e6 / 512, "kda_bwd_dhu": 266.09e6 / 512,
-                          "kda_bwd_par": 396.03e6 / 512}
+                          "kda_prep": 158.75e6 / 1024, "kda_fwd": 233.31e6 / 1024, "kda_bwd_dhu": 266.09e6 / 1024,
+                          "kda_bwd_par": 396.03e6 / 1024}
         if kname == "gdn_fwd" and self.name == "gdn_fwd_conv":
             return None     # the capture is of the training forward (it also writes the saved images)
         if kname in per_chunk_head and "T" in c:
