@@ -640,17 +640,32 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
       }
     }
     __syncthreads();
-    if (tid < rows) {
+    if (tid < kC) {
       // dg = reverse chunk-local cumulative sum of dgam; the last row additionally carries
       // e^{gam_L} <S, dS'> + sum_i e^{gam_L - gam_i} k_i.(Vn dS'^T)_i, which therefore reaches every row.
+      // Two warps: suffix sums by shuffles (dgam_s and red[3][0] are zero past the last valid row).
+      float suf = dgam_s[tid], tot3 = red[3][0][tid];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float dn = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += dn;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) tot3 += __shfl_xor_sync(0xffffffffu, tot3, o);
+      if (lane == 0) {
+        red[4][0][warp] = suf;      // total of this warp's 32 rows (suffix sum at its first row)
+        red[4][1][warp] = tot3;
+      }
+      asm volatile("bar.sync 2, 64;" ::: "memory");   // the two warps that own the 64 rows
+      if (warp == 0) suf += red[4][0][1];
       float tot = 0.f;
       for (int w = 0; w < 8; ++w) tot += sds_s[w];
-      float dgv = __expf(gam_s[rows - 1]) * tot;
-      for (int j = 0; j < rows; ++j) dgv += red[3][0][j];
-      for (int j = tid; j < rows; ++j) dgv += dgam_s[j];
-      const int64_t gidx = (tok0 + tid) * p.HV + hv;
-      if (p.grads_f32) static_cast<float*>(p.dg)[gidx] = dgv;
-      else static_cast<bf16*>(p.dg)[gidx] = __float2bfloat16_rn(dgv);
+      const float dgv = suf + __expf(gam_s[rows - 1]) * tot + red[4][1][0] + red[4][1][1];
+      if (tid < rows) {
+        const int64_t gidx = (tok0 + tid) * p.HV + hv;
+        if (p.grads_f32) static_cast<float*>(p.dg)[gidx] = dgv;
+        else static_cast<bf16*>(p.dg)[gidx] = __float2bfloat16_rn(dgv);
+      }
     }
     __syncthreads();
   }
