@@ -344,7 +344,7 @@ constexpr uint32_t qOffSH = 147456, qOffSL = 163840, qOffDSH = 180224, qOffDSL =
 constexpr uint32_t qOffPAH = qOffAH, qOffPAL = qOffAL;   // [dP ; dM] hi / lo reuse the [dO ; dZ] panels
 constexpr uint32_t qOffTile = qOffAH;           // three fp32 [64][129] tiles of the dg assembly reuse the step buffers
 constexpr uint32_t kKdaParSmem = 212992;
-constexpr int kTileStride = 129;
+constexpr int kTileStride = 132;   // 16-byte aligned rows; float4 row stores and scalar column reads are both conflict-free
 constexpr uint32_t kTileBytes = kC * kTileStride * 4;
 static_assert(qOffTile + 3 * kTileBytes <= kKdaParSmem, "dg tiles must fit in the step buffers");
 constexpr uint32_t qColQK = 0, qColDV = 64, qColTA = 128, qColTB1 = 256, qColTB2 = 384;
@@ -365,6 +365,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
   __shared__ float beta_s[kC], anchor_s[kK];
   __shared__ float red[2][2][kC];      // rkG, ma : [half][row]
   __shared__ float sds_s[2][kK];       // sum_v dS'a * Sa per key channel, by column half
+  __shared__ float colsum_s[4][kK];    // per 32-row part: column sums of the dgk tiles and of the last-row tile
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t mma_bar, load_bar, img_bar;
 
@@ -597,14 +598,18 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
             const float4 g0 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8);
             const float4 g1 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8 + 4);
             const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float tq[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int col = sub * 32 + ch * 8 + j;
               const float xv = x[ch * 8 + j];
               const float e1 = __expf(gv[j] - anchor_s[half * 64 + col]);
               acc_out[col] += live ? xv * e1 : 0.f;
-              tile_q[tok * kTileStride + half * 64 + col] = live ? qp[j] * xv : 0.f;
+              tq[j] = live ? qp[j] * xv : 0.f;
             }
+            float* dq_ = tile_q + tok * kTileStride + half * 64 + sub * 32 + ch * 8;
+            *reinterpret_cast<float4*>(dq_) = make_float4(tq[0], tq[1], tq[2], tq[3]);
+            *reinterpret_cast<float4*>(dq_ + 4) = make_float4(tq[4], tq[5], tq[6], tq[7]);
           }
         } else {
           float y1[32], y2[32];
@@ -619,6 +624,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
             const float4 g0 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8);
             const float4 g1 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8 + 4);
             const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float tk[8], tl[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int col = sub * 32 + ch * 8 + j;
@@ -626,9 +632,15 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
               const float e1 = __expf(d), e2 = __expf(-d);
               const float dkp = x[ch * 8 + j], t1 = y1[ch * 8 + j], dkn = t1 + y2[ch * 8 + j];
               acc_out[col] += live ? dkp * e1 + dkn * e2 : 0.f;
-              tile_k[tok * kTileStride + half * 64 + col] = live ? kp[j] * dkp - kn[j] * dkn : 0.f;
-              tile_1[tok * kTileStride + half * 64 + col] = live ? kn[j] * t1 : 0.f;
+              tk[j] = live ? kp[j] * dkp - kn[j] * dkn : 0.f;
+              tl[j] = live ? kn[j] * t1 : 0.f;
             }
+            float* dk_ = tile_k + tok * kTileStride + half * 64 + sub * 32 + ch * 8;
+            float* dl_ = tile_1 + tok * kTileStride + half * 64 + sub * 32 + ch * 8;
+            *reinterpret_cast<float4*>(dk_) = make_float4(tk[0], tk[1], tk[2], tk[3]);
+            *reinterpret_cast<float4*>(dk_ + 4) = make_float4(tk[4], tk[5], tk[6], tk[7]);
+            *reinterpret_cast<float4*>(dl_) = make_float4(tl[0], tl[1], tl[2], tl[3]);
+            *reinterpret_cast<float4*>(dl_ + 4) = make_float4(tl[4], tl[5], tl[6], tl[7]);
           }
         }
       }
@@ -637,15 +649,28 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
     __syncthreads();
     // dg = reverse chunk-local cumulative sum of dgk; the last row additionally carries
     // sum_v dS'a Sa + sum_i Kn_i (Vn dS'a^T)_i, which therefore reaches every row.
-    if (tid < kK) {
-      const int kc = tid;
-      float run = sds_s[0][kc] + sds_s[1][kc];
-      for (int i = 0; i < rows; ++i) run += tile_1[i * kTileStride + kc];
-      for (int t = rows - 1; t >= 0; --t) {
+    {
+      // Two threads per key channel, 32 rows each: local totals first, then the suffix sums with the loads unrolled.
+      const int kc = tid & (kK - 1), part = tid >> 7, r0 = part * 32;
+      float tot = 0.f, t1 = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < 32; ++i) {
+        tot += tile_q[(r0 + i) * kTileStride + kc] + tile_k[(r0 + i) * kTileStride + kc];   // rows past the end hold zeros
+        t1 += tile_1[(r0 + i) * kTileStride + kc];
+      }
+      colsum_s[part][kc] = tot;
+      colsum_s[2 + part][kc] = t1;
+      __syncthreads();
+      float run = sds_s[0][kc] + sds_s[1][kc] + colsum_s[2][kc] + colsum_s[3][kc] + (part == 0 ? colsum_s[1][kc] : 0.f);
+#pragma unroll 8
+      for (int i = 31; i >= 0; --i) {
+        const int t = r0 + i;
         run += tile_q[t * kTileStride + kc] + tile_k[t * kTileStride + kc];
-        const int64_t off = (tok0 + t) * p.dg_st + hv * p.dg_sh + kc;
-        if (p.grads_f32) static_cast<float*>(p.dg)[off] = run;
-        else static_cast<bf16*>(p.dg)[off] = __float2bfloat16_rn(run);
+        if (t < rows) {
+          const int64_t off = (tok0 + t) * p.dg_st + hv * p.dg_sh + kc;
+          if (p.grads_f32) static_cast<float*>(p.dg)[off] = run;
+          else static_cast<bf16*>(p.dg)[off] = __float2bfloat16_rn(run);
+        }
       }
     }
     __syncthreads();
