@@ -384,7 +384,18 @@ __device__ __forceinline__ void row_dot64(const uint8_t* pan0, uint32_t panel_st
   }
 }
 
+#ifdef FLA_STAGE_CLOCKS
+__device__ long long g_par_clocks[16];
+#define PSTAMP(i) do { long long now_ = clock64(); pclk_[i] += now_ - plast_; plast_ = now_; } while (0)
+#else
+#define PSTAMP(i)
+#endif
+
 __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
+#ifdef FLA_STAGE_CLOCKS
+  long long pclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long plast_ = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[kC], beta_s[kC];
@@ -412,11 +423,32 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     tmem_alloc(&tmem_base_s, 512);
     tmem_relinquish();
   }
+  const uint32_t sb = smem_u32(smem);
+  auto issue_loads = [&](int hv, int vb) {  // one thread: operands of one (value head, V block) step
+    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+    mbar_arrive_expect_tx(&load_bar, kStepBytes);
+    const bf16* dz = p.dz_img + (cidx * 2 + vb) * 12288;
+    bulk_load(sb + rOffAH, dz, 16384, &load_bar);
+    bulk_load(sb + rOffAL + 8192, dz + 8192, 8192, &load_bar);
+    bulk_load(sb + rOffVNH, p.vn_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + rOffSH, p.s_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + rOffDSH, p.ds_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
+  };
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
     mbar_init(&load_bar, 1);
     mbar_init_fence();
+    issue_loads(hk * G, 0);   // the first step's operands travel while the q, k rows are staged
   }
+  // per-row scalars of the first value head (later heads: fetched one head ahead)
+  float pf_gam = 0.f, pf_beta = 0.f;
+  auto prefetch_scalars = [&](int hv) {
+    if (tid < kC) {
+      pf_gam = p.gam[(tok0 + min(tid, rows - 1)) * p.HV + hv];
+      pf_beta = tid < rows ? ld_scalar(p.beta, (tok0 + tid) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+    }
+  };
+  prefetch_scalars(hk * G);
   // q, k rows of the chunk (shared by the value heads of the group) and the static zero rows of the lo operand
   {
     uint4 val[8];   // all loads in flight before the first one is consumed
@@ -442,21 +474,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, quad * 32, 0);
-  const uint32_t sb = smem_u32(smem);
   uint32_t mphase = 0, lphase = 0;
   bool ok = true;
-
-  auto issue_loads = [&](int hv, int vb) {  // one thread: operands of one (value head, V block) step
-    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
-    mbar_arrive_expect_tx(&load_bar, kStepBytes);
-    const bf16* dz = p.dz_img + (cidx * 2 + vb) * 12288;
-    bulk_load(sb + rOffAH, dz, 16384, &load_bar);
-    bulk_load(sb + rOffAL + 8192, dz + 8192, 8192, &load_bar);
-    bulk_load(sb + rOffVNH, p.vn_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + rOffSH, p.s_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
-    bulk_load(sb + rOffDSH, p.ds_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
-  };
-  if (tid == 0) issue_loads(hk * G, 0);
 
   const Operand opQK{sb + rOffQK, rQKPanel, 0};                      // [q; k], reduction over key dims
   const Operand opKb{sb + rOffQK + 8192, rQKPanel, 0};               // k as B, N = 64 tokens
@@ -474,17 +493,21 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
 #pragma unroll
   for (int i = 0; i < 64; ++i) acc_out[i] = 0.f;
 
+  PSTAMP(0);
   for (int h = 0; h < G && ok; ++h) {
     const int hv = hk * G + h;
     if (tid < kC) {
-      gam_s[tid] = p.gam[(tok0 + min(tid, rows - 1)) * p.HV + hv];
-      beta_s[tid] = tid < rows ? ld_scalar(p.beta, (tok0 + tid) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+      gam_s[tid] = pf_gam;
+      beta_s[tid] = pf_beta;
     }
+    if (h + 1 < G) prefetch_scalars(hv + 1);
     float sds = 0.f;
     for (int vb = 0; vb < 2; ++vb) {
+      PSTAMP(1);
       ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT);
       lphase ^= 1;
       if (!__syncthreads_and(ok)) break;
+      PSTAMP(2);
       if (tid == 0) {
         tc_fence_after();
         if (h == 0 && vb == 0) mma_tile(tbase + rColQK, opQK, opKb, 128, 64, 8, false);
@@ -512,9 +535,11 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) sds += (s1[j] + s2[j]) * (d1[j] + d2[j]);
       }
+      PSTAMP(3);
       ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
       mphase ^= 1;
       if (!__syncthreads_and(ok)) break;   // also: every thread is done reading the step's buffers
+      PSTAMP(4);
       tc_fence_after();
       if (tid == 0) {
         if (vb == 0) issue_loads(hv, 1);
@@ -526,6 +551,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     for (int o = 16; o > 0; o >>= 1) sds += __shfl_xor_sync(0xffffffffu, sds, o);
     if (lane == 0) sds_s[warp] = sds;
 
+    PSTAMP(5);
     // ---- epilogue 1: score-tile gradients -> [dP; dAt] operand, first parts of this head's dq / dk rows
     const float gam_i = gam_s[tok], beta_i = beta_s[tok], gam_last = gam_s[rows - 1];
     const float eg = __expf(gam_i);
@@ -582,6 +608,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     tc_fence_before();
     __syncthreads();
 
+    PSTAMP(6);
     // ---- [dP; dAt] K  and  [dP^T | dAt^T] [Q; K]
     if (tid == 0) {
       tc_fence_after();
@@ -596,6 +623,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
 
+    PSTAMP(7);
     // ---- epilogue 2: finish the rows, row dots for dg / dbeta
     {
       float t[64];
@@ -620,6 +648,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
       red[3][half][tok] = rkB;
       red[4][half][tok] = ma_part;
     }
+    PSTAMP(8);
     tc_fence_before();
     __syncthreads();
     if (tid < kC) {
@@ -670,6 +699,11 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     __syncthreads();
   }
 
+  PSTAMP(9);
+#ifdef FLA_STAGE_CLOCKS
+  if (tid == 0 && blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0)
+    for (int i = 0; i < 12; ++i) g_par_clocks[i] += pclk_[i];
+#endif
   if (ok && tok < rows) {
     void* base = kside ? p.dk : p.dq;
     const int64_t off = kside ? (tok0 + tok) * p.dk_st + hk * p.dk_sh + half * 64 : (tok0 + tok) * p.dq_st + hk * p.dq_sh + half * 64;
@@ -888,3 +922,9 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_ar
   // every other byte it later reads, so nothing else of the previous call's contents matters.
   return fla_b200_gdn_chunk_bwd(a, scratch, kStaticScratchBytes, stream);
 }
+
+#ifdef FLA_STAGE_CLOCKS
+extern "C" FLA_API int fla_b200_debug_par_clocks(long long* out16) {
+  return cudaMemcpyFromSymbol(out16, fla::g_par_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
+}
+#endif
