@@ -23,6 +23,7 @@
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
 #include "tri_inverse.h"
+#include "tensor_map.h"
 
 namespace fla {
 
@@ -179,7 +180,6 @@ constexpr uint32_t kColS = 0, kColRQ = 64, kColQK = 128, kColVN = 192;  // TMEM 
 constexpr int kFwdThreads = 256;
 
 struct FwdPrefetch {
-  uint4 qk[8];
   uint4 x[2];
   uint4 v[4];
   float gb;
@@ -192,7 +192,11 @@ __device__ long long g_stage_clocks[16];
 #define STAMP(i)
 #endif
 
-__global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p) {
+// q and k rows reach their operand panels as four 64 x 64 TMA tiles per chunk (the 128-byte swizzle of the tensor map
+// is the panel layout); rows past the end of a sequence then hold whatever follows in memory (zero past the end of
+// the tensor): harmless, because every product with them is multiplied by a zero row of X, P or beta.
+__global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                                  const __grid_constant__ CUtensorMap tm_k) {
 #ifdef FLA_STAGE_CLOCKS
   long long last_ = clock64();
 #endif
@@ -200,7 +204,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar, pbar;
+  __shared__ __align__(8) uint64_t bar, pbar, qk_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -219,12 +223,15 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
   if (tid == 0) {
     mbar_init(&bar, 1);
     mbar_init(&pbar, 1);
+    mbar_init(&qk_bar, 1);
     mbar_init_fence();
+    tma_prefetch_descriptor(&tm_q);
+    tma_prefetch_descriptor(&tm_k);
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
-  uint32_t phase = 0, pphase = 0;
+  uint32_t phase = 0, pphase = 0, qkphase = 0;
   bool dead = false;
   const uint32_t sb = smem_u32(smem);
 
@@ -233,17 +240,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     const int t0 = c * kC;
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * kFwdThreads;            // 0..2047: [q rows | k rows] x 16 chunks
-      const int r = (idx / 16) & 63, ch = idx % 16;
-      const bool isk = idx >= 1024;
-      pf.qk[i] = make_uint4(0, 0, 0, 0);
-      if (r < rows) {
-        const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
-        pf.qk[i] = *reinterpret_cast<const uint4*>(src + ch * 8);
-      }
-    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int idx = tid + i * kFwdThreads, r = idx / 8, ch = idx % 8;
@@ -300,18 +296,21 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
   };
   auto store_panels = [&]() {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * kFwdThreads;
-      const int r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
-      *reinterpret_cast<uint4*>(smem + kOffQK + (ch / 8) * kQKPanel + panel_chunk_off(r, ch % 8)) = pf.qk[i];
-    }
-#pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int idx = tid + i * kFwdThreads;
       *reinterpret_cast<uint4*>(smem + kOffX + panel_chunk_off(idx / 8, idx % 8)) = pf.x[i];
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) vcur[i] = pf.v[i];
+  };
+
+  auto issue_qk_load = [&](int c) {   // one thread: the chunk's q rows (panel rows 0-63) and k rows (rows 64-127)
+    const int row0 = sq.bos + c * kC;
+    mbar_arrive_expect_tx(&qk_bar, 4 * 8192);
+    tma_load_tile(sb + kOffQK, &tm_q, 0, hk, row0, &qk_bar);
+    tma_load_tile(sb + kOffQK + kQKPanel, &tm_q, 64, hk, row0, &qk_bar);
+    tma_load_tile(sb + kOffQK + 8192, &tm_k, 0, hk, row0, &qk_bar);
+    tma_load_tile(sb + kOffQK + kQKPanel + 8192, &tm_k, 64, hk, row0, &qk_bar);
   };
 
   // operands (shared addresses)
@@ -326,6 +325,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
   float srow[32];   // this thread's 32 columns of the fp32 state row
 
   // ---- prologue: chunk 0 operands and the initial state
+  if (tid == 0) issue_qk_load(0);
   prefetch_load(0);
   prefetch_scalars(0);
   store_scalars(0);
@@ -374,10 +374,12 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
         bulk_store(dst, sb + kOffSH, 32768);
         bulk_commit();
       }
+      if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
       mma_tile(tbase + kColRQ, opQK, opSH, 128, 64, 8, false);
       mma_tile(tbase + kColRQ, opQK, opSL, 128, 64, 8, true);
       mma_commit(&bar);
     }
+    qkphase ^= 1;
     if (c + 1 < sq.nt) {
       prefetch_l2(c + 1);
       prefetch_scalars(c + 1);
@@ -459,6 +461,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p)
     if (c + 1 < sq.nt) prefetch_load(c + 1);   // the next chunk's rows (L2-resident by now) travel while the MMAs run
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
+    if (tid == 0 && c + 1 < sq.nt) issue_qk_load(c + 1);   // every reader of the q / k / P panels has completed
 
     STAMP(5);
     // ---- stage 6: output rows, next state, next chunk's operand panels
@@ -639,9 +642,13 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
     TriInverseParams tp{p.at, p.X, nullptr, nullptr, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, 0};
     if (launch_tri_inverse(tp, nt_max, N, cs)) return FLA_ERR_CUDA;
   }
+  CUtensorMap tm_q, tm_k;
+  if (make_row_tile_map(&tm_q, p.q, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.q_sh), uint64_t(p.q_st)) ||
+      make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)))
+    return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_fwd", cs);
-    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p);
+    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p, tm_q, tm_k);
   }
   return cuda_status(cudaGetLastError());
 }

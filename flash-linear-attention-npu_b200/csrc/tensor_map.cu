@@ -1,0 +1,37 @@
+#include "tensor_map.h"
+
+#include <mutex>
+
+namespace fla {
+
+namespace {
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+std::once_flag g_once;
+
+void resolve() {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult st;
+  if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &st) == cudaSuccess &&
+      st == cudaDriverEntryPointSuccess)
+    g_encode = reinterpret_cast<EncodeFn>(fn);
+}
+}  // namespace
+
+int make_row_tile_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t heads, uint64_t rows,
+                      uint64_t head_stride, uint64_t row_stride) {
+  std::call_once(g_once, resolve);
+  if (!g_encode) return 6;
+  const cuuint64_t dims[3] = {cols, heads, rows};
+  const cuuint64_t strides[2] = {head_stride * 2, row_stride * 2};   // bytes, dims 1 and 2
+  const cuuint32_t box[3] = {64, 1, 64};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 6;
+}
+
+}  // namespace fla

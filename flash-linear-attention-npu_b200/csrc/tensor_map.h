@@ -1,0 +1,31 @@
+// Host-side construction of TMA tensor maps (cuTensorMapEncodeTiled through the runtime's driver entry point, so the
+// library does not link against libcuda) and the device-side tiled bulk load that consumes them.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace fla {
+
+// bf16 tensor viewed as [rows][heads][cols] (cols contiguous; strides in elements): boxes of 64 rows x 1 head x 64
+// columns, written to shared memory in the 128-byte-swizzled panel layout the MMA descriptors expect.
+// Returns 0, or 6 (FLA_ERR_CUDA) when the driver refuses the map.
+int make_row_tile_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t heads, uint64_t rows,
+                      uint64_t head_stride, uint64_t row_stride);
+
+#ifdef __CUDACC__
+// One 64 x 64 bf16 box (8 KB) at (col0, head, row0) -> shared memory; completes `bytes` on the mbarrier.
+// col0 must be a multiple of 8 elements (16 bytes); rows past the tensor's end read as zero.  No multicast.
+__device__ __forceinline__ void tma_load_tile(uint32_t smem_dst, const CUtensorMap* map, int col0, int head, int row0,
+                                              uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"(map), "r"(static_cast<uint32_t>(__cvta_generic_to_shared(bar))), "r"(col0), "r"(head), "r"(row0)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+#endif
+
+}  // namespace fla
