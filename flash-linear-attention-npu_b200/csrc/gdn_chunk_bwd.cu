@@ -26,6 +26,7 @@
 #include "gdn_common.cuh"
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
+#include "tensor_map.h"
 
 namespace fla {
 
@@ -62,19 +63,21 @@ constexpr uint32_t kDhuSmem = 98304;
 constexpr uint32_t hColDS = 0, hColW1 = 64, hColQK = 128, hColU1 = 192;
 
 struct DhuPrefetch {
-  uint4 qk[8];
-  uint4 x[2];
   uint4 row[4];   // q-side threads: my 32 columns of the dO row; k-side threads: of the v row
   float gb;
 };
 constexpr int kDhuThreads = 256;
 
-__global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParams p) {
+// q, k and X reach their operand panels as TMA tiles (see gdn_fwd_kernel); rows past the end of a sequence are
+// neutralised by zeroing the corresponding rows of dVn.
+__global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                                      const __grid_constant__ CUtensorMap tm_k,
+                                                                      const __grid_constant__ CUtensorMap tm_x) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar, pbar;
+  __shared__ __align__(8) uint64_t bar, pbar, qk_bar, x_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -91,14 +94,31 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
   if (tid == 0) {
     mbar_init(&bar, 1);
     mbar_init(&pbar, 1);
+    mbar_init(&qk_bar, 1);
+    mbar_init(&x_bar, 1);
     mbar_init_fence();
+    tma_prefetch_descriptor(&tm_q);
+    tma_prefetch_descriptor(&tm_k);
+    tma_prefetch_descriptor(&tm_x);
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
-  uint32_t phase = 0, pphase = 0;
+  uint32_t phase = 0, pphase = 0, qkphase = 0, xphase = 0;
   bool dead = false;
   const uint32_t sb = smem_u32(smem);
+  auto issue_qk_load = [&](int c) {  // one thread: the chunk's q rows (panel rows 0-63) and k rows (rows 64-127)
+    const int row0 = sq.bos + c * kC;
+    mbar_arrive_expect_tx(&qk_bar, 4 * 8192);
+    tma_load_tile(sb + hOffQK, &tm_q, 0, hk, row0, &qk_bar);
+    tma_load_tile(sb + hOffQK + hQKPanel, &tm_q, 64, hk, row0, &qk_bar);
+    tma_load_tile(sb + hOffQK + 8192, &tm_k, 0, hk, row0, &qk_bar);
+    tma_load_tile(sb + hOffQK + hQKPanel + 8192, &tm_k, 64, hk, row0, &qk_bar);
+  };
+  auto issue_x_load = [&](int c) {
+    mbar_arrive_expect_tx(&x_bar, 8192);
+    tma_load_tile(sb + hOffX, &tm_x, 0, hv, sq.bos + c * kC, &x_bar);
+  };
   auto issue_p_load = [&](int c) {   // P = tril(Q K^T * decay) of chunk c, built by the forward's prep kernel
     const bf16* src = p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192;
     mbar_arrive_expect_tx(&pbar, 16384);
@@ -110,23 +130,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     const int t0 = c * kC;
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * kDhuThreads;
-      const int r = (idx / 16) & 63, ch = idx % 16;
-      const bool isk = idx >= 1024;
-      pf.qk[i] = make_uint4(0, 0, 0, 0);
-      if (r < rows) {
-        const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
-        pf.qk[i] = *reinterpret_cast<const uint4*>(src + ch * 8);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int idx = tid + i * kDhuThreads, r = idx / 8, ch = idx % 8;
-      pf.x[i] = make_uint4(0, 0, 0, 0);
-      if (r < rows) pf.x[i] = *reinterpret_cast<const uint4*>(p.X + ((tok0 + r) * p.HV + hv) * kC + ch * 8);
-    }
     const bf16* rsrc = kside ? p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + c0
                              : p.dO + (tok0 + tok) * p.do_st + hv * p.do_sh + vb * kBV + c0;
 #pragma unroll
@@ -156,17 +159,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
   uint4 rcur[4];
   auto prefetch_store = [&](int c) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * kDhuThreads;
-      const int r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
-      *reinterpret_cast<uint4*>(smem + hOffQK + (ch / 8) * hQKPanel + panel_chunk_off(r, ch % 8)) = pf.qk[i];
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int idx = tid + i * kDhuThreads;
-      *reinterpret_cast<uint4*>(smem + hOffX + panel_chunk_off(idx / 8, idx % 8)) = pf.x[i];
-    }
-#pragma unroll
     for (int i = 0; i < 4; ++i) rcur[i] = pf.row[i];
     if (kside) {
       if (half == 0) beta_s[c & 1][tok] = pf.gb;
@@ -189,7 +181,11 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
   const int c_last = sq.nt - 1;
   prefetch_load(c_last);
   prefetch_store(c_last);
-  if (tid == 0) issue_p_load(c_last);
+  if (tid == 0) {
+    issue_qk_load(c_last);
+    issue_p_load(c_last);
+    issue_x_load(c_last);
+  }
   if (p.dht) {
     const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
 #pragma unroll
@@ -230,6 +226,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
       bf16* dst = p.ds_img + (cidx * 2 + vb) * (2 * 8192);
       bulk_store(dst, sb + hOffDSH, 32768);
       bulk_commit();
+      if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
       mma_tile(tbase + hColW1, opQK, opDSH, 128, 64, 8, false);
       mma_tile(tbase + hColW1, opQK, opDSL, 128, 64, 8, true);
       if (!mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // P panels have landed
@@ -238,6 +235,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
       mma_commit(&bar);
     }
     pphase ^= 1;
+    qkphase ^= 1;
     if (c > 0) prefetch_l2(c - 1);
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
@@ -250,8 +248,9 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
       tmem_ld32(trow + hColU1, acc);
       tmem_ld_wait();
       const float dk = __expf(gam_last - gam_i);
+      const bool live = tok < rows;   // rows past the end of the sequence hold foreign k rows: dVn = 0 there
 #pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] = p.scale * acc[i] + dk * w1[i];
+      for (int i = 0; i < 32; ++i) acc[i] = live ? p.scale * acc[i] + dk * w1[i] : 0.f;
       row32_to_hilo(smem + hOffPH, smem + hOffPL, tok, half, acc);
     }
     if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
@@ -262,12 +261,15 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
 
     // ---- stage 5: dZ = X^T dVn  (valid accumulator rows 64..127)
     if (tid == 0) {
+      if (!mbar_wait(&x_bar, xphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // the X tile has landed
       mma_tile(tbase + hColQK, opXT, opDVh, 128, 64, 4, false);
       mma_tile(tbase + hColQK, opXT, opDVl, 128, 64, 4, true);
       mma_commit(&bar);
     }
+    xphase ^= 1;
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
+    if (tid == 0 && c > 0) issue_x_load(c - 1);
 
     // ---- stage 6: k-side rows: dV, sum_v dZ*V, dZ images, -beta e^gam dZ;  q-side rows: scale e^gam dO
     if (kside) {
@@ -334,6 +336,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     if (c > 0) prefetch_load(c - 1);   // L2-resident by now; travels while the MMAs run
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
+    if (tid == 0 && c > 0) issue_qk_load(c - 1);   // the last readers of the q / k panels have completed
 
     // ---- stage 8: new dS to registers; next chunk's operands
     tmem_ld_row32(trow + hColDS, srow);
@@ -862,9 +865,14 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
     if (cudaFuncSetAttribute(gdn_bwd_par_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
+  CUtensorMap tm_q, tm_k, tm_x;
+  if (make_row_tile_map(&tm_q, p.q, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.q_sh), uint64_t(p.q_st)) ||
+      make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)) ||
+      make_row_tile_map(&tm_x, p.X, kC, uint64_t(HV), uint64_t(B * T), uint64_t(kC), uint64_t(HV) * kC))
+    return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_bwd_dhu", cs);
-    gdn_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), kDhuThreads, kDhuSmem + 1024, cs>>>(p);
+    gdn_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), kDhuThreads, kDhuSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   const int nt_max = (max_len + kC - 1) / kC;

@@ -180,7 +180,6 @@ constexpr uint32_t kColS = 0, kColRQ = 64, kColQK = 128, kColVN = 192;  // TMEM 
 constexpr int kFwdThreads = 256;
 
 struct FwdPrefetch {
-  uint4 x[2];
   uint4 v[4];
   float gb;
 };
@@ -196,7 +195,8 @@ __device__ long long g_stage_clocks[16];
 // is the panel layout); rows past the end of a sequence then hold whatever follows in memory (zero past the end of
 // the tensor): harmless, because every product with them is multiplied by a zero row of X, P or beta.
 __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p, const __grid_constant__ CUtensorMap tm_q,
-                                                                  const __grid_constant__ CUtensorMap tm_k) {
+                                                                  const __grid_constant__ CUtensorMap tm_k,
+                                                                  const __grid_constant__ CUtensorMap tm_x) {
 #ifdef FLA_STAGE_CLOCKS
   long long last_ = clock64();
 #endif
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar, pbar, qk_bar;
+  __shared__ __align__(8) uint64_t bar, pbar, qk_bar, x_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -224,14 +224,16 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     mbar_init(&bar, 1);
     mbar_init(&pbar, 1);
     mbar_init(&qk_bar, 1);
+    mbar_init(&x_bar, 1);
     mbar_init_fence();
     tma_prefetch_descriptor(&tm_q);
     tma_prefetch_descriptor(&tm_k);
+    tma_prefetch_descriptor(&tm_x);
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
-  uint32_t phase = 0, pphase = 0, qkphase = 0;
+  uint32_t phase = 0, pphase = 0, qkphase = 0, xphase = 0;
   bool dead = false;
   const uint32_t sb = smem_u32(smem);
 
@@ -240,12 +242,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     const int t0 = c * kC;
     const int rows = min(kC, sq.len - t0);
     const int64_t tok0 = int64_t(sq.bos) + t0;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int idx = tid + i * kFwdThreads, r = idx / 8, ch = idx % 8;
-      pf.x[i] = make_uint4(0, 0, 0, 0);
-      if (r < rows) pf.x[i] = *reinterpret_cast<const uint4*>(p.X + ((tok0 + r) * p.HV + hv) * kC + ch * 8);
-    }
     if (kside) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -296,11 +292,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
   };
   auto store_panels = [&]() {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int idx = tid + i * kFwdThreads;
-      *reinterpret_cast<uint4*>(smem + kOffX + panel_chunk_off(idx / 8, idx % 8)) = pf.x[i];
-    }
-#pragma unroll
     for (int i = 0; i < 4; ++i) vcur[i] = pf.v[i];
   };
 
@@ -311,6 +302,11 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     tma_load_tile(sb + kOffQK + kQKPanel, &tm_q, 64, hk, row0, &qk_bar);
     tma_load_tile(sb + kOffQK + 8192, &tm_k, 0, hk, row0, &qk_bar);
     tma_load_tile(sb + kOffQK + kQKPanel + 8192, &tm_k, 64, hk, row0, &qk_bar);
+  };
+
+  auto issue_x_load = [&](int c) {    // one thread: the chunk's 64 x 64 inverse
+    mbar_arrive_expect_tx(&x_bar, 8192);
+    tma_load_tile(sb + kOffX, &tm_x, 0, hv, sq.bos + c * kC, &x_bar);
   };
 
   // operands (shared addresses)
@@ -325,7 +321,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
   float srow[32];   // this thread's 32 columns of the fp32 state row
 
   // ---- prologue: chunk 0 operands and the initial state
-  if (tid == 0) issue_qk_load(0);
+  if (tid == 0) {
+    issue_qk_load(0);
+    issue_x_load(0);
+  }
   prefetch_load(0);
   prefetch_scalars(0);
   store_scalars(0);
@@ -417,17 +416,24 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     STAMP(2);
     // ---- stage 3: v_new = X Z  (rows 64..127 of the accumulator)
     if (tid == 0) {
+      if (!mbar_wait(&x_bar, xphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // the X tile has landed
       mma_tile(tbase + kColVN, opX, opZH, 128, 64, 4, false);
       mma_tile(tbase + kColVN, opX, opZL, 128, 64, 4, true);
       mma_commit(&bar);
     }
+    xphase ^= 1;
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
+    if (tid == 0 && c + 1 < sq.nt) issue_x_load(c + 1);
 
     STAMP(3);
     // ---- stage 4: k-side rows publish v_new and its decayed copy
     if (kside) {
       tmem_ld_row32(trow + kColVN, acc);
+      if (tok >= rows) {   // rows of the X tile past the end of the sequence belong to whatever follows in memory
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+      }
       row32_to_hilo(smem + kOffZH, smem + kOffZL, tok, half, acc);
       const float dk = __expf(gam_last - gam_i);
 #pragma unroll
@@ -642,13 +648,14 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
     TriInverseParams tp{p.at, p.X, nullptr, nullptr, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, 0};
     if (launch_tri_inverse(tp, nt_max, N, cs)) return FLA_ERR_CUDA;
   }
-  CUtensorMap tm_q, tm_k;
+  CUtensorMap tm_q, tm_k, tm_x;
   if (make_row_tile_map(&tm_q, p.q, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.q_sh), uint64_t(p.q_st)) ||
-      make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)))
+      make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)) ||
+      make_row_tile_map(&tm_x, p.X, kC, uint64_t(HV), uint64_t(B * T), uint64_t(kC), uint64_t(HV) * kC))
     return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_fwd", cs);
-    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p, tm_q, tm_k);
+    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
   }
   return cuda_status(cudaGetLastError());
 }
