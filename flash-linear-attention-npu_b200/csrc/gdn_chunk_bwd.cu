@@ -36,7 +36,7 @@ struct GdnBwdParams {
   const float* gam; const bf16* X;
   const bf16* s_img; const bf16* vn_img; const bf16* p_img;
   bf16* ds_img;        // [chunks, HV, 2, 2, 128x64]  state gradient entering each chunk (hi, lo)
-  bf16* dz_img;        // [chunks, HV, 2, {128x64 hi: rows 0-63 dO, rows 64-127 dZ_hi ; 64x64 dZ_lo}]
+  bf16* dz_img;        // [chunks, HV, 2, 128x64: rows 0-63 dO, rows 64-127 dZ rounded to bf16]
   float* bz;           // [4, tokens, HV] partial sums of dZ * V over the four 32-column slices of V
   const float* dht; float* dh0;
   void* dq; void* dk; void* dv; void* dg; void* dbeta;
@@ -51,7 +51,7 @@ struct GdnBwdParams {
 
 constexpr int64_t kSImg = 32768;   // bf16 elements of the state images per (chunk, head): 2 blocks x (hi, lo) x 128x64
 constexpr int64_t kVnImg = 16384;  // v_new images per (chunk, head): 2 x (hi, lo) x 64x64
-constexpr int64_t kDzImg = 24576;  // per (chunk, head): 2 x (128x64 hi + 64x64 lo)
+constexpr int64_t kDzImg = 16384;  // per (chunk, head): 2 x (64x64 dO + 64x64 dZ), single bf16
 
 // ============================================================================================= dhu
 constexpr uint32_t hOffQK = 0, hQKPanel = 16384;
@@ -283,7 +283,10 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
 #pragma unroll
         for (int j = 0; j < 8; ++j) bzsum += acc[i * 8 + j] * vv[j];
       }
-      row32_to_hilo(smem + hOffPH, smem + hOffPL, tok, half, acc);
+      // dZ for the second kernel as one bf16: its residual only enters products whose other factor is itself split,
+      // where dropping it costs a few 1e-4 (dk 1.3e-3 -> 1.6e-3 in emulation) and saves a pass and 8 KB per block
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(smem + hOffPH + panel_chunk_off(tok, half * 4 + ch)) = pack8(acc + ch * 8);
       if (tok < rows) {
         p.bz[(int64_t(vb * 2 + half) * p.total_tokens + tok0 + tok) * p.HV + hv] = bzsum;
         const int64_t off = (tok0 + tok) * p.dv_st + hv * p.dv_sh + vb * kBV + c0;
@@ -325,9 +328,9 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
 
     // ---- stage 7: dS += [Q^T | K^T] [scale e^gam dO ; -beta e^gam dZ]
     if (tid == 0) {
-      bf16* dst = p.dz_img + (cidx * 2 + vb) * 12288;
-      bulk_store(dst, sb + hOffDO, 8192);            // rows 0..63 of the hi image: dO
-      bulk_store(dst + 4096, sb + hOffPH, 16384);    // rows 64..127: dZ hi, then the dZ lo image
+      bf16* dst = p.dz_img + (cidx * 2 + vb) * 8192;
+      bulk_store(dst, sb + hOffDO, 8192);            // rows 0..63 of the image: dO
+      bulk_store(dst + 4096, sb + hOffPH, 8192);     // rows 64..127: dZ
       bulk_commit();
       mma_tile(tbase + hColDS, opQKT, opDSH, 128, 64, 8, true);
       mma_tile(tbase + hColDS, opQKT, opDSL, 128, 64, 8, true);
@@ -366,13 +369,13 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
 // ============================================================================================= par
 constexpr uint32_t rOffQK = 0, rQKPanel = 16384;
 constexpr uint32_t rOffAH = 32768;             // [dO ; dZ_hi] rows of one V block (128 rows)
-constexpr uint32_t rOffAL = 49152;             // rows 0-63 zero, rows 64-127 dZ_lo
+constexpr uint32_t rOffPad = 49152;            // 16 KB whose contents do not matter: the rows 0-63 of the Vn-as-A operand
 constexpr uint32_t rOffVNH = 65536, rOffVNL = 73728;
 constexpr uint32_t rOffSH = 81920, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 131072;
 constexpr uint32_t rOffPAH = 147456, rOffPAL = 163840;   // [dP ; dAt] hi / lo (128 rows x 64)
 constexpr uint32_t kParSmem = 180224;
 constexpr uint32_t rColQK = 0, rColDV = 64, rColTA = 128, rColTB = 256;
-constexpr uint32_t kStepBytes = 16384 + 8192 + 16384 + 32768 + 32768;
+constexpr uint32_t kStepBytes = 16384 + 16384 + 32768 + 32768;
 
 __device__ __forceinline__ void row_dot64(const uint8_t* pan0, uint32_t panel_stride, int row, int col0, const float* x,
                                           float& acc) {
@@ -430,9 +433,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
   auto issue_loads = [&](int hv, int vb) {  // one thread: operands of one (value head, V block) step
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
     mbar_arrive_expect_tx(&load_bar, kStepBytes);
-    const bf16* dz = p.dz_img + (cidx * 2 + vb) * 12288;
-    bulk_load(sb + rOffAH, dz, 16384, &load_bar);
-    bulk_load(sb + rOffAL + 8192, dz + 8192, 8192, &load_bar);
+    bulk_load(sb + rOffAH, p.dz_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
     bulk_load(sb + rOffVNH, p.vn_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
     bulk_load(sb + rOffSH, p.s_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
     bulk_load(sb + rOffDSH, p.ds_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
@@ -452,7 +453,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     }
   };
   prefetch_scalars(hk * G);
-  // q, k rows of the chunk (shared by the value heads of the group) and the static zero rows of the lo operand
+  // q, k rows of the chunk (shared by the value heads of the group)
   {
     uint4 val[8];   // all loads in flight before the first one is consumed
 #pragma unroll
@@ -472,7 +473,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
       *reinterpret_cast<uint4*>(smem + rOffQK + (ch / 8) * rQKPanel + panel_chunk_off(r + (isk ? 64 : 0), ch % 8)) = val[i];
     }
   }
-  for (int idx = tid; idx < 512; idx += 256) *reinterpret_cast<uint4*>(smem + rOffAL + idx * 16) = make_uint4(0, 0, 0, 0);
   fence_async_smem();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
@@ -484,7 +484,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
   const Operand opKb{sb + rOffQK + 8192, rQKPanel, 0};               // k as B, N = 64 tokens
   const Operand opKn{sb + rOffQK + 8192, rQKPanel, 1};               // k as B, N = 128 key dims, reduction over tokens
   const Operand opQKn{sb + rOffQK, rQKPanel, 1};                     // [q; k] as B, N = 128 key dims, reduction over 128 rows
-  const Operand opAH{sb + rOffAH, 16384, 0}, opAL{sb + rOffAL, 16384, 0};
+  const Operand opAH{sb + rOffAH, 16384, 0};
   const Operand opVNbH{sb + rOffVNH, 8192, 0}, opVNbL{sb + rOffVNL, 8192, 0};            // Vn as B (N = 64 tokens)
   const Operand opVNaH{sb + rOffVNH - 8192, 8192, 0}, opVNaL{sb + rOffVNL - 8192, 8192, 0};  // Vn as A, valid rows 64..127
   const Operand opSH{sb + rOffSH, 16384, 0}, opSL{sb + rOffSL, 16384, 0};                // S block as B (N = 128 key dims)
@@ -517,10 +517,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
         const bool accf = vb > 0;
         mma_tile(tbase + rColDV, opAH, opVNbH, 128, 64, 4, accf);
         mma_tile(tbase + rColDV, opAH, opVNbL, 128, 64, 4, true);
-        mma_tile(tbase + rColDV, opAL, opVNbH, 128, 64, 4, true);
         mma_tile(tbase + rColTA, opAH, opSH, 128, 128, 4, accf);
         mma_tile(tbase + rColTA, opAH, opSL, 128, 128, 4, true);
-        mma_tile(tbase + rColTA, opAL, opSH, 128, 128, 4, true);
         mma_tile(tbase + rColTB, opVNaH, opDSH, 128, 128, 4, accf);
         mma_tile(tbase + rColTB, opVNaH, opDSL, 128, 128, 4, true);
         mma_tile(tbase + rColTB, opVNaL, opDSH, 128, 128, 4, true);
