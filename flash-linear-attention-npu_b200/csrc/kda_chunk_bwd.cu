@@ -814,7 +814,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   f.q_st = a->q.stride[1]; f.q_sh = a->q.stride[2]; f.k_st = a->k.stride[1]; f.k_sh = a->k.stride[2];
   f.v_st = a->v.stride[1]; f.v_sh = a->v.stride[2];
   f.g_st = a->g.stride[1]; f.g_sh = a->g.stride[2]; f.beta_st = a->beta.stride[1];
-  f.N = N; f.T = int(T); f.HK = int(HK); f.HV = int(HV);
+  f.N = N; f.T = int(T); f.HK = int(HK); f.HV = int(HV); f.total_tokens = B * T;
   f.g_is_f32 = a->g.dtype == FLA_F32; f.beta_is_f32 = a->beta.dtype == FLA_F32;
   f.gate_mode = 0; f.scale = a->scale;
 

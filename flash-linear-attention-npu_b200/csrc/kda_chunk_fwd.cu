@@ -17,6 +17,7 @@
 #include "kernel_timer.h"
 #include "tri_inverse.h"
 #include "kda_common.cuh"
+#include "tensor_map.h"
 
 namespace fla {
 
@@ -35,13 +36,16 @@ __device__ __forceinline__ float kda_gate(float g, int mode, float eig, float bi
 }
 
 // Thread layout of the elementwise phases: 16 channel groups (8 channels each) x 16 token segments (4 tokens each).
-__global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p) {
+// The raw q and k rows arrive as TMA tiles in the residual panels (where each thread later overwrites exactly the
+// 16-byte pieces it read), so their latency is hidden behind the gate phases.
+__global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                          const __grid_constant__ CUtensorMap tm_k) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float tot_s[16][kK];          // gate sum of each token segment, per channel
   __shared__ float anchor_s[kK], last_s[kK];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar;
+  __shared__ __align__(8) uint64_t bar, qk_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int hv = blockIdx.y, n = blockIdx.z;
@@ -61,7 +65,15 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p) {
   }
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&qk_bar, 1);
     mbar_init_fence();
+    const uint32_t sbq = smem_u32(smem);
+    const int row0 = int(tok0);
+    mbar_arrive_expect_tx(&qk_bar, 4 * 8192);
+    tma_load_tile(sbq + pOffQKL, &tm_q, 0, hk, row0, &qk_bar);                  // q rows -> rows 0-63 of the lo panels
+    tma_load_tile(sbq + pOffQKL + 16384, &tm_q, 64, hk, row0, &qk_bar);
+    tma_load_tile(sbq + pOffQKL + 8192, &tm_k, 0, hk, row0, &qk_bar);           // k rows -> rows 64-127
+    tma_load_tile(sbq + pOffQKL + 16384 + 8192, &tm_k, 64, hk, row0, &qk_bar);
   }
   // 1. activated gates of my 4 tokens x 8 channels, prefix-summed inside the segment (zero past the sequence end)
   float gk[4][8];
@@ -136,14 +148,15 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) an[j] = anchor_s[r0 + j];
     const uint32_t pan = (cg / 8) * 16384, pan64 = (cg / 8) * 8192;
+    const bool landed = mbar_wait(&qk_bar, 0, p.status, FLA_ERR_TIMEOUT);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = seg * 4 + i;
       float qv[8], kv[8], qp[8], kp[8], kn[8];
       uint4 qraw = make_uint4(0, 0, 0, 0), kraw = qraw;
-      if (t < rows) {
-        qraw = *reinterpret_cast<const uint4*>(p.q + (tok0 + t) * p.q_st + hk * p.q_sh + r0);
-        kraw = *reinterpret_cast<const uint4*>(p.k + (tok0 + t) * p.k_st + hk * p.k_sh + r0);
+      if (t < rows && landed) {   // rows past the end of the sequence hold foreign tokens in the tile: use zeros
+        qraw = *reinterpret_cast<const uint4*>(smem + pOffQKL + pan + panel_chunk_off(t, cg % 8));
+        kraw = *reinterpret_cast<const uint4*>(smem + pOffQKL + pan + panel_chunk_off(64 + t, cg % 8));
       }
       unpack_bf16x8(qraw, qv);
       unpack_bf16x8(kraw, kv);
@@ -642,7 +655,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   p.q_st = a->q.stride[1]; p.q_sh = a->q.stride[2]; p.k_st = a->k.stride[1]; p.k_sh = a->k.stride[2];
   p.v_st = a->v.stride[1]; p.v_sh = a->v.stride[2]; p.o_st = a->o.stride[1]; p.o_sh = a->o.stride[2];
   p.g_st = a->g.stride[1]; p.g_sh = a->g.stride[2]; p.beta_st = be.stride[1];
-  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV);
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.total_tokens = B * T;
   p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = be.dtype == FLA_F32; p.o_is_f32 = a->o.dtype == FLA_F32;
   p.gate_mode = a->gate_mode; p.scale = a->scale; p.lower_bound = a->lower_bound;
 
@@ -660,9 +673,13 @@ int fla::kda_launch_forward(const KdaParams& p, int nt_max, cudaStream_t cs) {
     if (cudaFuncSetAttribute(kda_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
+  CUtensorMap tm_q, tm_k;
+  if (make_row_tile_map(&tm_q, p.q, kK, uint64_t(p.HK), uint64_t(p.total_tokens), uint64_t(p.q_sh), uint64_t(p.q_st)) ||
+      make_row_tile_map(&tm_k, p.k, kK, uint64_t(p.HK), uint64_t(p.total_tokens), uint64_t(p.k_sh), uint64_t(p.k_st)))
+    return FLA_ERR_CUDA;
   {
     KernelTimer kt("kda_prep", cs);
-    kda_prep_kernel<<<dim3(nt_max, unsigned(p.HV), p.N), 256, kKdaPrepSmem + 1024, cs>>>(p);
+    kda_prep_kernel<<<dim3(nt_max, unsigned(p.HV), p.N), 256, kKdaPrepSmem + 1024, cs>>>(p, tm_q, tm_k);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {

@@ -21,6 +21,7 @@ struct KdaParams {
   void* o;              // may be null when only the saved images are wanted
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int64_t q_st, q_sh, k_st, k_sh, v_st, v_sh, o_st, o_sh, g_st, g_sh, beta_st;
+  int64_t total_tokens;   // rows of the flat [tokens, heads, dim] views
   int N, T, HK, HV, g_is_f32, beta_is_f32, o_is_f32, gate_mode;
   float scale, lower_bound;
   int* status;
