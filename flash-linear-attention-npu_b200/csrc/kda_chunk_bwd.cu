@@ -24,6 +24,7 @@
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
 #include "kda_common.cuh"
+#include "tensor_map.h"
 
 namespace fla {
 
@@ -342,11 +343,13 @@ constexpr uint32_t qOffAL = 114688;             // rows 0-63 zero, rows 64-127 d
 constexpr uint32_t qOffVNH = 131072, qOffVNL = 139264;
 constexpr uint32_t qOffSH = 147456, qOffSL = 163840, qOffDSH = 180224, qOffDSL = 196608;
 constexpr uint32_t qOffPAH = qOffAH, qOffPAL = qOffAL;   // [dP ; dM] hi / lo reuse the [dO ; dZ] panels
-constexpr uint32_t qOffTile = qOffAH;           // three fp32 [64][129] tiles of the dg assembly reuse the step buffers
+constexpr uint32_t qOffTile = qOffAH;           // two fp32 [64][132] tiles of the dg assembly reuse the step buffers
 constexpr uint32_t kKdaParSmem = 212992;
 constexpr int kTileStride = 132;   // 16-byte aligned rows; float4 row stores and scalar column reads are both conflict-free
 constexpr uint32_t kTileBytes = kC * kTileStride * 4;
-static_assert(qOffTile + 3 * kTileBytes <= kKdaParSmem, "dg tiles must fit in the step buffers");
+constexpr uint32_t qOffGk = 165888;             // the chunk's gk rows: four 64 x 32 fp32 TMA tiles (swizzled), 32 KB
+static_assert(qOffTile + 2 * kTileBytes <= qOffGk && qOffGk % 1024 == 0 && qOffGk + 32768 <= kKdaParSmem &&
+              qOffGk >= qOffSL, "dg tiles and the gk tile must fit in the phase-1 step buffers behind the [dP; dM] panels");
 constexpr uint32_t qColQK = 0, qColDV = 64, qColTA = 128, qColTB1 = 256, qColTB2 = 384;
 constexpr uint32_t kKdaStepBytes = 16384 + 8192 + 16384 + 32768 + 32768;
 
@@ -359,15 +362,57 @@ __device__ __forceinline__ void chunk_vals(const uint8_t* pan_hi, const uint8_t*
   for (int j = 0; j < 8; ++j) f[j] += lo[j];
 }
 
-__global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
+#ifdef FLA_STAGE_CLOCKS
+__device__ long long g_kpar_clocks[16];
+#define KSTAMP(i) do { long long now_ = clock64(); kclk_[i] += now_ - klast_; klast_ = now_; } while (0)
+#else
+#define KSTAMP(i)
+#endif
+
+// Sum over the 32 lanes (rows) of each of 32 per-lane values (columns): lane l ends up with the total of column l.
+// Recursive halving: at every step a lane keeps one half of its values and hands the other half to its partner.
+__device__ __forceinline__ float warp_column_sums32(const float* v, int lane) {
+  float a[16], b[8], c[4], d[2];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float send = (lane & 16) ? v[i] : v[16 + i], keep = (lane & 16) ? v[16 + i] : v[i];
+    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float send = (lane & 8) ? a[i] : a[8 + i], keep = (lane & 8) ? a[8 + i] : a[i];
+    b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float send = (lane & 4) ? b[i] : b[4 + i], keep = (lane & 4) ? b[4 + i] : b[i];
+    c[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float send = (lane & 2) ? c[i] : c[2 + i], keep = (lane & 2) ? c[2 + i] : c[i];
+    d[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+  const float send = (lane & 1) ? d[0] : d[1], keep = (lane & 1) ? d[1] : d[0];
+  return keep + __shfl_xor_sync(0xffffffffu, send, 1);
+}
+
+// The chunk's gk rows arrive as TMA tiles once the phase-1 buffers are free; the last epilogue reads them from
+// shared memory (their global loads used to sit, one round trip each, on the critical path).
+__global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, const __grid_constant__ CUtensorMap tm_gk) {
+#ifdef FLA_STAGE_CLOCKS
+  long long kclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long klast_ = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float beta_s[kC], anchor_s[kK];
   __shared__ float red[2][2][kC];      // rkG, ma : [half][row]
   __shared__ float sds_s[2][kK];       // sum_v dS'a * Sa per key channel, by column half
-  __shared__ float colsum_s[4][kK];    // per 32-row part: column sums of the dgk tiles and of the last-row tile
+  __shared__ float colsum_s[2][kK];    // per 32-row part: column sums of the dgk tiles
+  __shared__ float t1col_s[2][kK];     // per 32-row quadrant: sum_i Kn_i (Vn dS'a^T)_i of the last-row term
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar, load_bar, img_bar;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar, img_bar, gk_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int hk = blockIdx.y, n = blockIdx.z;
@@ -391,13 +436,15 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
     mbar_init(&mma_bar, 1);
     mbar_init(&load_bar, 1);
     mbar_init(&img_bar, 1);
+    mbar_init(&gk_bar, 1);
     mbar_init_fence();
+    tma_prefetch_descriptor(&tm_gk);
   }
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, quad * 32, 0);
   const uint32_t sb = smem_u32(smem);
-  uint32_t mphase = 0, lphase = 0, iphase = 0;
+  uint32_t mphase = 0, lphase = 0, iphase = 0, gphase = 0;
   bool ok = true;
 
   auto issue_images = [&](int hv) {           // one thread: [Qp; Kp] and Kn of one value head
@@ -434,7 +481,6 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
   for (int i = 0; i < 64; ++i) acc_out[i] = 0.f;
   float* tile_q = reinterpret_cast<float*>(smem + qOffTile);
   float* tile_k = reinterpret_cast<float*>(smem + qOffTile + kTileBytes);
-  float* tile_1 = reinterpret_cast<float*>(smem + qOffTile + 2 * kTileBytes);
 
   for (int h = 0; h < G && ok; ++h) {
     const int hv = hk * G + h;
@@ -450,6 +496,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
       issue_loads(hv, 0);
     }
     float sds = 0.f;   // my key channel (tid & 127), my 32 columns (tid >> 7) of sum_v dS'a * Sa
+    KSTAMP(0);
     for (int vb = 0; vb < 2; ++vb) {
       if (vb == 0) {
         ok = mbar_wait(&img_bar, iphase, p.status, FLA_ERR_TIMEOUT);
@@ -458,6 +505,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
       ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT) && ok;
       lphase ^= 1;
       if (!__syncthreads_and(ok)) { ok = false; break; }
+      KSTAMP(1);
       if (tid == 0) {
         tc_fence_after();
         if (vb == 0) {
@@ -489,15 +537,26 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
           for (int j = 0; j < 8; ++j) sds += s[j] * d[j];
         }
       }
+      KSTAMP(2);
       ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
       mphase ^= 1;
       if (!__syncthreads_and(ok)) { ok = false; break; }   // also: every thread is done reading the step's buffers
+      KSTAMP(3);
       tc_fence_after();
-      if (tid == 0 && vb == 0) issue_loads(hv, 1);
+      if (tid == 0) {
+        if (vb == 0) {
+          issue_loads(hv, 1);
+        } else {   // the phase-1 buffers are free: this head's gk rows, channels 32 b .. 32 b + 31 in tile b
+          mbar_arrive_expect_tx(&gk_bar, 4 * 8192);
+#pragma unroll
+          for (int b = 0; b < 4; ++b) tma_load_tile(sb + qOffGk + b * 8192, &tm_gk, 32 * b, hv, int(tok0), &gk_bar);
+        }
+      }
     }
     if (!ok) break;
     sds_s[tid >> 7][tid & 127] = sds;
 
+    KSTAMP(4);
     // ---- epilogue 1: score-tile gradients -> [dP; dM] operand; row scaling of the first TA product in place
     const float beta_i = beta_s[tok];
     float ma_part = 0.f, rkG = 0.f;
@@ -554,6 +613,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
     tc_fence_before();
     __syncthreads();
 
+    KSTAMP(5);
     // ---- TA += [dP; dM] Kn   and   TB2 = [dP^T | dM^T] [Qp; Kp]
     if (tid == 0) {
       tc_fence_after();
@@ -580,11 +640,13 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
     if (!__syncthreads_and(ok)) { ok = false; break; }
     tc_fence_after();
 
+    KSTAMP(6);
     // ---- epilogue 2: dq / dk rows of this head and the three dg tiles (the step buffers are free now)
     {
       const int pan = half;   // my 64 key dims are panel `half` of the 128-wide images
-      const float* gkrow = p.gk + ((tok0 + min(tok, rows - 1)) * p.HV + hv) * kK + half * 64;
       const bool live = tok < rows;
+      ok = mbar_wait(&gk_bar, gphase, p.status, FLA_ERR_TIMEOUT) && ok;
+      gphase ^= 1;
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
         float x[32];
@@ -595,8 +657,9 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
           for (int ch = 0; ch < 4; ++ch) {
             float qp[8];
             chunk_vals(smem + qOffQKH + pan * 16384, smem + qOffQKL + pan * 16384, tok, sub * 4 + ch, qp);
-            const float4 g0 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8);
-            const float4 g1 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8 + 4);
+            const uint8_t* gt = smem + qOffGk + (half * 2 + sub) * 8192 + tok * 128;
+            const float4 g0 = *reinterpret_cast<const float4*>(gt + (((2 * ch) ^ (tok & 7)) << 4));
+            const float4 g1 = *reinterpret_cast<const float4*>(gt + (((2 * ch + 1) ^ (tok & 7)) << 4));
             const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
             float tq[8];
 #pragma unroll
@@ -612,7 +675,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
             *reinterpret_cast<float4*>(dq_ + 4) = make_float4(tq[4], tq[5], tq[6], tq[7]);
           }
         } else {
-          float y1[32], y2[32];
+          float y1[32], y2[32], t1v[32];
           tmem_ld32(trow + qColTB1 + half * 64 + sub * 32, y1);
           tmem_ld32(trow + qColTB2 + half * 64 + sub * 32, y2);
           tmem_ld_wait();
@@ -621,10 +684,11 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
             float kp[8], kn[8];
             chunk_vals(smem + qOffQKH + pan * 16384, smem + qOffQKL + pan * 16384, 64 + tok, sub * 4 + ch, kp);
             chunk_vals(smem + qOffKNH + pan * 8192, smem + qOffKNL + pan * 8192, tok, sub * 4 + ch, kn);
-            const float4 g0 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8);
-            const float4 g1 = *reinterpret_cast<const float4*>(gkrow + sub * 32 + ch * 8 + 4);
+            const uint8_t* gt = smem + qOffGk + (half * 2 + sub) * 8192 + tok * 128;
+            const float4 g0 = *reinterpret_cast<const float4*>(gt + (((2 * ch) ^ (tok & 7)) << 4));
+            const float4 g1 = *reinterpret_cast<const float4*>(gt + (((2 * ch + 1) ^ (tok & 7)) << 4));
             const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            float tk[8], tl[8];
+            float tk[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int col = sub * 32 + ch * 8 + j;
@@ -633,35 +697,31 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
               const float dkp = x[ch * 8 + j], t1 = y1[ch * 8 + j], dkn = t1 + y2[ch * 8 + j];
               acc_out[col] += live ? dkp * e1 + dkn * e2 : 0.f;
               tk[j] = live ? kp[j] * dkp - kn[j] * dkn : 0.f;
-              tl[j] = live ? kn[j] * t1 : 0.f;
+              t1v[ch * 8 + j] = live ? kn[j] * t1 : 0.f;
             }
             float* dk_ = tile_k + tok * kTileStride + half * 64 + sub * 32 + ch * 8;
-            float* dl_ = tile_1 + tok * kTileStride + half * 64 + sub * 32 + ch * 8;
             *reinterpret_cast<float4*>(dk_) = make_float4(tk[0], tk[1], tk[2], tk[3]);
             *reinterpret_cast<float4*>(dk_ + 4) = make_float4(tk[4], tk[5], tk[6], tk[7]);
-            *reinterpret_cast<float4*>(dl_) = make_float4(tl[0], tl[1], tl[2], tl[3]);
-            *reinterpret_cast<float4*>(dl_ + 4) = make_float4(tl[4], tl[5], tl[6], tl[7]);
           }
+          // last-row term: column sums of Kn * (Vn dS'a^T) over my warp's 32 rows
+          t1col_s[quad - 2][half * 64 + sub * 32 + lane] = warp_column_sums32(t1v, lane);
         }
       }
     }
+    KSTAMP(7);
     tc_fence_before();
-    __syncthreads();
+    if (!__syncthreads_and(ok)) { ok = false; break; }
     // dg = reverse chunk-local cumulative sum of dgk; the last row additionally carries
     // sum_v dS'a Sa + sum_i Kn_i (Vn dS'a^T)_i, which therefore reaches every row.
     {
       // Two threads per key channel, 32 rows each: local totals first, then the suffix sums with the loads unrolled.
       const int kc = tid & (kK - 1), part = tid >> 7, r0 = part * 32;
-      float tot = 0.f, t1 = 0.f;
+      float tot = 0.f;
 #pragma unroll 8
-      for (int i = 0; i < 32; ++i) {
-        tot += tile_q[(r0 + i) * kTileStride + kc] + tile_k[(r0 + i) * kTileStride + kc];   // rows past the end hold zeros
-        t1 += tile_1[(r0 + i) * kTileStride + kc];
-      }
+      for (int i = 0; i < 32; ++i) tot += tile_q[(r0 + i) * kTileStride + kc] + tile_k[(r0 + i) * kTileStride + kc];   // rows past the end hold zeros
       colsum_s[part][kc] = tot;
-      colsum_s[2 + part][kc] = t1;
       __syncthreads();
-      float run = sds_s[0][kc] + sds_s[1][kc] + colsum_s[2][kc] + colsum_s[3][kc] + (part == 0 ? colsum_s[1][kc] : 0.f);
+      float run = sds_s[0][kc] + sds_s[1][kc] + t1col_s[0][kc] + t1col_s[1][kc] + (part == 0 ? colsum_s[1][kc] : 0.f);
 #pragma unroll 8
       for (int i = 31; i >= 0; --i) {
         const int t = r0 + i;
@@ -676,6 +736,11 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p) {
     __syncthreads();
   }
 
+  KSTAMP(8);
+#ifdef FLA_STAGE_CLOCKS
+  if (tid == FLA_STAGE_THREAD && blockIdx.x == 100 && blockIdx.y == 7 && blockIdx.z == 2)
+    for (int i = 0; i < 12; ++i) g_kpar_clocks[i] += kclk_[i];
+#endif
   if (ok && tok < rows) {
     void* base = kside ? p.dk : p.dq;
     const int64_t off = kside ? (tok0 + tok) * p.dk_st + hk * p.dk_sh + half * 64 : (tok0 + tok) * p.dq_st + hk * p.dq_sh + half * 64;
@@ -853,9 +918,17 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
     kda_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), 256, kKdaDhuSmem + 1024, cs>>>(p);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  CUtensorMap tm_gk;
+  if (make_row_tile_map_f32(&tm_gk, p.gk, kK, uint64_t(HV), uint64_t(B * T), uint64_t(kK), uint64_t(HV) * kK)) return FLA_ERR_CUDA;
   {
     KernelTimer kt("kda_bwd_par", cs);
-    kda_bwd_par_kernel<<<dim3(nt_max, unsigned(HK), N), 256, kKdaParSmem + 1024, cs>>>(p);
+    kda_bwd_par_kernel<<<dim3(nt_max, unsigned(HK), N), 256, kKdaParSmem + 1024, cs>>>(p, tm_gk);
   }
   return cuda_status(cudaGetLastError());
 }
+
+#ifdef FLA_STAGE_CLOCKS
+extern "C" FLA_API int fla_b200_debug_kda_par_clocks(long long* out16) {
+  return cudaMemcpyFromSymbol(out16, fla::g_kpar_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
+}
+#endif

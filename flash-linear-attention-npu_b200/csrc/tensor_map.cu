@@ -20,18 +20,27 @@ void resolve() {
 }
 }  // namespace
 
-int make_row_tile_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t heads, uint64_t rows,
-                      uint64_t head_stride, uint64_t row_stride) {
+static int encode(CUtensorMap* map, CUtensorMapDataType dt, uint64_t esz, uint32_t box_cols, const void* base, uint64_t cols,
+                  uint64_t heads, uint64_t rows, uint64_t head_stride, uint64_t row_stride) {
   std::call_once(g_once, resolve);
   if (!g_encode) return 6;
   const cuuint64_t dims[3] = {cols, heads, rows};
-  const cuuint64_t strides[2] = {head_stride * 2, row_stride * 2};   // bytes, dims 1 and 2
-  const cuuint32_t box[3] = {64, 1, 64};
+  const cuuint64_t strides[2] = {head_stride * esz, row_stride * esz};   // bytes, dims 1 and 2
+  const cuuint32_t box[3] = {box_cols, 1, 64};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = g_encode(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 6;
+}
+
+int make_row_tile_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t heads, uint64_t rows,
+                      uint64_t head_stride, uint64_t row_stride) {
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 64, base, cols, heads, rows, head_stride, row_stride);
+}
+
+int make_row_tile_map_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t heads, uint64_t rows,
+                          uint64_t head_stride, uint64_t row_stride) {
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, 32, base, cols, heads, rows, head_stride, row_stride);
 }
 
 }  // namespace fla

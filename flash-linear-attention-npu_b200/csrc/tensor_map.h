@@ -13,6 +13,10 @@ namespace fla {
 int make_row_tile_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t heads, uint64_t rows,
                       uint64_t head_stride, uint64_t row_stride);
 
+// fp32 tensor viewed as [rows][heads][cols]: boxes of 64 rows x 1 head x 32 columns (128 bytes), same swizzle.
+int make_row_tile_map_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t heads, uint64_t rows,
+                          uint64_t head_stride, uint64_t row_stride);
+
 #ifdef __CUDACC__
 // One 64 x 64 bf16 box (8 KB) at (col0, head, row0) -> shared memory; completes `bytes` on the mbarrier.
 // col0 must be a multiple of 8 elements (16 bytes); rows past the tensor's end read as zero.  No multicast.
