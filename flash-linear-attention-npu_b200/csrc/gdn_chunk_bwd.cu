@@ -392,24 +392,30 @@ __device__ __forceinline__ void row_dot64(const uint8_t* pan0, uint32_t panel_st
 
 #ifdef FLA_STAGE_CLOCKS
 __device__ long long g_par_clocks[16];
+#ifndef FLA_STAGE_THREAD
+#define FLA_STAGE_THREAD 0
+#endif
 #define PSTAMP(i) do { long long now_ = clock64(); pclk_[i] += now_ - plast_; plast_ = now_; } while (0)
 #else
 #define PSTAMP(i)
 #endif
 
-__global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
+__global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                                const __grid_constant__ CUtensorMap tm_k) {
 #ifdef FLA_STAGE_CLOCKS
   long long pclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
   long long plast_ = clock64();
 #endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ float gam_s[kC], beta_s[kC];
-  __shared__ float red[5][2][kC];      // qdq, kdk, rkG, rkB, ma : [half][row]
-  __shared__ float sds_s[8];
-  __shared__ float dgam_s[kC];
+  // per-head row scalars and row reductions, double-buffered by head parity: the dg / dbeta rows of a head are
+  // finished while the tensor cores work on the next head
+  __shared__ float gam_s2[2][kC], beta_s2[2][kC];
+  __shared__ float red2[2][5][2][kC];  // qdq, kdk, rkG, rkB, ma : [half][row]
+  __shared__ float sds_s2[2][8];
+  __shared__ float fin_s[2][2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar, load_bar;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar, qk_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int hk = blockIdx.y, n = blockIdx.z;
@@ -441,8 +447,17 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
     mbar_init(&load_bar, 1);
+    mbar_init(&qk_bar, 1);
     mbar_init_fence();
-    issue_loads(hk * G, 0);   // the first step's operands travel while the q, k rows are staged
+    // q, k rows of the chunk (shared by the value heads of the group): four 64 x 64 tiles into the [q; k] panels.
+    // Rows past the end of the sequence hold whatever follows in memory; every product with them meets a zero
+    // row or column of dO, dZ, v_new or the masked score gradients, and those rows are never stored.
+    mbar_arrive_expect_tx(&qk_bar, 32768);
+    tma_load_tile(sb + rOffQK, &tm_q, 0, hk, int(tok0), &qk_bar);
+    tma_load_tile(sb + rOffQK + 8192, &tm_k, 0, hk, int(tok0), &qk_bar);
+    tma_load_tile(sb + rOffQK + rQKPanel, &tm_q, 64, hk, int(tok0), &qk_bar);
+    tma_load_tile(sb + rOffQK + rQKPanel + 8192, &tm_k, 64, hk, int(tok0), &qk_bar);
+    issue_loads(hk * G, 0);
   }
   // per-row scalars of the first value head (later heads: fetched one head ahead)
   float pf_gam = 0.f, pf_beta = 0.f;
@@ -453,26 +468,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     }
   };
   prefetch_scalars(hk * G);
-  // q, k rows of the chunk (shared by the value heads of the group)
-  {
-    uint4 val[8];   // all loads in flight before the first one is consumed
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * 256, r = (idx / 16) & 63, ch = idx % 16;
-      const bool isk = idx >= 1024;
-      val[i] = make_uint4(0, 0, 0, 0);
-      if (r < rows) {
-        const bf16* src = isk ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
-        val[i] = *reinterpret_cast<const uint4*>(src + ch * 8);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * 256, r = (idx / 16) & 63, ch = idx % 16;
-      const bool isk = idx >= 1024;
-      *reinterpret_cast<uint4*>(smem + rOffQK + (ch / 8) * rQKPanel + panel_chunk_off(r + (isk ? 64 : 0), ch % 8)) = val[i];
-    }
-  }
   fence_async_smem();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
@@ -496,20 +491,75 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
 #pragma unroll
   for (int i = 0; i < 64; ++i) acc_out[i] = 0.f;
 
+  // dg / dbeta rows of one value head from its row reductions (threads 0..63 = the two warps that own the 64 rows).
+  // dg = reverse chunk-local cumulative sum of dgam; the last row additionally carries
+  // e^{gam_L} <S, dS'> + sum_i e^{gam_L - gam_i} k_i.(Vn dS'^T)_i, which therefore reaches every row.
+  auto finish_head = [&](int hvf, int fb, float bz) {
+    const int i = tid;
+    const float (*rd)[2][kC] = red2[fb];
+    const float qdq = rd[0][0][i] + rd[0][1][i], kdk = rd[1][0][i] + rd[1][1][i];
+    const float g_ = rd[2][0][i] + rd[2][1][i], b_ = rd[3][0][i] + rd[3][1][i], ma = rd[4][0][i] + rd[4][1][i];
+    const float gi = gam_s2[fb][i], bi = beta_s2[fb][i], egi = __expf(gi), gl = gam_s2[fb][rows - 1], el = __expf(gl - gi);
+    const bool live = i < rows;
+    float suf = live ? qdq - kdk + 2.f * bi * ma - 2.f * bi * egi * g_ : 0.f;
+    float tot3 = live ? el * b_ : 0.f;
+    const int64_t gidx = (tok0 + i) * p.HV + hvf;
+    if (live) {
+      const float db = bz - egi * g_ + ma;
+      if (p.grads_f32) static_cast<float*>(p.dbeta)[gidx] = db;
+      else static_cast<bf16*>(p.dbeta)[gidx] = __float2bfloat16_rn(db);
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float dn = __shfl_down_sync(0xffffffffu, suf, o);
+      if (lane + o < 32) suf += dn;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot3 += __shfl_xor_sync(0xffffffffu, tot3, o);
+    if (lane == 0) {
+      fin_s[0][warp] = suf;      // total of this warp's 32 rows (suffix sum at its first row)
+      fin_s[1][warp] = tot3;
+    }
+    asm volatile("bar.sync 2, 64;" ::: "memory");
+    if (warp == 0) suf += fin_s[0][1];
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += sds_s2[fb][w];
+    const float dgv = suf + __expf(gl) * tot + fin_s[1][0] + fin_s[1][1];
+    if (live) {
+      if (p.grads_f32) static_cast<float*>(p.dg)[gidx] = dgv;
+      else static_cast<bf16*>(p.dg)[gidx] = __float2bfloat16_rn(dgv);
+    }
+    asm volatile("bar.sync 2, 64;" ::: "memory");   // fin_s is free again
+  };
+  auto load_bz = [&](int hvf) -> float {   // sum of the reverse scan's four partial row sums of dZ . V
+    if (tid >= rows) return 0.f;
+    const int64_t gidx = (tok0 + tid) * p.HV + hvf;
+    const int64_t bzs = p.total_tokens * p.HV;
+    return (p.bz[gidx] + p.bz[bzs + gidx]) + (p.bz[2 * bzs + gidx] + p.bz[3 * bzs + gidx]);
+  };
+
   PSTAMP(0);
+  float bz_prev = 0.f;
   for (int h = 0; h < G && ok; ++h) {
     const int hv = hk * G + h;
+    const int hb = h & 1;
+    float* gam_s = gam_s2[hb];
+    float* beta_s = beta_s2[hb];
+    float (*red)[2][kC] = red2[hb];
     if (tid < kC) {
       gam_s[tid] = pf_gam;
       beta_s[tid] = pf_beta;
     }
     if (h + 1 < G) prefetch_scalars(hv + 1);
+    const float bz_cur = load_bz(hv);     // lands while the step's operands are awaited
     float sds = 0.f;
     for (int vb = 0; vb < 2; ++vb) {
       PSTAMP(1);
       ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT);
       lphase ^= 1;
-      if (!__syncthreads_and(ok)) break;
+      if (h == 0 && vb == 0) ok = mbar_wait(&qk_bar, 0, p.status, FLA_ERR_TIMEOUT) && ok;
+      if (!__syncthreads_and(ok)) { ok = false; break; }
       PSTAMP(2);
       if (tid == 0) {
         tc_fence_after();
@@ -524,6 +574,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
         mma_tile(tbase + rColTB, opVNaL, opDSH, 128, 128, 4, true);
         mma_commit(&mma_bar);
       }
+      if (h > 0 && vb == 0 && tid < kC) finish_head(hv - 1, hb ^ 1, bz_prev);   // while the MMAs run
       // <S, dS'> over this V block while the MMAs run (elementwise on the raw panel images)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -539,7 +590,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
       PSTAMP(3);
       ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
       mphase ^= 1;
-      if (!__syncthreads_and(ok)) break;   // also: every thread is done reading the step's buffers
+      if (!__syncthreads_and(ok)) { ok = false; break; }   // also: every thread is done reading the step's buffers
       PSTAMP(4);
       tc_fence_after();
       if (tid == 0) {
@@ -550,7 +601,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     if (!ok) break;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sds += __shfl_xor_sync(0xffffffffu, sds, o);
-    if (lane == 0) sds_s[warp] = sds;
+    if (lane == 0) sds_s2[hb][warp] = sds;
 
     PSTAMP(5);
     // ---- epilogue 1: score-tile gradients -> [dP; dAt] operand, first parts of this head's dq / dk rows
@@ -621,7 +672,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     }
     ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
     mphase ^= 1;
-    if (!__syncthreads_and(ok)) break;
+    if (!__syncthreads_and(ok)) { ok = false; break; }
     tc_fence_after();
 
     PSTAMP(7);
@@ -652,57 +703,13 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p) {
     PSTAMP(8);
     tc_fence_before();
     __syncthreads();
-    if (tid < kC) {
-      const int i = tid;
-      const float qdq = red[0][0][i] + red[0][1][i], kdk = red[1][0][i] + red[1][1][i];
-      const float g_ = red[2][0][i] + red[2][1][i], b_ = red[3][0][i] + red[3][1][i], ma = red[4][0][i] + red[4][1][i];
-      const float gi = gam_s[i], bi = beta_s[i], egi = __expf(gi), el = __expf(gam_s[rows - 1] - gi);
-      float dgam = qdq - kdk + 2.f * bi * ma - 2.f * bi * egi * g_;
-      red[3][0][i] = (i < rows) ? el * b_ : 0.f;   // e^{gam_L - gam_i} k_i.(Vn dS'^T)_i, summed below for the last row
-      dgam_s[i] = (i < rows) ? dgam : 0.f;
-      if (i < rows) {
-        const int64_t gidx = (tok0 + i) * p.HV + hv;
-        const int64_t bzs = p.total_tokens * p.HV;
-        const float bz = (p.bz[gidx] + p.bz[bzs + gidx]) + (p.bz[2 * bzs + gidx] + p.bz[3 * bzs + gidx]);
-        const float db = bz - egi * g_ + ma;
-        if (p.grads_f32) static_cast<float*>(p.dbeta)[gidx] = db;
-        else static_cast<bf16*>(p.dbeta)[gidx] = __float2bfloat16_rn(db);
-      }
-    }
-    __syncthreads();
-    if (tid < kC) {
-      // dg = reverse chunk-local cumulative sum of dgam; the last row additionally carries
-      // e^{gam_L} <S, dS'> + sum_i e^{gam_L - gam_i} k_i.(Vn dS'^T)_i, which therefore reaches every row.
-      // Two warps: suffix sums by shuffles (dgam_s and red[3][0] are zero past the last valid row).
-      float suf = dgam_s[tid], tot3 = red[3][0][tid];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float dn = __shfl_down_sync(0xffffffffu, suf, o);
-        if (lane + o < 32) suf += dn;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) tot3 += __shfl_xor_sync(0xffffffffu, tot3, o);
-      if (lane == 0) {
-        red[4][0][warp] = suf;      // total of this warp's 32 rows (suffix sum at its first row)
-        red[4][1][warp] = tot3;
-      }
-      asm volatile("bar.sync 2, 64;" ::: "memory");   // the two warps that own the 64 rows
-      if (warp == 0) suf += red[4][0][1];
-      float tot = 0.f;
-      for (int w = 0; w < 8; ++w) tot += sds_s[w];
-      const float dgv = suf + __expf(gam_s[rows - 1]) * tot + red[4][1][0] + red[4][1][1];
-      if (tid < rows) {
-        const int64_t gidx = (tok0 + tid) * p.HV + hv;
-        if (p.grads_f32) static_cast<float*>(p.dg)[gidx] = dgv;
-        else static_cast<bf16*>(p.dg)[gidx] = __float2bfloat16_rn(dgv);
-      }
-    }
-    __syncthreads();
+    bz_prev = bz_cur;
   }
+  if (__syncthreads_and(ok) && tid < kC) finish_head(hk * G + G - 1, (G - 1) & 1, bz_prev);
 
   PSTAMP(9);
 #ifdef FLA_STAGE_CLOCKS
-  if (tid == 0 && blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0)
+  if (tid == FLA_STAGE_THREAD && blockIdx.x == 40 && blockIdx.y == 7 && blockIdx.z == 3)
     for (int i = 0; i < 12; ++i) g_par_clocks[i] += pclk_[i];
 #endif
   if (ok && tok < rows) {
@@ -876,7 +883,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   const int nt_max = (max_len + kC - 1) / kC;
   {
     KernelTimer kt("gdn_bwd_par", cs);
-    gdn_bwd_par_kernel<<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p);
+    gdn_bwd_par_kernel<<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p, tm_q, tm_k);
   }
   return cuda_status(cudaGetLastError());
 }
