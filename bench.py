@@ -40,7 +40,7 @@ sys.path.insert(0, str(REPO / "flash-linear-attention-npu_b200"))
 sys.path.insert(0, str(REPO))
 
 DEFAULT_WORKLOAD = "gdn_fwd_bwd"
-WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "decode", "conv_prefill", "conv_bwd"]
+WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "decode", "conv_prefill", "conv_bwd", "gdn_stage_fwd"]
 FWD_FLOP_PER_TOKEN_HEAD = 182955.0      # KK^T, inverse, w/u, state, output (dense 64x64 tiles, no causal credit)
 BWD_FLOP_PER_TOKEN_HEAD = 524288.0
 
@@ -57,10 +57,27 @@ KERNEL_FLOPS = {
     "gdn_prep": 16384.0,
     "tri_inverse": 8192.0,     # 2 * 64^2 FLOP per token-head of the triangular solve (CUDA cores; shown against the tensor peak)
 }
+# Algorithmic HBM bytes of the stand-alone stages: every input read once, every output written once
+# (bf16 token tensors, fp32 A and gates, bf16 per-chunk states).
+def _th(c, heads, width, es):
+    return float(c["B"]) * c["T"] * c[heads] * width * es
+
+
+STAGE_BYTES = {
+    "chunk_local_cumsum": lambda c: _th(c, "HV", 1, 2) + _th(c, "HV", 1, 4),
+    "chunk_scaled_dot_kkt": lambda c: _th(c, "HK", 128, 2) + _th(c, "HV", 1, 6) + _th(c, "HV", 64, 4),
+    "solve_tri": lambda c: _th(c, "HV", 64, 4) + _th(c, "HV", 64, 2),
+    "recompute_w_u_fwd": lambda c: _th(c, "HK", 128, 2) + _th(c, "HV", 128, 2) + _th(c, "HV", 64, 2) + 2 * _th(c, "HV", 128, 2),
+    "chunk_fwd_h": lambda c: _th(c, "HK", 128, 2) + 2 * _th(c, "HV", 128, 2) + _th(c, "HV", 128, 2) + _th(c, "HV", 256, 2),
+    "chunk_fwd_o": lambda c: 2 * _th(c, "HK", 128, 2) + _th(c, "HV", 128, 2) + _th(c, "HV", 256, 2) + _th(c, "HV", 128, 2),
+}
 KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
                  "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "kda_bwd_dhu": "kda_bwd_dhu_kernel", "kda_bwd_par": "kda_bwd_par_kernel", "gdn_prep": "gdn_prep_kernel", "tri_inverse": "tri_inverse_kernel",
                  "recurrent_gdn": "recurrent_gdn_kernel", "causal_conv1d_fwd": "conv_fwd_kernel",
-                 "causal_conv1d_update": "conv_update1_kernel", "causal_conv1d_bwd": "conv_bwd_kernel"}
+                 "causal_conv1d_update": "conv_update1_kernel", "causal_conv1d_bwd": "conv_bwd_kernel",
+                 "chunk_local_cumsum": "stage_cumsum_kernel", "chunk_scaled_dot_kkt": "stage_kkt_kernel",
+                 "solve_tri": "stage_solve_tri_kernel", "recompute_w_u_fwd": "stage_wu_kernel",
+                 "chunk_fwd_h": "stage_fwd_h_kernel", "chunk_fwd_o": "stage_fwd_o_kernel"}
 
 
 def _peaks():
@@ -124,7 +141,7 @@ class Workload:
     def __init__(self, name, shape):
         self.name = name
         self.graph = None
-        if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill", "conv_bwd"):
+        if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill", "conv_bwd", "gdn_stage_fwd"):
             self.cfg = dict(B=8, T=4096, HK=16, HV=32, K=128, V=128, D=8192, W=4)
         elif name in ("kda_fwd", "kda_fwd_bwd"):
             self.cfg = dict(B=4, T=8192, HK=32, HV=32, K=128, V=128)
@@ -147,7 +164,7 @@ class Workload:
         g_ = torch.Generator(device=device).manual_seed(seed)
         rn = lambda *s: torch.randn(*s, device=device, generator=g_)  # noqa: E731
         d = {}
-        if self.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd"):
+        if self.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "gdn_stage_fwd"):
             d["q"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
             d["k"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
             d["v"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
@@ -186,7 +203,7 @@ class Workload:
                 "kda_fwd": ["q", "k", "v", "g", "beta"],
                 "kda_fwd_bwd": ["q", "k", "v", "g", "beta", "do"],
                 "decode": ["q", "k", "v", "g", "beta", "x"],
-                "conv_prefill": ["x"], "conv_bwd": ["x", "dy"]}[self.name]
+                "conv_prefill": ["x"], "conv_bwd": ["x", "dy"], "gdn_stage_fwd": ["q", "k", "v", "g", "beta", "h0"]}[self.name]
 
     def step(self, d):
         """One pass through the public Python API.  Returns the tensors a caller reads back."""
@@ -208,6 +225,15 @@ class Workload:
             o, ht, grads = ops.chunk_kda_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"],
                                                  grad_dtype=torch.bfloat16, disable_recompute=True)
             return (o, ht) + tuple(x for x in grads if x is not None)
+        if n == "gdn_stage_fwd":
+            # the reference's stage-by-stage forward chain (examples/flash_gated_delta_rule.py:796-881) on head-first views
+            hf = lambda t: t.transpose(1, 2)  # noqa: E731
+            gam = ops.chunk_local_cumsum(d["g"], 64, head_first=False)
+            A = ops.chunk_scaled_dot_kkt(hf(d["k"]), hf(gam), hf(d["beta"]))
+            X = ops.solve_tri(A, layout="bnsd", output_dtype=torch.bfloat16)
+            w, u = ops.recompute_w_u_fwd(hf(d["k"]), hf(d["v"]), hf(d["beta"]), X, 64, g=hf(gam))
+            h, v_new, ht = ops.chunk_gated_delta_rule_fwd_h(hf(d["k"]), w, u, hf(gam), initial_state=d["h0"], output_final_state=True)
+            return ops.chunk_fwd_o(hf(d["q"]), hf(d["k"]), v_new, h, self.cfg["K"] ** -0.5, g=hf(gam)), ht
         if n == "conv_prefill":
             return ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")[:1]
         if n == "conv_bwd":
@@ -231,14 +257,17 @@ class Workload:
         return self.graph_out
 
     def launches_per_step(self):
-        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1, "conv_bwd": 2}[self.name]
+        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1, "conv_bwd": 2,
+                "gdn_stage_fwd": 6}[self.name]
 
     def kernel_names(self):
         return {"gdn_fwd_bwd": ["gdn_prep", "tri_inverse", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
                 "gdn_fwd_conv": ["causal_conv1d_fwd", "gdn_prep", "tri_inverse", "gdn_fwd"],
                 "kda_fwd": ["kda_prep", "tri_inverse", "kda_fwd"],
                 "kda_fwd_bwd": ["kda_prep", "tri_inverse", "kda_fwd", "kda_bwd_dhu", "kda_bwd_par"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
-                "conv_prefill": ["causal_conv1d_fwd"], "conv_bwd": ["causal_conv1d_bwd"]}[self.name]
+                "conv_prefill": ["causal_conv1d_fwd"], "conv_bwd": ["causal_conv1d_bwd"],
+                "gdn_stage_fwd": ["chunk_local_cumsum", "chunk_scaled_dot_kkt", "solve_tri", "recompute_w_u_fwd", "chunk_fwd_h",
+                                  "chunk_fwd_o"]}[self.name]
 
     def kernel_work(self, kname):
         """(bound, algorithmic work per launch, unit) of one kernel at this workload's shape."""
@@ -253,6 +282,8 @@ class Workload:
             return "hbm", 2.0 * c["B"] * c["T"] * c["D"] * 2, "GB/s"
         if kname == "causal_conv1d_bwd":  # x, dy read + dx write
             return "hbm", 3.0 * c["B"] * c["T"] * c["D"] * 2, "GB/s"
+        if kname in STAGE_BYTES:             # every stage streams its operands and results through HBM
+            return "hbm", STAGE_BYTES[kname](c), "GB/s"
         if kname == "causal_conv1d_update":  # state read + write, x read, y write
             return "hbm", (2.0 * c["N"] * c["D"] * (c["W"] - 1) + 2.0 * c["N"] * c["D"]) * 2, "GB/s"
         raise KeyError(kname)
@@ -279,7 +310,7 @@ class Workload:
             return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads
         if self.name == "kda_fwd_bwd":
             return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads
-        if self.name in ("gdn_fwd_conv", "kda_fwd"):
+        if self.name in ("gdn_fwd_conv", "kda_fwd", "gdn_stage_fwd"):
             return FWD_FLOP_PER_TOKEN_HEAD * self.token_heads
         return None
 

@@ -1,0 +1,844 @@
+// Stand-alone stages of the chunked gated-delta-rule forward, one entry point per reference operator
+// (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py): chunk_local_cumsum (:875-904),
+// chunk_scaled_dot_kkt (:907-936), solve_tri (:1786-1800), recompute_w_u_fwd (:618-651),
+// chunk_gated_delta_rule_fwd_h (:552-615) and chunk_fwd_o (:517-549).
+//
+// The fused kernels (gdn_chunk_fwd.cu) never materialise A, w, u or the per-chunk states; these operators exist for
+// call sites that drive the reference's stage-by-stage chain and therefore read and write those tensors in HBM.
+// Operands that arrive as bf16 tensors enter the MMAs as they are; operands computed on the way (k beta e^g, v beta, the
+// state copy, the decayed v_new, the decayed score tile) are split into a bf16 value and a bf16 residual and multiplied in
+// two passes, so each stage is accurate to fp32 round-off for the inputs it is given (the reference rounds them to one
+// bf16).  The running state of fwd_h stays in fp32 (in tensor memory) for the whole sequence.
+//
+// Every tensor is addressed as [B, H, T, D] (or [B, H, T]) through its strides, so the reference's head-first
+// tensors and sequence-first views of the same memory are both accepted; D must be contiguous.
+// Tensor-core tiles are M = 128 tcgen05 MMAs whose rows 0..63 hold the chunk's 64 tokens (rows 64..127 are
+// never read back), except for kkt, which packs two consecutive chunks into one 128-row tile.
+#include <algorithm>
+#include "gdn_common.cuh"
+#include "fla_b200_internal.h"
+#include "kernel_timer.h"
+
+namespace fla {
+
+struct StageView {     // [B, H, T, D] view, D contiguous
+  const void* p;
+  int64_t sb, sh, st;
+  int dtype;           // fla_dtype
+};
+
+struct StageParams {
+  StageView q, k, v, w, u, g, beta, a, h, h0;
+  StageView o0, o1, o2;
+  const int32_t* cu_seqlens;
+  const int32_t* chunk_offsets;
+  int T, H, HK, D;
+  int reverse, want_final;
+  float scale;
+  int* status;
+};
+
+__device__ __forceinline__ float ld_any(const void* p, int64_t idx, int dtype) {
+  if (dtype == FLA_F32) return static_cast<const float*>(p)[idx];
+  if (dtype == FLA_BF16) return __bfloat162float(static_cast<const bf16*>(p)[idx]);
+  return __half2float(static_cast<const __half*>(p)[idx]);
+}
+__device__ __forceinline__ void st_any(void* p, int64_t idx, int dtype, float v) {
+  if (dtype == FLA_F32) static_cast<float*>(p)[idx] = v;
+  else if (dtype == FLA_BF16) static_cast<bf16*>(p)[idx] = __float2bfloat16_rn(v);
+  else static_cast<__half*>(p)[idx] = __float2half_rn(v);
+}
+// first element of row (b, h, t)
+__device__ __forceinline__ int64_t row_off(const StageView& v, int64_t b, int64_t h, int64_t t) {
+  return b * v.sb + h * v.sh + t * v.st;
+}
+
+// ----------------------------------------------------------------------------- chunk_local_cumsum
+// out[t] = scale * sum of g over the tokens of t's chunk up to t (reverse: from t on).  D == 1: one thread per token,
+// two warps per chunk, shuffle scan.  D > 1 (per-channel gates): one thread per channel, serial over the chunk.
+__global__ void __launch_bounds__(128) stage_cumsum_kernel(StageParams p) {
+  const int n = blockIdx.z, hh = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int tid = threadIdx.x;
+  if (p.D == 1) {
+    __shared__ float wsum[2];
+    const int lane = tid & 31, warp = tid >> 5;
+    const int t = p.reverse ? kC - 1 - tid : tid;    // scan position tid <-> token t
+    float x = (tid < kC && t < rows) ? ld_any(p.g.p, row_off(p.g, b, hh, t0 + t), p.g.dtype) : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += up;
+    }
+    if (lane == 31 && warp < 2) wsum[warp] = x;
+    __syncthreads();
+    if (warp == 1) x += wsum[0];
+    if (tid < kC && t < rows) st_any(const_cast<void*>(p.o0.p), row_off(p.o0, b, hh, t0 + t), p.o0.dtype, x * p.scale);
+  } else {
+    for (int d = tid; d < p.D; d += blockDim.x) {
+      float run = 0.f;
+      for (int i = 0; i < rows; ++i) {
+        const int t = p.reverse ? rows - 1 - i : i;
+        run += ld_any(p.g.p, row_off(p.g, b, hh, t0 + t) + d, p.g.dtype);
+        st_any(const_cast<void*>(p.o0.p), row_off(p.o0, b, hh, t0 + t) + d, p.o0.dtype, run * p.scale);
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- staging helpers
+// 64 rows x 128 bf16 columns of a [.., T, 128] tensor -> two panels (columns 0..63 | 64..127), rows >= `rows` zeroed,
+// each row optionally scaled by rs[row].  `nthr` threads cooperate.  Panel p starts at dst + p * panel_stride.
+// With `rs` the scaled rows are written as bf16 value + bf16 residual (`dst_lo`, same layout).
+__device__ __forceinline__ void stage_rows128(uint8_t* dst, uint32_t panel_stride, const bf16* src, int64_t st, int rows,
+                                              const float* rs, int tid, int nthr, uint8_t* dst_lo = nullptr) {
+  for (int idx = tid; idx < kC * 16; idx += nthr) {
+    const int r = idx >> 4, ch = idx & 15;
+    uint4 val = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
+    if (r < rows) {
+      val = *reinterpret_cast<const uint4*>(src + r * st + ch * 8);
+      if (rs) {
+        float f[8];
+        unpack_bf16x8(val, f);
+        const float s = rs[r];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] *= s;
+        split8(f, val, lo);
+      }
+    }
+    const uint32_t off = (ch >> 3) * panel_stride + panel_chunk_off(r, ch & 7);
+    *reinterpret_cast<uint4*>(dst + off) = val;
+    if (dst_lo) *reinterpret_cast<uint4*>(dst_lo + off) = lo;
+  }
+}
+// 64 rows x 64 bf16 columns -> one panel, rows >= `rows` zeroed
+__device__ __forceinline__ void stage_rows64(uint8_t* dst, const bf16* src, int64_t st, int rows, int tid, int nthr) {
+  for (int idx = tid; idx < kC * 8; idx += nthr) {
+    const int r = idx >> 3, ch = idx & 7;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r < rows) val = *reinterpret_cast<const uint4*>(src + r * st + ch * 8);
+    *reinterpret_cast<uint4*>(dst + panel_chunk_off(r, ch)) = val;
+  }
+}
+__device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+}
+
+// ----------------------------------------------------------------------------- chunk_scaled_dot_kkt
+// A[i, j] = beta_i exp(clamp(g_i - g_j, -50, 50)) k_i . k_j for j < i, else 0.  One CTA per (chunk pair, q/k head):
+// one 128 x 128 product [k_c; k_c+1] [k_c; k_c+1]^T serves both chunks (diagonal blocks) and all value heads of the group.
+constexpr uint32_t kKktSmem = 32768;
+__global__ void __launch_bounds__(128) stage_kkt_kernel(StageParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float gam_s[2][kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, hk = blockIdx.y, c0 = blockIdx.x * 2;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c0 >= sq.nt) return;
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t tbeg = p.cu_seqlens ? sq.bos : 0;
+  const int G = p.H / p.HK;
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 128);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init_fence();
+  }
+  for (int which = 0; which < 2; ++which) {
+    const int c = c0 + which;
+    const int rows = c < sq.nt ? min(kC, sq.len - c * kC) : 0;
+    const bf16* src = static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, tbeg + c * kC);
+    stage_rows128(smem + which * 8192, 16384, src, p.k.st, rows, nullptr, tid, 128);
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t sb = smem_u32(smem);
+  if (tid == 0) {
+    tc_fence_after();
+    const Operand opK{sb, 16384, 0};
+    mma_tile(tbase, opK, opK, 128, 128, 8, false);
+    mma_commit(&mma_bar);
+  }
+  const bool ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT);
+  tc_fence_after();
+  const int which = tid >> 6, i = tid & 63;
+  const int c = c0 + which;
+  const int rows = c < sq.nt ? min(kC, sq.len - c * kC) : 0;
+  float s[64];
+  tmem_ld_row64(tmem_addr(tbase, warp * 32, which * 64), s);
+  for (int h = 0; h < G; ++h) {
+    const int hv = hk * G + h;
+    __syncthreads();
+    gam_s[which][i] = i < rows ? ld_any(p.g.p, row_off(p.g, b, hv, tbeg + c * kC + i), p.g.dtype) : 0.f;
+    __syncthreads();
+    if (ok && i < rows) {
+      const float gi = gam_s[which][i];
+      const float bi = ld_any(p.beta.p, row_off(p.beta, b, hv, tbeg + c * kC + i), p.beta.dtype);
+      float* dst = static_cast<float*>(const_cast<void*>(p.o0.p)) + row_off(p.o0, b, hv, tbeg + c * kC + i);
+#pragma unroll
+      for (int j4 = 0; j4 < kC; j4 += 4) {
+        float r[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = j4 + jj;
+          const float e = __expf(fminf(fmaxf(gi - gam_s[which][j], -50.f), 50.f));
+          r[jj] = (j < i) ? bi * e * s[j] : 0.f;
+        }
+        *reinterpret_cast<float4*>(dst + j4) = make_float4(r[0], r[1], r[2], r[3]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 128);
+}
+
+// ----------------------------------------------------------------------------- solve_tri
+// X = (I + A)^-1 per chunk, A strictly lower triangular (entries on and above the diagonal are ignored), fp32
+// forward substitution, one thread per column (the scheme of tri_inverse.cu), four matrices per CTA.
+constexpr int kSolveStride = 68;
+__global__ void __launch_bounds__(256) stage_solve_tri_kernel(StageParams p) {
+  extern __shared__ float tri_sm[];
+  const int tid = threadIdx.x, grp = tid / 64, c = tid % 64;
+  const int n = blockIdx.z, chunk = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (chunk >= sq.nt) return;
+  const int hh = blockIdx.y * 4 + grp;
+  const bool active = hh < p.H;
+  const int rows = min(kC, sq.len - chunk * kC);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + chunk * kC;
+  float* AT = tri_sm + grp * kC * kSolveStride;
+  if (active) {
+    // thread c stages row c: AT[j][c] = A[c][j] for j < c
+    const int64_t ro = row_off(p.a, b, hh, t0 + c);
+    for (int j = 0; j < kC; ++j) AT[j * kSolveStride + c] = (c < rows && j < c) ? ld_any(p.a.p, ro + j, p.a.dtype) : 0.f;
+  }
+  __syncthreads();
+  if (!active) return;
+  float x[kC];
+#pragma unroll
+  for (int i = 0; i < kC; ++i) x[i] = (i == c) ? 1.f : 0.f;
+  const int jmin = c & ~31;
+#pragma unroll
+  for (int j = 0; j < kC - 1; ++j) {
+    if (j >= jmin) {
+      const float xj = x[j];
+      const float* col = AT + j * kSolveStride;
+#pragma unroll
+      for (int i4 = (j + 1) & ~3; i4 < kC; i4 += 4) {
+        const float4 a4 = *reinterpret_cast<const float4*>(col + i4);
+        if (i4 > j) x[i4] -= a4.x * xj;
+        if (i4 + 1 > j) x[i4 + 1] -= a4.y * xj;
+        if (i4 + 2 > j) x[i4 + 2] -= a4.z * xj;
+        if (i4 + 3 > j) x[i4 + 3] -= a4.w * xj;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kC; ++i)
+    if (i < rows) st_any(const_cast<void*>(p.o0.p), row_off(p.o0, b, hh, t0 + i) + c, p.o0.dtype, c < rows ? x[i] : 0.f);
+}
+
+// ----------------------------------------------------------------------------- recompute_w_u_fwd
+// u = X (v beta),  w = X (k beta e^g) per chunk and value head; X is the chunk's 64 x 64 block of (I + A)^-1.
+constexpr uint32_t kWuSmem = 16384 + 4 * 16384;   // X | (k beta e^g) hi, lo | (v beta) hi, lo
+__global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float rs_k[kC], rs_v[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int hk = hv / (p.H / p.HK);
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init_fence();
+  }
+  if (tid < kC) {
+    const float bt = tid < rows ? ld_any(p.beta.p, row_off(p.beta, b, hv, t0 + tid), p.beta.dtype) : 0.f;
+    const float gm = tid < rows ? ld_any(p.g.p, row_off(p.g, b, hv, t0 + tid), p.g.dtype) : 0.f;
+    rs_v[tid] = bt;
+    rs_k[tid] = bt * __expf(gm);
+  }
+  // X block: rows >= rows and columns >= rows zeroed (row 128-byte panel rows, 64 columns)
+  {
+    const bf16* xs = static_cast<const bf16*>(p.a.p) + row_off(p.a, b, hv, t0);
+    for (int idx = tid; idx < kC * 8; idx += 128) {
+      const int r = idx >> 3, ch = idx & 7;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < rows && ch * 8 < rows) {
+        val = *reinterpret_cast<const uint4*>(xs + r * p.a.st + ch * 8);
+        if (ch * 8 + 8 > rows) {
+          uint16_t* e = reinterpret_cast<uint16_t*>(&val);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (ch * 8 + j >= rows) e[j] = 0;
+        }
+      }
+      *reinterpret_cast<uint4*>(smem + panel_chunk_off(r, ch)) = val;
+    }
+  }
+  __syncthreads();
+  stage_rows128(smem + 16384, 8192, static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, t0), p.k.st, rows, rs_k, tid, 128, smem + 32768);
+  stage_rows128(smem + 49152, 8192, static_cast<const bf16*>(p.v.p) + row_off(p.v, b, hv, t0), p.v.st, rows, rs_v, tid, 128, smem + 65536);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t sb = smem_u32(smem);
+  if (tid == 0) {
+    tc_fence_after();
+    const Operand opX{sb, 16384, 0}, opKh{sb + 16384, 8192, 1}, opKl{sb + 32768, 8192, 1}, opVh{sb + 49152, 8192, 1},
+        opVl{sb + 65536, 8192, 1};
+    mma_tile(tbase, opX, opKh, 128, 128, 4, false);
+    mma_tile(tbase, opX, opKl, 128, 128, 4, true);
+    mma_tile(tbase + 128, opX, opVh, 128, 128, 4, false);
+    mma_tile(tbase + 128, opX, opVl, 128, 128, 4, true);
+    mma_commit(&mma_bar);
+  }
+  const bool ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT);
+  tc_fence_after();
+  if (warp < 2) {
+    const int i = tid;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const StageView& ov = which ? p.o1 : p.o0;
+      bf16* dst = static_cast<bf16*>(const_cast<void*>(ov.p)) + row_off(ov, b, hv, t0 + i);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float r[64];
+        tmem_ld_row64(tmem_addr(tbase, warp * 32, which * 128 + half * 64), r);
+        if (ok && i < rows) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+// ----------------------------------------------------------------------------- chunk_gated_delta_rule_fwd_h
+// Sequential over the chunks of one (sequence, value head, block of 64 value columns):
+//   h_c = S;  v_new = u - w S;  S <- e^{g_last} S + k^T (e^{g_last - g} v_new).
+// S lives in tensor memory in fp32 (lane = key dim, 64 columns); a bf16 copy is the MMA operand and the stored h_c.
+constexpr uint32_t hsOffW = 0, hsOffK = 32768, hsOffS = 49152, hsOffSl = 65536, hsOffVd = 81920, hsOffVdl = 90112;
+constexpr uint32_t kFwdHSmem = 98304;
+__global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float gam_s[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, hv = blockIdx.y, vb = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t tbeg = p.cu_seqlens ? sq.bos : 0;
+  const int hk = hv / (p.H / p.HK);
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 128);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init_fence();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const uint32_t sb = smem_u32(smem);
+  const Operand opW{sb + hsOffW, 16384, 0}, opS{sb + hsOffS, 16384, 1}, opSl{sb + hsOffSl, 16384, 1}, opKt{sb + hsOffK, 8192, 1},
+      opVd{sb + hsOffVd, 8192, 1}, opVdl{sb + hsOffVdl, 8192, 1};
+  // my state row (key dim tid, value columns vb*64 ..)
+  {
+    float s[64];
+    if (p.h0.p) {
+      const float* src = static_cast<const float*>(p.h0.p) + (int64_t(n) * p.H + hv) * kK * kV + tid * kV + vb * 64;
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(src + i);
+        s[i] = t.x; s[i + 1] = t.y; s[i + 2] = t.z; s[i + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) s[i] = 0.f;
+    }
+    tmem_st_row64(trow, s);
+  }
+  uint32_t mphase = 0;
+  bool ok = true;
+  for (int c = 0; c < sq.nt && ok; ++c) {
+    const int rows = min(kC, sq.len - c * kC);
+    const int64_t t0 = tbeg + c * kC;
+    if (tid < kC) gam_s[tid] = ld_any(p.g.p, row_off(p.g, b, hv, t0 + min(tid, rows - 1)), p.g.dtype);
+    stage_rows128(smem + hsOffW, 16384, static_cast<const bf16*>(p.w.p) + row_off(p.w, b, hv, t0), p.w.st, rows, nullptr, tid, 128);
+    stage_rows128(smem + hsOffK, 8192, static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, t0), p.k.st, rows, nullptr, tid, 128);
+    __syncthreads();
+    const float g_last = gam_s[rows - 1];
+    {
+      float s[64];
+      tmem_ld_row64(trow, s);
+      row64_to_hilo(smem + hsOffS, smem + hsOffSl, tid, s);
+      bf16* hd = static_cast<bf16*>(const_cast<void*>(p.o0.p)) + ((b * p.H + hv) * p.o0.sh + (p.cu_seqlens ? sq.cbase : 0) + c) * int64_t(kK * kV) +
+                 tid * kV + vb * 64;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(hd + ch * 8) = pack8(s + ch * 8);
+      const float el = __expf(g_last);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) s[i] *= el;
+      tmem_st_row64(trow, s);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase + 64, opW, opS, 128, 64, 8, false);
+      mma_tile(tbase + 64, opW, opSl, 128, 64, 8, true);
+      mma_commit(&mma_bar);
+    }
+    float uval[64];
+    if (warp < 2) {
+      const bf16* us = static_cast<const bf16*>(p.u.p) + row_off(p.u, b, hv, t0 + tid) + vb * 64;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (tid < rows) raw = *reinterpret_cast<const uint4*>(us + ch * 8);
+        unpack_bf16x8(raw, uval + ch * 8);
+      }
+    }
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    mphase ^= 1;
+    tc_fence_after();
+    if (warp < 2) {
+      float d1[64];
+      tmem_ld_row64(trow + 64, d1);
+      const bool live = tid < rows;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) d1[i] = live ? uval[i] - d1[i] : 0.f;
+      if (live && ok) {
+        bf16* vd = static_cast<bf16*>(const_cast<void*>(p.o1.p)) + row_off(p.o1, b, hv, t0 + tid) + vb * 64;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vd + ch * 8) = pack8(d1 + ch * 8);
+      }
+      const float dec = __expf(g_last - gam_s[tid]);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) d1[i] *= dec;
+      row64_to_hilo(smem + hsOffVd, smem + hsOffVdl, tid, d1);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    if (!__syncthreads_and(ok)) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase, opKt, opVd, 128, 64, 4, true);
+      mma_tile(tbase, opKt, opVdl, 128, 64, 4, true);
+      mma_commit(&mma_bar);
+    }
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    mphase ^= 1;
+    tc_fence_after();
+    if (!__syncthreads_and(ok)) { ok = false; break; }
+  }
+  if (ok && p.want_final) {
+    float s[64];
+    tmem_ld_row64(trow, s);
+    float* dst = static_cast<float*>(const_cast<void*>(p.o2.p)) + (int64_t(n) * p.H + hv) * kK * kV + tid * kV + vb * 64;
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(s[i], s[i + 1], s[i + 2], s[i + 3]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 128);
+}
+
+// ----------------------------------------------------------------------------- chunk_fwd_o
+// o = scale [ e^{g_i} (q h_c) + tril(q k^T e^{g_i - g_j}) v_new ] per chunk and value head.
+constexpr uint32_t foOffQ = 0, foOffK = 32768, foOffH = 49152, foOffVn = 81920, foOffP = 98304;
+constexpr uint32_t kFwdOSmem = 114688;
+__global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float gam_s[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int hk = hv / (p.H / p.HK);
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init_fence();
+  }
+  if (tid < kC) gam_s[tid] = ld_any(p.g.p, row_off(p.g, b, hv, t0 + min(tid, rows - 1)), p.g.dtype);
+  stage_rows128(smem + foOffQ, 16384, static_cast<const bf16*>(p.q.p) + row_off(p.q, b, hk, t0), p.q.st, rows, nullptr, tid, 128);
+  stage_rows128(smem + foOffK, 8192, static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, t0), p.k.st, rows, nullptr, tid, 128);
+  stage_rows128(smem + foOffVn, 8192, static_cast<const bf16*>(p.v.p) + row_off(p.v, b, hv, t0), p.v.st, rows, nullptr, tid, 128);
+  {
+    // h_c: 128 key rows x 128 value columns, dense
+    const bf16* hs = static_cast<const bf16*>(p.h.p) + ((b * p.H + hv) * p.h.sh + (p.cu_seqlens ? sq.cbase : 0) + c) * int64_t(kK * kV);
+    for (int idx = tid; idx < kK * 16; idx += 128) {
+      const int r = idx >> 4, ch = idx & 15;
+      *reinterpret_cast<uint4*>(smem + foOffH + (ch >> 3) * 16384 + panel_chunk_off(r, ch & 7)) =
+          *reinterpret_cast<const uint4*>(hs + r * kV + ch * 8);
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const uint32_t sb = smem_u32(smem);
+  const Operand opQ{sb + foOffQ, 16384, 0}, opK{sb + foOffK, 8192, 0}, opH{sb + foOffH, 16384, 1}, opVn{sb + foOffVn, 8192, 1},
+      opP{sb + foOffP, 16384, 0}, opPl{sb + foOffK, 16384, 0};   // the residual of P reuses the k panels (dead after q k^T)
+  if (tid == 0) {
+    tc_fence_after();
+    mma_tile(tbase, opQ, opK, 128, 64, 8, false);          // columns 0..63: q k^T
+    mma_tile(tbase + 64, opQ, opH, 128, 128, 8, false);    // columns 64..191: q h_c
+    mma_commit(&mma_bar);
+  }
+  bool ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT);
+  tc_fence_after();
+  if (warp < 2) {
+    const int i = tid;
+    const float gi = gam_s[i];
+    {
+      float s[64];
+      tmem_ld_row64(trow, s);
+#pragma unroll
+      for (int j = 0; j < 64; ++j) s[j] = (j <= i && j < rows && i < rows) ? s[j] * __expf(gi - gam_s[j]) : 0.f;
+      row64_to_hilo(smem + foOffP, smem + foOffK, i, s);
+    }
+    const float eg = __expf(gi);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float r[64];
+      tmem_ld_row64(trow + 64 + half * 64, r);
+#pragma unroll
+      for (int j = 0; j < 64; ++j) r[j] *= eg;
+      tmem_st_row64(trow + 64 + half * 64, r);
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  ok = __syncthreads_and(ok);
+  if (ok) {
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase + 64, opP, opVn, 128, 128, 4, true);
+      mma_tile(tbase + 64, opPl, opVn, 128, 128, 4, true);
+      mma_commit(&mma_bar);
+    }
+    ok = mbar_wait(&mma_bar, 1, p.status, FLA_ERR_TIMEOUT);
+    tc_fence_after();
+    if (warp < 2) {
+      const int i = tid;
+      bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o0.p)) + row_off(p.o0, b, hv, t0 + i);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float r[64];
+        tmem_ld_row64(trow + 64 + half * 64, r);
+        if (ok && i < rows) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) r[j] *= p.scale;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+}  // namespace fla
+
+using namespace fla;
+
+// ----------------------------------------------------------------------------- host side
+namespace {
+
+// [B, H, T, D] (nd == 4) or [B, H, T] (nd == 3) view; D contiguous; rows 16-byte aligned when `vec` is set
+int make_view(const fla_tensor_t& t, int nd, bool vec, StageView* v) {
+  if (!t.data) return FLA_ERR_NULL;
+  if (t.ndim != nd) return FLA_ERR_SHAPE;
+  if (nd == 4 && t.shape[3] > 1 && t.stride[3] != 1) return FLA_ERR_LAYOUT;
+  v->p = t.data;
+  v->sb = t.stride[0]; v->sh = t.stride[1]; v->st = t.stride[2];
+  v->dtype = t.dtype;
+  if (vec) {
+    const int es = t.dtype == FLA_F32 ? 4 : 2;
+    if (!aligned16(t.data) || (v->sb * es) % 16 || (v->sh * es) % 16 || (v->st * es) % 16) return FLA_ERR_LAYOUT;
+  }
+  return FLA_OK;
+}
+
+struct Geometry {
+  int64_t B, H, T;
+  int N, nt_max;
+  int64_t total_chunks;
+};
+
+int geometry(const fla_chunk_stage_args* a, const fla_tensor_t& ref, Geometry* gm, StageParams* p) {
+  if (a->chunk_size != kC) return FLA_ERR_VALUE;
+  gm->B = ref.shape[0]; gm->H = ref.shape[1]; gm->T = ref.shape[2];
+  if (gm->B <= 0 || gm->H <= 0 || gm->T <= 0) return FLA_ERR_SHAPE;
+  gm->N = int(gm->B);
+  int max_len = int(gm->T);
+  gm->total_chunks = gm->B * ((gm->T + kC - 1) / kC);
+  p->cu_seqlens = nullptr;
+  p->chunk_offsets = nullptr;
+  if (a->cu_seqlens.data) {
+    if (gm->B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    gm->N = int(a->cu_seqlens.shape[0] - 1);
+    if (!a->chunk_offsets.data || a->chunk_offsets.dtype != FLA_I32 || a->chunk_offsets.shape[0] != gm->N + 1) return FLA_ERR_SHAPE;
+    if (a->max_seqlen <= 0 || a->max_seqlen > gm->T || a->total_chunks <= 0) return FLA_ERR_VALUE;
+    max_len = a->max_seqlen;
+    gm->total_chunks = a->total_chunks;
+    p->cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+    p->chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
+  }
+  gm->nt_max = (max_len + kC - 1) / kC;
+  p->T = int(gm->T);
+  p->H = int(gm->H);
+  return FLA_OK;
+}
+
+bool same_bht(const fla_tensor_t& t, const Geometry& gm, int64_t heads) {
+  return t.shape[0] == gm.B && t.shape[1] == heads && t.shape[2] == gm.T;
+}
+
+int prepare_status(void* workspace, uint64_t bytes, cudaStream_t cs, StageParams* p) {
+  if (!workspace || bytes < 256 || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
+  if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
+  p->status = static_cast<int*>(workspace);
+  return FLA_OK;
+}
+
+template <typename Kern>
+int opt_in_smem(Kern kern, uint32_t bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+}  // namespace
+
+// Every stage needs the same workspace: the status word of the bounded device-side waits.
+#define FLA_STAGE_WORKSPACE(op)                                                                              \
+  extern "C" FLA_API int fla_b200_##op##_workspace_size(const fla_chunk_stage_args* a, uint64_t* bytes) {     \
+    if (!a || !bytes) return FLA_ERR_NULL;                                                                   \
+    *bytes = 256;                                                                                            \
+    return FLA_OK;                                                                                           \
+  }
+FLA_STAGE_WORKSPACE(chunk_local_cumsum)
+FLA_STAGE_WORKSPACE(chunk_scaled_dot_kkt)
+FLA_STAGE_WORKSPACE(solve_tri)
+FLA_STAGE_WORKSPACE(recompute_w_u_fwd)
+FLA_STAGE_WORKSPACE(chunk_gated_delta_rule_fwd_h)
+FLA_STAGE_WORKSPACE(chunk_fwd_o)
+
+extern "C" FLA_API int fla_b200_chunk_local_cumsum(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes,
+                                                   void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  (void)workspace; (void)workspace_bytes;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  const int nd = a->g.ndim;
+  if (nd != 3 && nd != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->g, &gm, &p))) return st;
+  if ((st = make_view(a->g, nd, false, &p.g)) || (st = make_view(a->out0, nd, false, &p.o0))) return st;
+  for (int i = 0; i < nd; ++i)
+    if (a->out0.shape[i] != a->g.shape[i]) return FLA_ERR_SHAPE;
+  p.D = nd == 4 ? int(a->g.shape[3]) : 1;
+  if (p.D < 1 || p.D > 1024) return FLA_ERR_SHAPE;
+  p.reverse = a->reverse;
+  p.scale = a->scale;
+  const int threads = p.D == 1 ? 64 : ((std::min(p.D, 128) + 31) / 32) * 32;
+  KernelTimer kt("chunk_local_cumsum", cs);
+  stage_cumsum_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), threads, 0, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_chunk_scaled_dot_kkt(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes,
+                                                     void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  if (a->g.ndim != 3) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->g, &gm, &p))) return st;
+  if ((st = make_view(a->k, 4, true, &p.k)) || (st = make_view(a->g, 3, false, &p.g)) || (st = make_view(a->beta, 3, false, &p.beta)) ||
+      (st = make_view(a->out0, 4, true, &p.o0)))
+    return st;
+  const int64_t HK = a->k.shape[1];
+  if (a->k.dtype != FLA_BF16 || a->out0.dtype != FLA_F32) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->k.shape[0] != gm.B || a->k.shape[2] != gm.T || a->k.shape[3] != kK) return FLA_ERR_SHAPE;
+  if (!same_bht(a->beta, gm, gm.H) || !same_bht(a->out0, gm, gm.H) || a->out0.shape[3] != kC) return FLA_ERR_SHAPE;
+  p.HK = int(HK);
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if ((st = opt_in_smem(stage_kkt_kernel, kKktSmem + 1024))) return st;
+  KernelTimer kt("chunk_scaled_dot_kkt", cs);
+  stage_kkt_kernel<<<dim3((gm.nt_max + 1) / 2, unsigned(HK), gm.N), 128, kKktSmem + 1024, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_solve_tri(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes, void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  (void)workspace; (void)workspace_bytes;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  if (a->A.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->A, &gm, &p))) return st;
+  if ((st = make_view(a->A, 4, false, &p.a)) || (st = make_view(a->out0, 4, false, &p.o0))) return st;
+  if (a->A.shape[3] != kC || !same_bht(a->out0, gm, gm.H) || a->out0.shape[3] != kC) return FLA_ERR_SHAPE;
+  const uint32_t smem = 4 * kC * kSolveStride * sizeof(float);
+  if ((st = opt_in_smem(stage_solve_tri_kernel, smem))) return st;
+  KernelTimer kt("solve_tri", cs);
+  stage_solve_tri_kernel<<<dim3(gm.nt_max, unsigned((gm.H + 3) / 4), gm.N), 256, smem, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_recompute_w_u_fwd(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes,
+                                                  void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  if (a->v.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->v, &gm, &p))) return st;
+  if ((st = make_view(a->k, 4, true, &p.k)) || (st = make_view(a->v, 4, true, &p.v)) || (st = make_view(a->A, 4, true, &p.a)) ||
+      (st = make_view(a->g, 3, false, &p.g)) || (st = make_view(a->beta, 3, false, &p.beta)) ||
+      (st = make_view(a->out0, 4, true, &p.o0)) || (st = make_view(a->out1, 4, true, &p.o1)))
+    return st;
+  const int64_t HK = a->k.shape[1];
+  for (const fla_tensor_t* t : {&a->k, &a->v, &a->A, &a->out0, &a->out1})
+    if (t->dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->k.shape[0] != gm.B || a->k.shape[2] != gm.T || a->k.shape[3] != kK || a->v.shape[3] != kV) return FLA_ERR_SHAPE;
+  if (!same_bht(a->A, gm, gm.H) || a->A.shape[3] != kC || !same_bht(a->g, gm, gm.H) || !same_bht(a->beta, gm, gm.H)) return FLA_ERR_SHAPE;
+  if (!same_bht(a->out0, gm, gm.H) || a->out0.shape[3] != kK || !same_bht(a->out1, gm, gm.H) || a->out1.shape[3] != kV) return FLA_ERR_SHAPE;
+  p.HK = int(HK);
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if ((st = opt_in_smem(stage_wu_kernel, kWuSmem + 1024))) return st;
+  KernelTimer kt("recompute_w_u_fwd", cs);
+  stage_wu_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kWuSmem + 1024, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_chunk_gated_delta_rule_fwd_h(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes,
+                                                             void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  if (a->u.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->u, &gm, &p))) return st;
+  if ((st = make_view(a->k, 4, true, &p.k)) || (st = make_view(a->w, 4, true, &p.w)) || (st = make_view(a->u, 4, true, &p.u)) ||
+      (st = make_view(a->g, 3, false, &p.g)) || (st = make_view(a->out1, 4, true, &p.o1)))
+    return st;
+  const int64_t HK = a->k.shape[1];
+  for (const fla_tensor_t* t : {&a->k, &a->w, &a->u, &a->out0, &a->out1})
+    if (t->dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->k.shape[0] != gm.B || a->k.shape[2] != gm.T || a->k.shape[3] != kK || a->u.shape[3] != kV) return FLA_ERR_SHAPE;
+  if (!same_bht(a->w, gm, gm.H) || a->w.shape[3] != kK || !same_bht(a->g, gm, gm.H) || !same_bht(a->out1, gm, gm.H) || a->out1.shape[3] != kV)
+    return FLA_ERR_SHAPE;
+  // h [B, H, NT, K, V], dense
+  const fla_tensor_t& h = a->out0;
+  const int64_t NT = gm.total_chunks / gm.B;
+  if (!h.data) return FLA_ERR_NULL;
+  if (h.ndim != 5 || h.shape[0] != gm.B || h.shape[1] != gm.H || h.shape[2] != NT || h.shape[3] != kK || h.shape[4] != kV) return FLA_ERR_SHAPE;
+  if (h.stride[4] != 1 || h.stride[3] != kV || h.stride[2] != kK * kV || h.stride[1] != NT * kK * kV || !aligned16(h.data)) return FLA_ERR_LAYOUT;
+  p.o0.p = h.data;
+  p.o0.sh = NT;    // chunks per (batch row, head)
+  for (const fla_tensor_t* s : {&a->initial_state, &a->out2}) {
+    if (!s->data) continue;
+    if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
+    if (s->ndim != 4 || s->shape[0] != gm.N || s->shape[1] != gm.H || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != gm.H * kK * kV || !aligned16(s->data))
+      return FLA_ERR_LAYOUT;
+  }
+  p.h0.p = a->initial_state.data;
+  p.o2.p = a->out2.data;
+  p.want_final = a->out2.data != nullptr;
+  p.HK = int(HK);
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if ((st = opt_in_smem(stage_fwd_h_kernel, kFwdHSmem + 1024))) return st;
+  KernelTimer kt("chunk_fwd_h", cs);
+  stage_fwd_h_kernel<<<dim3(kV / 64, unsigned(gm.H), gm.N), 128, kFwdHSmem + 1024, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes, void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  if (a->v.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->v, &gm, &p))) return st;
+  if ((st = make_view(a->q, 4, true, &p.q)) || (st = make_view(a->k, 4, true, &p.k)) || (st = make_view(a->v, 4, true, &p.v)) ||
+      (st = make_view(a->g, 3, false, &p.g)) || (st = make_view(a->out0, 4, true, &p.o0)))
+    return st;
+  const int64_t HK = a->k.shape[1];
+  for (const fla_tensor_t* t : {&a->q, &a->k, &a->v, &a->h, &a->out0})
+    if (t->dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->k.shape[0] != gm.B || a->k.shape[2] != gm.T || a->k.shape[3] != kK || a->v.shape[3] != kV) return FLA_ERR_SHAPE;
+  if (a->q.shape[0] != gm.B || a->q.shape[1] != HK || a->q.shape[2] != gm.T || a->q.shape[3] != kK) return FLA_ERR_SHAPE;
+  if (!same_bht(a->g, gm, gm.H) || !same_bht(a->out0, gm, gm.H) || a->out0.shape[3] != kV) return FLA_ERR_SHAPE;
+  const fla_tensor_t& h = a->h;
+  const int64_t NT = gm.total_chunks / gm.B;
+  if (!h.data) return FLA_ERR_NULL;
+  if (h.ndim != 5 || h.shape[0] != gm.B || h.shape[1] != gm.H || h.shape[2] != NT || h.shape[3] != kK || h.shape[4] != kV) return FLA_ERR_SHAPE;
+  if (h.stride[4] != 1 || h.stride[3] != kV || h.stride[2] != kK * kV || h.stride[1] != NT * kK * kV || !aligned16(h.data)) return FLA_ERR_LAYOUT;
+  p.h.p = h.data;
+  p.h.sh = NT;
+  p.HK = int(HK);
+  p.scale = a->scale;
+  if (!(a->scale == a->scale)) return FLA_ERR_VALUE;
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if ((st = opt_in_smem(stage_fwd_o_kernel, kFwdOSmem + 1024))) return st;
+  KernelTimer kt("chunk_fwd_o", cs);
+  stage_fwd_o_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kFwdOSmem + 1024, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}

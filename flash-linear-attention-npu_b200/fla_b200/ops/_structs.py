@@ -60,3 +60,10 @@ class KdaChunkBwdArgs(ctypes.Structure):
 
 class L2NormArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("x", "y", "rstd", "dy", "dx")] + [("eps", ctypes.c_float)]
+
+
+class ChunkStageArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "w", "u", "g", "beta", "A", "h", "initial_state", "out0", "out1",
+                                           "out2", "cu_seqlens", "chunk_offsets")] + [
+        ("scale", ctypes.c_float), ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32),
+        ("total_chunks", ctypes.c_int32), ("reverse", ctypes.c_int32)]

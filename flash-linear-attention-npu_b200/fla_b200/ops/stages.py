@@ -1,0 +1,168 @@
+"""Stage-by-stage operators of the chunked gated-delta-rule forward, with the names, argument order and head-first
+`[B,H,T,D]` layouts of the reference's low-level surface (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py):
+`npu_chunk_local_cumsum` (:875-904), `npu_chunk_scaled_dot_kkt` (:907-936), `npu_solve_tri` (:1786-1800),
+`npu_recompute_w_u_fwd` (:618-651), `npu_chunk_gated_delta_rule_fwd_h` (:552-615), `npu_chunk_fwd_o` (:517-549).
+
+The fused `chunk_gated_delta_rule` never writes A, w, u or the per-chunk states to memory; these functions are for
+call sites that run the reference's chain one operator at a time (examples/flash_gated_delta_rule.py:796-881).
+Tensors are passed with their strides, so sequence-first tensors can be given as transposed views without a copy.
+`cu_seqlens` is a host list (or tensor) of sequence boundaries as in the reference; `chunk_indices` is accepted and
+ignored because the chunk geometry follows from `cu_seqlens`.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _runtime as rt
+from ._structs import ChunkStageArgs
+from .gdn import CHUNK, _varlen_meta
+
+_DTYPES = {"float": torch.float32, "float32": torch.float32, "half": torch.float16, "float16": torch.float16,
+           "bf16": torch.bfloat16, "bfloat16": torch.bfloat16}
+
+
+def _stage_call(op, fields, tensors, ref, cu_seqlens, chunk_size, scale=1.0, reverse=False):
+    if int(chunk_size) != CHUNK:
+        raise NotImplementedError(f"{op}: this build supports chunk_size = {CHUNK}, got {chunk_size}")
+    B, T = ref.shape[0], ref.shape[2]
+    dev = ref.device
+    cu = co = None
+    max_len, total_chunks = T, B * ((T + CHUNK - 1) // CHUNK)
+    if cu_seqlens is not None:
+        if B != 1:
+            raise RuntimeError(f"{op}: cu_seqlens requires batch size 1 (packed sequences)")
+        cu, co, max_len, total_chunks, _n, total = _varlen_meta(cu_seqlens, dev)
+        if total != T:
+            raise RuntimeError(f"{op}: cu_seqlens[-1]={total} must equal T={T}")
+    a = ChunkStageArgs()
+    for name, t in fields.items():
+        setattr(a, name, rt.desc(t))
+    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    a.scale, a.chunk_size, a.max_seqlen, a.total_chunks, a.reverse = float(scale), CHUNK, int(max_len), int(total_chunks), int(bool(reverse))
+    rt.call(op, a, list(tensors) + [cu, co])
+    return total_chunks
+
+
+def _num_sequences(B, cu_seqlens):
+    return B if cu_seqlens is None else len(cu_seqlens) - 1
+
+
+def chunk_local_cumsum(g, chunk_size, *, cu_seqlens=None, chunk_indices_out=None, reverse=False, scale=1.0, head_first=True,
+                       output_dtype="float32"):
+    """Chunk-local (reverse) cumulative sum of the gate.  g `[B,H,T]` (or `[B,H,T,D]`) when `head_first`, else
+    `[B,T,H]` / `[B,T,H,D]`; the result has g's shape and `output_dtype` ("same" keeps g's dtype)."""
+    del chunk_indices_out
+    if isinstance(output_dtype, torch.dtype) or output_dtype is None:
+        out_dtype = output_dtype or torch.float32
+    else:
+        name = str(output_dtype).removeprefix("torch.").lower()
+        if name in ("same", "input", "none"):
+            out_dtype = g.dtype
+        elif name in _DTYPES:
+            out_dtype = _DTYPES[name]
+        else:
+            raise TypeError(f"Unsupported chunk_local_cumsum output_dtype: {output_dtype}.")
+    if g.dim() not in (3, 4):
+        raise RuntimeError(f"chunk_local_cumsum: g must be 3-D or 4-D, got {tuple(g.shape)}")
+    out = torch.empty(g.shape, dtype=out_dtype, device=g.device)
+    gv, ov = (g, out) if head_first else (g.transpose(1, 2), out.transpose(1, 2))
+    _stage_call("chunk_local_cumsum", dict(g=gv, out0=ov), [g, out], gv, cu_seqlens, chunk_size, scale=scale, reverse=reverse)
+    return out
+
+
+def chunk_scaled_dot_kkt(k, g, beta, *, cu_seqlens=None, chunk_indices=None, chunk_size=64):
+    """A `[B,HV,T,C]` fp32: `beta_i exp(clip(g_i - g_j, +-50)) k_i.k_j` below the diagonal of every chunk, else 0.
+    k `[B,HK,T,K]` bf16, g (chunk-local cumulative gate) and beta `[B,HV,T]`."""
+    del chunk_indices
+    B, HK, T, K = k.shape
+    HV = g.shape[1]
+    out = torch.empty((B, HV, T, int(chunk_size)), dtype=torch.float32, device=k.device)
+    _stage_call("chunk_scaled_dot_kkt", dict(k=k, g=g, beta=beta, out0=out), [k, g, beta, out], g, cu_seqlens, chunk_size)
+    return out
+
+
+def solve_tri(x, *, cu_seqlens=None, chunk_indices=None, layout="bsnd", output_dtype=None):
+    """Per chunk `(I + strict_lower(x))^-1`.  x is `[B,T,H,C]` for layout "bsnd" and `[B,H,T,C]` for "bnsd"
+    ("tnd" `[T,H,C]` and "ntd" `[H,T,C]` are the packed 3-D forms, used with `cu_seqlens`).  The result has x's dtype
+    unless `output_dtype` (not in the reference's signature) asks for another, which saves the separate cast of A."""
+    del chunk_indices
+    lay = str(layout).lower()
+    if lay in ("tnd", "ntd"):     # packed 3-D forms of the same two layouts
+        if x.dim() != 3:
+            raise RuntimeError(f"solve_tri: layout {layout!r} expects a 3-D tensor, got {tuple(x.shape)}")
+        return solve_tri(x.unsqueeze(0), cu_seqlens=cu_seqlens, layout="bsnd" if lay == "tnd" else "bnsd",
+                         output_dtype=output_dtype).squeeze(0)
+    if lay not in ("bsnd", "bnsd"):
+        raise NotImplementedError(f"solve_tri: layout {layout!r} is not supported (bsnd, bnsd, tnd, ntd)")
+    if x.dim() != 4 or x.shape[-1] != CHUNK:
+        raise NotImplementedError(f"solve_tri: x must be 4-D with a last dimension of {CHUNK}, got {tuple(x.shape)}")
+    out = torch.empty(x.shape, dtype=output_dtype or x.dtype, device=x.device)
+    xv, ov = (x, out) if lay == "bnsd" else (x.transpose(1, 2), out.transpose(1, 2))
+    _stage_call("solve_tri", dict(A=xv, out0=ov), [x, out], xv, cu_seqlens, CHUNK)
+    return out
+
+
+def recompute_w_u_fwd(k, v, beta, A, chunk_size, *, g=None, gk=None, cu_seqlens=None, chunk_indices=None):
+    """`w = A (k beta e^g)`, `u = A (v beta)` per chunk.  k `[B,HK,T,K]`, v `[B,HV,T,V]`, A `[B,HV,T,C]` bf16,
+    beta and g `[B,HV,T]`.  Returns (w `[B,HV,T,K]`, u `[B,HV,T,V]`)."""
+    del chunk_indices
+    if gk is not None:
+        raise NotImplementedError("recompute_w_u_fwd: per-channel gates (gk) are handled by the fused KDA operator")
+    if g is None:
+        raise RuntimeError("recompute_w_u_fwd: g is required")
+    B, HV, T, V = v.shape
+    w = torch.empty((B, HV, T, k.shape[3]), dtype=k.dtype, device=k.device)
+    u = torch.empty_like(v)
+    _stage_call("recompute_w_u_fwd", dict(k=k, v=v, beta=beta, A=A, g=g, out0=w, out1=u), [k, v, beta, A, g, w, u], v, cu_seqlens,
+                chunk_size)
+    return w, u
+
+
+def chunk_gated_delta_rule_fwd_h(k, w, u, g=None, *, gk=None, initial_state=None, output_final_state=False, chunk_size=None,
+                                 cu_seqlens=None, chunk_indices=None, state_v_first=False):
+    """Sequential state pass: `h_c = S`, `v_new = u - w S`, `S <- e^{g_last} S + k^T (e^{g_last - g} v_new)`.
+    Returns (h `[B,HV,NT,K,V]`, v_new `[B,HV,T,V]`, final_state `[N,HV,K,V]` fp32 or None)."""
+    del chunk_indices
+    if gk is not None or g is None:
+        raise NotImplementedError("chunk_gated_delta_rule_fwd_h: scalar gates (g) only; gk belongs to the fused KDA operator")
+    if state_v_first:
+        raise NotImplementedError("chunk_gated_delta_rule_fwd_h: state_v_first is not supported")
+    chunk_size = CHUNK if chunk_size is None else int(chunk_size)
+    B, HV, T, V = u.shape
+    K = k.shape[3]
+    N = _num_sequences(B, cu_seqlens)
+    if cu_seqlens is None:
+        NT = (T + CHUNK - 1) // CHUNK
+    else:
+        cu_host = [int(x) for x in (cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens)]
+        NT = sum((b - a + CHUNK - 1) // CHUNK for a, b in zip(cu_host, cu_host[1:]))
+    if initial_state is not None:
+        if tuple(initial_state.shape) != (N, HV, K, V):
+            raise RuntimeError("npu_chunk_gated_delta_rule_fwd_h: initial_state shape does not match state_v_first.")
+        initial_state = initial_state.float().contiguous()
+    h = torch.empty((B, HV, NT, K, V), dtype=k.dtype, device=k.device)
+    v_new = torch.empty_like(u)
+    ht = torch.empty((N, HV, K, V), dtype=torch.float32, device=k.device) if output_final_state else None
+    _stage_call("chunk_gated_delta_rule_fwd_h", dict(k=k, w=w, u=u, g=g, initial_state=initial_state, out0=h, out1=v_new, out2=ht),
+                [k, w, u, g, initial_state, h, v_new, ht], u, cu_seqlens, chunk_size)
+    return h, v_new, ht
+
+
+def chunk_fwd_o(q, k, v, h, scale, *, g=None, g_gamma=None, cu_seqlens=None, chunk_indices=None, chunk_size=None,
+                transpose_state_layout=False):
+    """`o = scale (e^{g_i} q h_c + tril(q k^T e^{g_i - g_j}) v)` per chunk; v is the `v_new` of the state pass."""
+    del g_gamma, transpose_state_layout, chunk_indices
+    if g is None:
+        raise NotImplementedError("chunk_fwd_o: g is required")
+    chunk_size = CHUNK if chunk_size is None else int(chunk_size)
+    o = torch.empty_like(v)
+    _stage_call("chunk_fwd_o", dict(q=q, k=k, v=v, h=h, g=g, out0=o), [q, k, v, h, g, o], v, cu_seqlens, chunk_size, scale=scale)
+    return o
+
+
+npu_chunk_local_cumsum = chunk_local_cumsum
+npu_chunk_scaled_dot_kkt = chunk_scaled_dot_kkt
+npu_solve_tri = solve_tri
+npu_recompute_w_u_fwd = recompute_w_u_fwd
+npu_chunk_gated_delta_rule_fwd_h = chunk_gated_delta_rule_fwd_h
+npu_chunk_fwd_o = chunk_fwd_o

@@ -322,6 +322,60 @@ typedef struct fla_l2norm_args {
 FLA_API int fla_b200_l2norm_fwd(const fla_l2norm_args* args, void* stream);
 FLA_API int fla_b200_l2norm_bwd(const fla_l2norm_args* args, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Stand-alone stages of the chunked gated-delta-rule forward: one entry point per low-level reference operator,
+ * for call sites that drive the reference's stage-by-stage chain (examples/flash_gated_delta_rule.py:796-881)
+ * instead of the fused fla_b200_gdn_chunk_fwd.  Token tensors are [B, H, T, D] and gate tensors [B, H, T], addressed
+ * through their strides (the reference's head-first tensors, or sequence-first views of the same memory); D is
+ * contiguous.  K = V = 128, chunk_size = 64.  GVA: HV % HK == 0, value head hv reads q/k head hv / (HV/HK).
+ * cu_seqlens / chunk_offsets (int32 [N+1], device; B == 1): packed variable-length sequences; chunk_offsets[n] is the
+ * index of sequence n's first chunk among all chunks; max_seqlen and total_chunks describe the packing.
+ * All six share one argument block; each entry point reads the fields listed for it.
+ *
+ * fla_b200_chunk_local_cumsum   (aclnnChunkLocalCumsum, _aclnn_ctypes.py:875-904)
+ *     g [B,H,T] or [B,H,T,D] f32|bf16|f16 -> out0 same shape, f32|bf16|f16:
+ *     out0[t] = scale * sum of g over t's chunk up to t (reverse != 0: from t to the chunk's end).
+ * fla_b200_chunk_scaled_dot_kkt (aclnnChunkScaledDotKkt, :907-936; golden test_npu_chunk_scaled_dot_kkt.py:60-103)
+ *     k [B,HK,T,128] bf16, g (chunk-local cumulative gate) and beta [B,HV,T] -> out0 [B,HV,T,64] f32:
+ *     out0[i,j] = beta_i exp(clamp(g_i - g_j, -50, 50)) k_i.k_j for j < i inside a chunk, else 0.
+ * fla_b200_solve_tri            (aclnnSolveTri, :1786-1800; solve_tri/README.md:9-13)
+ *     A [B,H,T,64] f32|bf16|f16 -> out0 same shape and dtype: per chunk (I + strict_lower(A))^-1.
+ * fla_b200_recompute_w_u_fwd    (aclnnRecomputeWUFwd, :618-651; golden test_npu_recompute_w_u_fwd.py:38-145)
+ *     k [B,HK,T,128], v [B,HV,T,128], A [B,HV,T,64] bf16 (the inverse), beta, g [B,HV,T]
+ *     -> out0 = w [B,HV,T,128], out1 = u [B,HV,T,128] bf16:  w = A (k beta e^g),  u = A (v beta).
+ * fla_b200_chunk_gated_delta_rule_fwd_h (aclnnChunkGatedDeltaRuleFwdH, :552-615; golden
+ *     tests/atk/chunk_gated_delta_rule_fwd_h/executor_chunk_gated_delta_rule_fwd_h.py:79-135)
+ *     k, w [B,HV,T,128], u [B,HV,T,128] bf16, g [B,HV,T], initial_state [N,HV,128,128] f32 (optional)
+ *     -> out0 = h [B,HV,NT,128,128] bf16 dense (state at the start of every chunk), out1 = v_new [B,HV,T,128] bf16,
+ *        out2 = final_state [N,HV,128,128] f32 (optional).
+ * fla_b200_chunk_fwd_o          (aclnnChunkFwdO, :517-549; golden chunk_fwd_o/tests/pta/test_fwd_o.py:52-128)
+ *     q, k [B,HK,T,128], v (= v_new) [B,HV,T,128], h [B,HV,NT,128,128] bf16, g [B,HV,T]
+ *     -> out0 = o [B,HV,T,128] bf16:  o = scale (e^{g_i} q h_c + tril(q k^T e^{g_i - g_j}) v).
+ * Workspace: 256 bytes (status word of the bounded device-side waits). */
+typedef struct fla_chunk_stage_args {
+  fla_tensor_t q, k, v, w, u, g, beta, A, h, initial_state;
+  fla_tensor_t out0, out1, out2;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  float scale;
+  int32_t chunk_size;
+  int32_t max_seqlen;
+  int32_t total_chunks;
+  int32_t reverse;
+} fla_chunk_stage_args;
+FLA_API int fla_b200_chunk_local_cumsum_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_scaled_dot_kkt_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_solve_tri_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_recompute_w_u_fwd_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_gated_delta_rule_fwd_h_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_fwd_o_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_local_cumsum(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_chunk_scaled_dot_kkt(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_solve_tri(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_recompute_w_u_fwd(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_chunk_gated_delta_rule_fwd_h(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes,
+                                                  void* stream);
+FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

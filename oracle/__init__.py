@@ -15,3 +15,4 @@ from .recurrent import recurrent_gated_delta_rule_golden  # noqa: F401
 from .conv import (causal_conv1d_bwd_ref, causal_conv1d_ref, causal_conv1d_update_ref,  # noqa: F401
                    causal_conv1d_update_spec_ref)
 from .inputs import make_gdn_inputs, make_kda_inputs, make_decode_inputs, make_conv_inputs  # noqa: F401
+from . import stages  # noqa: F401

@@ -14,7 +14,7 @@ import math
 import os
 import sys
 from pathlib import Path
-from typing import Optional, Tuple  # noqa: F401  (used by exec'd reference code)
+from typing import Any, Iterable, Optional, Tuple  # noqa: F401  (used by exec'd reference code)
 
 import numpy as np
 import torch
@@ -25,10 +25,12 @@ REF = Path(os.environ.get("FLA_REFERENCE_ROOT", "/root/reference"))
 sys.path.insert(0, str(HERE.parent.parent))
 
 
-def extract(path: Path, names):
+def extract(path: Path, names, extra=None):
     src = path.read_text()
     tree = ast.parse(src)
-    ns = {"torch": torch, "F": F, "math": math, "Optional": Optional, "Tuple": Tuple}
+    ns = {"torch": torch, "F": F, "math": math, "np": np, "Optional": Optional, "Tuple": Tuple, "Iterable": Iterable, "Any": Any}
+    if extra:
+        ns.update(extra)
     for node in tree.body:
         if isinstance(node, ast.FunctionDef) and node.name in names:
             exec(compile(ast.Module([node], []), str(path), "exec"), ns)
@@ -147,11 +149,73 @@ def kda_fixture():
                         o=f32(out), ht=f32(st))
 
 
+def stages_fixture():
+    """Per-operator goldens of the forward chain (cumsum -> kkt -> solve_tri -> w,u -> fwd_h -> fwd_o), each produced by the
+    reference's own CPU golden for that operator, on one fixed-length and one packed variable-length case."""
+    test_dir = REF / "torch_custom/fla_npu/test"
+    cumsum_ref = extract(test_dir / "test_npu_chunk_local_cumsum.py", ["reference_impl"])["reference_impl"]
+    kkt_ref = extract(test_dir / "test_npu_chunk_scaled_dot_kkt.py",
+                      ["iter_chunk_ranges", "chunk_scaled_dot_kkt_reference"])["chunk_scaled_dot_kkt_reference"]
+    tri_ref = extract(test_dir / "test_npu_solve_tri_ascend910b.py", ["solve_tril_golden"])["solve_tril_golden"]
+    wu_ns = extract(test_dir / "test_npu_recompute_w_u_fwd.py", ["get_bos_eos", "compute_w_golden", "compute_u_golden"])
+    common = extract(REF / "tests/atk/common/_ascendc_common_executor.py", ["_chunks", "_num_chunks"])
+    h_ref = extract(REF / "tests/atk/chunk_gated_delta_rule_fwd_h/executor_chunk_gated_delta_rule_fwd_h.py",
+                    ["_round_elem", "_matmul_npu_aligned", "_forward_h_ref"],
+                    extra={"_chunks": common["_chunks"], "_num_chunks": common["_num_chunks"]})["_forward_h_ref"]
+    o_ns = extract(REF / "fla/ops/ascendc/gdn/chunk_gdn_fwd/chunk_fwd_o/tests/pta/test_fwd_o.py",
+                   ["cdiv_torch", "prepare_chunk_indices", "prepare_lens", "prepare_chunk_offsets", "forward_o_trans_cpu"])
+    torch.Tensor.npu = lambda self: self   # the golden moves its CPU tensors "to the device" before computing
+
+    C, K, V, HK, HV, T = 64, 128, 128, 1, 2, 160
+    g_ = torch.Generator().manual_seed(23)
+    rnd = lambda *s: torch.randn(*s, generator=g_)  # noqa: E731
+    bf = lambda t: t.bfloat16().float()  # noqa: E731
+    q = bf(F.normalize(rnd(1, HK, T, K), dim=-1))
+    k = bf(F.normalize(rnd(1, HK, T, K), dim=-1))
+    v = bf(rnd(1, HV, T, V))
+    g_raw = F.logsigmoid(rnd(1, HV, T))
+    beta = bf(torch.sigmoid(rnd(1, HV, T)))
+    out = dict(q=f32(q), k=f32(k), v=f32(v), g_raw=f32(g_raw), beta=f32(beta))
+    for tag, cu in (("fix", None), ("var", [0, 70, 160])):
+        cu_t = None if cu is None else torch.tensor(cu)
+        gam = cumsum_ref(g_raw, C, False, 1.0, cu_t, torch.float32)
+        rev = cumsum_ref(g_raw, C, True, 0.5, cu_t, torch.float32)
+        idx = None
+        if cu is not None:
+            idx = [x for si, (a, b) in enumerate(zip(cu[:-1], cu[1:])) for ci in range((b - a + C - 1) // C) for x in (si, ci)]
+        A = kkt_ref(k, gam, beta, C, cu, idx)
+        # the inverse golden has no variable-length form: invert sequence by sequence
+        if cu is None:
+            X = tri_ref(A, C, layout="bnsd")
+        else:
+            X = torch.cat([tri_ref(A[:, :, a:b].contiguous(), C, layout="bnsd") for a, b in zip(cu[:-1], cu[1:])], dim=2)
+        Xb = bf(X)
+        NT = len(idx) // 2 if idx else (T + C - 1) // C
+        w = wu_ns["compute_w_golden"](k, v, beta, Xb, gam, cu, idx, 1, HV, T, K, C, NT, HK)
+        u = wu_ns["compute_u_golden"](v, beta, Xb, cu, idx, 1, HV, T, C, NT)
+        wb, ub = bf(w), bf(u)
+        if cu is None:
+            h, v_new = h_ref(dict(k=k, w=wb, u=ub, g=gam, chunk_size=C), golden_mode="fp64")
+            h, v_new = h.float(), v_new.float()
+        else:
+            parts = [h_ref(dict(k=k[:, :, a:b], w=wb[:, :, a:b], u=ub[:, :, a:b], g=gam[:, :, a:b], chunk_size=C), golden_mode="fp64")
+                     for a, b in zip(cu[:-1], cu[1:])]
+            h = torch.cat([p_[0] for p_ in parts], dim=2).float()
+            v_new = torch.cat([p_[1] for p_ in parts], dim=2).float()
+        hb, vnb = bf(h), bf(v_new)
+        o = o_ns["forward_o_trans_cpu"](q, k, vnb, hb, gam, None, K ** -0.5, C, cu_t, None)
+        out.update({f"{tag}_gam": f32(gam), f"{tag}_rev": f32(rev), f"{tag}_A": f32(A), f"{tag}_X": f32(X), f"{tag}_w": f32(w),
+                    f"{tag}_u": f32(u), f"{tag}_h": f32(h), f"{tag}_v_new": f32(v_new), f"{tag}_o": f32(o)})
+    del torch.Tensor.npu
+    np.savez_compressed(HERE / "stages_golden.npz", **out)
+
+
 if __name__ == "__main__":
     gdn_fixture()
     decode_fixture()
     conv_fixture()
     conv_bwd_fixture()
     kda_fixture()
+    stages_fixture()
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)
