@@ -18,6 +18,7 @@
 #include "gdn_common.cuh"
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
+#include "tensor_map.h"
 
 namespace fla {
 
@@ -220,10 +221,27 @@ __global__ void __launch_bounds__(256) stage_solve_tri_kernel(StageParams p) {
   const int64_t b = p.cu_seqlens ? 0 : n;
   const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + chunk * kC;
   float* AT = tri_sm + grp * kC * kSolveStride;
-  if (active) {
-    // thread c stages row c: AT[j][c] = A[c][j] for j < c
-    const int64_t ro = row_off(p.a, b, hh, t0 + c);
-    for (int j = 0; j < kC; ++j) AT[j * kSolveStride + c] = (c < rows && j < c) ? ld_any(p.a.p, ro + j, p.a.dtype) : 0.f;
+  // The four matrices of the CTA are staged together as AT[j][i] = A[i][j] (j < i).  A warp covers 8 rows x 16 columns:
+  // each thread reads four consecutive elements of a row (64 contiguous bytes per row and warp for fp32) and the
+  // transposed stores of a warp fall on at most two addresses per bank.
+  const bool vec4 = p.a.dtype == FLA_F32 && (reinterpret_cast<uintptr_t>(p.a.p) & 15) == 0 && ((p.a.sb | p.a.sh | p.a.st) & 3) == 0;
+#pragma unroll 4
+  for (int idx = tid; idx < 4 * kC * 16; idx += 256) {
+    const int m = idx >> 10, i = ((idx >> 5) & 7) * 8 + (idx & 7), jc = ((idx >> 8) & 3) * 4 + ((idx >> 3) & 3);
+    const int hm = blockIdx.y * 4 + m;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (hm < p.H && i < rows && jc * 4 < i) {
+      const int64_t off = row_off(p.a, b, hm, t0 + i) + jc * 4;
+      if (vec4) {
+        const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(p.a.p) + off);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = ld_any(p.a.p, off + q, p.a.dtype);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) tri_sm[m * kC * kSolveStride + (jc * 4 + q) * kSolveStride + i] = (jc * 4 + q < i) ? v[q] : 0.f;
   }
   __syncthreads();
   if (!active) return;
@@ -253,86 +271,106 @@ __global__ void __launch_bounds__(256) stage_solve_tri_kernel(StageParams p) {
 
 // ----------------------------------------------------------------------------- recompute_w_u_fwd
 // u = X (v beta),  w = X (k beta e^g) per chunk and value head; X is the chunk's 64 x 64 block of (I + A)^-1.
-constexpr uint32_t kWuSmem = 16384 + 4 * 16384;   // X | (k beta e^g) hi, lo | (v beta) hi, lo
-__global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p) {
+// X, k and v rows arrive as TMA tiles; the scaled rows replace the raw k / v tiles in place (bf16 value) next to a
+// residual panel.
+constexpr uint32_t wuOffX = 0, wuOffKh = 8192, wuOffKl = 24576, wuOffVh = 40960, wuOffVl = 57344;
+constexpr uint32_t kWuSmem = 73728;
+__global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_k,
+                                                       const __grid_constant__ CUtensorMap tm_v,
+                                                       const __grid_constant__ CUtensorMap tm_x) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   __shared__ float rs_k[kC], rs_v[kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar;
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   if (c >= sq.nt) return;
   const int rows = min(kC, sq.len - c * kC);
-  const int64_t b = p.cu_seqlens ? 0 : n;
-  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int b = p.cu_seqlens ? 0 : n;
+  const int t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
   const int hk = hv / (p.H / p.HK);
+  const uint32_t sb = smem_u32(smem);
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 256);
     tmem_relinquish();
   }
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
+    mbar_init(&load_bar, 1);
     mbar_init_fence();
+    mbar_arrive_expect_tx(&load_bar, 8192 + 16384 + 16384);
+    tma_load_tile4(sb + wuOffX, &tm_x, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wuOffKh, &tm_k, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + wuOffKh + 8192, &tm_k, 64, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + wuOffVh, &tm_v, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wuOffVh + 8192, &tm_v, 64, t0, hv, b, &load_bar);
   }
   if (tid < kC) {
     const float bt = tid < rows ? ld_any(p.beta.p, row_off(p.beta, b, hv, t0 + tid), p.beta.dtype) : 0.f;
     const float gm = tid < rows ? ld_any(p.g.p, row_off(p.g, b, hv, t0 + tid), p.g.dtype) : 0.f;
-    rs_v[tid] = bt;
+    rs_v[tid] = bt;             // rows past the end of the sequence are scaled to zero
     rs_k[tid] = bt * __expf(gm);
   }
-  // X block: rows >= rows and columns >= rows zeroed (row 128-byte panel rows, 64 columns)
-  {
-    const bf16* xs = static_cast<const bf16*>(p.a.p) + row_off(p.a, b, hv, t0);
-    for (int idx = tid; idx < kC * 8; idx += 128) {
-      const int r = idx >> 3, ch = idx & 7;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (r < rows && ch * 8 < rows) {
-        val = *reinterpret_cast<const uint4*>(xs + r * p.a.st + ch * 8);
-        if (ch * 8 + 8 > rows) {
-          uint16_t* e = reinterpret_cast<uint16_t*>(&val);
+  __syncthreads();
+  bool ok = mbar_wait(&load_bar, 0, p.status, FLA_ERR_TIMEOUT);
+  // scale the raw rows in place and write the residual panels
+  for (int idx = tid; idx < 2 * kC * 16; idx += 128) {
+    const int isv = idx >> 10, r = (idx >> 4) & 63, ch = idx & 15;
+    const uint32_t off = (ch >> 3) * 8192 + panel_chunk_off(r, ch & 7);
+    uint8_t* hi = smem + (isv ? wuOffVh : wuOffKh) + off;
+    uint8_t* lo = smem + (isv ? wuOffVl : wuOffKl) + off;
+    float f[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(hi), f);
+    const float sc = isv ? rs_v[r] : rs_k[r];
+    uint4 h4 = make_uint4(0, 0, 0, 0), l4 = make_uint4(0, 0, 0, 0);
+    if (r < rows) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (ch * 8 + j >= rows) e[j] = 0;
-        }
-      }
-      *reinterpret_cast<uint4*>(smem + panel_chunk_off(r, ch)) = val;
+      for (int j = 0; j < 8; ++j) f[j] *= sc;
+      split8(f, h4, l4);
+    }
+    *reinterpret_cast<uint4*>(hi) = h4;
+    *reinterpret_cast<uint4*>(lo) = l4;
+  }
+  if (rows < kC) {   // a short chunk: columns of X past its end may hold anything
+    for (int idx = tid; idx < kC * kC; idx += 128) {
+      const int r = idx >> 6, cc = idx & 63;
+      if (cc >= rows) *reinterpret_cast<uint16_t*>(smem + wuOffX + panel_off(r, cc)) = 0;
     }
   }
-  __syncthreads();
-  stage_rows128(smem + 16384, 8192, static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, t0), p.k.st, rows, rs_k, tid, 128, smem + 32768);
-  stage_rows128(smem + 49152, 8192, static_cast<const bf16*>(p.v.p) + row_off(p.v, b, hv, t0), p.v.st, rows, rs_v, tid, 128, smem + 65536);
   fence_async_smem();
   tc_fence_before();
-  __syncthreads();
+  ok = __syncthreads_and(ok);
   const uint32_t tbase = tmem_base_s;
-  const uint32_t sb = smem_u32(smem);
-  if (tid == 0) {
+  if (ok) {
+    if (tid == 0) {
+      tc_fence_after();
+      // X as A: rows 64..127 of the M = 128 tile read the k panels behind it and are never used
+      const Operand opX{sb + wuOffX, 8192, 0}, opKh{sb + wuOffKh, 8192, 1}, opKl{sb + wuOffKl, 8192, 1}, opVh{sb + wuOffVh, 8192, 1},
+          opVl{sb + wuOffVl, 8192, 1};
+      mma_tile(tbase, opX, opKh, 128, 128, 4, false);
+      mma_tile(tbase, opX, opKl, 128, 128, 4, true);
+      mma_tile(tbase + 128, opX, opVh, 128, 128, 4, false);
+      mma_tile(tbase + 128, opX, opVl, 128, 128, 4, true);
+      mma_commit(&mma_bar);
+    }
+    ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT);
     tc_fence_after();
-    const Operand opX{sb, 16384, 0}, opKh{sb + 16384, 8192, 1}, opKl{sb + 32768, 8192, 1}, opVh{sb + 49152, 8192, 1},
-        opVl{sb + 65536, 8192, 1};
-    mma_tile(tbase, opX, opKh, 128, 128, 4, false);
-    mma_tile(tbase, opX, opKl, 128, 128, 4, true);
-    mma_tile(tbase + 128, opX, opVh, 128, 128, 4, false);
-    mma_tile(tbase + 128, opX, opVl, 128, 128, 4, true);
-    mma_commit(&mma_bar);
-  }
-  const bool ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT);
-  tc_fence_after();
-  if (warp < 2) {
-    const int i = tid;
+    if (warp < 2) {
+      const int i = tid;
 #pragma unroll
-    for (int which = 0; which < 2; ++which) {
-      const StageView& ov = which ? p.o1 : p.o0;
-      bf16* dst = static_cast<bf16*>(const_cast<void*>(ov.p)) + row_off(ov, b, hv, t0 + i);
+      for (int which = 0; which < 2; ++which) {
+        const StageView& ov = which ? p.o1 : p.o0;
+        bf16* dst = static_cast<bf16*>(const_cast<void*>(ov.p)) + row_off(ov, b, hv, t0 + i);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float r[64];
-        tmem_ld_row64(tmem_addr(tbase, warp * 32, which * 128 + half * 64), r);
-        if (ok && i < rows) {
+        for (int half = 0; half < 2; ++half) {
+          float r[64];
+          tmem_ld_row64(tmem_addr(tbase, warp * 32, which * 128 + half * 64), r);
+          if (ok && i < rows) {
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
+            for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
+          }
         }
       }
     }
@@ -345,36 +383,62 @@ __global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p) {
 // ----------------------------------------------------------------------------- chunk_gated_delta_rule_fwd_h
 // Sequential over the chunks of one (sequence, value head, block of 64 value columns):
 //   h_c = S;  v_new = u - w S;  S <- e^{g_last} S + k^T (e^{g_last - g} v_new).
-// S lives in tensor memory in fp32 (lane = key dim, 64 columns); a bf16 copy is the MMA operand and the stored h_c.
-constexpr uint32_t hsOffW = 0, hsOffK = 32768, hsOffS = 49152, hsOffSl = 65536, hsOffVd = 81920, hsOffVdl = 90112;
-constexpr uint32_t kFwdHSmem = 98304;
-__global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p) {
+// S lives in tensor memory in fp32 (lane = key dim, 64 columns); its bf16 value is the stored h_c and, with a bf16
+// residual, the MMA operand.  w, k and u tiles of the next chunk are fetched by TMA as soon as their buffer is free.
+constexpr uint32_t hsOffW = 0, hsOffK = 16384, hsOffS = 32768, hsOffSl = 49152, hsOffVd = 65536, hsOffVdl = 73728, hsOffU = 81920;
+constexpr uint32_t kFwdHSmem = 90112;
+__global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_w,
+                                                          const __grid_constant__ CUtensorMap tm_k,
+                                                          const __grid_constant__ CUtensorMap tm_u) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   __shared__ float gam_s[kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar;
+  __shared__ __align__(8) uint64_t mma_bar, w_bar, k_bar, u_bar;
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n = blockIdx.z, hv = blockIdx.y, vb = blockIdx.x;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
-  const int64_t b = p.cu_seqlens ? 0 : n;
-  const int64_t tbeg = p.cu_seqlens ? sq.bos : 0;
+  const int b = p.cu_seqlens ? 0 : n;
+  const int tbeg = p.cu_seqlens ? sq.bos : 0;
   const int hk = hv / (p.H / p.HK);
+  const uint32_t sb = smem_u32(smem);
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 128);
     tmem_relinquish();
   }
+  auto load_w = [&](int c) {
+    mbar_arrive_expect_tx(&w_bar, 16384);
+    tma_load_tile4(sb + hsOffW, &tm_w, 0, tbeg + c * kC, hv, b, &w_bar);
+    tma_load_tile4(sb + hsOffW + 8192, &tm_w, 64, tbeg + c * kC, hv, b, &w_bar);
+  };
+  auto load_k = [&](int c) {
+    mbar_arrive_expect_tx(&k_bar, 16384);
+    tma_load_tile4(sb + hsOffK, &tm_k, 0, tbeg + c * kC, hk, b, &k_bar);
+    tma_load_tile4(sb + hsOffK + 8192, &tm_k, 64, tbeg + c * kC, hk, b, &k_bar);
+  };
+  auto load_u = [&](int c) {
+    mbar_arrive_expect_tx(&u_bar, 8192);
+    tma_load_tile4(sb + hsOffU, &tm_u, vb * 64, tbeg + c * kC, hv, b, &u_bar);
+  };
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
+    mbar_init(&w_bar, 1);
+    mbar_init(&k_bar, 1);
+    mbar_init(&u_bar, 1);
     mbar_init_fence();
+    if (sq.nt > 0) {
+      load_w(0);
+      load_k(0);
+      load_u(0);
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
-  const uint32_t sb = smem_u32(smem);
-  const Operand opW{sb + hsOffW, 16384, 0}, opS{sb + hsOffS, 16384, 1}, opSl{sb + hsOffSl, 16384, 1}, opKt{sb + hsOffK, 8192, 1},
+  // w as A: rows 64..127 of the M = 128 tile read the memory behind each 64-row panel and are never used
+  const Operand opW{sb + hsOffW, 8192, 0}, opS{sb + hsOffS, 16384, 1}, opSl{sb + hsOffSl, 16384, 1}, opKt{sb + hsOffK, 8192, 1},
       opVd{sb + hsOffVd, 8192, 1}, opVdl{sb + hsOffVdl, 8192, 1};
   // my state row (key dim tid, value columns vb*64 ..)
   {
@@ -392,22 +456,27 @@ __global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p) {
     }
     tmem_st_row64(trow, s);
   }
-  uint32_t mphase = 0;
+  auto load_gate = [&](int c) -> float {
+    if (tid >= kC || c >= sq.nt) return 0.f;
+    const int rows_c = min(kC, sq.len - c * kC);
+    return ld_any(p.g.p, row_off(p.g, b, hv, tbeg + c * kC + min(tid, rows_c - 1)), p.g.dtype);
+  };
+  float pf_g = load_gate(0);
+  uint32_t mphase = 0, lphase = 0;
   bool ok = true;
-  for (int c = 0; c < sq.nt && ok; ++c) {
+  for (int c = 0; c < sq.nt; ++c) {
     const int rows = min(kC, sq.len - c * kC);
-    const int64_t t0 = tbeg + c * kC;
-    if (tid < kC) gam_s[tid] = ld_any(p.g.p, row_off(p.g, b, hv, t0 + min(tid, rows - 1)), p.g.dtype);
-    stage_rows128(smem + hsOffW, 16384, static_cast<const bf16*>(p.w.p) + row_off(p.w, b, hv, t0), p.w.st, rows, nullptr, tid, 128);
-    stage_rows128(smem + hsOffK, 8192, static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, t0), p.k.st, rows, nullptr, tid, 128);
+    const int t0 = tbeg + c * kC;
+    if (tid < kC) gam_s[tid] = pf_g;
+    pf_g = load_gate(c + 1);
     __syncthreads();
     const float g_last = gam_s[rows - 1];
     {
       float s[64];
       tmem_ld_row64(trow, s);
       row64_to_hilo(smem + hsOffS, smem + hsOffSl, tid, s);
-      bf16* hd = static_cast<bf16*>(const_cast<void*>(p.o0.p)) + ((b * p.H + hv) * p.o0.sh + (p.cu_seqlens ? sq.cbase : 0) + c) * int64_t(kK * kV) +
-                 tid * kV + vb * 64;
+      bf16* hd = static_cast<bf16*>(const_cast<void*>(p.o0.p)) +
+                 ((int64_t(b) * p.H + hv) * p.o0.sh + (p.cu_seqlens ? sq.cbase : 0) + c) * int64_t(kK * kV) + tid * kV + vb * 64;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(hd + ch * 8) = pack8(s + ch * 8);
       const float el = __expf(g_last);
@@ -419,6 +488,7 @@ __global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p) {
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
+      ok = mbar_wait(&w_bar, lphase, p.status, FLA_ERR_TIMEOUT);
       tc_fence_after();
       mma_tile(tbase + 64, opW, opS, 128, 64, 8, false);
       mma_tile(tbase + 64, opW, opSl, 128, 64, 8, true);
@@ -426,21 +496,17 @@ __global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p) {
     }
     float uval[64];
     if (warp < 2) {
-      const bf16* us = static_cast<const bf16*>(p.u.p) + row_off(p.u, b, hv, t0 + tid) + vb * 64;
+      ok = mbar_wait(&u_bar, lphase, p.status, FLA_ERR_TIMEOUT) && ok;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (tid < rows) raw = *reinterpret_cast<const uint4*>(us + ch * 8);
-        unpack_bf16x8(raw, uval + ch * 8);
-      }
+      for (int ch = 0; ch < 8; ++ch) unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + hsOffU + panel_chunk_off(tid, ch)), uval + ch * 8);
     }
-    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT) && ok;
     mphase ^= 1;
     tc_fence_after();
     if (warp < 2) {
       float d1[64];
       tmem_ld_row64(trow + 64, d1);
-      const bool live = tid < rows;
+      const bool live = tid < rows;     // rows past the end of the sequence (foreign or zero tile rows) carry nothing
 #pragma unroll
       for (int i = 0; i < 64; ++i) d1[i] = live ? uval[i] - d1[i] : 0.f;
       if (live && ok) {
@@ -457,15 +523,22 @@ __global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p) {
     tc_fence_before();
     if (!__syncthreads_and(ok)) { ok = false; break; }
     if (tid == 0) {
+      if (c + 1 < sq.nt) {   // w and u of this chunk are consumed
+        load_w(c + 1);
+        load_u(c + 1);
+      }
+      ok = mbar_wait(&k_bar, lphase, p.status, FLA_ERR_TIMEOUT);
       tc_fence_after();
       mma_tile(tbase, opKt, opVd, 128, 64, 4, true);
       mma_tile(tbase, opKt, opVdl, 128, 64, 4, true);
       mma_commit(&mma_bar);
     }
-    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT) && ok;
     mphase ^= 1;
+    lphase ^= 1;
     tc_fence_after();
     if (!__syncthreads_and(ok)) { ok = false; break; }
+    if (tid == 0 && c + 1 < sq.nt) load_k(c + 1);
   }
   if (ok && p.want_final) {
     float s[64];
@@ -480,59 +553,65 @@ __global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p) {
 }
 
 // ----------------------------------------------------------------------------- chunk_fwd_o
-// o = scale [ e^{g_i} (q h_c) + tril(q k^T e^{g_i - g_j}) v_new ] per chunk and value head.
-constexpr uint32_t foOffQ = 0, foOffK = 32768, foOffH = 49152, foOffVn = 81920, foOffP = 98304;
-constexpr uint32_t kFwdOSmem = 114688;
-__global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p) {
+// o = scale [ e^{g_i} (q h_c) + tril(q k^T e^{g_i - g_j}) v_new ] per chunk and value head.  All operands arrive as TMA
+// tiles issued up front; the decayed score tile is split into a bf16 value and a residual (which reuses the k panels).
+constexpr uint32_t foOffP = 0, foOffQ = 8192, foOffK = 24576, foOffH = 40960, foOffVn = 73728;
+constexpr uint32_t kFwdOSmem = 90112;
+__global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                          const __grid_constant__ CUtensorMap tm_k,
+                                                          const __grid_constant__ CUtensorMap tm_v,
+                                                          const __grid_constant__ CUtensorMap tm_h) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   __shared__ float gam_s[kC];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar;
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   if (c >= sq.nt) return;
   const int rows = min(kC, sq.len - c * kC);
-  const int64_t b = p.cu_seqlens ? 0 : n;
-  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int b = p.cu_seqlens ? 0 : n;
+  const int t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
   const int hk = hv / (p.H / p.HK);
+  const uint32_t sb = smem_u32(smem);
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 256);
     tmem_relinquish();
   }
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
+    mbar_init(&load_bar, 1);
     mbar_init_fence();
+    mbar_arrive_expect_tx(&load_bar, 16384 + 16384 + 32768 + 16384);
+    tma_load_tile4(sb + foOffQ, &tm_q, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + foOffQ + 8192, &tm_q, 64, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + foOffK, &tm_k, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + foOffK + 8192, &tm_k, 64, t0, hk, b, &load_bar);
+    // h_c: 128 key rows x 128 value columns of the dense [chunks * 128, 128] state tensor
+    const int hrow = int((((int64_t(b) * p.H + hv) * p.h.sh + (p.cu_seqlens ? sq.cbase : 0) + c)) * kK);
+    tma_load_tile4(sb + foOffH, &tm_h, 0, hrow, 0, 0, &load_bar);
+    tma_load_tile4(sb + foOffH + 16384, &tm_h, 64, hrow, 0, 0, &load_bar);
+    tma_load_tile4(sb + foOffVn, &tm_v, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + foOffVn + 8192, &tm_v, 64, t0, hv, b, &load_bar);
   }
   if (tid < kC) gam_s[tid] = ld_any(p.g.p, row_off(p.g, b, hv, t0 + min(tid, rows - 1)), p.g.dtype);
-  stage_rows128(smem + foOffQ, 16384, static_cast<const bf16*>(p.q.p) + row_off(p.q, b, hk, t0), p.q.st, rows, nullptr, tid, 128);
-  stage_rows128(smem + foOffK, 8192, static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, t0), p.k.st, rows, nullptr, tid, 128);
-  stage_rows128(smem + foOffVn, 8192, static_cast<const bf16*>(p.v.p) + row_off(p.v, b, hv, t0), p.v.st, rows, nullptr, tid, 128);
-  {
-    // h_c: 128 key rows x 128 value columns, dense
-    const bf16* hs = static_cast<const bf16*>(p.h.p) + ((b * p.H + hv) * p.h.sh + (p.cu_seqlens ? sq.cbase : 0) + c) * int64_t(kK * kV);
-    for (int idx = tid; idx < kK * 16; idx += 128) {
-      const int r = idx >> 4, ch = idx & 15;
-      *reinterpret_cast<uint4*>(smem + foOffH + (ch >> 3) * 16384 + panel_chunk_off(r, ch & 7)) =
-          *reinterpret_cast<const uint4*>(hs + r * kV + ch * 8);
-    }
-  }
-  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
   const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
-  const uint32_t sb = smem_u32(smem);
-  const Operand opQ{sb + foOffQ, 16384, 0}, opK{sb + foOffK, 8192, 0}, opH{sb + foOffH, 16384, 1}, opVn{sb + foOffVn, 8192, 1},
-      opP{sb + foOffP, 16384, 0}, opPl{sb + foOffK, 16384, 0};   // the residual of P reuses the k panels (dead after q k^T)
+  // q and the score tile as A: rows 64..127 of the M = 128 tiles read the panels behind them and are never used
+  const Operand opQ{sb + foOffQ, 8192, 0}, opK{sb + foOffK, 8192, 0}, opH{sb + foOffH, 16384, 1}, opVn{sb + foOffVn, 8192, 1},
+      opP{sb + foOffP, 8192, 0}, opPl{sb + foOffK, 8192, 0};
+  bool ok = true;
   if (tid == 0) {
+    ok = mbar_wait(&load_bar, 0, p.status, FLA_ERR_TIMEOUT);
     tc_fence_after();
     mma_tile(tbase, opQ, opK, 128, 64, 8, false);          // columns 0..63: q k^T
     mma_tile(tbase + 64, opQ, opH, 128, 128, 8, false);    // columns 64..191: q h_c
     mma_commit(&mma_bar);
   }
-  bool ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT);
+  ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT) && ok;
   tc_fence_after();
   if (warp < 2) {
     const int i = tid;
@@ -540,6 +619,7 @@ __global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p) {
     {
       float s[64];
       tmem_ld_row64(trow, s);
+      // rows and columns past the end of the sequence (foreign or zero tile rows) are masked here
 #pragma unroll
       for (int j = 0; j < 64; ++j) s[j] = (j <= i && j < rows && i < rows) ? s[j] * __expf(gi - gam_s[j]) : 0.f;
       row64_to_hilo(smem + foOffP, smem + foOffK, i, s);
@@ -651,6 +731,12 @@ int prepare_status(void* workspace, uint64_t bytes, cudaStream_t cs, StageParams
   return FLA_OK;
 }
 
+// 64-token x 64-column bf16 tiles of a [B, H, T, D] tensor
+int token_tile_map(const fla_tensor_t& t, CUtensorMap* map) {
+  return make_bhtd_tile_map(map, t.data, 2, uint64_t(t.shape[3]), uint64_t(t.shape[2]), uint64_t(t.shape[1]), uint64_t(t.shape[0]),
+                            uint64_t(t.stride[2]), uint64_t(t.stride[1]), uint64_t(t.stride[0]), 64, 64);
+}
+
 template <typename Kern>
 int opt_in_smem(Kern kern, uint32_t bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
@@ -760,8 +846,10 @@ extern "C" FLA_API int fla_b200_recompute_w_u_fwd(const fla_chunk_stage_args* a,
   p.HK = int(HK);
   if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
   if ((st = opt_in_smem(stage_wu_kernel, kWuSmem + 1024))) return st;
+  CUtensorMap tm_k, tm_v, tm_x;
+  if (token_tile_map(a->k, &tm_k) || token_tile_map(a->v, &tm_v) || token_tile_map(a->A, &tm_x)) return FLA_ERR_CUDA;
   KernelTimer kt("recompute_w_u_fwd", cs);
-  stage_wu_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kWuSmem + 1024, cs>>>(p);
+  stage_wu_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kWuSmem + 1024, cs>>>(p, tm_k, tm_v, tm_x);
   return cuda_status(cudaGetLastError());
 }
 
@@ -804,8 +892,10 @@ extern "C" FLA_API int fla_b200_chunk_gated_delta_rule_fwd_h(const fla_chunk_sta
   p.HK = int(HK);
   if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
   if ((st = opt_in_smem(stage_fwd_h_kernel, kFwdHSmem + 1024))) return st;
+  CUtensorMap tm_w, tm_k, tm_u;
+  if (token_tile_map(a->w, &tm_w) || token_tile_map(a->k, &tm_k) || token_tile_map(a->u, &tm_u)) return FLA_ERR_CUDA;
   KernelTimer kt("chunk_fwd_h", cs);
-  stage_fwd_h_kernel<<<dim3(kV / 64, unsigned(gm.H), gm.N), 128, kFwdHSmem + 1024, cs>>>(p);
+  stage_fwd_h_kernel<<<dim3(kV / 64, unsigned(gm.H), gm.N), 128, kFwdHSmem + 1024, cs>>>(p, tm_w, tm_k, tm_u);
   return cuda_status(cudaGetLastError());
 }
 
@@ -838,7 +928,11 @@ extern "C" FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* a, void*
   if (!(a->scale == a->scale)) return FLA_ERR_VALUE;
   if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
   if ((st = opt_in_smem(stage_fwd_o_kernel, kFwdOSmem + 1024))) return st;
+  CUtensorMap tm_q, tm_k, tm_v, tm_h;
+  if (token_tile_map(a->q, &tm_q) || token_tile_map(a->k, &tm_k) || token_tile_map(a->v, &tm_v) ||
+      make_bhtd_tile_map(&tm_h, h.data, 2, kV, uint64_t(gm.B) * gm.H * NT * kK, 1, 1, kV, 0, 0, 64, 128))
+    return FLA_ERR_CUDA;
   KernelTimer kt("chunk_fwd_o", cs);
-  stage_fwd_o_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kFwdOSmem + 1024, cs>>>(p);
+  stage_fwd_o_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kFwdOSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_h);
   return cuda_status(cudaGetLastError());
 }

@@ -61,7 +61,8 @@ FLA_API int fla_b200_version(void);
  * launching stream.  Enabling or disabling clears earlier records.  kernel_timing_read synchronises the
  * recorded events and returns the summed duration and the number of launches of `kernel_name`
  * (names: "gdn_prep", "tri_inverse", "kda_prep", "kda_fwd", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par", "recurrent_gdn", "causal_conv1d_fwd",
- * "causal_conv1d_update"). */
+ * "causal_conv1d_update", "causal_conv1d_bwd", "kda_bwd_dhu", "kda_bwd_par", "chunk_local_cumsum", "chunk_scaled_dot_kkt",
+ * "solve_tri", "recompute_w_u_fwd", "chunk_fwd_h", "chunk_fwd_o"). */
 FLA_API int fla_b200_kernel_timing_enable(int enable);
 FLA_API int fla_b200_kernel_timing_read(const char* kernel_name, float* total_ms, int* launches);
 
