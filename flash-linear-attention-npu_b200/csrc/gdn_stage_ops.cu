@@ -667,6 +667,296 @@ __global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p, const _
   if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
+// ----------------------------------------------------------------------------- chunk_bwd_dv_local
+// dv_j = sum_{i >= j} scale (k_j . q_i) e^{g_i - g_j} dO_i inside a chunk, per value head.
+constexpr uint32_t dvOffP = 0, dvOffPl = 8192, dvOffK = 16384, dvOffQ = 32768, dvOffDo = 49152;
+constexpr uint32_t kDvLocalSmem = 65536;
+__global__ void __launch_bounds__(128) stage_dv_local_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                             const __grid_constant__ CUtensorMap tm_k,
+                                                             const __grid_constant__ CUtensorMap tm_do) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float gam_s[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int b = p.cu_seqlens ? 0 : n;
+  const int t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int hk = hv / (p.H / p.HK);
+  const uint32_t sb = smem_u32(smem);
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init(&load_bar, 1);
+    mbar_init_fence();
+    mbar_arrive_expect_tx(&load_bar, 3 * 16384);
+    tma_load_tile4(sb + dvOffK, &tm_k, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + dvOffK + 8192, &tm_k, 64, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + dvOffQ, &tm_q, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + dvOffQ + 8192, &tm_q, 64, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + dvOffDo, &tm_do, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + dvOffDo + 8192, &tm_do, 64, t0, hv, b, &load_bar);
+  }
+  if (tid < kC) gam_s[tid] = ld_any(p.g.p, row_off(p.g, b, hv, t0 + min(tid, rows - 1)), p.g.dtype);
+  tc_fence_before();
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  // k and the score tile as A: rows 64..127 of the M = 128 tiles read the panels behind them and are never used
+  const Operand opK{sb + dvOffK, 8192, 0}, opQ{sb + dvOffQ, 8192, 0}, opDo{sb + dvOffDo, 8192, 1}, opP{sb + dvOffP, 8192, 0},
+      opPl{sb + dvOffPl, 8192, 0};
+  bool ok = true;
+  if (tid == 0) {
+    ok = mbar_wait(&load_bar, 0, p.status, FLA_ERR_TIMEOUT);
+    tc_fence_after();
+    mma_tile(tbase, opK, opQ, 128, 64, 8, false);   // rows j (keys), columns i (queries)
+    mma_commit(&mma_bar);
+  }
+  ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT) && ok;
+  tc_fence_after();
+  if (warp < 2) {
+    const int j = tid;
+    const float gj = gam_s[j];
+    float s[64];
+    tmem_ld_row64(trow, s);
+#pragma unroll
+    for (int i = 0; i < 64; ++i) s[i] = (i >= j && i < rows && j < rows) ? p.scale * s[i] * __expf(gam_s[i] - gj) : 0.f;
+    row64_to_hilo(smem + dvOffP, smem + dvOffPl, j, s);
+  }
+  fence_async_smem();
+  tc_fence_before();
+  ok = __syncthreads_and(ok);
+  if (ok) {
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase + 64, opP, opDo, 128, 128, 4, false);
+      mma_tile(tbase + 64, opPl, opDo, 128, 128, 4, true);
+      mma_commit(&mma_bar);
+    }
+    ok = mbar_wait(&mma_bar, 1, p.status, FLA_ERR_TIMEOUT);
+    tc_fence_after();
+    if (warp < 2) {
+      const int j = tid;
+      bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o0.p)) + row_off(p.o0, b, hv, t0 + j);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float r[64];
+        tmem_ld_row64(trow + 64 + half * 64, r);
+        if (ok && j < rows) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+// ----------------------------------------------------------------------------- chunk_gated_delta_rule_bwd_dhu
+// Reverse scan over the chunks of one (sequence, value head, block of 64 value columns):
+//   dh_c = dS;  dv2 = dv + e^{g_last - g} (k dS);  dS <- e^{g_last} dS + q^T (scale e^{g} dO) - w^T dv2.
+// dS lives in tensor memory in fp32 (lane = key dim); its bf16 value is the stored dh_c and, with a residual, the MMA
+// operand.  k and w share one buffer (k is consumed by the first product of a chunk, w by the last).
+constexpr uint32_t bhOffKW = 0, bhOffQ = 16384, bhOffS = 32768, bhOffSl = 49152, bhOffDo = 65536, bhOffDol = 73728, bhOffDv = 81920,
+                   bhOffDvl = 90112;
+constexpr uint32_t kBwdDhuSmem = 98304;
+__global__ void __launch_bounds__(128) stage_bwd_dhu_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                            const __grid_constant__ CUtensorMap tm_k,
+                                                            const __grid_constant__ CUtensorMap tm_w,
+                                                            const __grid_constant__ CUtensorMap tm_do,
+                                                            const __grid_constant__ CUtensorMap tm_dv) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float gam_s[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar, kw_bar, q_bar, d_bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, hv = blockIdx.y, vb = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const int b = p.cu_seqlens ? 0 : n;
+  const int tbeg = p.cu_seqlens ? sq.bos : 0;
+  const int hk = hv / (p.H / p.HK);
+  const uint32_t sb = smem_u32(smem);
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 128);
+    tmem_relinquish();
+  }
+  auto load_k = [&](int c) {
+    mbar_arrive_expect_tx(&kw_bar, 16384);
+    tma_load_tile4(sb + bhOffKW, &tm_k, 0, tbeg + c * kC, hk, b, &kw_bar);
+    tma_load_tile4(sb + bhOffKW + 8192, &tm_k, 64, tbeg + c * kC, hk, b, &kw_bar);
+  };
+  auto load_w = [&](int c) {
+    mbar_arrive_expect_tx(&kw_bar, 16384);
+    tma_load_tile4(sb + bhOffKW, &tm_w, 0, tbeg + c * kC, hv, b, &kw_bar);
+    tma_load_tile4(sb + bhOffKW + 8192, &tm_w, 64, tbeg + c * kC, hv, b, &kw_bar);
+  };
+  auto load_q = [&](int c) {
+    mbar_arrive_expect_tx(&q_bar, 16384);
+    tma_load_tile4(sb + bhOffQ, &tm_q, 0, tbeg + c * kC, hk, b, &q_bar);
+    tma_load_tile4(sb + bhOffQ + 8192, &tm_q, 64, tbeg + c * kC, hk, b, &q_bar);
+  };
+  auto load_d = [&](int c) {   // the dO and dv blocks of this CTA's value columns
+    mbar_arrive_expect_tx(&d_bar, 16384);
+    tma_load_tile4(sb + bhOffDo, &tm_do, vb * 64, tbeg + c * kC, hv, b, &d_bar);
+    tma_load_tile4(sb + bhOffDv, &tm_dv, vb * 64, tbeg + c * kC, hv, b, &d_bar);
+  };
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init(&kw_bar, 1);
+    mbar_init(&q_bar, 1);
+    mbar_init(&d_bar, 1);
+    mbar_init_fence();
+    if (sq.nt > 0) {
+      load_k(sq.nt - 1);
+      load_q(sq.nt - 1);
+      load_d(sq.nt - 1);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  // k as A (rows = tokens): rows 64..127 of the M = 128 tile read the memory behind each panel and are never used
+  const Operand opK{sb + bhOffKW, 8192, 0}, opWt{sb + bhOffKW, 8192, 1}, opQt{sb + bhOffQ, 8192, 1}, opS{sb + bhOffS, 16384, 1},
+      opSl{sb + bhOffSl, 16384, 1}, opDo{sb + bhOffDo, 8192, 1}, opDol{sb + bhOffDol, 8192, 1}, opDv{sb + bhOffDv, 8192, 1},
+      opDvl{sb + bhOffDvl, 8192, 1};
+  {
+    float s[64];
+    if (p.h0.p) {   // the cotangent of the final state
+      const float* src = static_cast<const float*>(p.h0.p) + (int64_t(n) * p.H + hv) * kK * kV + tid * kV + vb * 64;
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(src + i);
+        s[i] = t.x; s[i + 1] = t.y; s[i + 2] = t.z; s[i + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) s[i] = 0.f;
+    }
+    tmem_st_row64(trow, s);
+  }
+  auto load_gate = [&](int c) -> float {
+    if (tid >= kC || c < 0) return 0.f;
+    const int rows_c = min(kC, sq.len - c * kC);
+    return ld_any(p.g.p, row_off(p.g, b, hv, tbeg + c * kC + min(tid, rows_c - 1)), p.g.dtype);
+  };
+  float pf_g = load_gate(sq.nt - 1);
+  uint32_t mphase = 0, kwphase = 0, lphase = 0;
+  bool ok = true;
+  for (int c = sq.nt - 1; c >= 0; --c) {
+    const int rows = min(kC, sq.len - c * kC);
+    const int t0 = tbeg + c * kC;
+    if (tid < kC) gam_s[tid] = pf_g;
+    pf_g = load_gate(c - 1);
+    __syncthreads();
+    const float g_last = gam_s[rows - 1];
+    {
+      float s[64];
+      tmem_ld_row64(trow, s);
+      row64_to_hilo(smem + bhOffS, smem + bhOffSl, tid, s);
+      bf16* hd = static_cast<bf16*>(const_cast<void*>(p.o0.p)) +
+                 ((int64_t(b) * p.H + hv) * p.o0.sh + (p.cu_seqlens ? sq.cbase : 0) + c) * int64_t(kK * kV) + tid * kV + vb * 64;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(hd + ch * 8) = pack8(s + ch * 8);
+      const float el = __expf(g_last);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) s[i] *= el;
+      tmem_st_row64(trow, s);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      ok = mbar_wait(&kw_bar, kwphase, p.status, FLA_ERR_TIMEOUT);
+      tc_fence_after();
+      mma_tile(tbase + 64, opK, opS, 128, 64, 8, false);
+      mma_tile(tbase + 64, opK, opSl, 128, 64, 8, true);
+      mma_commit(&mma_bar);
+    }
+    kwphase ^= 1;
+    float dov[64], dvv[64];
+    if (warp < 2) {
+      ok = mbar_wait(&d_bar, lphase, p.status, FLA_ERR_TIMEOUT) && ok;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + bhOffDo + panel_chunk_off(tid, ch)), dov + ch * 8);
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + bhOffDv + panel_chunk_off(tid, ch)), dvv + ch * 8);
+      }
+    }
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT) && ok;
+    mphase ^= 1;
+    tc_fence_after();
+    if (!__syncthreads_and(ok)) { ok = false; break; }
+    if (tid == 0) load_w(c);   // k is consumed: its buffer takes this chunk's w
+    if (warp < 2) {
+      float d1[64];
+      tmem_ld_row64(trow + 64, d1);
+      const bool live = tid < rows;     // rows past the end of the sequence (foreign or zero tile rows) carry nothing
+      const float gi = gam_s[tid];
+      const float dec = __expf(g_last - gi), qs = live ? p.scale * __expf(gi) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        d1[i] = live ? dvv[i] + dec * d1[i] : 0.f;
+        dov[i] *= qs;
+      }
+      if (live) {
+        bf16* vd = static_cast<bf16*>(const_cast<void*>(p.o1.p)) + row_off(p.o1, b, hv, t0 + tid) + vb * 64;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vd + ch * 8) = pack8(d1 + ch * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < 64; ++i) d1[i] = -d1[i];
+      row64_to_hilo(smem + bhOffDo, smem + bhOffDol, tid, dov);   // in place over the raw tiles
+      row64_to_hilo(smem + bhOffDv, smem + bhOffDvl, tid, d1);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      ok = mbar_wait(&q_bar, lphase, p.status, FLA_ERR_TIMEOUT);
+      ok = mbar_wait(&kw_bar, kwphase, p.status, FLA_ERR_TIMEOUT) && ok;
+      tc_fence_after();
+      mma_tile(tbase, opQt, opDo, 128, 64, 4, true);
+      mma_tile(tbase, opQt, opDol, 128, 64, 4, true);
+      mma_tile(tbase, opWt, opDv, 128, 64, 4, true);
+      mma_tile(tbase, opWt, opDvl, 128, 64, 4, true);
+      mma_commit(&mma_bar);
+    }
+    kwphase ^= 1;
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT) && ok;
+    mphase ^= 1;
+    lphase ^= 1;
+    tc_fence_after();
+    if (!__syncthreads_and(ok)) { ok = false; break; }
+    if (tid == 0 && c > 0) {
+      load_k(c - 1);
+      load_q(c - 1);
+      load_d(c - 1);
+    }
+  }
+  if (ok && p.want_final) {
+    float s[64];
+    tmem_ld_row64(trow, s);
+    float* dst = static_cast<float*>(const_cast<void*>(p.o2.p)) + (int64_t(n) * p.H + hv) * kK * kV + tid * kV + vb * 64;
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(s[i], s[i + 1], s[i + 2], s[i + 3]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 128);
+}
+
 }  // namespace fla
 
 using namespace fla;
@@ -757,6 +1047,8 @@ FLA_STAGE_WORKSPACE(solve_tri)
 FLA_STAGE_WORKSPACE(recompute_w_u_fwd)
 FLA_STAGE_WORKSPACE(chunk_gated_delta_rule_fwd_h)
 FLA_STAGE_WORKSPACE(chunk_fwd_o)
+FLA_STAGE_WORKSPACE(chunk_bwd_dv_local)
+FLA_STAGE_WORKSPACE(chunk_gated_delta_rule_bwd_dhu)
 
 extern "C" FLA_API int fla_b200_chunk_local_cumsum(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes,
                                                    void* stream) {
@@ -934,5 +1226,90 @@ extern "C" FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* a, void*
     return FLA_ERR_CUDA;
   KernelTimer kt("chunk_fwd_o", cs);
   stage_fwd_o_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kFwdOSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_h);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_chunk_bwd_dv_local(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes,
+                                                   void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  const fla_tensor_t& d_o = a->v;
+  if (d_o.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, d_o, &gm, &p))) return st;
+  StageView vq, vk, vdo;
+  if ((st = make_view(a->q, 4, true, &vq)) || (st = make_view(a->k, 4, true, &vk)) || (st = make_view(d_o, 4, true, &vdo)) ||
+      (st = make_view(a->g, 3, false, &p.g)) || (st = make_view(a->out0, 4, true, &p.o0)))
+    return st;
+  const int64_t HK = a->k.shape[1];
+  for (const fla_tensor_t* t : {&a->q, &a->k, &d_o, &a->out0})
+    if (t->dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->k.shape[0] != gm.B || a->k.shape[2] != gm.T || a->k.shape[3] != kK || d_o.shape[3] != kV) return FLA_ERR_SHAPE;
+  if (a->q.shape[0] != gm.B || a->q.shape[1] != HK || a->q.shape[2] != gm.T || a->q.shape[3] != kK) return FLA_ERR_SHAPE;
+  if (!same_bht(a->g, gm, gm.H) || !same_bht(a->out0, gm, gm.H) || a->out0.shape[3] != kV) return FLA_ERR_SHAPE;
+  p.HK = int(HK);
+  p.scale = a->scale;
+  if (!(a->scale == a->scale)) return FLA_ERR_VALUE;
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if ((st = opt_in_smem(stage_dv_local_kernel, kDvLocalSmem + 1024))) return st;
+  CUtensorMap tm_q, tm_k, tm_do;
+  if (token_tile_map(a->q, &tm_q) || token_tile_map(a->k, &tm_k) || token_tile_map(d_o, &tm_do)) return FLA_ERR_CUDA;
+  KernelTimer kt("chunk_bwd_dv_local", cs);
+  stage_dv_local_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kDvLocalSmem + 1024, cs>>>(p, tm_q, tm_k, tm_do);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu(const fla_chunk_stage_args* a, void* workspace,
+                                                               uint64_t workspace_bytes, void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  const fla_tensor_t &d_o = a->u, &dv = a->v;
+  if (dv.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, dv, &gm, &p))) return st;
+  StageView tmp;
+  if ((st = make_view(a->q, 4, true, &tmp)) || (st = make_view(a->k, 4, true, &tmp)) || (st = make_view(a->w, 4, true, &tmp)) ||
+      (st = make_view(d_o, 4, true, &tmp)) || (st = make_view(dv, 4, true, &tmp)) || (st = make_view(a->g, 3, false, &p.g)) ||
+      (st = make_view(a->out1, 4, true, &p.o1)))
+    return st;
+  const int64_t HK = a->k.shape[1];
+  for (const fla_tensor_t* t : {&a->q, &a->k, &a->w, &d_o, &dv, &a->out0, &a->out1})
+    if (t->dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->k.shape[0] != gm.B || a->k.shape[2] != gm.T || a->k.shape[3] != kK || dv.shape[3] != kV) return FLA_ERR_SHAPE;
+  if (a->q.shape[0] != gm.B || a->q.shape[1] != HK || a->q.shape[2] != gm.T || a->q.shape[3] != kK) return FLA_ERR_SHAPE;
+  if (!same_bht(a->w, gm, gm.H) || a->w.shape[3] != kK || !same_bht(d_o, gm, gm.H) || d_o.shape[3] != kV) return FLA_ERR_SHAPE;
+  if (!same_bht(a->g, gm, gm.H) || !same_bht(a->out1, gm, gm.H) || a->out1.shape[3] != kV) return FLA_ERR_SHAPE;
+  const fla_tensor_t& h = a->out0;
+  const int64_t NT = gm.total_chunks / gm.B;
+  if (!h.data) return FLA_ERR_NULL;
+  if (h.ndim != 5 || h.shape[0] != gm.B || h.shape[1] != gm.H || h.shape[2] != NT || h.shape[3] != kK || h.shape[4] != kV) return FLA_ERR_SHAPE;
+  if (h.stride[4] != 1 || h.stride[3] != kV || h.stride[2] != kK * kV || h.stride[1] != NT * kK * kV || !aligned16(h.data)) return FLA_ERR_LAYOUT;
+  p.o0.p = h.data;
+  p.o0.sh = NT;
+  for (const fla_tensor_t* s : {&a->initial_state, &a->out2}) {
+    if (!s->data) continue;
+    if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
+    if (s->ndim != 4 || s->shape[0] != gm.N || s->shape[1] != gm.H || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != gm.H * kK * kV || !aligned16(s->data))
+      return FLA_ERR_LAYOUT;
+  }
+  p.h0.p = a->initial_state.data;   // dht
+  p.o2.p = a->out2.data;            // dh0
+  p.want_final = a->out2.data != nullptr;
+  p.HK = int(HK);
+  p.scale = a->scale;
+  if (!(a->scale == a->scale)) return FLA_ERR_VALUE;
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if ((st = opt_in_smem(stage_bwd_dhu_kernel, kBwdDhuSmem + 1024))) return st;
+  CUtensorMap tm_q, tm_k, tm_w, tm_do, tm_dv;
+  if (token_tile_map(a->q, &tm_q) || token_tile_map(a->k, &tm_k) || token_tile_map(a->w, &tm_w) || token_tile_map(d_o, &tm_do) ||
+      token_tile_map(dv, &tm_dv))
+    return FLA_ERR_CUDA;
+  KernelTimer kt("chunk_bwd_dhu", cs);
+  stage_bwd_dhu_kernel<<<dim3(kV / 64, unsigned(gm.H), gm.N), 128, kBwdDhuSmem + 1024, cs>>>(p, tm_q, tm_k, tm_w, tm_do, tm_dv);
   return cuda_status(cudaGetLastError());
 }

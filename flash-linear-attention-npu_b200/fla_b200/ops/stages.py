@@ -160,6 +160,50 @@ def chunk_fwd_o(q, k, v, h, scale, *, g=None, g_gamma=None, cu_seqlens=None, chu
     return o
 
 
+def chunk_bwd_dv_local(q, k, d_o, g, scale, chunk_size, *, g_gamma=None, A=None, cu_seqlens=None, chunk_indices=None):
+    """Intra-chunk part of dv: `dv_j = sum_{i >= j} scale (k_j.q_i) e^{g_i - g_j} d_o_i`.  q, k `[B,HK,T,K]`, d_o `[B,HV,T,V]`,
+    g `[B,HV,T]` (chunk-local cumulative gate)."""
+    del g_gamma, A, chunk_indices
+    dv = torch.empty_like(d_o)
+    _stage_call("chunk_bwd_dv_local", dict(q=q, k=k, v=d_o, g=g, out0=dv), [q, k, d_o, g, dv], d_o, cu_seqlens, chunk_size, scale=scale)
+    return dv
+
+
+def chunk_gated_delta_rule_bwd_dhu(q, k, w, d_o, dv, scale, chunk_size, *, g=None, gK=None, h0=None, dht=None, cu_seqlens=None,
+                                   chunk_indices=None, use_exp2=False, transpose_state_layout=False):
+    """Reverse state pass of the backward: `dh_c = dS`, `dv2 = dv + e^{g_last - g} (k dS)`,
+    `dS <- e^{g_last} dS + q^T (scale e^g d_o) - w^T dv2`.  Returns (dh `[B,HV,NT,K,V]`, dh0, dv2).
+    dh0 is returned when `h0` is given, as fp32 `[N,HV,K,V]` (the reference allocates `[B,HV,NT,K,V]` and fills chunk 0);
+    `dht` `[N,HV,K,V]` seeds dS (the reference accepts the argument and ignores it)."""
+    del chunk_indices
+    if gK is not None or g is None:
+        raise NotImplementedError("chunk_gated_delta_rule_bwd_dhu: scalar gates (g) only; gK belongs to the fused KDA operator")
+    if use_exp2 or transpose_state_layout:
+        raise NotImplementedError("chunk_gated_delta_rule_bwd_dhu: use_exp2 / transpose_state_layout are not supported")
+    if any(t.dtype != q.dtype for t in (k, w, d_o, dv)):
+        raise ValueError("q, k, w, d_o and dv must have the same dtype.")
+    B, HV, T, V = dv.shape
+    K = q.shape[3]
+    N = _num_sequences(B, cu_seqlens)
+    if cu_seqlens is None:
+        NT = (T + CHUNK - 1) // CHUNK
+    else:
+        cu_host = [int(x) for x in (cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens)]
+        NT = sum((b - a + CHUNK - 1) // CHUNK for a, b in zip(cu_host, cu_host[1:]))
+    if dht is not None:
+        if tuple(dht.shape) != (N, HV, K, V):
+            raise RuntimeError(f"chunk_gated_delta_rule_bwd_dhu: dht must be {(N, HV, K, V)}, got {tuple(dht.shape)}")
+        dht = dht.float().contiguous()
+    dh = torch.empty((B, HV, NT, K, V), dtype=q.dtype, device=q.device)
+    dv2 = torch.empty_like(dv)
+    dh0 = torch.empty((N, HV, K, V), dtype=torch.float32, device=q.device) if h0 is not None else None
+    _stage_call("chunk_gated_delta_rule_bwd_dhu", dict(q=q, k=k, w=w, u=d_o, v=dv, g=g, initial_state=dht, out0=dh, out1=dv2, out2=dh0),
+                [q, k, w, d_o, dv, g, dht, dh, dv2, dh0], dv, cu_seqlens, chunk_size, scale=scale)
+    return dh, dh0, dv2
+
+
+npu_chunk_bwd_dv_local = chunk_bwd_dv_local
+npu_chunk_gated_delta_rule_bwd_dhu = chunk_gated_delta_rule_bwd_dhu
 npu_chunk_local_cumsum = chunk_local_cumsum
 npu_chunk_scaled_dot_kkt = chunk_scaled_dot_kkt
 npu_solve_tri = solve_tri

@@ -352,6 +352,18 @@ FLA_API int fla_b200_l2norm_bwd(const fla_l2norm_args* args, void* stream);
  * fla_b200_chunk_fwd_o          (aclnnChunkFwdO, :517-549; golden chunk_fwd_o/tests/pta/test_fwd_o.py:52-128)
  *     q, k [B,HK,T,128], v (= v_new) [B,HV,T,128], h [B,HV,NT,128,128] bf16, g [B,HV,T]
  *     -> out0 = o [B,HV,T,128] bf16:  o = scale (e^{g_i} q h_c + tril(q k^T e^{g_i - g_j}) v).
+ * Two stages of the backward chain use the same block:
+ * fla_b200_chunk_bwd_dv_local   (aclnnChunkBwdDvLocal, :397-427; golden
+ *     fla/ops/ascendc/gdn/chunk_gdn_bwd/chunk_bwd_dv_local/tests/ATK/executor_chunk_bwd_dv_local.py:57-130)
+ *     q, k [B,HK,T,128], v = d_o [B,HV,T,128] bf16, g [B,HV,T], scale
+ *     -> out0 = dv [B,HV,T,128] bf16:  dv_j = sum_{i >= j in chunk} scale (k_j.q_i) e^{g_i - g_j} d_o_i.
+ * fla_b200_chunk_gated_delta_rule_bwd_dhu (aclnnChunkGatedDeltaRuleBwdDhu, :324-394; golden
+ *     torch_custom/fla_npu/test/test_bwd_dhu.py:61-290)
+ *     q, k [B,HK,T,128], w [B,HV,T,128], u = d_o, v = dv [B,HV,T,128] bf16, g [B,HV,T], scale,
+ *     initial_state = dht [N,HV,128,128] f32 (optional cotangent of the final state; the reference ignores it)
+ *     -> out0 = dh [B,HV,NT,128,128] bf16 dense (gradient of the state at the END of every chunk), out1 = dv2 bf16,
+ *        out2 = dh0 [N,HV,128,128] f32 (optional).  Reverse over chunks: dh_c = dS; dv2 = dv + e^{g_last - g} (k dS);
+ *        dS <- e^{g_last} dS + q^T (scale e^g d_o) - w^T dv2.
  * Workspace: 256 bytes (status word of the bounded device-side waits). */
 typedef struct fla_chunk_stage_args {
   fla_tensor_t q, k, v, w, u, g, beta, A, h, initial_state;
@@ -376,6 +388,11 @@ FLA_API int fla_b200_recompute_w_u_fwd(const fla_chunk_stage_args* args, void* w
 FLA_API int fla_b200_chunk_gated_delta_rule_fwd_h(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes,
                                                   void* stream);
 FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_chunk_bwd_dv_local_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_bwd_dv_local(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes,
+                                                    void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,6 +8,9 @@ CPU restatements of the reference's per-operator goldens, on head-first `[B,H,T,
   fwd_h                 tests/atk/chunk_gated_delta_rule_fwd_h/executor_chunk_gated_delta_rule_fwd_h.py:75-126
                         ("fp64" mode), extended with an initial state and the final state the reference omits
   fwd_o                 fla/ops/ascendc/gdn/chunk_gdn_fwd/chunk_fwd_o/tests/pta/test_fwd_o.py:42-117
+  dv_local              fla/ops/ascendc/gdn/chunk_gdn_bwd/chunk_bwd_dv_local/tests/ATK/executor_chunk_bwd_dv_local.py:57-130
+  bwd_dhu               torch_custom/fla_npu/test/test_bwd_dhu.py:61-290 ("fp64" mode), extended with the cotangent of the
+                        final state (the reference deletes `dht`) and a `[N,HV,K,V]` dh0
 Pinned by tests/golden/stages_golden.npz, which tests/golden/make_golden.py produces by running those reference
 functions themselves.
 """
@@ -136,3 +139,55 @@ def chunk_fwd_o_ref(q, k, v, h, g, scale, chunk_size, cu_seqlens=None):
         inter = (qq[:, :, s:e] * torch.exp(g[:, :, s:e])[..., None]) @ h[:, :, ci]
         o[:, :, s:e] = (inter + attn @ v[:, :, s:e]) * scale
     return o
+
+
+def chunk_bwd_dv_local_ref(q, k, d_o, g, scale, chunk_size, cu_seqlens=None):
+    """dv_j = sum_{i >= j in chunk} scale (k_j.q_i) e^{g_i - g_j} d_o_i, fp64."""
+    B, HV, T, V = d_o.shape
+    HK = k.shape[1]
+    qq = q.double().repeat_interleave(HV // HK, dim=1)
+    kk = k.double().repeat_interleave(HV // HK, dim=1)
+    d_o, g = d_o.double(), g.double()
+    dv = torch.zeros(B, HV, T, V, dtype=torch.float64)
+    for s, e in chunk_ranges(T, chunk_size, cu_seqlens):
+        A = kk[:, :, s:e] @ qq[:, :, s:e].transpose(-1, -2) * scale            # [j, i]
+        A = torch.triu(A * torch.exp(g[:, :, None, s:e] - g[:, :, s:e, None]))  # i >= j
+        dv[:, :, s:e] = A @ d_o[:, :, s:e]
+    return dv
+
+
+def chunk_bwd_dhu_ref(q, k, w, d_o, dv, g, scale, chunk_size, dht=None, cu_seqlens=None):
+    """Reverse state pass in fp64.  Returns (dh [B,HV,NT,K,V] = dS at the end of every chunk, dh0 [N,HV,K,V], dv2)."""
+    B, HV, T, V = dv.shape
+    HK, K = k.shape[1], k.shape[3]
+    qq = q.double().repeat_interleave(HV // HK, dim=1)
+    kk = k.double().repeat_interleave(HV // HK, dim=1)
+    w, d_o, dv, g = w.double(), d_o.double(), dv.double(), g.double()
+    seqs = sequence_chunk_ranges(T, chunk_size, cu_seqlens)
+    nt_total = sum(len(s) for s in seqs)
+    packed = cu_seqlens is not None
+    N = len(seqs) if packed else B
+    dh = torch.zeros(B, HV, nt_total, K, V, dtype=torch.float64)
+    dv2 = torch.zeros(B, HV, T, V, dtype=torch.float64)
+    dh0 = torch.zeros(N, HV, K, V, dtype=torch.float64)
+    base = 0
+    for si, chunks in enumerate(seqs):
+        rows = [0] if packed else list(range(B))
+        dS = torch.zeros(len(rows), HV, K, V, dtype=torch.float64)
+        if dht is not None:
+            dS = dht.double()[[si] if packed else rows].clone()
+        for ci in range(len(chunks) - 1, -1, -1):
+            s, e = chunks[ci]
+            dh[rows, :, base + ci] = dS
+            gl = g[rows, :, e - 1]
+            cur = dv[rows, :, s:e] + torch.exp(gl[..., None] - g[rows, :, s:e])[..., None] * (kk[rows, :, s:e] @ dS)
+            dv2[rows, :, s:e] = cur
+            qg = qq[rows, :, s:e] * torch.exp(g[rows, :, s:e])[..., None]
+            dS = dS * torch.exp(gl)[..., None, None] + scale * qg.transpose(-1, -2) @ d_o[rows, :, s:e] \
+                - w[rows, :, s:e].transpose(-1, -2) @ cur
+        if packed:
+            dh0[si] = dS[0]
+        else:
+            dh0[:] = dS
+        base += len(chunks)
+    return dh, dh0, dv2

@@ -14,7 +14,7 @@ import math
 import os
 import sys
 from pathlib import Path
-from typing import Any, Iterable, Optional, Tuple  # noqa: F401  (used by exec'd reference code)
+from typing import Any, Iterable, List, Optional, Tuple  # noqa: F401  (used by exec'd reference code)
 
 import numpy as np
 import torch
@@ -28,7 +28,7 @@ sys.path.insert(0, str(HERE.parent.parent))
 def extract(path: Path, names, extra=None):
     src = path.read_text()
     tree = ast.parse(src)
-    ns = {"torch": torch, "F": F, "math": math, "np": np, "Optional": Optional, "Tuple": Tuple, "Iterable": Iterable, "Any": Any}
+    ns = {"torch": torch, "F": F, "math": math, "np": np, "Optional": Optional, "Tuple": Tuple, "Iterable": Iterable, "Any": Any, "List": List}
     if extra:
         ns.update(extra)
     for node in tree.body:
@@ -164,6 +164,11 @@ def stages_fixture():
                     extra={"_chunks": common["_chunks"], "_num_chunks": common["_num_chunks"]})["_forward_h_ref"]
     o_ns = extract(REF / "fla/ops/ascendc/gdn/chunk_gdn_fwd/chunk_fwd_o/tests/pta/test_fwd_o.py",
                    ["cdiv_torch", "prepare_chunk_indices", "prepare_lens", "prepare_chunk_offsets", "forward_o_trans_cpu"])
+    dv_ns = extract(REF / "fla/ops/ascendc/gdn/chunk_gdn_bwd/chunk_bwd_dv_local/tests/ATK/executor_chunk_bwd_dv_local.py",
+                    ["prepare_lens", "cdiv", "prepare_chunk_indices", "chunk_bwd_dv_local_torch"])
+    dhu_ref = extract(test_dir / "test_bwd_dhu.py", ["_round_elem", "_matmul_npu_aligned", "_gate_exp2", "_gate_exp",
+                                                      "chunk_gated_delta_rule_bwd_dhu_cpu"],
+                      extra={"_LN2": math.log(2.0)})["chunk_gated_delta_rule_bwd_dhu_cpu"]
     torch.Tensor.npu = lambda self: self   # the golden moves its CPU tensors "to the device" before computing
 
     C, K, V, HK, HV, T = 64, 128, 128, 1, 2, 160
@@ -175,7 +180,8 @@ def stages_fixture():
     v = bf(rnd(1, HV, T, V))
     g_raw = F.logsigmoid(rnd(1, HV, T))
     beta = bf(torch.sigmoid(rnd(1, HV, T)))
-    out = dict(q=f32(q), k=f32(k), v=f32(v), g_raw=f32(g_raw), beta=f32(beta))
+    d_o = bf(rnd(1, HV, T, V))
+    out = dict(q=f32(q), k=f32(k), v=f32(v), g_raw=f32(g_raw), beta=f32(beta), d_o=f32(d_o))
     for tag, cu in (("fix", None), ("var", [0, 70, 160])):
         cu_t = None if cu is None else torch.tensor(cu)
         gam = cumsum_ref(g_raw, C, False, 1.0, cu_t, torch.float32)
@@ -204,6 +210,16 @@ def stages_fixture():
             v_new = torch.cat([p_[1] for p_ in parts], dim=2).float()
         hb, vnb = bf(h), bf(v_new)
         o = o_ns["forward_o_trans_cpu"](q, k, vnb, hb, gam, None, K ** -0.5, C, cu_t, None)
+        # backward stages: intra-chunk dv, then the reverse state pass (the goldens take cu_seqlens as tensor / list)
+        cu_b = cu if cu is not None else [0, T]
+        dv_loc = dv_ns["chunk_bwd_dv_local_torch"](q, k, d_o, gam, K ** -0.5, torch.tensor(cu_b), C, HV // HK)
+        dvb = bf(dv_loc)
+        idx_b = idx if idx is not None else [x for ci in range(NT) for x in (0, ci)]
+        dh, dh0, dv2 = dhu_ref(q, k, wb, d_o, dvb, cu_seqlens=cu_b, chunk_indices=idx_b, g=gam, h0=torch.zeros(1), scale=K ** -0.5,
+                               chunk_size=C, golden_mode="fp64")
+        first = [i for i in range(NT) if idx_b[2 * i + 1] == 0]
+        out.update({f"{tag}_dv_local": f32(dv_loc), f"{tag}_dh": f32(dh), f"{tag}_dh0": f32(dh0[0, :, first].transpose(0, 1)),
+                    f"{tag}_dv2": f32(dv2)})
         out.update({f"{tag}_gam": f32(gam), f"{tag}_rev": f32(rev), f"{tag}_A": f32(A), f"{tag}_X": f32(X), f"{tag}_w": f32(w),
                     f"{tag}_u": f32(u), f"{tag}_h": f32(h), f"{tag}_v_new": f32(v_new), f"{tag}_o": f32(o)})
     del torch.Tensor.npu

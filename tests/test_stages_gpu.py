@@ -42,6 +42,11 @@ def _case(B, T, HK, HV, seed, cu=None):
     wb, ub = _bf(d["w"]), _bf(d["u"])
     d["h"], d["v_new"], d["ht"] = stages.chunk_fwd_h_ref(k, wb, ub, d["gam"], C, initial_state=h0, cu_seqlens=cu)
     d["o"] = stages.chunk_fwd_o_ref(q, k, _bf(d["v_new"]), _bf(d["h"]), d["gam"], 128 ** -0.5, C, cu)
+    d["d_o"] = hf(inp["do"])
+    d["dht"] = 0.1 * torch.randn(N, HV, 128, 128, generator=torch.Generator().manual_seed(seed + 2))
+    d["dv_local"] = stages.chunk_bwd_dv_local_ref(q, k, d["d_o"], d["gam"], 128 ** -0.5, C, cu)
+    d["dh"], d["dh0"], d["dv2"] = stages.chunk_bwd_dhu_ref(q, k, wb, d["d_o"], _bf(d["dv_local"]), d["gam"], 128 ** -0.5, C, dht=d["dht"],
+                                                           cu_seqlens=cu)
     return d
 
 
@@ -129,6 +134,28 @@ def test_chunk_fwd_o(case):
     assert_close("o", o, d["o"], TOL, stored_bf16=True)
 
 
+def test_chunk_bwd_dv_local(case):
+    from fla_b200.ops import chunk_bwd_dv_local
+    d, cu = case
+    dv = chunk_bwd_dv_local(d["q"].cuda(), d["k"].cuda(), d["d_o"].cuda(), d["gam"].cuda(), 128 ** -0.5, C, cu_seqlens=cu)
+    assert_close("dv_local", dv, d["dv_local"], TOL, stored_bf16=True)
+
+
+def test_chunk_bwd_dhu(case):
+    from fla_b200.ops import chunk_gated_delta_rule_bwd_dhu
+    d, cu = case
+    args = (d["q"].cuda(), d["k"].cuda(), _bf(d["w"]).cuda(), d["d_o"].cuda(), _bf(d["dv_local"]).cuda(), 128 ** -0.5, C)
+    dh, dh0, dv2 = chunk_gated_delta_rule_bwd_dhu(*args, g=d["gam"].cuda(), h0=d["h0"].cuda(), dht=d["dht"].cuda(), cu_seqlens=cu)
+    assert_close("dh", dh, d["dh"], TOL, stored_bf16=True)
+    assert_close("dv2", dv2, d["dv2"], TOL, stored_bf16=True)
+    assert_close("dh0", dh0, d["dh0"], TOL)
+    dh_b, none, _ = chunk_gated_delta_rule_bwd_dhu(*args, g=d["gam"].cuda(), cu_seqlens=cu)
+    assert none is None
+    last = -1 if cu is None else None
+    if last is not None:
+        assert (dh_b[:, :, last] == 0).all()     # without dht the gradient of the last chunk's end state is zero
+
+
 def test_stage_chain_matches_fused_operator():
     """Running the six stages one after the other gives the fused operator's output (and the oracle's)."""
     from fla_b200 import ops
@@ -174,3 +201,12 @@ def test_stage_goldens_from_the_reference():
         o = ops.chunk_fwd_o(q, k, fx[f"{tag}_v_new"].bfloat16().cuda(), fx[f"{tag}_h"].bfloat16().cuda(), 128 ** -0.5, g=gam, cu_seqlens=cu)
         # this golden is itself rounded to bf16 and, in its fixed-length branch, rounds the gate to fp16 before the exponential
         assert_close("o", o, fx[f"{tag}_o"], 2e-2, stored_bf16=True)
+        d_o = fx["d_o"].bfloat16().cuda()
+        dv = ops.chunk_bwd_dv_local(q, k, d_o, gam, 128 ** -0.5, C, cu_seqlens=cu)
+        assert_close("dv_local", dv, fx[f"{tag}_dv_local"], TOL, stored_bf16=True)
+        N = 1 if cu is None else len(cu) - 1
+        dh, dh0, dv2 = ops.chunk_gated_delta_rule_bwd_dhu(q, k, fx[f"{tag}_w"].bfloat16().cuda(), d_o, fx[f"{tag}_dv_local"].bfloat16().cuda(),
+                                                          128 ** -0.5, C, g=gam, h0=torch.zeros(N, 2, 128, 128).cuda(), cu_seqlens=cu)
+        assert_close("dh", dh, fx[f"{tag}_dh"], TOL, stored_bf16=True)
+        assert_close("dh0", dh0, fx[f"{tag}_dh0"], TOL)
+        assert_close("dv2", dv2, fx[f"{tag}_dv2"], TOL, stored_bf16=True)

@@ -41,6 +41,13 @@ def test_stage_oracle_matches_reference_goldens(fx, tag, cu):
     _close(v_new, fx[f"{tag}_v_new"], 2e-6)
     o = stages.chunk_fwd_o_ref(fx["q"], fx["k"], bf(fx[f"{tag}_v_new"]), bf(fx[f"{tag}_h"]), gam, 128 ** -0.5, C, cu)
     _close(o, fx[f"{tag}_o"], 2.0 ** -8)   # the reference golden returns bf16
+    scale = 128 ** -0.5
+    _close(stages.chunk_bwd_dv_local_ref(fx["q"], fx["k"], fx["d_o"], gam, scale, C, cu), fx[f"{tag}_dv_local"], 2e-6)
+    dh, dh0, dv2 = stages.chunk_bwd_dhu_ref(fx["q"], fx["k"], bf(fx[f"{tag}_w"]), fx["d_o"], bf(fx[f"{tag}_dv_local"]), gam, scale, C,
+                                            cu_seqlens=cu)
+    _close(dh, fx[f"{tag}_dh"], 2e-6)
+    _close(dh0, fx[f"{tag}_dh0"], 2e-6)
+    _close(dv2, fx[f"{tag}_dv2"], 2e-6)
 
 
 def test_stage_chain_reproduces_the_recurrence():
