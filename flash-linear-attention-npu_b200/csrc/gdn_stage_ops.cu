@@ -30,11 +30,17 @@ struct StageView {     // [B, H, T, D] view, D contiguous
 
 struct StageParams {
   StageView q, k, v, w, u, g, beta, a, h, h0;
-  StageView o0, o1, o2;
+  StageView o0, o1, o2, o3;
+  float* ws_dq;   // dqkwg with GVA: per-value-head fp32 rows [B*H*T, 128] of dq and dk, reduced over the group afterwards
+  float* ws_dk;
   const int32_t* cu_seqlens;
   const int32_t* chunk_offsets;
   int T, H, HK, D;
   int reverse, want_final;
+  int gate_mode;            // cumsum of per-channel gates: 0 raw, 1 -e^{A_log} softplus(g + dt_bias), 2 lower_bound sigmoid(e^{A_log} (g + dt_bias))
+  const float* a_log;       // [H]
+  const float* dt_bias;     // [H, D] or null
+  float lower_bound;
   float scale;
   int* status;
 };
@@ -82,9 +88,18 @@ __global__ void __launch_bounds__(128) stage_cumsum_kernel(StageParams p) {
   } else {
     for (int d = tid; d < p.D; d += blockDim.x) {
       float run = 0.f;
+      const float eig = p.gate_mode ? __expf(p.a_log[hh]) : 0.f;
+      const float bias = (p.gate_mode && p.dt_bias) ? p.dt_bias[hh * p.D + d] : 0.f;
       for (int i = 0; i < rows; ++i) {
         const int t = p.reverse ? rows - 1 - i : i;
-        run += ld_any(p.g.p, row_off(p.g, b, hh, t0 + t) + d, p.g.dtype);
+        float x = ld_any(p.g.p, row_off(p.g, b, hh, t0 + t) + d, p.g.dtype);
+        if (p.gate_mode == 1) {
+          const float r = x + bias;
+          x = -eig * (r > 20.f ? r : log1pf(__expf(r)));
+        } else if (p.gate_mode == 2) {
+          x = p.lower_bound / (1.f + __expf(-eig * (x + bias)));
+        }
+        run += x;
         st_any(const_cast<void*>(p.o0.p), row_off(p.o0, b, hh, t0 + t) + d, p.o0.dtype, run * p.scale);
       }
     }
@@ -957,6 +972,245 @@ __global__ void __launch_bounds__(128) stage_bwd_dhu_kernel(StageParams p, const
   if (warp == 0) tmem_dealloc(tbase, 128);
 }
 
+// ----------------------------------------------------------------------------- chunk_bwd_dqkwg
+// Per chunk and value head (v = v_new, dv = dv2 of the reverse state pass, h / dh = state and its gradient at the chunk):
+//   dq = scale e^{g_i} (dO h^T) + ds k,   dk = e^{g_last - g_i} (v dh^T) + ds^T q,   dw = -(dv h^T),
+//   ds = scale tril(dO v^T e^{g_i - g_j}),
+//   dg_i = q_i.dq_state_i - k_i.dk_state_i + sum_j ds2_ij - sum_j ds2_ji  (ds2 = ds * q k^T),
+//   dg_last += e^{g_last} <h, dh> + sum_i k_i.dk_state_i.
+// [dO; dv] are stacked into one 128-row operand so that dO h^T and dv h^T are one product.  dq / dk of a value head
+// go to fp32 scratch rows when several value heads share a q/k head (summed by stage_group_sum_kernel).
+constexpr uint32_t dqOffA = 0, dqOffV = 32768, dqOffQ = 49152, dqOffK = 65536, dqOffH = 81920, dqOffDH = 114688, dqOffDS = 147456,
+                   dqOffDSl = 155648;
+constexpr uint32_t kDqkwgSmem = 172032;   // 8 KB behind the residual panel: rows 64..127 of the M = 128 views of it
+constexpr int kColTile = 65;              // fp32 row stride of the ds2 tile (reuses the h panels)
+__global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                          const __grid_constant__ CUtensorMap tm_k,
+                                                          const __grid_constant__ CUtensorMap tm_v,
+                                                          const __grid_constant__ CUtensorMap tm_do,
+                                                          const __grid_constant__ CUtensorMap tm_dv,
+                                                          const __grid_constant__ CUtensorMap tm_h,
+                                                          const __grid_constant__ CUtensorMap tm_dh) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float gam_s[kC];
+  __shared__ float red_s[8];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int b = p.cu_seqlens ? 0 : n;
+  const int t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int G = p.H / p.HK, hk = hv / G;
+  const uint32_t sb = smem_u32(smem);
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init(&load_bar, 1);
+    mbar_init_fence();
+    mbar_arrive_expect_tx(&load_bar, 147456);
+    const int hrow = int((((int64_t(b) * p.H + hv) * p.h.sh + (p.cu_seqlens ? sq.cbase : 0) + c)) * kK);
+    tma_load_tile4(sb + dqOffH, &tm_h, 0, hrow, 0, 0, &load_bar);
+    tma_load_tile4(sb + dqOffH + 16384, &tm_h, 64, hrow, 0, 0, &load_bar);
+    tma_load_tile4(sb + dqOffDH, &tm_dh, 0, hrow, 0, 0, &load_bar);
+    tma_load_tile4(sb + dqOffDH + 16384, &tm_dh, 64, hrow, 0, 0, &load_bar);
+    tma_load_tile4(sb + dqOffA, &tm_do, 0, t0, hv, b, &load_bar);             // panel 0: dO rows | dv rows
+    tma_load_tile4(sb + dqOffA + 8192, &tm_dv, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + dqOffA + 16384, &tm_do, 64, t0, hv, b, &load_bar);    // panel 1
+    tma_load_tile4(sb + dqOffA + 24576, &tm_dv, 64, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + dqOffV, &tm_v, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + dqOffV + 8192, &tm_v, 64, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + dqOffQ, &tm_q, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + dqOffQ + 8192, &tm_q, 64, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + dqOffK, &tm_k, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + dqOffK + 8192, &tm_k, 64, t0, hk, b, &load_bar);
+  }
+  if (tid < kC) gam_s[tid] = ld_any(p.g.p, row_off(p.g, b, hv, t0 + min(tid, rows - 1)), p.g.dtype);
+  tc_fence_before();
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  constexpr uint32_t cT0 = 0, cT1 = 128, cDs = 256, cQk = 320;
+  const Operand opA{sb + dqOffA, 16384, 0}, opH{sb + dqOffH, 16384, 0}, opDH{sb + dqOffDH, 16384, 0}, opVa{sb + dqOffV, 8192, 0},
+      opQa{sb + dqOffQ, 8192, 0}, opKb{sb + dqOffK, 8192, 0}, opKn{sb + dqOffK, 8192, 1}, opQn{sb + dqOffQ, 8192, 1},
+      opDS{sb + dqOffDS, 8192, 0}, opDSl{sb + dqOffDSl, 8192, 0}, opDSt{sb + dqOffDS, 8192, 1}, opDSlt{sb + dqOffDSl, 8192, 1};
+  bool ok = mbar_wait(&load_bar, 0, p.status, FLA_ERR_TIMEOUT);
+  if (tid == 0) {
+    tc_fence_after();
+    mma_tile(tbase + cT0, opA, opH, 128, 128, 8, false);     // rows 0..63: dO h^T, rows 64..127: dv h^T
+    mma_tile(tbase + cT1, opVa, opDH, 128, 128, 8, false);   // v dh^T
+    mma_tile(tbase + cDs, opA, opVa, 128, 64, 8, false);     // dO v^T
+    mma_tile(tbase + cQk, opQa, opKb, 128, 64, 8, false);    // q k^T
+    mma_commit(&mma_bar);
+  }
+  // <h, dh> while the MMAs run: thread t owns key row t of both tiles
+  float hd = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 16; ++ch) {
+    const uint32_t off = (ch >> 3) * 16384 + panel_chunk_off(tid, ch & 7);
+    float a[8], d[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + dqOffH + off), a);
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + dqOffDH + off), d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) hd += a[j] * d[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, o);
+  if (lane == 0) red_s[warp] = hd;
+  ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT) && ok;
+  tc_fence_after();
+  ok = __syncthreads_and(ok);   // also: every thread is done with the h / dh panels (the ds2 tile reuses them)
+  if (ok) {
+    float* tile = reinterpret_cast<float*>(smem + dqOffH);
+    float dgA = 0.f, dgB = 0.f, dgC = 0.f;
+    const int i = tid & 63;
+    const bool live = i < rows;
+    const float gi = gam_s[i], gl = gam_s[rows - 1];
+    if (warp >= 2) {
+      // dw rows: -(dv h^T)
+      if (p.o2.p) {
+        bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o2.p)) + row_off(p.o2, b, hv, t0 + i);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float r[64];
+          tmem_ld_row64(trow + cT0 + half * 64, r);
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) r[j] = -r[j];
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
+          }
+        }
+      }
+    } else {
+      {
+        float ds[64], qk[64];
+        tmem_ld_row64(trow + cDs, ds);
+        tmem_ld_row64(trow + cQk, qk);
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          ds[j] = (live && j <= i) ? p.scale * ds[j] * __expf(gi - gam_s[j]) : 0.f;
+          const float d2 = ds[j] * qk[j];
+          dgC += d2;
+          tile[i * kColTile + j] = d2;
+        }
+        row64_to_hilo(smem + dqOffDS, smem + dqOffDSl, i, ds);
+      }
+      const float fq = live ? p.scale * __expf(gi) : 0.f, fk = live ? __expf(gl - gi) : 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float r[64];
+        tmem_ld_row64(trow + cT0 + half * 64, r);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float qv[8];
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + dqOffQ + half * 8192 + panel_chunk_off(i, ch)), qv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            r[ch * 8 + j] *= fq;
+            dgA += r[ch * 8 + j] * qv[j];
+          }
+        }
+        tmem_st_row64(trow + cT0 + half * 64, r);
+        tmem_ld_row64(trow + cT1 + half * 64, r);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float kv[8];
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + dqOffK + half * 8192 + panel_chunk_off(i, ch)), kv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            r[ch * 8 + j] *= fk;
+            dgB += r[ch * 8 + j] * kv[j];
+          }
+        }
+        tmem_st_row64(trow + cT1 + half * 64, r);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase + cT0, opDS, opKn, 128, 128, 4, true);      // += ds k
+      mma_tile(tbase + cT0, opDSl, opKn, 128, 128, 4, true);
+      mma_tile(tbase + cT1, opDSt, opQn, 128, 128, 4, true);     // += ds^T q
+      mma_tile(tbase + cT1, opDSlt, opQn, 128, 128, 4, true);
+      mma_commit(&mma_bar);
+    }
+    if (warp < 2) {
+      // dg while the MMAs run: column sums of ds2, the last-row term
+      float col = 0.f;
+#pragma unroll 8
+      for (int r = 0; r < kC; ++r) col += tile[r * kColTile + i];
+      float sB = dgB;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sB += __shfl_xor_sync(0xffffffffu, sB, o);
+      if (lane == 0) red_s[4 + warp] = sB;
+      asm volatile("bar.sync 3, 64;" ::: "memory");
+      float dg = dgA - dgB + dgC - col;
+      if (i == rows - 1) dg += __expf(gl) * (red_s[0] + red_s[1] + red_s[2] + red_s[3]) + red_s[4] + red_s[5];
+      if (live) st_any(const_cast<void*>(p.o3.p), row_off(p.o3, b, hv, t0 + i), p.o3.dtype, dg);
+    }
+    ok = mbar_wait(&mma_bar, 1, p.status, FLA_ERR_TIMEOUT);
+    tc_fence_after();
+    if (warp < 2) {
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const StageView& ov = which ? p.o1 : p.o0;
+        float* wrow = (which ? p.ws_dk : p.ws_dq);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float r[64];
+          tmem_ld_row64(trow + (which ? cT1 : cT0) + half * 64, r);
+          if (ok && live) {
+            if (wrow) {   // per-value-head fp32 rows, summed over the group afterwards
+              float* dst = wrow + ((int64_t(b) * p.H + hv) * p.T + (t0 + i)) * kK + half * 64;
+#pragma unroll
+              for (int j = 0; j < 64; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+              bf16* dst = static_cast<bf16*>(const_cast<void*>(ov.p)) + row_off(ov, b, hk, t0 + i) + half * 64;
+#pragma unroll
+              for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(r + ch * 8);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
+// dq / dk of a q/k head = sum over the value heads of its group of the fp32 scratch rows
+__global__ void __launch_bounds__(256) stage_group_sum_kernel(StageParams p, int B) {
+  const int G = p.H / p.HK;
+  const int64_t total = int64_t(B) * p.HK * p.T * (kK / 4);
+  for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
+    const int c4 = int(idx % (kK / 4));
+    const int64_t t = (idx / (kK / 4)) % p.T;
+    const int64_t hk = (idx / (kK / 4) / p.T) % p.HK, b = idx / (kK / 4) / p.T / p.HK;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const float* src = which ? p.ws_dk : p.ws_dq;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int g = 0; g < G; ++g) {
+        const float4 v = *reinterpret_cast<const float4*>(src + ((b * p.H + hk * G + g) * p.T + t) * kK + c4 * 4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      const StageView& ov = which ? p.o1 : p.o0;
+      bf16* dst = static_cast<bf16*>(const_cast<void*>(ov.p)) + row_off(ov, b, hk, t) + c4 * 4;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    }
+  }
+}
+
 }  // namespace fla
 
 using namespace fla;
@@ -1068,6 +1322,18 @@ extern "C" FLA_API int fla_b200_chunk_local_cumsum(const fla_chunk_stage_args* a
   if (p.D < 1 || p.D > 1024) return FLA_ERR_SHAPE;
   p.reverse = a->reverse;
   p.scale = a->scale;
+  p.gate_mode = a->gate_mode;
+  if (a->gate_mode < 0 || a->gate_mode > 2) return FLA_ERR_VALUE;
+  if (a->gate_mode) {   // per-channel gate activation: A_log [H] in `q`, dt_bias [H, D] (optional) in `k`, both f32
+    if (nd != 4) return FLA_ERR_SHAPE;
+    const fla_tensor_t &al = a->q, &db = a->k;
+    if (!al.data) return FLA_ERR_NULL;
+    if (al.dtype != FLA_F32 || numel(al) != gm.H || !is_contig_last(al)) return FLA_ERR_SHAPE;
+    if (db.data && (db.dtype != FLA_F32 || numel(db) != gm.H * p.D || !is_contig_last(db))) return FLA_ERR_SHAPE;
+    p.a_log = static_cast<const float*>(al.data);
+    p.dt_bias = static_cast<const float*>(db.data);
+    p.lower_bound = a->lower_bound;
+  }
   const int threads = p.D == 1 ? 64 : ((std::min(p.D, 128) + 31) / 32) * 32;
   KernelTimer kt("chunk_local_cumsum", cs);
   stage_cumsum_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), threads, 0, cs>>>(p);
@@ -1311,5 +1577,79 @@ extern "C" FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu(const fla_chunk_s
     return FLA_ERR_CUDA;
   KernelTimer kt("chunk_bwd_dhu", cs);
   stage_bwd_dhu_kernel<<<dim3(kV / 64, unsigned(gm.H), gm.N), 128, kBwdDhuSmem + 1024, cs>>>(p, tm_q, tm_k, tm_w, tm_do, tm_dv);
+  return cuda_status(cudaGetLastError());
+}
+
+static uint64_t dqkwg_scratch_bytes(const fla_chunk_stage_args* a) {
+  const fla_tensor_t &q = a->q, &v = a->v;
+  if (q.ndim != 4 || v.ndim != 4 || q.shape[1] <= 0 || v.shape[1] == q.shape[1]) return 0;
+  return 2ull * uint64_t(v.shape[0]) * v.shape[1] * v.shape[2] * kK * sizeof(float);
+}
+
+extern "C" FLA_API int fla_b200_chunk_bwd_dqkwg_workspace_size(const fla_chunk_stage_args* a, uint64_t* bytes) {
+  if (!a || !bytes) return FLA_ERR_NULL;
+  *bytes = 256 + dqkwg_scratch_bytes(a);
+  return FLA_OK;
+}
+
+extern "C" FLA_API int fla_b200_chunk_bwd_dqkwg(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes, void* stream) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  const fla_tensor_t &d_o = a->u, &dv = a->w, &dh = a->A;
+  if (a->v.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->v, &gm, &p))) return st;
+  StageView tmp;
+  if ((st = make_view(a->q, 4, true, &tmp)) || (st = make_view(a->k, 4, true, &tmp)) || (st = make_view(a->v, 4, true, &tmp)) ||
+      (st = make_view(d_o, 4, true, &tmp)) || (st = make_view(dv, 4, true, &tmp)) || (st = make_view(a->g, 3, false, &p.g)) ||
+      (st = make_view(a->out0, 4, true, &p.o0)) || (st = make_view(a->out1, 4, true, &p.o1)) || (st = make_view(a->out3, 3, false, &p.o3)))
+    return st;
+  if (a->out2.data && (st = make_view(a->out2, 4, true, &p.o2))) return st;
+  const int64_t HK = a->k.shape[1];
+  for (const fla_tensor_t* t : {&a->q, &a->k, &a->v, &d_o, &dv, &a->h, &dh, &a->out0, &a->out1})
+    if (t->dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (a->out2.data && a->out2.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->v.shape[3] != kV) return FLA_ERR_SHAPE;
+  for (const fla_tensor_t* t : {&a->q, &a->k, &a->out0, &a->out1})
+    if (t->shape[0] != gm.B || t->shape[1] != HK || t->shape[2] != gm.T || t->shape[3] != kK) return FLA_ERR_SHAPE;
+  for (const fla_tensor_t* t : {&d_o, &dv})
+    if (!same_bht(*t, gm, gm.H) || t->shape[3] != kV) return FLA_ERR_SHAPE;
+  if (a->out2.data && (!same_bht(a->out2, gm, gm.H) || a->out2.shape[3] != kK)) return FLA_ERR_SHAPE;
+  if (!same_bht(a->g, gm, gm.H) || !same_bht(a->out3, gm, gm.H)) return FLA_ERR_SHAPE;
+  const int64_t NT = gm.total_chunks / gm.B;
+  for (const fla_tensor_t* h : {&a->h, &dh}) {
+    if (!h->data) return FLA_ERR_NULL;
+    if (h->ndim != 5 || h->shape[0] != gm.B || h->shape[1] != gm.H || h->shape[2] != NT || h->shape[3] != kK || h->shape[4] != kV) return FLA_ERR_SHAPE;
+    if (h->stride[4] != 1 || h->stride[3] != kV || h->stride[2] != kK * kV || h->stride[1] != NT * kK * kV || !aligned16(h->data)) return FLA_ERR_LAYOUT;
+  }
+  p.h.sh = NT;
+  p.HK = int(HK);
+  p.scale = a->scale;
+  if (!(a->scale == a->scale)) return FLA_ERR_VALUE;
+  const uint64_t scratch = dqkwg_scratch_bytes(a);
+  if (!workspace || workspace_bytes < 256 + scratch) return FLA_ERR_WORKSPACE;
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if (scratch) {
+    p.ws_dq = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+    p.ws_dk = p.ws_dq + scratch / 8;
+  }
+  if ((st = opt_in_smem(stage_dqkwg_kernel, kDqkwgSmem + 1024))) return st;
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dv, tm_h, tm_dh;
+  const uint64_t hrows = uint64_t(gm.B) * gm.H * NT * kK;
+  if (token_tile_map(a->q, &tm_q) || token_tile_map(a->k, &tm_k) || token_tile_map(a->v, &tm_v) || token_tile_map(d_o, &tm_do) ||
+      token_tile_map(dv, &tm_dv) || make_bhtd_tile_map(&tm_h, a->h.data, 2, kV, hrows, 1, 1, kV, 0, 0, 64, 128) ||
+      make_bhtd_tile_map(&tm_dh, dh.data, 2, kV, hrows, 1, 1, kV, 0, 0, 64, 128))
+    return FLA_ERR_CUDA;
+  {
+    KernelTimer kt("chunk_bwd_dqkwg", cs);
+    stage_dqkwg_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kDqkwgSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_do, tm_dv, tm_h, tm_dh);
+  }
+  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  if (scratch) {
+    KernelTimer kt("chunk_bwd_dqkwg_group_sum", cs);
+    stage_group_sum_kernel<<<148 * 8, 256, 0, cs>>>(p, int(gm.B));
+  }
   return cuda_status(cudaGetLastError());
 }

@@ -10,7 +10,9 @@ from .recurrent import fused_recurrent_gated_delta_rule, recurrent_gated_delta_r
 
 npu_recurrent_gated_delta_rule = recurrent_gated_delta_rule
 npu_recurrent_kda = recurrent_kda
-from .stages import (chunk_bwd_dv_local, chunk_gated_delta_rule_bwd_dhu, npu_chunk_bwd_dv_local,  # noqa: F401,E402
+from .stages import chunk_bwd_dqkwg, npu_chunk_bwd_dqkwg  # noqa: F401,E402
+from .stages import (chunk_bwd_dv_local, chunk_gated_delta_rule_bwd_dhu, kda_gate_cumsum, npu_chunk_bwd_dv_local,  # noqa: F401,E402
+                     npu_kda_gate_cumsum,
                      npu_chunk_gated_delta_rule_bwd_dhu)
 from .stages import (chunk_fwd_o, chunk_gated_delta_rule_fwd_h, chunk_local_cumsum, chunk_scaled_dot_kkt,  # noqa: F401,E402
                      npu_chunk_fwd_o, npu_chunk_gated_delta_rule_fwd_h, npu_chunk_local_cumsum, npu_chunk_scaled_dot_kkt,

@@ -64,6 +64,7 @@ class L2NormArgs(ctypes.Structure):
 
 class ChunkStageArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "w", "u", "g", "beta", "A", "h", "initial_state", "out0", "out1",
-                                           "out2", "cu_seqlens", "chunk_offsets")] + [
+                                           "out2", "out3", "cu_seqlens", "chunk_offsets")] + [
         ("scale", ctypes.c_float), ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32),
-        ("total_chunks", ctypes.c_int32), ("reverse", ctypes.c_int32)]
+        ("total_chunks", ctypes.c_int32), ("reverse", ctypes.c_int32), ("gate_mode", ctypes.c_int32),
+        ("lower_bound", ctypes.c_float)]

@@ -21,7 +21,7 @@ _DTYPES = {"float": torch.float32, "float32": torch.float32, "half": torch.float
            "bf16": torch.bfloat16, "bfloat16": torch.bfloat16}
 
 
-def _stage_call(op, fields, tensors, ref, cu_seqlens, chunk_size, scale=1.0, reverse=False):
+def _stage_call(op, fields, tensors, ref, cu_seqlens, chunk_size, scale=1.0, reverse=False, gate_mode=0, lower_bound=0.0):
     if int(chunk_size) != CHUNK:
         raise NotImplementedError(f"{op}: this build supports chunk_size = {CHUNK}, got {chunk_size}")
     B, T = ref.shape[0], ref.shape[2]
@@ -39,6 +39,7 @@ def _stage_call(op, fields, tensors, ref, cu_seqlens, chunk_size, scale=1.0, rev
         setattr(a, name, rt.desc(t))
     a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
     a.scale, a.chunk_size, a.max_seqlen, a.total_chunks, a.reverse = float(scale), CHUNK, int(max_len), int(total_chunks), int(bool(reverse))
+    a.gate_mode, a.lower_bound = int(gate_mode), float(lower_bound)
     rt.call(op, a, list(tensors) + [cu, co])
     return total_chunks
 
@@ -67,6 +68,28 @@ def chunk_local_cumsum(g, chunk_size, *, cu_seqlens=None, chunk_indices_out=None
     out = torch.empty(g.shape, dtype=out_dtype, device=g.device)
     gv, ov = (g, out) if head_first else (g.transpose(1, 2), out.transpose(1, 2))
     _stage_call("chunk_local_cumsum", dict(g=gv, out0=ov), [g, out], gv, cu_seqlens, chunk_size, scale=scale, reverse=reverse)
+    return out
+
+
+def kda_gate_cumsum(g, chunk_size, *, A_log=None, dt_bias=None, cu_seqlens=None, use_gate_in_kernel=False, safe_gate=False,
+                    lower_bound=None):
+    """Per-channel gate activation and chunk-local cumulative sum in base 2: `gk = cumsum_chunk(gate) / ln 2` with
+    gate = g, `-e^{A_log} softplus(g + dt_bias)` (`use_gate_in_kernel`) or `lower_bound sigmoid(e^{A_log} (g + dt_bias))`
+    (`use_gate_in_kernel` and `safe_gate`).  g `[B,T,HV,K]` -> fp32 of the same shape."""
+    if g.dim() != 4:
+        raise RuntimeError(f"kda_gate_cumsum: g must be [B,T,HV,K], got {tuple(g.shape)}")
+    HV, K = g.shape[2], g.shape[3]
+    mode, al, db = 0, None, None
+    if use_gate_in_kernel:
+        if A_log is None:
+            raise RuntimeError("kda_gate_cumsum: use_gate_in_kernel needs A_log")
+        mode = 2 if safe_gate else 1
+        al = A_log.float().reshape(HV).contiguous()
+        db = None if dt_bias is None else dt_bias.float().reshape(HV, K).contiguous()
+    out = torch.empty(g.shape, dtype=torch.float32, device=g.device)
+    gv, ov = g.transpose(1, 2), out.transpose(1, 2)
+    _stage_call("chunk_local_cumsum", dict(g=gv, out0=ov, q=al, k=db), [g, out, al, db], gv, cu_seqlens, chunk_size,
+                scale=1.4426950408889634, gate_mode=mode, lower_bound=-5.0 if lower_bound is None else lower_bound)
     return out
 
 
@@ -202,6 +225,26 @@ def chunk_gated_delta_rule_bwd_dhu(q, k, w, d_o, dv, scale, chunk_size, *, g=Non
     return dh, dh0, dv2
 
 
+def chunk_bwd_dqkwg(q, k, v, g, h, dox, dh, dv, chunk_size, *, cu_seqlens=None, chunk_indices=None, w=None, g_gamma=None, scale=None,
+                    use_exp2=None, transpose_state_layout=None):
+    """dq, dk (summed over the value heads of a group), dw and the pre-cumsum dg of one backward step from the per-chunk
+    states.  q, k `[B,HK,T,K]`; v (= v_new), dox (= dO), dv (= dv2) `[B,HV,T,V]`; h, dh `[B,HV,NT,K,V]`; g `[B,HV,T]`.
+    Returns (dq, dk, dw, dg); dw is produced when `w` is given (as in the reference, whose kernel only needs its presence)."""
+    del chunk_indices
+    if g is None or g_gamma is not None or use_exp2 or transpose_state_layout:
+        raise NotImplementedError("chunk_bwd_dqkwg: scalar gates g only; g_gamma / use_exp2 / transpose_state_layout are not supported")
+    scale = 1.0 if scale is None else float(scale)
+    B, HV, T, V = v.shape
+    dq, dk = torch.empty_like(q), torch.empty_like(k)
+    dw = torch.empty((B, HV, T, q.shape[3]), dtype=q.dtype, device=q.device) if w is not None else None
+    dg = torch.empty_like(g)
+    _stage_call("chunk_bwd_dqkwg", dict(q=q, k=k, v=v, g=g, h=h, u=dox, A=dh, w=dv, out0=dq, out1=dk, out2=dw, out3=dg),
+                [q, k, v, g, h, dox, dh, dv, dq, dk, dw, dg], v, cu_seqlens, chunk_size, scale=scale)
+    return dq, dk, dw, dg
+
+
+npu_chunk_bwd_dqkwg = chunk_bwd_dqkwg
+npu_kda_gate_cumsum = kda_gate_cumsum
 npu_chunk_bwd_dv_local = chunk_bwd_dv_local
 npu_chunk_gated_delta_rule_bwd_dhu = chunk_gated_delta_rule_bwd_dhu
 npu_chunk_local_cumsum = chunk_local_cumsum

@@ -336,6 +336,10 @@ FLA_API int fla_b200_l2norm_bwd(const fla_l2norm_args* args, void* stream);
  * fla_b200_chunk_local_cumsum   (aclnnChunkLocalCumsum, _aclnn_ctypes.py:875-904)
  *     g [B,H,T] or [B,H,T,D] f32|bf16|f16 -> out0 same shape, f32|bf16|f16:
  *     out0[t] = scale * sum of g over t's chunk up to t (reverse != 0: from t to the chunk's end).
+ *     With a 4-D g and gate_mode != 0 this is aclnnKdaGateCumsum (:1268-1296; kda/chunk_kda_fwd/docs/api.md:103-115):
+ *     the gate is activated first, -e^{A_log[h]} softplus(g + dt_bias[h,:]) (gate_mode 1) or
+ *     lower_bound sigmoid(e^{A_log[h]} (g + dt_bias[h,:])) (gate_mode 2), with A_log [H] f32 passed in `q` and
+ *     dt_bias [H,D] f32 (optional) in `k`; scale = 1/ln 2 gives the reference's base-2 gk.
  * fla_b200_chunk_scaled_dot_kkt (aclnnChunkScaledDotKkt, :907-936; golden test_npu_chunk_scaled_dot_kkt.py:60-103)
  *     k [B,HK,T,128] bf16, g (chunk-local cumulative gate) and beta [B,HV,T] -> out0 [B,HV,T,64] f32:
  *     out0[i,j] = beta_i exp(clamp(g_i - g_j, -50, 50)) k_i.k_j for j < i inside a chunk, else 0.
@@ -364,16 +368,24 @@ FLA_API int fla_b200_l2norm_bwd(const fla_l2norm_args* args, void* stream);
  *     -> out0 = dh [B,HV,NT,128,128] bf16 dense (gradient of the state at the END of every chunk), out1 = dv2 bf16,
  *        out2 = dh0 [N,HV,128,128] f32 (optional).  Reverse over chunks: dh_c = dS; dv2 = dv + e^{g_last - g} (k dS);
  *        dS <- e^{g_last} dS + q^T (scale e^g d_o) - w^T dv2.
- * Workspace: 256 bytes (status word of the bounded device-side waits). */
+ * fla_b200_chunk_bwd_dqkwg      (aclnnChunkBwdDqkwg, :463-514; golden tests/atk/chunk_bwd_dqkwg/scripts/chunk_bwd_dqkwg_cpu.py:66-409)
+ *     q, k [B,HK,T,128], v = v_new, u = d_o, w = dv (the dv2 of the reverse pass) [B,HV,T,128] bf16, g [B,HV,T],
+ *     h and A = dh [B,HV,NT,128,128] bf16 dense, scale
+ *     -> out0 = dq, out1 = dk [B,HK,T,128] bf16 (summed over the value heads of a group), out2 = dw [B,HV,T,128] bf16
+ *        (optional), out3 = dg [B,HV,T] (before the reverse cumulative sum, the chunk's last row carrying the state terms).
+ *     Workspace: 256 bytes, plus 2 * B*HV*T*128 fp32 when HV > HK (fla_b200_chunk_bwd_dqkwg_workspace_size).
+ * Workspace of the others: 256 bytes (status word of the bounded device-side waits). */
 typedef struct fla_chunk_stage_args {
   fla_tensor_t q, k, v, w, u, g, beta, A, h, initial_state;
-  fla_tensor_t out0, out1, out2;
+  fla_tensor_t out0, out1, out2, out3;
   fla_tensor_t cu_seqlens, chunk_offsets;
   float scale;
   int32_t chunk_size;
   int32_t max_seqlen;
   int32_t total_chunks;
   int32_t reverse;
+  int32_t gate_mode;   /* chunk_local_cumsum of per-channel gates only */
+  float lower_bound;
 } fla_chunk_stage_args;
 FLA_API int fla_b200_chunk_local_cumsum_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
 FLA_API int fla_b200_chunk_scaled_dot_kkt_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
@@ -390,6 +402,8 @@ FLA_API int fla_b200_chunk_gated_delta_rule_fwd_h(const fla_chunk_stage_args* ar
 FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
 FLA_API int fla_b200_chunk_bwd_dv_local_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
 FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_bwd_dqkwg_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_bwd_dqkwg(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
 FLA_API int fla_b200_chunk_bwd_dv_local(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
 FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes,
                                                     void* stream);

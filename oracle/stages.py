@@ -11,6 +11,7 @@ CPU restatements of the reference's per-operator goldens, on head-first `[B,H,T,
   dv_local              fla/ops/ascendc/gdn/chunk_gdn_bwd/chunk_bwd_dv_local/tests/ATK/executor_chunk_bwd_dv_local.py:57-130
   bwd_dhu               torch_custom/fla_npu/test/test_bwd_dhu.py:61-290 ("fp64" mode), extended with the cotangent of the
                         final state (the reference deletes `dht`) and a `[N,HV,K,V]` dh0
+  dqkwg                 tests/atk/chunk_bwd_dqkwg/scripts/chunk_bwd_dqkwg_cpu.py:66-409 (benchmark = fp64 mode)
 Pinned by tests/golden/stages_golden.npz, which tests/golden/make_golden.py produces by running those reference
 functions themselves.
 """
@@ -191,3 +192,32 @@ def chunk_bwd_dhu_ref(q, k, w, d_o, dv, g, scale, chunk_size, dht=None, cu_seqle
             dh0[:] = dS
         base += len(chunks)
     return dh, dh0, dv2
+
+
+def chunk_bwd_dqkwg_ref(q, k, v, g, h, d_o, dh, dv, scale, chunk_size, cu_seqlens=None):
+    """dq, dk [B,HK,T,K] (summed over each group's value heads), dw [B,HV,T,K], dg [B,HV,T] (before the reverse cumulative
+    sum; the last row of a chunk carries e^{g_last} <h, dh> + sum_i k_i.dk_state_i), fp64."""
+    B, HV, T, V = v.shape
+    HK, K = k.shape[1], k.shape[3]
+    G = HV // HK
+    qq = q.double().repeat_interleave(G, dim=1)
+    kk = k.double().repeat_interleave(G, dim=1)
+    v, g, h, d_o, dh, dv = (t.double() for t in (v, g, h, d_o, dh, dv))
+    dq = torch.zeros(B, HV, T, K, dtype=torch.float64)
+    dk = torch.zeros_like(dq)
+    dw = torch.zeros_like(dq)
+    dg = torch.zeros(B, HV, T, dtype=torch.float64)
+    for ci, (s, e) in enumerate(chunk_ranges(T, chunk_size, cu_seqlens)):
+        gc, gl = g[:, :, s:e], g[:, :, e - 1]
+        hc, dhc = h[:, :, ci], dh[:, :, ci]
+        dq_state = (d_o[:, :, s:e] @ hc.transpose(-1, -2)) * torch.exp(gc)[..., None] * scale
+        dk_state = (v[:, :, s:e] @ dhc.transpose(-1, -2)) * torch.exp(gl[..., None] - gc)[..., None]
+        dw[:, :, s:e] = -(dv[:, :, s:e] @ hc.transpose(-1, -2))
+        ds = torch.tril(d_o[:, :, s:e] @ v[:, :, s:e].transpose(-1, -2) * torch.exp(gc[..., :, None] - gc[..., None, :])) * scale
+        ds2 = ds * (qq[:, :, s:e] @ kk[:, :, s:e].transpose(-1, -2))
+        dgc = (dq_state * qq[:, :, s:e]).sum(-1) - (kk[:, :, s:e] * dk_state).sum(-1) + ds2.sum(-1) - ds2.sum(-2)
+        dgc[:, :, -1] += (hc * dhc).sum((-1, -2)) * torch.exp(gl) + (dk_state * kk[:, :, s:e]).sum((-1, -2))
+        dg[:, :, s:e] = dgc
+        dq[:, :, s:e] = dq_state + ds @ kk[:, :, s:e]
+        dk[:, :, s:e] = dk_state + ds.transpose(-1, -2) @ qq[:, :, s:e]
+    return dq.view(B, HK, G, T, K).sum(2), dk.view(B, HK, G, T, K).sum(2), dw, dg

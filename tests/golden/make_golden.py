@@ -169,6 +169,7 @@ def stages_fixture():
     dhu_ref = extract(test_dir / "test_bwd_dhu.py", ["_round_elem", "_matmul_npu_aligned", "_gate_exp2", "_gate_exp",
                                                       "chunk_gated_delta_rule_bwd_dhu_cpu"],
                       extra={"_LN2": math.log(2.0)})["chunk_gated_delta_rule_bwd_dhu_cpu"]
+    dqkwg_ref = extract(REF / "tests/atk/chunk_bwd_dqkwg/scripts/chunk_bwd_dqkwg_cpu.py", ["chunk_bwd_dqkwg_cpu"])["chunk_bwd_dqkwg_cpu"]
     torch.Tensor.npu = lambda self: self   # the golden moves its CPU tensors "to the device" before computing
 
     C, K, V, HK, HV, T = 64, 128, 128, 1, 2, 160
@@ -218,6 +219,12 @@ def stages_fixture():
         dh, dh0, dv2 = dhu_ref(q, k, wb, d_o, dvb, cu_seqlens=cu_b, chunk_indices=idx_b, g=gam, h0=torch.zeros(1), scale=K ** -0.5,
                                chunk_size=C, golden_mode="fp64")
         first = [i for i in range(NT) if idx_b[2 * i + 1] == 0]
+        # dq, dk, dw, dg from the per-chunk states (this golden is sequence-first, h / dh as [B,NT,H,K,V])
+        sf = lambda t: t.transpose(1, 2).contiguous()  # noqa: E731
+        dhb, dv2b = bf(dh.float()), bf(dv2.float())
+        dq_, dk_, dw_, dg_ = dqkwg_ref(sf(q), sf(k), sf(vnb), sf(d_o), sf(hb), sf(dhb), torch.zeros(1), sf(gam), sf(dv2b), K ** -0.5,
+                                       cu_t, C, benchmark=True)
+        out.update({f"{tag}_dq": f32(sf(dq_)), f"{tag}_dk": f32(sf(dk_)), f"{tag}_dw": f32(sf(dw_)), f"{tag}_dg": f32(sf(dg_))})
         out.update({f"{tag}_dv_local": f32(dv_loc), f"{tag}_dh": f32(dh), f"{tag}_dh0": f32(dh0[0, :, first].transpose(0, 1)),
                     f"{tag}_dv2": f32(dv2)})
         out.update({f"{tag}_gam": f32(gam), f"{tag}_rev": f32(rev), f"{tag}_A": f32(A), f"{tag}_X": f32(X), f"{tag}_w": f32(w),

@@ -47,6 +47,8 @@ def _case(B, T, HK, HV, seed, cu=None):
     d["dv_local"] = stages.chunk_bwd_dv_local_ref(q, k, d["d_o"], d["gam"], 128 ** -0.5, C, cu)
     d["dh"], d["dh0"], d["dv2"] = stages.chunk_bwd_dhu_ref(q, k, wb, d["d_o"], _bf(d["dv_local"]), d["gam"], 128 ** -0.5, C, dht=d["dht"],
                                                            cu_seqlens=cu)
+    d["dq"], d["dk"], d["dw"], d["dg"] = stages.chunk_bwd_dqkwg_ref(q, k, _bf(d["v_new"]), d["gam"], _bf(d["h"]), d["d_o"], _bf(d["dh"]),
+                                                                    _bf(d["dv2"]), 128 ** -0.5, C, cu)
     return d
 
 
@@ -80,6 +82,32 @@ def test_chunk_local_cumsum_per_channel():
     g = torch.nn.functional.logsigmoid(torch.randn(2, 3, 150, 128, generator=torch.Generator().manual_seed(3))) / 16
     out = chunk_local_cumsum(g.cuda(), C, scale=1.4426950408889634)
     assert_close("gk", out, stages.chunk_local_cumsum_ref(g, C, scale=1.4426950408889634), 1e-6)
+
+
+@pytest.mark.parametrize("mode", ["raw", "softplus", "safe"])
+@pytest.mark.parametrize("cu", [None, [0, 40, 150]])
+def test_kda_gate_cumsum(mode, cu):
+    """aclnnKdaGateCumsum semantics (kda/chunk_kda_fwd/docs/api.md:103-115; golden
+    tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:316-343)."""
+    import math
+    from fla_b200.ops import kda_gate_cumsum
+    g_ = torch.Generator().manual_seed(17)
+    B, T, HV, K = (2, 150, 3, 128) if cu is None else (1, 150, 3, 128)
+    g = torch.randn(B, T, HV, K, generator=g_).bfloat16()
+    A_log = 0.5 * torch.randn(HV, generator=g_)
+    dt_bias = 0.5 * torch.randn(HV * K, generator=g_)
+    gf = g.double()
+    if mode == "raw":
+        gate, kw = gf, {}
+    else:
+        raw = gf + dt_bias.double().view(1, 1, HV, K)
+        eig = A_log.double().exp().view(1, 1, HV, 1)
+        gate = -4.0 * torch.sigmoid(eig * raw) if mode == "safe" else -eig * torch.nn.functional.softplus(raw)
+        kw = dict(A_log=A_log.cuda(), dt_bias=dt_bias.cuda(), use_gate_in_kernel=True, safe_gate=mode == "safe", lower_bound=-4.0)
+    ref = stages.chunk_local_cumsum_ref(gate.transpose(1, 2), C, scale=1.0 / math.log(2.0), cu_seqlens=cu).transpose(1, 2)
+    out = kda_gate_cumsum(g.cuda(), C, cu_seqlens=cu, **kw)
+    assert out.dtype == torch.float32 and out.shape == g.shape
+    assert_close("gk", out, ref, 1e-5)
 
 
 def test_chunk_scaled_dot_kkt(case):
@@ -154,6 +182,18 @@ def test_chunk_bwd_dhu(case):
     last = -1 if cu is None else None
     if last is not None:
         assert (dh_b[:, :, last] == 0).all()     # without dht the gradient of the last chunk's end state is zero
+
+
+def test_chunk_bwd_dqkwg(case):
+    from fla_b200.ops import chunk_bwd_dqkwg
+    d, cu = case
+    dq, dk, dw, dg = chunk_bwd_dqkwg(d["q"].cuda(), d["k"].cuda(), _bf(d["v_new"]).cuda(), d["gam"].cuda(), _bf(d["h"]).cuda(),
+                                     d["d_o"].cuda(), _bf(d["dh"]).cuda(), _bf(d["dv2"]).cuda(), C, cu_seqlens=cu, w=_bf(d["w"]).cuda(),
+                                     scale=128 ** -0.5)
+    assert_close("dq", dq, d["dq"], TOL, stored_bf16=True)
+    assert_close("dk", dk, d["dk"], TOL, stored_bf16=True)
+    assert_close("dw", dw, d["dw"], TOL, stored_bf16=True)
+    assert_close("dg", dg, d["dg"], TOL)
 
 
 def test_stage_chain_matches_fused_operator():

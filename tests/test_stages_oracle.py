@@ -48,6 +48,10 @@ def test_stage_oracle_matches_reference_goldens(fx, tag, cu):
     _close(dh, fx[f"{tag}_dh"], 2e-6)
     _close(dh0, fx[f"{tag}_dh0"], 2e-6)
     _close(dv2, fx[f"{tag}_dv2"], 2e-6)
+    dq, dk, dw, dg = stages.chunk_bwd_dqkwg_ref(fx["q"], fx["k"], bf(fx[f"{tag}_v_new"]), gam, bf(fx[f"{tag}_h"]), fx["d_o"],
+                                                bf(fx[f"{tag}_dh"]), bf(fx[f"{tag}_dv2"]), scale, C, cu)
+    for name, got in (("dq", dq), ("dk", dk), ("dw", dw), ("dg", dg)):
+        _close(got, fx[f"{tag}_{name}"], 2e-6)
 
 
 def test_stage_chain_reproduces_the_recurrence():
