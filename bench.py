@@ -40,7 +40,7 @@ sys.path.insert(0, str(REPO / "flash-linear-attention-npu_b200"))
 sys.path.insert(0, str(REPO))
 
 DEFAULT_WORKLOAD = "gdn_fwd_bwd"
-WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "decode", "conv_prefill", "conv_bwd", "gdn_stage_fwd"]
+WORKLOADS = ["gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "decode", "conv_prefill", "conv_bwd", "gdn_stage_fwd", "gdn_stage_fwd_bwd"]
 FWD_FLOP_PER_TOKEN_HEAD = 182955.0      # KK^T, inverse, w/u, state, output (dense 64x64 tiles, no causal credit)
 BWD_FLOP_PER_TOKEN_HEAD = 524288.0
 
@@ -70,6 +70,16 @@ STAGE_BYTES = {
     "recompute_w_u_fwd": lambda c: _th(c, "HK", 128, 2) + _th(c, "HV", 128, 2) + _th(c, "HV", 64, 2) + 2 * _th(c, "HV", 128, 2),
     "chunk_fwd_h": lambda c: _th(c, "HK", 128, 2) + 2 * _th(c, "HV", 128, 2) + _th(c, "HV", 128, 2) + _th(c, "HV", 256, 2),
     "chunk_fwd_o": lambda c: 2 * _th(c, "HK", 128, 2) + _th(c, "HV", 128, 2) + _th(c, "HV", 256, 2) + _th(c, "HV", 128, 2),
+    "chunk_bwd_dv_local": lambda c: 2 * _th(c, "HK", 128, 2) + 2 * _th(c, "HV", 128, 2),
+    "chunk_bwd_dhu": lambda c: 2 * _th(c, "HK", 128, 2) + 4 * _th(c, "HV", 128, 2) + _th(c, "HV", 256, 2),
+    # q, k, v_new, dO, dv2, h, dh in; dw and the per-value-head fp32 dq, dk rows out
+    "chunk_bwd_dqkwg": lambda c: 2 * _th(c, "HK", 128, 2) + 3 * _th(c, "HV", 128, 2) + 2 * _th(c, "HV", 256, 2) + _th(c, "HV", 128, 2) +
+    2 * _th(c, "HV", 128, 4),
+    "chunk_bwd_dqkwg_group_sum": lambda c: 2 * _th(c, "HV", 128, 4) + 2 * _th(c, "HK", 128, 2),
+    # k, v, X, dw, du in; dv and the per-value-head fp32 dk rows out
+    "prepare_wy_repr_bwd": lambda c: _th(c, "HK", 128, 2) + 3 * _th(c, "HV", 128, 2) + _th(c, "HV", 64, 2) + _th(c, "HV", 128, 2) +
+    _th(c, "HV", 128, 4),
+    "prepare_wy_repr_bwd_group_sum": lambda c: _th(c, "HV", 128, 4) + _th(c, "HK", 128, 2),
 }
 KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
                  "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "kda_bwd_dhu": "kda_bwd_dhu_kernel", "kda_bwd_par": "kda_bwd_par_kernel", "gdn_prep": "gdn_prep_kernel", "tri_inverse": "tri_inverse_kernel",
@@ -77,7 +87,10 @@ KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel
                  "causal_conv1d_update": "conv_update1_kernel", "causal_conv1d_bwd": "conv_bwd_kernel",
                  "chunk_local_cumsum": "stage_cumsum_kernel", "chunk_scaled_dot_kkt": "stage_kkt_kernel",
                  "solve_tri": "stage_solve_tri_kernel", "recompute_w_u_fwd": "stage_wu_kernel",
-                 "chunk_fwd_h": "stage_fwd_h_kernel", "chunk_fwd_o": "stage_fwd_o_kernel"}
+                 "chunk_fwd_h": "stage_fwd_h_kernel", "chunk_fwd_o": "stage_fwd_o_kernel",
+                 "chunk_bwd_dv_local": "stage_dv_local_kernel", "chunk_bwd_dhu": "stage_bwd_dhu_kernel",
+                 "chunk_bwd_dqkwg": "stage_dqkwg_kernel", "chunk_bwd_dqkwg_group_sum": "stage_group_sum_kernel",
+                 "prepare_wy_repr_bwd": "stage_wy_bwd_kernel", "prepare_wy_repr_bwd_group_sum": "stage_group_sum_kernel"}
 
 
 def _peaks():
@@ -141,7 +154,7 @@ class Workload:
     def __init__(self, name, shape):
         self.name = name
         self.graph = None
-        if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill", "conv_bwd", "gdn_stage_fwd"):
+        if name in ("gdn_fwd_bwd", "gdn_fwd_conv", "conv_prefill", "conv_bwd", "gdn_stage_fwd", "gdn_stage_fwd_bwd"):
             self.cfg = dict(B=8, T=4096, HK=16, HV=32, K=128, V=128, D=8192, W=4)
         elif name in ("kda_fwd", "kda_fwd_bwd"):
             self.cfg = dict(B=4, T=8192, HK=32, HV=32, K=128, V=128)
@@ -164,7 +177,7 @@ class Workload:
         g_ = torch.Generator(device=device).manual_seed(seed)
         rn = lambda *s: torch.randn(*s, device=device, generator=g_)  # noqa: E731
         d = {}
-        if self.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "gdn_stage_fwd"):
+        if self.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "kda_fwd", "kda_fwd_bwd", "gdn_stage_fwd", "gdn_stage_fwd_bwd"):
             d["q"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
             d["k"] = F.normalize(rn(c["B"], c["T"], c["HK"], c["K"]), dim=-1).bfloat16()
             d["v"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
@@ -174,7 +187,7 @@ class Workload:
             else:
                 d["g"] = F.logsigmoid(rn(c["B"], c["T"], c["HV"])).bfloat16()
                 d["h0"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
-        if self.name == "gdn_fwd_bwd":
+        if self.name in ("gdn_fwd_bwd", "gdn_stage_fwd_bwd"):
             d["do"] = rn(c["B"], c["T"], c["HV"], c["V"]).bfloat16()
             d["dht"] = 0.1 * rn(c["B"], c["HV"], c["K"], c["V"])
         if self.name == "kda_fwd_bwd":
@@ -203,7 +216,8 @@ class Workload:
                 "kda_fwd": ["q", "k", "v", "g", "beta"],
                 "kda_fwd_bwd": ["q", "k", "v", "g", "beta", "do"],
                 "decode": ["q", "k", "v", "g", "beta", "x"],
-                "conv_prefill": ["x"], "conv_bwd": ["x", "dy"], "gdn_stage_fwd": ["q", "k", "v", "g", "beta", "h0"]}[self.name]
+                "conv_prefill": ["x"], "conv_bwd": ["x", "dy"], "gdn_stage_fwd": ["q", "k", "v", "g", "beta", "h0"],
+                "gdn_stage_fwd_bwd": ["q", "k", "v", "g", "beta", "h0", "do", "dht"]}[self.name]
 
     def step(self, d):
         """One pass through the public Python API.  Returns the tensors a caller reads back."""
@@ -225,15 +239,29 @@ class Workload:
             o, ht, grads = ops.chunk_kda_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"],
                                                  grad_dtype=torch.bfloat16, disable_recompute=True)
             return (o, ht) + tuple(x for x in grads if x is not None)
-        if n == "gdn_stage_fwd":
-            # the reference's stage-by-stage forward chain (examples/flash_gated_delta_rule.py:796-881) on head-first views
+        if n in ("gdn_stage_fwd", "gdn_stage_fwd_bwd"):
+            # the reference's stage-by-stage chains (examples/flash_gated_delta_rule.py:796-881 forward, :884-1023 backward) on
+            # head-first views
             hf = lambda t: t.transpose(1, 2)  # noqa: E731
-            gam = ops.chunk_local_cumsum(d["g"], 64, head_first=False)
-            A = ops.chunk_scaled_dot_kkt(hf(d["k"]), hf(gam), hf(d["beta"]))
+            scale = self.cfg["K"] ** -0.5
+            q, k, v, beta = hf(d["q"]), hf(d["k"]), hf(d["v"]), hf(d["beta"])
+            gam = hf(ops.chunk_local_cumsum(d["g"], 64, head_first=False))
+            A = ops.chunk_scaled_dot_kkt(k, gam, beta)
             X = ops.solve_tri(A, layout="bnsd", output_dtype=torch.bfloat16)
-            w, u = ops.recompute_w_u_fwd(hf(d["k"]), hf(d["v"]), hf(d["beta"]), X, 64, g=hf(gam))
-            h, v_new, ht = ops.chunk_gated_delta_rule_fwd_h(hf(d["k"]), w, u, hf(gam), initial_state=d["h0"], output_final_state=True)
-            return ops.chunk_fwd_o(hf(d["q"]), hf(d["k"]), v_new, h, self.cfg["K"] ** -0.5, g=hf(gam)), ht
+            w, u = ops.recompute_w_u_fwd(k, v, beta, X, 64, g=gam)
+            h, v_new, ht = ops.chunk_gated_delta_rule_fwd_h(k, w, u, gam, initial_state=d["h0"], output_final_state=True)
+            o = ops.chunk_fwd_o(q, k, v_new, h, scale, g=gam)
+            if n == "gdn_stage_fwd":
+                return o, ht
+            do = hf(d["do"])
+            dv = ops.chunk_bwd_dv_local(q, k, do, gam, scale, 64)
+            dh, dh0, dv2 = ops.chunk_gated_delta_rule_bwd_dhu(q, k, w, do, dv, scale, 64, g=gam, h0=d["h0"], dht=d["dht"])
+            dq, dk, dw, dg = ops.chunk_bwd_dqkwg(q, k, v_new, gam, h, do, dh, dv2, 64, w=w, scale=scale)
+            dk2, dv_f, dbeta, dg2 = ops.prepare_wy_repr_bwd(k, v, beta, X, dw, dv2, gam, 64)
+            # the reference's glue adds dk2 and dg2 with torch ops and reverse-cumsums dg (:1010-1021)
+            dk = dk + dk2
+            dg = ops.chunk_local_cumsum(dg + dg2, 64, reverse=True)
+            return o, ht, dq, dk, dv_f, dbeta, dg, dh0
         if n == "conv_prefill":
             return ops.causal_conv1d(d["x"], d["w"], d["bias"], activation="silu")[:1]
         if n == "conv_bwd":
@@ -258,7 +286,7 @@ class Workload:
 
     def launches_per_step(self):
         return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1, "conv_bwd": 2,
-                "gdn_stage_fwd": 6}[self.name]
+                "gdn_stage_fwd": 6, "gdn_stage_fwd_bwd": 13}[self.name]
 
     def kernel_names(self):
         return {"gdn_fwd_bwd": ["gdn_prep", "tri_inverse", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
@@ -267,7 +295,10 @@ class Workload:
                 "kda_fwd_bwd": ["kda_prep", "tri_inverse", "kda_fwd", "kda_bwd_dhu", "kda_bwd_par"], "decode": ["causal_conv1d_update", "recurrent_gdn"],
                 "conv_prefill": ["causal_conv1d_fwd"], "conv_bwd": ["causal_conv1d_bwd"],
                 "gdn_stage_fwd": ["chunk_local_cumsum", "chunk_scaled_dot_kkt", "solve_tri", "recompute_w_u_fwd", "chunk_fwd_h",
-                                  "chunk_fwd_o"]}[self.name]
+                                  "chunk_fwd_o"],
+                "gdn_stage_fwd_bwd": ["chunk_local_cumsum", "chunk_scaled_dot_kkt", "solve_tri", "recompute_w_u_fwd", "chunk_fwd_h",
+                                      "chunk_fwd_o", "chunk_bwd_dv_local", "chunk_bwd_dhu", "chunk_bwd_dqkwg",
+                                      "chunk_bwd_dqkwg_group_sum", "prepare_wy_repr_bwd", "prepare_wy_repr_bwd_group_sum"]}[self.name]
 
     def kernel_work(self, kname):
         """(bound, algorithmic work per launch, unit) of one kernel at this workload's shape."""
@@ -307,7 +338,7 @@ class Workload:
         return None
 
     def step_flops(self):
-        if self.name == "gdn_fwd_bwd":
+        if self.name in ("gdn_fwd_bwd", "gdn_stage_fwd_bwd"):
             return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads
         if self.name == "kda_fwd_bwd":
             return (FWD_FLOP_PER_TOKEN_HEAD + BWD_FLOP_PER_TOKEN_HEAD) * self.token_heads

@@ -37,6 +37,7 @@ struct StageParams {
   const int32_t* chunk_offsets;
   int T, H, HK, D;
   int reverse, want_final;
+  int wy_mode;              // prepare_wy_repr_bwd: 0 fused, 1 dA only, 2 dk / dv / dbeta / dg from a given dA
   int gate_mode;            // cumsum of per-channel gates: 0 raw, 1 -e^{A_log} softplus(g + dt_bias), 2 lower_bound sigmoid(e^{A_log} (g + dt_bias))
   const float* a_log;       // [H]
   const float* dt_bias;     // [H, D] or null
@@ -1189,15 +1190,14 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
 }
 
 // dq / dk of a q/k head = sum over the value heads of its group of the fp32 scratch rows
-__global__ void __launch_bounds__(256) stage_group_sum_kernel(StageParams p, int B) {
+__global__ void __launch_bounds__(256) stage_group_sum_kernel(StageParams p, int B, int n_out) {
   const int G = p.H / p.HK;
   const int64_t total = int64_t(B) * p.HK * p.T * (kK / 4);
   for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
     const int c4 = int(idx % (kK / 4));
     const int64_t t = (idx / (kK / 4)) % p.T;
     const int64_t hk = (idx / (kK / 4) / p.T) % p.HK, b = idx / (kK / 4) / p.T / p.HK;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
+    for (int which = 0; which < n_out; ++which) {
       const float* src = which ? p.ws_dk : p.ws_dq;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int g = 0; g < G; ++g) {
@@ -1209,6 +1209,292 @@ __global__ void __launch_bounds__(256) stage_group_sum_kernel(StageParams p, int
       *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
   }
+}
+
+// ----------------------------------------------------------------------------- prepare_wy_repr_bwd (+ _da, _full)
+// Backward of  w = X (k beta e^g),  u = X (v beta),  X = (I + A)^-1,  A_ij = beta_i e^{g_i - g_j} k_i.k_j (j < i),
+// per chunk and value head, from dw and du:
+//   P   = strict_lower(dw (k beta e^g)^T + du (v beta)^T)
+//   dA  = strict_lower(-(X^T P X^T) * e^{g_i - g_j})          (stored transposed, like the reference operator)
+//   dkbg = X^T dw,  dvb = X^T du,  dv = beta dvb
+//   dk  = dA^T (k beta) + beta (dA k) + beta e^g dkbg          (summed over the value heads of a group)
+//   dbeta = (dA k).k + e^g dkbg.k + dvb.v
+//   dg  = beta e^g dkbg.k + rowsum(W) - colsum(W),  W = dA * (beta_i k_i.k_j)
+// wy_mode 0 runs everything, 1 stops after dA, 2 reads dA (transposed) instead of computing it.
+constexpr uint32_t wyOffX = 0, wyOffK = 8192, wyOffV = 24576, wyOffDW = 40960, wyOffDU = 57344, wyOffR = 73728;
+// region R (80 KB): first (k beta e^g) hi, lo and (v beta) hi, lo (16 KB each); once the first products are done it is
+// reused for P (hi, lo), X^T-side P5 (hi, lo), dA (hi, lo), beta dA (hi, lo) (8 KB each) and the fp32 W tile
+constexpr uint32_t wyOffKbg = wyOffR, wyOffKbgl = wyOffR + 16384, wyOffVb = wyOffR + 32768, wyOffVbl = wyOffR + 49152;
+constexpr uint32_t wyOffP = wyOffR, wyOffPl = wyOffR + 8192, wyOffP5 = wyOffR + 16384, wyOffP5l = wyOffR + 24576,
+                   wyOffM = wyOffR + 32768, wyOffMl = wyOffR + 40960, wyOffMb = wyOffR + 49152, wyOffMbl = wyOffR + 57344,
+                   wyOffW = wyOffR + 65536;
+constexpr uint32_t kWySmem = wyOffR + 65536 + 16896;
+__global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_x,
+                                                           const __grid_constant__ CUtensorMap tm_k,
+                                                           const __grid_constant__ CUtensorMap tm_v,
+                                                           const __grid_constant__ CUtensorMap tm_dw,
+                                                           const __grid_constant__ CUtensorMap tm_du) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  __shared__ float gam_s[kC], beta_s[kC];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar, load_bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int b = p.cu_seqlens ? 0 : n;
+  const int t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int G = p.H / p.HK, hk = hv / G;
+  const uint32_t sb = smem_u32(smem);
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    mbar_init(&load_bar, 1);
+    mbar_init_fence();
+    mbar_arrive_expect_tx(&load_bar, 8192 + 4 * 16384);
+    tma_load_tile4(sb + wyOffX, &tm_x, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wyOffK, &tm_k, 0, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + wyOffK + 8192, &tm_k, 64, t0, hk, b, &load_bar);
+    tma_load_tile4(sb + wyOffV, &tm_v, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wyOffV + 8192, &tm_v, 64, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wyOffDW, &tm_dw, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wyOffDW + 8192, &tm_dw, 64, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wyOffDU, &tm_du, 0, t0, hv, b, &load_bar);
+    tma_load_tile4(sb + wyOffDU + 8192, &tm_du, 64, t0, hv, b, &load_bar);
+  }
+  if (tid < kC) {
+    gam_s[tid] = ld_any(p.g.p, row_off(p.g, b, hv, t0 + min(tid, rows - 1)), p.g.dtype);
+    beta_s[tid] = tid < rows ? ld_any(p.beta.p, row_off(p.beta, b, hv, t0 + tid), p.beta.dtype) : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  constexpr uint32_t cP = 0, cS = 64, cKbg = 128, cVb = 256, cT2 = 384;   // cVb is reused for dA k
+  bool ok = mbar_wait(&load_bar, 0, p.status, FLA_ERR_TIMEOUT);
+  // rows >= rows of every tile are zeroed in place (they hold the next sequence's rows or zeros), X also in its columns
+  for (int idx = tid; idx < kC * 72; idx += 128) {
+    const int r = idx / 72, ch = idx % 72;
+    if (r < rows && (ch >= 8 || ch * 8 + 8 <= rows)) continue;
+    uint8_t* base = ch < 8 ? smem + wyOffX + panel_chunk_off(r, ch)
+                           : smem + wyOffK + ((ch - 8) >> 4) * 16384 + (((ch - 8) >> 3) & 1) * 8192 + panel_chunk_off(r, (ch - 8) & 7);
+    if (r >= rows) {
+      *reinterpret_cast<uint4*>(base) = make_uint4(0, 0, 0, 0);
+    } else {   // a chunk of X that straddles the end of a short chunk
+      uint16_t* e = reinterpret_cast<uint16_t*>(base);
+      for (int j = 0; j < 8; ++j)
+        if (ch * 8 + j >= rows) e[j] = 0;
+    }
+  }
+  __syncthreads();
+  // (k beta e^g) and (v beta) as value + residual
+  for (int idx = tid; idx < 2 * kC * 16; idx += 128) {
+    const int isv = idx >> 10, r = (idx >> 4) & 63, ch = idx & 15;
+    const uint32_t off = (ch >> 3) * 8192 + panel_chunk_off(r, ch & 7);
+    float f[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + (isv ? wyOffV : wyOffK) + off), f);
+    const float sc = isv ? beta_s[r] : beta_s[r] * __expf(gam_s[r]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= sc;
+    uint4 h4, l4;
+    split8(f, h4, l4);
+    *reinterpret_cast<uint4*>(smem + (isv ? wyOffVb : wyOffKbg) + off) = h4;
+    *reinterpret_cast<uint4*>(smem + (isv ? wyOffVbl : wyOffKbgl) + off) = l4;
+  }
+  fence_async_smem();
+  tc_fence_before();
+  ok = __syncthreads_and(ok);
+  // operands; rows 64..127 of every M = 128 A view read the memory behind the panel and are never used
+  const Operand opXb{sb + wyOffX, 8192, 0}, opXt{sb + wyOffX, 8192, 1}, opKa{sb + wyOffK, 8192, 0}, opKn{sb + wyOffK, 8192, 1},
+      opDWa{sb + wyOffDW, 8192, 0}, opDWn{sb + wyOffDW, 8192, 1}, opDUa{sb + wyOffDU, 8192, 0}, opDUn{sb + wyOffDU, 8192, 1},
+      opKbg{sb + wyOffKbg, 8192, 0}, opKbgl{sb + wyOffKbgl, 8192, 0}, opVb{sb + wyOffVb, 8192, 0}, opVbl{sb + wyOffVbl, 8192, 0},
+      opP{sb + wyOffP, 8192, 0}, opPl{sb + wyOffPl, 8192, 0}, opP5{sb + wyOffP5, 8192, 1}, opP5l{sb + wyOffP5l, 8192, 1},
+      opM{sb + wyOffM, 8192, 0}, opMl{sb + wyOffMl, 8192, 0}, opMbt{sb + wyOffMb, 8192, 1}, opMblt{sb + wyOffMbl, 8192, 1};
+  uint32_t mphase = 0;
+  const int i = tid & 63;
+  const bool live = i < rows;
+  float m_row[64];   // my row of dA (row = later token)
+  if (ok) {
+    if (tid == 0) {
+      tc_fence_after();
+      if (p.wy_mode != 2) {
+        mma_tile(tbase + cP, opDWa, opKbg, 128, 64, 8, false);
+        mma_tile(tbase + cP, opDWa, opKbgl, 128, 64, 8, true);
+        mma_tile(tbase + cP, opDUa, opVb, 128, 64, 8, true);
+        mma_tile(tbase + cP, opDUa, opVbl, 128, 64, 8, true);
+      }
+      if (p.wy_mode != 1) {
+        mma_tile(tbase + cS, opKa, opKa, 128, 64, 8, false);        // k k^T
+        mma_tile(tbase + cKbg, opXt, opDWn, 128, 128, 4, false);    // X^T dw
+        mma_tile(tbase + cVb, opXt, opDUn, 128, 128, 4, false);     // X^T du
+      }
+      mma_commit(&mma_bar);
+    }
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    mphase ^= 1;
+    tc_fence_after();
+    ok = __syncthreads_and(ok);
+  }
+  if (ok && p.wy_mode != 2) {
+    if (warp < 2) {
+      float r[64];
+      tmem_ld_row64(trow + cP, r);
+#pragma unroll
+      for (int j = 0; j < 64; ++j) r[j] = (live && j < i) ? r[j] : 0.f;
+      row64_to_hilo(smem + wyOffP, smem + wyOffPl, i, r);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase + cP, opP, opXb, 128, 64, 4, false);    // P X^T
+      mma_tile(tbase + cP, opPl, opXb, 128, 64, 4, true);
+      mma_commit(&mma_bar);
+    }
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    mphase ^= 1;
+    tc_fence_after();
+    if (warp < 2) {
+      float r[64];
+      tmem_ld_row64(trow + cP, r);
+      row64_to_hilo(smem + wyOffP5, smem + wyOffP5l, i, r);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (ok) {
+      if (tid == 0) {
+        tc_fence_after();
+        mma_tile(tbase + cP, opXt, opP5, 128, 64, 4, false);   // X^T (P X^T)
+        mma_tile(tbase + cP, opXt, opP5l, 128, 64, 4, true);
+        mma_commit(&mma_bar);
+      }
+      ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+      mphase ^= 1;
+      tc_fence_after();
+      if (warp < 2) {
+        tmem_ld_row64(trow + cP, m_row);
+        const float gi = gam_s[i];
+#pragma unroll
+        for (int j = 0; j < 64; ++j) m_row[j] = (live && j < i) ? -m_row[j] * __expf(gi - gam_s[j]) : 0.f;
+        if (p.wy_mode == 1) {   // dA is stored transposed: element (j, i) of the chunk's block (zero on and above the diagonal)
+          for (int j = 0; j < rows; ++j) st_any(const_cast<void*>(p.o0.p), row_off(p.o0, b, hv, t0 + j) + i, p.o0.dtype, m_row[j]);
+        }
+      }
+      ok = __syncthreads_and(ok);
+    }
+  } else if (ok && warp < 2) {
+    // the given dA is stored transposed: my row i of dA is column i of the chunk's block
+#pragma unroll 8
+    for (int j = 0; j < 64; ++j)
+      m_row[j] = (live && j < i) ? ld_any(p.a.p, row_off(p.a, b, hv, t0 + j) + i, p.a.dtype) : 0.f;
+  }
+  if (ok && p.wy_mode != 1) {
+    float* wt = reinterpret_cast<float*>(smem + wyOffW);
+    float dbeta = 0.f, row_w = 0.f;
+    const float bi = beta_s[i], egi = __expf(gam_s[i]);
+    if (warp < 2) {
+      row64_to_hilo(smem + wyOffM, smem + wyOffMl, i, m_row);
+      float s[64];
+      tmem_ld_row64(trow + cS, s);
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        m_row[j] *= bi;
+        const float w = m_row[j] * s[j];
+        row_w += w;
+        wt[i * kColTile + j] = w;
+      }
+      row64_to_hilo(smem + wyOffMb, smem + wyOffMbl, i, m_row);
+      // dv = beta (X^T du) and its part of dbeta; this frees the accumulator for dA k
+      bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o1.p)) + row_off(p.o1, b, hv, t0 + i);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float r[64];
+        tmem_ld_row64(trow + cVb + half * 64, r);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float vv[8];
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + wyOffV + half * 8192 + panel_chunk_off(i, ch)), vv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            dbeta += r[ch * 8 + j] * vv[j];
+            r[ch * 8 + j] *= bi;
+          }
+        }
+        if (live) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      mma_tile(tbase + cVb, opM, opKn, 128, 128, 4, false);      // dA k
+      mma_tile(tbase + cVb, opMl, opKn, 128, 128, 4, true);
+      mma_tile(tbase + cT2, opMbt, opKn, 128, 128, 4, false);    // (beta dA)^T k = dA^T (k beta)
+      mma_tile(tbase + cT2, opMblt, opKn, 128, 128, 4, true);
+      mma_commit(&mma_bar);
+    }
+    float col_w = 0.f;
+    if (warp < 2) {
+#pragma unroll 8
+      for (int r = 0; r < kC; ++r) col_w += wt[r * kColTile + i];
+    }
+    ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
+    mphase ^= 1;
+    tc_fence_after();
+    if (warp < 2 && ok) {
+      float kdk = 0.f, kdkbg = 0.f;
+      const float f2 = bi * egi;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float t1[64], acc[64];
+        tmem_ld_row64(trow + cVb + half * 64, t1);
+        tmem_ld_row64(trow + cT2 + half * 64, acc);
+        float kb[64];
+        tmem_ld_row64(trow + cKbg + half * 64, kb);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float kv[8];
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + wyOffK + half * 8192 + panel_chunk_off(i, ch)), kv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int q = ch * 8 + j;
+            kdk += t1[q] * kv[j];
+            kdkbg += kb[q] * kv[j];
+            acc[q] += bi * t1[q] + f2 * kb[q];
+          }
+        }
+        if (live) {
+          if (p.ws_dq) {
+            float* dst = p.ws_dq + ((int64_t(b) * p.H + hv) * p.T + (t0 + i)) * kK + half * 64;
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          } else {
+            bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o0.p)) + row_off(p.o0, b, hk, t0 + i) + half * 64;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(acc + ch * 8);
+          }
+        }
+      }
+      if (live) {
+        st_any(const_cast<void*>(p.o2.p), row_off(p.o2, b, hv, t0 + i), p.o2.dtype, dbeta + kdk + egi * kdkbg);
+        st_any(const_cast<void*>(p.o3.p), row_off(p.o3, b, hv, t0 + i), p.o3.dtype, f2 * kdkbg + row_w - col_w);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
 }  // namespace fla
@@ -1649,7 +1935,86 @@ extern "C" FLA_API int fla_b200_chunk_bwd_dqkwg(const fla_chunk_stage_args* a, v
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   if (scratch) {
     KernelTimer kt("chunk_bwd_dqkwg_group_sum", cs);
-    stage_group_sum_kernel<<<148 * 8, 256, 0, cs>>>(p, int(gm.B));
+    stage_group_sum_kernel<<<148 * 8, 256, 0, cs>>>(p, int(gm.B), 2);
   }
   return cuda_status(cudaGetLastError());
 }
+
+static uint64_t wy_scratch_bytes(const fla_chunk_stage_args* a) {
+  const fla_tensor_t &k = a->k, &v = a->v;
+  if (k.ndim != 4 || v.ndim != 4 || k.shape[1] <= 0 || v.shape[1] == k.shape[1]) return 0;
+  return uint64_t(v.shape[0]) * v.shape[1] * v.shape[2] * kK * sizeof(float);
+}
+
+static int wy_bwd_launch(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes, void* stream, int mode) {
+  if (!a) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  StageParams p{};
+  Geometry gm;
+  int st;
+  const fla_tensor_t &dw = a->w, &du = a->u, &dA = a->q;
+  if (a->v.ndim != 4) return FLA_ERR_SHAPE;
+  if ((st = geometry(a, a->v, &gm, &p))) return st;
+  StageView tmp;
+  if ((st = make_view(a->k, 4, true, &tmp)) || (st = make_view(a->v, 4, true, &tmp)) || (st = make_view(a->A, 4, true, &tmp)) ||
+      (st = make_view(dw, 4, true, &tmp)) || (st = make_view(du, 4, true, &tmp)) || (st = make_view(a->g, 3, false, &p.g)) ||
+      (st = make_view(a->beta, 3, false, &p.beta)))
+    return st;
+  const int64_t HK = a->k.shape[1];
+  for (const fla_tensor_t* t : {&a->k, &a->v, &a->A, &dw, &du})
+    if (t->dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if (HK <= 0 || gm.H % HK || a->k.shape[0] != gm.B || a->k.shape[2] != gm.T || a->k.shape[3] != kK || a->v.shape[3] != kV) return FLA_ERR_SHAPE;
+  if (!same_bht(a->A, gm, gm.H) || a->A.shape[3] != kC || !same_bht(dw, gm, gm.H) || dw.shape[3] != kK || !same_bht(du, gm, gm.H) ||
+      du.shape[3] != kV || !same_bht(a->g, gm, gm.H) || !same_bht(a->beta, gm, gm.H))
+    return FLA_ERR_SHAPE;
+  uint64_t scratch = 0;
+  if (mode == 1) {
+    if ((st = make_view(a->out0, 4, false, &p.o0))) return st;
+    if (!same_bht(a->out0, gm, gm.H) || a->out0.shape[3] != kC) return FLA_ERR_SHAPE;
+  } else {
+    if ((st = make_view(a->out0, 4, true, &p.o0)) || (st = make_view(a->out1, 4, true, &p.o1)) || (st = make_view(a->out2, 3, false, &p.o2)) ||
+        (st = make_view(a->out3, 3, false, &p.o3)))
+      return st;
+    if (a->out0.dtype != FLA_BF16 || a->out1.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+    if (a->out0.shape[0] != gm.B || a->out0.shape[1] != HK || a->out0.shape[2] != gm.T || a->out0.shape[3] != kK) return FLA_ERR_SHAPE;
+    if (!same_bht(a->out1, gm, gm.H) || a->out1.shape[3] != kV || !same_bht(a->out2, gm, gm.H) || !same_bht(a->out3, gm, gm.H)) return FLA_ERR_SHAPE;
+    if (mode == 2) {
+      if ((st = make_view(dA, 4, false, &p.a))) return st;
+      if (!same_bht(dA, gm, gm.H) || dA.shape[3] != kC) return FLA_ERR_SHAPE;
+    }
+    scratch = wy_scratch_bytes(a);
+  }
+  p.HK = int(HK);
+  p.wy_mode = mode;
+  if (!workspace || workspace_bytes < 256 + scratch) return FLA_ERR_WORKSPACE;
+  if ((st = prepare_status(workspace, workspace_bytes, cs, &p))) return st;
+  if (scratch) p.ws_dq = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+  if ((st = opt_in_smem(stage_wy_bwd_kernel, kWySmem + 1024))) return st;
+  CUtensorMap tm_x, tm_k, tm_v, tm_dw, tm_du;
+  if (token_tile_map(a->A, &tm_x) || token_tile_map(a->k, &tm_k) || token_tile_map(a->v, &tm_v) || token_tile_map(dw, &tm_dw) ||
+      token_tile_map(du, &tm_du))
+    return FLA_ERR_CUDA;
+  {
+    KernelTimer kt("prepare_wy_repr_bwd", cs);
+    stage_wy_bwd_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kWySmem + 1024, cs>>>(p, tm_x, tm_k, tm_v, tm_dw, tm_du);
+  }
+  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  if (scratch) {
+    KernelTimer kt("prepare_wy_repr_bwd_group_sum", cs);
+    stage_group_sum_kernel<<<148 * 8, 256, 0, cs>>>(p, int(gm.B), 1);
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+#define FLA_WY_ENTRY(op, mode)                                                                                              \
+  extern "C" FLA_API int fla_b200_##op##_workspace_size(const fla_chunk_stage_args* a, uint64_t* bytes) {                    \
+    if (!a || !bytes) return FLA_ERR_NULL;                                                                                  \
+    *bytes = 256 + ((mode) == 1 ? 0 : wy_scratch_bytes(a));                                                                 \
+    return FLA_OK;                                                                                                          \
+  }                                                                                                                         \
+  extern "C" FLA_API int fla_b200_##op(const fla_chunk_stage_args* a, void* workspace, uint64_t workspace_bytes, void* stream) { \
+    return wy_bwd_launch(a, workspace, workspace_bytes, stream, mode);                                                      \
+  }
+FLA_WY_ENTRY(prepare_wy_repr_bwd, 0)
+FLA_WY_ENTRY(prepare_wy_repr_bwd_da, 1)
+FLA_WY_ENTRY(prepare_wy_repr_bwd_full, 2)

@@ -243,6 +243,43 @@ def chunk_bwd_dqkwg(q, k, v, g, h, dox, dh, dv, chunk_size, *, cu_seqlens=None, 
     return dq, dk, dw, dg
 
 
+def _wy_outputs(k, v, beta, g):
+    return torch.empty_like(k), torch.empty_like(v), torch.empty_like(beta), torch.empty_like(g)
+
+
+def prepare_wy_repr_bwd(k, v, beta, A, dw, du, g, chunk_size, *, cu_seqlens=None, chunk_indices=None):
+    """Backward of `w = A (k beta e^g)`, `u = A (v beta)` (A = the chunk inverses) from dw, du in one launch.
+    k `[B,HK,T,K]`; v, du `[B,HV,T,V]`; dw `[B,HV,T,K]`; A `[B,HV,T,C]`; beta, g `[B,HV,T]`.
+    Returns (dk `[B,HK,T,K]` summed over each group's value heads, dv, dbeta, dg)."""
+    del chunk_indices
+    dk, dv, dbeta, dg = _wy_outputs(k, v, beta, g)
+    _stage_call("prepare_wy_repr_bwd", dict(k=k, v=v, beta=beta, A=A, w=dw, u=du, g=g, out0=dk, out1=dv, out2=dbeta, out3=dg),
+                [k, v, beta, A, dw, du, g, dk, dv, dbeta, dg], v, cu_seqlens, chunk_size)
+    return dk, dv, dbeta, dg
+
+
+def prepare_wy_repr_bwd_da(k, v, beta, A, dw, du, g, *, chunk_size, cu_seqlens=None, chunk_indices=None):
+    """Gradient of the chunk's strictly-lower score block, stored transposed within each chunk like the reference:
+    `dA^T = strict_lower(-(A^T strict_lower(dw (k beta e^g)^T + du (v beta)^T) A^T) * e^{g_i - g_j})`.  `[B,HV,T,C]`, A's dtype."""
+    del chunk_indices
+    dA = torch.empty_like(A)
+    _stage_call("prepare_wy_repr_bwd_da", dict(k=k, v=v, beta=beta, A=A, w=dw, u=du, g=g, out0=dA), [k, v, beta, A, dw, du, g, dA], v,
+                cu_seqlens, chunk_size)
+    return dA
+
+
+def prepare_wy_repr_bwd_full(k, v, beta, A, dA, dw, du, g, chunk_size, *, cu_seqlens=None, chunk_indices=None):
+    """dk, dv, dbeta, dg of the WY representation from dw, du and the dA of `prepare_wy_repr_bwd_da`."""
+    del chunk_indices
+    dk, dv, dbeta, dg = _wy_outputs(k, v, beta, g)
+    _stage_call("prepare_wy_repr_bwd_full", dict(k=k, v=v, beta=beta, A=A, q=dA, w=dw, u=du, g=g, out0=dk, out1=dv, out2=dbeta, out3=dg),
+                [k, v, beta, A, dA, dw, du, g, dk, dv, dbeta, dg], v, cu_seqlens, chunk_size)
+    return dk, dv, dbeta, dg
+
+
+npu_prepare_wy_repr_bwd = prepare_wy_repr_bwd
+npu_prepare_wy_repr_bwd_da = prepare_wy_repr_bwd_da
+npu_prepare_wy_repr_bwd_full = prepare_wy_repr_bwd_full
 npu_chunk_bwd_dqkwg = chunk_bwd_dqkwg
 npu_kda_gate_cumsum = kda_gate_cumsum
 npu_chunk_bwd_dv_local = chunk_bwd_dv_local

@@ -374,6 +374,16 @@ FLA_API int fla_b200_l2norm_bwd(const fla_l2norm_args* args, void* stream);
  *     -> out0 = dq, out1 = dk [B,HK,T,128] bf16 (summed over the value heads of a group), out2 = dw [B,HV,T,128] bf16
  *        (optional), out3 = dg [B,HV,T] (before the reverse cumulative sum, the chunk's last row carrying the state terms).
  *     Workspace: 256 bytes, plus 2 * B*HV*T*128 fp32 when HV > HK (fla_b200_chunk_bwd_dqkwg_workspace_size).
+ * fla_b200_prepare_wy_repr_bwd_da   (aclnnPrepareWyReprBwdDa, :430-460; golden test_npu_prepare_wy_repr_bwd_da.py:166-291)
+ *     k [B,HK,T,128], v [B,HV,T,128], A (the inverse) [B,HV,T,64], w = dw, u = du [B,HV,T,128] bf16, beta, g [B,HV,T]
+ *     -> out0 = dA [B,HV,T,64] (any float dtype), stored transposed within each chunk:
+ *        dA^T = strict_lower(-(A^T strict_lower(dw (k beta e^g)^T + du (v beta)^T) A^T) * e^{g_i - g_j}).
+ * fla_b200_prepare_wy_repr_bwd_full (aclnnPrepareWyReprBwdFull, :242-281; goldens test_npu_prepare_wy_repr_bwd_full.py:47-428)
+ *     the same inputs plus q = dA (as produced above)
+ *     -> out0 = dk [B,HK,T,128] bf16 (summed over the value heads of a group), out1 = dv [B,HV,T,128] bf16,
+ *        out2 = dbeta, out3 = dg [B,HV,T].
+ * fla_b200_prepare_wy_repr_bwd      (aclnnPrepareWyReprBwd, :284-321): both steps in one launch, dA never leaves the chip.
+ *     Workspace of the last two: 256 bytes, plus B*HV*T*128 fp32 when HV > HK.
  * Workspace of the others: 256 bytes (status word of the bounded device-side waits). */
 typedef struct fla_chunk_stage_args {
   fla_tensor_t q, k, v, w, u, g, beta, A, h, initial_state;
@@ -402,6 +412,12 @@ FLA_API int fla_b200_chunk_gated_delta_rule_fwd_h(const fla_chunk_stage_args* ar
 FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
 FLA_API int fla_b200_chunk_bwd_dv_local_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
 FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_prepare_wy_repr_bwd_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_prepare_wy_repr_bwd(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_prepare_wy_repr_bwd_da_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_prepare_wy_repr_bwd_da(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+FLA_API int fla_b200_prepare_wy_repr_bwd_full_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
+FLA_API int fla_b200_prepare_wy_repr_bwd_full(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
 FLA_API int fla_b200_chunk_bwd_dqkwg_workspace_size(const fla_chunk_stage_args* args, uint64_t* bytes);
 FLA_API int fla_b200_chunk_bwd_dqkwg(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
 FLA_API int fla_b200_chunk_bwd_dv_local(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes, void* stream);

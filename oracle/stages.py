@@ -12,6 +12,8 @@ CPU restatements of the reference's per-operator goldens, on head-first `[B,H,T,
   bwd_dhu               torch_custom/fla_npu/test/test_bwd_dhu.py:61-290 ("fp64" mode), extended with the cotangent of the
                         final state (the reference deletes `dht`) and a `[N,HV,K,V]` dh0
   dqkwg                 tests/atk/chunk_bwd_dqkwg/scripts/chunk_bwd_dqkwg_cpu.py:66-409 (benchmark = fp64 mode)
+  wy bwd (dA)           torch_custom/fla_npu/test/test_npu_prepare_wy_repr_bwd_da.py:165-291
+  wy bwd (dk,dv,dg,db)  torch_custom/fla_npu/test/test_npu_prepare_wy_repr_bwd_full.py:95-486 (the *_high_precision goldens)
 Pinned by tests/golden/stages_golden.npz, which tests/golden/make_golden.py produces by running those reference
 functions themselves.
 """
@@ -221,3 +223,42 @@ def chunk_bwd_dqkwg_ref(q, k, v, g, h, d_o, dh, dv, scale, chunk_size, cu_seqlen
         dq[:, :, s:e] = dq_state + ds @ kk[:, :, s:e]
         dk[:, :, s:e] = dk_state + ds.transpose(-1, -2) @ qq[:, :, s:e]
     return dq.view(B, HK, G, T, K).sum(2), dk.view(B, HK, G, T, K).sum(2), dw, dg
+
+
+def prepare_wy_repr_bwd_ref(k, v, beta, A, dw, du, g, chunk_size, cu_seqlens=None, dA=None):
+    """Backward of w = A (k beta e^g), u = A (v beta) in fp64.  Returns (dA stored transposed per chunk [B,HV,T,C],
+    dk [B,HK,T,K] summed over groups, dv, dbeta, dg).  With `dA` given (transposed storage) it is used instead of the computed one."""
+    B, HV, T, V = v.shape
+    HK, K = k.shape[1], k.shape[3]
+    G = HV // HK
+    kk = k.double().repeat_interleave(G, dim=1)
+    v, beta, A, dw, du, g = (t.double() for t in (v, beta, A, dw, du, g))
+    dA_out = torch.zeros(B, HV, T, chunk_size, dtype=torch.float64)
+    dk = torch.zeros(B, HV, T, K, dtype=torch.float64)
+    dv = torch.zeros(B, HV, T, V, dtype=torch.float64)
+    dbeta = torch.zeros(B, HV, T, dtype=torch.float64)
+    dg = torch.zeros(B, HV, T, dtype=torch.float64)
+    for s, e in chunk_ranges(T, chunk_size, cu_seqlens):
+        n = e - s
+        X = A[:, :, s:e, :n]
+        kc, vc, bc, gc = kk[:, :, s:e], v[:, :, s:e], beta[:, :, s:e], g[:, :, s:e]
+        eg = torch.exp(gc)
+        kbg = kc * (bc * eg)[..., None]
+        vb = vc * bc[..., None]
+        if dA is None:
+            P = torch.tril(dw[:, :, s:e] @ kbg.transpose(-1, -2) + du[:, :, s:e] @ vb.transpose(-1, -2), diagonal=-1)
+            P6 = X.transpose(-1, -2) @ (P @ X.transpose(-1, -2))
+            M = torch.tril(-P6 * torch.exp(gc[..., :, None] - gc[..., None, :]), diagonal=-1)
+        else:
+            M = torch.tril(dA.double()[:, :, s:e, :n].transpose(-1, -2), diagonal=-1)
+        dA_out[:, :, s:e, :n] = M.transpose(-1, -2)
+        dkbg = X.transpose(-1, -2) @ dw[:, :, s:e]
+        dvb = X.transpose(-1, -2) @ du[:, :, s:e]
+        dv[:, :, s:e] = dvb * bc[..., None]
+        T1 = M @ kc
+        dk[:, :, s:e] = M.transpose(-1, -2) @ (kc * bc[..., None]) + T1 * bc[..., None] + dkbg * (bc * eg)[..., None]
+        kd = (dkbg * kc).sum(-1)
+        dbeta[:, :, s:e] = (T1 * kc).sum(-1) + eg * kd + (dvb * vc).sum(-1)
+        W = M * (kc @ kc.transpose(-1, -2)) * bc[..., None]
+        dg[:, :, s:e] = bc * eg * kd + W.sum(-1) - W.sum(-2)
+    return dA_out, dk.view(B, HK, G, T, K).sum(2), dv, dbeta, dg

@@ -170,6 +170,10 @@ def stages_fixture():
                                                       "chunk_gated_delta_rule_bwd_dhu_cpu"],
                       extra={"_LN2": math.log(2.0)})["chunk_gated_delta_rule_bwd_dhu_cpu"]
     dqkwg_ref = extract(REF / "tests/atk/chunk_bwd_dqkwg/scripts/chunk_bwd_dqkwg_cpu.py", ["chunk_bwd_dqkwg_cpu"])["chunk_bwd_dqkwg_cpu"]
+    da_ref = extract(test_dir / "test_npu_prepare_wy_repr_bwd_da.py", ["get_bos_eos", "compute_dA_cpu"])["compute_dA_cpu"]
+    full_ns = extract(test_dir / "test_npu_prepare_wy_repr_bwd_full.py",
+                      ["get_bos_eos", "_hv_to_hk", "compute_dv_golden_high_precision", "compute_dk_golden_high_precision",
+                       "compute_dg_golden_high_precision", "compute_dbeta_golden_high_precision"])
     torch.Tensor.npu = lambda self: self   # the golden moves its CPU tensors "to the device" before computing
 
     C, K, V, HK, HV, T = 64, 128, 128, 1, 2, 160
@@ -225,6 +229,16 @@ def stages_fixture():
         dq_, dk_, dw_, dg_ = dqkwg_ref(sf(q), sf(k), sf(vnb), sf(d_o), sf(hb), sf(dhb), torch.zeros(1), sf(gam), sf(dv2b), K ** -0.5,
                                        cu_t, C, benchmark=True)
         out.update({f"{tag}_dq": f32(sf(dq_)), f"{tag}_dk": f32(sf(dk_)), f"{tag}_dw": f32(sf(dw_)), f"{tag}_dg": f32(sf(dg_))})
+        # backward of the WY representation from dw (of dqkwg) and du (= dv2), through the reference's fp32-input goldens
+        dwb, dub = bf(dw_.float().transpose(1, 2)), dv2b
+        k_hv = k.repeat_interleave(HV // HK, dim=1)
+        dA_ = da_ref(Xb, dwb, gam, beta, k_hv, v, dub, idx, cu, 1, HV, T, K, C, NT)
+        wy_dv = full_ns["compute_dv_golden_high_precision"](Xb, dub, beta, cu, idx, 1, HV, T, V, C, NT)
+        wy_dk = full_ns["compute_dk_golden_high_precision"](Xb, dwb, gam, beta, dA_, k, cu, idx, 1, HK, HV, T, K, C, NT)
+        wy_dg = full_ns["compute_dg_golden_high_precision"](Xb, dwb, gam, beta, dA_, k, cu, idx, 1, HK, HV, T, K, C, NT)
+        wy_db = full_ns["compute_dbeta_golden_high_precision"](Xb, dwb, gam, beta, dA_, k, v, dub, cu, idx, 1, HK, HV, T, K, C, NT)
+        out.update({f"{tag}_wy_dA": f32(dA_), f"{tag}_wy_dv": f32(wy_dv), f"{tag}_wy_dk": f32(wy_dk), f"{tag}_wy_dg": f32(wy_dg),
+                    f"{tag}_wy_dbeta": f32(wy_db)})
         out.update({f"{tag}_dv_local": f32(dv_loc), f"{tag}_dh": f32(dh), f"{tag}_dh0": f32(dh0[0, :, first].transpose(0, 1)),
                     f"{tag}_dv2": f32(dv2)})
         out.update({f"{tag}_gam": f32(gam), f"{tag}_rev": f32(rev), f"{tag}_A": f32(A), f"{tag}_X": f32(X), f"{tag}_w": f32(w),

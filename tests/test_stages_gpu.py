@@ -49,6 +49,7 @@ def _case(B, T, HK, HV, seed, cu=None):
                                                            cu_seqlens=cu)
     d["dq"], d["dk"], d["dw"], d["dg"] = stages.chunk_bwd_dqkwg_ref(q, k, _bf(d["v_new"]), d["gam"], _bf(d["h"]), d["d_o"], _bf(d["dh"]),
                                                                     _bf(d["dv2"]), 128 ** -0.5, C, cu)
+    d["wy"] = stages.prepare_wy_repr_bwd_ref(k, v, beta, Xb, _bf(d["dw"]), _bf(d["dv2"]), d["gam"], C, cu)
     return d
 
 
@@ -196,6 +197,35 @@ def test_chunk_bwd_dqkwg(case):
     assert_close("dg", dg, d["dg"], TOL)
 
 
+def _wy_args(d):
+    return (d["k"].cuda(), d["v"].cuda(), d["beta"].cuda(), _bf(d["X"]).cuda())
+
+
+def test_prepare_wy_repr_bwd_fused_and_split(case):
+    from fla_b200.ops import prepare_wy_repr_bwd, prepare_wy_repr_bwd_da, prepare_wy_repr_bwd_full
+    d, cu = case
+    dA_ref, dk_ref, dv_ref, db_ref, dg_ref = d["wy"]
+    k, v, beta, X = _wy_args(d)
+    dw, du, g = _bf(d["dw"]).cuda(), _bf(d["dv2"]).cuda(), d["gam"].cuda()
+    dk, dv, dbeta, dg = prepare_wy_repr_bwd(k, v, beta, X, dw, du, g, C, cu_seqlens=cu)
+    assert_close("dk", dk, dk_ref, TOL, stored_bf16=True)
+    assert_close("dv", dv, dv_ref, TOL, stored_bf16=True)
+    assert_close("dbeta", dbeta, db_ref, TOL, stored_bf16=True)
+    assert_close("dg", dg, dg_ref, TOL)
+    # the two-step form: dA, then the rest from a given (bf16-rounded) dA
+    X32 = _bf(d["X"]).cuda()
+    dA = prepare_wy_repr_bwd_da(k, v, beta, X32, dw, du, g, chunk_size=C, cu_seqlens=cu)
+    assert dA.dtype == X32.dtype
+    assert_close("dA", dA, dA_ref, TOL, stored_bf16=True)
+    dk2, dv2, db2, dg2 = prepare_wy_repr_bwd_full(k, v, beta, X, _bf(dA_ref).cuda(), dw, du, g, C, cu_seqlens=cu)
+    ref2 = stages.prepare_wy_repr_bwd_ref(d["k"], d["v"], d["beta"], _bf(d["X"]), _bf(d["dw"]), _bf(d["dv2"]), d["gam"], C, cu,
+                                          dA=_bf(dA_ref))
+    assert_close("dk (from dA)", dk2, ref2[1], TOL, stored_bf16=True)
+    assert_close("dv (from dA)", dv2, ref2[2], TOL, stored_bf16=True)
+    assert_close("dbeta (from dA)", db2, ref2[3], TOL, stored_bf16=True)
+    assert_close("dg (from dA)", dg2, ref2[4], TOL)
+
+
 def test_stage_chain_matches_fused_operator():
     """Running the six stages one after the other gives the fused operator's output (and the oracle's)."""
     from fla_b200 import ops
@@ -219,6 +249,37 @@ def test_stage_chain_matches_fused_operator():
         assert torch.allclose(got, want, rtol=5e-3, atol=5e-3), f"{name}: max abs err {(got - want).abs().max().item():.3e}"
         cos = torch.nn.functional.cosine_similarity(got.flatten().double(), want.flatten().double(), dim=0).item()
         assert cos >= 0.999, f"{name}: cosine {cos}"
+
+
+def test_backward_stage_chain_matches_autograd_oracle():
+    """The reference's backward chain (examples/flash_gated_delta_rule.py:884-1023) run operator by operator:
+    w,u -> fwd_h -> dv_local -> bwd_dhu -> dqkwg -> prepare_wy_repr_bwd, dk and dg summed, dg reverse-cumsummed;
+    checked with the reference's end-to-end pass rule (:1738-1761,1894-1901) against autograd through the recurrence."""
+    from fla_b200 import ops
+    inp = oracle.make_gdn_inputs(B=2, T=192, HK=2, HV=4, K=128, V=128, seed=13, dtype=torch.bfloat16)
+    q, k, v, g, beta, h0, do = (inp[n].cuda() for n in ("q", "k", "v", "g", "beta", "h0", "do"))
+    hf = lambda t: t.transpose(1, 2)  # noqa: E731
+    scale = 128 ** -0.5
+    gam = ops.chunk_local_cumsum(g.float(), C, head_first=False)
+    A = ops.chunk_scaled_dot_kkt(hf(k), hf(gam), hf(beta))
+    X = ops.solve_tri(A, layout="bnsd", output_dtype=torch.bfloat16)
+    w, u = ops.recompute_w_u_fwd(hf(k), hf(v), hf(beta), X, C, g=hf(gam))
+    h, v_new, _ = ops.chunk_gated_delta_rule_fwd_h(hf(k), w, u, hf(gam), initial_state=h0)
+    dv = ops.chunk_bwd_dv_local(hf(q), hf(k), hf(do), hf(gam), scale, C)
+    dh, dh0, dv2 = ops.chunk_gated_delta_rule_bwd_dhu(hf(q), hf(k), w, hf(do), dv, scale, C, g=hf(gam), h0=h0)
+    dq, dk, dw, dg = ops.chunk_bwd_dqkwg(hf(q), hf(k), v_new, hf(gam), h, hf(do), dh, dv2, C, w=w, scale=scale)
+    dk2, dv_f, dbeta, dg2 = ops.prepare_wy_repr_bwd(hf(k), hf(v), hf(beta), X, dw, dv2, hf(gam), C)
+    dk = dk.float() + dk2.float()
+    dg = ops.chunk_local_cumsum((dg.float() + dg2.float()).contiguous(), C, reverse=True)
+    ref = oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"], do=inp["do"])
+    checks = (("dq", hf(dq), ref["dq"], 8e-3, 0.999), ("dk", hf(dk), ref["dk"], 8e-3, 0.999), ("dv", hf(dv_f), ref["dv"], 8e-3, 0.999),
+              ("dbeta", hf(dbeta), ref["dbeta"], 2e-2, 0.99), ("dg", hf(dg), ref["dg"], 2e-2, 0.99), ("dh0", dh0, ref["dh0"], 8e-3, 0.999))
+    for name, got, want, tol, cos_min in checks:
+        got, want = got.float().cpu(), want.float()
+        assert torch.isfinite(got).all(), name
+        assert torch.allclose(got, want, rtol=tol, atol=tol), f"{name}: max abs err {(got - want).abs().max().item():.3e}"
+        cos = torch.nn.functional.cosine_similarity(got.flatten().double(), want.flatten().double(), dim=0).item()
+        assert cos >= cos_min, f"{name}: cosine {cos}"
 
 
 def test_stage_goldens_from_the_reference():

@@ -52,6 +52,10 @@ def test_stage_oracle_matches_reference_goldens(fx, tag, cu):
                                                 bf(fx[f"{tag}_dh"]), bf(fx[f"{tag}_dv2"]), scale, C, cu)
     for name, got in (("dq", dq), ("dk", dk), ("dw", dw), ("dg", dg)):
         _close(got, fx[f"{tag}_{name}"], 2e-6)
+    dwb, dub = bf(fx[f"{tag}_dw"]), bf(fx[f"{tag}_dv2"])
+    wy = stages.prepare_wy_repr_bwd_ref(fx["k"], fx["v"], fx["beta"], Xb, dwb, dub, gam, C, cu)
+    for name, got in zip(("wy_dA", "wy_dk", "wy_dv", "wy_dbeta", "wy_dg"), wy):
+        _close(got, fx[f"{tag}_{name}"], 1e-5)     # these goldens round intermediates to the inputs' dtype (fp32 here)
 
 
 def test_stage_chain_reproduces_the_recurrence():
