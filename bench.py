@@ -353,15 +353,18 @@ def cpu_reference(wl: Workload, threads: int, steps: int = 1, warmup: int = 0):
     import oracle
     torch.set_num_threads(threads)
     c = wl.cfg
-    if wl.name in ("gdn_fwd_bwd", "gdn_fwd_conv"):
+    if wl.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "gdn_stage_fwd", "gdn_stage_fwd_bwd"):
         Ts = 1024
         inp = oracle.make_gdn_inputs(1, Ts, c["HK"], c["HV"], seed=1001)
         xs, w = torch.randn(1, c["D"], Ts), 0.5 * torch.randn(c["D"], c["W"])
         desc = f"B=1 T={Ts} HQK={c['HK']} HV={c['HV']} K=V=128 fp32 naive recurrence"
-        if wl.name == "gdn_fwd_bwd":
+        if wl.name in ("gdn_fwd_bwd", "gdn_stage_fwd_bwd"):
             fn = lambda: oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"],  # noqa: E731
                                                       initial_state=inp["h0"], do=inp["do"], dht=inp["dht"])
             desc += " + autograd"
+        elif wl.name == "gdn_stage_fwd":
+            fn = lambda: oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"],  # noqa: E731
+                                                      initial_state=inp["h0"])
         else:
             def fn():
                 oracle.causal_conv1d_ref(xs, w, None, None, False, "silu")
