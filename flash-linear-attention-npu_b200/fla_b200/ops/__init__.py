@@ -10,7 +10,7 @@ from .recurrent import fused_recurrent_gated_delta_rule, recurrent_gated_delta_r
 
 npu_recurrent_gated_delta_rule = recurrent_gated_delta_rule
 npu_recurrent_kda = recurrent_kda
-from .stages import chunk_bwd_dqkwg, npu_chunk_bwd_dqkwg  # noqa: F401,E402
+from .stages import chunk_bwd_dqkwg, chunk_kda_bwd_intra, npu_chunk_bwd_dqkwg, npu_chunk_kda_bwd_intra  # noqa: F401,E402
 from .stages import (npu_prepare_wy_repr_bwd, npu_prepare_wy_repr_bwd_da, npu_prepare_wy_repr_bwd_full,  # noqa: F401,E402
                      prepare_wy_repr_bwd, prepare_wy_repr_bwd_da, prepare_wy_repr_bwd_full)
 from .stages import (chunk_bwd_dv_local, chunk_gated_delta_rule_bwd_dhu, kda_gate_cumsum, npu_chunk_bwd_dv_local,  # noqa: F401,E402

@@ -68,3 +68,9 @@ class ChunkStageArgs(ctypes.Structure):
         ("scale", ctypes.c_float), ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32),
         ("total_chunks", ctypes.c_int32), ("reverse", ctypes.c_int32), ("gate_mode", ctypes.c_int32),
         ("lower_bound", ctypes.c_float)]
+
+
+class ChunkKdaBwdIntraArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "gk", "beta", "d_aqk", "d_akk", "dq", "dk", "db", "dg", "cu_seqlens",
+                                           "chunk_offsets")] + [
+        ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32), ("total_chunks", ctypes.c_int32)]

@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from .. import _runtime as rt
-from ._structs import ChunkStageArgs
+from ._structs import ChunkKdaBwdIntraArgs, ChunkStageArgs
 from .gdn import CHUNK, _varlen_meta
 
 _DTYPES = {"float": torch.float32, "float32": torch.float32, "half": torch.float16, "float16": torch.float16,
@@ -277,6 +277,67 @@ def prepare_wy_repr_bwd_full(k, v, beta, A, dA, dw, du, g, chunk_size, *, cu_seq
     return dk, dv, dbeta, dg
 
 
+def chunk_kda_bwd_intra(q, k, gk, beta, dAqk, dAkk, dq, dk, db, dg, *, cu_seqlens=None, chunk_indices=None, chunk_size=64,
+                        safe_gate=True, layout="BSND"):
+    """Intra-chunk part of the KDA backward, accumulated IN PLACE onto dq, dk, db, dg (which are also returned).
+    Layouts as in the reference: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" `[T,H,D]` (with `cu_seqlens`).
+    q, k bf16; gk (base-2 cumulative gate), dAqk, dAkk `[..., 64]`, dq, dk, dg fp32; beta bf16 or fp32; db fp32."""
+    del chunk_indices
+    op = "npu_chunk_kda_bwd_intra"
+    layout = str(layout)
+    if layout not in {"BSND", "BNSD", "TND"}:
+        raise RuntimeError(f"{op}: supports dense BSND/BNSD or varlen TND.")
+    if not bool(safe_gate):
+        raise RuntimeError(f"{op}: safe_gate=False is reserved but not supported in v1.")
+    if int(chunk_size) != CHUNK:
+        raise RuntimeError(f"{op}: chunk_size must be 64.")
+    tensors = dict(q=q, k=k, gk=gk, beta=beta, dAqk=dAqk, dAkk=dAkk, dq=dq, dk=dk, db=db, dg=dg)
+    want = dict(q=torch.bfloat16, k=torch.bfloat16, gk=torch.float32, dAqk=torch.float32, dAkk=torch.float32, dq=torch.float32,
+                dk=torch.float32, db=torch.float32, dg=torch.float32)
+    for name, t in tensors.items():
+        if name == "beta":
+            if t.dtype not in (torch.bfloat16, torch.float32):
+                raise RuntimeError(f"{op}: beta must be torch.bfloat16 or torch.float32.")
+        elif t.dtype != want[name]:
+            raise RuntimeError(f"{op}: {name} must be {want[name]}.")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{op}: {name} must be contiguous; implicit copies are disabled.")
+    if cu_seqlens is not None and layout == "BNSD":
+        raise RuntimeError(f"{op}: varlen supports TND or BSND, not BNSD.")
+    if cu_seqlens is None and layout == "TND":
+        raise RuntimeError(f"{op}: TND requires cu_seqlens.")
+    rt.reject_requires_grad(op, dq=dq, dk=dk, db=db, dg=dg)
+
+    def view(t):     # -> [B, T, H, .] (3-D gate tensors: [B, T, H])
+        if layout == "TND":
+            return t.unsqueeze(0)
+        return t.transpose(1, 2) if layout == "BNSD" else t
+
+    v = {n: view(t) for n, t in tensors.items()}
+    B, T, H, K = v["q"].shape
+    if K != 128:
+        raise NotImplementedError(f"{op}: this build supports K = 128, got {K}")
+    dev = q.device
+    cu = co = None
+    max_len, total_chunks = T, B * ((T + CHUNK - 1) // CHUNK)
+    if cu_seqlens is not None:
+        if B != 1:
+            raise RuntimeError(f"{op}: varlen BSND compatibility requires B=1.")
+        cu, co, max_len, total_chunks, _n, total = _varlen_meta(cu_seqlens, dev)
+        if total != T:
+            raise RuntimeError(f"{op}: cu_seqlens must start at 0 and end at T.")
+    a = ChunkKdaBwdIntraArgs()
+    a.q, a.k, a.gk, a.beta = rt.desc(v["q"]), rt.desc(v["k"]), rt.desc(v["gk"]), rt.desc(v["beta"])
+    a.d_aqk, a.d_akk = rt.desc(v["dAqk"]), rt.desc(v["dAkk"])
+    a.dq, a.dk, a.db, a.dg = rt.desc(v["dq"]), rt.desc(v["dk"]), rt.desc(v["db"]), rt.desc(v["dg"])
+    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    a.chunk_size, a.max_seqlen, a.total_chunks = CHUNK, int(max_len), int(total_chunks)
+    rt.call("chunk_kda_bwd_intra", a, list(tensors.values()) + [cu, co])
+    rt.mark_mutated(dq, dk, db, dg)
+    return dq, dk, db, dg
+
+
+npu_chunk_kda_bwd_intra = chunk_kda_bwd_intra
 npu_prepare_wy_repr_bwd = prepare_wy_repr_bwd
 npu_prepare_wy_repr_bwd_da = prepare_wy_repr_bwd_da
 npu_prepare_wy_repr_bwd_full = prepare_wy_repr_bwd_full

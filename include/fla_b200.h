@@ -424,6 +424,31 @@ FLA_API int fla_b200_chunk_bwd_dv_local(const fla_chunk_stage_args* args, void* 
 FLA_API int fla_b200_chunk_gated_delta_rule_bwd_dhu(const fla_chunk_stage_args* args, void* workspace, uint64_t workspace_bytes,
                                                     void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * chunk_kda_bwd_intra: intra-chunk part of the KDA backward as a stand-alone, accumulating operator.
+ * Replaces aclnnChunkKdaBwdIntra as bound by npu_chunk_kda_bwd_intra
+ * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1534-1783; golden
+ * torch_custom/fla_npu/test/test_npu_chunk_kda_bwd_intra.py:7-91).  (fla_b200_kda_chunk_bwd computes the complete KDA
+ * gradient without this split.)
+ *   q, k [B,T,H,128] bf16; gk [B,T,H,128] f32 (base-2 chunk-local cumulative gate); beta [B,T,H] bf16|f32;
+ *   d_aqk, d_akk [B,T,H,64] f32: gradients of the two score blocks, lower triangle with diagonal used;
+ *   dq, dk, dg [B,T,H,128] f32 and db [B,T,H] f32 are updated IN PLACE (+=):
+ *     dq_i += sum_{j<=i} d_aqk[i][j] k_j 2^{g_i-g_j};  lower_i = sum_{j<=i} d_akk[i][j] k_j 2^{g_i-g_j};
+ *     upper_j = sum_{i>=j} (d_aqk[i][j] q_i + d_akk[i][j] beta_i k_i) 2^{g_i-g_j};
+ *     dk_i += beta_i lower_i + upper_i;  db_i += lower_i.k_i;  dg_i += q_i*dq_delta_i + k_i*(beta_i lower_i - upper_i).
+ *   Head-first tensors are passed as strided views; q, k, gk, dq, dk, dg share one set of strides, d_aqk and d_akk another,
+ *   beta and db a third.  chunk_size = 64.  cu_seqlens / chunk_offsets as for the chunk operators.  No workspace. */
+typedef struct fla_chunk_kda_bwd_intra_args {
+  fla_tensor_t q, k, gk, beta, d_aqk, d_akk, dq, dk, db, dg;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  int32_t chunk_size;
+  int32_t max_seqlen;
+  int32_t total_chunks;
+} fla_chunk_kda_bwd_intra_args;
+FLA_API int fla_b200_chunk_kda_bwd_intra_workspace_size(const fla_chunk_kda_bwd_intra_args* args, uint64_t* bytes);
+FLA_API int fla_b200_chunk_kda_bwd_intra(const fla_chunk_kda_bwd_intra_args* args, void* workspace, uint64_t workspace_bytes,
+                                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -56,3 +56,34 @@ def kda_reference_fwd_bwd(q, k, v, g, beta, *, scale=None, initial_state=None, d
         res.update(dq=leaves["q"].grad, dk=leaves["k"].grad, dv=leaves["v"].grad, dg=leaves["g"].grad,
                    dbeta=leaves["beta"].grad, dh0=None if leaves["h0"] is None else leaves["h0"].grad)
     return res
+
+
+def chunk_kda_bwd_intra_ref(q, k, gk, beta, d_aqk, d_akk, dq, dk, db, dg, chunk_size=64, cu_seqlens=None):
+    """Intra-chunk KDA backward accumulated onto dq, dk, db, dg (returns new tensors), fp64, `[B,T,H,.]` layout.
+    Restates torch_custom/fla_npu/test/test_npu_chunk_kda_bwd_intra.py:7-91 without its 16-row anchoring (exact in fp64):
+      dq_i += sum_{j<=i} dAqk[i][j] k_j 2^{g_i-g_j};  lower_i = sum_{j<=i} dAkk[i][j] k_j 2^{g_i-g_j};
+      upper_j = sum_{i>=j} (dAqk[i][j] q_i + dAkk[i][j] beta_i k_i) 2^{g_i-g_j};
+      dk_i += beta_i lower_i + upper_i;  db_i += lower_i.k_i;  dg_i += q_i dq_delta_i + k_i (beta_i lower_i - upper_i)."""
+    q, k, gk, beta, d_aqk, d_akk = (t.double() for t in (q, k, gk, beta, d_aqk, d_akk))
+    dq, dk, db, dg = (t.double().clone() for t in (dq, dk, db, dg))
+    T = q.shape[1]
+    bounds = [0, T] if cu_seqlens is None else [int(x) for x in cu_seqlens]
+    for bos, eos in zip(bounds[:-1], bounds[1:]):
+        for s in range(bos, eos, chunk_size):
+            e = min(s + chunk_size, eos)
+            n = e - s
+            qc, kc, gc, bc = q[:, s:e], k[:, s:e], gk[:, s:e], beta[:, s:e]          # [B, n, H, K], [B, n, H]
+            aqk = torch.tril(d_aqk[:, s:e, :, :n].permute(0, 2, 1, 3))               # [B, H, i, j]
+            akk = torch.tril(d_akk[:, s:e, :, :n].permute(0, 2, 1, 3))
+            gh = gc.permute(0, 2, 1, 3)                                              # [B, H, n, K]
+            D = torch.exp2(gh[:, :, :, None, :] - gh[:, :, None, :, :]) * torch.tril(torch.ones(n, n, dtype=torch.float64))[..., None]
+            kh, qh, bh = kc.permute(0, 2, 1, 3), qc.permute(0, 2, 1, 3), bc.permute(0, 2, 1)
+            dq_delta = torch.einsum("bhij,bhijk,bhjk->bhik", aqk, D, kh)
+            lower = torch.einsum("bhij,bhijk,bhjk->bhik", akk, D, kh)
+            upper = torch.einsum("bhij,bhijk,bhik->bhjk", aqk, D, qh) + torch.einsum("bhij,bhijk,bhik->bhjk", akk, D, kh * bh[..., None])
+            bl = bh[..., None] * lower
+            dq[:, s:e] += dq_delta.permute(0, 2, 1, 3)
+            dk[:, s:e] += (bl + upper).permute(0, 2, 1, 3)
+            db[:, s:e] += (lower * kh).sum(-1).permute(0, 2, 1)
+            dg[:, s:e] += (qh * dq_delta + kh * (bl - upper)).permute(0, 2, 1, 3)
+    return dq, dk, db, dg

@@ -247,6 +247,26 @@ def stages_fixture():
     np.savez_compressed(HERE / "stages_golden.npz", **out)
 
 
+def kda_bwd_intra_fixture():
+    """The reference's golden of chunk_kda_bwd_intra on one dense case with a ragged last chunk."""
+    ref = extract(REF / "torch_custom/fla_npu/test/test_npu_chunk_kda_bwd_intra.py",
+                  ["_chunk_kda_bwd_intra_reference_bsnd"])["_chunk_kda_bwd_intra_reference_bsnd"]
+    g_ = torch.Generator().manual_seed(31)
+    B, T, H, K, C = 1, 88, 2, 128, 64
+    rnd = lambda *s: torch.randn(*s, generator=g_)  # noqa: E731
+    q = F.normalize(rnd(B, T, H, K), dim=-1).bfloat16().float()
+    k = F.normalize(rnd(B, T, H, K), dim=-1).bfloat16().float()
+    gate = -4.0 * torch.sigmoid(rnd(B, T, H, K))            # safe-gate range (lower bound -4)
+    gk = torch.cat([gate[:, s:s + C].cumsum(1) for s in range(0, T, C)], 1) / math.log(2.0)
+    beta = torch.sigmoid(rnd(B, T, H))
+    d_aqk, d_akk = rnd(B, T, H, C), rnd(B, T, H, C)
+    dq, dk, db, dg = rnd(B, T, H, K), rnd(B, T, H, K), rnd(B, T, H), rnd(B, T, H, K)
+    out = ref(q, k, gk, beta, d_aqk, d_akk, dq, dk, db, dg, chunk_size=C)
+    np.savez_compressed(HERE / "kda_bwd_intra_golden.npz", q=f32(q), k=f32(k), gk=f32(gk), beta=f32(beta), d_aqk=f32(d_aqk),
+                        d_akk=f32(d_akk), dq=f32(dq), dk=f32(dk), db=f32(db), dg=f32(dg), dq_out=f32(out[0]), dk_out=f32(out[1]),
+                        db_out=f32(out[2]), dg_out=f32(out[3]))
+
+
 if __name__ == "__main__":
     gdn_fixture()
     decode_fixture()
@@ -254,5 +274,6 @@ if __name__ == "__main__":
     conv_bwd_fixture()
     kda_fixture()
     stages_fixture()
+    kda_bwd_intra_fixture()
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)

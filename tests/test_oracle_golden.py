@@ -96,3 +96,10 @@ def test_conv_backward_golden_matches_reference():
             torch.testing.assert_close(got.float(), f[f"{name}_{n}"], rtol=2e-5, atol=2e-5)
         if init is not None:
             torch.testing.assert_close(dh0.float(), f[f"{name}_dh0"], rtol=2e-5, atol=2e-5)
+
+
+def test_kda_bwd_intra_matches_reference_golden():
+    f = _load("kda_bwd_intra_golden.npz")
+    out = oracle.chunk_kda_bwd_intra_ref(f["q"], f["k"], f["gk"], f["beta"], f["d_aqk"], f["d_akk"], f["dq"], f["dk"], f["db"], f["dg"])
+    for name, got in zip(("dq_out", "dk_out", "db_out", "dg_out"), out):
+        _close(got.float(), f[name], 2e-5)
