@@ -134,3 +134,25 @@ def test_conv_config1_identity_taps_copy_the_input_and_states_chain():
     y1, s1 = causal_conv1d(x[:, :T // 2], wr, activation="silu", output_final_state=True)
     y2, s2 = causal_conv1d(x[:, T // 2:], wr, activation="silu", initial_state=s1, output_final_state=True)
     assert torch.equal(torch.cat([y1, y2], 1), yf) and torch.equal(s2, sf)
+
+
+def test_gdn_long_sequence_65536_tokens_prefix_and_chaining():
+    """The reference's smoke shape B=1, T=65536 (ci/example_st_cases.json:124-339): the first 4096 output tokens equal a run
+    over those tokens alone bit for bit (causality at a length where 32-bit element offsets would overflow), and the
+    sequence chained in two halves reproduces the single pass."""
+    from fla_b200.ops import chunk_gated_delta_rule
+    B, T, HK, HV = 1, 65536, 16, 32
+    d = _gdn_inputs(B, T, HK, HV, seed=2010)
+    with torch.no_grad():
+        o, ht = chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True)
+        assert torch.isfinite(o.float()).all() and torch.isfinite(ht).all()
+        P = 4096
+        o_p, _ = chunk_gated_delta_rule(d["q"][:, :P], d["k"][:, :P], d["v"][:, :P], d["g"][:, :P], d["beta"][:, :P],
+                                        initial_state=d["h0"], output_final_state=True)
+        assert torch.equal(o_p, o[:, :P])
+        h = T // 2
+        o1, hm = chunk_gated_delta_rule(d["q"][:, :h], d["k"][:, :h], d["v"][:, :h], d["g"][:, :h], d["beta"][:, :h],
+                                        initial_state=d["h0"], output_final_state=True)
+        o2, ht2 = chunk_gated_delta_rule(d["q"][:, h:], d["k"][:, h:], d["v"][:, h:], d["g"][:, h:], d["beta"][:, h:],
+                                         initial_state=hm, output_final_state=True)
+        assert torch.equal(torch.cat([o1, o2], 1), o) and torch.equal(ht2, ht)

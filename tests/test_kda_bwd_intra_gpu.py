@@ -67,7 +67,7 @@ def test_steepest_safe_gate():
 
 @pytest.mark.parametrize("layout", ["TND", "BSND"])
 def test_varlen(layout):
-    cu = [0, 70, 71, 200, 300]
+    cu = [0, 70, 70, 71, 200, 300]      # an empty and a one-token sequence among ragged ones
     _check(_inputs(1, 300, 2, seed=21, cu=cu), cu=cu, layout=layout)
 
 

@@ -53,7 +53,8 @@ def _case(B, T, HK, HV, seed, cu=None):
     return d
 
 
-CASES = [(1, 160, 1, 2, None), (2, 256, 2, 4, None), (1, 300, 2, 2, [0, 70, 71, 200, 300]), (3, 64, 1, 1, None)]
+# the third case packs an empty sequence, a one-token sequence and ragged tails
+CASES = [(1, 160, 1, 2, None), (2, 256, 2, 4, None), (1, 300, 2, 2, [0, 70, 70, 71, 200, 300]), (3, 64, 1, 1, None)]
 
 
 @pytest.fixture(scope="module", params=range(len(CASES)), ids=lambda i: f"case{i}")
