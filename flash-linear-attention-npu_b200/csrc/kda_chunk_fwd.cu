@@ -501,6 +501,52 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
   if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
+// The two 64 x 64 score blocks of every chunk as plain tensors, for callers of the reference's low-level forward
+// (npu_chunk_kda_fwd returns them): Aqk = scale tril(q k^T 2^{gk_i - gk_j}) from the P image and Akk = the chunk inverse
+// from the X image (value + residual panels summed), rows and columns past a short chunk as zeros.
+struct KdaExportParams {
+  const bf16* img[2];
+  void* out[2];
+  int is_f32[2];
+  int64_t sb[2], st[2], sh[2];
+  const int32_t* cu_seqlens;
+  const int32_t* chunk_offsets;
+  int T, HV;
+  float scale;
+};
+__global__ void __launch_bounds__(128) kda_export_scores_kernel(KdaExportParams p) {
+  const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;
+  const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+  for (int which = 0; which < 2; ++which) {
+    if (!p.out[which]) continue;
+    const uint8_t* hi = reinterpret_cast<const uint8_t*>(p.img[which] + cidx * 8192);
+    const uint8_t* lo = hi + 8192;
+    const float f = which ? 1.f : p.scale;
+    for (int idx = threadIdx.x; idx < kC * 8; idx += 128) {
+      const int r = idx >> 3, ch = idx & 7;
+      if (r >= rows) continue;
+      float a[8], l[8];
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(hi + panel_chunk_off(r, ch)), a);
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(lo + panel_chunk_off(r, ch)), l);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = (ch * 8 + j < rows && ch * 8 + j <= r) ? f * (a[j] + l[j]) : 0.f;
+      const int64_t off = b * p.sb[which] + (t0 + r) * p.st[which] + hv * p.sh[which] + ch * 8;
+      if (p.is_f32[which]) {
+        float* dst = static_cast<float*>(p.out[which]) + off;
+        *reinterpret_cast<float4*>(dst) = make_float4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(a[4], a[5], a[6], a[7]);
+      } else {
+        *reinterpret_cast<uint4*>(static_cast<bf16*>(p.out[which]) + off) = pack8(a);
+      }
+    }
+  }
+}
+
 }  // namespace fla
 
 using namespace fla;
@@ -659,9 +705,27 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = be.dtype == FLA_F32; p.o_is_f32 = a->o.dtype == FLA_F32;
   p.gate_mode = a->gate_mode; p.scale = a->scale; p.lower_bound = a->lower_bound;
 
+  KdaExportParams ep{};
+  for (int which = 0; which < 2; ++which) {
+    const fla_tensor_t& t = which ? a->akk : a->aqk;
+    if (!t.data) continue;
+    if (t.ndim != 4 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != HV || t.shape[3] != kC) return FLA_ERR_SHAPE;
+    if (t.dtype != FLA_BF16 && t.dtype != FLA_F32) return FLA_ERR_DTYPE;
+    if (t.stride[3] != 1 || !aligned16(t.data) || (t.stride[0] % 8) || (t.stride[1] % 8) || (t.stride[2] % 8)) return FLA_ERR_LAYOUT;
+    ep.out[which] = t.data; ep.is_f32[which] = t.dtype == FLA_F32;
+    ep.sb[which] = t.stride[0]; ep.st[which] = t.stride[1]; ep.sh[which] = t.stride[2];
+  }
+
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
-  return kda_launch_forward(p, (max_len + kC - 1) / kC, cs);
+  const int nt_max = (max_len + kC - 1) / kC;
+  st = kda_launch_forward(p, nt_max, cs);
+  if (st || (!ep.out[0] && !ep.out[1])) return st;
+  ep.img[0] = p.p_img; ep.img[1] = p.x_img;
+  ep.cu_seqlens = p.cu_seqlens; ep.chunk_offsets = p.chunk_offsets; ep.T = p.T; ep.HV = p.HV; ep.scale = p.scale;
+  KernelTimer kt("kda_export_scores", cs);
+  kda_export_scores_kernel<<<dim3(nt_max, unsigned(p.HV), p.N), 128, 0, cs>>>(ep);
+  return cuda_status(cudaGetLastError());
 }
 
 int fla::kda_launch_forward(const KdaParams& p, int nt_max, cudaStream_t cs) {

@@ -46,7 +46,7 @@ class GdnChunkBwdArgs(ctypes.Structure):
 
 class KdaChunkFwdArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "g", "beta", "a_log", "dt_bias", "initial_state", "o",
-                                           "final_state", "gk", "cu_seqlens", "chunk_offsets", "saved")] + [
+                                           "final_state", "gk", "cu_seqlens", "chunk_offsets", "saved", "aqk", "akk")] + [
         ("scale", ctypes.c_float), ("lower_bound", ctypes.c_float), ("gate_mode", ctypes.c_int32),
         ("chunk_size", ctypes.c_int32), ("max_seqlen", ctypes.c_int32), ("total_chunks", ctypes.c_int32)]
 

@@ -23,7 +23,7 @@ from .gdn import CHUNK, _as_rows, _varlen_meta
 
 
 def _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias, lower_bound,
-                 meta, return_gate_cumsum, output_dtype, keep_for_backward=False):
+                 meta, return_gate_cumsum, output_dtype, keep_for_backward=False, scores=None):
     B, T, HK, K = q.shape
     HV, V = v.shape[2], v.shape[3]
     cu, co, N, max_len, total_chunks = meta
@@ -38,6 +38,8 @@ def _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gat
     a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
     a.scale, a.lower_bound, a.gate_mode = scale, float(lower_bound or 0.0), gate_mode
     a.chunk_size, a.max_seqlen, a.total_chunks = CHUNK, int(max_len), int(total_chunks)
+    if scores is not None:   # (aqk, akk) as [B,T,HV,64] views, filled from the forward's score images
+        a.aqk, a.akk = rt.desc(scores[0]), rt.desc(scores[1])
     saved = None
     if keep_for_backward:   # the reference's disable_recompute=True: keep the intermediates instead of recomputing them
         nbytes = ctypes.c_uint64(0)
@@ -46,7 +48,7 @@ def _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gat
             raise RuntimeError(f"kda_chunk_saved_size failed with status={status}")
         saved = torch.empty((nbytes.value + 1) // 2, dtype=torch.bfloat16, device=dev)
         a.saved = rt.desc(saved)
-    rt.call("kda_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gk, cu, co, saved])
+    rt.call("kda_chunk_fwd", a, [q, k, v, g, beta, initial_state, o, ht, gk, cu, co, saved] + list(scores or ()))
     if keep_for_backward:
         return o, ht, saved
     return o, ht, gk
@@ -133,9 +135,10 @@ def _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound):
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
               use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
               cu_seqlens=None, safe_gate=False, lower_bound=None, A_log=None, dt_bias=None,
-              return_gate_cumsum=False, output_dtype=None, disable_recompute=False):
+              return_gate_cumsum=False, output_dtype=None, disable_recompute=False, export_scores=None):
     """Returns ``(o [B,T,HV,V], final_state [N,HV,K,V] | None)`` (plus the cumulative gate `[B,T,HV,K]` fp32
-    when ``return_gate_cumsum``)."""
+    when ``return_gate_cumsum``).  ``export_scores`` (inference only): a pair of `[B,T,HV,64]` views that receive the
+    per-chunk blocks Aqk and Akk (what `npu_chunk_kda_fwd` returns)."""
     op = "chunk_kda"
     if use_qk_l2norm_in_kernel or use_beta_sigmoid_in_kernel:
         raise NotImplementedError(f"{op}: in-kernel q/k L2 norm and beta sigmoid are not available yet")
@@ -183,13 +186,71 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         initial_state = initial_state.float().contiguous()
     meta = (cu, co, N, max_len, total_chunks)
     if needs_grad:
-        if return_gate_cumsum:
-            raise NotImplementedError(f"{op}: return_gate_cumsum is not available on the differentiable path")
+        if return_gate_cumsum or export_scores is not None:
+            raise NotImplementedError(f"{op}: return_gate_cumsum / export_scores are not available on the differentiable path")
         o, ht = ChunkKdaFunction.apply(q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype,
                                        bool(disable_recompute))
         return o, ht
     o, ht, gk = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias,
-                             lower_bound, meta, return_gate_cumsum, output_dtype)
+                             lower_bound, meta, return_gate_cumsum, output_dtype, scores=export_scores)
     if return_gate_cumsum:
         return o, ht, gk
     return o, ht
+
+
+def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", initial_state=None, output_final_state=False,
+                      cu_seqlens=None, chunk_indices=None, safe_gate=False, lower_bound=None, use_gate_in_kernel=False,
+                      A_log=None, dt_bias=None, disable_recompute=False, return_intermediate_states=False, state_v_first=False):
+    """The reference's low-level KDA forward (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1066-1265) with its
+    12-value return `(attn_out, final_state, gk, Aqk, Akk, w, u, qg, kg, v_new, h, initial_state)` and the visibility rule of
+    `_kda_policy.py:15-37`: final_state when asked for, gk (base-2 chunk-local cumulative gate, head-first fp32) unless the gate
+    is activated in the kernel, Aqk and Akk `[B,HV,T,64]` always.  The head-major intermediates w, u, qg, kg, v_new, h never exist
+    in the fused kernels, so `disable_recompute=True` and `return_intermediate_states=True` (which make them visible) are
+    refused.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
+    comes back in the input's layout."""
+    del chunk_indices
+    op = "npu_chunk_kda_fwd"
+    layout = str(layout)
+    if layout not in {"BSND", "BNSD", "TND", "NTD"}:
+        raise RuntimeError(f"{op}: layout must be uppercase and one of BSND, BNSD, TND, NTD.")
+    if int(chunk_size) not in {64, 128}:
+        raise RuntimeError(f"{op}: chunk_size must be 64 or 128.")
+    if int(chunk_size) != CHUNK:
+        raise NotImplementedError(f"{op}: this build supports chunk_size = 64")
+    if disable_recompute or return_intermediate_states:
+        raise NotImplementedError(f"{op}: w, u, qg, kg, v_new and h are not materialised by the fused kernels")
+    if state_v_first:
+        raise NotImplementedError(f"{op}: state_v_first is not supported")
+    rank3 = layout in {"TND", "NTD"}
+
+    def to_bsnd(t):
+        if t is None:
+            return None
+        if rank3:
+            t = t.unsqueeze(0)
+        return t.transpose(1, 2) if layout in {"BNSD", "NTD"} else t
+
+    qb, kb, vb, gb, bb = (to_bsnd(t) for t in (q, k, v, g, beta))
+    B, T, HK, K = qb.shape
+    HV = vb.shape[2]
+    dev = q.device
+    aqk = torch.zeros((B, HV, T, CHUNK), dtype=q.dtype, device=dev)
+    akk = torch.zeros_like(aqk)
+    gate_kw = {}
+    if use_gate_in_kernel:
+        gate_kw = dict(use_gate_in_kernel=True, safe_gate=safe_gate, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias)
+    # forward with the score blocks exported (chunk_kda's own checks and metadata apply)
+    with torch.no_grad():
+        o, ht = chunk_kda(qb, kb, vb, gb, bb, scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+                          cu_seqlens=cu_seqlens, export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), **gate_kw)
+    gk_out = None
+    if not use_gate_in_kernel:
+        from .stages import kda_gate_cumsum
+        gk_out = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens).permute(0, 2, 1, 3)       # [B,HV,T,K]
+    if layout in {"BNSD", "NTD"}:
+        o = o.transpose(1, 2).contiguous()
+    if rank3:
+        o, aqk, akk = o.squeeze(0), aqk.squeeze(0), akk.squeeze(0)
+        gk_out = None if gk_out is None else gk_out.squeeze(0)
+    return o, ht, gk_out, aqk, akk, None, None, None, None, None, None, initial_state
+

@@ -269,6 +269,8 @@ typedef struct fla_kda_chunk_fwd_args {
   fla_tensor_t o, final_state, gk;
   fla_tensor_t cu_seqlens, chunk_offsets;
   fla_tensor_t saved;   /* optional out, 1-D bf16 of fla_b200_kda_chunk_saved_size bytes: what the backward otherwise recomputes */
+  fla_tensor_t aqk, akk; /* optional out [B, T, HV, 64] bf16|f32 (any strides, e.g. head-first views): the per-chunk blocks
+                            scale tril(q k^T 2^{gk_i-gk_j}) and (I + beta strict(k k^T 2^{gk_i-gk_j}))^-1 that npu_chunk_kda_fwd returns */
   float scale;
   float lower_bound;
   int32_t gate_mode;

@@ -1,0 +1,93 @@
+"""The reference's low-level KDA forward surface (npu_chunk_kda_fwd, 12-value return): outputs, score blocks and visibility
+against an fp64 restatement of the reference's chunked golden
+(tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:361-530: Aqk = scale tril(q k^T 2^{gk_i-gk_j}),
+Akk = (I + beta strict(k k^T 2^{gk_i-gk_j}))^-1, gk = chunk cumsum of the gate / ln 2)."""
+import math
+
+import pytest
+import torch
+
+import oracle
+from _util import assert_close
+
+pytestmark = pytest.mark.gpu
+C = 64
+
+
+def _golden_blocks(q, k, g, beta, scale, cu=None):
+    """fp64 Aqk, Akk [B,HV,T,64] and base-2 gk [B,HV,T,K] per chunk."""
+    B, T, HK, K = q.shape
+    HV = beta.shape[2]
+    G = HV // HK
+    qq = q.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
+    kk = k.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
+    gg = g.double().permute(0, 2, 1, 3)
+    bb = beta.double().permute(0, 2, 1)
+    aqk = torch.zeros(B, HV, T, C, dtype=torch.float64)
+    akk = torch.zeros_like(aqk)
+    gk = torch.zeros_like(gg)
+    bounds = [0, T] if cu is None else cu
+    for bos, eos in zip(bounds[:-1], bounds[1:]):
+        for s in range(bos, eos, C):
+            e = min(s + C, eos)
+            n = e - s
+            gc = gg[:, :, s:e].cumsum(2) / math.log(2.0)
+            gk[:, :, s:e] = gc
+            D = torch.exp2(gc[:, :, :, None, :] - gc[:, :, None, :, :]) * torch.tril(torch.ones(n, n, dtype=torch.float64))[..., None]
+            qk = torch.einsum("bhik,bhijk,bhjk->bhij", qq[:, :, s:e], D, kk[:, :, s:e]) * scale
+            kkm = torch.einsum("bhik,bhijk,bhjk->bhij", kk[:, :, s:e], D, kk[:, :, s:e])
+            lhs = torch.tril(kkm * bb[:, :, s:e, None], diagonal=-1) + torch.eye(n, dtype=torch.float64)
+            aqk[:, :, s:e, :n] = qk
+            akk[:, :, s:e, :n] = torch.linalg.inv(lhs)
+    return aqk, akk, gk
+
+
+@pytest.mark.parametrize("layout,cu", [("BSND", None), ("BNSD", None), ("TND", [0, 70, 71, 200])])
+def test_npu_chunk_kda_fwd_matches_golden(layout, cu):
+    from fla_b200.ops import npu_chunk_kda_fwd
+    B, T, HK, HV = (1, 200, 2, 4) if cu else (2, 150, 2, 4)
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=31, with_grad=False)
+    scale = 128 ** -0.5
+    N = B if cu is None else len(cu) - 1
+    h0 = 0.1 * torch.randn(N, HV, 128, 128, generator=torch.Generator().manual_seed(3))
+    ref = oracle.kda_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], scale=scale, initial_state=h0) if cu is None else None
+    aqk_r, akk_r, gk_r = _golden_blocks(inp["q"], inp["k"], inp["g"], inp["beta"], scale, cu)
+
+    def lay(t):
+        t = t.cuda()
+        if layout == "BNSD":
+            return t.transpose(1, 2).contiguous()
+        return t.squeeze(0).contiguous() if layout == "TND" else t
+
+    out = npu_chunk_kda_fwd(lay(inp["q"]), lay(inp["k"]), lay(inp["v"]), lay(inp["g"]), lay(inp["beta"]), scale, 64, layout=layout,
+                            initial_state=h0.cuda(), output_final_state=True, cu_seqlens=cu)
+    assert len(out) == 12 and all(x is None for x in out[5:11]) and out[11] is not None
+    o, ht, gk, aqk, akk = out[:5]
+    if layout == "TND":
+        o, gk, aqk, akk = o.unsqueeze(0), gk.unsqueeze(0), aqk.unsqueeze(0), akk.unsqueeze(0)
+    elif layout == "BNSD":
+        o = o.transpose(1, 2)
+    assert aqk.dtype == torch.bfloat16 and gk.dtype == torch.float32 and tuple(aqk.shape) == (B, HV, T, C)
+    assert_close("gk", gk, gk_r, 1e-5)
+    assert_close("Aqk", aqk, aqk_r, 5e-3, stored_bf16=True)
+    assert_close("Akk", akk, akk_r, 5e-3, stored_bf16=True)
+    if ref is not None:
+        assert_close("o", o, ref["o"], 5e-3, stored_bf16=True)
+        assert_close("ht", ht, ref["ht"], 5e-3)
+
+
+def test_visibility_and_refusals():
+    from fla_b200.ops import npu_chunk_kda_fwd
+    inp = oracle.make_kda_inputs(1, 64, 1, 1, seed=5, with_grad=False)
+    args = [inp[n].cuda() for n in ("q", "k", "v", "g", "beta")]
+    out = npu_chunk_kda_fwd(*args, 128 ** -0.5, 64)
+    assert out[1] is None and out[2] is not None and out[11] is None          # no final state asked, gk visible
+    A_log = torch.zeros(1).cuda()
+    out = npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, use_gate_in_kernel=True, A_log=A_log)
+    assert out[2] is None                                                      # gate activated in the kernel: gk hidden
+    with pytest.raises(NotImplementedError):
+        npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, disable_recompute=True)
+    with pytest.raises(RuntimeError, match="chunk_size must be 64 or 128"):
+        npu_chunk_kda_fwd(*args, 128 ** -0.5, 32)
+    with pytest.raises(RuntimeError, match="layout must be uppercase"):
+        npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, layout="bsnd")
