@@ -3,7 +3,7 @@ nothing here computes on the CPU or through PyTorch math."""
 from .conv import (causal_conv1d, causal_conv1d_bwd, causal_conv1d_update, npu_causal_conv1d,  # noqa: F401
                    npu_causal_conv1d_bwd)
 from .gdn import (chunk_gated_delta_rule, chunk_gated_delta_rule_bwd, chunk_gated_delta_rule_fwd_bwd,  # noqa: F401
-                  ChunkGatedDeltaRuleFunction)
+                  ChunkGatedDeltaRuleFunction, flash_gated_delta_rule)
 from .kda import chunk_kda, chunk_kda_fwd_bwd, kda_chunk_bwd, npu_chunk_kda_fwd  # noqa: F401
 from .l2norm import l2norm_bwd, l2norm_fwd  # noqa: F401
 from .recurrent import fused_recurrent_gated_delta_rule, recurrent_gated_delta_rule, recurrent_kda  # noqa: F401

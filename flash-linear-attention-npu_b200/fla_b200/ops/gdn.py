@@ -198,10 +198,52 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
                            output_dtype=None):
     """Returns ``(o [B,T,HV,V], final_state [N,HV,K,V] | None)``; differentiable w.r.t. q, k, v, g, beta, initial_state."""
     op = "chunk_gated_delta_rule"
-    if head_first:
-        raise NotImplementedError(f"{op}: head_first layouts are not provided; pass [B,T,H,D] tensors")
+    if head_first:   # [B,H,T,D] tokens and [B,H,T] gates: the same operator on transposed views, output back in [B,H,T,V]
+        o, ht = chunk_gated_delta_rule(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), g.transpose(1, 2), beta.transpose(1, 2),
+                                       scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+                                       use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens, chunk_size=chunk_size,
+                                       output_dtype=output_dtype)
+        return o.transpose(1, 2), ht
     if chunk_size != CHUNK:
         raise NotImplementedError(f"{op}: chunk_size must be {CHUNK}")
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                                              output_dtype, bool(use_qk_l2norm_in_kernel))
+
+
+def flash_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, cu_seqlens_list=None, chunk_indices=None,
+                           chunk_indices_list=None, chunk_size=64, head_first=False):
+    """The reference's composed entry with its own layout and checks (examples/flash_gated_delta_rule.py:1126-1228):
+    q, k `[B,H,T,K]`, v `[B,H,T,V]` (head-first), g, beta `[B,T,H]`; returns (o `[B,T,H,V]`, final_state `[N,H,K,V]` or None).
+    The host-side chunk metadata arguments (`cu_seqlens_list`, `chunk_indices`, `chunk_indices_list`) are accepted and not
+    needed: the chunk geometry follows from `cu_seqlens`.  GVA callers pass q, k with fewer heads than v."""
+    del cu_seqlens_list, chunk_indices, chunk_indices_list
+    if q.dtype != k.dtype or k.dtype != v.dtype:
+        raise ValueError(f"q current type is {q.dtype}, k current type is {k.dtype}, v current type is {v.dtype}; they should be equal")
+    if q.dtype == torch.float32:
+        raise ValueError("ChunkGatedDeltaRuleFunction does not support float32. Please use float16/bfloat16.")
+    if beta.ndim != 3 or g.ndim != 3:
+        raise ValueError("g and beta must be rank-3 tensors with shape [B, T, H].")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("q, k and v must be rank-4 tensors with shape [B, H, T, D].")
+    if q.shape[:3] != k.shape[:3] or q.shape[0] != v.shape[0] or q.shape[2] != v.shape[2]:
+        raise ValueError(f"q/k/v shape prefixes must match, got {q.shape}, {k.shape}, {v.shape}.")
+    if g.shape != beta.shape:
+        raise ValueError(f"g and beta shapes must match, got {g.shape} and {beta.shape}.")
+    if g.shape[0] != v.shape[0] or g.shape[1] != v.shape[2] or g.shape[2] != v.shape[1]:
+        raise ValueError(f"Expected q/k/v in [B, H, T, D] and g/beta in [B, T, H]; got q={tuple(q.shape)}, g={tuple(g.shape)}.")
+    if head_first:
+        import warnings
+        warnings.warn("head_first is kept only for API compatibility. This entry always expects q/k/v as [B, H, T, D].", stacklevel=2)
+    if chunk_size != 2 ** (int(chunk_size).bit_length() - 1):
+        raise ValueError(f"chunk_size must be a power of 2, got {chunk_size}.")
+    if cu_seqlens is not None and q.shape[0] != 1:
+        raise ValueError(f"The batch size is expected to be 1 rather than {q.shape[0]} when using cu_seqlens. "
+                         "Please flatten variable-length inputs before processing.")
+    if cu_seqlens is not None and initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+        raise ValueError("The number of initial states is expected to match the number of input sequences, "
+                         f"got initial_state.shape[0]={initial_state.shape[0]} and sequences={len(cu_seqlens) - 1}.")
+    return chunk_gated_delta_rule(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), g, beta, scale=scale,
+                                  initial_state=initial_state, output_final_state=output_final_state,
+                                  use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens, chunk_size=chunk_size)

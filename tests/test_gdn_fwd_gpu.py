@@ -61,3 +61,26 @@ def test_forward_is_deterministic():
     o1, h1, _ = _run(1, 256, 2, 4, seed=3)
     o2, h2, _ = _run(1, 256, 2, 4, seed=3)
     assert torch.equal(o1, o2) and torch.equal(h1, h2)
+
+
+def test_head_first_and_reference_entry_are_views_of_the_same_operator():
+    """`head_first=True` and the reference's composed entry `flash_gated_delta_rule` ([B,H,T,D] tokens) give bit-identical
+    results to the sequence-first call, forward and backward."""
+    from fla_b200.ops import chunk_gated_delta_rule, flash_gated_delta_rule
+    inp = oracle.make_gdn_inputs(B=2, T=130, HK=2, HV=4, K=128, V=128, seed=77, dtype=torch.bfloat16)
+    q, k, v, g, beta, h0, do = (inp[n].cuda() for n in ("q", "k", "v", "g", "beta", "h0", "do"))
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    o, ht = chunk_gated_delta_rule(*leaves, g, beta, initial_state=h0, output_final_state=True)
+    (o.float() * do.float()).sum().backward()
+    hf = [t.transpose(1, 2).contiguous() for t in (q, k, v)]
+    o1, ht1 = chunk_gated_delta_rule(*hf, g.transpose(1, 2).contiguous(), beta.transpose(1, 2).contiguous(), initial_state=h0,
+                                     output_final_state=True, head_first=True)
+    assert torch.equal(o1.transpose(1, 2), o) and torch.equal(ht1, ht)
+    leaves2 = [t.clone().requires_grad_(True) for t in hf]
+    o2, ht2 = flash_gated_delta_rule(*leaves2, g, beta, initial_state=h0, output_final_state=True)
+    assert tuple(o2.shape) == tuple(o.shape) and torch.equal(o2, o) and torch.equal(ht2, ht)
+    (o2.float() * do.float()).sum().backward()
+    for a, b in zip(leaves, leaves2):
+        assert torch.equal(b.grad.transpose(1, 2), a.grad)
+    with pytest.raises(ValueError, match="does not support float32"):
+        flash_gated_delta_rule(*(t.float() for t in hf), g, beta)
