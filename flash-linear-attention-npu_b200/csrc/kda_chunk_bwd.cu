@@ -714,25 +714,42 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
     // dg = reverse chunk-local cumulative sum of dgk; the last row additionally carries
     // sum_v dS'a Sa + sum_i Kn_i (Vn dS'a^T)_i, which therefore reaches every row.
     {
-      // Two threads per key channel, 32 rows each: local totals first, then the suffix sums with the loads unrolled.
+      // Two threads per key channel, 32 rows each: local totals first, then the suffix sums.  Each group of eight rows is
+      // read into registers before any of its results is stored: a global store between two shared-memory loads would keep
+      // the compiler from overlapping them (it cannot tell the generic pointers apart).
       const int kc = tid & (kK - 1), part = tid >> 7, r0 = part * 32;
       float tot = 0.f;
 #pragma unroll 8
       for (int i = 0; i < 32; ++i) tot += tile_q[(r0 + i) * kTileStride + kc] + tile_k[(r0 + i) * kTileStride + kc];   // rows past the end hold zeros
       colsum_s[part][kc] = tot;
+      KSTAMP(9);
       __syncthreads();
+      KSTAMP(10);
       float run = sds_s[0][kc] + sds_s[1][kc] + t1col_s[0][kc] + t1col_s[1][kc] + (part == 0 ? colsum_s[1][kc] : 0.f);
-#pragma unroll 8
-      for (int i = 31; i >= 0; --i) {
-        const int t = r0 + i;
-        run += tile_q[t * kTileStride + kc] + tile_k[t * kTileStride + kc];
-        if (t < rows) {
-          const int64_t off = (tok0 + t) * p.dg_st + hv * p.dg_sh + kc;
-          if (p.grads_f32) static_cast<float*>(p.dg)[off] = run;
-          else static_cast<bf16*>(p.dg)[off] = __float2bfloat16_rn(run);
+      const int64_t base = tok0 * p.dg_st + hv * p.dg_sh + kc;
+      for (int blk = 3; blk >= 0; --blk) {
+        float vals[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int t = r0 + blk * 8 + j;
+          vals[j] = tile_q[t * kTileStride + kc] + tile_k[t * kTileStride + kc];
+        }
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+          run += vals[j];
+          vals[j] = run;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int t = r0 + blk * 8 + j;
+          if (t < rows) {
+            if (p.grads_f32) static_cast<float*>(p.dg)[base + t * p.dg_st] = vals[j];
+            else static_cast<bf16*>(p.dg)[base + t * p.dg_st] = __float2bfloat16_rn(vals[j]);
+          }
         }
       }
     }
+    KSTAMP(11);
     __syncthreads();
   }
 
