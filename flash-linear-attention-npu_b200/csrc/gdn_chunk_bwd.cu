@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
 // ============================================================================================= par
 constexpr uint32_t rOffQK = 0, rQKPanel = 16384;
 constexpr uint32_t rOffAH = 32768;             // [dO ; dZ_hi] rows of one V block (128 rows)
-constexpr uint32_t rOffPad = 49152;            // 16 KB whose contents do not matter: the rows 0-63 of the Vn-as-A operand
+// 49152 .. 65535: 16 KB whose contents do not matter (rows 0-63 of the Vn-as-A operand, which starts 8 KB before rOffVNH)
 constexpr uint32_t rOffVNH = 65536, rOffVNL = 73728;
 constexpr uint32_t rOffSH = 81920, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 131072;
 constexpr uint32_t rOffPAH = 147456, rOffPAL = 163840;   // [dP ; dAt] hi / lo (128 rows x 64)

@@ -132,15 +132,6 @@ __device__ __forceinline__ void stage_rows128(uint8_t* dst, uint32_t panel_strid
     if (dst_lo) *reinterpret_cast<uint4*>(dst_lo + off) = lo;
   }
 }
-// 64 rows x 64 bf16 columns -> one panel, rows >= `rows` zeroed
-__device__ __forceinline__ void stage_rows64(uint8_t* dst, const bf16* src, int64_t st, int rows, int tid, int nthr) {
-  for (int idx = tid; idx < kC * 8; idx += nthr) {
-    const int r = idx >> 3, ch = idx & 7;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (r < rows) val = *reinterpret_cast<const uint4*>(src + r * st + ch * 8);
-    *reinterpret_cast<uint4*>(dst + panel_chunk_off(r, ch)) = val;
-  }
-}
 __device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
 }

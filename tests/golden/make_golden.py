@@ -1,7 +1,7 @@
 """Generate the committed golden fixtures by running the REFERENCE's own CPU functions.
 
-Run once in a container that has the reference checkout (path in $FLA_REFERENCE_ROOT, default
-/root/reference):  python tests/golden/make_golden.py
+Run once on a machine that has the reference checkout:
+    FLA_REFERENCE_ROOT=<path to the reference tree> python tests/golden/make_golden.py
 The reference modules import Ascend-only packages at module level, so the needed pure-torch
 functions are extracted from the source text with `ast` and executed on their own.  The outputs
 (inputs + reference results, float32/int32 numpy arrays) are written next to this script as .npz;
@@ -21,7 +21,9 @@ import torch
 import torch.nn.functional as F
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("FLA_REFERENCE_ROOT", "/root/reference"))
+if "FLA_REFERENCE_ROOT" not in os.environ:
+    raise SystemExit("set FLA_REFERENCE_ROOT to the reference checkout")
+REF = Path(os.environ["FLA_REFERENCE_ROOT"])
 sys.path.insert(0, str(HERE.parent.parent))
 
 
