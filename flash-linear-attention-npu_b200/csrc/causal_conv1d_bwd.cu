@@ -57,7 +57,18 @@ __device__ __forceinline__ float dsilu(float p) {
   return s * fmaf(p, 1.f - s, 1.f);
 }
 
-constexpr int kBwdGroup = 4;     // tokens per inner step: their loads are issued together
+constexpr int kBwdGroup = 2;     // tokens per inner step
+constexpr int kBwdAhead = 3;     // groups requested ahead of the one being processed (ring = 48 KB per CTA)
+constexpr int kBwdRing = kBwdAhead + 1;
+constexpr uint32_t kBwdSmem = kBwdRing * kBwdGroup * 3 * kBwdThreads * sizeof(uint4);   // x, dy, y_pre slots
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // weight element (d, j) at w[d * wsd + j * wsw]; taps of 8 channels starting at d0
 template <int W>
@@ -84,6 +95,7 @@ __device__ __forceinline__ void load_taps(const bf16* w, int64_t wsd, int64_t ws
 template <int W, bool SILU>
 __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams p) {
   constexpr int G = kBwdGroup;
+  extern __shared__ uint4 ring[];
   const int d0 = (blockIdx.x * kBwdThreads + threadIdx.x) * 8;
   if (d0 >= p.D) return;
   const int b = blockIdx.z;
@@ -156,14 +168,42 @@ __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams 
 #pragma unroll
       for (int c = 0; c < 8; ++c) gs[j][c] = 0.f;
     }
-    for (int ug = t; ug < u_stop; ug += G) {
-      uint4 xin[G], gin[G], yin[G];
+    // Loads run kBwdAhead groups ahead of the arithmetic as asynchronous copies into a per-thread ring in shared memory
+    // (cp.async, 16 bytes each): they occupy no registers while in flight, so every thread keeps
+    // kBwdAhead * G * (2 or 3) * 16 bytes on their way and the copies' latency is covered by the work on earlier groups.
+    // A thread only ever reads the slots it wrote itself: cp.async.wait_group orders them, no barrier is needed.
+    auto request = [&](int ug) {
+      const int slot = ((ug - t) / G) % kBwdRing;
 #pragma unroll
       for (int i = 0; i < G; ++i) {
-        const bool valid = ug + i < u_real_end;
-        xin[i] = valid ? *reinterpret_cast<const uint4*>(xb + (ug + i) * p.x_st) : make_uint4(0, 0, 0, 0);
-        gin[i] = valid ? *reinterpret_cast<const uint4*>(gb + (ug + i) * p.dy_st) : make_uint4(0, 0, 0, 0);
-        if (SILU && yb) yin[i] = valid ? *reinterpret_cast<const uint4*>(yb + (ug + i) * p.yp_st) : make_uint4(0, 0, 0, 0);
+        uint4* dst = ring + ((slot * G + i) * 3) * kBwdThreads + threadIdx.x;
+        if (ug + i < u_real_end) {
+          cp_async16(dst, xb + (ug + i) * p.x_st);
+          cp_async16(dst + kBwdThreads, gb + (ug + i) * p.dy_st);
+          if (SILU && yb) cp_async16(dst + 2 * kBwdThreads, yb + (ug + i) * p.yp_st);
+        } else {
+          dst[0] = make_uint4(0, 0, 0, 0);
+          dst[kBwdThreads] = make_uint4(0, 0, 0, 0);
+          dst[2 * kBwdThreads] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int a = 0; a < kBwdAhead; ++a) request(t + a * G);
+    for (int ug = t; ug < u_stop; ug += G) {
+      request(ug + kBwdAhead * G);            // past the end: zeros, and an empty group keeps the count uniform
+      cp_async_wait<kBwdAhead>();
+      uint4 xin[G], gin[G], yin[G];
+      {
+        const int slot = ((ug - t) / G) % kBwdRing;
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+          const uint4* src = ring + ((slot * G + i) * 3) * kBwdThreads + threadIdx.x;
+          xin[i] = src[0];
+          gin[i] = src[kBwdThreads];
+          if (SILU) yin[i] = src[2 * kBwdThreads];
+        }
       }
 #pragma unroll
       for (int i = 0; i < G; ++i) {
@@ -223,6 +263,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams 
           gs[j][c] = gs[G + j][c];
         }
     }
+    cp_async_wait<0>();     // the groups requested past the segment's end
     if (t == seq_begin && p.dh0) {
       // dh0[i] = sum_{rel <= i} gr[rel] w[i - rel]: the first W-1 tokens of the sequence, recomputed on their own
       const int len = seq_end - seq_begin;
@@ -387,8 +428,8 @@ extern "C" FLA_API int fla_b200_causal_conv1d_bwd(const fla_causal_conv1d_bwd_ar
     KernelTimer kt("causal_conv1d_bwd", st);
     const bool silu = a->activation_silu != 0;
 #define FLA_LAUNCH_BWD(WW)                                                        \
-  if (silu) conv_bwd_kernel<WW, true><<<grid, kBwdThreads, 0, st>>>(p);           \
-  else conv_bwd_kernel<WW, false><<<grid, kBwdThreads, 0, st>>>(p);
+  if (silu) conv_bwd_kernel<WW, true><<<grid, kBwdThreads, kBwdSmem, st>>>(p);    \
+  else conv_bwd_kernel<WW, false><<<grid, kBwdThreads, kBwdSmem, st>>>(p);
     if (W == 4) { FLA_LAUNCH_BWD(4) } else if (W == 3) { FLA_LAUNCH_BWD(3) } else { FLA_LAUNCH_BWD(2) }
 #undef FLA_LAUNCH_BWD
   }
