@@ -13,6 +13,9 @@ distributions of BASELINE.json.  Workloads (the default is the one the headline 
                  one CUDA graph replay per step
   conv_prefill   the conv half of config 1 alone
   conv_bwd       backward of that conv (dx, dw, db from x, dy; SiLU pre-activation recomputed)
+  gdn_stage_fwd / gdn_stage_fwd_bwd   configs 1 / 2 through the stand-alone stage operators, one launch per reference operator
+`value` times K steps issued round-robin on `--streams` CUDA streams (default 2): the steps are independent batches, and a
+second step in flight fills the SMs that the tail of a kernel leaves idle.  `single_stream` repeats the K steps on one stream.
 With N > 1 every rank (one process per GPU, launched by torch.distributed.run) processes its own batch of that
 shape (weak scaling; the path has no exchange step, so there is no collective on the data path); NCCL carries only
 the barrier and the max-over-ranks reduction of the measured time.  Rank 0 prints ONE JSON line.
@@ -443,6 +446,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=WORKLOADS)
     ap.add_argument("--shape", default=None, help="B,T override (N,1 for decode) for small profiling cases")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--streams", type=int, default=2,
+                    help="CUDA streams the timed steps are issued on round-robin (1 = every step waits for the one before)")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     wl = Workload(args.workload, args.shape)
@@ -480,18 +485,42 @@ def main():
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(K):
-        wl.step_fast(d)
-    e1.record()
-    barrier()
-    elapsed_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+    main = torch.cuda.current_stream(dev)
+    n_streams = 1 if wl.name == "decode" else max(1, args.streams)     # decode steps chain through the state pool
+    side = [torch.cuda.Stream(dev) for _ in range(n_streams)] if n_streams > 1 else []
+
+    def timed(streams):
+        """K steps; with several streams the (independent) steps are issued round-robin, so the tail of one step's
+        kernels, where SMs run out of CTAs, is filled by the next step's kernels.  Device time between two events on the main stream."""
+        barrier()
+        e0.record()
+        for st in streams:
+            st.wait_stream(main)
+        for i in range(K):
+            if streams:
+                with torch.cuda.stream(streams[i % len(streams)]):
+                    wl.step_fast(d)
+            else:
+                wl.step_fast(d)
+        for st in streams:
+            main.wait_stream(st)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() / K
+
+    for i in range(2 * len(side)):      # warm the side streams' allocator pools
+        with torch.cuda.stream(side[i % len(side)]):
+            wl.step_fast(d)
+    ms_per_step = timed(side)
     clocks = sampler.stop() if rank == 0 else None
-    ms_per_step = elapsed_ms.item() / K
     value = world * wl.tokens_per_step / (ms_per_step * 1e-3)
+    single = None
+    if side:
+        ms1 = timed([])
+        single = {"ms_per_step": ms1, "value": world * wl.tokens_per_step / (ms1 * 1e-3)}
 
     # ---- per-kernel durations of the same step (CUDA events around each launch, on the launching stream)
     lib.fla_b200_kernel_timing_enable(1)
@@ -625,7 +654,10 @@ def main():
                        "parallelism": f"one replica of the batch per GPU x{world}, no collective",
                        "l2": "inputs per step exceed the 126 MB L2" if wl.name != "decode" else
                              "the 1.07 GB state pool streamed every step exceeds the 126 MB L2",
-                       "cuda_graph": wl.name == "decode"},
+                       "cuda_graph": wl.name == "decode",
+                       "streams": f"{n_streams}: the K independent steps are issued round-robin on {n_streams} CUDA streams"
+                                  if n_streams > 1 else "1"},
+            "single_stream": single,
             "roofline": roofline, "kernels": ktimes, "step_roofline": step_roofline, "cpu_baseline": cpu_baseline,
             "e2e": e2e, "gpu_launches": wl.launches_per_step() * K, "clocks": clocks,
         }
