@@ -186,7 +186,10 @@ struct FwdPrefetch {
 
 #ifdef FLA_STAGE_CLOCKS
 __device__ long long g_stage_clocks[16];
-#define STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { long long now_ = clock64(); g_stage_clocks[i] += now_ - last_; last_ = now_; } } while (0)
+#ifndef FLA_STAGE_THREAD
+#define FLA_STAGE_THREAD 0
+#endif
+#define STAMP(i) do { long long now_ = clock64(); fclk_[i] += now_ - last_; last_ = now_; } while (0)
 #else
 #define STAMP(i)
 #endif
@@ -198,6 +201,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
                                                                   const __grid_constant__ CUtensorMap tm_k,
                                                                   const __grid_constant__ CUtensorMap tm_x) {
 #ifdef FLA_STAGE_CLOCKS
+  long long fclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
   long long last_ = clock64();
 #endif
   extern __shared__ uint8_t smem_raw[];
@@ -373,10 +377,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
         bulk_store(dst, sb + kOffSH, 32768);
         bulk_commit();
       }
+      STAMP(10);
       if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
+      STAMP(7);
       mma_tile(tbase + kColRQ, opQK, opSH, 128, 64, 8, false);
       mma_tile(tbase + kColRQ, opQK, opSL, 128, 64, 8, true);
       mma_commit(&bar);
+      STAMP(8);
     }
     qkphase ^= 1;
     if (c + 1 < sq.nt) {
@@ -499,6 +506,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     STAMP(6);
   }
 
+#ifdef FLA_STAGE_CLOCKS
+  if (tid == FLA_STAGE_THREAD && blockIdx.x == 1 && blockIdx.y == 9 && blockIdx.z == 3)
+    for (int i = 0; i < 12; ++i) g_stage_clocks[i] += fclk_[i];
+#endif
   if (!dead && p.ht) {
     float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
 #pragma unroll
