@@ -70,9 +70,23 @@ constexpr int kDhuThreads = 256;
 
 // q, k and X reach their operand panels as TMA tiles (see gdn_fwd_kernel); rows past the end of a sequence are
 // neutralised by zeroing the corresponding rows of dVn.
+#ifdef FLA_STAGE_CLOCKS
+#ifndef FLA_STAGE_THREAD
+#define FLA_STAGE_THREAD 0
+#endif
+__device__ long long g_dhu_clocks[16];
+#define DSTAMP(i) do { long long now_ = clock64(); dclk_[i] += now_ - dlast_; dlast_ = now_; } while (0)
+#else
+#define DSTAMP(i)
+#endif
+
 __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                       const __grid_constant__ CUtensorMap tm_k,
                                                                       const __grid_constant__ CUtensorMap tm_x) {
+#ifdef FLA_STAGE_CLOCKS
+  long long dclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long dlast_ = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
@@ -208,6 +222,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     const float gam_i = gam_s[cur][tok];
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
 
+    DSTAMP(0);
     // ---- stage 0: publish dS' (split copy for the MMAs and for the second kernel), pre-decayed master in TMEM
     row32_to_hilo(smem + hOffDSH, smem + hOffDSL, row, half, srow);
     {
@@ -221,6 +236,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     __syncthreads();
     tc_fence_after();
 
+    DSTAMP(1);
     // ---- stage 1: [Q;K] dS'  and  U1 = P^T dO (valid accumulator rows 64..127)
     if (tid == 0) {
       bf16* dst = p.ds_img + (cidx * 2 + vb) * (2 * 8192);
@@ -240,6 +256,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
+    DSTAMP(2);
     // ---- stage 4: k-side rows: dVn = scale U1 + e^{gam_L - gam} (K dS')
     float acc[32];
     if (kside) {
@@ -259,6 +276,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     __syncthreads();
     tc_fence_after();
 
+    DSTAMP(3);
     // ---- stage 5: dZ = X^T dVn  (valid accumulator rows 64..127)
     if (tid == 0) {
       if (!mbar_wait(&x_bar, xphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // the X tile has landed
@@ -271,6 +289,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     tc_fence_after();
     if (tid == 0 && c > 0) issue_x_load(c - 1);
 
+    DSTAMP(4);
     // ---- stage 6: k-side rows: dV, sum_v dZ*V, dZ images, -beta e^gam dZ;  q-side rows: scale e^gam dO
     if (kside) {
       tmem_ld_row32(trow + hColQK, acc);
@@ -326,6 +345,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     __syncthreads();
     tc_fence_after();
 
+    DSTAMP(5);
     // ---- stage 7: dS += [Q^T | K^T] [scale e^gam dO ; -beta e^gam dZ]
     if (tid == 0) {
       bf16* dst = p.dz_img + (cidx * 2 + vb) * 8192;
@@ -341,6 +361,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     tc_fence_after();
     if (tid == 0 && c > 0) issue_qk_load(c - 1);   // the last readers of the q / k panels have completed
 
+    DSTAMP(6);
     // ---- stage 8: new dS to registers; next chunk's operands
     tmem_ld_row32(trow + hColDS, srow);
     if (tid == 0) {
@@ -355,6 +376,11 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     }
   }
 
+#ifdef FLA_STAGE_CLOCKS
+  DSTAMP(7);
+  if (tid == FLA_STAGE_THREAD && blockIdx.x == 1 && blockIdx.y == 9 && blockIdx.z == 3)
+    for (int i = 0; i < 12; ++i) g_dhu_clocks[i] += dclk_[i];
+#endif
   if (!dead && p.dh0) {
     float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
 #pragma unroll
@@ -937,6 +963,9 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_ar
 }
 
 #ifdef FLA_STAGE_CLOCKS
+extern "C" FLA_API int fla_b200_debug_dhu_clocks(long long* out16) {
+  return cudaMemcpyFromSymbol(out16, fla::g_dhu_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
+}
 extern "C" FLA_API int fla_b200_debug_par_clocks(long long* out16) {
   return cudaMemcpyFromSymbol(out16, fla::g_par_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
 }
