@@ -285,6 +285,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
       mma_commit(&bar);
     }
     xphase ^= 1;
+    if (c > 0) prefetch_load(c - 1);   // the next chunk's rows: requested two stages before they are stored
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
     if (tid == 0 && c > 0) issue_x_load(c - 1);
@@ -356,7 +357,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
       mma_tile(tbase + hColDS, opQKT, opDSL, 128, 64, 8, true);
       mma_commit(&bar);
     }
-    if (c > 0) prefetch_load(c - 1);   // L2-resident by now; travels while the MMAs run
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
     if (tid == 0 && c > 0) issue_qk_load(c - 1);   // the last readers of the q / k panels have completed
