@@ -363,7 +363,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
       for (int i = 0; i < 32; ++i) srow[i] *= dl;
       tmem_st_row32(trow + kColS, srow);
     }
-    if (tid == 0 && p.s_img) bulk_wait_read();  // the previous chunk's v_new images have left shared memory
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -372,11 +371,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     STAMP(0);
     // ---- stage 1: [Q;K] S  (split state: two passes)
     if (tid == 0) {
-      if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format
-        bf16* dst = p.s_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 8192);
-        bulk_store(dst, sb + kOffSH, 32768);
-        bulk_commit();
-      }
       STAMP(10);
       if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
       STAMP(7);
@@ -386,6 +380,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
       STAMP(8);
     }
     qkphase ^= 1;
+    if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format: plain 16-byte
+                    // copies by all threads while the MMAs run (bulk stores would queue ahead of the chunk's TMA loads)
+      uint4* dst = reinterpret_cast<uint4*>(p.s_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 8192));
+      const uint4* src = reinterpret_cast<const uint4*>(smem + kOffSH);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[tid + i * kFwdThreads] = src[tid + i * kFwdThreads];
+    }
     if (c + 1 < sq.nt) {
       prefetch_l2(c + 1);
       prefetch_scalars(c + 1);
@@ -447,7 +448,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
       for (int i = 0; i < 32; ++i) acc[i] *= dk;
       row32_to_hilo(smem + kOffVH, smem + kOffVL, tok, half, acc);
     }
-    if (tid == 0 && p.s_img) bulk_wait_read();  // this chunk's state images have left shared memory
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -456,12 +456,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     STAMP(4);
     // ---- stage 5: P v_new (three passes) and the state update S += K^T vhat
     if (tid == 0) {
-      if (p.vn_img) {
-        bf16* dst = p.vn_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 4096);
-        bulk_store(dst, sb + kOffZH, 8192);
-        bulk_store(dst + 4096, sb + kOffZL, 8192);
-        bulk_commit();
-      }
       mma_tile(tbase + kColS, opKT, opVH, 128, 64, 4, true);
       mma_tile(tbase + kColS, opKT, opVL, 128, 64, 4, true);
       if (!mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // P panels have landed
@@ -471,6 +465,12 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
       mma_commit(&bar);
     }
     pphase ^= 1;
+    if (p.vn_img) {
+      uint4* dst = reinterpret_cast<uint4*>(p.vn_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 4096));
+      const uint4* src = reinterpret_cast<const uint4*>(smem + kOffZH);     // Z_hi and Z_lo panels are adjacent
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dst[tid + i * kFwdThreads] = src[tid + i * kFwdThreads];
+    }
     if (c + 1 < sq.nt) prefetch_load(c + 1);   // the next chunk's rows (L2-resident by now) travel while the MMAs run
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
@@ -515,7 +515,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
 #pragma unroll
     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
-  if (tid == 0 && p.s_img) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 256);
