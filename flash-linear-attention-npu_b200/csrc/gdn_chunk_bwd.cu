@@ -239,9 +239,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     DSTAMP(1);
     // ---- stage 1: [Q;K] dS'  and  U1 = P^T dO (valid accumulator rows 64..127)
     if (tid == 0) {
-      bf16* dst = p.ds_img + (cidx * 2 + vb) * (2 * 8192);
-      bulk_store(dst, sb + hOffDSH, 32768);
-      bulk_commit();
       if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
       mma_tile(tbase + hColW1, opQK, opDSH, 128, 64, 8, false);
       mma_tile(tbase + hColW1, opQK, opDSL, 128, 64, 8, true);
@@ -252,6 +249,13 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     }
     pphase ^= 1;
     qkphase ^= 1;
+    {   // the split dS' copy is already in the panel-image format the chunk-parallel kernel loads: plain 16-byte copies by
+        // all threads while the MMAs run (bulk stores would queue ahead of the next chunk's TMA loads)
+      uint4* dst = reinterpret_cast<uint4*>(p.ds_img + (cidx * 2 + vb) * (2 * 8192));
+      const uint4* src = reinterpret_cast<const uint4*>(smem + hOffDSH);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[tid + i * kDhuThreads] = src[tid + i * kDhuThreads];
+    }
     if (c > 0) prefetch_l2(c - 1);
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
@@ -270,7 +274,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
       for (int i = 0; i < 32; ++i) acc[i] = live ? p.scale * acc[i] + dk * w1[i] : 0.f;
       row32_to_hilo(smem + hOffPH, smem + hOffPL, tok, half, acc);
     }
-    if (tid == 0) bulk_wait_read();  // the dS' images have left shared memory (it is reused in stage 6)
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -349,13 +352,18 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     DSTAMP(5);
     // ---- stage 7: dS += [Q^T | K^T] [scale e^gam dO ; -beta e^gam dZ]
     if (tid == 0) {
-      bf16* dst = p.dz_img + (cidx * 2 + vb) * 8192;
-      bulk_store(dst, sb + hOffDO, 8192);            // rows 0..63 of the image: dO
-      bulk_store(dst + 4096, sb + hOffPH, 8192);     // rows 64..127: dZ
-      bulk_commit();
       mma_tile(tbase + hColDS, opQKT, opDSH, 128, 64, 8, true);
       mma_tile(tbase + hColDS, opQKT, opDSL, 128, 64, 8, true);
       mma_commit(&bar);
+    }
+    {   // the [dO ; dZ] image of this V block: rows 0..63 from the dO panel, rows 64..127 from the dZ panel
+      uint4* dst = reinterpret_cast<uint4*>(p.dz_img + (cidx * 2 + vb) * 8192);
+      const uint4* s0 = reinterpret_cast<const uint4*>(smem + hOffDO);
+      const uint4* s1 = reinterpret_cast<const uint4*>(smem + hOffPH);
+      dst[tid] = s0[tid];
+      dst[tid + 256] = s0[tid + 256];
+      dst[tid + 512] = s1[tid];
+      dst[tid + 768] = s1[tid + 256];
     }
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
@@ -364,12 +372,9 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     DSTAMP(6);
     // ---- stage 8: new dS to registers; next chunk's operands
     tmem_ld_row32(trow + hColDS, srow);
-    if (tid == 0) {
-      bulk_wait_read();                  // the dZ images have left the P / dVn / dZ panels
-      if (c > 0) issue_p_load(c - 1);    // ... which now receive the next chunk's P
-    }
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();                     // every thread has copied its part of the dO / dZ image
+    if (tid == 0 && c > 0) issue_p_load(c - 1);    // the P / dVn / dZ panels now receive the next chunk's P
     if (c > 0) {
       prefetch_store(c - 1);
       __syncthreads();
@@ -386,7 +391,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
 #pragma unroll
     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
-  if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 256);
