@@ -1,6 +1,6 @@
 // Fused-recurrent gated delta rule (decode / short-sequence step) over a pool of per-sequence states.
 //
-// One CTA owns one (sequence, value-head) state matrix, streams it from HBM once with 16-byte
+// One CTA owns one (sequence, value-head) state matrix (128 of its value channels when V = 256), streams it from HBM once with 16-byte
 // loads, applies up to a few tokens of
 //     S <- exp(g) S  (scalar g per head and / or a per-key-channel gate gk: S <- diag(exp(gk)) S) ;
 //     d = beta (v - S^T k) ;  S <- S + k d^T ;  o = S^T (scale q)
@@ -74,11 +74,15 @@ __device__ __forceinline__ float load_scalar(const void* p, int64_t idx, int is_
 
 constexpr int kRecThreads = 256;
 
-// ROWS x COLS state tile as stored (COLS contiguous).  K-first: ROWS = K, COLS = V.  V-first: ROWS = V, COLS = K.
-template <int K, int V, typename ST, bool VFIRST>
+// ROWS x COLS state tile held by one CTA (COLS contiguous in memory, LD elements between rows).  The columns of V
+// are independent recurrences, so a CTA owns VT of the V value channels: K-first ROWS = K, COLS = VT, LD = V;
+// V-first ROWS = VT, COLS = K, LD = K.
+template <int K, int V, int VT, typename ST, bool VFIRST>
 __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentParams p) {
-  constexpr int ROWS = VFIRST ? V : K;
-  constexpr int COLS = VFIRST ? K : V;
+  constexpr int ROWS = VFIRST ? VT : K;
+  constexpr int COLS = VFIRST ? K : VT;
+  constexpr int LD = VFIRST ? K : V;
+  constexpr int NVB = V / VT;
   constexpr int TPR = COLS / 4;              // threads per row
   constexpr int RG = kRecThreads / TPR;      // row groups handled per pass
   constexpr int R = ROWS / RG;               // rows per thread
@@ -88,7 +92,10 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
   __shared__ __align__(16) float red[VFIRST ? 1 : RG][VFIRST ? 4 : COLS];
   __shared__ float norm_s[2];
 
-  const int seq = blockIdx.x / p.HV, hv = blockIdx.x % p.HV;
+  const int vb = blockIdx.x % NVB;
+  const int seq = (blockIdx.x / NVB) / p.HV, hv = (blockIdx.x / NVB) % p.HV;
+  const int v0 = vb * VT;                                   // first value channel of this CTA
+  const int64_t tile_off = VFIRST ? int64_t(v0) * LD : v0;  // offset of the tile inside the stored K x V (V x K) matrix
   const int hk = hv / (p.HV / p.HK);
   const int tid = threadIdx.x;
   const int rg = tid / TPR, c0 = (tid % TPR) * 4;
@@ -114,7 +121,7 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
   {
     const ST* src = static_cast<const ST*>(p.state_in) + blk * p.state_in_stride_b + hv * p.state_in_stride_h;
 #pragma unroll
-    for (int i = 0; i < R; ++i) s[i] = load4<ST>(src + int64_t(rg + i * RG) * COLS + c0);
+    for (int i = 0; i < R; ++i) s[i] = load4<ST>(src + tile_off + int64_t(rg + i * RG) * LD + c0);
   }
 
   for (int t = t0; t < t1; ++t) {
@@ -182,7 +189,7 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
         const float4 x = *reinterpret_cast<const float4*>(&red[r][c0]);
         dot.x += x.x; dot.y += x.y; dot.z += x.z; dot.w += x.w;
       }
-      const float4 vv = load4<__nv_bfloat16>(p.v + t * p.v_stride_t + hv * p.v_stride_h + c0);
+      const float4 vv = load4<__nv_bfloat16>(p.v + t * p.v_stride_t + hv * p.v_stride_h + v0 + c0);
       float4 d;
       d.x = beta * (vv.x - decay * dot.x); d.y = beta * (vv.y - decay * dot.y);
       d.z = beta * (vv.z - decay * dot.z); d.w = beta * (vv.w - decay * dot.w);
@@ -204,7 +211,7 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
           const float4 x = *reinterpret_cast<const float4*>(&red[r][c0]);
           o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
         }
-        const int64_t off = t * p.out_stride_t + hv * p.out_stride_h + c0;
+        const int64_t off = t * p.out_stride_t + hv * p.out_stride_h + v0 + c0;
         if (p.out_is_f32) store4<float>(static_cast<float*>(p.out) + off, o);
         else store4<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p.out) + off, o);
       }
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
       const float4 qq = make_float4(q_s[c0] * qscale, q_s[c0 + 1] * qscale, q_s[c0 + 2] * qscale, q_s[c0 + 3] * qscale);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        const int row = rg + i * RG;
+        const int row = v0 + rg + i * RG;
         float dot = s[i].x * kk.x + s[i].y * kk.y + s[i].z * kk.z + s[i].w * kk.w;
 #pragma unroll
         for (int o = TPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
@@ -240,21 +247,22 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentPar
     if (wblk >= 0 && wblk < p.nblocks_out) {
       ST* dst = static_cast<ST*>(p.state_out) + wblk * p.state_out_stride_b + hv * p.state_out_stride_h;
 #pragma unroll
-      for (int i = 0; i < R; ++i) store4<ST>(dst + int64_t(rg + i * RG) * COLS + c0, s[i]);
+      for (int i = 0; i < R; ++i) store4<ST>(dst + tile_off + int64_t(rg + i * RG) * LD + c0, s[i]);
     }
   }
 }
 
 template <int K, int V>
 int launch_recurrent(const RecurrentParams& p, int nseq, bool state_f32, bool vfirst, cudaStream_t st) {
-  const dim3 grid(nseq * p.HV), block(kRecThreads);
+  constexpr int VT = V > 128 ? 128 : V;
+  const dim3 grid(nseq * p.HV * (V / VT)), block(kRecThreads);
   KernelTimer kt("recurrent_gdn", st);
   if (state_f32) {
-    if (vfirst) recurrent_gdn_kernel<K, V, float, true><<<grid, block, 0, st>>>(p);
-    else recurrent_gdn_kernel<K, V, float, false><<<grid, block, 0, st>>>(p);
+    if (vfirst) recurrent_gdn_kernel<K, V, VT, float, true><<<grid, block, 0, st>>>(p);
+    else recurrent_gdn_kernel<K, V, VT, float, false><<<grid, block, 0, st>>>(p);
   } else {
-    if (vfirst) recurrent_gdn_kernel<K, V, __nv_bfloat16, true><<<grid, block, 0, st>>>(p);
-    else recurrent_gdn_kernel<K, V, __nv_bfloat16, false><<<grid, block, 0, st>>>(p);
+    if (vfirst) recurrent_gdn_kernel<K, V, VT, __nv_bfloat16, true><<<grid, block, 0, st>>>(p);
+    else recurrent_gdn_kernel<K, V, VT, __nv_bfloat16, false><<<grid, block, 0, st>>>(p);
   }
   return cuda_status(cudaGetLastError());
 }
@@ -361,5 +369,7 @@ extern "C" FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* a, v
   if (K == 64 && V == 64) return launch_recurrent<64, 64>(p, nseq, f32, vfirst, st);
   if (K == 64 && V == 128) return launch_recurrent<64, 128>(p, nseq, f32, vfirst, st);
   if (K == 128 && V == 64) return launch_recurrent<128, 64>(p, nseq, f32, vfirst, st);
+  if (K == 128 && V == 256) return launch_recurrent<128, 256>(p, nseq, f32, vfirst, st);
+  if (K == 64 && V == 256) return launch_recurrent<64, 256>(p, nseq, f32, vfirst, st);
   return FLA_ERR_SHAPE;
 }

@@ -22,7 +22,7 @@ def _oracle_decode(inp, N, tps, vfirst_state=None):
 
 
 @pytest.mark.parametrize("N,HK,HV,K,V,tps", [(4, 2, 4, 128, 128, 1), (3, 2, 2, 64, 64, 3), (2, 1, 2, 64, 128, 2),
-                                             (2, 2, 4, 128, 64, 1)])
+                                             (2, 2, 4, 128, 64, 1), (3, 2, 4, 128, 256, 2), (2, 1, 2, 64, 256, 1)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_fused_recurrent_matches_oracle(N, HK, HV, K, V, tps, out_dtype):
     from fla_b200.ops import fused_recurrent_gated_delta_rule

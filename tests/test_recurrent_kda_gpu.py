@@ -43,6 +43,21 @@ def test_recurrent_kda_matches_recurrence(B, T, H, HV, v_first):
     assert_close("state", ht.transpose(-1, -2) if v_first else ht, ref_s, 1e-5)
 
 
+@pytest.mark.parametrize("v_first", [False, True])
+def test_recurrent_kda_value_dim_256(v_first):
+    """K = 128, V = 256 (the reference accepts V up to 256): each state is updated by two CTAs of 128 value channels."""
+    from fla_b200.ops import recurrent_kda
+    B, T, H, HV = 2, 3, 2, 4
+    q, k, v, g, beta, state = _inputs(B, T, H, HV, seed=41, V=256)
+    scale = 128 ** -0.5
+    ref_o, ref_s = _ref(q, k, v, g, beta, state, scale)
+    pool = (state.transpose(-1, -2) if v_first else state).contiguous().cuda()
+    o, ht = recurrent_kda(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), pool, output_final_state=True,
+                          inplace_final_state=True, state_v_first=v_first)
+    assert_close("o", o, ref_o, 5e-3, stored_bf16=True)
+    assert_close("state", ht.transpose(-1, -2) if v_first else ht, ref_s, 1e-5)
+
+
 def test_recurrent_kda_gate_beta_activations_and_l2norm():
     from fla_b200.ops import recurrent_kda
     B, T, H, HV = 2, 3, 2, 4
