@@ -35,9 +35,9 @@ struct GdnBwdParams {
   const void* beta;
   const float* gam; const bf16* X;
   const bf16* s_img; const bf16* vn_img; const bf16* p_img;
-  bf16* ds_img;        // [chunks, HV, 2, 2, 128x64]  state gradient entering each chunk (hi, lo)
-  bf16* dz_img;        // [chunks, HV, 2, 128x64: rows 0-63 dO, rows 64-127 dZ rounded to bf16]
-  float* bz;           // [4, tokens, HV] partial sums of dZ * V over the four 32-column slices of V
+  bf16* ds_img;        // [chunks, HV, V/64, 2, 128x64]  state gradient entering each chunk (hi, lo)
+  bf16* dz_img;        // [chunks, HV, V/64, 128x64: rows 0-63 dO, rows 64-127 dZ rounded to bf16]
+  float* bz;           // [V/32, tokens, HV] partial sums of dZ * V over the 32-column slices of V
   const float* dht; float* dh0;
   void* dq; void* dk; void* dv; void* dg; void* dbeta;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
@@ -45,13 +45,14 @@ struct GdnBwdParams {
   int64_t dq_st, dq_sh, dk_st, dk_sh, dv_st, dv_sh;
   int64_t total_tokens;
   int N, T, HK, HV, beta_is_f32, grads_f32;
+  int V, nvb;          // value head dim (128 or 256) and its number of 64-column blocks
   float scale;
   int* status;
 };
 
-constexpr int64_t kSImg = 32768;   // bf16 elements of the state images per (chunk, head): 2 blocks x (hi, lo) x 128x64
-constexpr int64_t kVnImg = 16384;  // v_new images per (chunk, head): 2 x (hi, lo) x 64x64
-constexpr int64_t kDzImg = 16384;  // per (chunk, head): 2 x (64x64 dO + 64x64 dZ), single bf16
+constexpr int64_t kSImg = 16384;   // bf16 elements of the state images per (chunk, head, 64-column block of V): (hi, lo) x 128x64
+constexpr int64_t kVnImg = 8192;   // v_new images per (chunk, head, block): (hi, lo) x 64x64
+constexpr int64_t kDzImg = 8192;   // per (chunk, head, block): 64x64 dO + 64x64 dZ, single bf16
 
 // ============================================================================================= dhu
 constexpr uint32_t hOffQK = 0, hQKPanel = 16384;
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     issue_x_load(c_last);
   }
   if (p.dht) {
-    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       const float4 t = *reinterpret_cast<const float4*>(src + i);
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     qkphase ^= 1;
     {   // the split dS' copy is already in the panel-image format the chunk-parallel kernel loads: plain 16-byte copies by
         // all threads while the MMAs run (bulk stores would queue ahead of the next chunk's TMA loads)
-      uint4* dst = reinterpret_cast<uint4*>(p.ds_img + (cidx * 2 + vb) * (2 * 8192));
+      uint4* dst = reinterpret_cast<uint4*>(p.ds_img + (cidx * p.nvb + vb) * (2 * 8192));
       const uint4* src = reinterpret_cast<const uint4*>(smem + hOffDSH);
 #pragma unroll
       for (int i = 0; i < 8; ++i) dst[tid + i * kDhuThreads] = src[tid + i * kDhuThreads];
@@ -357,7 +358,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
       mma_commit(&bar);
     }
     {   // the [dO ; dZ] image of this V block: rows 0..63 from the dO panel, rows 64..127 from the dZ panel
-      uint4* dst = reinterpret_cast<uint4*>(p.dz_img + (cidx * 2 + vb) * 8192);
+      uint4* dst = reinterpret_cast<uint4*>(p.dz_img + (cidx * p.nvb + vb) * 8192);
       const uint4* s0 = reinterpret_cast<const uint4*>(smem + hOffDO);
       const uint4* s1 = reinterpret_cast<const uint4*>(smem + hOffPH);
       dst[tid] = s0[tid];
@@ -387,7 +388,7 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     for (int i = 0; i < 12; ++i) g_dhu_clocks[i] += dclk_[i];
 #endif
   if (!dead && p.dh0) {
-    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
@@ -469,10 +470,10 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   auto issue_loads = [&](int hv, int vb) {  // one thread: operands of one (value head, V block) step
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
     mbar_arrive_expect_tx(&load_bar, kStepBytes);
-    bulk_load(sb + rOffAH, p.dz_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + rOffVNH, p.vn_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + rOffSH, p.s_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
-    bulk_load(sb + rOffDSH, p.ds_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + rOffAH, p.dz_img + (cidx * p.nvb + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + rOffVNH, p.vn_img + (cidx * p.nvb + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + rOffSH, p.s_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + rOffDSH, p.ds_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
   };
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
@@ -562,11 +563,13 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     }
     asm volatile("bar.sync 2, 64;" ::: "memory");   // fin_s is free again
   };
-  auto load_bz = [&](int hvf) -> float {   // sum of the reverse scan's four partial row sums of dZ . V
+  auto load_bz = [&](int hvf) -> float {   // sum of the reverse scan's partial row sums of dZ . V (one per 32 columns of V)
     if (tid >= rows) return 0.f;
     const int64_t gidx = (tok0 + tid) * p.HV + hvf;
     const int64_t bzs = p.total_tokens * p.HV;
-    return (p.bz[gidx] + p.bz[bzs + gidx]) + (p.bz[2 * bzs + gidx] + p.bz[3 * bzs + gidx]);
+    float acc = 0.f;
+    for (int i = 0; i < p.nvb; ++i) acc += p.bz[(2 * i) * bzs + gidx] + p.bz[(2 * i + 1) * bzs + gidx];
+    return acc;
   };
 
   PSTAMP(0);
@@ -584,7 +587,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     if (h + 1 < G) prefetch_scalars(hv + 1);
     const float bz_cur = load_bz(hv);     // lands while the step's operands are awaited
     float sds = 0.f;
-    for (int vb = 0; vb < 2; ++vb) {
+    for (int vb = 0; vb < p.nvb; ++vb) {
       PSTAMP(1);
       ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT);
       lphase ^= 1;
@@ -624,7 +627,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
       PSTAMP(4);
       tc_fence_after();
       if (tid == 0) {
-        if (vb == 0) issue_loads(hv, 1);
+        if (vb + 1 < p.nvb) issue_loads(hv, vb + 1);
         else if (h + 1 < G) issue_loads(hv + 1, 0);
       }
     }
@@ -764,12 +767,12 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
 
 using namespace fla;
 
-static uint64_t bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t tokens, uint64_t* off_ds, uint64_t* off_dz,
+static uint64_t bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t nvb, int64_t tokens, uint64_t* off_ds, uint64_t* off_dz,
                               uint64_t* off_bz) {
   uint64_t o = 256;  // status block
-  *off_ds = o; o += align_up(uint64_t(total_chunks) * HV * kSImg * 2, 256);
-  *off_dz = o; o += align_up(uint64_t(total_chunks) * HV * kDzImg * 2, 256);
-  *off_bz = o; o += align_up(uint64_t(4) * tokens * HV * 4, 256);
+  *off_ds = o; o += align_up(uint64_t(total_chunks) * HV * nvb * kSImg * 2, 256);
+  *off_dz = o; o += align_up(uint64_t(total_chunks) * HV * nvb * kDzImg * 2, 256);
+  *off_bz = o; o += align_up(uint64_t(2 * nvb) * tokens * HV * 4, 256);
   return o;
 }
 
@@ -797,7 +800,9 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd_workspace_size(const fla_gdn_chunk
   int st = bwd_geometry(a, &total_chunks, &N, &max_len);
   if (st) return st;
   uint64_t o1, o2, o3;
-  *bytes = bwd_ws_layout(total_chunks, a->v.shape[2], a->q.shape[0] * a->q.shape[1], &o1, &o2, &o3);
+  const int64_t V = a->v.shape[3];
+  if (V != kV && V != 2 * kV) return FLA_ERR_SHAPE;
+  *bytes = bwd_ws_layout(total_chunks, a->v.shape[2], V / kBV, a->q.shape[0] * a->q.shape[1], &o1, &o2, &o3);
   return FLA_OK;
 }
 
@@ -827,13 +832,15 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   if (st) return st;
   const int64_t B = a->q.shape[0], T = a->q.shape[1], HK = a->q.shape[2], HV = a->v.shape[2];
   if (HK <= 0 || HV <= 0 || HV % HK) return FLA_ERR_SHAPE;
+  const int64_t V = a->v.shape[3], nvb = V / kBV;
+  if (V != kV && V != 2 * kV) return FLA_ERR_SHAPE;
   if ((st = check_tok4(a->q, B, T, HK, kK, false))) return st;
   if ((st = check_tok4(a->k, B, T, HK, kK, false))) return st;
-  if ((st = check_tok4(a->v, B, T, HV, kV, false))) return st;
-  if ((st = check_tok4(a->d_o, B, T, HV, kV, false))) return st;
+  if ((st = check_tok4(a->v, B, T, HV, V, false))) return st;
+  if ((st = check_tok4(a->d_o, B, T, HV, V, false))) return st;
   if ((st = check_tok4(a->dq, B, T, HK, kK, true))) return st;
   if ((st = check_tok4(a->dk, B, T, HK, kK, true))) return st;
-  if ((st = check_tok4(a->dv, B, T, HV, kV, true))) return st;
+  if ((st = check_tok4(a->dv, B, T, HV, V, true))) return st;
   if ((st = check_tok3(a->beta, B, T, HV, false))) return st;
   if ((st = check_tok3(a->dg, B, T, HV, true))) return st;
   if ((st = check_tok3(a->dbeta, B, T, HV, true))) return st;
@@ -849,20 +856,20 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
     return FLA_ERR_SHAPE;
   if (a->p_img.dtype != FLA_BF16 || a->p_img.ndim != 1 || a->p_img.shape[0] != total_chunks * HV * 8192 || !aligned16(a->p_img.data))
     return FLA_ERR_SHAPE;
-  if (a->s_img.dtype != FLA_BF16 || a->s_img.ndim != 1 || a->s_img.shape[0] != total_chunks * HV * kSImg || !aligned16(a->s_img.data))
+  if (a->s_img.dtype != FLA_BF16 || a->s_img.ndim != 1 || a->s_img.shape[0] != total_chunks * HV * nvb * kSImg || !aligned16(a->s_img.data))
     return FLA_ERR_SHAPE;
-  if (a->vn_img.dtype != FLA_BF16 || a->vn_img.ndim != 1 || a->vn_img.shape[0] != total_chunks * HV * kVnImg || !aligned16(a->vn_img.data))
+  if (a->vn_img.dtype != FLA_BF16 || a->vn_img.ndim != 1 || a->vn_img.shape[0] != total_chunks * HV * nvb * kVnImg || !aligned16(a->vn_img.data))
     return FLA_ERR_SHAPE;
   for (const fla_tensor_t* s : {&a->dht, &a->dh0}) {
     if (!s->data) continue;
     if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
-    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
-    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != HV * kK * kV || !aligned16(s->data))
+    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != V) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != V || s->stride[1] != kK * V || s->stride[0] != HV * kK * V || !aligned16(s->data))
       return FLA_ERR_LAYOUT;
   }
   if (a->chunk_size != kC) return FLA_ERR_VALUE;
   uint64_t off_ds, off_dz, off_bz;
-  const uint64_t need = bwd_ws_layout(total_chunks, HV, B * T, &off_ds, &off_dz, &off_bz);
+  const uint64_t need = bwd_ws_layout(total_chunks, HV, nvb, B * T, &off_ds, &off_dz, &off_bz);
   if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
 
   GdnBwdParams p{};
@@ -886,7 +893,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   p.dq_st = a->dq.stride[1]; p.dq_sh = a->dq.stride[2]; p.dk_st = a->dk.stride[1]; p.dk_sh = a->dk.stride[2];
   p.dv_st = a->dv.stride[1]; p.dv_sh = a->dv.stride[2];
   p.total_tokens = B * T;
-  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV);
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.V = int(V); p.nvb = int(nvb);
   p.beta_is_f32 = a->beta.dtype == FLA_F32; p.grads_f32 = gdt == FLA_F32;
   p.scale = a->scale;
 
@@ -907,7 +914,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
     return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_bwd_dhu", cs);
-    gdn_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), kDhuThreads, kDhuSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
+    gdn_bwd_dhu_kernel<<<dim3(unsigned(nvb), unsigned(HV), N), kDhuThreads, kDhuSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   const int nt_max = (max_len + kC - 1) / kC;

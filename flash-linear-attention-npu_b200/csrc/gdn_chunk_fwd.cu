@@ -37,11 +37,12 @@ struct GdnFwdParams {
   const float* h0;     // [N, HV, K, V] or null
   float* ht;           // [N, HV, K, V] or null
   void* o;             // [tokens, HV, V]
-  bf16* s_img;         // [chunks, HV, 2, 2, 128x64] panel images of the state at chunk start (hi, lo), optional
-  bf16* vn_img;        // [chunks, HV, 2, 2, 64x64]  panel images of v_new (hi, lo), optional
+  bf16* s_img;         // [chunks, HV, V/64, 2, 128x64] panel images of the state at chunk start (hi, lo), optional
+  bf16* vn_img;        // [chunks, HV, V/64, 2, 64x64]  panel images of v_new (hi, lo), optional
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int64_t q_st, q_sh, k_st, k_sh, v_st, v_sh, o_st, o_sh, g_st, beta_st;
   int N, T, HK, HV, g_is_f32, beta_is_f32, o_is_f32;
+  int V, nvb;          // value head dim (128 or 256) and its number of 64-column blocks
   float scale;
   int* status;
 };
@@ -334,7 +335,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
   store_scalars(0);
   store_panels();
   if (p.h0) {
-    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       const float4 t = *reinterpret_cast<const float4*>(src + i);
@@ -382,7 +383,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     qkphase ^= 1;
     if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format: plain 16-byte
                     // copies by all threads while the MMAs run (bulk stores would queue ahead of the chunk's TMA loads)
-      uint4* dst = reinterpret_cast<uint4*>(p.s_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 8192));
+      uint4* dst = reinterpret_cast<uint4*>(p.s_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * p.nvb + vb) * (2 * 8192));
       const uint4* src = reinterpret_cast<const uint4*>(smem + kOffSH);
 #pragma unroll
       for (int i = 0; i < 8; ++i) dst[tid + i * kFwdThreads] = src[tid + i * kFwdThreads];
@@ -466,7 +467,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     }
     pphase ^= 1;
     if (p.vn_img) {
-      uint4* dst = reinterpret_cast<uint4*>(p.vn_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * 2 + vb) * (2 * 4096));
+      uint4* dst = reinterpret_cast<uint4*>(p.vn_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * p.nvb + vb) * (2 * 4096));
       const uint4* src = reinterpret_cast<const uint4*>(smem + kOffZH);     // Z_hi and Z_lo panels are adjacent
 #pragma unroll
       for (int i = 0; i < 4; ++i) dst[tid + i * kFwdThreads] = src[tid + i * kFwdThreads];
@@ -511,7 +512,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     for (int i = 0; i < 12; ++i) g_stage_clocks[i] += fclk_[i];
 #endif
   if (!dead && p.ht) {
-    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
@@ -565,8 +566,10 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   int st;
   if ((st = check_token_tensor(q, HK, kK, FLA_BF16, FLA_BF16))) return st;
   if ((st = check_token_tensor(k, HK, kK, FLA_BF16, FLA_BF16))) return st;
-  if ((st = check_token_tensor(v, HV, kV, FLA_BF16, FLA_BF16))) return st;
-  if ((st = check_token_tensor(o, HV, kV, FLA_BF16, FLA_F32))) return st;
+  const int64_t V = v.shape[3];
+  if (V != kV && V != 2 * kV) return FLA_ERR_SHAPE;
+  if ((st = check_token_tensor(v, HV, V, FLA_BF16, FLA_BF16))) return st;
+  if ((st = check_token_tensor(o, HV, V, FLA_BF16, FLA_F32))) return st;
   if (k.shape[0] != B || k.shape[1] != T || o.shape[0] != B || o.shape[1] != T) return FLA_ERR_SHAPE;
   if ((st = check_gate_tensor(a->g, B, T, HV))) return st;
   if ((st = check_gate_tensor(a->beta, B, T, HV))) return st;
@@ -595,8 +598,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   for (const fla_tensor_t* s : {&a->initial_state, &a->final_state}) {
     if (!s->data) continue;
     if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
-    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
-    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != HV * kK * kV || !aligned16(s->data))
+    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != V) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != V || s->stride[1] != kK * V || s->stride[0] != HV * kK * V || !aligned16(s->data))
       return FLA_ERR_LAYOUT;
   }
   GdnFwdParams p{};
@@ -608,8 +611,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   if (a->s_img.data || a->vn_img.data) {
     const fla_tensor_t &si = a->s_img, &vi = a->vn_img;
     if (!si.data || !vi.data) return FLA_ERR_NULL;
-    if (si.dtype != FLA_BF16 || si.ndim != 1 || si.shape[0] != total_chunks * HV * 32768 || !aligned16(si.data)) return FLA_ERR_SHAPE;
-    if (vi.dtype != FLA_BF16 || vi.ndim != 1 || vi.shape[0] != total_chunks * HV * 16384 || !aligned16(vi.data)) return FLA_ERR_SHAPE;
+    if (si.dtype != FLA_BF16 || si.ndim != 1 || si.shape[0] != total_chunks * HV * (V / kBV) * 16384 || !aligned16(si.data)) return FLA_ERR_SHAPE;
+    if (vi.dtype != FLA_BF16 || vi.ndim != 1 || vi.shape[0] != total_chunks * HV * (V / kBV) * 8192 || !aligned16(vi.data)) return FLA_ERR_SHAPE;
     p.s_img = static_cast<bf16*>(si.data);
     p.vn_img = static_cast<bf16*>(vi.data);
   }
@@ -618,7 +621,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   p.q_st = q.stride[1]; p.q_sh = q.stride[2]; p.k_st = k.stride[1]; p.k_sh = k.stride[2];
   p.v_st = v.stride[1]; p.v_sh = v.stride[2]; p.o_st = o.stride[1]; p.o_sh = o.stride[2];
   p.g_st = a->g.stride[1]; p.beta_st = a->beta.stride[1];
-  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV);
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.V = int(V); p.nvb = int(V / kBV);
   p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = a->beta.dtype == FLA_F32; p.o_is_f32 = o.dtype == FLA_F32;
   p.scale = a->scale;
   p.status = static_cast<int*>(workspace);
@@ -665,7 +668,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
     return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_fwd", cs);
-    gdn_fwd_kernel<<<dim3(kV / kBV, unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
+    gdn_fwd_kernel<<<dim3(unsigned(p.nvb), unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
   }
   return cuda_status(cudaGetLastError());
 }

@@ -53,8 +53,8 @@ def gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
         raise RuntimeError(f"{op}: expected q,k [B,T,HK,K] and v [B,T,HV,V], got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
     B, T, HK, K = q.shape
     HV, V = v.shape[2], v.shape[3]
-    if K != 128 or V != 128:
-        raise RuntimeError(f"{op}: this build supports K = V = 128, got K={K}, V={V}")
+    if K != 128 or V not in (128, 256):
+        raise RuntimeError(f"{op}: this build supports K = 128 and V = 128 or 256, got K={K}, V={V}")
     if HV % HK:
         raise RuntimeError(f"{op}: HV={HV} must be a multiple of HK={HK}")
     if tuple(g.shape) != (B, T, HV) or tuple(beta.shape) != (B, T, HV):
@@ -79,8 +79,8 @@ def gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     x_inv = torch.empty((B, T, HV, CHUNK), dtype=torch.bfloat16, device=dev)
     s_img = vn_img = p_img = None
     if save_for_backward:
-        s_img = torch.empty(total_chunks * HV * 32768, dtype=torch.bfloat16, device=dev)
-        vn_img = torch.empty(total_chunks * HV * 16384, dtype=torch.bfloat16, device=dev)
+        s_img = torch.empty(total_chunks * HV * (V // 64) * 16384, dtype=torch.bfloat16, device=dev)
+        vn_img = torch.empty(total_chunks * HV * (V // 64) * 8192, dtype=torch.bfloat16, device=dev)
         p_img = torch.empty(total_chunks * HV * 8192, dtype=torch.bfloat16, device=dev)
     a = GdnChunkFwdArgs()
     a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)

@@ -14,13 +14,13 @@ TOL = 5e-3
 NAMES = ("dq", "dk", "dv", "dg", "dbeta")
 
 
-def _ref_and_inputs(B, T, HK, HV, seed, cu=None, h0=True):
-    inp = oracle.make_gdn_inputs(B, T, HK, HV, seed=seed, h0_scale=0.1 if h0 else 0.0)
+def _ref_and_inputs(B, T, HK, HV, seed, cu=None, h0=True, V=128):
+    inp = oracle.make_gdn_inputs(B, T, HK, HV, V=V, seed=seed, h0_scale=0.1 if h0 else 0.0)
     N = B if cu is None else len(cu) - 1
     if cu is not None:
         gen = torch.Generator().manual_seed(seed + 1)
-        inp["h0"] = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float() if h0 else None
-        inp["dht"] = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float()
+        inp["h0"] = (0.1 * torch.randn(N, HV, 128, V, generator=gen)).float() if h0 else None
+        inp["dht"] = (0.1 * torch.randn(N, HV, 128, V, generator=gen)).float()
     ref = oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"],
                                        do=inp["do"], dht=inp["dht"], dtype=torch.float64, cu_seqlens=cu)
     d = {n: (t.cuda() if t is not None else None) for n, t in inp.items()}
@@ -34,6 +34,23 @@ def test_backward_fp32_grads(B, T, HK, HV):
     o, ht, grads = chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
                                                   dht=d["dht"], output_dtype=torch.float32, grad_dtype=torch.float32)
     torch.cuda.synchronize()
+    assert_close("o", o, ref["o"], TOL)
+    assert_close("ht", ht, ref["ht"], TOL)
+    for name, got in zip(NAMES + ("dh0",), grads):
+        assert_close(name, got, ref[name], TOL)
+
+
+@pytest.mark.parametrize("B,T,HK,HV,cu", [(2, 256, 1, 2, None), (1, 100, 2, 2, None),
+                                          (1, 300, 1, 2, [0, 70, 71, 200, 300])])
+def test_value_dim_256(B, T, HK, HV, cu):
+    """V = 256 (the reference's second tiling key for the value head): four 64-column blocks of V per head."""
+    from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
+    ref, d = _ref_and_inputs(B, T, HK, HV, seed=4100 + T, cu=cu, V=256)
+    o, ht, grads = chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
+                                                  dht=d["dht"], output_dtype=torch.float32, grad_dtype=torch.float32,
+                                                  cu_seqlens=None if cu is None else torch.tensor(cu, dtype=torch.int32))
+    torch.cuda.synchronize()
+    assert o.shape[-1] == 256 and ht.shape[-1] == 256
     assert_close("o", o, ref["o"], TOL)
     assert_close("ht", ht, ref["ht"], TOL)
     for name, got in zip(NAMES + ("dh0",), grads):
