@@ -33,9 +33,9 @@ struct KdaBwdParams {
   const bf16* qk_img; const bf16* kn_img; const bf16* p_img; const bf16* x_img;
   const float* vec; const float* gk;
   const bf16* s_img; const bf16* vn_img;
-  bf16* ds_img;        // [chunks, HV, 2, {hi, lo}, 128x64]  dS'a entering each chunk
-  bf16* dz_img;        // [chunks, HV, 2, {64x64 dO, 64x64 dZ hi, 64x64 dZ lo}]
-  float* bz;           // [4, tokens, HV] partial sums of dZ * V over the four 32-column slices of V
+  bf16* ds_img;        // [chunks, HV, V/64, {hi, lo}, 128x64]  dS'a entering each chunk
+  bf16* dz_img;        // [chunks, HV, V/64, {64x64 dO, 64x64 dZ hi, 64x64 dZ lo}]
+  float* bz;           // [V/32, tokens, HV] partial sums of dZ * V over the 32-column slices of V
   const float* dht; float* dh0;
   void* dq; void* dk; void* dv; void* dg; void* dbeta;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
@@ -43,11 +43,12 @@ struct KdaBwdParams {
   int64_t dq_st, dq_sh, dk_st, dk_sh, dv_st, dv_sh, dg_st, dg_sh;
   int64_t total_tokens;
   int N, T, HK, HV, beta_is_f32, grads_f32;
+  int V, nvb;          // value head dim (128 or 256) and its number of 64-column blocks
   float scale;
   int* status;
 };
 
-constexpr int64_t kKdaDsImg = 32768, kKdaDzImg = 24576;   // bf16 elements per (chunk, head)
+constexpr int64_t kKdaDsImg = 16384, kKdaDzImg = 12288;   // bf16 elements per (chunk, head, 64-column block of V)
 
 // ============================================================================================= dhu
 constexpr uint32_t dOffQKH = 0, dOffQKL = 32768, dOffKNH = 65536, dOffKNL = 81920;
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_dhu_kernel(KdaBwdParams p) {
   prefetch_load(c_last);
   prefetch_store(c_last);
   if (p.dht) {
-    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       const float4 t = *reinterpret_cast<const float4*>(src + i);
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_dhu_kernel(KdaBwdParams p) {
 
     // ---- stage 1: W1 = Kn dS'a  and  U1 = P^T dO  (valid accumulator rows 64..127)
     if (tid == 0) {
-      bulk_store(p.ds_img + (cidx * 2 + vb) * 16384, sb + dOffDSH, 32768);
+      bulk_store(p.ds_img + (cidx * p.nvb + vb) * 16384, sb + dOffDSH, 32768);
       bulk_commit();
       if (!mbar_wait(&kn_bar, knphase, p.status, FLA_ERR_TIMEOUT)) dead = true;
       mma_tile(tbase + dColW1, opKnAh, opDSH, 128, 64, 8, false);
@@ -290,7 +291,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_dhu_kernel(KdaBwdParams p) {
 
     // ---- stage 5: dSa += [Qp^T | Kp^T] [scale dO ; -beta dZ]
     if (tid == 0) {
-      bf16* dst = p.dz_img + (cidx * 2 + vb) * 12288;
+      bf16* dst = p.dz_img + (cidx * p.nvb + vb) * 12288;
       bulk_store(dst, sb + dOffDO, 8192);            // dO
       bulk_store(dst + 4096, sb + dOffPH, 16384);    // dZ hi, dZ lo
       bulk_commit();
@@ -326,7 +327,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_dhu_kernel(KdaBwdParams p) {
   }
 
   if (!dead && p.dh0) {
-    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
@@ -456,12 +457,12 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
   auto issue_loads = [&](int hv, int vb) {    // one thread: operands of one (value head, V block) step
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
     mbar_arrive_expect_tx(&load_bar, kKdaStepBytes);
-    const bf16* dz = p.dz_img + (cidx * 2 + vb) * 12288;
+    const bf16* dz = p.dz_img + (cidx * p.nvb + vb) * 12288;
     bulk_load(sb + qOffAH, dz, 16384, &load_bar);
     bulk_load(sb + qOffAL + 8192, dz + 8192, 8192, &load_bar);
-    bulk_load(sb + qOffVNH, p.vn_img + (cidx * 2 + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + qOffSH, p.s_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
-    bulk_load(sb + qOffDSH, p.ds_img + (cidx * 2 + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + qOffVNH, p.vn_img + (cidx * p.nvb + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + qOffSH, p.s_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + qOffDSH, p.ds_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
   };
 
   const Operand opQKh{sb + qOffQKH, 16384, 0}, opQKl{sb + qOffQKL, 16384, 0};           // [Qp; Kp], reduction over key dims
@@ -497,7 +498,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
     }
     float sds = 0.f;   // my key channel (tid & 127), my 32 columns (tid >> 7) of sum_v dS'a * Sa
     KSTAMP(0);
-    for (int vb = 0; vb < 2; ++vb) {
+    for (int vb = 0; vb < p.nvb; ++vb) {
       if (vb == 0) {
         ok = mbar_wait(&img_bar, iphase, p.status, FLA_ERR_TIMEOUT);
         iphase ^= 1;
@@ -544,8 +545,8 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
       KSTAMP(3);
       tc_fence_after();
       if (tid == 0) {
-        if (vb == 0) {
-          issue_loads(hv, 1);
+        if (vb + 1 < p.nvb) {
+          issue_loads(hv, vb + 1);
         } else {   // the phase-1 buffers are free: this head's gk rows, channels 32 b .. 32 b + 31 in tile b
           mbar_arrive_expect_tx(&gk_bar, 4 * 8192);
 #pragma unroll
@@ -630,7 +631,8 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
       const int i = tid;
       const int64_t gidx = (tok0 + i) * p.HV + hv;
       const int64_t bzs = p.total_tokens * p.HV;
-      const float bz = (p.bz[gidx] + p.bz[bzs + gidx]) + (p.bz[2 * bzs + gidx] + p.bz[3 * bzs + gidx]);
+      float bz = 0.f;
+      for (int s = 0; s < p.nvb; ++s) bz += p.bz[(2 * s) * bzs + gidx] + p.bz[(2 * s + 1) * bzs + gidx];
       const float db = bz - (red[0][0][i] + red[0][1][i]) + (red[1][0][i] + red[1][1][i]);
       if (p.grads_f32) static_cast<float*>(p.dbeta)[gidx] = db;
       else static_cast<bf16*>(p.dbeta)[gidx] = __float2bfloat16_rn(db);
@@ -781,15 +783,15 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
 using namespace fla;
 
 // Workspace: status | [forward workspace | gk | s_img | vn_img unless the caller passes the forward's saved buffer] | ds_img | dz_img | bz
-static uint64_t kda_bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t tokens, bool have_saved, uint64_t* off_saved,
+static uint64_t kda_bwd_ws_layout(int64_t total_chunks, int64_t HV, int64_t nvb, int64_t tokens, bool have_saved, uint64_t* off_saved,
                                   uint64_t off[3]) {
   const uint64_t per = uint64_t(total_chunks) * HV;
   uint64_t o = 256, so[4];
   *off_saved = o;
-  if (!have_saved) o += align_up(kda_saved_layout(total_chunks, HV, tokens, so), 256);
-  off[0] = o; o += align_up(per * kKdaDsImg * 2, 256);
-  off[1] = o; o += align_up(per * kKdaDzImg * 2, 256);
-  off[2] = o; o += align_up(uint64_t(4) * tokens * HV * 4, 256);
+  if (!have_saved) o += align_up(kda_saved_layout(total_chunks, HV, nvb, tokens, so), 256);
+  off[0] = o; o += align_up(per * nvb * kKdaDsImg * 2, 256);
+  off[1] = o; o += align_up(per * nvb * kKdaDzImg * 2, 256);
+  off[2] = o; o += align_up(uint64_t(2 * nvb) * tokens * HV * 4, 256);
   return o;
 }
 
@@ -817,7 +819,9 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd_workspace_size(const fla_kda_chunk
   const int st = kda_bwd_geometry(a, &total_chunks, &N, &max_len);
   if (st) return st;
   uint64_t off[3], off_saved;
-  *bytes = kda_bwd_ws_layout(total_chunks, a->v.shape[2], a->q.shape[0] * a->q.shape[1], a->saved.data != nullptr, &off_saved, off);
+  const int64_t V = a->v.shape[3];
+  if (V != kV && V != 2 * kV) return FLA_ERR_SHAPE;
+  *bytes = kda_bwd_ws_layout(total_chunks, a->v.shape[2], V / kBV, a->q.shape[0] * a->q.shape[1], a->saved.data != nullptr, &off_saved, off);
   return FLA_OK;
 }
 
@@ -847,14 +851,16 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   if (st) return st;
   const int64_t B = a->q.shape[0], T = a->q.shape[1], HK = a->q.shape[2], HV = a->v.shape[2];
   if (HK <= 0 || HV <= 0 || HV % HK) return FLA_ERR_SHAPE;
+  const int64_t V = a->v.shape[3], nvb = V / kBV;
+  if (V != kV && V != 2 * kV) return FLA_ERR_SHAPE;
   if ((st = kda_bwd_check_tok(a->q, B, T, HK, kK, false))) return st;
   if ((st = kda_bwd_check_tok(a->k, B, T, HK, kK, false))) return st;
-  if ((st = kda_bwd_check_tok(a->v, B, T, HV, kV, false))) return st;
+  if ((st = kda_bwd_check_tok(a->v, B, T, HV, V, false))) return st;
   if ((st = kda_bwd_check_tok(a->g, B, T, HV, kK, true))) return st;
-  if ((st = kda_bwd_check_tok(a->d_o, B, T, HV, kV, false))) return st;
+  if ((st = kda_bwd_check_tok(a->d_o, B, T, HV, V, false))) return st;
   if ((st = kda_bwd_check_tok(a->dq, B, T, HK, kK, true))) return st;
   if ((st = kda_bwd_check_tok(a->dk, B, T, HK, kK, true))) return st;
-  if ((st = kda_bwd_check_tok(a->dv, B, T, HV, kV, true))) return st;
+  if ((st = kda_bwd_check_tok(a->dv, B, T, HV, V, true))) return st;
   if ((st = kda_bwd_check_tok(a->dg, B, T, HV, kK, true))) return st;
   if ((st = kda_bwd_check_tok3(a->beta, B, T, HV, false))) return st;
   if ((st = kda_bwd_check_tok3(a->dbeta, B, T, HV, true))) return st;
@@ -863,16 +869,16 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   for (const fla_tensor_t* s : {&a->initial_state, &a->dht, &a->dh0}) {
     if (!s->data) continue;
     if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
-    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
-    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != HV * kK * kV || !aligned16(s->data))
+    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != V) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != V || s->stride[1] != kK * V || s->stride[0] != HV * kK * V || !aligned16(s->data))
       return FLA_ERR_LAYOUT;
   }
   if (a->chunk_size != kC) return FLA_ERR_VALUE;
   uint64_t off[3], off_saved, so[4], fo[6];
   const bool have_saved = a->saved.data != nullptr;
-  const uint64_t need = kda_bwd_ws_layout(total_chunks, HV, B * T, have_saved, &off_saved, off);
+  const uint64_t need = kda_bwd_ws_layout(total_chunks, HV, nvb, B * T, have_saved, &off_saved, off);
   if (!workspace || workspace_bytes < need || !aligned16(workspace)) return FLA_ERR_WORKSPACE;
-  const uint64_t sbytes = kda_saved_layout(total_chunks, HV, B * T, so);
+  const uint64_t sbytes = kda_saved_layout(total_chunks, HV, nvb, B * T, so);
   if (have_saved && (a->saved.dtype != FLA_BF16 || a->saved.ndim != 1 || uint64_t(a->saved.shape[0]) * 2 < sbytes ||
                      !aligned16(a->saved.data)))
     return FLA_ERR_SHAPE;
@@ -896,7 +902,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   f.q_st = a->q.stride[1]; f.q_sh = a->q.stride[2]; f.k_st = a->k.stride[1]; f.k_sh = a->k.stride[2];
   f.v_st = a->v.stride[1]; f.v_sh = a->v.stride[2];
   f.g_st = a->g.stride[1]; f.g_sh = a->g.stride[2]; f.beta_st = a->beta.stride[1];
-  f.N = N; f.T = int(T); f.HK = int(HK); f.HV = int(HV); f.total_tokens = B * T;
+  f.N = N; f.T = int(T); f.HK = int(HK); f.HV = int(HV); f.total_tokens = B * T; f.V = int(V); f.nvb = int(nvb);
   f.g_is_f32 = a->g.dtype == FLA_F32; f.beta_is_f32 = a->beta.dtype == FLA_F32;
   f.gate_mode = 0; f.scale = a->scale;
 
@@ -913,7 +919,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   p.dq_st = a->dq.stride[1]; p.dq_sh = a->dq.stride[2]; p.dk_st = a->dk.stride[1]; p.dk_sh = a->dk.stride[2];
   p.dv_st = a->dv.stride[1]; p.dv_sh = a->dv.stride[2]; p.dg_st = a->dg.stride[1]; p.dg_sh = a->dg.stride[2];
   p.total_tokens = B * T;
-  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV);
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.V = int(V); p.nvb = int(nvb);
   p.beta_is_f32 = f.beta_is_f32; p.grads_f32 = gdt == FLA_F32;
   p.scale = a->scale;
   p.status = f.status;
@@ -932,7 +938,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   }
   {
     KernelTimer kt("kda_bwd_dhu", cs);
-    kda_bwd_dhu_kernel<<<dim3(kV / kBV, unsigned(HV), N), 256, kKdaDhuSmem + 1024, cs>>>(p);
+    kda_bwd_dhu_kernel<<<dim3(unsigned(nvb), unsigned(HV), N), 256, kKdaDhuSmem + 1024, cs>>>(p);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   CUtensorMap tm_gk;

@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
   store_scalars(0);
   take_values();
   if (p.h0) {
-    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       const float4 t = *reinterpret_cast<const float4*>(src + i);
@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
     if (tid == 0) {
       if (p.s_img) {
         const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
-        bulk_store(p.s_img + (cidx * 2 + vb) * 16384, sb + fOffSH, 32768);
+        bulk_store(p.s_img + (cidx * p.nvb + vb) * 16384, sb + fOffSH, 32768);
         bulk_commit();
       }
       mma_tile(tbase + fColRQ, opQKH, opSH, 128, 64, 8, false);
@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
     if (tid == 0) {
       if (p.vn_img) {
         const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
-        bulk_store(p.vn_img + (cidx * 2 + vb) * 8192, sb + fOffZH, 16384);
+        bulk_store(p.vn_img + (cidx * p.nvb + vb) * 8192, sb + fOffZH, 16384);
         bulk_commit();
       }
       mma_tile(tbase + fColPV, opPH, opZH, 128, 64, 4, false);
@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
   }
 
   if (!dead && p.ht) {
-    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * kV + vb * kBV + c0;
+    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
   }
@@ -563,14 +563,14 @@ uint64_t fla::kda_ws_layout(int64_t total_chunks, int64_t HV, uint64_t off[6]) {
   return o;
 }
 
-uint64_t fla::kda_saved_layout(int64_t total_chunks, int64_t HV, int64_t tokens, uint64_t off[4]) {
+uint64_t fla::kda_saved_layout(int64_t total_chunks, int64_t HV, int64_t nvb, int64_t tokens, uint64_t off[4]) {
   uint64_t fo[6];
   const uint64_t per = uint64_t(total_chunks) * HV;
   uint64_t o = 0;
   off[0] = o; o += align_up(kda_ws_layout(total_chunks, HV, fo), 256);
   off[1] = o; o += align_up(uint64_t(tokens) * HV * kK * 4, 256);
-  off[2] = o; o += align_up(per * kKdaSImg * 2, 256);
-  off[3] = o; o += align_up(per * kKdaVnImg * 2, 256);
+  off[2] = o; o += align_up(per * nvb * kKdaSImg * 2, 256);
+  off[3] = o; o += align_up(per * nvb * kKdaVnImg * 2, 256);
   return o;
 }
 
@@ -608,7 +608,9 @@ extern "C" FLA_API int fla_b200_kda_chunk_saved_size(const fla_kda_chunk_fwd_arg
   const int st = kda_geometry(a, &total_chunks, &N, &max_len);
   if (st) return st;
   uint64_t off[4];
-  *bytes = kda_saved_layout(total_chunks, a->v.shape[2], a->q.shape[0] * a->q.shape[1], off);
+  const int64_t V = a->v.shape[3];
+  if (V != kV && V != 2 * kV) return FLA_ERR_SHAPE;
+  *bytes = kda_saved_layout(total_chunks, a->v.shape[2], V / kBV, a->q.shape[0] * a->q.shape[1], off);
   return FLA_OK;
 }
 
@@ -630,11 +632,13 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   if (st) return st;
   const int64_t B = a->q.shape[0], T = a->q.shape[1], HK = a->q.shape[2], HV = a->v.shape[2];
   if (HK <= 0 || HV <= 0 || HV % HK) return FLA_ERR_SHAPE;
+  const int64_t V = a->v.shape[3];
+  if (V != kV && V != 2 * kV) return FLA_ERR_SHAPE;
   if ((st = kda_check_tok(a->q, B, T, HK, kK, false))) return st;
   if ((st = kda_check_tok(a->k, B, T, HK, kK, false))) return st;
-  if ((st = kda_check_tok(a->v, B, T, HV, kV, false))) return st;
+  if ((st = kda_check_tok(a->v, B, T, HV, V, false))) return st;
   if ((st = kda_check_tok(a->g, B, T, HV, kK, true))) return st;
-  if ((st = kda_check_tok(a->o, B, T, HV, kV, true))) return st;
+  if ((st = kda_check_tok(a->o, B, T, HV, V, true))) return st;
   const fla_tensor_t& be = a->beta;
   if (!be.data) return FLA_ERR_NULL;
   if (be.ndim != 3 || be.shape[0] != B || be.shape[1] != T || be.shape[2] != HV || be.stride[2] != 1 ||
@@ -644,8 +648,8 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   for (const fla_tensor_t* s : {&a->initial_state, &a->final_state}) {
     if (!s->data) continue;
     if (s->dtype != FLA_F32) return FLA_ERR_DTYPE;
-    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != kV) return FLA_ERR_SHAPE;
-    if (s->stride[3] != 1 || s->stride[2] != kV || s->stride[1] != kK * kV || s->stride[0] != HV * kK * kV || !aligned16(s->data))
+    if (s->ndim != 4 || s->shape[0] != N || s->shape[1] != HV || s->shape[2] != kK || s->shape[3] != V) return FLA_ERR_SHAPE;
+    if (s->stride[3] != 1 || s->stride[2] != V || s->stride[1] != kK * V || s->stride[0] != HV * kK * V || !aligned16(s->data))
       return FLA_ERR_LAYOUT;
   }
   if (a->gate_mode < 0 || a->gate_mode > 2) return FLA_ERR_VALUE;
@@ -668,7 +672,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   uint8_t* images = static_cast<uint8_t*>(workspace);   // where the operand images go
   uint64_t soff[4] = {0, 0, 0, 0};
   if (a->saved.data) {
-    const uint64_t sbytes = kda_saved_layout(total_chunks, HV, B * T, soff);
+    const uint64_t sbytes = kda_saved_layout(total_chunks, HV, V / kBV, B * T, soff);
     if (a->saved.dtype != FLA_BF16 || a->saved.ndim != 1 || uint64_t(a->saved.shape[0]) * 2 < sbytes || !aligned16(a->saved.data))
       return FLA_ERR_SHAPE;
     if (a->gate_mode != 0 || a->gk.data) return FLA_ERR_VALUE;
@@ -701,7 +705,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
   p.q_st = a->q.stride[1]; p.q_sh = a->q.stride[2]; p.k_st = a->k.stride[1]; p.k_sh = a->k.stride[2];
   p.v_st = a->v.stride[1]; p.v_sh = a->v.stride[2]; p.o_st = a->o.stride[1]; p.o_sh = a->o.stride[2];
   p.g_st = a->g.stride[1]; p.g_sh = a->g.stride[2]; p.beta_st = be.stride[1];
-  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.total_tokens = B * T;
+  p.N = N; p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.total_tokens = B * T; p.V = int(V); p.nvb = int(V / kBV);
   p.g_is_f32 = a->g.dtype == FLA_F32; p.beta_is_f32 = be.dtype == FLA_F32; p.o_is_f32 = a->o.dtype == FLA_F32;
   p.gate_mode = a->gate_mode; p.scale = a->scale; p.lower_bound = a->lower_bound;
 
@@ -753,7 +757,7 @@ int fla::kda_launch_forward(const KdaParams& p, int nt_max, cudaStream_t cs) {
   }
   {
     KernelTimer kt("kda_fwd", cs);
-    kda_fwd_kernel<<<dim3(kV / kBV, unsigned(p.HV), p.N), 256, kKdaFwdSmem + 1024, cs>>>(p);
+    kda_fwd_kernel<<<dim3(unsigned(p.nvb), unsigned(p.HV), p.N), 256, kKdaFwdSmem + 1024, cs>>>(p);
   }
   return cuda_status(cudaGetLastError());
 }

@@ -149,8 +149,8 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         raise RuntimeError(f"{op}: expected q,k [B,T,HK,K] and v [B,T,HV,V]")
     B, T, HK, K = q.shape
     HV, V = v.shape[2], v.shape[3]
-    if K != 128 or V != 128:
-        raise RuntimeError(f"{op}: this build supports K = V = 128, got K={K}, V={V}")
+    if K != 128 or V not in (128, 256):
+        raise RuntimeError(f"{op}: this build supports K = 128 and V = 128 or 256, got K={K}, V={V}")
     if HV % HK:
         raise RuntimeError(f"{op}: HV={HV} must be a multiple of HK={HK}")
     if tuple(g.shape) != (B, T, HV, K) or tuple(beta.shape) != (B, T, HV):

@@ -30,15 +30,15 @@ def _reference(inp, cu, dht):
     return ref
 
 
-def _run(B, T, HK, HV, seed, h0=True, with_dht=True, cu=None, gate_scale=1.0, **kw):
+def _run(B, T, HK, HV, seed, h0=True, with_dht=True, cu=None, gate_scale=1.0, V=128, **kw):
     from fla_b200.ops import chunk_kda
-    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=seed)
+    inp = oracle.make_kda_inputs(B, T, HK, HV, V=V, seed=seed)
     inp["g"] = (inp["g"].float() * gate_scale).bfloat16()
     N = B if cu is None else len(cu) - 1
     gen = torch.Generator().manual_seed(seed + 1)
     if h0:
-        inp["h0"] = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float()
-    dht = (0.1 * torch.randn(N, HV, 128, 128, generator=gen)).float() if with_dht else None
+        inp["h0"] = (0.1 * torch.randn(N, HV, 128, V, generator=gen)).float()
+    dht = (0.1 * torch.randn(N, HV, 128, V, generator=gen)).float() if with_dht else None
     ref = _reference(inp, cu, dht)
     leaves = {n: inp[n].cuda().requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
     h0_d = inp["h0"].cuda().requires_grad_(True) if h0 else None
@@ -100,6 +100,16 @@ def test_kda_backward_from_saved_intermediates():
     _check(got, ref)
     cu = [0, 70, 71, 199, 263, 300]
     got, ref = _run(1, 300, 2, 2, seed=14, cu=cu, disable_recompute=True)
+    _check(got, ref)
+
+
+@pytest.mark.parametrize("recompute", [True, False])
+def test_kda_value_dim_256(recompute):
+    """K = 128, V = 256 (the shape of the reference's published KDA forward case): four 64-column blocks of V per head."""
+    got, ref = _run(2, 200, 1, 2, seed=4300, V=256, disable_recompute=not recompute)
+    assert got["o"].shape[-1] == 256
+    _check(got, ref)
+    got, ref = _run(1, 300, 1, 2, seed=4301, V=256, cu=[0, 70, 71, 199, 300], disable_recompute=not recompute)
     _check(got, ref)
 
 
