@@ -8,6 +8,9 @@
 // HBM streaming like the forward: a thread owns 8 adjacent channels, walks a tile of tokens once with the input
 // and gradient windows in registers, recomputes the pre-activation (or reads it when the caller kept it) and
 // leaves its dw / db partial sums in a workspace that a second, tiny kernel reduces in a fixed order.
+// The arithmetic runs on channel pairs with the packed fp32x2 instructions of sm_100 (fma / mul / add .f32x2: two
+// IEEE fp32 operations per issue slot), and the four-token windows live in a register ring with compile-time
+// indices, so no register is moved when the window advances; the kernel is bound by instruction issue otherwise.
 #include <cuda_bf16.h>
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
@@ -92,30 +95,87 @@ __device__ __forceinline__ void load_taps(const bf16* w, int64_t wsd, int64_t ws
   }
 }
 
+// two fp32 values in one 64-bit register pair, operated on by the packed .f32x2 instructions
+using f2 = unsigned long long;
+__device__ __forceinline__ f2 mk2(float lo, float hi) {
+  f2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void un2(f2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+  f2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
+  f2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f2 add2(f2 a, f2 b) {
+  f2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f2 bf2_to_f2(uint32_t raw) { return mk2(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u)); }
+__device__ __forceinline__ uint32_t f2_to_bf2(f2 v) {
+  float lo, hi;
+  un2(v, lo, hi);
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ void unpack4p(const uint4& raw, f2* out) {
+  out[0] = bf2_to_f2(raw.x); out[1] = bf2_to_f2(raw.y); out[2] = bf2_to_f2(raw.z); out[3] = bf2_to_f2(raw.w);
+}
+__device__ __forceinline__ void pairs_from(const float* f, f2* out) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) out[c] = mk2(f[2 * c], f[2 * c + 1]);
+}
+// derivative of SiLU on a channel pair, the same operations as dsilu() on each half
+__device__ __forceinline__ f2 dsilu2(f2 p, f2 half2, f2 one2, f2 neg2) {
+  float h0, h1, t0, t1;
+  un2(mul2(half2, p), h0, h1);
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(h0));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(h1));
+  const f2 s = fma2(half2, mk2(t0, t1), half2);
+  return mul2(s, fma2(p, fma2(neg2, s, one2), one2));
+}
+
+constexpr int kBwdRot = 4;   // tokens per rotation of the register windows (two groups)
+
 template <int W, bool SILU>
 __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams p) {
   constexpr int G = kBwdGroup;
+  static_assert(G == 2 && kBwdRot == 4 && W <= kBwdRot, "window ring layout");
   extern __shared__ uint4 ring[];
   const int d0 = (blockIdx.x * kBwdThreads + threadIdx.x) * 8;
   if (d0 >= p.D) return;
   const int b = blockIdx.z;
   const int s0 = blockIdx.y * kBwdTile;
   const int s1 = min(p.T, s0 + kBwdTile);
+  const f2 half2 = mk2(0.5f, 0.5f), one2 = mk2(1.f, 1.f), neg2 = mk2(-1.f, -1.f), zero2 = mk2(0.f, 0.f);
 
-  float w[W][8], bias[8];
-  load_taps<W>(p.weight, p.w_sd, p.w_sw, d0, w);
-  if (p.bias) unpack8b(*reinterpret_cast<const uint4*>(p.bias + d0), bias);
-  else {
+  f2 w[W][4], bias[4];
+  {
+    float wf[W][8], bf[8];
+    load_taps<W>(p.weight, p.w_sd, p.w_sw, d0, wf);
+    if (p.bias) unpack8b(*reinterpret_cast<const uint4*>(p.bias + d0), bf);
+    else {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) bias[c] = 0.f;
+      for (int c = 0; c < 8; ++c) bf[c] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j) pairs_from(wf[j], w[j]);
+    pairs_from(bf, bias);
   }
 
-  float dw[W][8], db[8];
+  f2 dw[W][4], db[4];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    db[c] = 0.f;
+  for (int c = 0; c < 4; ++c) {
+    db[c] = zero2;
 #pragma unroll
-    for (int j = 0; j < W; ++j) dw[j][c] = 0.f;
+    for (int j = 0; j < W; ++j) dw[j][c] = zero2;
   }
 
   int seq = b, seq_begin = 0, seq_end = p.T;
@@ -160,13 +220,17 @@ __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams 
     // it); steps up to u_stop-1 flush the window with zero gradient when the sequence ends first.
     const int u_real_end = min(seg_end + (W - 1), seq_end);
     const int u_stop = seg_end + (W - 1);
-    // xs[i + j] = x[u - (W-1) + j] and gs[i + k] = gr[u - (W-1) + k] while token u = ug + i is processed
-    float xs[W - 1 + G][8], gs[W - 1 + G][8];
+    // Register windows as rings of kBwdRot token slots: token u = t + n lives in slot n % 4, so while it is processed
+    // x[u - (W-1) + j] and gr[u - (W-1) + k] sit in slots (n - (W-1) + j) % 4: every index below is a compile-time
+    // constant of the unrolled rotation and nothing is shifted.
+    f2 xr[kBwdRot][4], gr[kBwdRot][4];
 #pragma unroll
     for (int j = 0; j < W - 1; ++j) {
-      input_at(t - (W - 1) + j, xs[j]);
+      float xv[8];
+      input_at(t - (W - 1) + j, xv);
+      pairs_from(xv, xr[(j - (W - 1)) & 3]);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) gs[j][c] = 0.f;
+      for (int c = 0; c < 4; ++c) gr[(j - (W - 1)) & 3][c] = zero2;
     }
     // Loads run kBwdAhead groups ahead of the arithmetic as asynchronous copies into a per-thread ring in shared memory
     // (cp.async, 16 bytes each): they occupy no registers while in flight, so every thread keeps
@@ -191,77 +255,81 @@ __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams 
     };
 #pragma unroll
     for (int a = 0; a < kBwdAhead; ++a) request(t + a * G);
-    for (int ug = t; ug < u_stop; ug += G) {
-      request(ug + kBwdAhead * G);            // past the end: zeros, and an empty group keeps the count uniform
-      cp_async_wait<kBwdAhead>();
-      uint4 xin[G], gin[G], yin[G];
-      {
-        const int slot = ((ug - t) / G) % kBwdRing;
+    for (int ug = t; ug < u_stop; ug += kBwdRot) {
+#pragma unroll
+      for (int hg = 0; hg < kBwdRot / G; ++hg) {   // a second group past u_stop only sees zero gradients and stores nothing
+        const int uh = ug + hg * G;
+        request(uh + kBwdAhead * G);            // past the end: zeros, and an empty group keeps the count uniform
+        cp_async_wait<kBwdAhead>();
+        uint4 xin[G], gin[G], yin[G];
+        {
+          const int slot = ((uh - t) / G) % kBwdRing;
+#pragma unroll
+          for (int i = 0; i < G; ++i) {
+            const uint4* src = ring + ((slot * G + i) * 3) * kBwdThreads + threadIdx.x;
+            xin[i] = src[0];
+            gin[i] = src[kBwdThreads];
+            if (SILU) yin[i] = src[2 * kBwdThreads];
+          }
+        }
 #pragma unroll
         for (int i = 0; i < G; ++i) {
-          const uint4* src = ring + ((slot * G + i) * 3) * kBwdThreads + threadIdx.x;
-          xin[i] = src[0];
-          gin[i] = src[kBwdThreads];
-          if (SILU) yin[i] = src[2 * kBwdThreads];
-        }
-      }
+          const int ii = hg * G + i;   // slot of this token
+          const int u = uh + i;
+          f2 g4[4];
+          unpack4p(xin[i], xr[ii]);
+          unpack4p(gin[i], g4);
+          if constexpr (SILU) {
+            f2 pre[4];
+            if (yb) {
+              unpack4p(yin[i], pre);
+            } else {
 #pragma unroll
-      for (int i = 0; i < G; ++i) {
-        const int u = ug + i;
-        float g8[8];
-        unpack8b(xin[i], xs[W - 1 + i]);
-        unpack8b(gin[i], g8);
-        if constexpr (SILU) {
-          float pre[8];
-          if (yb) {
-            unpack8b(yin[i], pre);
-          } else {
+              for (int c = 0; c < 4; ++c) {
+                f2 a = bias[c];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              float a = bias[c];
+                for (int j = 0; j < W; ++j) a = fma2(w[j][c], xr[(ii - (W - 1) + j) & 3][c], a);
+                pre[c] = a;
+              }
+            }
 #pragma unroll
-              for (int j = 0; j < W; ++j) a = fmaf(w[j][c], xs[i + j][c], a);
-              pre[c] = a;
+            for (int c = 0; c < 4; ++c) g4[c] = mul2(g4[c], dsilu2(pre[c], half2, one2, neg2));   // zero beyond the last real token
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c) gr[ii][c] = g4[c];
+          if (u < seg_end) {   // tokens of this segment own their dw / db contributions
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              db[c] = add2(db[c], g4[c]);
+#pragma unroll
+              for (int j = 0; j < W; ++j) dw[j][c] = fma2(g4[c], xr[(ii - (W - 1) + j) & 3][c], dw[j][c]);
             }
           }
+          const int s = u - (W - 1);   // dx[s] = sum_k w[W-1-k] gr[s+k] is complete now
+          if (s >= t && s < seg_end) {
+            f2 o[4];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) g8[c] *= dsilu(pre[c]);   // zero beyond the last real token: its dy was read as 0
-        }
+            for (int c = 0; c < 4; ++c) {
+              f2 a = zero2;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) gs[W - 1 + i][c] = g8[c];
-        if (u < seg_end) {   // tokens of this segment own their dw / db contributions
+              for (int k = 0; k < W; ++k) a = fma2(w[W - 1 - k][c], gr[(ii - (W - 1) + k) & 3][c], a);
+              o[c] = a;
+            }
+            const int ti = s - (seq_end - (W - 1));   // index into the final state when s is one of the last W-1 inputs
+            if (p.dht && ti >= 0) {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            db[c] += g8[c];
-#pragma unroll
-            for (int j = 0; j < W; ++j) dw[j][c] = fmaf(g8[c], xs[i + j][c], dw[j][c]);
+              for (int c = 0; c < 4; ++c) {
+                float lo, hi;
+                un2(o[c], lo, hi);
+                lo += __bfloat162float(p.dht[seq * p.t_sn + (d0 + 2 * c) * p.t_sd + ti * p.t_sw]);
+                hi += __bfloat162float(p.dht[seq * p.t_sn + (d0 + 2 * c + 1) * p.t_sd + ti * p.t_sw]);
+                o[c] = mk2(lo, hi);
+              }
+            }
+            *reinterpret_cast<uint4*>(dxb + s * p.dx_st) = make_uint4(f2_to_bf2(o[0]), f2_to_bf2(o[1]), f2_to_bf2(o[2]), f2_to_bf2(o[3]));
           }
-        }
-        const int s = u - (W - 1);   // dx[s] = sum_k w[W-1-k] gr[s+k] is complete now
-        if (s >= t && s < seg_end) {
-          float o[8];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            float a = 0.f;
-#pragma unroll
-            for (int k = 0; k < W; ++k) a = fmaf(w[W - 1 - k][c], gs[i + k][c], a);
-            o[c] = a;
-          }
-          const int ti = s - (seq_end - (W - 1));   // index into the final state when s is one of the last W-1 inputs
-          if (p.dht && ti >= 0) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) o[c] += __bfloat162float(p.dht[seq * p.t_sn + (d0 + c) * p.t_sd + ti * p.t_sw]);
-          }
-          *reinterpret_cast<uint4*>(dxb + s * p.dx_st) = pack8b(o);
         }
       }
-#pragma unroll
-      for (int j = 0; j < W - 1; ++j)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          xs[j][c] = xs[G + j][c];
-          gs[j][c] = gs[G + j][c];
-        }
     }
     cp_async_wait<0>();     // the groups requested past the segment's end
     if (t == seq_begin && p.dh0) {
@@ -284,22 +352,28 @@ __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams 
               unpack8b(*reinterpret_cast<const uint4*>(yb + u * p.yp_st), pre);
             } else {
 #pragma unroll
-              for (int c = 0; c < 8; ++c) pre[c] = bias[c];
+              for (int c = 0; c < 4; ++c) un2(bias[c], pre[2 * c], pre[2 * c + 1]);
 #pragma unroll
               for (int j = 0; j < W; ++j) {
-                float xv[8];
+                float xv[8], wj[8];
                 input_at(u - (W - 1) + j, xv);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) pre[c] = fmaf(w[j][c], xv[c], pre[c]);
+                for (int c = 0; c < 4; ++c) un2(w[j][c], wj[2 * c], wj[2 * c + 1]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) pre[c] = fmaf(wj[c], xv[c], pre[c]);
               }
             }
 #pragma unroll
             for (int c = 0; c < 8; ++c) g8[c] *= dsilu(pre[c]);
           }
 #pragma unroll
-          for (int i = rel; i < W - 1; ++i)
+          for (int i = rel; i < W - 1; ++i) {
+            float wj[8];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) dh[i][c] = fmaf(g8[c], w[i - rel][c], dh[i][c]);
+            for (int c = 0; c < 4; ++c) un2(w[i - rel][c], wj[2 * c], wj[2 * c + 1]);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) dh[i][c] = fmaf(g8[c], wj[c], dh[i][c]);
+          }
         }
       }
 #pragma unroll
@@ -322,12 +396,21 @@ __global__ void __launch_bounds__(kBwdThreads, 2) conv_bwd_kernel(ConvBwdParams 
   float* dst = p.part + (int64_t(b) * p.tiles_per_row + blockIdx.y) * (W + 1) * p.D + d0;
 #pragma unroll
   for (int j = 0; j < W; ++j) {
-    *reinterpret_cast<float4*>(dst + j * p.D) = make_float4(dw[j][0], dw[j][1], dw[j][2], dw[j][3]);
-    *reinterpret_cast<float4*>(dst + j * p.D + 4) = make_float4(dw[j][4], dw[j][5], dw[j][6], dw[j][7]);
+    float f[8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) un2(dw[j][c], f[2 * c], f[2 * c + 1]);
+    *reinterpret_cast<float4*>(dst + j * p.D) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(dst + j * p.D + 4) = make_float4(f[4], f[5], f[6], f[7]);
   }
-  *reinterpret_cast<float4*>(dst + W * p.D) = make_float4(db[0], db[1], db[2], db[3]);
-  *reinterpret_cast<float4*>(dst + W * p.D + 4) = make_float4(db[4], db[5], db[6], db[7]);
+  {
+    float f[8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) un2(db[c], f[2 * c], f[2 * c + 1]);
+    *reinterpret_cast<float4*>(dst + W * p.D) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(dst + W * p.D + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
 }
+
 
 struct ConvBwdReduceParams {
   const float* part; float* dw; float* db;

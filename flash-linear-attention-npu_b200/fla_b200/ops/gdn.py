@@ -204,8 +204,10 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
                                        use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens, chunk_size=chunk_size,
                                        output_dtype=output_dtype)
         return o.transpose(1, 2), ht
-    if chunk_size != CHUNK:
-        raise NotImplementedError(f"{op}: chunk_size must be {CHUNK}")
+    # chunk_size is the reference's blocking parameter: o, the final state and every gradient are the same function of
+    # the inputs for any blocking, so the fused kernels keep their own 64-token tiling for the sizes the reference tiles for
+    if int(chunk_size) not in (16, 32, 64, 128):
+        raise NotImplementedError(f"{op}: chunk_size must be one of 16, 32, 64, 128, got {chunk_size}")
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                                              output_dtype, bool(use_qk_l2norm_in_kernel))

@@ -173,19 +173,19 @@ FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* a
                                           uint64_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Chunked gated delta rule, forward (chunk = 64, K = V = 128).
+ * Chunked gated delta rule, forward (chunk = 64, K = 128, V = 128 or 256).
  * Replaces the reference's forward chain chunk_local_cumsum -> chunk_scaled_dot_kkt -> solve_tri ->
  * recompute_w_u_fwd -> chunk_gated_delta_rule_fwd_h -> chunk_fwd_o as composed by
  * flash_chunk_gated_delta_rule_fwd (examples/flash_gated_delta_rule.py:796-881; per-op bindings
  * torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:875-936, 1786-1800, 618-651, 552-615, 517-549).
- *   q, k [B, T, HK, 128] bf16;  v [B, T, HV, 128] bf16;  g, beta [B, T, HV] f32|bf16 (g = log decay per token)
- *   o [B, T, HV, 128] bf16|f32
- *   initial_state / final_state [N, HV, 128(K), 128(V)] f32, optional
+ *   q, k [B, T, HK, 128] bf16;  v [B, T, HV, V] bf16;  g, beta [B, T, HV] f32|bf16 (g = log decay per token)
+ *   o [B, T, HV, V] bf16|f32
+ *   initial_state / final_state [N, HV, 128(K), V] f32, optional
  *   gam   [B, T, HV] f32      out: chunk-local cumulative sum of g      (saved for backward)
  *   x_inv [B, T, HV, 64] bf16 out: rows of (I + strict_tril(beta_i exp(gam_i-gam_j) k_i.k_j))^-1 per chunk
- *   s_img  [chunks * HV * 32768] bf16, optional out (for backward): per (chunk, head) the state at chunk start as
- *          2 (64-column blocks of V) x 2 (hi, lo = bf16 residual) swizzled 128x64 operand panels
- *   vn_img [chunks * HV * 16384] bf16, optional out (for backward): v_new, 2 x 2 (hi, lo = bf16 residual) 64x64 panels
+ *   s_img  [chunks * HV * (V/64) * 16384] bf16, optional out (for backward): per (chunk, head) the state at chunk start as
+ *          V/64 (64-column blocks of V) x 2 (hi, lo = bf16 residual) swizzled 128x64 operand panels
+ *   vn_img [chunks * HV * (V/64) * 8192] bf16, optional out (for backward): v_new, V/64 x 2 (hi, lo = bf16 residual) 64x64 panels
  *   p_img  [chunks * HV * 8192] bf16, optional out (for backward): tril(Q K^T * decay), 2 (hi, lo) 64x64 panels;
  *          when absent the forward keeps these panels in its workspace
  *          (s_img, vn_img, p_img are opaque to the caller: produced here, consumed by fla_b200_gdn_chunk_bwd)
@@ -209,15 +209,15 @@ FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* args, void* wor
                                    void* stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Chunked gated delta rule, backward (chunk = 64, K = V = 128).
+ * Chunked gated delta rule, backward (chunk = 64, K = 128, V = 128 or 256).
  * Replaces the reference's backward chain chunk_bwd_dv_local -> chunk_gated_delta_rule_bwd_dhu -> chunk_bwd_dqkwg ->
  * prepare_wy_repr_bwd_da -> prepare_wy_repr_bwd_full -> reverse chunk_local_cumsum as composed by
  * flash_chunk_gated_delta_rule_bwd (examples/flash_gated_delta_rule.py:884-1023; per-op bindings
  * torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:397-427, 324-394, 463-514, 430-460, 242-281).
  * Unlike the reference's composition it also consumes the final-state cotangent dht and produces dh0.
  *   q, k, v, beta, gam, x_inv, s_img, vn_img, p_img: the forward's inputs and saved outputs (same shapes as there)
- *   d_o [B, T, HV, 128] bf16;   dht [N, HV, 128, 128] f32, optional
- *   dq, dk [B, T, HK, 128], dv [B, T, HV, 128], dg, dbeta [B, T, HV]: all bf16 or all f32;  dh0 [N, HV, 128, 128] f32, optional
+ *   d_o [B, T, HV, V] bf16;   dht [N, HV, 128, V] f32, optional
+ *   dq, dk [B, T, HK, 128], dv [B, T, HV, V], dg, dbeta [B, T, HV]: all bf16 or all f32;  dh0 [N, HV, 128, V] f32, optional
  *   dq / dk are summed over the value heads of each GVA group inside the kernel (deterministic).
  * Workspace (size from the _workspace_size call): status block + state-gradient images + [dO; dZ] images + row sums. */
 typedef struct fla_gdn_chunk_bwd_args {
@@ -253,11 +253,11 @@ FLA_API int fla_b200_gdn_chunk_bwd_static_scratch_bytes(uint64_t* bytes);
 FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Chunked Kimi Delta Attention, forward (per-channel log gate, chunk = 64, K = V = 128).
+ * Chunked Kimi Delta Attention, forward (per-channel log gate, chunk = 64, K = 128, V = 128 or 256).
  * Replaces aclnnKdaGateCumsum + aclnnChunkKdaFwd as bound by npu_kda_gate_cumsum / npu_chunk_kda_fwd
  * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1268-1296, 1066-1265; stages in
  * fla/ops/ascendc/kda/chunk_kda_fwd/docs/design.md:11-78).
- *   q, k [B, T, HK, 128] bf16;  v [B, T, HV, 128] bf16;  g [B, T, HV, 128] f32|bf16;  beta [B, T, HV] f32|bf16
+ *   q, k [B, T, HK, 128] bf16;  v [B, T, HV, V] bf16;  g [B, T, HV, 128] f32|bf16;  beta [B, T, HV] f32|bf16
  *   gate_mode 0: g is the log decay;  1: -exp(a_log[h]) * softplus(g + dt_bias[h, :]);
  *             2: lower_bound * sigmoid(exp(a_log[h]) * (g + dt_bias[h, :]))   (a_log [HV] f32, dt_bias [HV, 128] f32 optional)
  *   o [B, T, HV, 128] bf16|f32;  initial_state / final_state [N, HV, 128(K), 128(V)] f32, optional

@@ -84,3 +84,20 @@ def test_head_first_and_reference_entry_are_views_of_the_same_operator():
         assert torch.equal(b.grad.transpose(1, 2), a.grad)
     with pytest.raises(ValueError, match="does not support float32"):
         flash_gated_delta_rule(*(t.float() for t in hf), g, beta)
+
+
+def test_reference_chunk_sizes_give_the_same_function():
+    """The reference tiles for chunk sizes 16 .. 128; the blocking does not change o or the final state, so the operator
+    accepts them (and keeps its own tiling) and still meets the oracle."""
+    from fla_b200.ops import chunk_gated_delta_rule
+    inp = oracle.make_gdn_inputs(B=1, T=300, HK=1, HV=2, K=128, V=128, seed=91, dtype=torch.bfloat16, with_grad=False)
+    ref = oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"],
+                                       dtype=torch.float64)
+    q, k, v, g, beta, h0 = (inp[n].cuda() for n in ("q", "k", "v", "g", "beta", "h0"))
+    o64, h64 = chunk_gated_delta_rule(q, k, v, g, beta, initial_state=h0, output_final_state=True, chunk_size=64)
+    o128, h128 = chunk_gated_delta_rule(q, k, v, g, beta, initial_state=h0, output_final_state=True, chunk_size=128)
+    assert torch.equal(o64, o128) and torch.equal(h64, h128)
+    assert_close("o", o128, ref["o"], 5e-3, stored_bf16=True)
+    assert_close("ht", h128, ref["ht"], 5e-3)
+    with pytest.raises(NotImplementedError):
+        chunk_gated_delta_rule(q, k, v, g, beta, chunk_size=48)
