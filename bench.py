@@ -326,7 +326,7 @@ class Workload:
         """DRAM bytes (read + write) of one launch: the per-unit figure of one ncu capture of a small case of the
         same kernel (profiles/), scaled by the units this launch processes; None where no capture exists."""
         c = self.cfg
-        per_chunk_head = {"gdn_fwd": 309.85e6 / 2048, "gdn_bwd_dhu": 346.35e6 / 2048, "gdn_bwd_par": 469.52e6 / 2048,
+        per_chunk_head = {"gdn_fwd": 312.98e6 / 2048, "gdn_bwd_dhu": 346.22e6 / 2048, "gdn_bwd_par": 469.55e6 / 2048,
                           "kda_prep": 159.25e6 / 1024, "kda_fwd": 232.05e6 / 1024, "kda_bwd_dhu": 266.41e6 / 1024,
                           "kda_bwd_par": 396.41e6 / 1024, "recompute_w_u_fwd": 88.55e6 / 2048, "chunk_fwd_h": 145.06e6 / 2048,
                           "chunk_fwd_o": 152.34e6 / 2048}
