@@ -338,6 +338,8 @@ class Workload:
             return 212.33e6 / 64 * c["N"] * c["HV"] / 32
         if kname == "causal_conv1d_fwd":   # 227.88 MB for 2 x 4096 x 8192 elements
             return 227.88e6 / (2 * 4096 * 8192) * c["B"] * c["T"] * c["D"]
+        if kname == "causal_conv1d_bwd":   # 391.52 MB for 2 x 4096 x 8192 elements
+            return 391.52e6 / (2 * 4096 * 8192) * c["B"] * c["T"] * c["D"]
         return None
 
     def step_flops(self):

@@ -29,13 +29,6 @@ __device__ __forceinline__ void unpack8b(const uint4& raw, float* f) {
     f[2 * i + 1] = __high2float(h[i]);
   }
 }
-__device__ __forceinline__ uint4 pack8b(const float* f) {
-  uint4 raw;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-  return raw;
-}
 
 struct ConvBwdParams {
   const bf16* x; const bf16* dy; const bf16* ypre; bf16* dx;
