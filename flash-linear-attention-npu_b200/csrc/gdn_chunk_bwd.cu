@@ -431,6 +431,7 @@ __device__ long long g_par_clocks[16];
 #define PSTAMP(i)
 #endif
 
+template <int NVB>   // 64-column blocks of V per head (2 or 4): a compile-time trip count keeps the block loop unrolled
 __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_k) {
 #ifdef FLA_STAGE_CLOCKS
@@ -470,10 +471,10 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   auto issue_loads = [&](int hv, int vb) {  // one thread: operands of one (value head, V block) step
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
     mbar_arrive_expect_tx(&load_bar, kStepBytes);
-    bulk_load(sb + rOffAH, p.dz_img + (cidx * p.nvb + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + rOffVNH, p.vn_img + (cidx * p.nvb + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + rOffSH, p.s_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
-    bulk_load(sb + rOffDSH, p.ds_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + rOffAH, p.dz_img + (cidx * NVB + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + rOffVNH, p.vn_img + (cidx * NVB + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + rOffSH, p.s_img + (cidx * NVB + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + rOffDSH, p.ds_img + (cidx * NVB + vb) * 16384, 32768, &load_bar);
   };
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
@@ -568,7 +569,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     const int64_t gidx = (tok0 + tid) * p.HV + hvf;
     const int64_t bzs = p.total_tokens * p.HV;
     float acc = 0.f;
-    for (int i = 0; i < p.nvb; ++i) acc += p.bz[(2 * i) * bzs + gidx] + p.bz[(2 * i + 1) * bzs + gidx];
+    for (int i = 0; i < NVB; ++i) acc += p.bz[(2 * i) * bzs + gidx] + p.bz[(2 * i + 1) * bzs + gidx];
     return acc;
   };
 
@@ -587,7 +588,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     if (h + 1 < G) prefetch_scalars(hv + 1);
     const float bz_cur = load_bz(hv);     // lands while the step's operands are awaited
     float sds = 0.f;
-    for (int vb = 0; vb < p.nvb; ++vb) {
+    for (int vb = 0; vb < NVB; ++vb) {
       PSTAMP(1);
       ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT);
       lphase ^= 1;
@@ -627,7 +628,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
       PSTAMP(4);
       tc_fence_after();
       if (tid == 0) {
-        if (vb + 1 < p.nvb) issue_loads(hv, vb + 1);
+        if (vb + 1 < NVB) issue_loads(hv, vb + 1);
         else if (h + 1 < G) issue_loads(hv + 1, 0);
       }
     }
@@ -904,7 +905,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
   if (!attr_done_dev[dev]) {
     if (cudaFuncSetAttribute(gdn_bwd_dhu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDhuSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
-    if (cudaFuncSetAttribute(gdn_bwd_par_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(gdn_bwd_par_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(gdn_bwd_par_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
   CUtensorMap tm_q, tm_k, tm_x;
@@ -920,7 +922,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   const int nt_max = (max_len + kC - 1) / kC;
   {
     KernelTimer kt("gdn_bwd_par", cs);
-    gdn_bwd_par_kernel<<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p, tm_q, tm_k);
+    if (nvb == 2) gdn_bwd_par_kernel<2><<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p, tm_q, tm_k);
+    else gdn_bwd_par_kernel<4><<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p, tm_q, tm_k);
   }
   return cuda_status(cudaGetLastError());
 }

@@ -400,6 +400,7 @@ __device__ __forceinline__ float warp_column_sums32(const float* v, int lane) {
 
 // The chunk's gk rows arrive as TMA tiles once the phase-1 buffers are free; the last epilogue reads them from
 // shared memory (their global loads used to sit, one round trip each, on the critical path).
+template <int NVB>   // 64-column blocks of V per head (2 or 4): a compile-time trip count keeps the block loop unrolled
 __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, const __grid_constant__ CUtensorMap tm_gk) {
 #ifdef FLA_STAGE_CLOCKS
   long long kclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
@@ -457,12 +458,12 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
   auto issue_loads = [&](int hv, int vb) {    // one thread: operands of one (value head, V block) step
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
     mbar_arrive_expect_tx(&load_bar, kKdaStepBytes);
-    const bf16* dz = p.dz_img + (cidx * p.nvb + vb) * 12288;
+    const bf16* dz = p.dz_img + (cidx * NVB + vb) * 12288;
     bulk_load(sb + qOffAH, dz, 16384, &load_bar);
     bulk_load(sb + qOffAL + 8192, dz + 8192, 8192, &load_bar);
-    bulk_load(sb + qOffVNH, p.vn_img + (cidx * p.nvb + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + qOffSH, p.s_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
-    bulk_load(sb + qOffDSH, p.ds_img + (cidx * p.nvb + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + qOffVNH, p.vn_img + (cidx * NVB + vb) * 8192, 16384, &load_bar);
+    bulk_load(sb + qOffSH, p.s_img + (cidx * NVB + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + qOffDSH, p.ds_img + (cidx * NVB + vb) * 16384, 32768, &load_bar);
   };
 
   const Operand opQKh{sb + qOffQKH, 16384, 0}, opQKl{sb + qOffQKL, 16384, 0};           // [Qp; Kp], reduction over key dims
@@ -498,7 +499,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
     }
     float sds = 0.f;   // my key channel (tid & 127), my 32 columns (tid >> 7) of sum_v dS'a * Sa
     KSTAMP(0);
-    for (int vb = 0; vb < p.nvb; ++vb) {
+    for (int vb = 0; vb < NVB; ++vb) {
       if (vb == 0) {
         ok = mbar_wait(&img_bar, iphase, p.status, FLA_ERR_TIMEOUT);
         iphase ^= 1;
@@ -545,7 +546,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
       KSTAMP(3);
       tc_fence_after();
       if (tid == 0) {
-        if (vb + 1 < p.nvb) {
+        if (vb + 1 < NVB) {
           issue_loads(hv, vb + 1);
         } else {   // the phase-1 buffers are free: this head's gk rows, channels 32 b .. 32 b + 31 in tile b
           mbar_arrive_expect_tx(&gk_bar, 4 * 8192);
@@ -632,7 +633,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
       const int64_t gidx = (tok0 + i) * p.HV + hv;
       const int64_t bzs = p.total_tokens * p.HV;
       float bz = 0.f;
-      for (int s = 0; s < p.nvb; ++s) bz += p.bz[(2 * s) * bzs + gidx] + p.bz[(2 * s + 1) * bzs + gidx];
+      for (int s = 0; s < NVB; ++s) bz += p.bz[(2 * s) * bzs + gidx] + p.bz[(2 * s + 1) * bzs + gidx];
       const float db = bz - (red[0][0][i] + red[0][1][i]) + (red[1][0][i] + red[1][1][i]);
       if (p.grads_f32) static_cast<float*>(p.dbeta)[gidx] = db;
       else static_cast<bf16*>(p.dbeta)[gidx] = __float2bfloat16_rn(db);
@@ -933,7 +934,8 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
   if (!attr_done_dev[dev]) {
     if (cudaFuncSetAttribute(kda_bwd_dhu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaDhuSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
-    if (cudaFuncSetAttribute(kda_bwd_par_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(kda_bwd_par_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(kda_bwd_par_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
   {
@@ -945,7 +947,8 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   if (make_row_tile_map_f32(&tm_gk, p.gk, kK, uint64_t(HV), uint64_t(B * T), uint64_t(kK), uint64_t(HV) * kK)) return FLA_ERR_CUDA;
   {
     KernelTimer kt("kda_bwd_par", cs);
-    kda_bwd_par_kernel<<<dim3(nt_max, unsigned(HK), N), 256, kKdaParSmem + 1024, cs>>>(p, tm_gk);
+    if (nvb == 2) kda_bwd_par_kernel<2><<<dim3(nt_max, unsigned(HK), N), 256, kKdaParSmem + 1024, cs>>>(p, tm_gk);
+    else kda_bwd_par_kernel<4><<<dim3(nt_max, unsigned(HK), N), 256, kKdaParSmem + 1024, cs>>>(p, tm_gk);
   }
   return cuda_status(cudaGetLastError());
 }
