@@ -5,6 +5,7 @@ from .conv import (causal_conv1d, causal_conv1d_bwd, causal_conv1d_update, npu_c
 from .gdn import (chunk_gated_delta_rule, chunk_gated_delta_rule_bwd, chunk_gated_delta_rule_fwd_bwd,  # noqa: F401
                   ChunkGatedDeltaRuleFunction, flash_gated_delta_rule)
 from .kda import chunk_kda, chunk_kda_fwd_bwd, kda_chunk_bwd, npu_chunk_kda_fwd  # noqa: F401
+from .gelu import fast_gelu_custom, npu_fast_gelu_custom, npu_fast_gelu_custom_backward  # noqa: F401
 from .l2norm import l2norm_bwd, l2norm_fwd  # noqa: F401
 from .recurrent import fused_recurrent_gated_delta_rule, recurrent_gated_delta_rule, recurrent_kda  # noqa: F401
 

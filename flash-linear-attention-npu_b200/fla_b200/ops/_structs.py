@@ -62,6 +62,10 @@ class L2NormArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("x", "y", "rstd", "dy", "dx")] + [("eps", ctypes.c_float)]
 
 
+class FastGeluArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("x", "y", "dy", "dx")]
+
+
 class ChunkStageArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "w", "u", "g", "beta", "A", "h", "initial_state", "out0", "out1",
                                            "out2", "out3", "cu_seqlens", "chunk_offsets")] + [

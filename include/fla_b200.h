@@ -326,6 +326,19 @@ FLA_API int fla_b200_l2norm_fwd(const fla_l2norm_args* args, void* stream);
 FLA_API int fla_b200_l2norm_bwd(const fla_l2norm_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * FastGELU  y = x / (1 + exp(-1.702 x))  and its backward  dx = dy * (s + 1.702 x s (1 - s)), s = sigmoid(1.702 x).
+ * Replaces npu_fast_gelu_custom / npu_fast_gelu_custom_backward (aclnnFastGelu / aclnnFastGeluBackward,
+ * torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:224-239; golden formula
+ * torch_custom/fla_npu/test/test_npu_fast_gelu_custom.py:22-24).
+ *   x, y (fwd) / x, dy, dx (bwd): the same dtype (f32 | bf16 | f16) and element count, dense (contiguous) and 16-byte
+ *   aligned; any rank up to FLA_MAX_DIMS.  Single-phase (no workspace). */
+typedef struct fla_fast_gelu_args {
+  fla_tensor_t x, y, dy, dx;
+} fla_fast_gelu_args;
+FLA_API int fla_b200_fast_gelu(const fla_fast_gelu_args* args, void* stream);
+FLA_API int fla_b200_fast_gelu_bwd(const fla_fast_gelu_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Stand-alone stages of the chunked gated-delta-rule forward: one entry point per low-level reference operator,
  * for call sites that drive the reference's stage-by-stage chain (examples/flash_gated_delta_rule.py:796-881)
  * instead of the fused fla_b200_gdn_chunk_fwd.  Token tensors are [B, H, T, D] and gate tensors [B, H, T], addressed

@@ -16,3 +16,4 @@ from .conv import (causal_conv1d_bwd_ref, causal_conv1d_ref, causal_conv1d_updat
                    causal_conv1d_update_spec_ref)
 from .inputs import make_gdn_inputs, make_kda_inputs, make_decode_inputs, make_conv_inputs  # noqa: F401
 from . import stages  # noqa: F401
+from .gelu import fast_gelu_bwd_ref, fast_gelu_ref  # noqa: F401

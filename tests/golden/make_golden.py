@@ -269,7 +269,17 @@ def kda_bwd_intra_fixture():
                         db_out=f32(out[2]), dg_out=f32(out[3]))
 
 
+def fast_gelu_fixture():
+    """Forward golden of the reference's FastGELU test on its own input grid (fp32 and bf16 inputs)."""
+    ns = extract(REF / "torch_custom/fla_npu/test/test_npu_fast_gelu_custom.py", ["fast_gelu_ref"])
+    x = torch.linspace(-3, 3, steps=3 * 16 * 32, dtype=torch.float32).reshape(3, 16, 32)
+    xb = (4.0 * torch.randn(5, 7, 24, generator=torch.Generator().manual_seed(7))).bfloat16()
+    np.savez_compressed(HERE / "fast_gelu_golden.npz", x=f32(x), y=f32(ns["fast_gelu_ref"](x)), xb=f32(xb),
+                        yb=f32(ns["fast_gelu_ref"](xb)))
+
+
 if __name__ == "__main__":
+    fast_gelu_fixture()
     gdn_fixture()
     decode_fixture()
     conv_fixture()

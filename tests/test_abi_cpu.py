@@ -59,6 +59,7 @@ def _c_struct_fields(name):
                                           ("fla_kda_chunk_fwd_args", "KdaChunkFwdArgs"),
                                           ("fla_kda_chunk_bwd_args", "KdaChunkBwdArgs"),
                                           ("fla_l2norm_args", "L2NormArgs"),
+                                          ("fla_fast_gelu_args", "FastGeluArgs"),
                                           ("fla_chunk_stage_args", "ChunkStageArgs"),
                                           ("fla_chunk_kda_bwd_intra_args", "ChunkKdaBwdIntraArgs")])
 def test_arg_structs_match_header_field_order(cname, pyname):

@@ -103,3 +103,14 @@ def test_kda_bwd_intra_matches_reference_golden():
     out = oracle.chunk_kda_bwd_intra_ref(f["q"], f["k"], f["gk"], f["beta"], f["d_aqk"], f["d_akk"], f["dq"], f["dk"], f["db"], f["dg"])
     for name, got in zip(("dq_out", "dk_out", "db_out", "dg_out"), out):
         _close(got.float(), f[name], 2e-5)
+
+
+def test_fast_gelu_matches_reference_golden_and_autograd():
+    f = _load("fast_gelu_golden.npz")
+    torch.testing.assert_close(oracle.fast_gelu_ref(f["x"]).float(), f["y"], rtol=1e-6, atol=1e-6)
+    # the golden casts back to the input dtype (bf16 for the second case)
+    torch.testing.assert_close(oracle.fast_gelu_ref(f["xb"]).bfloat16().float(), f["yb"], rtol=0, atol=0)
+    x = f["x"].double().requires_grad_(True)
+    dy = torch.randn(x.shape, dtype=torch.float64, generator=torch.Generator().manual_seed(3))
+    (x / (1 + torch.exp(-1.702 * x)) * dy).sum().backward()
+    torch.testing.assert_close(oracle.fast_gelu_bwd_ref(dy, x.detach()), x.grad, rtol=1e-12, atol=1e-12)
