@@ -206,7 +206,7 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     `_kda_policy.py:15-37`: final_state when asked for, gk (base-2 chunk-local cumulative gate, head-first fp32) unless the gate
     is activated in the kernel, Aqk and Akk `[B,HV,T,64]` always.  The head-major intermediates w, u, qg, kg, v_new, h never exist
     in the fused kernels, so `disable_recompute=True` and `return_intermediate_states=True` (which make them visible) are
-    refused.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
+    refused.  `state_v_first=True` takes and returns the recurrent state as `[N,HV,V,K]`.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
     comes back in the input's layout."""
     del chunk_indices
     op = "npu_chunk_kda_fwd"
@@ -219,8 +219,6 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
         raise NotImplementedError(f"{op}: this build supports chunk_size = 64")
     if disable_recompute or return_intermediate_states:
         raise NotImplementedError(f"{op}: w, u, qg, kg, v_new and h are not materialised by the fused kernels")
-    if state_v_first:
-        raise NotImplementedError(f"{op}: state_v_first is not supported")
     rank3 = layout in {"TND", "NTD"}
 
     def to_bsnd(t):
@@ -240,13 +238,21 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     if use_gate_in_kernel:
         gate_kw = dict(use_gate_in_kernel=True, safe_gate=safe_gate, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias)
     # forward with the score blocks exported (chunk_kda's own checks and metadata apply)
+    # state_v_first: the caller's states are `[N,HV,V,K]`; the kernels keep `[N,HV,K,V]` (a transposed copy of a small tensor)
+    h0 = initial_state
+    if state_v_first and initial_state is not None:
+        if initial_state.dim() != 4 or initial_state.shape[-2] != vb.shape[-1] or initial_state.shape[-1] != K:
+            raise RuntimeError(f"{op}: initial_state shape does not match state_v_first.")
+        h0 = initial_state.transpose(-1, -2)
     with torch.no_grad():
-        o, ht = chunk_kda(qb, kb, vb, gb, bb, scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+        o, ht = chunk_kda(qb, kb, vb, gb, bb, scale=scale, initial_state=h0, output_final_state=output_final_state,
                           cu_seqlens=cu_seqlens, export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), **gate_kw)
     gk_out = None
     if not use_gate_in_kernel:
         from .stages import kda_gate_cumsum
         gk_out = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens).permute(0, 2, 1, 3)       # [B,HV,T,K]
+    if state_v_first and ht is not None:
+        ht = ht.transpose(-1, -2).contiguous()
     if layout in {"BNSD", "NTD"}:
         o = o.transpose(1, 2).contiguous()
     if rank3:

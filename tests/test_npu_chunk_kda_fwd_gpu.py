@@ -91,3 +91,23 @@ def test_visibility_and_refusals():
         npu_chunk_kda_fwd(*args, 128 ** -0.5, 32)
     with pytest.raises(RuntimeError, match="layout must be uppercase"):
         npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, layout="bsnd")
+
+
+def test_state_v_first_and_value_dim_256():
+    """`state_v_first=True` takes / returns `[N,HV,V,K]` states; V = 256 flows through the same surface."""
+    from fla_b200.ops import npu_chunk_kda_fwd
+    B, T, HK, HV, V = 2, 130, 1, 2, 256
+    inp = oracle.make_kda_inputs(B, T, HK, HV, V=V, seed=37, with_grad=False)
+    scale = 128 ** -0.5
+    h0 = 0.1 * torch.randn(B, HV, 128, V, generator=torch.Generator().manual_seed(4))
+    ref = oracle.kda_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], scale=scale, initial_state=h0)
+    args = [inp[n].cuda() for n in ("q", "k", "v", "g", "beta")]
+    a = npu_chunk_kda_fwd(*args, scale, 64, initial_state=h0.cuda(), output_final_state=True)
+    b = npu_chunk_kda_fwd(*args, scale, 64, initial_state=h0.transpose(-1, -2).contiguous().cuda(), output_final_state=True,
+                          state_v_first=True)
+    assert tuple(b[1].shape) == (B, HV, V, 128) and b[1].is_contiguous()
+    assert torch.equal(b[1].transpose(-1, -2), a[1]) and torch.equal(a[0], b[0])
+    assert_close("o", a[0], ref["o"], 5e-3, stored_bf16=True)
+    assert_close("ht", a[1], ref["ht"], 5e-3)
+    with pytest.raises(RuntimeError, match="state_v_first"):
+        npu_chunk_kda_fwd(*args, scale, 64, initial_state=h0.cuda(), state_v_first=True)
