@@ -104,3 +104,27 @@ def test_forward_only_call_saves_nothing_and_matches():
                                        output_final_state=True, output_dtype=torch.float32)
     assert not o.requires_grad
     assert_close("o", o, ref["o"], TOL)
+
+
+def test_empty_sequence_in_a_packed_batch():
+    """A zero-length sequence between two others changes nothing for its neighbours; its final state is its initial state
+    and its dh0 is its dht."""
+    from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
+    cu_a, cu_b = [0, 70, 71, 200], [0, 70, 70, 71, 200]
+    inp = oracle.make_gdn_inputs(1, 200, 1, 2, seed=123, h0_scale=0.0)
+    gen = torch.Generator().manual_seed(124)
+    h0 = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
+    dht = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
+    keep = [0, 2, 3]                                   # sequence 1 of the second batch is the empty one
+    d = {n: inp[n].cuda() for n in ("q", "k", "v", "g", "beta", "do")}
+
+    def run(cu, h, dh):
+        return chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=h.cuda(), dht=dh.cuda(),
+                                              cu_seqlens=torch.tensor(cu, dtype=torch.int32), grad_dtype=torch.float32)
+    o_a, ht_a, g_a = run(cu_a, h0[keep], dht[keep])
+    o_b, ht_b, g_b = run(cu_b, h0, dht)
+    assert torch.equal(o_a, o_b) and torch.equal(ht_a, ht_b[keep])
+    for x, y in zip(g_a[:5], g_b[:5]):
+        assert torch.equal(x, y)
+    assert torch.equal(g_a[5], g_b[5][keep])
+    assert torch.equal(ht_b[1].cpu(), h0[1]) and torch.equal(g_b[5][1].cpu(), dht[1])

@@ -156,3 +156,31 @@ def test_kda_backward_through_the_gate_activation():
     assert_close("d_raw_gate", raw_d.grad, raw64.grad, TOL, stored_bf16=True)
     assert_close("dA_log", A_d.grad, A64.grad, TOL)
     assert_close("d_dt_bias", b_d.grad, b64.grad, TOL)
+
+
+@pytest.mark.parametrize("recompute", [True, False])
+def test_kda_empty_sequence_in_a_packed_batch(recompute):
+    """A zero-length sequence between two others changes nothing for its neighbours; its final state is its initial state
+    and the gradient of its initial state is its dht."""
+    from fla_b200.ops import chunk_kda
+    cu_a, cu_b = [0, 70, 71, 200], [0, 70, 70, 71, 200]
+    inp = oracle.make_kda_inputs(1, 200, 1, 2, seed=321)
+    gen = torch.Generator().manual_seed(322)
+    h0 = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
+    dht = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
+    keep = [0, 2, 3]                                   # sequence 1 of the second batch is the empty one
+
+    def run(cu, h, dh):
+        leaves = {n: inp[n].cuda().requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
+        h_d = h.cuda().requires_grad_(True)
+        o, ht = chunk_kda(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], initial_state=h_d,
+                          output_final_state=True, cu_seqlens=torch.tensor(cu, dtype=torch.int32), disable_recompute=not recompute)
+        ((o.float() * inp["do"].cuda().float()).sum() + (ht * dh.cuda()).sum()).backward()
+        return o.detach(), ht.detach(), [leaves[n].grad for n in ("q", "k", "v", "g", "beta")], h_d.grad
+    o_a, ht_a, g_a, dh_a = run(cu_a, h0[keep], dht[keep])
+    o_b, ht_b, g_b, dh_b = run(cu_b, h0, dht)
+    assert torch.equal(o_a, o_b) and torch.equal(ht_a, ht_b[keep])
+    for x, y in zip(g_a, g_b):
+        assert torch.equal(x, y)
+    assert torch.equal(dh_a, dh_b[keep])
+    assert torch.equal(ht_b[1].cpu(), h0[1]) and torch.equal(dh_b[1].cpu(), dht[1])
