@@ -86,22 +86,35 @@ class ChunkKdaFunction(torch.autograd.Function):
     """Autograd glue of `chunk_kda` (gate already activated): saves only the inputs, the backward recomputes."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype, disable_recompute):
+    def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype, disable_recompute,
+                qk_l2norm=False):
+        ctx.qk_l2norm = qk_l2norm
+        rstd = ()
+        if qk_l2norm:   # q, k <- x * rsqrt(sum x^2 + 1e-6) stored in the input dtype; rstd kept for the backward
+            from .l2norm import l2norm_fwd
+            q, q_rstd = l2norm_fwd(q)
+            k, k_rstd = l2norm_fwd(k)
+            rstd = (q_rstd, k_rstd)
         o, ht, saved = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, 0, None, None, None, meta,
                                     False, output_dtype, keep_for_backward=disable_recompute)
-        ctx.save_for_backward(q, k, v, g, beta, initial_state, saved if disable_recompute else None)
+        ctx.save_for_backward(q, k, v, g, beta, initial_state, saved if disable_recompute else None, *rstd)
         ctx.scale, ctx.meta = scale, meta
         ctx.in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, g, beta, h0, saved = ctx.saved_tensors
+        q, k, v, g, beta, h0, saved = ctx.saved_tensors[:7]
         dq, dk, dv, dg, dbeta, dh0 = kda_chunk_bwd(q, k, v, g, beta, ctx.scale, h0, do.contiguous(), dht, ctx.meta,
-                                                   saved=saved)
+                                                   saved=saved, grad_dtype=torch.float32 if ctx.qk_l2norm else None)
+        if ctx.qk_l2norm:
+            from .l2norm import l2norm_bwd
+            q_rstd, k_rstd = ctx.saved_tensors[7:9]
+            dq = l2norm_bwd(q, q_rstd, dq)
+            dk = l2norm_bwd(k, k_rstd, dk)
         dts = ctx.in_dtypes
         return (dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]), dg.to(dts[3]), dbeta.to(dts[4]), dh0,
-                None, None, None, None, None)
+                None, None, None, None, None, None)
 
 
 def chunk_kda_fwd_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, output_dtype=None, grad_dtype=None,
@@ -140,8 +153,8 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     when ``return_gate_cumsum``).  ``export_scores`` (inference only): a pair of `[B,T,HV,64]` views that receive the
     per-chunk blocks Aqk and Akk (what `npu_chunk_kda_fwd` returns)."""
     op = "chunk_kda"
-    if use_qk_l2norm_in_kernel or use_beta_sigmoid_in_kernel:
-        raise NotImplementedError(f"{op}: in-kernel q/k L2 norm and beta sigmoid are not available yet")
+    if use_beta_sigmoid_in_kernel:
+        raise NotImplementedError(f"{op}: the beta sigmoid is only fused into the decode operator (recurrent_kda)")
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != torch.bfloat16:
             raise TypeError(f"{op}: {name} must be bfloat16, got {t.dtype}")
@@ -189,8 +202,11 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         if return_gate_cumsum or export_scores is not None:
             raise NotImplementedError(f"{op}: return_gate_cumsum / export_scores are not available on the differentiable path")
         o, ht = ChunkKdaFunction.apply(q, k, v, g, beta, initial_state, scale, output_final_state, meta, output_dtype,
-                                       bool(disable_recompute))
+                                       bool(disable_recompute), bool(use_qk_l2norm_in_kernel))
         return o, ht
+    if use_qk_l2norm_in_kernel:   # x * rsqrt(sum x^2 + 1e-6), stored in the input dtype (the l2norm kernels)
+        from .l2norm import l2norm_fwd
+        q, k = l2norm_fwd(q)[0], l2norm_fwd(k)[0]
     o, ht, gk = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias,
                              lower_bound, meta, return_gate_cumsum, output_dtype, scores=export_scores)
     if return_gate_cumsum:

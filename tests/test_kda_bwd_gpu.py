@@ -184,3 +184,30 @@ def test_kda_empty_sequence_in_a_packed_batch(recompute):
         assert torch.equal(x, y)
     assert torch.equal(dh_a, dh_b[keep])
     assert torch.equal(ht_b[1].cpu(), h0[1]) and torch.equal(dh_b[1].cpu(), dht[1])
+
+
+def test_kda_qk_l2norm_in_kernel():
+    """use_qk_l2norm_in_kernel normalises raw q, k rows (x * rsqrt(sum x^2 + 1e-6)) and differentiates through it."""
+    from fla_b200.ops import chunk_kda
+    B, T, HK, HV = 1, 150, 1, 2
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=555)
+    gen = torch.Generator().manual_seed(556)
+    q_raw = (2.0 * torch.randn(B, T, HK, 128, generator=gen)).bfloat16()
+    k_raw = (0.5 * torch.randn(B, T, HK, 128, generator=gen)).bfloat16()
+
+    def norm(x):
+        return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+    qr, kr = q_raw.double().requires_grad_(True), k_raw.double().requires_grad_(True)
+    # the operator stores the normalised rows in bf16, like the reference's l2norm_fwd: the oracle sees the same rounding
+    qn = norm(qr) + (norm(qr).detach().bfloat16().double() - norm(qr).detach())
+    kn = norm(kr) + (norm(kr).detach().bfloat16().double() - norm(kr).detach())
+    ref = oracle.naive_recurrent_kda(qn.repeat_interleave(HV // HK, 2), kn.repeat_interleave(HV // HK, 2), inp["v"].double(),
+                                     inp["g"].double(), inp["beta"].double(), scale=128 ** -0.5, dtype=torch.float64)[0]
+    (ref * inp["do"].double()).sum().backward()
+    qd, kd = q_raw.cuda().requires_grad_(True), k_raw.cuda().requires_grad_(True)
+    o, _ = chunk_kda(qd, kd, inp["v"].cuda(), inp["g"].cuda(), inp["beta"].cuda(), use_qk_l2norm_in_kernel=True,
+                     output_dtype=torch.float32)
+    (o * inp["do"].cuda().float()).sum().backward()
+    assert_close("o", o, ref.detach(), TOL)
+    assert_close("dq", qd.grad, qr.grad, TOL, stored_bf16=True)
+    assert_close("dk", kd.grad, kr.grad, TOL, stored_bf16=True)
