@@ -78,7 +78,7 @@ constexpr int kRecThreads = 256;
 // are independent recurrences, so a CTA owns VT of the V value channels: K-first ROWS = K, COLS = VT, LD = V;
 // V-first ROWS = VT, COLS = K, LD = K.
 template <int K, int V, int VT, typename ST, bool VFIRST>
-__global__ void __launch_bounds__(kRecThreads) recurrent_gdn_kernel(RecurrentParams p) {
+__global__ void __launch_bounds__(kRecThreads, 3) recurrent_gdn_kernel(RecurrentParams p) {
   constexpr int ROWS = VFIRST ? VT : K;
   constexpr int COLS = VFIRST ? K : VT;
   constexpr int LD = VFIRST ? K : V;
