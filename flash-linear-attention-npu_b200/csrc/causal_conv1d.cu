@@ -72,11 +72,11 @@ struct ConvFwdParams {
 };
 
 constexpr int kConvTile = 64;     // tokens per CTA tile
-constexpr int kConvGroup = 8;     // tokens processed per inner step (independent 16-byte loads in flight)
+constexpr int kConvGroup = 4;     // tokens processed per inner step (independent 16-byte loads in flight); 4 keeps 128 registers = 4 CTAs per SM
 constexpr int kConvThreads = 128;
 
 template <int W, bool HAS_RES, bool SILU>
-__global__ void __launch_bounds__(kConvThreads, 3) conv_fwd_kernel(ConvFwdParams p) {
+__global__ void __launch_bounds__(kConvThreads, 4) conv_fwd_kernel(ConvFwdParams p) {
   constexpr int G = kConvGroup;
   const int d0 = (blockIdx.x * kConvThreads + threadIdx.x) * 8;
   if (d0 >= p.D) return;
