@@ -334,10 +334,10 @@ class Workload:
             return None     # the capture is of the training forward (it also writes the saved images)
         if kname in per_chunk_head and "T" in c:
             return per_chunk_head[kname] * c["B"] * ((c["T"] + 63) // 64) * c["HV"]
-        if kname == "recurrent_gdn":       # 212.33 MB for 64 sequences x 32 heads
-            return 212.33e6 / 64 * c["N"] * c["HV"] / 32
-        if kname == "causal_conv1d_fwd":   # 227.88 MB for 2 x 4096 x 8192 elements
-            return 227.88e6 / (2 * 4096 * 8192) * c["B"] * c["T"] * c["D"]
+        if kname == "recurrent_gdn":       # 212.29 MB for 64 sequences x 32 heads
+            return 212.29e6 / 64 * c["N"] * c["HV"] / 32
+        if kname == "causal_conv1d_fwd":   # 229.92 MB for 2 x 4096 x 8192 elements
+            return 229.92e6 / (2 * 4096 * 8192) * c["B"] * c["T"] * c["D"]
         if kname == "causal_conv1d_bwd":   # 391.52 MB for 2 x 4096 x 8192 elements
             return 391.52e6 / (2 * 4096 * 8192) * c["B"] * c["T"] * c["D"]
         return None
