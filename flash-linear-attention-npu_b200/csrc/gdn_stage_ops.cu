@@ -1220,7 +1220,7 @@ constexpr uint32_t wyOffP = wyOffR, wyOffPl = wyOffR + 8192, wyOffP5 = wyOffR + 
                    wyOffM = wyOffR + 32768, wyOffMl = wyOffR + 40960, wyOffMb = wyOffR + 49152, wyOffMbl = wyOffR + 57344,
                    wyOffW = wyOffR + 65536;
 constexpr uint32_t kWySmem = wyOffR + 65536 + 16896;
-__global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_x,
+__global__ void __launch_bounds__(256) stage_wy_bwd_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_x,
                                                            const __grid_constant__ CUtensorMap tm_k,
                                                            const __grid_constant__ CUtensorMap tm_v,
                                                            const __grid_constant__ CUtensorMap tm_dw,
@@ -1228,9 +1228,15 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   __shared__ float gam_s[kC], beta_s[kC];
+  __shared__ float part_s[5][kC];    // second column half's partial row sums: row_w, dbeta, col_w, kdk, kdkbg
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t mma_bar, load_bar;
+  // 8 warps: the accumulator rows 0..63 live in TMEM lanes 0..63, which only warps 0, 1, 4, 5 can read; warps 0, 1 take
+  // the first half of a tile's columns and warps 4, 5 the second (`half`), the other four warps help with the
+  // cooperative shared-memory passes only.
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int half = warp >> 2;
+  const bool rowwarp = (warp & 3) < 2;
   const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   if (c >= sq.nt) return;
@@ -1265,11 +1271,11 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
   tc_fence_before();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const uint32_t trow = tmem_addr(tbase, (warp & 3) * 32, 0);
   constexpr uint32_t cP = 0, cS = 64, cKbg = 128, cVb = 256, cT2 = 384;   // cVb is reused for dA k
   bool ok = mbar_wait(&load_bar, 0, p.status, FLA_ERR_TIMEOUT);
   // rows >= rows of every tile are zeroed in place (they hold the next sequence's rows or zeros), X also in its columns
-  for (int idx = tid; idx < kC * 72; idx += 128) {
+  for (int idx = tid; idx < kC * 72; idx += 256) {
     const int r = idx / 72, ch = idx % 72;
     if (r < rows && (ch >= 8 || ch * 8 + 8 <= rows)) continue;
     uint8_t* base = ch < 8 ? smem + wyOffX + panel_chunk_off(r, ch)
@@ -1284,7 +1290,7 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
   }
   __syncthreads();
   // (k beta e^g) and (v beta) as value + residual
-  for (int idx = tid; idx < 2 * kC * 16; idx += 128) {
+  for (int idx = tid; idx < 2 * kC * 16; idx += 256) {
     const int isv = idx >> 10, r = (idx >> 4) & 63, ch = idx & 15;
     const uint32_t off = (ch >> 3) * 8192 + panel_chunk_off(r, ch & 7);
     float f[8];
@@ -1309,7 +1315,7 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
   uint32_t mphase = 0;
   const int i = tid & 63;
   const bool live = i < rows;
-  float m_row[64];   // my row of dA (row = later token)
+  float m_row[32];   // my 32 columns (32 * half ..) of row i of dA (row = later token)
   if (ok) {
     if (tid == 0) {
       tc_fence_after();
@@ -1332,12 +1338,13 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
     ok = __syncthreads_and(ok);
   }
   if (ok && p.wy_mode != 2) {
-    if (warp < 2) {
-      float r[64];
-      tmem_ld_row64(trow + cP, r);
+    if (rowwarp) {
+      float r[32];
+      tmem_ld32(trow + cP + half * 32, r);
+      tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 64; ++j) r[j] = (live && j < i) ? r[j] : 0.f;
-      row64_to_hilo(smem + wyOffP, smem + wyOffPl, i, r);
+      for (int j = 0; j < 32; ++j) r[j] = (live && half * 32 + j < i) ? r[j] : 0.f;
+      row32_to_hilo(smem + wyOffP, smem + wyOffPl, i, half, r);
     }
     fence_async_smem();
     tc_fence_before();
@@ -1351,10 +1358,11 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
     ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
     mphase ^= 1;
     tc_fence_after();
-    if (warp < 2) {
-      float r[64];
-      tmem_ld_row64(trow + cP, r);
-      row64_to_hilo(smem + wyOffP5, smem + wyOffP5l, i, r);
+    if (rowwarp) {
+      float r[32];
+      tmem_ld32(trow + cP + half * 32, r);
+      tmem_ld_wait();
+      row32_to_hilo(smem + wyOffP5, smem + wyOffP5l, i, half, r);
     }
     fence_async_smem();
     tc_fence_before();
@@ -1369,43 +1377,52 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
       ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
       mphase ^= 1;
       tc_fence_after();
-      if (warp < 2) {
-        tmem_ld_row64(trow + cP, m_row);
+      if (rowwarp) {
+        tmem_ld32(trow + cP + half * 32, m_row);
+        tmem_ld_wait();
         const float gi = gam_s[i];
 #pragma unroll
-        for (int j = 0; j < 64; ++j) m_row[j] = (live && j < i) ? -m_row[j] * __expf(gi - gam_s[j]) : 0.f;
+        for (int j = 0; j < 32; ++j) {
+          const int jj = half * 32 + j;
+          m_row[j] = (live && jj < i) ? -m_row[j] * __expf(gi - gam_s[jj]) : 0.f;
+        }
         if (p.wy_mode == 1) {   // dA is stored transposed: element (j, i) of the chunk's block (zero on and above the diagonal)
-          for (int j = 0; j < rows; ++j) st_any(const_cast<void*>(p.o0.p), row_off(p.o0, b, hv, t0 + j) + i, p.o0.dtype, m_row[j]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (half * 32 + j < rows)
+              st_any(const_cast<void*>(p.o0.p), row_off(p.o0, b, hv, t0 + half * 32 + j) + i, p.o0.dtype, m_row[j]);
         }
       }
       ok = __syncthreads_and(ok);
     }
-  } else if (ok && warp < 2) {
+  } else if (ok && rowwarp) {
     // the given dA is stored transposed: my row i of dA is column i of the chunk's block
 #pragma unroll 8
-    for (int j = 0; j < 64; ++j)
-      m_row[j] = (live && j < i) ? ld_any(p.a.p, row_off(p.a, b, hv, t0 + j) + i, p.a.dtype) : 0.f;
+    for (int j = 0; j < 32; ++j) {
+      const int jj = half * 32 + j;
+      m_row[j] = (live && jj < i) ? ld_any(p.a.p, row_off(p.a, b, hv, t0 + jj) + i, p.a.dtype) : 0.f;
+    }
   }
   if (ok && p.wy_mode != 1) {
     float* wt = reinterpret_cast<float*>(smem + wyOffW);
     float dbeta = 0.f, row_w = 0.f;
     const float bi = beta_s[i], egi = __expf(gam_s[i]);
-    if (warp < 2) {
-      row64_to_hilo(smem + wyOffM, smem + wyOffMl, i, m_row);
-      float s[64];
-      tmem_ld_row64(trow + cS, s);
+    if (rowwarp) {
+      row32_to_hilo(smem + wyOffM, smem + wyOffMl, i, half, m_row);
+      float s[32];
+      tmem_ld32(trow + cS + half * 32, s);
+      tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
+      for (int j = 0; j < 32; ++j) {
         m_row[j] *= bi;
         const float w = m_row[j] * s[j];
         row_w += w;
-        wt[i * kColTile + j] = w;
+        wt[i * kColTile + half * 32 + j] = w;
       }
-      row64_to_hilo(smem + wyOffMb, smem + wyOffMbl, i, m_row);
-      // dv = beta (X^T du) and its part of dbeta; this frees the accumulator for dA k
+      row32_to_hilo(smem + wyOffMb, smem + wyOffMbl, i, half, m_row);
+      // dv = beta (X^T du) and its part of dbeta (my 64 of the 128 value columns); this frees the accumulator for dA k
       bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o1.p)) + row_off(p.o1, b, hv, t0 + i);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float r[64];
         tmem_ld_row64(trow + cVb + half * 64, r);
 #pragma unroll
@@ -1436,18 +1453,17 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
       mma_commit(&mma_bar);
     }
     float col_w = 0.f;
-    if (warp < 2) {
+    if (rowwarp) {   // column i of W, my 32 of its 64 rows
 #pragma unroll 8
-      for (int r = 0; r < kC; ++r) col_w += wt[r * kColTile + i];
+      for (int r = 0; r < 32; ++r) col_w += wt[(half * 32 + r) * kColTile + i];
     }
     ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
     mphase ^= 1;
     tc_fence_after();
-    if (warp < 2 && ok) {
-      float kdk = 0.f, kdkbg = 0.f;
-      const float f2 = bi * egi;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+    float kdk = 0.f, kdkbg = 0.f;
+    const float f2 = bi * egi;
+    if (rowwarp && ok) {
+      {   // my 64 of the 128 key columns
         float t1[64], acc[64];
         tmem_ld_row64(trow + cVb + half * 64, t1);
         tmem_ld_row64(trow + cT2 + half * 64, acc);
@@ -1477,10 +1493,16 @@ __global__ void __launch_bounds__(128) stage_wy_bwd_kernel(StageParams p, const 
           }
         }
       }
-      if (live) {
-        st_any(const_cast<void*>(p.o2.p), row_off(p.o2, b, hv, t0 + i), p.o2.dtype, dbeta + kdk + egi * kdkbg);
-        st_any(const_cast<void*>(p.o3.p), row_off(p.o3, b, hv, t0 + i), p.o3.dtype, f2 * kdkbg + row_w - col_w);
-      }
+    }
+    // the two column halves add their row sums: the second half publishes, the first finishes the row
+    if (rowwarp && half == 1) {
+      part_s[0][i] = row_w; part_s[1][i] = dbeta; part_s[2][i] = col_w; part_s[3][i] = kdk; part_s[4][i] = kdkbg;
+    }
+    __syncthreads();
+    if (rowwarp && half == 0 && ok && live) {
+      row_w += part_s[0][i]; dbeta += part_s[1][i]; col_w += part_s[2][i]; kdk += part_s[3][i]; kdkbg += part_s[4][i];
+      st_any(const_cast<void*>(p.o2.p), row_off(p.o2, b, hv, t0 + i), p.o2.dtype, dbeta + kdk + egi * kdkbg);
+      st_any(const_cast<void*>(p.o3.p), row_off(p.o3, b, hv, t0 + i), p.o3.dtype, f2 * kdkbg + row_w - col_w);
     }
   }
   tc_fence_before();
@@ -1987,7 +2009,7 @@ static int wy_bwd_launch(const fla_chunk_stage_args* a, void* workspace, uint64_
     return FLA_ERR_CUDA;
   {
     KernelTimer kt("prepare_wy_repr_bwd", cs);
-    stage_wy_bwd_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kWySmem + 1024, cs>>>(p, tm_x, tm_k, tm_v, tm_dw, tm_du);
+    stage_wy_bwd_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 256, kWySmem + 1024, cs>>>(p, tm_x, tm_k, tm_v, tm_dw, tm_du);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   if (scratch) {
