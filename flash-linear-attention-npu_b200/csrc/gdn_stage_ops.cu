@@ -976,7 +976,7 @@ constexpr uint32_t dqOffA = 0, dqOffV = 32768, dqOffQ = 49152, dqOffK = 65536, d
                    dqOffDSl = 155648;
 constexpr uint32_t kDqkwgSmem = 172032;   // 8 KB behind the residual panel: rows 64..127 of the M = 128 views of it
 constexpr int kColTile = 65;              // fp32 row stride of the ds2 tile (reuses the h panels)
-__global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(256) stage_dqkwg_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
                                                           const __grid_constant__ CUtensorMap tm_k,
                                                           const __grid_constant__ CUtensorMap tm_v,
                                                           const __grid_constant__ CUtensorMap tm_do,
@@ -986,10 +986,13 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   __shared__ float gam_s[kC];
-  __shared__ float red_s[8];
+  __shared__ float red_s[10];        // <h, dh> per warp (8), k.dk_state per row warp (2)
+  __shared__ float part_s[3][kC];    // second column half's partial row sums dgA, dgB, dgC
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(8) uint64_t mma_bar, load_bar;
+  // 8 warps: warp w reads TMEM lanes 32 (w % 4) ..; `half` = w / 4 selects which half of a tile's columns it handles
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int half = warp >> 2, quad = warp & 3;
   const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   if (c >= sq.nt) return;
@@ -1027,7 +1030,7 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
   tc_fence_before();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const uint32_t trow = tmem_addr(tbase, quad * 32, 0);
   constexpr uint32_t cT0 = 0, cT1 = 128, cDs = 256, cQk = 320;
   const Operand opA{sb + dqOffA, 16384, 0}, opH{sb + dqOffH, 16384, 0}, opDH{sb + dqOffDH, 16384, 0}, opVa{sb + dqOffV, 8192, 0},
       opQa{sb + dqOffQ, 8192, 0}, opKb{sb + dqOffK, 8192, 0}, opKn{sb + dqOffK, 8192, 1}, opQn{sb + dqOffQ, 8192, 1},
@@ -1041,11 +1044,11 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
     mma_tile(tbase + cQk, opQa, opKb, 128, 64, 8, false);    // q k^T
     mma_commit(&mma_bar);
   }
-  // <h, dh> while the MMAs run: thread t owns key row t of both tiles
+  // <h, dh> while the MMAs run: thread t owns one panel (64 value columns) of key row t % 128 of both tiles
   float hd = 0.f;
 #pragma unroll
-  for (int ch = 0; ch < 16; ++ch) {
-    const uint32_t off = (ch >> 3) * 16384 + panel_chunk_off(tid, ch & 7);
+  for (int ch = 0; ch < 8; ++ch) {
+    const uint32_t off = (tid >> 7) * 16384 + panel_chunk_off(tid & 127, ch);
     float a[8], d[8];
     unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + dqOffH + off), a);
     unpack_bf16x8(*reinterpret_cast<const uint4*>(smem + dqOffDH + off), d);
@@ -1064,12 +1067,11 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
     const int i = tid & 63;
     const bool live = i < rows;
     const float gi = gam_s[i], gl = gam_s[rows - 1];
-    if (warp >= 2) {
-      // dw rows: -(dv h^T)
+    if (quad >= 2) {
+      // dw rows: -(dv h^T), my 64 of the 128 key columns
       if (p.o2.p) {
         bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o2.p)) + row_off(p.o2, b, hv, t0 + i);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        {
           float r[64];
           tmem_ld_row64(trow + cT0 + half * 64, r);
           if (live) {
@@ -1081,22 +1083,23 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
         }
       }
     } else {
-      {
-        float ds[64], qk[64];
-        tmem_ld_row64(trow + cDs, ds);
-        tmem_ld_row64(trow + cQk, qk);
+      {   // my 32 of the 64 score columns
+        float ds[32], qk[32];
+        tmem_ld32(trow + cDs + half * 32, ds);
+        tmem_ld32(trow + cQk + half * 32, qk);
+        tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          ds[j] = (live && j <= i) ? p.scale * ds[j] * __expf(gi - gam_s[j]) : 0.f;
+        for (int j = 0; j < 32; ++j) {
+          const int jj = half * 32 + j;
+          ds[j] = (live && jj <= i) ? p.scale * ds[j] * __expf(gi - gam_s[jj]) : 0.f;
           const float d2 = ds[j] * qk[j];
           dgC += d2;
-          tile[i * kColTile + j] = d2;
+          tile[i * kColTile + jj] = d2;
         }
-        row64_to_hilo(smem + dqOffDS, smem + dqOffDSl, i, ds);
+        row32_to_hilo(smem + dqOffDS, smem + dqOffDSl, i, half, ds);
       }
       const float fq = live ? p.scale * __expf(gi) : 0.f, fk = live ? __expf(gl - gi) : 0.f;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {   // my 64 of the 128 key columns
         float r[64];
         tmem_ld_row64(trow + cT0 + half * 64, r);
 #pragma unroll
@@ -1123,6 +1126,7 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
         }
         tmem_st_row64(trow + cT1 + half * 64, r);
       }
+      if (half == 1) { part_s[0][i] = dgA; part_s[1][i] = dgB; part_s[2][i] = dgC; }
     }
     fence_async_smem();
     tc_fence_before();
@@ -1136,28 +1140,30 @@ __global__ void __launch_bounds__(128) stage_dqkwg_kernel(StageParams p, const _
       mma_commit(&mma_bar);
     }
     if (warp < 2) {
-      // dg while the MMAs run: column sums of ds2, the last-row term
+      // dg while the MMAs run (first column half's threads, which add the other half's row sums): column sums of ds2,
+      // the last-row term
+      dgA += part_s[0][i]; dgB += part_s[1][i]; dgC += part_s[2][i];
       float col = 0.f;
 #pragma unroll 8
       for (int r = 0; r < kC; ++r) col += tile[r * kColTile + i];
       float sB = dgB;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) sB += __shfl_xor_sync(0xffffffffu, sB, o);
-      if (lane == 0) red_s[4 + warp] = sB;
+      if (lane == 0) red_s[8 + warp] = sB;
       asm volatile("bar.sync 3, 64;" ::: "memory");
       float dg = dgA - dgB + dgC - col;
-      if (i == rows - 1) dg += __expf(gl) * (red_s[0] + red_s[1] + red_s[2] + red_s[3]) + red_s[4] + red_s[5];
+      if (i == rows - 1)
+        dg += __expf(gl) * (((red_s[0] + red_s[1]) + (red_s[2] + red_s[3])) + ((red_s[4] + red_s[5]) + (red_s[6] + red_s[7]))) + red_s[8] + red_s[9];
       if (live) st_any(const_cast<void*>(p.o3.p), row_off(p.o3, b, hv, t0 + i), p.o3.dtype, dg);
     }
     ok = mbar_wait(&mma_bar, 1, p.status, FLA_ERR_TIMEOUT);
     tc_fence_after();
-    if (warp < 2) {
+    if (quad < 2) {
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const StageView& ov = which ? p.o1 : p.o0;
         float* wrow = (which ? p.ws_dk : p.ws_dq);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        {   // my 64 of the 128 key columns
           float r[64];
           tmem_ld_row64(trow + (which ? cT1 : cT0) + half * 64, r);
           if (ok && live) {
@@ -1943,7 +1949,7 @@ extern "C" FLA_API int fla_b200_chunk_bwd_dqkwg(const fla_chunk_stage_args* a, v
     return FLA_ERR_CUDA;
   {
     KernelTimer kt("chunk_bwd_dqkwg", cs);
-    stage_dqkwg_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kDqkwgSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_do, tm_dv, tm_h, tm_dh);
+    stage_dqkwg_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 256, kDqkwgSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_do, tm_dv, tm_h, tm_dh);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   if (scratch) {
