@@ -564,7 +564,7 @@ __global__ void __launch_bounds__(128) stage_fwd_h_kernel(StageParams p, const _
 // tiles issued up front; the decayed score tile is split into a bf16 value and a residual (which reuses the k panels).
 constexpr uint32_t foOffP = 0, foOffQ = 8192, foOffK = 24576, foOffH = 40960, foOffVn = 73728;
 constexpr uint32_t kFwdOSmem = 90112;
-__global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(256) stage_fwd_o_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
                                                           const __grid_constant__ CUtensorMap tm_k,
                                                           const __grid_constant__ CUtensorMap tm_v,
                                                           const __grid_constant__ CUtensorMap tm_h) {
@@ -606,7 +606,9 @@ __global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p, const _
   tc_fence_before();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const int half = warp >> 2;                       // warps 0, 1 / 4, 5 read the 64 accumulator rows: one column half each
+  const bool rowwarp = (warp & 3) < 2;
+  const uint32_t trow = tmem_addr(tbase, (warp & 3) * 32, 0);
   // q and the score tile as A: rows 64..127 of the M = 128 tiles read the panels behind them and are never used
   const Operand opQ{sb + foOffQ, 8192, 0}, opK{sb + foOffK, 8192, 0}, opH{sb + foOffH, 16384, 1}, opVn{sb + foOffVn, 8192, 1},
       opP{sb + foOffP, 8192, 0}, opPl{sb + foOffK, 8192, 0};
@@ -620,20 +622,23 @@ __global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p, const _
   }
   ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT) && ok;
   tc_fence_after();
-  if (warp < 2) {
-    const int i = tid;
+  if (rowwarp) {
+    const int i = tid & 63;
     const float gi = gam_s[i];
     {
-      float s[64];
-      tmem_ld_row64(trow, s);
+      float s[32];
+      tmem_ld32(trow + half * 32, s);
+      tmem_ld_wait();
       // rows and columns past the end of the sequence (foreign or zero tile rows) are masked here
 #pragma unroll
-      for (int j = 0; j < 64; ++j) s[j] = (j <= i && j < rows && i < rows) ? s[j] * __expf(gi - gam_s[j]) : 0.f;
-      row64_to_hilo(smem + foOffP, smem + foOffK, i, s);
+      for (int j = 0; j < 32; ++j) {
+        const int jj = half * 32 + j;
+        s[j] = (jj <= i && jj < rows && i < rows) ? s[j] * __expf(gi - gam_s[jj]) : 0.f;
+      }
+      row32_to_hilo(smem + foOffP, smem + foOffK, i, half, s);
     }
     const float eg = __expf(gi);
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    {
       float r[64];
       tmem_ld_row64(trow + 64 + half * 64, r);
 #pragma unroll
@@ -653,11 +658,10 @@ __global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p, const _
     }
     ok = mbar_wait(&mma_bar, 1, p.status, FLA_ERR_TIMEOUT);
     tc_fence_after();
-    if (warp < 2) {
-      const int i = tid;
+    if (rowwarp) {
+      const int i = tid & 63;
       bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o0.p)) + row_off(p.o0, b, hv, t0 + i);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float r[64];
         tmem_ld_row64(trow + 64 + half * 64, r);
         if (ok && i < rows) {
@@ -678,7 +682,7 @@ __global__ void __launch_bounds__(128) stage_fwd_o_kernel(StageParams p, const _
 // dv_j = sum_{i >= j} scale (k_j . q_i) e^{g_i - g_j} dO_i inside a chunk, per value head.
 constexpr uint32_t dvOffP = 0, dvOffPl = 8192, dvOffK = 16384, dvOffQ = 32768, dvOffDo = 49152;
 constexpr uint32_t kDvLocalSmem = 65536;
-__global__ void __launch_bounds__(128) stage_dv_local_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(256) stage_dv_local_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_q,
                                                              const __grid_constant__ CUtensorMap tm_k,
                                                              const __grid_constant__ CUtensorMap tm_do) {
   extern __shared__ uint8_t smem_raw[];
@@ -715,7 +719,9 @@ __global__ void __launch_bounds__(128) stage_dv_local_kernel(StageParams p, cons
   tc_fence_before();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, warp * 32, 0);
+  const int half = warp >> 2;                       // warps 0, 1 / 4, 5 read the 64 accumulator rows: one column half each
+  const bool rowwarp = (warp & 3) < 2;
+  const uint32_t trow = tmem_addr(tbase, (warp & 3) * 32, 0);
   // k and the score tile as A: rows 64..127 of the M = 128 tiles read the panels behind them and are never used
   const Operand opK{sb + dvOffK, 8192, 0}, opQ{sb + dvOffQ, 8192, 0}, opDo{sb + dvOffDo, 8192, 1}, opP{sb + dvOffP, 8192, 0},
       opPl{sb + dvOffPl, 8192, 0};
@@ -728,14 +734,18 @@ __global__ void __launch_bounds__(128) stage_dv_local_kernel(StageParams p, cons
   }
   ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT) && ok;
   tc_fence_after();
-  if (warp < 2) {
-    const int j = tid;
+  if (rowwarp) {
+    const int j = tid & 63;
     const float gj = gam_s[j];
-    float s[64];
-    tmem_ld_row64(trow, s);
+    float s[32];
+    tmem_ld32(trow + half * 32, s);
+    tmem_ld_wait();
 #pragma unroll
-    for (int i = 0; i < 64; ++i) s[i] = (i >= j && i < rows && j < rows) ? p.scale * s[i] * __expf(gam_s[i] - gj) : 0.f;
-    row64_to_hilo(smem + dvOffP, smem + dvOffPl, j, s);
+    for (int i = 0; i < 32; ++i) {
+      const int ii = half * 32 + i;
+      s[i] = (ii >= j && ii < rows && j < rows) ? p.scale * s[i] * __expf(gam_s[ii] - gj) : 0.f;
+    }
+    row32_to_hilo(smem + dvOffP, smem + dvOffPl, j, half, s);
   }
   fence_async_smem();
   tc_fence_before();
@@ -749,11 +759,10 @@ __global__ void __launch_bounds__(128) stage_dv_local_kernel(StageParams p, cons
     }
     ok = mbar_wait(&mma_bar, 1, p.status, FLA_ERR_TIMEOUT);
     tc_fence_after();
-    if (warp < 2) {
-      const int j = tid;
+    if (rowwarp) {
+      const int j = tid & 63;
       bf16* dst = static_cast<bf16*>(const_cast<void*>(p.o0.p)) + row_off(p.o0, b, hv, t0 + j);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float r[64];
         tmem_ld_row64(trow + 64 + half * 64, r);
         if (ok && j < rows) {
@@ -1796,7 +1805,7 @@ extern "C" FLA_API int fla_b200_chunk_fwd_o(const fla_chunk_stage_args* a, void*
       make_bhtd_tile_map(&tm_h, h.data, 2, kV, uint64_t(gm.B) * gm.H * NT * kK, 1, 1, kV, 0, 0, 64, 128))
     return FLA_ERR_CUDA;
   KernelTimer kt("chunk_fwd_o", cs);
-  stage_fwd_o_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kFwdOSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_h);
+  stage_fwd_o_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 256, kFwdOSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_h);
   return cuda_status(cudaGetLastError());
 }
 
@@ -1828,7 +1837,7 @@ extern "C" FLA_API int fla_b200_chunk_bwd_dv_local(const fla_chunk_stage_args* a
   CUtensorMap tm_q, tm_k, tm_do;
   if (token_tile_map(a->q, &tm_q) || token_tile_map(a->k, &tm_k) || token_tile_map(d_o, &tm_do)) return FLA_ERR_CUDA;
   KernelTimer kt("chunk_bwd_dv_local", cs);
-  stage_dv_local_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kDvLocalSmem + 1024, cs>>>(p, tm_q, tm_k, tm_do);
+  stage_dv_local_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 256, kDvLocalSmem + 1024, cs>>>(p, tm_q, tm_k, tm_do);
   return cuda_status(cudaGetLastError());
 }
 
