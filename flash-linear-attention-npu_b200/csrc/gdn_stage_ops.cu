@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(256) stage_solve_tri_kernel(StageParams p) {
 // residual panel.
 constexpr uint32_t wuOffX = 0, wuOffKh = 8192, wuOffKl = 24576, wuOffVh = 40960, wuOffVl = 57344;
 constexpr uint32_t kWuSmem = 73728;
-__global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_k,
+__global__ void __launch_bounds__(256) stage_wu_kernel(StageParams p, const __grid_constant__ CUtensorMap tm_k,
                                                        const __grid_constant__ CUtensorMap tm_v,
                                                        const __grid_constant__ CUtensorMap tm_x) {
   extern __shared__ uint8_t smem_raw[];
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p, const __gr
   __syncthreads();
   bool ok = mbar_wait(&load_bar, 0, p.status, FLA_ERR_TIMEOUT);
   // scale the raw rows in place and write the residual panels
-  for (int idx = tid; idx < 2 * kC * 16; idx += 128) {
+  for (int idx = tid; idx < 2 * kC * 16; idx += 256) {
     const int isv = idx >> 10, r = (idx >> 4) & 63, ch = idx & 15;
     const uint32_t off = (ch >> 3) * 8192 + panel_chunk_off(r, ch & 7);
     uint8_t* hi = smem + (isv ? wuOffVh : wuOffKh) + off;
@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p, const __gr
     *reinterpret_cast<uint4*>(lo) = l4;
   }
   if (rows < kC) {   // a short chunk: columns of X past its end may hold anything
-    for (int idx = tid; idx < kC * kC; idx += 128) {
+    for (int idx = tid; idx < kC * kC; idx += 256) {
       const int r = idx >> 6, cc = idx & 63;
       if (cc >= rows) *reinterpret_cast<uint16_t*>(smem + wuOffX + panel_off(r, cc)) = 0;
     }
@@ -364,16 +364,15 @@ __global__ void __launch_bounds__(128) stage_wu_kernel(StageParams p, const __gr
     }
     ok = mbar_wait(&mma_bar, 0, p.status, FLA_ERR_TIMEOUT);
     tc_fence_after();
-    if (warp < 2) {
-      const int i = tid;
+    if ((warp & 3) < 2) {   // warps 0, 1 / 4, 5 read the 64 accumulator rows: 64 of the 128 columns of w and of u each
+      const int i = tid & 63, half = warp >> 2;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const StageView& ov = which ? p.o1 : p.o0;
         bf16* dst = static_cast<bf16*>(const_cast<void*>(ov.p)) + row_off(ov, b, hv, t0 + i);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        {
           float r[64];
-          tmem_ld_row64(tmem_addr(tbase, warp * 32, which * 128 + half * 64), r);
+          tmem_ld_row64(tmem_addr(tbase, (warp & 3) * 32, which * 128 + half * 64), r);
           if (ok && i < rows) {
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + half * 64 + ch * 8) = pack8(r + ch * 8);
@@ -1721,7 +1720,7 @@ extern "C" FLA_API int fla_b200_recompute_w_u_fwd(const fla_chunk_stage_args* a,
   CUtensorMap tm_k, tm_v, tm_x;
   if (token_tile_map(a->k, &tm_k) || token_tile_map(a->v, &tm_v) || token_tile_map(a->A, &tm_x)) return FLA_ERR_CUDA;
   KernelTimer kt("recompute_w_u_fwd", cs);
-  stage_wu_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 128, kWuSmem + 1024, cs>>>(p, tm_k, tm_v, tm_x);
+  stage_wu_kernel<<<dim3(gm.nt_max, unsigned(gm.H), gm.N), 256, kWuSmem + 1024, cs>>>(p, tm_k, tm_v, tm_x);
   return cuda_status(cudaGetLastError());
 }
 
