@@ -328,8 +328,8 @@ class Workload:
         c = self.cfg
         per_chunk_head = {"gdn_fwd": 312.98e6 / 2048, "gdn_bwd_dhu": 346.22e6 / 2048, "gdn_bwd_par": 469.55e6 / 2048,
                           "kda_prep": 159.25e6 / 1024, "kda_fwd": 232.05e6 / 1024, "kda_bwd_dhu": 266.41e6 / 1024,
-                          "kda_bwd_par": 396.41e6 / 1024, "recompute_w_u_fwd": 88.55e6 / 2048, "chunk_fwd_h": 145.06e6 / 2048,
-                          "chunk_fwd_o": 152.34e6 / 2048}
+                          "kda_bwd_par": 396.41e6 / 1024, "recompute_w_u_fwd": 87.51e6 / 2048, "chunk_fwd_h": 144.66e6 / 2048,
+                          "chunk_fwd_o": 151.88e6 / 2048}
         if kname == "gdn_fwd" and self.name == "gdn_fwd_conv":
             return None     # the capture is of the training forward (it also writes the saved images)
         if kname in per_chunk_head and "T" in c:
