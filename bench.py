@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--shape B,T]
 
 One "step" is one pass of the hot path over one batch of seeded synthetic input with the shapes and value
-distributions of BASELINE.json.  Workloads (the default is the one the headline metric is quoted on):
+distributions of the benchmark specification.  Workloads (the default is the one the headline metric is quoted on):
   gdn_fwd_bwd    config 2: chunked GDN forward + backward, B=8 T=4096 HQK=16 HV=32 K=V=128, nonzero fp32 h0, dO, dht
   gdn_fwd_conv   config 1: causal_conv1d (W=4, SiLU) over x[8,4096,8192] bf16, then the chunked GDN forward
   kda_fwd        config 3 (forward half): chunked KDA, B=4 T=8192 H=32 K=V=128, g = logsigmoid/16 per channel
@@ -173,7 +173,7 @@ class Workload:
         self.tokens_per_step = c["N"] if name == "decode" else c["B"] * c["T"]
         self.token_heads = self.tokens_per_step * c["HV"]
 
-    # -- inputs (BASELINE.json distributions): q,k ~ N(0,1) L2-normalised; v ~ N(0,1); g = logsigmoid(N(0,1))
+    # -- inputs (the benchmark specification's distributions): q,k ~ N(0,1) L2-normalised; v ~ N(0,1); g = logsigmoid(N(0,1))
     #    (/16 per channel for KDA); beta = sigmoid(N(0,1)); states ~ 0.1 N(0,1) fp32; conv weights ~ N(0, 1/4).
     def make_inputs(self, device, seed):
         c = self.cfg

@@ -1,7 +1,7 @@
 """GDN oracle (test infrastructure only; never imported by the shipped package).
 
 `naive_recurrent_gated_delta_rule` follows the reference's naive fp32 recurrence
-(examples/flash_gated_delta_rule.py:1545-1571) and extends it with the two things BASELINE's
+(examples/flash_gated_delta_rule.py:1545-1571) and extends it with the two things the benchmark
 configurations need and the reference version lacks: an `initial_state` and the final state as a
 second return value.  `gdn_reference_fwd_bwd` follows the reference's autograd harness
 (examples/flash_gated_delta_rule.py:1574-1631): GVA by repeat_interleave, optional q/k L2
