@@ -214,28 +214,29 @@ __global__ void __launch_bounds__(128) stage_kkt_kernel(StageParams p) {
 
 // ----------------------------------------------------------------------------- solve_tri
 // X = (I + A)^-1 per chunk, A strictly lower triangular (entries on and above the diagonal are ignored), fp32
-// forward substitution, one thread per column (the scheme of tri_inverse.cu), four matrices per CTA.
+// forward substitution, one thread per column (the scheme of tri_inverse.cu), two matrices per CTA.
 constexpr int kSolveStride = 68;
-__global__ void __launch_bounds__(256) stage_solve_tri_kernel(StageParams p) {
+constexpr int kSolveTiles = 2;   // matrices per CTA; small CTAs under a register bound keep ten solves in flight per SM
+__global__ void __launch_bounds__(64 * kSolveTiles, 5) stage_solve_tri_kernel(StageParams p) {
   extern __shared__ float tri_sm[];
   const int tid = threadIdx.x, grp = tid / 64, c = tid % 64;
   const int n = blockIdx.z, chunk = blockIdx.x;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   if (chunk >= sq.nt) return;
-  const int hh = blockIdx.y * 4 + grp;
+  const int hh = blockIdx.y * kSolveTiles + grp;
   const bool active = hh < p.H;
   const int rows = min(kC, sq.len - chunk * kC);
   const int64_t b = p.cu_seqlens ? 0 : n;
   const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + chunk * kC;
   float* AT = tri_sm + grp * kC * kSolveStride;
-  // The four matrices of the CTA are staged together as AT[j][i] = A[i][j] (j < i).  A warp covers 8 rows x 16 columns:
+  // The matrices of the CTA are staged together as AT[j][i] = A[i][j] (j < i).  A warp covers 8 rows x 16 columns:
   // each thread reads four consecutive elements of a row (64 contiguous bytes per row and warp for fp32) and the
   // transposed stores of a warp fall on at most two addresses per bank.
   const bool vec4 = p.a.dtype == FLA_F32 && (reinterpret_cast<uintptr_t>(p.a.p) & 15) == 0 && ((p.a.sb | p.a.sh | p.a.st) & 3) == 0;
 #pragma unroll 4
-  for (int idx = tid; idx < 4 * kC * 16; idx += 256) {
+  for (int idx = tid; idx < kSolveTiles * kC * 16; idx += 64 * kSolveTiles) {
     const int m = idx >> 10, i = ((idx >> 5) & 7) * 8 + (idx & 7), jc = ((idx >> 8) & 3) * 4 + ((idx >> 3) & 3);
-    const int hm = blockIdx.y * 4 + m;
+    const int hm = blockIdx.y * kSolveTiles + m;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (hm < p.H && i < rows && jc * 4 < i) {
       const int64_t off = row_off(p.a, b, hm, t0 + i) + jc * 4;
@@ -1688,10 +1689,10 @@ extern "C" FLA_API int fla_b200_solve_tri(const fla_chunk_stage_args* a, void* w
   if ((st = geometry(a, a->A, &gm, &p))) return st;
   if ((st = make_view(a->A, 4, false, &p.a)) || (st = make_view(a->out0, 4, false, &p.o0))) return st;
   if (a->A.shape[3] != kC || !same_bht(a->out0, gm, gm.H) || a->out0.shape[3] != kC) return FLA_ERR_SHAPE;
-  const uint32_t smem = 4 * kC * kSolveStride * sizeof(float);
+  const uint32_t smem = kSolveTiles * kC * kSolveStride * sizeof(float);
   if ((st = opt_in_smem(stage_solve_tri_kernel, smem))) return st;
   KernelTimer kt("solve_tri", cs);
-  stage_solve_tri_kernel<<<dim3(gm.nt_max, unsigned((gm.H + 3) / 4), gm.N), 256, smem, cs>>>(p);
+  stage_solve_tri_kernel<<<dim3(gm.nt_max, unsigned((gm.H + kSolveTiles - 1) / kSolveTiles), gm.N), 64 * kSolveTiles, smem, cs>>>(p);
   return cuda_status(cudaGetLastError());
 }
 
