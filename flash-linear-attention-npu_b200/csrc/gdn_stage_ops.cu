@@ -107,31 +107,6 @@ __global__ void __launch_bounds__(128) stage_cumsum_kernel(StageParams p) {
   }
 }
 
-// ----------------------------------------------------------------------------- staging helpers
-// 64 rows x 128 bf16 columns of a [.., T, 128] tensor -> two panels (columns 0..63 | 64..127), rows >= `rows` zeroed,
-// each row optionally scaled by rs[row].  `nthr` threads cooperate.  Panel p starts at dst + p * panel_stride.
-// With `rs` the scaled rows are written as bf16 value + bf16 residual (`dst_lo`, same layout).
-__device__ __forceinline__ void stage_rows128(uint8_t* dst, uint32_t panel_stride, const bf16* src, int64_t st, int rows,
-                                              const float* rs, int tid, int nthr, uint8_t* dst_lo = nullptr) {
-  for (int idx = tid; idx < kC * 16; idx += nthr) {
-    const int r = idx >> 4, ch = idx & 15;
-    uint4 val = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
-    if (r < rows) {
-      val = *reinterpret_cast<const uint4*>(src + r * st + ch * 8);
-      if (rs) {
-        float f[8];
-        unpack_bf16x8(val, f);
-        const float s = rs[r];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] *= s;
-        split8(f, val, lo);
-      }
-    }
-    const uint32_t off = (ch >> 3) * panel_stride + panel_chunk_off(r, ch & 7);
-    *reinterpret_cast<uint4*>(dst + off) = val;
-    if (dst_lo) *reinterpret_cast<uint4*>(dst_lo + off) = lo;
-  }
-}
 __device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
 }
@@ -161,11 +136,25 @@ __global__ void __launch_bounds__(128) stage_kkt_kernel(StageParams p) {
     mbar_init(&mma_bar, 1);
     mbar_init_fence();
   }
-  for (int which = 0; which < 2; ++which) {
-    const int c = c0 + which;
-    const int rows = c < sq.nt ? min(kC, sq.len - c * kC) : 0;
-    const bf16* src = static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, tbeg + c * kC);
-    stage_rows128(smem + which * 8192, 16384, src, p.k.st, rows, nullptr, tid, 128);
+  {   // k rows of both chunks: all sixteen 16-byte loads of a thread are issued before the first shared-memory store (a store
+      // through a generic pointer between two loads would keep the compiler from overlapping them)
+    uint4 val[16];
+#pragma unroll
+    for (int it = 0; it < 16; ++it) {
+      const int which = it >> 3, idx = tid + (it & 7) * 128, r = idx >> 4, ch = idx & 15;
+      const int c = c0 + which;
+      const int rows = c < sq.nt ? min(kC, sq.len - c * kC) : 0;
+      val[it] = make_uint4(0, 0, 0, 0);
+      if (r < rows) {
+        const bf16* src = static_cast<const bf16*>(p.k.p) + row_off(p.k, b, hk, tbeg + c * kC);
+        val[it] = *reinterpret_cast<const uint4*>(src + r * p.k.st + ch * 8);
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < 16; ++it) {
+      const int which = it >> 3, idx = tid + (it & 7) * 128, r = idx >> 4, ch = idx & 15;
+      *reinterpret_cast<uint4*>(smem + which * 8192 + (ch >> 3) * 16384 + panel_chunk_off(r, ch & 7)) = val[it];
+    }
   }
   fence_async_smem();
   tc_fence_before();
@@ -185,14 +174,22 @@ __global__ void __launch_bounds__(128) stage_kkt_kernel(StageParams p) {
   const int rows = c < sq.nt ? min(kC, sq.len - c * kC) : 0;
   float s[64];
   tmem_ld_row64(tmem_addr(tbase, warp * 32, which * 64), s);
+  // gate and beta of my row: fetched one value head ahead of their use
+  auto load_gb = [&](int hv, float& gv, float& bv) {
+    gv = i < rows ? ld_any(p.g.p, row_off(p.g, b, hv, tbeg + c * kC + i), p.g.dtype) : 0.f;
+    bv = i < rows ? ld_any(p.beta.p, row_off(p.beta, b, hv, tbeg + c * kC + i), p.beta.dtype) : 0.f;
+  };
+  float g_next, b_next;
+  load_gb(hk * G, g_next, b_next);
   for (int h = 0; h < G; ++h) {
     const int hv = hk * G + h;
+    const float bi = b_next;
     __syncthreads();
-    gam_s[which][i] = i < rows ? ld_any(p.g.p, row_off(p.g, b, hv, tbeg + c * kC + i), p.g.dtype) : 0.f;
+    gam_s[which][i] = g_next;
+    if (h + 1 < G) load_gb(hv + 1, g_next, b_next);
     __syncthreads();
     if (ok && i < rows) {
       const float gi = gam_s[which][i];
-      const float bi = ld_any(p.beta.p, row_off(p.beta, b, hv, tbeg + c * kC + i), p.beta.dtype);
       float* dst = static_cast<float*>(const_cast<void*>(p.o0.p)) + row_off(p.o0, b, hv, tbeg + c * kC + i);
 #pragma unroll
       for (int j4 = 0; j4 < kC; j4 += 4) {
