@@ -75,3 +75,16 @@ extern "C" FLA_API int fla_b200_kernel_timing_read(const char* kernel_name, floa
   }
   return FLA_OK;
 }
+
+// The operators whose kernels wait on barriers keep a status word at the head of their workspace (cleared at launch,
+// set to FLA_ERR_TIMEOUT by a wait that ran out).  This reads it back: it waits for `stream`, so call it only where a
+// synchronisation is acceptable (a debug mode, the end of a step, a failing test).
+extern "C" FLA_API int fla_b200_read_status_word(const void* workspace, void* stream, int32_t* status_out) {
+  if (!workspace || !status_out) return FLA_ERR_NULL;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  int32_t word = 0;
+  if (cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, cs) != cudaSuccess) return FLA_ERR_CUDA;
+  if (cudaStreamSynchronize(cs) != cudaSuccess) return FLA_ERR_CUDA;
+  *status_out = word;
+  return FLA_OK;
+}

@@ -51,13 +51,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and leaves *err_flag = code) when the limit is hit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag, int code) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+// Bounded wait.  Returns false (and leaves *err_flag = code) when `limit` polls have passed without the phase completing.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint32_t limit, int* err_flag, int code) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   if (err_flag) atomicExch(err_flag, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag, int code) {
+  return mbar_wait_limit(bar, parity, kSpinLimit, err_flag, code);
 }
 
 // ----------------------------------------------------------------------------- bulk async copies

@@ -1,5 +1,6 @@
 // Internal helpers shared by the C-ABI translation units (not installed).
 #pragma once
+#include <atomic>
 #include <cstdint>
 #include <cuda_runtime.h>
 #include "../../include/fla_b200.h"

@@ -71,23 +71,10 @@ constexpr int kDhuThreads = 256;
 
 // q, k and X reach their operand panels as TMA tiles (see gdn_fwd_kernel); rows past the end of a sequence are
 // neutralised by zeroing the corresponding rows of dVn.
-#ifdef FLA_STAGE_CLOCKS
-#ifndef FLA_STAGE_THREAD
-#define FLA_STAGE_THREAD 0
-#endif
-__device__ long long g_dhu_clocks[16];
-#define DSTAMP(i) do { long long now_ = clock64(); dclk_[i] += now_ - dlast_; dlast_ = now_; } while (0)
-#else
-#define DSTAMP(i)
-#endif
 
 __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                       const __grid_constant__ CUtensorMap tm_k,
                                                                       const __grid_constant__ CUtensorMap tm_x) {
-#ifdef FLA_STAGE_CLOCKS
-  long long dclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long dlast_ = clock64();
-#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
@@ -194,12 +181,14 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
 
   float srow[32];   // this thread's 32 columns of the fp32 state-gradient row
   const int c_last = sq.nt - 1;
-  prefetch_load(c_last);
-  prefetch_store(c_last);
-  if (tid == 0) {
-    issue_qk_load(c_last);
-    issue_p_load(c_last);
-    issue_x_load(c_last);
+  if (sq.nt > 0) {   // a sequence without tokens requests nothing: dh0 = dht below
+    prefetch_load(c_last);
+    prefetch_store(c_last);
+    if (tid == 0) {
+      issue_qk_load(c_last);
+      issue_p_load(c_last);
+      issue_x_load(c_last);
+    }
   }
   if (p.dht) {
     const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
@@ -223,7 +212,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     const float gam_i = gam_s[cur][tok];
     const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
 
-    DSTAMP(0);
     // ---- stage 0: publish dS' (split copy for the MMAs and for the second kernel), pre-decayed master in TMEM
     row32_to_hilo(smem + hOffDSH, smem + hOffDSL, row, half, srow);
     {
@@ -237,7 +225,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     __syncthreads();
     tc_fence_after();
 
-    DSTAMP(1);
     // ---- stage 1: [Q;K] dS'  and  U1 = P^T dO (valid accumulator rows 64..127)
     if (tid == 0) {
       if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
@@ -261,7 +248,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     wait_or_mark(&bar, phase, dead, p.status);
     tc_fence_after();
 
-    DSTAMP(2);
     // ---- stage 4: k-side rows: dVn = scale U1 + e^{gam_L - gam} (K dS')
     float acc[32];
     if (kside) {
@@ -280,7 +266,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     __syncthreads();
     tc_fence_after();
 
-    DSTAMP(3);
     // ---- stage 5: dZ = X^T dVn  (valid accumulator rows 64..127)
     if (tid == 0) {
       if (!mbar_wait(&x_bar, xphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // the X tile has landed
@@ -294,7 +279,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     tc_fence_after();
     if (tid == 0 && c > 0) issue_x_load(c - 1);
 
-    DSTAMP(4);
     // ---- stage 6: k-side rows: dV, sum_v dZ*V, dZ images, -beta e^gam dZ;  q-side rows: scale e^gam dO
     if (kside) {
       tmem_ld_row32(trow + hColQK, acc);
@@ -350,7 +334,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     __syncthreads();
     tc_fence_after();
 
-    DSTAMP(5);
     // ---- stage 7: dS += [Q^T | K^T] [scale e^gam dO ; -beta e^gam dZ]
     if (tid == 0) {
       mma_tile(tbase + hColDS, opQKT, opDSH, 128, 64, 8, true);
@@ -370,7 +353,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     tc_fence_after();
     if (tid == 0 && c > 0) issue_qk_load(c - 1);   // the last readers of the q / k panels have completed
 
-    DSTAMP(6);
     // ---- stage 8: new dS to registers; next chunk's operands
     tmem_ld_row32(trow + hColDS, srow);
     tc_fence_before();
@@ -382,11 +364,6 @@ __global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParam
     }
   }
 
-#ifdef FLA_STAGE_CLOCKS
-  DSTAMP(7);
-  if (tid == FLA_STAGE_THREAD && blockIdx.x == 1 && blockIdx.y == 9 && blockIdx.z == 3)
-    for (int i = 0; i < 12; ++i) g_dhu_clocks[i] += dclk_[i];
-#endif
   if (!dead && p.dh0) {
     float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
@@ -421,23 +398,10 @@ __device__ __forceinline__ void row_dot64(const uint8_t* pan0, uint32_t panel_st
   }
 }
 
-#ifdef FLA_STAGE_CLOCKS
-__device__ long long g_par_clocks[16];
-#ifndef FLA_STAGE_THREAD
-#define FLA_STAGE_THREAD 0
-#endif
-#define PSTAMP(i) do { long long now_ = clock64(); pclk_[i] += now_ - plast_; plast_ = now_; } while (0)
-#else
-#define PSTAMP(i)
-#endif
 
 template <int NVB>   // 64-column blocks of V per head (2 or 4): a compile-time trip count keeps the block loop unrolled
 __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_k) {
-#ifdef FLA_STAGE_CLOCKS
-  long long pclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long plast_ = clock64();
-#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // per-head row scalars and row reductions, double-buffered by head parity: the dg / dbeta rows of a head are
@@ -573,7 +537,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     return acc;
   };
 
-  PSTAMP(0);
   float bz_prev = 0.f;
   for (int h = 0; h < G && ok; ++h) {
     const int hv = hk * G + h;
@@ -589,12 +552,10 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     const float bz_cur = load_bz(hv);     // lands while the step's operands are awaited
     float sds = 0.f;
     for (int vb = 0; vb < NVB; ++vb) {
-      PSTAMP(1);
       ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT);
       lphase ^= 1;
       if (h == 0 && vb == 0) ok = mbar_wait(&qk_bar, 0, p.status, FLA_ERR_TIMEOUT) && ok;
       if (!__syncthreads_and(ok)) { ok = false; break; }
-      PSTAMP(2);
       if (tid == 0) {
         tc_fence_after();
         if (h == 0 && vb == 0) mma_tile(tbase + rColQK, opQK, opKb, 128, 64, 8, false);
@@ -621,11 +582,9 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
 #pragma unroll
         for (int j = 0; j < 8; ++j) sds += (s1[j] + s2[j]) * (d1[j] + d2[j]);
       }
-      PSTAMP(3);
       ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
       mphase ^= 1;
       if (!__syncthreads_and(ok)) { ok = false; break; }   // also: every thread is done reading the step's buffers
-      PSTAMP(4);
       tc_fence_after();
       if (tid == 0) {
         if (vb + 1 < NVB) issue_loads(hv, vb + 1);
@@ -637,7 +596,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     for (int o = 16; o > 0; o >>= 1) sds += __shfl_xor_sync(0xffffffffu, sds, o);
     if (lane == 0) sds_s2[hb][warp] = sds;
 
-    PSTAMP(5);
     // ---- epilogue 1: score-tile gradients -> [dP; dAt] operand, first parts of this head's dq / dk rows
     const float gam_i = gam_s[tok], beta_i = beta_s[tok], gam_last = gam_s[rows - 1];
     const float eg = __expf(gam_i);
@@ -694,7 +652,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     tc_fence_before();
     __syncthreads();
 
-    PSTAMP(6);
     // ---- [dP; dAt] K  and  [dP^T | dAt^T] [Q; K]
     if (tid == 0) {
       tc_fence_after();
@@ -709,7 +666,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     if (!__syncthreads_and(ok)) { ok = false; break; }
     tc_fence_after();
 
-    PSTAMP(7);
     // ---- epilogue 2: finish the rows, row dots for dg / dbeta
     {
       float t[64];
@@ -734,18 +690,12 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
       red[3][half][tok] = rkB;
       red[4][half][tok] = ma_part;
     }
-    PSTAMP(8);
     tc_fence_before();
     __syncthreads();
     bz_prev = bz_cur;
   }
   if (__syncthreads_and(ok) && tid < kC) finish_head(hk * G + G - 1, (G - 1) & 1, bz_prev);
 
-  PSTAMP(9);
-#ifdef FLA_STAGE_CLOCKS
-  if (tid == FLA_STAGE_THREAD && blockIdx.x == 40 && blockIdx.y == 7 && blockIdx.z == 3)
-    for (int i = 0; i < 12; ++i) g_par_clocks[i] += pclk_[i];
-#endif
   if (ok && tok < rows) {
     void* base = kside ? p.dk : p.dq;
     const int64_t off = kside ? (tok0 + tok) * p.dk_st + hk * p.dk_sh + half * 64 : (tok0 + tok) * p.dq_st + hk * p.dq_sh + half * 64;
@@ -900,7 +850,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
-  static bool attr_done_dev[64] = {};
+  static std::atomic<bool> attr_done_dev[64] = {};   // per device ordinal; setting the attributes twice is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
   if (!attr_done_dev[dev]) {
@@ -976,11 +926,26 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_ar
   return fla_b200_gdn_chunk_bwd(a, scratch, kStaticScratchBytes, stream);
 }
 
-#ifdef FLA_STAGE_CLOCKS
-extern "C" FLA_API int fla_b200_debug_dhu_clocks(long long* out16) {
-  return cudaMemcpyFromSymbol(out16, fla::g_dhu_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
+// The status word of the allocation-free entry lives at the head of the built-in array, which the caller cannot
+// address; this copies it out after waiting for `stream` (the stream of the call being checked).
+extern "C" FLA_API int fla_b200_gdn_chunk_bwd_noalloc_status(void* stream, int32_t* status_out) {
+  if (!status_out) return FLA_ERR_NULL;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    scratch = g_static_ptr[dev];
+  }
+  if (!scratch) {   // no call on this device yet: nothing has run, nothing can have timed out
+    *status_out = FLA_OK;
+    return FLA_OK;
+  }
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  int32_t word = 0;
+  if (cudaMemcpyAsync(&word, scratch, sizeof(word), cudaMemcpyDeviceToHost, cs) != cudaSuccess) return FLA_ERR_CUDA;
+  if (cudaStreamSynchronize(cs) != cudaSuccess) return FLA_ERR_CUDA;
+  *status_out = word;
+  return FLA_OK;
 }
-extern "C" FLA_API int fla_b200_debug_par_clocks(long long* out16) {
-  return cudaMemcpyFromSymbol(out16, fla::g_par_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
-}
-#endif
+

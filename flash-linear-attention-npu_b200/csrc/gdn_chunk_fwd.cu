@@ -185,15 +185,6 @@ struct FwdPrefetch {
   float gb;
 };
 
-#ifdef FLA_STAGE_CLOCKS
-__device__ long long g_stage_clocks[16];
-#ifndef FLA_STAGE_THREAD
-#define FLA_STAGE_THREAD 0
-#endif
-#define STAMP(i) do { long long now_ = clock64(); fclk_[i] += now_ - last_; last_ = now_; } while (0)
-#else
-#define STAMP(i)
-#endif
 
 // q and k rows reach their operand panels as four 64 x 64 TMA tiles per chunk (the 128-byte swizzle of the tensor map
 // is the panel layout); rows past the end of a sequence then hold whatever follows in memory (zero past the end of
@@ -201,10 +192,6 @@ __device__ long long g_stage_clocks[16];
 __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                   const __grid_constant__ CUtensorMap tm_k,
                                                                   const __grid_constant__ CUtensorMap tm_x) {
-#ifdef FLA_STAGE_CLOCKS
-  long long fclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long last_ = clock64();
-#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float gam_s[2][kC], beta_s[2][kC];
@@ -325,15 +312,18 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
 
   float srow[32];   // this thread's 32 columns of the fp32 state row
 
-  // ---- prologue: chunk 0 operands and the initial state
-  if (tid == 0) {
-    issue_qk_load(0);
-    issue_x_load(0);
+  // ---- prologue: chunk 0 operands and the initial state.  A sequence without tokens (packed batches may hold some)
+  // requests nothing: its chunk loop does not run and the final state below is the initial state.
+  if (sq.nt > 0) {
+    if (tid == 0) {
+      issue_qk_load(0);
+      issue_x_load(0);
+    }
+    prefetch_load(0);
+    prefetch_scalars(0);
+    store_scalars(0);
+    store_panels();
   }
-  prefetch_load(0);
-  prefetch_scalars(0);
-  store_scalars(0);
-  store_panels();
   if (p.h0) {
     const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
@@ -355,7 +345,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     const float gam_last = gam_s[cur][rows - 1];
     const float gam_i = gam_s[cur][tok];
 
-    STAMP(9);
     // ---- stage 0: publish the state at chunk start (split copy for the MMAs, pre-decayed master in TMEM)
     row32_to_hilo(smem + kOffSH, smem + kOffSL, row, half, srow);
     {
@@ -369,16 +358,12 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     __syncthreads();
     tc_fence_after();
 
-    STAMP(0);
     // ---- stage 1: [Q;K] S  (split state: two passes)
     if (tid == 0) {
-      STAMP(10);
       if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
-      STAMP(7);
       mma_tile(tbase + kColRQ, opQK, opSH, 128, 64, 8, false);
       mma_tile(tbase + kColRQ, opQK, opSL, 128, 64, 8, true);
       mma_commit(&bar);
-      STAMP(8);
     }
     qkphase ^= 1;
     if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format: plain 16-byte
@@ -401,7 +386,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
       bulk_load(sb + kOffQK, src, 8192, &pbar);
       bulk_load(sb + kOffQK + kQKPanel, src + 4096, 8192, &pbar);
     }
-    STAMP(1);
 
     // ---- stage 2: k-side rows build Z = beta (V - exp(gam) K S)
     float acc[32];
@@ -422,7 +406,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     __syncthreads();
     tc_fence_after();
 
-    STAMP(2);
     // ---- stage 3: v_new = X Z  (rows 64..127 of the accumulator)
     if (tid == 0) {
       if (!mbar_wait(&x_bar, xphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // the X tile has landed
@@ -435,7 +418,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     tc_fence_after();
     if (tid == 0 && c + 1 < sq.nt) issue_x_load(c + 1);
 
-    STAMP(3);
     // ---- stage 4: k-side rows publish v_new and its decayed copy
     if (kside) {
       tmem_ld_row32(trow + kColVN, acc);
@@ -454,7 +436,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     __syncthreads();
     tc_fence_after();
 
-    STAMP(4);
     // ---- stage 5: P v_new (three passes) and the state update S += K^T vhat
     if (tid == 0) {
       mma_tile(tbase + kColS, opKT, opVH, 128, 64, 4, true);
@@ -477,7 +458,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     tc_fence_after();
     if (tid == 0 && c + 1 < sq.nt) issue_qk_load(c + 1);   // every reader of the q / k / P panels has completed
 
-    STAMP(5);
     // ---- stage 6: output rows, next state, next chunk's operand panels
     if (!kside) {
       float qs[32];
@@ -504,13 +484,8 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p,
     // The only readers of the q/k/X panels were this chunk's MMAs, which have completed; no barrier is needed
     // before the next iteration (its first barrier orders everything else).
     if (c + 1 < sq.nt) store_panels();
-    STAMP(6);
   }
 
-#ifdef FLA_STAGE_CLOCKS
-  if (tid == FLA_STAGE_THREAD && blockIdx.x == 1 && blockIdx.y == 9 && blockIdx.z == 3)
-    for (int i = 0; i < 12; ++i) g_stage_clocks[i] += fclk_[i];
-#endif
   if (!dead && p.ht) {
     float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
@@ -641,10 +616,10 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
   const int prep_smem = 32768 + 1024;
-  static bool attr_done_dev[64] = {};
+  static std::atomic<bool> attr_done_dev[64] = {};   // per device ordinal; setting the attributes twice is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
-  bool& attr_done = attr_done_dev[dev];
+  std::atomic<bool>& attr_done = attr_done_dev[dev];
   if (!attr_done) {
     if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prep_smem) != cudaSuccess) return FLA_ERR_CUDA;
     if (cudaFuncSetAttribute(gdn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
@@ -673,8 +648,3 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   return cuda_status(cudaGetLastError());
 }
 
-#ifdef FLA_STAGE_CLOCKS
-extern "C" FLA_API int fla_b200_debug_stage_clocks(long long* out16) {
-  return cudaMemcpyFromSymbol(out16, fla::g_stage_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
-}
-#endif

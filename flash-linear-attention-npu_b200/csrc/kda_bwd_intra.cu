@@ -244,7 +244,7 @@ extern "C" FLA_API int fla_b200_chunk_kda_bwd_intra(const fla_chunk_kda_bwd_intr
     p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
     p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
   }
-  static bool attr_done_dev[64] = {};
+  static std::atomic<bool> attr_done_dev[64] = {};   // per device ordinal; setting the attributes twice is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
   if (!attr_done_dev[dev]) {

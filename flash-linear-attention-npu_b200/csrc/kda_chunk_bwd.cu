@@ -149,14 +149,16 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_dhu_kernel(KdaBwdParams p) {
 
   float srow[32];   // this thread's 32 columns of the fp32 state-gradient row (row = key channel)
   const int c_last = sq.nt - 1;
-  if (tid == 0) {
-    issue_kn_load(c_last);
-    issue_p_load(c_last);
-    issue_x_load(c_last);
-    issue_qk_load(c_last);
+  if (sq.nt > 0) {   // a sequence without tokens requests nothing: dh0 = dht below
+    if (tid == 0) {
+      issue_kn_load(c_last);
+      issue_p_load(c_last);
+      issue_x_load(c_last);
+      issue_qk_load(c_last);
+    }
+    prefetch_load(c_last);
+    prefetch_store(c_last);
   }
-  prefetch_load(c_last);
-  prefetch_store(c_last);
   if (p.dht) {
     const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
@@ -363,12 +365,6 @@ __device__ __forceinline__ void chunk_vals(const uint8_t* pan_hi, const uint8_t*
   for (int j = 0; j < 8; ++j) f[j] += lo[j];
 }
 
-#ifdef FLA_STAGE_CLOCKS
-__device__ long long g_kpar_clocks[16];
-#define KSTAMP(i) do { long long now_ = clock64(); kclk_[i] += now_ - klast_; klast_ = now_; } while (0)
-#else
-#define KSTAMP(i)
-#endif
 
 // Sum over the 32 lanes (rows) of each of 32 per-lane values (columns): lane l ends up with the total of column l.
 // Recursive halving: at every step a lane keeps one half of its values and hands the other half to its partner.
@@ -402,10 +398,6 @@ __device__ __forceinline__ float warp_column_sums32(const float* v, int lane) {
 // shared memory (their global loads used to sit, one round trip each, on the critical path).
 template <int NVB>   // 64-column blocks of V per head (2 or 4): a compile-time trip count keeps the block loop unrolled
 __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, const __grid_constant__ CUtensorMap tm_gk) {
-#ifdef FLA_STAGE_CLOCKS
-  long long kclk_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long klast_ = clock64();
-#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ float beta_s[kC], anchor_s[kK];
@@ -498,7 +490,6 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
       issue_loads(hv, 0);
     }
     float sds = 0.f;   // my key channel (tid & 127), my 32 columns (tid >> 7) of sum_v dS'a * Sa
-    KSTAMP(0);
     for (int vb = 0; vb < NVB; ++vb) {
       if (vb == 0) {
         ok = mbar_wait(&img_bar, iphase, p.status, FLA_ERR_TIMEOUT);
@@ -507,7 +498,6 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
       ok = mbar_wait(&load_bar, lphase, p.status, FLA_ERR_TIMEOUT) && ok;
       lphase ^= 1;
       if (!__syncthreads_and(ok)) { ok = false; break; }
-      KSTAMP(1);
       if (tid == 0) {
         tc_fence_after();
         if (vb == 0) {
@@ -539,11 +529,9 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
           for (int j = 0; j < 8; ++j) sds += s[j] * d[j];
         }
       }
-      KSTAMP(2);
       ok = mbar_wait(&mma_bar, mphase, p.status, FLA_ERR_TIMEOUT);
       mphase ^= 1;
       if (!__syncthreads_and(ok)) { ok = false; break; }   // also: every thread is done reading the step's buffers
-      KSTAMP(3);
       tc_fence_after();
       if (tid == 0) {
         if (vb + 1 < NVB) {
@@ -558,7 +546,6 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
     if (!ok) break;
     sds_s[tid >> 7][tid & 127] = sds;
 
-    KSTAMP(4);
     // ---- epilogue 1: score-tile gradients -> [dP; dM] operand; row scaling of the first TA product in place
     const float beta_i = beta_s[tok];
     float ma_part = 0.f, rkG = 0.f;
@@ -615,7 +602,6 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
     tc_fence_before();
     __syncthreads();
 
-    KSTAMP(5);
     // ---- TA += [dP; dM] Kn   and   TB2 = [dP^T | dM^T] [Qp; Kp]
     if (tid == 0) {
       tc_fence_after();
@@ -643,7 +629,6 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
     if (!__syncthreads_and(ok)) { ok = false; break; }
     tc_fence_after();
 
-    KSTAMP(6);
     // ---- epilogue 2: dq / dk rows of this head and the three dg tiles (the step buffers are free now)
     {
       const int pan = half;   // my 64 key dims are panel `half` of the 128-wide images
@@ -711,7 +696,6 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
         }
       }
     }
-    KSTAMP(7);
     tc_fence_before();
     if (!__syncthreads_and(ok)) { ok = false; break; }
     // dg = reverse chunk-local cumulative sum of dgk; the last row additionally carries
@@ -725,9 +709,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
 #pragma unroll 8
       for (int i = 0; i < 32; ++i) tot += tile_q[(r0 + i) * kTileStride + kc] + tile_k[(r0 + i) * kTileStride + kc];   // rows past the end hold zeros
       colsum_s[part][kc] = tot;
-      KSTAMP(9);
       __syncthreads();
-      KSTAMP(10);
       float run = sds_s[0][kc] + sds_s[1][kc] + t1col_s[0][kc] + t1col_s[1][kc] + (part == 0 ? colsum_s[1][kc] : 0.f);
       const int64_t base = tok0 * p.dg_st + hv * p.dg_sh + kc;
       for (int blk = 3; blk >= 0; --blk) {
@@ -752,15 +734,9 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
         }
       }
     }
-    KSTAMP(11);
     __syncthreads();
   }
 
-  KSTAMP(8);
-#ifdef FLA_STAGE_CLOCKS
-  if (tid == FLA_STAGE_THREAD && blockIdx.x == 100 && blockIdx.y == 7 && blockIdx.z == 2)
-    for (int i = 0; i < 12; ++i) g_kpar_clocks[i] += kclk_[i];
-#endif
   if (ok && tok < rows) {
     void* base = kside ? p.dk : p.dq;
     const int64_t off = kside ? (tok0 + tok) * p.dk_st + hk * p.dk_sh + half * 64 : (tok0 + tok) * p.dq_st + hk * p.dq_sh + half * 64;
@@ -929,7 +905,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   if (cudaMemsetAsync(workspace, 0, 256, cs) != cudaSuccess) return FLA_ERR_CUDA;
   const int nt_max = (max_len + kC - 1) / kC;
   if (!have_saved && (st = kda_launch_forward(f, nt_max, cs))) return st;
-  static bool attr_done_dev[64] = {};
+  static std::atomic<bool> attr_done_dev[64] = {};   // per device ordinal; setting the attributes twice is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
   if (!attr_done_dev[dev]) {
@@ -953,8 +929,3 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
   return cuda_status(cudaGetLastError());
 }
 
-#ifdef FLA_STAGE_CLOCKS
-extern "C" FLA_API int fla_b200_debug_kda_par_clocks(long long* out16) {
-  return cudaMemcpyFromSymbol(out16, fla::g_kpar_clocks, sizeof(long long) * 16) == cudaSuccess ? 0 : 6;
-}
-#endif

@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
     bulk_load(sb + fOffPH, p.p_img + cidx * kKdaPImg, 16384, &load2_bar);
     bulk_load(sb + fOffX, p.x_img + cidx * kKdaXImg, 16384, &load2_bar);
   };
-  if (tid == 0) {
+  if (tid == 0 && sq.nt > 0) {   // a sequence without tokens requests nothing: its final state is its initial state
     issue_load1(0);
     issue_load2(0);
   }
@@ -331,9 +331,11 @@ __global__ void __launch_bounds__(256, 1) kda_fwd_kernel(KdaParams p) {
   };
 
   float srow[32];
-  prefetch_load(0);
-  store_scalars(0);
-  take_values();
+  if (sq.nt > 0) {
+    prefetch_load(0);
+    store_scalars(0);
+    take_values();
+  }
   if (p.h0) {
     const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
 #pragma unroll
@@ -733,7 +735,7 @@ extern "C" FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* a, v
 }
 
 int fla::kda_launch_forward(const KdaParams& p, int nt_max, cudaStream_t cs) {
-  static bool attr_done_dev[64] = {};
+  static std::atomic<bool> attr_done_dev[64] = {};   // per device ordinal; setting the attributes twice is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
   if (!attr_done_dev[dev]) {

@@ -91,7 +91,39 @@ __global__ void __launch_bounds__(128) selftest_mma_kernel(SelftestParams p) {
   if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
+// A CTA that holds TMEM and waits on an mbarrier nobody arrives at: the wait gives up after `spin_limit` polls, records
+// FLA_ERR_TIMEOUT in the status word, releases the TMEM and returns - the way every kernel of the library leaves a wait
+// that runs out.  Nothing traps and nothing spins without a bound.
+__global__ void __launch_bounds__(128) selftest_wait_timeout_kernel(uint32_t spin_limit, int* status) {
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+  const int warp = threadIdx.x / 32;
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 32);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  mbar_wait_limit(&bar, 0, spin_limit, status, FLA_ERR_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 32);
+}
+
 }  // namespace fla
+
+extern "C" FLA_API int fla_b200_selftest_wait_timeout(uint32_t spin_limit, void* status_word, void* stream) {
+  if (!status_word) return FLA_ERR_NULL;
+  if (spin_limit == 0 || spin_limit > (1u << 20)) return FLA_ERR_VALUE;   // a test hook: keep the wait short
+  fla::selftest_wait_timeout_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(spin_limit, static_cast<int*>(status_word));
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
 
 extern "C" FLA_API int fla_b200_selftest_mma(const void* a, const void* b, float* d, int M, int N, int K, int a_mn, int b_mn,
                                      int d_lane_off, int prefill, int* err_flag, void* stream) {

@@ -8,6 +8,7 @@
 // because the entries above a column's diagonal are zero.
 #include "gdn_common.cuh"
 #include "tri_inverse.h"
+#include <atomic>
 
 namespace fla {
 
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(64 * kTriTiles, 5) tri_inverse_kernel(TriInver
 
 int launch_tri_inverse(const TriInverseParams& p, int nt_max, int N, cudaStream_t stream) {
   const int smem = kTriTiles * kC * kTriStride * 4;
-  static bool attr_done_dev[64] = {};
+  static std::atomic<bool> attr_done_dev[64] = {};   // per device ordinal; setting the attributes twice is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 6;
   if (!attr_done_dev[dev]) {

@@ -9,6 +9,7 @@ the workspace allocated as a uint8 torch tensor (:388-429), and non-zero status 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Iterable, Optional, Sequence
 
 import torch
@@ -99,6 +100,44 @@ def _check_arch(dev: torch.device, op: str) -> None:
     _checked_devices.add(dev.index)
 
 
+# Operators whose kernels wait on barriers: byte 0 of their workspace is an int32 status word that a wait which ran
+# out sets to FLA_ERR_TIMEOUT (include/fla_b200.h, "Device-side failure reporting").
+_STATUS_WORD_OPS = frozenset({
+    "gdn_chunk_fwd", "gdn_chunk_bwd", "kda_chunk_fwd", "kda_chunk_bwd", "chunk_local_cumsum", "chunk_scaled_dot_kkt",
+    "solve_tri", "recompute_w_u_fwd", "chunk_gated_delta_rule_fwd_h", "chunk_fwd_o", "chunk_bwd_dv_local",
+    "chunk_gated_delta_rule_bwd_dhu", "chunk_bwd_dqkwg", "prepare_wy_repr_bwd", "prepare_wy_repr_bwd_da",
+    "prepare_wy_repr_bwd_full",
+})
+
+_check_device_status = os.environ.get("FLA_B200_CHECK", "0") not in ("", "0")
+
+
+def set_device_status_check(enabled: bool) -> bool:
+    """Turn the per-call read-back of the device status word on or off (also: ``FLA_B200_CHECK=1`` in the environment);
+    returns the previous setting.  When on, every chunk operator waits for its stream after the launch and raises
+    ``RuntimeError`` if a kernel recorded a failure - the synchronous behaviour of the reference, whose launches return
+    an aclnnStatus (torch_custom/fla_npu/fla_npu/ops/ascendc/_runtime.py:410-411,427-428).  Off by default: launches
+    stay asynchronous and a caller can check a workspace itself with :func:`read_device_status`."""
+    global _check_device_status
+    prev, _check_device_status = _check_device_status, bool(enabled)
+    return prev
+
+
+def read_device_status(workspace: torch.Tensor, op: str = "operator") -> None:
+    """Wait for the current stream of ``workspace``'s device, read the int32 status word at its head and raise
+    ``RuntimeError`` if a kernel left a non-zero status there (FLA_ERR_TIMEOUT: a bounded device-side wait ran out and
+    the outputs of that call are invalid)."""
+    lib = load_library()
+    with torch.cuda.device(workspace.device):
+        word = ctypes.c_int32(0)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(workspace.device).cuda_stream)
+        status = lib.fla_b200_read_status_word(ctypes.c_void_p(workspace.data_ptr()), stream, ctypes.byref(word))
+    if status != 0:
+        raise RuntimeError(f"{op}: reading the device status word failed with status={status}: {_STATUS_NAMES.get(status, '?')}")
+    if word.value != 0:
+        raise RuntimeError(f"{op} failed on the device with status={word.value}: {_STATUS_NAMES.get(word.value, '?')}")
+
+
 def call(op: str, args: ctypes.Structure, tensors: Sequence[Optional[torch.Tensor]]) -> None:
     """Two-phase call: ``fla_b200_<op>_workspace_size`` then ``fla_b200_<op>`` on the current stream."""
     lib = load_library()
@@ -120,6 +159,8 @@ def call(op: str, args: ctypes.Structure, tensors: Sequence[Optional[torch.Tenso
         status = run_fn(ctypes.byref(args), ws_ptr, ctypes.c_uint64(nbytes.value), stream)
         if status != 0:
             raise RuntimeError(f"{op} failed with status={status}: {_STATUS_NAMES.get(status, '?')}")
+        if _check_device_status and ws is not None and op in _STATUS_WORD_OPS:
+            read_device_status(ws, op)
         # `ws` is released to the caching allocator in stream order when it goes out of scope
 
 

@@ -58,6 +58,9 @@ def fused_recurrent_gated_delta_rule(q, k, v, g=None, beta=None, scale=None, ini
     else:
         if tuple(initial_state.shape) != sshape:
             raise RuntimeError(f"{op}: initial_state shape must be {sshape}, got {tuple(initial_state.shape)}")
+        if inplace_final_state and not initial_state.is_contiguous():
+            # a copy would receive the update and leave the caller's state pool as it was
+            raise RuntimeError(f"{op}: inplace_final_state=True needs a contiguous initial_state, got strides {initial_state.stride()}")
         state_in = initial_state if initial_state.is_contiguous() else initial_state.contiguous()
     if inplace_final_state:
         rt.reject_requires_grad(op, initial_state=initial_state)

@@ -1,6 +1,7 @@
 """The names the reference exports from its second operator package (`fla_npu.ops.triton`,
 torch_custom/fla_npu/fla_npu/ops/triton/__init__.py:9-40; name list scripts/check_packaged_wheel_api.py:34-44), served by
-the CUDA kernels of this library with that package's sequence-first layouts (`[B,T,H,...]`) and keyword names, so that
+the CUDA kernels of this library with that package's own layouts (sequence-first `[B,T,H,...]` gates and score blocks,
+head-first `[B,HK,T,K]` keys for `chunk_scaled_dot_kkt_fwd`) and keyword names, so that
 `from fla_npu.ops.triton import chunk_local_cumsum` becomes `from fla_b200.ops.upstream import chunk_local_cumsum`.
 Not served: that package's `causal_conv1d` / `causal_conv1d_triton` (weight `[W,D]`, a head count argument, output re-laid
 as `[B,H,T,D/H]` and a final state of W rather than W-1 inputs: fla/ops/triton/triton_core/causal_conv1d.py:720-880) --
@@ -33,17 +34,23 @@ chunk_local_cumsum_scalar = chunk_local_cumsum
 
 def chunk_scaled_dot_kkt_fwd(k, g=None, gk=None, beta=None, cu_seqlens=None, chunk_indices=None, chunk_size=64,
                              output_dtype=torch.float32):
-    """fla/ops/triton/triton_core/chunk_scaled_dot_kkt.py:325-360: k `[B,T,HK,K]`, g (chunk-local cumulative gate) and beta
-    `[B,T,HV]` -> A `[B,T,HV,chunk_size]`, `beta_i exp(g_i - g_j) k_i.k_j` strictly below the diagonal of every chunk."""
+    """fla/ops/triton/triton_core/chunk_scaled_dot_kkt.py:325-360, with that function's own layouts: k is head-first
+    `[B,HK,T,K]` (it unpacks `B, H_K, T, K = k.shape`, :359), g (chunk-local cumulative gate) and beta are `[B,T,HV]`
+    -> A `[B,T,HV,chunk_size]`, `beta_i exp(clip(g_i - g_j, -50, 50)) k_i.k_j` strictly below the diagonal of every chunk
+    (the reference kernel clamps the exponent the same way)."""
     del chunk_indices
     if gk is not None:
         raise NotImplementedError("chunk_scaled_dot_kkt_fwd: the per-channel gate gk is not supported")
     if beta is None:
         raise NotImplementedError("chunk_scaled_dot_kkt_fwd: beta is required")
+    if k.dim() != 4 or beta.dim() != 3 or k.shape[0] != beta.shape[0] or k.shape[2] != beta.shape[1]:
+        raise ValueError(f"chunk_scaled_dot_kkt_fwd: expected k [B, Hk, T, K] and beta [B, T, Hv], got {tuple(k.shape)} and "
+                         f"{tuple(beta.shape)}")
+    if beta.shape[-1] % k.shape[1] != 0:
+        raise ValueError(f"Expected beta/g head count Hv to be a multiple of Hk, got Hk={k.shape[1]}, Hv={beta.shape[-1]}.")
     if g is None:
         g = torch.zeros(beta.shape, dtype=torch.float32, device=k.device)
-    A = _st.chunk_scaled_dot_kkt(k.transpose(1, 2), g.transpose(1, 2), beta.transpose(1, 2), cu_seqlens=cu_seqlens,
-                                 chunk_size=chunk_size)
+    A = _st.chunk_scaled_dot_kkt(k, g.transpose(1, 2), beta.transpose(1, 2), cu_seqlens=cu_seqlens, chunk_size=chunk_size)
     A = A.transpose(1, 2)
     return A if output_dtype in (None, torch.float32) else A.to(output_dtype)
 

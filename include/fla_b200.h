@@ -73,6 +73,21 @@ FLA_API int fla_b200_kernel_timing_read(const char* kernel_name, float* total_ms
 FLA_API int fla_b200_selftest_mma(const void* a, const void* b, float* d, int M, int N, int K, int a_mn, int b_mn,
                           int d_lane_off, int prefill, int* err_flag, void* stream);
 
+/* Device-side failure reporting (the counterpart of the non-zero aclnnStatus the reference turns into a
+ * RuntimeError, torch_custom/fla_npu/fla_npu/ops/ascendc/_runtime.py:410-411,427-428).  Launches are
+ * asynchronous, so a kernel cannot fail through the return value of its entry point: the chunk operators
+ * (gdn_chunk_fwd / bwd, kda_chunk_fwd / bwd and the stage operators) keep an int32 status word at byte 0
+ * of their workspace, cleared when the call is enqueued; a kernel whose bounded wait on a barrier runs out
+ * writes FLA_ERR_TIMEOUT there, releases what it holds and returns (its outputs are then invalid).
+ *   fla_b200_read_status_word  copies that word to the host after waiting for `stream`.  Call it while the
+ *                              workspace is still alive and where a synchronisation is acceptable.
+ *   fla_b200_selftest_wait_timeout  launches one CTA that allocates TMEM and waits, for at most `spin_limit`
+ *                              polls (1 .. 2^20), on a barrier nobody arrives at, then records FLA_ERR_TIMEOUT in
+ *                              *status_word (device int32), frees its TMEM and returns: the give-up path of
+ *                              every kernel, exercised without hanging or faulting anything. */
+FLA_API int fla_b200_read_status_word(const void* workspace, void* stream, int32_t* status_out);
+FLA_API int fla_b200_selftest_wait_timeout(uint32_t spin_limit, void* status_word, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Fused-recurrent gated delta rule (decode step), in-place over a state pool.
  * Replaces aclnnRecurrentGatedDeltaRule as bound by npu_recurrent_gated_delta_rule
@@ -245,12 +260,18 @@ FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* args, void* wor
  *     fla_b200_gdn_chunk_bwd_static_scratch_bytes (32 MiB, about 290 (chunk, value-head) pairs, e.g. T = 512
  *     with HV = 32 or T = 1024 with HV = 16 for one sequence); larger problems return FLA_ERR_TOO_LARGE.
  *   - Every GPU whose context loads the library holds the 32 MiB until the process exits.
- *   - The first call on a device looks up the array's device address (with that device current); make
- *     that first call before starting any stream capture.
+ *   - The first call on a device looks up the array's device address (with that device current); if the
+ *     library's device code has not been loaded on that device yet, this lookup is also what loads it and
+ *     places the 32 MiB (the CUDA runtime loads modules lazily), so the device's free memory drops once,
+ *     at that call.  Make that first call before starting any stream capture.
  *   - All calls on one device share the array: two calls whose kernels can overlap on the GPU (different
- *     streams, or a second process thread) race on it.  Serialise them, or use the workspace entry point. */
+ *     streams, or a second process thread) race on it.  Serialise them, or use the workspace entry point.
+ *   - The status word of a call (see fla_b200_read_status_word) sits at the head of the built-in array,
+ *     which the caller cannot address: fla_b200_gdn_chunk_bwd_noalloc_status waits for `stream` and returns
+ *     the word left by the last call on the current device (FLA_OK when no call was made yet). */
 FLA_API int fla_b200_gdn_chunk_bwd_static_scratch_bytes(uint64_t* bytes);
 FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_args* args, void* stream);
+FLA_API int fla_b200_gdn_chunk_bwd_noalloc_status(void* stream, int32_t* status_out);
 
 /* ---------------------------------------------------------------------------------------------
  * Chunked Kimi Delta Attention, forward (per-channel log gate, chunk = 64, K = 128, V = 128 or 256).

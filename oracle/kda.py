@@ -58,6 +58,42 @@ def kda_reference_fwd_bwd(q, k, v, g, beta, *, scale=None, initial_state=None, d
     return res
 
 
+def kda_chunk_score_blocks_ref(q, k, g, beta, scale, cu_seqlens=None, chunk_size=64):
+    """Per-chunk score blocks of the chunked KDA forward in fp64, `[B,T,H,.]` inputs (g = log decay per channel):
+        gk  = chunk-local cumsum(g) / ln 2                                  [B,HV,T,K]
+        Aqk = scale * tril(q k^T 2^{gk_i-gk_j})                              [B,HV,T,chunk]
+        Akk = (I + beta_i strict_tril(k k^T 2^{gk_i-gk_j}))^-1               [B,HV,T,chunk]
+    Restates the score / inverse part of the reference's chunked golden
+    (tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:361-399 `_stable_causal_scores`, :455-468) without its 16-row
+    anchoring, which only matters in float32."""
+    import math
+    C = chunk_size
+    B, T, HK, K = q.shape
+    HV = beta.shape[2]
+    G = HV // HK
+    qq = q.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
+    kk = k.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
+    gg = g.double().permute(0, 2, 1, 3)
+    bb = beta.double().permute(0, 2, 1)
+    aqk = torch.zeros(B, HV, T, C, dtype=torch.float64)
+    akk = torch.zeros_like(aqk)
+    gk = torch.zeros_like(gg)
+    bounds = [0, T] if cu_seqlens is None else [int(x) for x in cu_seqlens]
+    for bos, eos in zip(bounds[:-1], bounds[1:]):
+        for s in range(bos, eos, C):
+            e = min(s + C, eos)
+            n = e - s
+            gc = gg[:, :, s:e].cumsum(2) / math.log(2.0)
+            gk[:, :, s:e] = gc
+            D = torch.exp2(gc[:, :, :, None, :] - gc[:, :, None, :, :]) * torch.tril(torch.ones(n, n, dtype=torch.float64))[..., None]
+            qk = torch.einsum("bhik,bhijk,bhjk->bhij", qq[:, :, s:e], D, kk[:, :, s:e]) * scale
+            kkm = torch.einsum("bhik,bhijk,bhjk->bhij", kk[:, :, s:e], D, kk[:, :, s:e])
+            lhs = torch.tril(kkm * bb[:, :, s:e, None], diagonal=-1) + torch.eye(n, dtype=torch.float64)
+            aqk[:, :, s:e, :n] = qk
+            akk[:, :, s:e, :n] = torch.linalg.inv(lhs)
+    return aqk, akk, gk
+
+
 def chunk_kda_bwd_intra_ref(q, k, gk, beta, d_aqk, d_akk, dq, dk, db, dg, chunk_size=64, cu_seqlens=None):
     """Intra-chunk KDA backward accumulated onto dq, dk, db, dg (returns new tensors), fp64, `[B,T,H,.]` layout.
     Restates torch_custom/fla_npu/test/test_npu_chunk_kda_bwd_intra.py:7-91 without its 16-row anchoring (exact in fp64):

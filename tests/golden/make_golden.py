@@ -34,7 +34,7 @@ def extract(path: Path, names, extra=None):
     if extra:
         ns.update(extra)
     for node in tree.body:
-        if isinstance(node, ast.FunctionDef) and node.name in names:
+        if isinstance(node, (ast.FunctionDef, ast.ClassDef)) and node.name in names:
             exec(compile(ast.Module([node], []), str(path), "exec"), ns)
     missing = [n for n in names if n not in ns]
     assert not missing, missing
@@ -269,6 +269,34 @@ def kda_bwd_intra_fixture():
                         db_out=f32(out[2]), dg_out=f32(out[3]))
 
 
+def kda_chunk_fwd_fixture():
+    """The reference's chunked golden of chunk_kda_fwd (tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:361-530,
+    `_reference_impl` with its helpers), run in float64 on bf16-valued inputs with every intermediate exported:
+    one packed variable-length GVA case (HK = 1, HV = 2) with a ragged last chunk and an initial state."""
+    from dataclasses import dataclass
+    ns = extract(REF / "tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py",
+                 ["_PreparedInputs", "_as_bool", "_layout_to_bsnd", "_gate_cumsum", "_spans", "_stable_causal_scores",
+                  "_reference_impl"], extra={"dataclass": dataclass})
+    g_ = torch.Generator().manual_seed(41)
+    T, H, HV, K, V, C = 136, 1, 2, 128, 128, 64
+    cu = [0, 70, 136]
+    rnd = lambda *s: torch.randn(*s, generator=g_)  # noqa: E731
+    bf = lambda t: t.bfloat16().double()  # noqa: E731
+    q, k = bf(F.normalize(rnd(1, T, H, K), dim=-1)), bf(F.normalize(rnd(1, T, H, K), dim=-1))
+    v, g = bf(rnd(1, T, HV, V)), bf(F.logsigmoid(rnd(1, T, HV, K)) / 16)
+    beta = bf(torch.sigmoid(rnd(1, T, HV)))
+    h0 = (0.1 * rnd(len(cu) - 1, HV, K, V)).double()
+    scale = K ** -0.5
+    inputs = ns["_PreparedInputs"](q=q, k=k, v=v, g=g, beta=beta, A_log=None, dt_bias=None, initial_state=h0, cu_seqlens=cu,
+                                   chunk_indices=None, seed=41)
+    spec = dict(layout="BSND", chunk_size=C, T=T, HV=HV, K=K, scale=scale, use_gate_in_kernel=False, safe_gate=False,
+                disable_recompute=True, return_intermediate_states=True, state_v_first=False, output_final_state=True)
+    names = ("o", "final_state", "gk", "aqk", "akk", "w", "u", "qg", "kg", "v_new", "h")
+    out = dict(zip(names, ns["_reference_impl"](inputs, spec)[:11]))
+    np.savez_compressed(HERE / "kda_chunk_fwd_golden.npz", q=f32(q), k=f32(k), v=f32(v), g=f32(g), beta=f32(beta), h0=f32(h0),
+                        cu=np.asarray(cu, dtype=np.int32), scale=np.float32(scale), **{n: f32(t) for n, t in out.items()})
+
+
 def fast_gelu_fixture():
     """Forward golden of the reference's FastGELU test on its own input grid (fp32 and bf16 inputs)."""
     ns = extract(REF / "torch_custom/fla_npu/test/test_npu_fast_gelu_custom.py", ["fast_gelu_ref"])
@@ -287,5 +315,6 @@ if __name__ == "__main__":
     kda_fixture()
     stages_fixture()
     kda_bwd_intra_fixture()
+    kda_chunk_fwd_fixture()
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)

@@ -106,16 +106,27 @@ def test_forward_only_call_saves_nothing_and_matches():
     assert_close("o", o, ref["o"], TOL)
 
 
-def test_empty_sequence_in_a_packed_batch():
-    """A zero-length sequence between two others changes nothing for its neighbours; its final state is its initial state
-    and its dh0 is its dht."""
+# where the zero-length sequence sits in the packed batch: first (its token range starts at row 0 of every buffer), between two
+# others, last (its chunk index is one past the last chunk), and two in a row
+EMPTY_CASES = {
+    "leading": ([0, 70, 71, 200], [0, 0, 70, 71, 200], [1, 2, 3], [0]),
+    "interior": ([0, 70, 71, 200], [0, 70, 70, 71, 200], [0, 2, 3], [1]),
+    "trailing": ([0, 70, 71, 200], [0, 70, 71, 200, 200], [0, 1, 2], [3]),
+    "two_leading_one_trailing": ([0, 128, 200], [0, 0, 0, 128, 200, 200], [2, 3], [0, 1, 4]),
+}
+
+
+@pytest.mark.parametrize("case", list(EMPTY_CASES))
+def test_empty_sequence_in_a_packed_batch(case):
+    """Zero-length sequences change nothing for the others; their final state is their initial state and their dh0 is
+    their dht."""
     from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
-    cu_a, cu_b = [0, 70, 71, 200], [0, 70, 70, 71, 200]
+    cu_a, cu_b, keep, empty = EMPTY_CASES[case]
+    n_b = len(cu_b) - 1
     inp = oracle.make_gdn_inputs(1, 200, 1, 2, seed=123, h0_scale=0.0)
     gen = torch.Generator().manual_seed(124)
-    h0 = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
-    dht = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
-    keep = [0, 2, 3]                                   # sequence 1 of the second batch is the empty one
+    h0 = (0.1 * torch.randn(n_b, 2, 128, 128, generator=gen)).float()
+    dht = (0.1 * torch.randn(n_b, 2, 128, 128, generator=gen)).float()
     d = {n: inp[n].cuda() for n in ("q", "k", "v", "g", "beta", "do")}
 
     def run(cu, h, dh):
@@ -127,4 +138,5 @@ def test_empty_sequence_in_a_packed_batch():
     for x, y in zip(g_a[:5], g_b[:5]):
         assert torch.equal(x, y)
     assert torch.equal(g_a[5], g_b[5][keep])
-    assert torch.equal(ht_b[1].cpu(), h0[1]) and torch.equal(g_b[5][1].cpu(), dht[1])
+    for e in empty:
+        assert torch.equal(ht_b[e].cpu(), h0[e]) and torch.equal(g_b[5][e].cpu(), dht[e])

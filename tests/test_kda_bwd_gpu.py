@@ -158,17 +158,25 @@ def test_kda_backward_through_the_gate_activation():
     assert_close("d_dt_bias", b_d.grad, b64.grad, TOL)
 
 
+KDA_EMPTY_CASES = {
+    "leading": ([0, 70, 71, 200], [0, 0, 70, 71, 200], [1, 2, 3], [0]),
+    "interior": ([0, 70, 71, 200], [0, 70, 70, 71, 200], [0, 2, 3], [1]),
+    "trailing": ([0, 70, 71, 200], [0, 70, 71, 200, 200], [0, 1, 2], [3]),
+}
+
+
+@pytest.mark.parametrize("case", list(KDA_EMPTY_CASES))
 @pytest.mark.parametrize("recompute", [True, False])
-def test_kda_empty_sequence_in_a_packed_batch(recompute):
-    """A zero-length sequence between two others changes nothing for its neighbours; its final state is its initial state
-    and the gradient of its initial state is its dht."""
+def test_kda_empty_sequence_in_a_packed_batch(recompute, case):
+    """A zero-length sequence (first, between two others, or last in the packed batch) changes nothing for the others; its
+    final state is its initial state and the gradient of its initial state is its dht."""
     from fla_b200.ops import chunk_kda
-    cu_a, cu_b = [0, 70, 71, 200], [0, 70, 70, 71, 200]
+    cu_a, cu_b, keep, empty = KDA_EMPTY_CASES[case]
+    n_b = len(cu_b) - 1
     inp = oracle.make_kda_inputs(1, 200, 1, 2, seed=321)
     gen = torch.Generator().manual_seed(322)
-    h0 = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
-    dht = (0.1 * torch.randn(4, 2, 128, 128, generator=gen)).float()
-    keep = [0, 2, 3]                                   # sequence 1 of the second batch is the empty one
+    h0 = (0.1 * torch.randn(n_b, 2, 128, 128, generator=gen)).float()
+    dht = (0.1 * torch.randn(n_b, 2, 128, 128, generator=gen)).float()
 
     def run(cu, h, dh):
         leaves = {n: inp[n].cuda().requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
@@ -183,7 +191,8 @@ def test_kda_empty_sequence_in_a_packed_batch(recompute):
     for x, y in zip(g_a, g_b):
         assert torch.equal(x, y)
     assert torch.equal(dh_a, dh_b[keep])
-    assert torch.equal(ht_b[1].cpu(), h0[1]) and torch.equal(dh_b[1].cpu(), dht[1])
+    for e in empty:
+        assert torch.equal(ht_b[e].cpu(), h0[e]) and torch.equal(dh_b[e].cpu(), dht[e])
 
 
 def test_kda_qk_l2norm_in_kernel():

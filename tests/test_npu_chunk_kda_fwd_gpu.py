@@ -1,8 +1,7 @@
 """The reference's low-level KDA forward surface (npu_chunk_kda_fwd, 12-value return): outputs, score blocks and visibility
-against an fp64 restatement of the reference's chunked golden
-(tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:361-530: Aqk = scale tril(q k^T 2^{gk_i-gk_j}),
-Akk = (I + beta strict(k k^T 2^{gk_i-gk_j}))^-1, gk = chunk cumsum of the gate / ln 2)."""
-import math
+against the reference's chunked golden (tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:361-530: Aqk = scale tril(q k^T
+2^{gk_i-gk_j}), Akk = (I + beta strict(k k^T 2^{gk_i-gk_j}))^-1, gk = chunk cumsum of the gate / ln 2): once replayed from the
+fixture the reference's own function produced, and on further layouts through the oracle restatement pinned to that fixture."""
 
 import pytest
 import torch
@@ -15,31 +14,28 @@ C = 64
 
 
 def _golden_blocks(q, k, g, beta, scale, cu=None):
-    """fp64 Aqk, Akk [B,HV,T,64] and base-2 gk [B,HV,T,K] per chunk."""
-    B, T, HK, K = q.shape
-    HV = beta.shape[2]
-    G = HV // HK
-    qq = q.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
-    kk = k.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
-    gg = g.double().permute(0, 2, 1, 3)
-    bb = beta.double().permute(0, 2, 1)
-    aqk = torch.zeros(B, HV, T, C, dtype=torch.float64)
-    akk = torch.zeros_like(aqk)
-    gk = torch.zeros_like(gg)
-    bounds = [0, T] if cu is None else cu
-    for bos, eos in zip(bounds[:-1], bounds[1:]):
-        for s in range(bos, eos, C):
-            e = min(s + C, eos)
-            n = e - s
-            gc = gg[:, :, s:e].cumsum(2) / math.log(2.0)
-            gk[:, :, s:e] = gc
-            D = torch.exp2(gc[:, :, :, None, :] - gc[:, :, None, :, :]) * torch.tril(torch.ones(n, n, dtype=torch.float64))[..., None]
-            qk = torch.einsum("bhik,bhijk,bhjk->bhij", qq[:, :, s:e], D, kk[:, :, s:e]) * scale
-            kkm = torch.einsum("bhik,bhijk,bhjk->bhij", kk[:, :, s:e], D, kk[:, :, s:e])
-            lhs = torch.tril(kkm * bb[:, :, s:e, None], diagonal=-1) + torch.eye(n, dtype=torch.float64)
-            aqk[:, :, s:e, :n] = qk
-            akk[:, :, s:e, :n] = torch.linalg.inv(lhs)
-    return aqk, akk, gk
+    """fp64 Aqk, Akk [B,HV,T,64] and base-2 gk [B,HV,T,K] per chunk: the oracle's restatement, itself pinned to the
+    reference's chunked golden by tests/test_oracle_golden.py."""
+    return oracle.kda_chunk_score_blocks_ref(q, k, g, beta, scale, cu, C)
+
+
+def test_npu_chunk_kda_fwd_replays_the_reference_golden():
+    """The fixture made by running the reference's own chunked golden (tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:
+    402-530) on a packed GVA case with an initial state: outputs, final state, gk and both score blocks."""
+    import numpy as np
+    from pathlib import Path
+    from fla_b200.ops import npu_chunk_kda_fwd
+    f = {n: torch.from_numpy(np.asarray(a)) for n, a in np.load(Path(__file__).parent / "golden" / "kda_chunk_fwd_golden.npz").items()}
+    cu = [int(x) for x in f["cu"]]
+    bf = lambda n: f[n].squeeze(0).bfloat16().cuda()  # noqa: E731   (the fixture's inputs are bf16-valued)
+    out = npu_chunk_kda_fwd(bf("q"), bf("k"), bf("v"), bf("g"), bf("beta"), float(f["scale"]), 64, layout="TND",
+                            initial_state=f["h0"].cuda(), output_final_state=True, cu_seqlens=cu)
+    o, ht, gk, aqk, akk = out[:5]
+    assert_close("o", o.unsqueeze(0), f["o"], 5e-3, stored_bf16=True)
+    assert_close("final_state", ht, f["final_state"], 5e-3)
+    assert_close("gk", gk.unsqueeze(0), f["gk"], 1e-5)
+    assert_close("Aqk", aqk.unsqueeze(0), f["aqk"], 5e-3, stored_bf16=True)
+    assert_close("Akk", akk.unsqueeze(0), f["akk"], 5e-3, stored_bf16=True)
 
 
 @pytest.mark.parametrize("layout,cu", [("BSND", None), ("BNSD", None), ("TND", [0, 70, 71, 200])])

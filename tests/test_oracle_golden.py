@@ -114,3 +114,24 @@ def test_fast_gelu_matches_reference_golden_and_autograd():
     dy = torch.randn(x.shape, dtype=torch.float64, generator=torch.Generator().manual_seed(3))
     (x / (1 + torch.exp(-1.702 * x)) * dy).sum().backward()
     torch.testing.assert_close(oracle.fast_gelu_bwd_ref(dy, x.detach()), x.grad, rtol=1e-12, atol=1e-12)
+
+
+def test_kda_chunked_forward_golden_pins_the_score_blocks_and_the_recurrence():
+    """The reference's chunked chunk_kda_fwd golden (float64, packed GVA case with an initial state): its Aqk / Akk / gk
+    pin the oracle's score-block restatement, and its output / final state pin the naive recurrence with an initial
+    state on every sequence of the packed batch."""
+    f = _load("kda_chunk_fwd_golden.npz")
+    cu = [int(x) for x in f["cu"]]
+    scale = float(f["scale"])
+    aqk, akk, gk = oracle.kda_chunk_score_blocks_ref(f["q"], f["k"], f["g"], f["beta"], scale, cu)
+    for name, got, ref in (("gk", gk, f["gk"]), ("Aqk", aqk, f["aqk"]), ("Akk", akk, f["akk"])):
+        err = (got - ref.double()).abs().max().item() / ref.double().pow(2).mean().sqrt().item()
+        assert err < 2e-6, (name, err)                       # the fixture is stored in float32
+    for i, (bos, eos) in enumerate(zip(cu[:-1], cu[1:])):
+        q = f["q"][:, bos:eos].double().repeat_interleave(2, dim=2)
+        k = f["k"][:, bos:eos].double().repeat_interleave(2, dim=2)
+        o, ht = oracle.naive_recurrent_kda(q, k, f["v"][:, bos:eos], f["g"][:, bos:eos], f["beta"][:, bos:eos], scale=scale,
+                                           initial_state=f["h0"][i:i + 1].double(), dtype=torch.float64)
+        for name, got, ref in (("o", o, f["o"][:, bos:eos]), ("ht", ht, f["final_state"][i:i + 1])):
+            err = (got - ref.double()).abs().max().item() / ref.double().pow(2).mean().sqrt().item()
+            assert err < 2e-6, (name, i, err)

@@ -32,7 +32,10 @@ def test_cumsum_kkt_solve_chain_sequence_first(cu):
     gr = up.chunk_local_cumsum(g.cuda(), 64, reverse=True, cu_seqlens=cu_t, head_first=False)
     assert_close("reverse cumsum", gr.transpose(1, 2), st.chunk_local_cumsum_ref(g.transpose(1, 2), 64, cu_seqlens=cu, reverse=True), 1e-5)
     A_ref = st.chunk_scaled_dot_kkt_ref(k.transpose(1, 2), g_ref, beta.transpose(1, 2), 64, cu_seqlens=cu)
-    A = up.chunk_scaled_dot_kkt_fwd(k.cuda(), g=gc, beta=beta.cuda(), cu_seqlens=cu_t, chunk_size=64)
+    # the reference function takes k head-first ([B,HK,T,K]) next to sequence-first g / beta
+    A = up.chunk_scaled_dot_kkt_fwd(k.transpose(1, 2).contiguous().cuda(), g=gc, beta=beta.cuda(), cu_seqlens=cu_t, chunk_size=64)
+    with pytest.raises(ValueError, match=r"expected k \[B, Hk, T, K\]"):
+        up.chunk_scaled_dot_kkt_fwd(k.cuda(), g=gc, beta=beta.cuda(), cu_seqlens=cu_t, chunk_size=64)
     assert tuple(A.shape) == (B, T, HV, 64) and A.dtype == torch.float32
     assert_close("A", A.transpose(1, 2), A_ref, 5e-3)
     X_ref = st.solve_tri_ref(A_ref.float(), 64, cu_seqlens=cu)
