@@ -61,5 +61,10 @@ def test_sharded_by_gva_group_equals_single_gpu():
             p.start()
         for p in procs:
             p.join(300)
-            assert p.exitcode == 0
+        hung = [p for p in procs if p.is_alive()]
+        for p in hung:                      # a worker that is still running after the limit is stopped, not left behind
+            p.terminate()
+            p.join(30)
+        assert not hung, f"{len(hung)} worker(s) did not finish"
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
         assert ret.get("ok") is True
