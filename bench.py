@@ -18,7 +18,13 @@ distributions of the benchmark specification.  Workloads (the default is the one
 second step in flight fills the SMs that the tail of a kernel leaves idle.  `single_stream` repeats the K steps on one stream.
 With N > 1 every rank (one process per GPU, launched by torch.distributed.run) processes its own batch of that
 shape (weak scaling; the path has no exchange step, so there is no collective on the data path); NCCL carries only
-the barrier and the max-over-ranks reduction of the measured time.  Rank 0 prints ONE JSON line.
+the barrier and the max-over-ranks reduction of the measured time.  The same line then carries a `strong` block: the
+named shape's ONE global batch partitioned over the ranks (batch rows, then whole GVA groups of heads) through
+fla_b200.sharding, timed the same way, with speed-up and efficiency against this run's own one-GPU time of the whole
+batch, and a `shard_check` (outside any timed region) that gathers a small partitioned result with NCCL and compares
+it bit for bit with rank 0's single-GPU result.  At N = 1 the line also carries `workloads` (the other configurations
+of the specification, each timed like the headline) and `parity` (the CUDA operators against the CPU baseline's oracle
+results on that leg's sample).  Rank 0 prints ONE JSON line.
 
 `--impl reference` times the reference's CPU algorithm (the oracle port of its naive fp32 torch goldens) on the
 host cores for the same metric, each step a bounded sample of the workload.
@@ -354,10 +360,12 @@ class Workload:
 
 def cpu_reference(wl: Workload, threads: int, steps: int = 1, warmup: int = 0):
     """The reference's CPU algorithm for one step on a bounded sample of the workload.
-    Returns (tokens/s, description of the sample)."""
+    Returns (tokens/s, description of the sample, the sample's inputs, the oracle's results on it); the last two are
+    None for workloads whose parity block is not built from this leg."""
     import oracle
     torch.set_num_threads(threads)
     c = wl.cfg
+    inp = None
     if wl.name in ("gdn_fwd_bwd", "gdn_fwd_conv", "gdn_stage_fwd", "gdn_stage_fwd_bwd"):
         Ts = 1024
         inp = oracle.make_gdn_inputs(1, Ts, c["HK"], c["HV"], seed=1001)
@@ -373,7 +381,7 @@ def cpu_reference(wl: Workload, threads: int, steps: int = 1, warmup: int = 0):
         else:
             def fn():
                 oracle.causal_conv1d_ref(xs, w, None, None, False, "silu")
-                oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"])
+                return oracle.gdn_reference_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["h0"])
             desc += " + conv1d"
         tokens = Ts
     elif wl.name in ("kda_fwd", "kda_fwd_bwd"):
@@ -410,17 +418,66 @@ def cpu_reference(wl: Workload, threads: int, steps: int = 1, warmup: int = 0):
     for _ in range(warmup):
         fn()
     t0 = time.perf_counter()
+    ref = None
     for _ in range(steps):
-        fn()
+        ref = fn()
     dt = (time.perf_counter() - t0) / steps
-    return tokens / dt, f"{desc}, {threads} threads"
+    if not isinstance(ref, dict):
+        inp = ref = None
+    return tokens / dt, f"{desc}, {threads} threads", inp, ref
+
+
+def parity_block(wl: Workload, inp, ref, dev):
+    """max-abs-error / RMS(oracle) per tensor of the CUDA operators on the CPU baseline's own sample (the oracle results
+    of that leg are the checker): once with fp32 outputs / gradients, once as stored in bf16 (whose final rounding alone
+    can reach 2^-8 |x|; `excess` is the largest error beyond 5e-3 RMS + 2^-8 |ref|, <= 0 when the bar is met)."""
+    import fla_b200.ops as ops
+    if inp is None or ref is None:
+        return None
+    d = {n: (t.to(dev) if isinstance(t, torch.Tensor) else t) for n, t in inp.items()}
+    bwd = "dq" in ref
+
+    def run(out_dtype, grad_dtype):
+        if wl.name.startswith("gdn"):
+            if bwd:
+                o, ht, gr = ops.chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
+                                                               dht=d["dht"], output_dtype=out_dtype, grad_dtype=grad_dtype)
+                return dict(o=o, ht=ht, dq=gr[0], dk=gr[1], dv=gr[2], dg=gr[3], dbeta=gr[4], dh0=gr[5])
+            with torch.no_grad():
+                o, ht = ops.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
+                                                   output_final_state=True, output_dtype=out_dtype)
+            return dict(o=o, ht=ht)
+        if bwd:
+            o, ht, gr = ops.chunk_kda_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], output_dtype=out_dtype,
+                                              grad_dtype=grad_dtype)
+            return dict(o=o, ht=ht, dq=gr[0], dk=gr[1], dv=gr[2], dg=gr[3], dbeta=gr[4])
+        with torch.no_grad():
+            o, ht = ops.chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True, output_dtype=out_dtype)
+        return dict(o=o, ht=ht)
+
+    out = {"sample": "the cpu_baseline sample", "oracle": "naive fp32 recurrence (+ autograd)", "tolerance": 5e-3, "fp32_out": {},
+           "bf16_out": {}}
+    for tag, res in (("fp32_out", run(torch.float32, torch.float32)), ("bf16_out", run(None, None))):
+        for name, got in res.items():
+            r = ref.get(name)
+            if got is None or r is None:
+                continue
+            got, r = got.detach().double().cpu(), r.detach().double()
+            rms = max(r.pow(2).mean().sqrt().item(), 1e-30)
+            err = (got - r).abs()
+            entry = {"max_abs_over_rms": err.max().item() / rms}
+            if tag == "bf16_out" and res[name].dtype == torch.bfloat16:
+                entry["excess_over_bar_plus_half_ulp"] = (err - (5e-3 * rms + r.abs() * 2.0 ** -8)).max().item() / rms
+            out[tag][name] = entry
+    out["worst_fp32_out"] = max(v["max_abs_over_rms"] for v in out["fp32_out"].values())
+    return out
 
 
 def run_reference(args, wl: Workload):
     if int(os.environ.get("RANK", "0")) != 0:
         return
     threads = os.cpu_count() or 1
-    tps, sample = cpu_reference(wl, threads, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    tps, sample, _, _ = cpu_reference(wl, threads, steps=max(1, args.steps), warmup=min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": f"GDN/KDA tokens/s ({wl.name})", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
@@ -439,6 +496,232 @@ def kernel_time(lib, name):
     return ms.value, n.value
 
 
+class Bench:
+    """Timing helpers shared by the headline workload, the other workloads of the `workloads` block and the
+    strong-scaling partition: barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks."""
+
+    def __init__(self, dev, world, rank, lib):
+        self.dev, self.world, self.rank, self.lib = dev, world, rank, lib
+        self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        t = torch.tensor([x], device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def timed(self, step, K, streams):
+        """K steps; with several streams the (independent) steps are issued round-robin, so the tail of one step's
+        kernels, where SMs run out of CTAs, is filled by the next step's kernels.  Device time between two events on
+        the main stream, max over ranks, per step."""
+        main = torch.cuda.current_stream(self.dev)
+        self.barrier()
+        self.e0.record()
+        for st in streams:
+            st.wait_stream(main)
+        for i in range(K):
+            if streams:
+                with torch.cuda.stream(streams[i % len(streams)]):
+                    step()
+            else:
+                step()
+        for st in streams:
+            main.wait_stream(st)
+        self.e1.record()
+        self.barrier()
+        return self.max_over_ranks(self.e0.elapsed_time(self.e1)) / K
+
+    def device_timing(self, step, K, W, n_streams):
+        """W warm-up steps, then exactly K timed steps on `n_streams` streams and (when n_streams > 1) again on one.
+        Returns (ms per step, single-stream ms per step or None)."""
+        for _ in range(W):
+            step()
+        side = [torch.cuda.Stream(self.dev) for _ in range(n_streams)] if n_streams > 1 else []
+        for i in range(2 * len(side)):      # warm the side streams' allocator pools
+            with torch.cuda.stream(side[i % len(side)]):
+                step()
+        ms = self.timed(step, K, side)
+        ms1 = self.timed(step, K, []) if side else None
+        return ms, ms1
+
+    def kernel_times(self, wl, d, steps):
+        """Per-kernel durations of the same step (CUDA events around each launch, on the launching stream)."""
+        self.lib.fla_b200_kernel_timing_enable(1)
+        for _ in range(steps):
+            wl.step(d)
+        torch.cuda.synchronize()
+        ktimes = {}
+        for nm in wl.kernel_names():
+            ms, n = kernel_time(self.lib, nm)
+            if n:
+                ktimes[nm] = {"ms_per_launch": ms / n, "launches": n}
+        self.lib.fla_b200_kernel_timing_enable(0)
+        return ktimes
+
+
+def roofline_of(wl, ktimes, peaks):
+    """Roofline entry of the kernel with the longest launch, and the per-kernel fractions (filled into `ktimes`)."""
+    if not ktimes:
+        return None
+    dom = max(ktimes, key=lambda k: ktimes[k]["ms_per_launch"])
+    bound, work, unit = wl.kernel_work(dom)
+    sec = ktimes[dom]["ms_per_launch"] * 1e-3
+    achieved = work / sec / (1e12 if bound == "tensor" else 1e9)
+    peak = peaks["bf16_tflops"] if bound == "tensor" else peaks["hbm_gbs"]
+    roofline = {"kernel": KERNEL_SYMBOL[dom], "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                "frac": achieved / peak, "traffic": wl.kernel_traffic(dom),
+                "peak_source": peaks["source"] + (" (burst)" if bound == "tensor" else ""),
+                "ms_per_launch": ktimes[dom]["ms_per_launch"]}
+    for k in ktimes:
+        b, wk, _ = wl.kernel_work(k)
+        sk = ktimes[k]["ms_per_launch"] * 1e-3
+        denom = 1e12 * peaks["bf16_tflops"] if b == "tensor" else 1e9 * peaks["hbm_gbs"]
+        ktimes[k]["frac_of_peak"] = wk / sk / denom
+        ktimes[k]["bound"] = b
+        tr = wl.kernel_traffic(k)
+        if tr is not None:   # DRAM bytes of the ncu capture scaled to this launch, as a share of the copy bandwidth
+            ktimes[k]["dram_gb"] = tr / 1e9
+            ktimes[k]["dram_frac_of_hbm_peak"] = tr / sk / (1e9 * peaks["hbm_gbs"])
+    return roofline
+
+
+def other_workloads(bench, headline, local, peaks, K=10, W=3):
+    """The benchmark specification's other configurations, each timed like the headline (device-resident inputs, CUDA
+    events, W warm-up + K timed steps on two streams and on one, clocks sampled during its own timed region)."""
+    out = {}
+    for name in ("gdn_fwd_conv", "kda_fwd_bwd", "decode", "conv_prefill"):
+        if name == headline:
+            continue
+        wl = Workload(name, None)
+        d = wl.make_inputs(bench.dev, 2001)
+        n_streams = 1 if name == "decode" else 2
+        sampler = ClockSampler(local)
+        sampler.start()
+        ms, ms1 = bench.device_timing(lambda: wl.step_fast(d), K, W, n_streams)
+        clocks = sampler.stop()
+        ktimes = bench.kernel_times(wl, d, min(K, 5))
+        roof = roofline_of(wl, ktimes, peaks)
+        entry = {"config": dict(wl.cfg), "ms_per_step": ms, "value": wl.tokens_per_step / (ms * 1e-3), "unit": "tokens/s",
+                 "steps": K, "warmup": W, "streams": n_streams,
+                 "single_stream": None if ms1 is None else {"ms_per_step": ms1, "value": wl.tokens_per_step / (ms1 * 1e-3)},
+                 "roofline": roof,
+                 "kernels": {k: {"ms_per_launch": round(v["ms_per_launch"], 5), "frac_of_peak": round(v["frac_of_peak"], 4),
+                                 "bound": v["bound"]} for k, v in ktimes.items()},
+                 "clocks": clocks}
+        if wl.step_flops():
+            tf = wl.step_flops() / ((ms1 or ms) * 1e-3) / 1e12
+            entry["step_roofline"] = {"algorithmic_tflops_single_stream": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
+        if name == "decode":   # the whole step (conv update + recurrent kernel) against the measured copy bandwidth
+            by = sum(wl.kernel_work(k)[1] for k in wl.kernel_names())
+            entry["step_hbm_frac"] = by / (ms * 1e-3) / (1e9 * peaks["hbm_gbs"])
+        out[name] = entry
+        del d, wl
+        torch.cuda.empty_cache()
+    return out
+
+
+def strong_partition(wl, world, rank):
+    """How the named shape (global batch B) is partitioned over `world` ranks: batch rows first, then whole GVA groups of
+    heads when ranks outnumber rows.  Returns (row begin, row end, q/k head begin, q/k head end, description)."""
+    from fla_b200 import sharding
+    c = wl.cfg
+    nb = min(world, c["B"])
+    while world % nb:
+        nb -= 1
+    nh = world // nb
+    if c["HK"] % nh:
+        raise SystemExit(f"cannot split {c['HK']} q/k heads over {nh} ranks")
+    rb, rh = rank // nh, rank % nh
+    b0, b1 = sharding.shard_range(c["B"], nb, rb)
+    h0, h1 = sharding.shard_range(c["HK"], nh, rh)
+    return b0, b1, h0, h1, f"{nb} batch shard(s) x {nh} head-group shard(s)"
+
+
+def shard_inputs(wl, d, b0, b1, h0, h1):
+    """The rank's shard of a step's inputs (contiguous copies, made once outside the timed region)."""
+    c = wl.cfg
+    rep = c["HV"] // c["HK"]
+    out = {}
+    for n, t in d.items():
+        if n in ("q", "k"):
+            out[n] = t[b0:b1, :, h0:h1].contiguous()
+        elif n in ("v", "do", "g", "beta"):
+            out[n] = t[b0:b1, :, h0 * rep:h1 * rep].contiguous()
+        elif n in ("h0", "dht"):
+            out[n] = t[b0:b1, h0 * rep:h1 * rep].contiguous()
+        else:
+            out[n] = t
+    return out
+
+
+def strong_scaling(bench, wl, K, W, n_streams, ms_full, ms_full_single):
+    """Strong scaling of the named shape: the SAME global batch partitioned over the ranks with no exchange step.
+    `ms_full` / `ms_full_single` are this run's times for the whole batch on one GPU (what every rank ran for the weak
+    figure), so speed-up and efficiency come from one run on one set of GPUs."""
+    world, rank = bench.world, bench.rank
+    d_full = wl.make_inputs(bench.dev, 1001)           # the same global batch on every rank
+    b0, b1, h0, h1, how = strong_partition(wl, world, rank)
+    d = shard_inputs(wl, d_full, b0, b1, h0, h1)
+    del d_full
+    torch.cuda.empty_cache()
+    ms, ms1 = bench.device_timing(lambda: wl.step(d), K, W, n_streams)
+    tokens = wl.tokens_per_step
+    out = {"scaling": "strong", "global_batch": wl.cfg["B"], "partition": how, "ms_per_step": ms,
+           "value": tokens / (ms * 1e-3), "unit": "tokens/s", "speedup_vs_one_gpu": ms_full / ms,
+           "efficiency": ms_full / ms / world}
+    if ms1 is not None and ms_full_single is not None:
+        out["single_stream"] = {"ms_per_step": ms1, "value": tokens / (ms1 * 1e-3), "speedup_vs_one_gpu": ms_full_single / ms1,
+                                "efficiency": ms_full_single / ms1 / world}
+    ktimes = bench.kernel_times(wl, d, min(K, 5))
+    if ktimes:
+        # the kernel that limits the partitioned step on this rank, and how much slower than linear it runs
+        out["kernels_ms"] = {k: round(v["ms_per_launch"], 5) for k, v in ktimes.items()}
+        out["limiting_kernel"] = KERNEL_SYMBOL[max(ktimes, key=lambda k: ktimes[k]["ms_per_launch"])]
+    return out
+
+
+def shard_check(bench):
+    """Outside any timed region: a small GDN forward + backward partitioned like the strong-scaling run, its o / dq / dg
+    gathered with NCCL, against rank 0's own single-GPU result of the whole problem, bit for bit."""
+    from fla_b200 import sharding
+    import fla_b200.ops as ops
+    world, rank = bench.world, bench.rank
+    wl = Workload("gdn_fwd_bwd", None)
+    wl.cfg.update(B=max(2, min(world, 8)), T=320, HK=4, HV=8)
+    d = wl.make_inputs(bench.dev, 4242)
+    b0, b1, h0, h1, how = strong_partition(wl, world, rank)
+    s = shard_inputs(wl, d, b0, b1, h0, h1)
+    o, ht, gr = ops.chunk_gated_delta_rule_fwd_bwd(s["q"], s["k"], s["v"], s["g"], s["beta"], s["do"], initial_state=s["h0"],
+                                                   dht=s["dht"])
+    nb = min(world, wl.cfg["B"])
+    while world % nb:
+        nb -= 1
+    nh = world // nb
+
+    def gather(t):   # ranks are laid out row-major over (batch shard, head shard): gather heads inside a row shard, then rows
+        parts = [torch.empty_like(t) for _ in range(world)]
+        import torch.distributed as dist
+        dist.all_gather(parts, t.contiguous())
+        rows = [torch.cat(parts[r * nh:(r + 1) * nh], dim=2) for r in range(nb)]
+        return torch.cat(rows, dim=0)
+    o_all, dq_all, dg_all = gather(o), gather(gr[0]), gather(gr[3])
+    ok = None
+    if rank == 0:
+        o1, _, g1 = ops.chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
+                                                       dht=d["dht"])
+        ok = bool(torch.equal(o_all, o1) and torch.equal(dq_all, g1[0]) and torch.equal(dg_all, g1[3]))
+    del sharding
+    return {"ok": ok, "compared": ["o", "dq", "dg"], "how": "NCCL all_gather of the shards vs rank 0's single-GPU run, bit-exact",
+            "shape": {k: wl.cfg[k] for k in ("B", "T", "HK", "HV")}, "partition": how}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -451,6 +734,7 @@ def main():
     ap.add_argument("--streams", type=int, default=2,
                     help="CUDA streams the timed steps are issued on round-robin (1 = every step waits for the one before)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the `workloads` block (the other configurations)")
     args = ap.parse_args()
     wl = Workload(args.workload, args.shape)
 
@@ -473,68 +757,20 @@ def main():
     lib = fla_b200.load_library()
     K, W = args.steps, max(args.warmup, 3)
     d = wl.make_inputs(dev, 1001 + rank)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    bench = Bench(dev, world, rank, lib)
+    barrier = bench.barrier
+    e0, e1 = bench.e0, bench.e1
 
     # ---- device-resident timing: W warm-up steps, then exactly K timed steps
-    for _ in range(W):
-        wl.step_fast(d)
-    barrier()
+    n_streams = 1 if wl.name == "decode" else max(1, args.streams)     # decode steps chain through the state pool
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    main = torch.cuda.current_stream(dev)
-    n_streams = 1 if wl.name == "decode" else max(1, args.streams)     # decode steps chain through the state pool
-    side = [torch.cuda.Stream(dev) for _ in range(n_streams)] if n_streams > 1 else []
-
-    def timed(streams):
-        """K steps; with several streams the (independent) steps are issued round-robin, so the tail of one step's
-        kernels, where SMs run out of CTAs, is filled by the next step's kernels.  Device time between two events on the main stream."""
-        barrier()
-        e0.record()
-        for st in streams:
-            st.wait_stream(main)
-        for i in range(K):
-            if streams:
-                with torch.cuda.stream(streams[i % len(streams)]):
-                    wl.step_fast(d)
-            else:
-                wl.step_fast(d)
-        for st in streams:
-            main.wait_stream(st)
-        e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return t.item() / K
-
-    for i in range(2 * len(side)):      # warm the side streams' allocator pools
-        with torch.cuda.stream(side[i % len(side)]):
-            wl.step_fast(d)
-    ms_per_step = timed(side)
+    ms_per_step, ms1 = bench.device_timing(lambda: wl.step_fast(d), K, W, n_streams)
     clocks = sampler.stop() if rank == 0 else None
     value = world * wl.tokens_per_step / (ms_per_step * 1e-3)
-    single = None
-    if side:
-        ms1 = timed([])
-        single = {"ms_per_step": ms1, "value": world * wl.tokens_per_step / (ms1 * 1e-3)}
-
-    # ---- per-kernel durations of the same step (CUDA events around each launch, on the launching stream)
-    lib.fla_b200_kernel_timing_enable(1)
-    for _ in range(min(K, 10)):
-        wl.step(d)
-    torch.cuda.synchronize()
-    ktimes = {}
-    for nm in wl.kernel_names():
-        ms, n = kernel_time(lib, nm)
-        if n:
-            ktimes[nm] = {"ms_per_launch": ms / n, "launches": n}
-    lib.fla_b200_kernel_timing_enable(0)
+    single = None if ms1 is None else {"ms_per_step": ms1, "value": world * wl.tokens_per_step / (ms1 * 1e-3)}
+    ktimes = bench.kernel_times(wl, d, min(K, 10))
 
     # ---- end to end through the public API with host buffers: pinned H2D of the step's inputs, D2H of its outputs
     e2e = None
@@ -608,46 +844,43 @@ def main():
         s_cmp.wait_event(ev_out[1])
         e1.record()
         barrier()
-        e2e_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-        e2e = {"value": world * wl.tokens_per_step / (e2e_ms.item() / Ke * 1e-3), "unit": "tokens/s",
+        e2e_ms = bench.max_over_ranks(e0.elapsed_time(e1))
+        e2e = {"value": world * wl.tokens_per_step / (e2e_ms / Ke * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               # what each rank's host link sustained in each direction while all ranks copied at once
+               "per_rank_copy_gbs": {"h2d": h2d / (e2e_ms / Ke * 1e-3) / 1e9, "d2h": d2h / (e2e_ms / Ke * 1e-3) / 1e9},
                "pipeline": "3 streams (H2D, kernels, D2H), double-buffered staging" +
                            ("; the step's API calls replayed as one CUDA graph per staging buffer" if graphs is not None else "")}
+        del host, stages, host_outs, graphs
+        torch.cuda.empty_cache()
+
+    # ---- the partition the path is built for: the SAME global batch split over the ranks (strong scaling) + its check
+    strong = check = None
+    if world > 1 and wl.name in ("gdn_fwd_bwd", "kda_fwd_bwd", "kda_fwd"):
+        del d
+        torch.cuda.empty_cache()
+        strong = strong_scaling(bench, wl, K, W, n_streams, ms_per_step, ms1)
+        check = shard_check(bench)
 
     if rank == 0:
         peaks = _peaks()
-        roofline = None
-        if ktimes:
-            dom = max(ktimes, key=lambda k: ktimes[k]["ms_per_launch"])
-            bound, work, unit = wl.kernel_work(dom)
-            sec = ktimes[dom]["ms_per_launch"] * 1e-3
-            achieved = work / sec / (1e12 if bound == "tensor" else 1e9)
-            peak = peaks["bf16_tflops"] if bound == "tensor" else peaks["hbm_gbs"]
-            roofline = {"kernel": KERNEL_SYMBOL[dom], "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                        "frac": achieved / peak, "traffic": wl.kernel_traffic(dom),
-                        "peak_source": peaks["source"] + (" (burst)" if bound == "tensor" else ""),
-                        "ms_per_launch": ktimes[dom]["ms_per_launch"]}
-            for k in ktimes:
-                b, wk, _ = wl.kernel_work(k)
-                s = ktimes[k]["ms_per_launch"] * 1e-3
-                denom = 1e12 * peaks["bf16_tflops"] if b == "tensor" else 1e9 * peaks["hbm_gbs"]
-                ktimes[k]["frac_of_peak"] = wk / s / denom
-                ktimes[k]["bound"] = b
-                tr = wl.kernel_traffic(k)
-                if tr is not None:   # DRAM bytes of the ncu capture scaled to this launch, as a share of the copy bandwidth
-                    ktimes[k]["dram_gb"] = tr / 1e9
-                    ktimes[k]["dram_frac_of_hbm_peak"] = tr / s / (1e9 * peaks["hbm_gbs"])
+        roofline = roofline_of(wl, ktimes, peaks)
         step_roofline = None
         if wl.step_flops():
             tf = wl.step_flops() / (ms_per_step * 1e-3) / 1e12
             step_roofline = {"algorithmic_tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
-        cpu_baseline = None
+            if ms1 is not None:
+                tf1 = wl.step_flops() / (ms1 * 1e-3) / 1e12
+                step_roofline["single_stream"] = {"algorithmic_tflops": tf1, "frac_of_bf16_peak": tf1 / peaks["bf16_tflops"]}
+        cpu_baseline = parity = None
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            tps, sample = cpu_reference(wl, threads)
+            tps, sample, inp, ref = cpu_reference(wl, threads, steps=2, warmup=1)   # warmed, like the --impl reference arm
             cpu_baseline = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+            parity = parity_block(wl, inp, ref, dev)
+        workloads = None
+        if world == 1 and not args.no_workloads and not args.shape:
+            workloads = other_workloads(bench, wl.name, local, peaks)
         line = {
             "metric": f"GDN/KDA tokens/s ({wl.name})", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -661,7 +894,8 @@ def main():
                                   if n_streams > 1 else "1"},
             "single_stream": single,
             "roofline": roofline, "kernels": ktimes, "step_roofline": step_roofline, "cpu_baseline": cpu_baseline,
-            "e2e": e2e, "gpu_launches": wl.launches_per_step() * K, "clocks": clocks,
+            "parity": parity, "e2e": e2e, "strong": strong, "shard_check": check, "workloads": workloads,
+            "gpu_launches": wl.launches_per_step() * K, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
