@@ -197,6 +197,20 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand in tensor memory: row m of A is TMEM lane m (M = 128), its 16-bit elements are packed two
+// per 32-bit column (element 2c in the low half of column c), so one K = 16 step reads 8 columns starting at `a_tmem`.
+// A written with tcgen05.st needs tcgen05.wait::st + tcgen05.fence::before_thread_sync + a barrier before this is issued.
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Make the mbarrier observe completion of every MMA this thread issued so far.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -234,6 +248,20 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, cons
     const uint64_t ad = (uint64_t(kDescHi) << 32) | uint64_t(alo + ao);
     const uint64_t bd = (uint64_t(kDescHi) << 32) | uint64_t(blo + bo);
     mma_ss(d_tmem, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+
+// D (+)= A * B over `ksteps` MMAs of K = 16 with A in tensor memory at columns [a_tmem, a_tmem + 8 * ksteps).
+__device__ __forceinline__ void mma_tile_ts(uint32_t d_tmem, uint32_t a_tmem, const Operand& b, int N, int ksteps,
+                                            bool accumulate) {
+  const uint32_t idesc = make_idesc_bf16(128, N, 0, b.mn_major);
+  const uint32_t blo = operand_desc_lo(b);
+  const uint32_t bps = b.panel_stride >> 4;
+#pragma unroll
+  for (int ks = 0; ks < ksteps; ++ks) {
+    const uint32_t bo = b.mn_major ? uint32_t(ks) * 128u : uint32_t(ks >> 2) * bps + uint32_t(ks & 3) * 2u;
+    const uint64_t bd = (uint64_t(kDescHi) << 32) | uint64_t(blo + bo);
+    mma_ts(d_tmem, a_tmem + uint32_t(ks) * 8u, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 

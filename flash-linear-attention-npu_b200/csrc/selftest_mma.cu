@@ -91,6 +91,68 @@ __global__ void __launch_bounds__(128) selftest_mma_kernel(SelftestParams p) {
   if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
+// The same product with the A operand read from tensor memory: thread r packs row r of A (bf16 pairs, element 2c in the low
+// half of column c) and writes it with tcgen05.st; B is staged in panels as above.  Pins the packing and the column stride
+// of a K = 16 step (8 columns) that the transposed scan kernels rely on.
+__global__ void __launch_bounds__(128) selftest_mma_ts_kernel(SelftestParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int b_rows = p.b_mn ? p.K : p.N, b_cols = p.b_mn ? p.N : p.K;
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  stage_panels(smem, p.b, b_rows, b_cols);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t a_col = 256 + uint32_t(p.d_lane_off);   // d_lane_off doubles as a column offset of the A operand here
+  {
+    const __nv_bfloat16* arow = p.a + size_t(threadIdx.x) * p.K;
+    for (int c0 = 0; c0 < p.K / 2; c0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t lo = __bfloat16_as_ushort(arow[2 * (c0 + i)]), hi = __bfloat16_as_ushort(arow[2 * (c0 + i) + 1]);
+        v[i] = __uint_as_float(lo | (hi << 16));
+      }
+      tmem_st16(tmem_addr(tbase, warp * 32, a_col + c0), v);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x == 0) {
+    Operand B{smem_u32(smem), uint32_t(b_rows) * 128u, p.b_mn};
+    mma_tile_ts(tbase, tbase + a_col, B, p.N, p.K / 16, false);
+    mma_commit(&bar);
+  }
+  const bool ok = mbar_wait(&bar, 0, p.err, 1);
+  tc_fence_after();
+  if (ok) {
+    for (int c0 = 0; c0 < p.N; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem_addr(tbase, warp * 32, c0), v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) p.d[size_t(warp * 32 + lane) * p.N + c0 + i] = v[i];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
 // A CTA that holds TMEM and waits on an mbarrier nobody arrives at: the wait gives up after `spin_limit` polls, records
 // FLA_ERR_TIMEOUT in the status word, releases the TMEM and returns - the way every kernel of the library leaves a wait
 // that runs out.  Nothing traps and nothing spins without a bound.
@@ -122,6 +184,21 @@ extern "C" FLA_API int fla_b200_selftest_wait_timeout(uint32_t spin_limit, void*
   if (!status_word) return FLA_ERR_NULL;
   if (spin_limit == 0 || spin_limit > (1u << 20)) return FLA_ERR_VALUE;   // a test hook: keep the wait short
   fla::selftest_wait_timeout_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(spin_limit, static_cast<int*>(status_word));
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+extern "C" FLA_API int fla_b200_selftest_mma_ts(const void* a, const void* b, float* d, int N, int K, int b_mn, int a_col_off,
+                                                int* err_flag, void* stream) {
+  using namespace fla;
+  if (!a || !b || !d || !err_flag) return FLA_ERR_NULL;
+  if (N % 16 || N < 16 || N > 256 || K % 32 || K < 32 || K > 128) return FLA_ERR_SHAPE;
+  if ((b_mn ? N : K) % 64 || N * K * 2 > 65536) return FLA_ERR_SHAPE;
+  if (a_col_off < 0 || a_col_off % 8 || a_col_off + K / 2 > 256) return FLA_ERR_VALUE;
+  SelftestParams p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, 128, N, K,
+                   0, b_mn, a_col_off, 0, err_flag};
+  const int smem = 65536 + 1024;
+  if (cudaFuncSetAttribute(selftest_mma_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FLA_ERR_CUDA;
+  selftest_mma_ts_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
 

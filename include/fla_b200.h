@@ -72,6 +72,10 @@ FLA_API int fla_b200_kernel_timing_read(const char* kernel_name, float* total_ms
  * dumps the 128-lane TMEM accumulator into d[128][N].  err_flag: device int, set non-zero on timeout. */
 FLA_API int fla_b200_selftest_mma(const void* a, const void* b, float* d, int M, int N, int K, int a_mn, int b_mn,
                           int d_lane_off, int prefill, int* err_flag, void* stream);
+/* The same check for products whose A operand is read from tensor memory (M = 128): A [128][K] row-major bf16 is packed
+ * into TMEM columns 256 + a_col_off .. by the kernel (two elements per 32-bit column), B as above, d[128][N] out. */
+FLA_API int fla_b200_selftest_mma_ts(const void* a, const void* b, float* d, int N, int K, int b_mn, int a_col_off,
+                             int* err_flag, void* stream);
 
 /* Device-side failure reporting (the counterpart of the non-zero aclnnStatus the reference turns into a
  * RuntimeError, torch_custom/fla_npu/fla_npu/ops/ascendc/_runtime.py:410-411,427-428).  Launches are

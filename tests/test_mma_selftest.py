@@ -61,3 +61,24 @@ def test_accumulate_on_tmem_store(lib):
     got, ref = _run(lib, 128, 64, 64, 0, 0, prefill=1)
     assert (got - ref).abs().max().item() < 1e-2
 
+
+
+@pytest.mark.parametrize("N,K,b_mn,a_col", [(128, 128, 0, 0), (64, 64, 0, 64), (128, 64, 1, 8), (64, 64, 1, 0), (256, 64, 1, 128)])
+def test_tile_gemm_with_a_from_tensor_memory(lib, N, K, b_mn, a_col):
+    """A operand packed into TMEM by the kernel (two bf16 per 32-bit column, 8 columns per K = 16 step), B from panels."""
+    g = torch.Generator().manual_seed(100 + N + K + b_mn)
+    A = torch.randn(128, K, generator=g).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    b_dev = (B.t().contiguous() if b_mn else B.contiguous()).cuda()
+    a_dev = A.contiguous().cuda()
+    d = torch.full((128, N), float("nan"), device="cuda", dtype=torch.float32)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = lib.fla_b200_selftest_mma_ts(ctypes.c_void_p(a_dev.data_ptr()), ctypes.c_void_p(b_dev.data_ptr()), ctypes.c_void_p(d.data_ptr()),
+                                      N, K, b_mn, a_col, ctypes.c_void_p(err.data_ptr()),
+                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0, f"status {st}"
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0, "device-side wait timed out"
+    ref = A.double() @ B.double().t()
+    e = (d.cpu().double() - ref).abs().max().item()
+    assert e < 1e-3 * max(1.0, ref.abs().max().item()), f"max err {e}"
