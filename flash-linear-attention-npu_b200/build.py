@@ -24,7 +24,7 @@ FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "--expt-relaxed-constexpr",
     "-I", str(CSRC),
-]
+] + os.environ.get("FLA_B200_NVCC_FLAGS", "").split()
 
 
 def _deps_mtime() -> float:

@@ -50,329 +50,13 @@ struct GdnBwdParams {
   int* status;
 };
 
+}  // namespace fla
+#include "gdn_scan_bwd.cuh"
+namespace fla {
+
 constexpr int64_t kSImg = 16384;   // bf16 elements of the state images per (chunk, head, 64-column block of V): (hi, lo) x 128x64
 constexpr int64_t kVnImg = 8192;   // v_new images per (chunk, head, block): (hi, lo) x 64x64
 constexpr int64_t kDzImg = 8192;   // per (chunk, head, block): 64x64 dO + 64x64 dZ, single bf16
-
-// ============================================================================================= dhu
-constexpr uint32_t hOffQK = 0, hQKPanel = 16384;
-constexpr uint32_t hOffDSH = 32768, hOffDSL = 49152;      // dS' hi / lo, later rows 0-63 scale e^gam dO, rows 64-127 -beta e^gam dZ
-constexpr uint32_t hOffDO = 65536;                         // raw dO rows of this V block
-constexpr uint32_t hOffPH = 73728, hOffPL = 81920;         // P, then dVn, then dZ (hi / lo)
-constexpr uint32_t hOffX = 90112;
-constexpr uint32_t kDhuSmem = 98304;
-constexpr uint32_t hColDS = 0, hColW1 = 64, hColQK = 128, hColU1 = 192;
-
-struct DhuPrefetch {
-  uint4 row[4];   // q-side threads: my 32 columns of the dO row; k-side threads: of the v row
-  float gb;
-};
-constexpr int kDhuThreads = 256;
-
-// q, k and X reach their operand panels as TMA tiles (see gdn_fwd_kernel); rows past the end of a sequence are
-// neutralised by zeroing the corresponding rows of dVn.
-
-__global__ void __launch_bounds__(kDhuThreads, 2) gdn_bwd_dhu_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
-                                                                      const __grid_constant__ CUtensorMap tm_k,
-                                                                      const __grid_constant__ CUtensorMap tm_x) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ float gam_s[2][kC], beta_s[2][kC];
-  __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar, pbar, qk_bar, x_bar;
-
-  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
-  const int hk = hv / (p.HV / p.HK);
-  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
-  const int quad = warp & 3, half = warp >> 2;   // TMEM lane quadrant; which 32 of the tile's 64 columns
-  const bool kside = quad >= 2;
-  const int row = quad * 32 + lane, tok = row & 63, c0 = half * 32;
-
-  if (warp == 0) {
-    tmem_alloc(&tmem_base_s, 256);
-    tmem_relinquish();
-  }
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_init(&pbar, 1);
-    mbar_init(&qk_bar, 1);
-    mbar_init(&x_bar, 1);
-    mbar_init_fence();
-    tma_prefetch_descriptor(&tm_q);
-    tma_prefetch_descriptor(&tm_k);
-    tma_prefetch_descriptor(&tm_x);
-  }
-  __syncthreads();
-  const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
-  uint32_t phase = 0, pphase = 0, qkphase = 0, xphase = 0;
-  bool dead = false;
-  const uint32_t sb = smem_u32(smem);
-  auto issue_qk_load = [&](int c) {  // one thread: the chunk's q rows (panel rows 0-63) and k rows (rows 64-127)
-    const int row0 = sq.bos + c * kC;
-    mbar_arrive_expect_tx(&qk_bar, 4 * 8192);
-    tma_load_tile(sb + hOffQK, &tm_q, 0, hk, row0, &qk_bar);
-    tma_load_tile(sb + hOffQK + hQKPanel, &tm_q, 64, hk, row0, &qk_bar);
-    tma_load_tile(sb + hOffQK + 8192, &tm_k, 0, hk, row0, &qk_bar);
-    tma_load_tile(sb + hOffQK + hQKPanel + 8192, &tm_k, 64, hk, row0, &qk_bar);
-  };
-  auto issue_x_load = [&](int c) {
-    mbar_arrive_expect_tx(&x_bar, 8192);
-    tma_load_tile(sb + hOffX, &tm_x, 0, hv, sq.bos + c * kC, &x_bar);
-  };
-  auto issue_p_load = [&](int c) {   // P = tril(Q K^T * decay) of chunk c, built by the forward's prep kernel
-    const bf16* src = p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192;
-    mbar_arrive_expect_tx(&pbar, 16384);
-    bulk_load(sb + hOffPH, src, 16384, &pbar);
-  };
-
-  DhuPrefetch pf;
-  auto prefetch_load = [&](int c) {
-    const int t0 = c * kC;
-    const int rows = min(kC, sq.len - t0);
-    const int64_t tok0 = int64_t(sq.bos) + t0;
-    const bf16* rsrc = kside ? p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + c0
-                             : p.dO + (tok0 + tok) * p.do_st + hv * p.do_sh + vb * kBV + c0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      pf.row[i] = make_uint4(0, 0, 0, 0);
-      if (tok < rows) pf.row[i] = *reinterpret_cast<const uint4*>(rsrc + i * 8);
-    }
-    if (kside) pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
-    else pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
-  };
-  // Touch the next chunk's rows early so that the register loads issued late in the iteration hit L2.
-  auto prefetch_l2 = [&](int c) {
-    const int t0 = c * kC;
-    const int rows = min(kC, sq.len - t0);
-    const int64_t tok0 = int64_t(sq.bos) + t0;
-    const int r = tid & 63;
-    if (tid < 128 && r < rows) {
-      const bf16* src = tid >= 64 ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 64));
-    } else if (tid >= 128 && r < rows) {
-      const bf16* s2 = tid >= 192 ? p.v + (tok0 + r) * p.v_st + hv * p.v_sh + vb * kBV : p.dO + (tok0 + r) * p.do_st + hv * p.do_sh + vb * kBV;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(s2));
-      if (tid < 192) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.X + ((tok0 + r) * p.HV + hv) * kC));
-    }
-  };
-  uint4 rcur[4];
-  auto prefetch_store = [&](int c) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) rcur[i] = pf.row[i];
-    if (kside) {
-      if (half == 0) beta_s[c & 1][tok] = pf.gb;
-    } else {
-      if (half == 0) gam_s[c & 1][tok] = pf.gb;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(smem + hOffDO + panel_chunk_off(tok, half * 4 + i)) = pf.row[i];
-    }
-  };
-
-  const Operand opQK{sb + hOffQK, hQKPanel, 0};
-  const Operand opQKT{sb + hOffQK, hQKPanel, 1};               // [q^T | k^T]: M = 128 key dims, reduction over 128 rows
-  const Operand opDSH{sb + hOffDSH, 16384, 1}, opDSL{sb + hOffDSL, 16384, 1};
-  const Operand opPTh{sb + hOffPH - 8192, 8192, 1}, opPTl{sb + hOffPL - 8192, 8192, 1};  // P^T, valid rows 64..127
-  const Operand opDO{sb + hOffDO, 8192, 1};
-  const Operand opXT{sb + hOffX - 8192, 8192, 1};              // X^T, valid rows 64..127
-  const Operand opDVh{sb + hOffPH, 8192, 1}, opDVl{sb + hOffPL, 8192, 1};
-
-  float srow[32];   // this thread's 32 columns of the fp32 state-gradient row
-  const int c_last = sq.nt - 1;
-  if (sq.nt > 0) {   // a sequence without tokens requests nothing: dh0 = dht below
-    prefetch_load(c_last);
-    prefetch_store(c_last);
-    if (tid == 0) {
-      issue_qk_load(c_last);
-      issue_p_load(c_last);
-      issue_x_load(c_last);
-    }
-  }
-  if (p.dht) {
-    const float* src = p.dht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      const float4 t = *reinterpret_cast<const float4*>(src + i);
-      srow[i] = t.x; srow[i + 1] = t.y; srow[i + 2] = t.z; srow[i + 3] = t.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) srow[i] = 0.f;
-  }
-  __syncthreads();
-
-  for (int c = c_last; c >= 0; --c) {
-    const int cur = c & 1;
-    const int t0 = c * kC;
-    const int rows = min(kC, sq.len - t0);
-    const int64_t tok0 = int64_t(sq.bos) + t0;
-    const float gam_last = gam_s[cur][rows - 1];
-    const float gam_i = gam_s[cur][tok];
-    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
-
-    // ---- stage 0: publish dS' (split copy for the MMAs and for the second kernel), pre-decayed master in TMEM
-    row32_to_hilo(smem + hOffDSH, smem + hOffDSL, row, half, srow);
-    {
-      const float dl = __expf(gam_last);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) srow[i] *= dl;
-      tmem_st_row32(trow + hColDS, srow);
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- stage 1: [Q;K] dS'  and  U1 = P^T dO (valid accumulator rows 64..127)
-    if (tid == 0) {
-      if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
-      mma_tile(tbase + hColW1, opQK, opDSH, 128, 64, 8, false);
-      mma_tile(tbase + hColW1, opQK, opDSL, 128, 64, 8, true);
-      if (!mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // P panels have landed
-      mma_tile(tbase + hColU1, opPTh, opDO, 128, 64, 4, false);
-      mma_tile(tbase + hColU1, opPTl, opDO, 128, 64, 4, true);
-      mma_commit(&bar);
-    }
-    pphase ^= 1;
-    qkphase ^= 1;
-    {   // the split dS' copy is already in the panel-image format the chunk-parallel kernel loads: plain 16-byte copies by
-        // all threads while the MMAs run (bulk stores would queue ahead of the next chunk's TMA loads)
-      uint4* dst = reinterpret_cast<uint4*>(p.ds_img + (cidx * p.nvb + vb) * (2 * 8192));
-      const uint4* src = reinterpret_cast<const uint4*>(smem + hOffDSH);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) dst[tid + i * kDhuThreads] = src[tid + i * kDhuThreads];
-    }
-    if (c > 0) prefetch_l2(c - 1);
-    wait_or_mark(&bar, phase, dead, p.status);
-    tc_fence_after();
-
-    // ---- stage 4: k-side rows: dVn = scale U1 + e^{gam_L - gam} (K dS')
-    float acc[32];
-    if (kside) {
-      float w1[32];
-      tmem_ld32(trow + hColW1, w1);
-      tmem_ld32(trow + hColU1, acc);
-      tmem_ld_wait();
-      const float dk = __expf(gam_last - gam_i);
-      const bool live = tok < rows;   // rows past the end of the sequence hold foreign k rows: dVn = 0 there
-#pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] = live ? p.scale * acc[i] + dk * w1[i] : 0.f;
-      row32_to_hilo(smem + hOffPH, smem + hOffPL, tok, half, acc);
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- stage 5: dZ = X^T dVn  (valid accumulator rows 64..127)
-    if (tid == 0) {
-      if (!mbar_wait(&x_bar, xphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // the X tile has landed
-      mma_tile(tbase + hColQK, opXT, opDVh, 128, 64, 4, false);
-      mma_tile(tbase + hColQK, opXT, opDVl, 128, 64, 4, true);
-      mma_commit(&bar);
-    }
-    xphase ^= 1;
-    if (c > 0) prefetch_load(c - 1);   // the next chunk's rows: requested two stages before they are stored
-    wait_or_mark(&bar, phase, dead, p.status);
-    tc_fence_after();
-    if (tid == 0 && c > 0) issue_x_load(c - 1);
-
-    // ---- stage 6: k-side rows: dV, sum_v dZ*V, dZ images, -beta e^gam dZ;  q-side rows: scale e^gam dO
-    if (kside) {
-      tmem_ld_row32(trow + hColQK, acc);
-      const float bi = beta_s[cur][tok];
-      float bzsum = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float vv[8];
-        unpack_bf16x8(rcur[i], vv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) bzsum += acc[i * 8 + j] * vv[j];
-      }
-      // dZ for the second kernel as one bf16: its residual only enters products whose other factor is itself split,
-      // where dropping it costs a few 1e-4 (dk 1.3e-3 -> 1.6e-3 in emulation) and saves a pass and 8 KB per block
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(smem + hOffPH + panel_chunk_off(tok, half * 4 + ch)) = pack8(acc + ch * 8);
-      if (tok < rows) {
-        p.bz[(int64_t(vb * 2 + half) * p.total_tokens + tok0 + tok) * p.HV + hv] = bzsum;
-        const int64_t off = (tok0 + tok) * p.dv_st + hv * p.dv_sh + vb * kBV + c0;
-        if (p.grads_f32) {
-          float* dst = static_cast<float*>(p.dv) + off;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4*>(dst + i) = make_float4(bi * acc[i], bi * acc[i + 1], bi * acc[i + 2], bi * acc[i + 3]);
-        } else {
-          bf16* dst = static_cast<bf16*>(p.dv) + off;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            float t[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) t[j] = bi * acc[ch * 8 + j];
-            *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(t);
-          }
-        }
-      }
-      const float f = -bi * __expf(gam_i);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] *= f;
-      row32_to_hilo(smem + hOffDSH, smem + hOffDSL, 64 + tok, half, acc);
-    } else {
-      const float f = p.scale * __expf(gam_i);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float vv[8];
-        unpack_bf16x8(rcur[i], vv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i * 8 + j] = f * vv[j];
-      }
-      row32_to_hilo(smem + hOffDSH, smem + hOffDSL, tok, half, acc);
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- stage 7: dS += [Q^T | K^T] [scale e^gam dO ; -beta e^gam dZ]
-    if (tid == 0) {
-      mma_tile(tbase + hColDS, opQKT, opDSH, 128, 64, 8, true);
-      mma_tile(tbase + hColDS, opQKT, opDSL, 128, 64, 8, true);
-      mma_commit(&bar);
-    }
-    {   // the [dO ; dZ] image of this V block: rows 0..63 from the dO panel, rows 64..127 from the dZ panel
-      uint4* dst = reinterpret_cast<uint4*>(p.dz_img + (cidx * p.nvb + vb) * 8192);
-      const uint4* s0 = reinterpret_cast<const uint4*>(smem + hOffDO);
-      const uint4* s1 = reinterpret_cast<const uint4*>(smem + hOffPH);
-      dst[tid] = s0[tid];
-      dst[tid + 256] = s0[tid + 256];
-      dst[tid + 512] = s1[tid];
-      dst[tid + 768] = s1[tid + 256];
-    }
-    wait_or_mark(&bar, phase, dead, p.status);
-    tc_fence_after();
-    if (tid == 0 && c > 0) issue_qk_load(c - 1);   // the last readers of the q / k panels have completed
-
-    // ---- stage 8: new dS to registers; next chunk's operands
-    tmem_ld_row32(trow + hColDS, srow);
-    tc_fence_before();
-    __syncthreads();                     // every thread has copied its part of the dO / dZ image
-    if (tid == 0 && c > 0) issue_p_load(c - 1);    // the P / dVn / dZ panels now receive the next chunk's P
-    if (c > 0) {
-      prefetch_store(c - 1);
-      __syncthreads();
-    }
-  }
-
-  if (!dead && p.dh0) {
-    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tbase, 256);
-}
 
 // ============================================================================================= par
 constexpr uint32_t rOffQK = 0, rQKPanel = 16384;
@@ -432,13 +116,25 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     tmem_relinquish();
   }
   const uint32_t sb = smem_u32(smem);
-  auto issue_loads = [&](int hv, int vb) {  // one thread: operands of one (value head, V block) step
-    const int64_t cidx = (int64_t(sq.cbase) + c) * p.HV + hv;
+  // One thread: operands of one (value head, 64-channel slice of V) step.  The scans store their panels with value
+  // channels as rows (128 per block of V); a step takes the 64 rows of one half of every panel, which are contiguous.
+  auto issue_loads = [&](int hv, int vb) {
+    const int64_t blk = ((int64_t(sq.cbase) + c) * p.HV + hv) * (NVB / 2) + (vb >> 1);
+    const int64_t half = int64_t(vb & 1) * 4096;                         // elements: 64 rows x 64 columns
+    const bf16* dz = p.dz_img + blk * 16384 + half;                      // [dO^T | dZ^T] panels
+    const bf16* vn = p.vn_img + blk * 16384 + half;                      // [value | residual] panels
+    const bf16* sp = p.s_img + blk * 32768 + half;                       // [value | residual] x [key dims 0-63 | 64-127]
+    const bf16* dp = p.ds_img + blk * 32768 + half;
     mbar_arrive_expect_tx(&load_bar, kStepBytes);
-    bulk_load(sb + rOffAH, p.dz_img + (cidx * NVB + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + rOffVNH, p.vn_img + (cidx * NVB + vb) * 8192, 16384, &load_bar);
-    bulk_load(sb + rOffSH, p.s_img + (cidx * NVB + vb) * 16384, 32768, &load_bar);
-    bulk_load(sb + rOffDSH, p.ds_img + (cidx * NVB + vb) * 16384, 32768, &load_bar);
+    bulk_load(sb + rOffAH, dz, 8192, &load_bar);
+    bulk_load(sb + rOffAH + 8192, dz + 8192, 8192, &load_bar);
+    bulk_load(sb + rOffVNH, vn, 8192, &load_bar);
+    bulk_load(sb + rOffVNL, vn + 8192, 8192, &load_bar);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {                                         // panels in stored order: value kd 0-63, 64-127, residual ...
+      bulk_load(sb + rOffSH + i * 8192, sp + i * 8192, 8192, &load_bar);
+      bulk_load(sb + rOffDSH + i * 8192, dp + i * 8192, 8192, &load_bar);
+    }
   };
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
@@ -475,11 +171,12 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   const Operand opKb{sb + rOffQK + 8192, rQKPanel, 0};               // k as B, N = 64 tokens
   const Operand opKn{sb + rOffQK + 8192, rQKPanel, 1};               // k as B, N = 128 key dims, reduction over tokens
   const Operand opQKn{sb + rOffQK, rQKPanel, 1};                     // [q; k] as B, N = 128 key dims, reduction over 128 rows
-  const Operand opAH{sb + rOffAH, 16384, 0};
-  const Operand opVNbH{sb + rOffVNH, 8192, 0}, opVNbL{sb + rOffVNL, 8192, 0};            // Vn as B (N = 64 tokens)
-  const Operand opVNaH{sb + rOffVNH - 8192, 8192, 0}, opVNaL{sb + rOffVNL - 8192, 8192, 0};  // Vn as A, valid rows 64..127
-  const Operand opSH{sb + rOffSH, 16384, 0}, opSL{sb + rOffSL, 16384, 0};                // S block as B (N = 128 key dims)
-  const Operand opDSH{sb + rOffDSH, 16384, 0}, opDSL{sb + rOffDSL, 16384, 0};
+  // operands of a step: every saved panel has value channels as rows, i.e. the reduction dim of these products runs over rows
+  const Operand opAH{sb + rOffAH, 8192, 1};                                               // [dO; dZ]: M = 128 tokens over two panels
+  const Operand opVNbH{sb + rOffVNH, 8192, 1}, opVNbL{sb + rOffVNL, 8192, 1};            // Vn as B (N = 64 tokens)
+  const Operand opVNaH{sb + rOffVNH - 8192, 8192, 1}, opVNaL{sb + rOffVNL - 8192, 8192, 1};  // Vn as A: accumulator rows 64..127 are valid
+  const Operand opSH{sb + rOffSH, 8192, 1}, opSL{sb + rOffSL, 8192, 1};                  // S block as B (N = 128 key dims over two panels)
+  const Operand opDSH{sb + rOffDSH, 8192, 1}, opDSL{sb + rOffDSL, 8192, 1};
   const Operand opPAH{sb + rOffPAH, 16384, 0}, opPAL{sb + rOffPAL, 16384, 0};            // [dP; dAt], reduction over j
   const Operand opPATh{sb + rOffPAH - 8192, 8192, 1}, opPATl{sb + rOffPAL - 8192, 8192, 1};  // its transpose, valid rows 64..127
 
@@ -854,19 +551,21 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
   if (!attr_done_dev[dev]) {
-    if (cudaFuncSetAttribute(gdn_bwd_dhu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDhuSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kScanBwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     if (cudaFuncSetAttribute(gdn_bwd_par_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     if (cudaFuncSetAttribute(gdn_bwd_par_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
-  CUtensorMap tm_q, tm_k, tm_x;
+  CUtensorMap tm_q, tm_k, tm_x, tm_v, tm_d;
   if (make_row_tile_map(&tm_q, p.q, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.q_sh), uint64_t(p.q_st)) ||
       make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)) ||
-      make_row_tile_map(&tm_x, p.X, kC, uint64_t(HV), uint64_t(B * T), uint64_t(kC), uint64_t(HV) * kC))
+      make_row_tile_map(&tm_x, p.X, kC, uint64_t(HV), uint64_t(B * T), uint64_t(kC), uint64_t(HV) * kC) ||
+      make_row_tile_map(&tm_v, p.v, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.v_sh), uint64_t(p.v_st)) ||
+      make_row_tile_map(&tm_d, p.dO, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.do_sh), uint64_t(p.do_st)))
     return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_bwd_dhu", cs);
-    gdn_bwd_dhu_kernel<<<dim3(unsigned(nvb), unsigned(HV), N), kDhuThreads, kDhuSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
+    gdn_scan_bwd_kernel<<<dim3(unsigned(V / 128), unsigned(HV), N), kScanThreads, kScanBwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x, tm_v, tm_d);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   const int nt_max = (max_len + kC - 1) / kC;

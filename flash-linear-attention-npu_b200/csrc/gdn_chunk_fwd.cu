@@ -6,7 +6,7 @@
 //                    triangular inverse runs in tri_inverse_kernel (fp32 forward substitution on CUDA cores).
 //                    Replaces chunk_local_cumsum + chunk_scaled_dot_kkt + solve_tri of the reference
 //                    (examples/flash_gated_delta_rule.py:811-838).
-//  gdn_fwd_kernel    (sequential over chunks, one CTA per (sequence, value head, 64-column block of V)):
+//  gdn_scan_fwd_kernel (gdn_scan_fwd.cuh; sequential over chunks, one CTA per (sequence, value head, 128-column block of V)):
 //                    v_new = X (beta * (V - exp(gam) * (K S)))
 //                    o     = scale (exp(gam) * (Q S) + tril(Q K^T * exp(gam_i - gam_j)) v_new)
 //                    S    <- exp(gam_L) S + K^T (exp(gam_L - gam) * v_new)
@@ -46,6 +46,10 @@ struct GdnFwdParams {
   float scale;
   int* status;
 };
+
+}  // namespace fla
+#include "gdn_scan_fwd.cuh"
+namespace fla {
 
 // --------------------------------------------------------------------------------------------- prep
 // One CTA per (chunk, q/k head).  One M = 128 product [q; k] k^T leaves Q K^T in TMEM lanes 0..63 and K K^T in
@@ -166,334 +170,6 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
     }
     __syncthreads();
   }
-}
-
-// --------------------------------------------------------------------------------------------- forward
-// Shared-memory map of gdn_fwd_kernel (offsets from a 1024-byte aligned base).
-constexpr uint32_t kOffQK = 0;                    // 2 panels x 128 rows: rows 0-63 q, rows 64-127 k
-constexpr uint32_t kQKPanel = 16384;
-constexpr uint32_t kOffSH = 32768, kOffSL = 49152;            // state copy hi / lo: 128 rows x 64 cols
-constexpr uint32_t kOffZH = 65536, kOffZL = 73728;            // beta*(V - ..) hi / lo, then v_new hi / lo
-constexpr uint32_t kOffVH = 81920, kOffVL = 90112;            // decayed v_new hi / lo
-constexpr uint32_t kOffX = 98304;                             // X panel (64 rows); the 64 rows before it are VL
-constexpr uint32_t kFwdSmem = 106496;
-constexpr uint32_t kColS = 0, kColRQ = 64, kColQK = 128, kColVN = 192;  // TMEM column map (256 columns)
-constexpr int kFwdThreads = 256;
-
-struct FwdPrefetch {
-  uint4 v[4];
-  float gb;
-};
-
-
-// q and k rows reach their operand panels as four 64 x 64 TMA tiles per chunk (the 128-byte swizzle of the tensor map
-// is the panel layout); rows past the end of a sequence then hold whatever follows in memory (zero past the end of
-// the tensor): harmless, because every product with them is multiplied by a zero row of X, P or beta.
-__global__ void __launch_bounds__(kFwdThreads, 2) gdn_fwd_kernel(GdnFwdParams p, const __grid_constant__ CUtensorMap tm_q,
-                                                                  const __grid_constant__ CUtensorMap tm_k,
-                                                                  const __grid_constant__ CUtensorMap tm_x) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ float gam_s[2][kC], beta_s[2][kC];
-  __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t bar, pbar, qk_bar, x_bar;
-
-  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
-  const int hk = hv / (p.HV / p.HK);
-  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
-  const int quad = warp & 3, half = warp >> 2;   // TMEM lane quadrant; which 32 of the tile's 64 columns
-  const bool kside = quad >= 2;                  // rows 64..127 hold the k-side results
-  const int row = quad * 32 + lane;              // TMEM lane == accumulator row
-  const int tok = row & 63;                      // token row inside the chunk
-  const int c0 = half * 32;
-
-  if (warp == 0) {
-    tmem_alloc(&tmem_base_s, 256);
-    tmem_relinquish();
-  }
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_init(&pbar, 1);
-    mbar_init(&qk_bar, 1);
-    mbar_init(&x_bar, 1);
-    mbar_init_fence();
-    tma_prefetch_descriptor(&tm_q);
-    tma_prefetch_descriptor(&tm_k);
-    tma_prefetch_descriptor(&tm_x);
-  }
-  __syncthreads();
-  const uint32_t tbase = tmem_base_s;
-  const uint32_t trow = tmem_addr(tbase, quad * 32, c0);
-  uint32_t phase = 0, pphase = 0, qkphase = 0, xphase = 0;
-  bool dead = false;
-  const uint32_t sb = smem_u32(smem);
-
-  FwdPrefetch pf;
-  auto prefetch_load = [&](int c) {
-    const int t0 = c * kC;
-    const int rows = min(kC, sq.len - t0);
-    const int64_t tok0 = int64_t(sq.bos) + t0;
-    if (kside) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        pf.v[i] = make_uint4(0, 0, 0, 0);
-        if (tok < rows) pf.v[i] = *reinterpret_cast<const uint4*>(p.v + (tok0 + tok) * p.v_st + hv * p.v_sh + vb * kBV + c0 + i * 8);
-      }
-    }
-  };
-  // The per-token scalars travel separately and early: they are published to shared memory well before the
-  // barriers that precede their first use in the next iteration.
-  auto prefetch_scalars = [&](int c) {
-    const int t0 = c * kC;
-    const int rows = min(kC, sq.len - t0);
-    const int64_t tok0 = int64_t(sq.bos) + t0;
-    if (kside) {
-      pf.gb = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
-    } else {
-      // rows past the end of the sequence carry the last valid cumulative decay so every exponent stays finite
-      pf.gb = p.gam[(tok0 + min(tok, rows - 1)) * p.HV + hv];
-    }
-  };
-  // Touch the next chunk's rows early so that the register loads issued late in the iteration hit L2.
-  auto prefetch_l2 = [&](int c) {
-    const int t0 = c * kC;
-    const int rows = min(kC, sq.len - t0);
-    const int64_t tok0 = int64_t(sq.bos) + t0;
-    if (tid < 128) {
-      const int r = tid & 63;
-      if (r < rows) {
-        const bf16* src = tid >= 64 ? p.k + (tok0 + r) * p.k_st + hk * p.k_sh : p.q + (tok0 + r) * p.q_st + hk * p.q_sh;
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 64));
-      }
-    } else if (tid < 192) {
-      const int r = tid - 128;
-      if (r < rows) {
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.X + ((tok0 + r) * p.HV + hv) * kC));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.v + (tok0 + r) * p.v_st + hv * p.v_sh + vb * kBV));
-      }
-    }
-  };
-  uint4 vcur[4];
-  auto store_scalars = [&](int c) {   // double-buffered by chunk parity: may be written while chunk c-1 is in flight
-    if (half == 0) {
-      if (kside) beta_s[c & 1][tok] = pf.gb;
-      else gam_s[c & 1][tok] = pf.gb;
-    }
-  };
-  auto store_panels = [&]() {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) vcur[i] = pf.v[i];
-  };
-
-  auto issue_qk_load = [&](int c) {   // one thread: the chunk's q rows (panel rows 0-63) and k rows (rows 64-127)
-    const int row0 = sq.bos + c * kC;
-    mbar_arrive_expect_tx(&qk_bar, 4 * 8192);
-    tma_load_tile(sb + kOffQK, &tm_q, 0, hk, row0, &qk_bar);
-    tma_load_tile(sb + kOffQK + kQKPanel, &tm_q, 64, hk, row0, &qk_bar);
-    tma_load_tile(sb + kOffQK + 8192, &tm_k, 0, hk, row0, &qk_bar);
-    tma_load_tile(sb + kOffQK + kQKPanel + 8192, &tm_k, 64, hk, row0, &qk_bar);
-  };
-
-  auto issue_x_load = [&](int c) {    // one thread: the chunk's 64 x 64 inverse
-    mbar_arrive_expect_tx(&x_bar, 8192);
-    tma_load_tile(sb + kOffX, &tm_x, 0, hv, sq.bos + c * kC, &x_bar);
-  };
-
-  // operands (shared addresses)
-  const Operand opQK{sb + kOffQK, kQKPanel, 0};                 // [q; k]  M = 128, reduction over K
-  const Operand opKT{sb + kOffQK + 8192, kQKPanel, 1};          // k^T     M = 128 (K dims), reduction over tokens
-  const Operand opSH{sb + kOffSH, 16384, 1}, opSL{sb + kOffSL, 16384, 1};
-  const Operand opZH{sb + kOffZH, 8192, 1}, opZL{sb + kOffZL, 8192, 1};
-  const Operand opVH{sb + kOffVH, 8192, 1}, opVL{sb + kOffVL, 8192, 1};
-  const Operand opX{sb + kOffX - 8192, 16384, 0};               // rows 64..127 of this tile are X
-  const Operand opPH{sb + kOffQK, kQKPanel, 0}, opPL{sb + kOffQK + kQKPanel, kQKPanel, 0};  // alias the q rows
-
-  float srow[32];   // this thread's 32 columns of the fp32 state row
-
-  // ---- prologue: chunk 0 operands and the initial state.  A sequence without tokens (packed batches may hold some)
-  // requests nothing: its chunk loop does not run and the final state below is the initial state.
-  if (sq.nt > 0) {
-    if (tid == 0) {
-      issue_qk_load(0);
-      issue_x_load(0);
-    }
-    prefetch_load(0);
-    prefetch_scalars(0);
-    store_scalars(0);
-    store_panels();
-  }
-  if (p.h0) {
-    const float* src = p.h0 + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      const float4 t = *reinterpret_cast<const float4*>(src + i);
-      srow[i] = t.x; srow[i + 1] = t.y; srow[i + 2] = t.z; srow[i + 3] = t.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) srow[i] = 0.f;
-  }
-  __syncthreads();  // gam_s[0] visible
-
-  for (int c = 0; c < sq.nt; ++c) {
-    const int cur = c & 1;
-    const int t0 = c * kC;
-    const int rows = min(kC, sq.len - t0);
-    const int64_t tok0 = int64_t(sq.bos) + t0;
-    const float gam_last = gam_s[cur][rows - 1];
-    const float gam_i = gam_s[cur][tok];
-
-    // ---- stage 0: publish the state at chunk start (split copy for the MMAs, pre-decayed master in TMEM)
-    row32_to_hilo(smem + kOffSH, smem + kOffSL, row, half, srow);
-    {
-      const float dl = __expf(gam_last);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) srow[i] *= dl;
-      tmem_st_row32(trow + kColS, srow);
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- stage 1: [Q;K] S  (split state: two passes)
-    if (tid == 0) {
-      if (!mbar_wait(&qk_bar, qkphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // q, k tiles have landed
-      mma_tile(tbase + kColRQ, opQK, opSH, 128, 64, 8, false);
-      mma_tile(tbase + kColRQ, opQK, opSL, 128, 64, 8, true);
-      mma_commit(&bar);
-    }
-    qkphase ^= 1;
-    if (p.s_img) {  // the split state copy in shared memory is already in the saved panel-image format: plain 16-byte
-                    // copies by all threads while the MMAs run (bulk stores would queue ahead of the chunk's TMA loads)
-      uint4* dst = reinterpret_cast<uint4*>(p.s_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * p.nvb + vb) * (2 * 8192));
-      const uint4* src = reinterpret_cast<const uint4*>(smem + kOffSH);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) dst[tid + i * kFwdThreads] = src[tid + i * kFwdThreads];
-    }
-    if (c + 1 < sq.nt) {
-      prefetch_l2(c + 1);
-      prefetch_scalars(c + 1);
-      store_scalars(c + 1);
-    }
-    wait_or_mark(&bar, phase, dead, p.status);
-    tc_fence_after();
-    if (tid == 0) {  // the q rows are consumed: the chunk's P panels (from the prep kernel) take their place
-      const bf16* src = p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192;
-      mbar_arrive_expect_tx(&pbar, 16384);
-      bulk_load(sb + kOffQK, src, 8192, &pbar);
-      bulk_load(sb + kOffQK + kQKPanel, src + 4096, 8192, &pbar);
-    }
-
-    // ---- stage 2: k-side rows build Z = beta (V - exp(gam) K S)
-    float acc[32];
-    if (kside) {
-      tmem_ld_row32(trow + kColRQ, acc);
-      const float eg = __expf(gam_i), bi = beta_s[cur][tok];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float vv[8];
-        unpack_bf16x8(vcur[i], vv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i * 8 + j] = bi * (vv[j] - eg * acc[i * 8 + j]);
-      }
-      row32_to_hilo(smem + kOffZH, smem + kOffZL, tok, half, acc);
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- stage 3: v_new = X Z  (rows 64..127 of the accumulator)
-    if (tid == 0) {
-      if (!mbar_wait(&x_bar, xphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // the X tile has landed
-      mma_tile(tbase + kColVN, opX, opZH, 128, 64, 4, false);
-      mma_tile(tbase + kColVN, opX, opZL, 128, 64, 4, true);
-      mma_commit(&bar);
-    }
-    xphase ^= 1;
-    wait_or_mark(&bar, phase, dead, p.status);
-    tc_fence_after();
-    if (tid == 0 && c + 1 < sq.nt) issue_x_load(c + 1);
-
-    // ---- stage 4: k-side rows publish v_new and its decayed copy
-    if (kside) {
-      tmem_ld_row32(trow + kColVN, acc);
-      if (tok >= rows) {   // rows of the X tile past the end of the sequence belong to whatever follows in memory
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-      }
-      row32_to_hilo(smem + kOffZH, smem + kOffZL, tok, half, acc);
-      const float dk = __expf(gam_last - gam_i);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] *= dk;
-      row32_to_hilo(smem + kOffVH, smem + kOffVL, tok, half, acc);
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- stage 5: P v_new (three passes) and the state update S += K^T vhat
-    if (tid == 0) {
-      mma_tile(tbase + kColS, opKT, opVH, 128, 64, 4, true);
-      mma_tile(tbase + kColS, opKT, opVL, 128, 64, 4, true);
-      if (!mbar_wait(&pbar, pphase, p.status, FLA_ERR_TIMEOUT)) dead = true;   // P panels have landed
-      mma_tile(tbase + kColQK, opPH, opZH, 128, 64, 4, false);
-      mma_tile(tbase + kColQK, opPH, opZL, 128, 64, 4, true);
-      mma_tile(tbase + kColQK, opPL, opZH, 128, 64, 4, true);
-      mma_commit(&bar);
-    }
-    pphase ^= 1;
-    if (p.vn_img) {
-      uint4* dst = reinterpret_cast<uint4*>(p.vn_img + (((int64_t(sq.cbase) + c) * p.HV + hv) * p.nvb + vb) * (2 * 4096));
-      const uint4* src = reinterpret_cast<const uint4*>(smem + kOffZH);     // Z_hi and Z_lo panels are adjacent
-#pragma unroll
-      for (int i = 0; i < 4; ++i) dst[tid + i * kFwdThreads] = src[tid + i * kFwdThreads];
-    }
-    if (c + 1 < sq.nt) prefetch_load(c + 1);   // the next chunk's rows (L2-resident by now) travel while the MMAs run
-    wait_or_mark(&bar, phase, dead, p.status);
-    tc_fence_after();
-    if (tid == 0 && c + 1 < sq.nt) issue_qk_load(c + 1);   // every reader of the q / k / P panels has completed
-
-    // ---- stage 6: output rows, next state, next chunk's operand panels
-    if (!kside) {
-      float qs[32];
-      tmem_ld32(trow + kColRQ, qs);
-      tmem_ld32(trow + kColQK, acc);
-      tmem_ld_wait();
-      const float eg = __expf(gam_i) * p.scale;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] = eg * qs[i] + p.scale * acc[i];
-      if (tok < rows) {
-        const int64_t off = (tok0 + tok) * p.o_st + hv * p.o_sh + vb * kBV + c0;
-        if (p.o_is_f32) {
-          float* dst = static_cast<float*>(p.o) + off;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-        } else {
-          bf16* dst = static_cast<bf16*>(p.o) + off;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(acc + ch * 8);
-        }
-      }
-    }
-    tmem_ld_row32(trow + kColS, srow);
-    // The only readers of the q/k/X panels were this chunk's MMAs, which have completed; no barrier is needed
-    // before the next iteration (its first barrier orders everything else).
-    if (c + 1 < sq.nt) store_panels();
-  }
-
-  if (!dead && p.ht) {
-    float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + row) * p.V + vb * kBV + c0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
 }  // namespace fla
@@ -622,7 +298,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   std::atomic<bool>& attr_done = attr_done_dev[dev];
   if (!attr_done) {
     if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prep_smem) != cudaSuccess) return FLA_ERR_CUDA;
-    if (cudaFuncSetAttribute(gdn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(gdn_scan_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kScanFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
+    if (cudaFuncSetAttribute(gdn_scan_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kScanFwdSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done = true;
   }
   const int nt_max = (max_len + kC - 1) / kC;
@@ -641,10 +318,15 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
       make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)) ||
       make_row_tile_map(&tm_x, p.X, kC, uint64_t(HV), uint64_t(B * T), uint64_t(kC), uint64_t(HV) * kC))
     return FLA_ERR_CUDA;
+  CUtensorMap tm_v;
+  if (make_row_tile_map(&tm_v, p.v, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.v_sh), uint64_t(p.v_st))) return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_fwd", cs);
-    gdn_fwd_kernel<<<dim3(unsigned(p.nvb), unsigned(HV), N), kFwdThreads, kFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x);
+    const dim3 grid(unsigned(V / 128), unsigned(HV), N);
+    if (p.s_img) gdn_scan_fwd_kernel<true><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x, tm_v);
+    else gdn_scan_fwd_kernel<false><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x, tm_v);
   }
   return cuda_status(cudaGetLastError());
 }
+
 

@@ -1,0 +1,427 @@
+// Reverse scan of the chunked gated-delta-rule backward (chunk_bwd_dv_local + chunk_gated_delta_rule_bwd_dhu of the
+// reference, examples/flash_gated_delta_rule.py:930-960, and the dv / du parts of prepare_wy_repr_bwd_*).
+//
+// One CTA per (sequence, value head, 128-column block of V); the state gradient lives transposed in tensor memory
+// (scan_common.cuh: TMEM lane v = value channel v).  Per chunk, in reverse order, with dS' the gradient entering the
+// chunk from the right:
+//     W1^T   = dS'^T K^T                           N = 64 tokens, reduction over the 128 key dims
+//     U1^T   = dO^T P                              (= (P^T dO)^T; both operands from shared memory)
+//     dVn^T  = scale U1^T + e^{gam_L-gam} W1^T     epilogue, zero for tokens past the end of the sequence
+//     dZ^T   = dVn^T X                             (= (X^T dVn)^T)
+//     dV     = beta dZ;   bz = sum_v dZ V  (partial sums per 32 value channels);   dR = -beta e^gam dZ
+//     dS^T   = e^{gam_L} dS'^T + [scale e^gam dO^T | dR^T] [Q; K]     N = 128 key dims, reduction over 128 rows
+// dO^T and V^T reach tensor memory through identity products.  For the chunk-parallel kernel the scan saves, per
+// (chunk, head, block), operand panels whose rows are value channels:
+//     ds_img  dS' as [value | residual] x [key dims 0-63 | 64-127] x 128 rows (v) x 64 columns   = 64 KB
+//     dz_img  [dO^T | dZ^T] x 128 rows (v) x 64 columns (tokens), one bf16 each                   = 32 KB
+#pragma once
+#include "scan_common.cuh"
+
+namespace fla {
+
+// tensor-memory columns (512 allocated)
+constexpr uint32_t uDS = 0;        // dS^T fp32 accumulator (128 key dims)
+constexpr uint32_t uAh = 128;      // dS'^T as A operand (128 key dims in 64 columns); later [scale e^gam dO^T | dR^T] (128 rows of [q; k])
+constexpr uint32_t uAl = 192;      // residuals of the same
+constexpr uint32_t uW = 256;       // W1^T accumulator, later the dZ^T accumulator
+constexpr uint32_t uU = 320;       // U1^T accumulator, later dO^T (fp32)
+constexpr uint32_t uDVh = 384;     // dVn^T as A operand: 64 tokens in 32 columns
+constexpr uint32_t uDVl = 416;
+constexpr uint32_t uVT = 448;      // V^T (fp32, 64 tokens)
+
+// shared memory: load buffers twice (chunk parity)
+constexpr uint32_t bQK = 0;                  // 2 x 32 KB
+constexpr uint32_t bX = 65536;               // 2 x 8 KB
+constexpr uint32_t bP = 81920;               // 2 x 16 KB (value, residual)
+constexpr uint32_t bV = 114688;              // 2 x 16 KB: v rows, two 64-column panels of 64 rows
+constexpr uint32_t bD = 147456;              // 2 x 16 KB: dO rows, same layout
+constexpr uint32_t bO = 180224;              // 32 KB: dV rows [64 tokens][128 channels] on their way out
+constexpr uint32_t bI = 212992;              // 8 KB: identity panel
+constexpr uint32_t kScanBwdSmem = 221184;
+
+struct ScanBwdBars {
+  uint64_t *mma_bar, *qk_bar, *x_bar, *p_bar, *v_bar, *d_bar;
+};
+__device__ __noinline__ bool scan_bwd_mma1(uint32_t tbase, uint32_t sb, int b, uint32_t ph, ScanBwdBars bars, int* status, bool dead) {
+  tc_fence_after();
+  if (!dead && !mbar_wait(&bars.qk_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opK{sb + bQK + b * 32768 + 8192, 16384, 0};          // k rows as B: N = 64 tokens, reduction over key dims
+  mma_tile_ts(tbase + uW, tbase + uAh, opK, 64, 8, false);
+  mma_tile_ts(tbase + uW, tbase + uAl, opK, 64, 8, true);
+  if (!dead && !mbar_wait(&bars.d_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  if (!dead && !mbar_wait(&bars.p_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opDt{sb + bD + b * 16384, 8192, 1};                  // dO^T: M = 128 channels over two panels, reduction over tokens
+  const Operand opPh{sb + bP + b * 16384, 8192, 1}, opPl{sb + bP + b * 16384 + 8192, 8192, 1};   // P with its rows as the reduction
+  mma_tile(tbase + uU, opDt, opPh, 128, 64, 4, false);
+  mma_tile(tbase + uU, opDt, opPl, 128, 64, 4, true);
+  mma_commit(bars.mma_bar);
+  return dead;
+}
+__device__ __noinline__ bool scan_bwd_mma2(uint32_t tbase, uint32_t sb, int b, uint32_t ph, ScanBwdBars bars, int* status, bool dead) {
+  tc_fence_after();
+  if (!dead && !mbar_wait(&bars.x_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opX{sb + bX + b * 8192, 8192, 1};                    // X with its rows as the reduction: X^T dVn
+  mma_tile_ts(tbase + uW, tbase + uDVh, opX, 64, 4, false);
+  mma_tile_ts(tbase + uW, tbase + uDVl, opX, 64, 4, true);
+  if (!dead && !mbar_wait(&bars.v_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opI{sb + bI, 8192, 0};
+  const Operand opDt{sb + bD + b * 16384, 8192, 1}, opVt{sb + bV + b * 16384, 8192, 1};
+  mma_tile(tbase + uU, opDt, opI, 128, 64, 4, false);                // dO^T, exact
+  mma_tile(tbase + uVT, opVt, opI, 128, 64, 4, false);               // V^T, exact
+  mma_commit(bars.mma_bar);
+  return dead;
+}
+__device__ __noinline__ bool scan_bwd_mma3(uint32_t tbase, uint32_t sb, int b, ScanBwdBars bars, bool dead) {
+  tc_fence_after();
+  const Operand opQK{sb + bQK + b * 32768, 16384, 1};                // [q; k] rows as the reduction, N = 128 key dims
+  mma_tile_ts(tbase + uDS, tbase + uAh, opQK, 128, 8, true);
+  mma_tile_ts(tbase + uDS, tbase + uAl, opQK, 128, 8, true);
+  mma_commit(bars.mma_bar);
+  return dead;
+}
+
+// 32 values per lane -> lane l keeps the sum over the warp of value l (recursive halving: 31 shuffles)
+__device__ __forceinline__ float warp_transpose_reduce32(float* x, int lane) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const bool up = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < off; ++i) {
+      const float send = up ? x[i] : x[i + off];
+      const float keep = up ? x[i + off] : x[i];
+      x[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+  return x[0];
+}
+
+__global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
+                                                                        const __grid_constant__ CUtensorMap tm_k,
+                                                                        const __grid_constant__ CUtensorMap tm_x,
+                                                                        const __grid_constant__ CUtensorMap tm_v,
+                                                                        const __grid_constant__ CUtensorMap tm_d) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ ScanFactors fac[3];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t mma_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2], d_bar[2];
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
+  const int hk = hv / (p.HV / p.HK);
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  const uint32_t sb = smem_u32(smem);
+  const int nt = sq.nt;
+
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&mma_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qk_bar[i], 1);
+      mbar_init(&x_bar[i], 1);
+      mbar_init(&p_bar[i], 1);
+      mbar_init(&v_bar[i], 1);
+      mbar_init(&d_bar[i], 1);
+    }
+    mbar_init_fence();
+  }
+  write_identity_panel(smem + bI, tid, kScanThreads);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  bool dead = false;
+  // chunks are visited last to first; step s = 0, 1, ... handles chunk nt - 1 - s and uses the buffers of parity s & 1
+
+  if (warp == 8) {
+    // ============================================================ helper warp: TMA loads and per-token factors
+    auto issue_loads = [&](int s) {
+      const int c = nt - 1 - s, b = s & 1, row0 = sq.bos + c * kC;
+      const uint32_t qk = sb + bQK + b * 32768;
+      mbar_arrive_expect_tx(&qk_bar[b], 32768);
+      tma_load_tile(qk, &tm_q, 0, hk, row0, &qk_bar[b]);
+      tma_load_tile(qk + 16384, &tm_q, 64, hk, row0, &qk_bar[b]);
+      tma_load_tile(qk + 8192, &tm_k, 0, hk, row0, &qk_bar[b]);
+      tma_load_tile(qk + 16384 + 8192, &tm_k, 64, hk, row0, &qk_bar[b]);
+      mbar_arrive_expect_tx(&d_bar[b], 16384);
+      tma_load_tile(sb + bD + b * 16384, &tm_d, vb * 128, hv, row0, &d_bar[b]);
+      tma_load_tile(sb + bD + b * 16384 + 8192, &tm_d, vb * 128 + 64, hv, row0, &d_bar[b]);
+      mbar_arrive_expect_tx(&p_bar[b], 16384);
+      bulk_load(sb + bP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
+      mbar_arrive_expect_tx(&x_bar[b], 8192);
+      tma_load_tile(sb + bX + b * 8192, &tm_x, 0, hv, row0, &x_bar[b]);
+      mbar_arrive_expect_tx(&v_bar[b], 16384);
+      tma_load_tile(sb + bV + b * 16384, &tm_v, vb * 128, hv, row0, &v_bar[b]);
+      tma_load_tile(sb + bV + b * 16384 + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[b]);
+    };
+    float pf_g[2] = {0.f, 0.f}, pf_b[2] = {0.f, 0.f}, pf_gl = 0.f;
+    auto load_scalars = [&](int s) {
+      if (s < nt) {
+        const int c = nt - 1 - s;
+        const int rows = min(kC, sq.len - c * kC);
+        const int64_t tok0 = int64_t(sq.bos) + c * kC;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int t = lane + 32 * j;
+          pf_g[j] = p.gam[(tok0 + min(t, rows - 1)) * p.HV + hv];
+          pf_b[j] = t < rows ? ld_scalar(p.beta, (tok0 + t) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+        }
+        pf_gl = p.gam[(tok0 + rows - 1) * p.HV + hv];
+      }
+    };
+    auto make_factors = [&](int s) {
+      if (s < nt) {
+        ScanFactors& f = fac[s % 3];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int t = lane + 32 * j;
+          const float eg = __expf(pf_g[j]);
+          f.b[t] = pf_b[j];
+          f.bg[t] = pf_b[j] * eg;
+          f.se[t] = p.scale * eg;
+          f.dk[t] = __expf(pf_gl - pf_g[j]);
+        }
+        if (lane == 0) f.dl = __expf(pf_gl);
+      }
+    };
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tm_q);
+      tma_prefetch_descriptor(&tm_k);
+      tma_prefetch_descriptor(&tm_x);
+      tma_prefetch_descriptor(&tm_v);
+      tma_prefetch_descriptor(&tm_d);
+      if (nt > 0) issue_loads(0);
+    }
+    __syncwarp();
+    load_scalars(0);
+    make_factors(0);
+    load_scalars(1);
+    scan_sync();   // factors of the first step are visible
+    for (int s = 0; s < nt; ++s) {
+      scan_sync();                                          // sync 1
+      if (lane == 0 && s + 1 < nt) issue_loads(s + 1);
+      __syncwarp();
+      make_factors(s + 1);
+      load_scalars(s + 2);
+      scan_sync();                                          // sync 2
+      scan_sync();                                          // sync 3
+    }
+    scan_sync();
+    return;
+  }
+
+  // ================================================================ epilogue warps
+  const ScanBwdBars bars{&mma_bar, qk_bar, x_bar, p_bar, v_bar, d_bar};
+  const int quad = warp & 3, half = warp >> 2;
+  const int vrow = quad * 32 + lane;
+  const uint32_t tlane = tmem_addr(tbase, quad * 32, 0);
+  const int t_lo = half * 32;
+  const int k_lo = half * 64;
+  uint32_t mphase = 0;
+
+  {   // dht (or zero) into the accumulator columns
+    const float* src = p.dht ? p.dht + ((int64_t(n) * p.HV + hv) * kK + k_lo) * p.V + vb * 128 + vrow : nullptr;
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {
+      float s16[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) s16[i] = src ? src[int64_t(part * 16 + i) * p.V] : 0.f;
+      tmem_st16(tlane + uDS + k_lo + part * 16, s16);
+    }
+    tmem_st_wait();
+  }
+  // The dO rows of a ragged last chunk that lie past the end of the sequence belong to whatever follows in memory: they
+  // are zeroed in shared memory (every other operand meets a zero row of beta or of dVn there).
+  if (nt > 0 && sq.len - (nt - 1) * kC < kC) {
+    const int rows = sq.len - (nt - 1) * kC;
+    if (!mbar_wait(&d_bar[0], 0, p.status, FLA_ERR_TIMEOUT)) dead = true;
+    for (int idx = tid; idx < (kC - rows) * 16; idx += kScanEpiThreads) {
+      const int r = rows + idx / 16, pc = idx % 16;
+      *reinterpret_cast<uint4*>(smem + bD + (pc >> 3) * 8192 + panel_chunk_off(r, pc & 7)) = make_uint4(0, 0, 0, 0);
+    }
+    fence_async_smem();
+  }
+  scan_sync();   // factors of the first step are visible
+
+  // dV rows of the chunk handled in step s: formed in the second epilogue, stored while the state update runs
+  float ov[32];
+  auto store_dv = [&](int c) {
+    const int rows = min(kC, sq.len - c * kC);
+    const int64_t tok0 = int64_t(sq.bos) + c * kC;
+    uint8_t* tile = smem + bO;
+    if (p.grads_f32) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) *reinterpret_cast<float*>(tile + (t_lo + i) * 512 + vrow * 4) = ov[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) *reinterpret_cast<bf16*>(tile + (t_lo + i) * 256 + vrow * 2) = __float2bfloat16_rn(ov[i]);
+    }
+    epi_sync();
+    if (p.grads_f32)
+      copy_out_tile<512>(tile, reinterpret_cast<uint8_t*>(static_cast<float*>(p.dv) + tok0 * p.dv_st + hv * p.dv_sh + vb * 128),
+                         p.dv_st * 4, rows, tid);
+    else
+      copy_out_tile<256>(tile, reinterpret_cast<uint8_t*>(static_cast<bf16*>(p.dv) + tok0 * p.dv_st + hv * p.dv_sh + vb * 128),
+                         p.dv_st * 2, rows, tid);
+  };
+
+  for (int s = 0; s < nt; ++s) {
+    const int c = nt - 1 - s, b = s & 1;
+    const uint32_t ph = (s >> 1) & 1;
+    const ScanFactors& f = fac[s % 3];
+    const int rows = min(kC, sq.len - c * kC);
+    const int64_t cidx = ((int64_t(sq.cbase) + c) * p.HV + hv) * (p.V / 128) + vb;
+
+    // ---- A: publish dS' (the gradient entering this chunk): bf16 value + residual as A operand, decayed copy as accumulator
+    {
+      const float dl = f.dl;
+#pragma unroll
+      for (int g4 = 0; g4 < 4; ++g4) {
+        float s16[16];
+        tmem_ld16(tlane + uDS + k_lo + g4 * 16, s16);
+        tmem_ld_wait();
+        uint32_t hi[8], lo[8];
+        split16(s16, hi, lo);
+        tmem_st8u(tlane + uAh + half * 32 + g4 * 8, hi);
+        tmem_st8u(tlane + uAl + half * 32 + g4 * 8, lo);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s16[i] *= dl;
+        tmem_st16(tlane + uDS + k_lo + g4 * 16, s16);
+        group_fence();
+      }
+      tmem_st_wait();
+    }
+    tc_fence_before();
+    scan_sync();                                   // sync 1
+    tc_fence_after();
+    if (tid == 0) dead = scan_bwd_mma1(tbase, sb, b, ph, bars, p.status, dead);
+    // ---- while W1 / U1 run: the dS' image for the chunk-parallel kernel
+    {
+      uint8_t* img = reinterpret_cast<uint8_t*>(p.ds_img + cidx * 32768);
+      uint32_t w[16];
+#pragma unroll
+      for (int part = 0; part < 4; ++part) {
+        tmem_ld16u(tlane + ((part < 2) ? uAh : uAl) + half * 32 + (part & 1) * 16, w);
+        tmem_ld_wait();
+        uint8_t* dst = img + (part < 2 ? 0 : 32768) + half * 16384;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+          *reinterpret_cast<uint4*>(dst + panel_chunk_off(vrow, (part & 1) * 4 + ch)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+      }
+    }
+    wait_or_mark(&mma_bar, mphase, dead, p.status);
+    tc_fence_after();
+
+    // ---- B: dVn^T = scale U1^T + e^{gam_L-gam} W1^T (zero past the end of the sequence) for my 32 tokens
+    {
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        float w1[16], u1[16];
+        tmem_ld16(tlane + uW + t_lo + g * 16, w1);
+        tmem_ld16(tlane + uU + t_lo + g * 16, u1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i4 = 0; i4 < 16; i4 += 4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(&f.dk[t_lo + g * 16 + i4]);
+          const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = i4 + j;
+            u1[i] = (t_lo + g * 16 + i < rows) ? p.scale * u1[i] + dv4[j] * w1[i] : 0.f;
+          }
+        }
+        uint32_t hi[8], lo[8];
+        split16(u1, hi, lo);
+        tmem_st8u(tlane + uDVh + half * 16 + g * 8, hi);
+        tmem_st8u(tlane + uDVl + half * 16 + g * 8, lo);
+        group_fence();
+      }
+      tmem_st_wait();
+    }
+    tc_fence_before();
+    scan_sync();                                   // sync 2
+    tc_fence_after();
+    if (tid == 0) dead = scan_bwd_mma2(tbase, sb, b, ph, bars, p.status, dead);
+    wait_or_mark(&mma_bar, mphase, dead, p.status);
+    tc_fence_after();
+
+    // ---- C: dZ^T -> dV rows, partial sums of dZ V, the [dO^T | dZ^T] image, the operand [scale e^gam dO^T | -beta e^gam dZ^T]
+    {
+      uint8_t* img = reinterpret_cast<uint8_t*>(p.dz_img + cidx * 16384);
+      float pr[32];
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        float dz[16], t16[16];
+        tmem_ld16(tlane + uW + t_lo + g * 16, dz);
+        tmem_ld16(tlane + uVT + t_lo + g * 16, t16);     // V^T
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pr[g * 16 + i] = dz[i] * t16[i];
+        uint32_t w8[8];
+        pack16(dz, w8);
+        *reinterpret_cast<uint4*>(img + 16384 + panel_chunk_off(vrow, half * 4 + g * 2)) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+        *reinterpret_cast<uint4*>(img + 16384 + panel_chunk_off(vrow, half * 4 + g * 2 + 1)) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+#pragma unroll
+        for (int i4 = 0; i4 < 16; i4 += 4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(&f.b[t_lo + g * 16 + i4]);
+          const float4 g4 = *reinterpret_cast<const float4*>(&f.bg[t_lo + g * 16 + i4]);
+          ov[g * 16 + i4] = b4.x * dz[i4];         dz[i4] *= -g4.x;
+          ov[g * 16 + i4 + 1] = b4.y * dz[i4 + 1]; dz[i4 + 1] *= -g4.y;
+          ov[g * 16 + i4 + 2] = b4.z * dz[i4 + 2]; dz[i4 + 2] *= -g4.z;
+          ov[g * 16 + i4 + 3] = b4.w * dz[i4 + 3]; dz[i4 + 3] *= -g4.w;
+        }
+        uint32_t hi[8], lo[8];
+        split16(dz, hi, lo);                              // dR^T: rows 64..127 of the [q; k] reduction = columns 32..63 of the operand
+        tmem_st8u(tlane + uAh + 32 + half * 16 + g * 8, hi);
+        tmem_st8u(tlane + uAl + 32 + half * 16 + g * 8, lo);
+        tmem_ld16(tlane + uU + t_lo + g * 16, t16);       // dO^T
+        tmem_ld_wait();
+        pack16(t16, w8);                                  // exact: these are the bf16 inputs
+        *reinterpret_cast<uint4*>(img + panel_chunk_off(vrow, half * 4 + g * 2)) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+        *reinterpret_cast<uint4*>(img + panel_chunk_off(vrow, half * 4 + g * 2 + 1)) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+#pragma unroll
+        for (int i4 = 0; i4 < 16; i4 += 4) {
+          const float4 s4 = *reinterpret_cast<const float4*>(&f.se[t_lo + g * 16 + i4]);
+          t16[i4] *= s4.x; t16[i4 + 1] *= s4.y; t16[i4 + 2] *= s4.z; t16[i4 + 3] *= s4.w;
+        }
+        split16(t16, hi, lo);                             // scale e^gam dO^T: rows 0..63 of the reduction
+        tmem_st8u(tlane + uAh + half * 16 + g * 8, hi);
+        tmem_st8u(tlane + uAl + half * 16 + g * 8, lo);
+        group_fence();
+      }
+      tmem_st_wait();
+      // sum over my warp's 32 channels of dZ V for each of my 32 tokens; lane l ends up with token t_lo + l
+      const float bzsum = warp_transpose_reduce32(pr, lane);
+      if (t_lo + lane < rows)
+        p.bz[(int64_t(vb * 4 + quad) * p.total_tokens + int64_t(sq.bos) + c * kC + t_lo + lane) * p.HV + hv] = bzsum;
+    }
+    tc_fence_before();
+    scan_sync();                                   // sync 3
+    tc_fence_after();
+    if (tid == 0) dead = scan_bwd_mma3(tbase, sb, b, bars, dead);
+    store_dv(c);                                   // while the state-gradient update runs
+    wait_or_mark(&mma_bar, mphase, dead, p.status);
+    tc_fence_after();
+  }
+
+  if (!dead && p.dh0) {
+    float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + k_lo) * p.V + vb * 128 + vrow;
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {
+      float s16[16];
+      tmem_ld16(tlane + uDS + k_lo + part * 16, s16);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) dst[int64_t(part * 16 + i) * p.V] = s16[i];
+    }
+  }
+  tc_fence_before();
+  scan_sync();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
+}  // namespace fla
