@@ -31,14 +31,17 @@ constexpr uint32_t tZAl = 416;
 constexpr uint32_t tVAh = 448;     // V^T (fp32, 64 columns) until Z is built, then the decayed v_new^T as A operand
 constexpr uint32_t tVAl = 480;
 
-// shared memory (offsets from a 1024-byte aligned base); the load buffers exist twice (chunk parity)
+// shared memory (offsets from a 1024-byte aligned base).  The [q; k] panels exist twice (chunk parity): k is read by the
+// last product of a chunk and q, k of the next chunk by the first one right after.  X, P and the v rows have one buffer
+// each: they are reloaded as soon as the product that reads them has completed, most of a chunk before their next use.
 constexpr uint32_t sQK = 0;                  // 2 x 32 KB: [q; k] rows, two 64-column panels of 128 rows
-constexpr uint32_t sX = 65536;               // 2 x 8 KB
-constexpr uint32_t sP = 81920;               // 2 x 16 KB (value, residual)
-constexpr uint32_t sV = 114688;              // 2 x 16 KB: v rows of the chunk, two 64-column panels of 64 rows
-constexpr uint32_t sO = 147456;              // 32 KB: the chunk's output rows [64 tokens][128 channels] on their way out
-constexpr uint32_t sI = 180224;              // 8 KB: identity panel
-constexpr uint32_t kScanFwdSmem = 188416;
+constexpr uint32_t sX = 65536;               // 8 KB
+constexpr uint32_t sP = 73728;               // 16 KB (value, residual)
+constexpr uint32_t sV = 90112;               // 16 KB: v rows of the chunk, two 64-column panels of 64 rows
+constexpr uint32_t sO = 106496;              // 16 KB: the chunk's output rows on their way out
+constexpr uint32_t sI = 122880;              // 8 KB: identity panel
+constexpr uint32_t sG = 131072;              // 64 KB: the saved panels of a chunk on their way out (state image, then v_new image)
+constexpr uint32_t kScanFwdSmem = 196608;
 
 struct ScanBars {
   uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;
@@ -54,18 +57,16 @@ __device__ __noinline__ bool scan_fwd_mma1(uint32_t tbase, uint32_t sb, int c, S
   mma_tile_ts(tbase + tKQ, tbase + tSAh, opKQ, 128, 8, false);
   mma_tile_ts(tbase + tKQ, tbase + tSAl, opKQ, 128, 8, true);
   // V^T into the columns the decayed v_new of this chunk will occupy later
-  if (!dead && !mbar_wait(&bars.v_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opVt{sb + sV + b * 16384, 8192, 1}, opI{sb + sI, 8192, 0};
+  if (!dead && !mbar_wait(bars.v_bar, c & 1, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opVt{sb + sV, 8192, 1}, opI{sb + sI, 8192, 0};
   mma_tile(tbase + tVAh, opVt, opI, 128, 64, 4, false);
   mma_commit(bars.mma_bar);
   return dead;
 }
 __device__ __noinline__ bool scan_fwd_mma2(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
-  const int b = c & 1;
-  const uint32_t ph = (c >> 1) & 1;
   tc_fence_after();
-  if (!dead && !mbar_wait(&bars.x_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opX{sb + sX + b * 8192, 8192, 0};
+  if (!dead && !mbar_wait(bars.x_bar, c & 1, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opX{sb + sX, 8192, 0};
   mma_tile_ts(tbase + tVN, tbase + tZAh, opX, 64, 4, false);
   mma_tile_ts(tbase + tVN, tbase + tZAl, opX, 64, 4, true);
   mma_commit(bars.mma_bar);
@@ -73,14 +74,13 @@ __device__ __noinline__ bool scan_fwd_mma2(uint32_t tbase, uint32_t sb, int c, S
 }
 __device__ __noinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
   const int b = c & 1;
-  const uint32_t ph = (c >> 1) & 1;
   tc_fence_after();
   const Operand opK{sb + sQK + b * 32768 + 8192, 16384, 1};   // k rows: reduction over tokens, N = 128 key dims over two panels
   mma_tile_ts(tbase + tST, tbase + tVAh, opK, 128, 4, true);
   mma_tile_ts(tbase + tST, tbase + tVAl, opK, 128, 4, true);
   mma_commit(bars.mma_bar);                                   // the state update: what the next chunk waits for
-  if (!dead && !mbar_wait(&bars.p_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opPh{sb + sP + b * 16384, 8192, 0}, opPl{sb + sP + b * 16384 + 8192, 8192, 0};
+  if (!dead && !mbar_wait(bars.p_bar, c & 1, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opPh{sb + sP, 8192, 0}, opPl{sb + sP + 8192, 8192, 0};
   mma_tile_ts(tbase + tVN, tbase + tZAh, opPh, 64, 4, false);
   mma_tile_ts(tbase + tVN, tbase + tZAl, opPh, 64, 4, true);
   mma_tile_ts(tbase + tVN, tbase + tZAh, opPl, 64, 4, true);
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ ScanFactors fac[3];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar, o_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2];
+  __shared__ __align__(8) uint64_t mma_bar, o_bar, qk_bar[2], x_bar, p_bar, v_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -113,12 +113,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
     mbar_init(&o_bar, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&qk_bar[i], 1);
-      mbar_init(&x_bar[i], 1);
-      mbar_init(&p_bar[i], 1);
-      mbar_init(&v_bar[i], 1);
-    }
+    mbar_init(&qk_bar[0], 1);
+    mbar_init(&qk_bar[1], 1);
+    mbar_init(&x_bar, 1);
+    mbar_init(&p_bar, 1);
+    mbar_init(&v_bar, 1);
     mbar_init_fence();
   }
   write_identity_panel(smem + sI, tid, kScanThreads);
@@ -131,7 +130,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
 
   if (warp == 8) {
     // ============================================================ helper warp: TMA loads and per-token factors
-    auto issue_loads = [&](int c) {
+    auto load_qk = [&](int c) {
       const int b = c & 1, row0 = sq.bos + c * kC;
       const uint32_t qk = sb + sQK + b * 32768;
       mbar_arrive_expect_tx(&qk_bar[b], 32768);
@@ -139,13 +138,20 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       tma_load_tile(qk + 16384, &tm_q, 64, hk, row0, &qk_bar[b]);
       tma_load_tile(qk + 8192, &tm_k, 0, hk, row0, &qk_bar[b]);
       tma_load_tile(qk + 16384 + 8192, &tm_k, 64, hk, row0, &qk_bar[b]);
-      mbar_arrive_expect_tx(&v_bar[b], 16384);
-      tma_load_tile(sb + sV + b * 16384, &tm_v, vb * 128, hv, row0, &v_bar[b]);
-      tma_load_tile(sb + sV + b * 16384 + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[b]);
-      mbar_arrive_expect_tx(&x_bar[b], 8192);
-      tma_load_tile(sb + sX + b * 8192, &tm_x, 0, hv, row0, &x_bar[b]);
-      mbar_arrive_expect_tx(&p_bar[b], 16384);
-      bulk_load(sb + sP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
+    };
+    auto load_v = [&](int c) {
+      const int row0 = sq.bos + c * kC;
+      mbar_arrive_expect_tx(&v_bar, 16384);
+      tma_load_tile(sb + sV, &tm_v, vb * 128, hv, row0, &v_bar);
+      tma_load_tile(sb + sV + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar);
+    };
+    auto load_x = [&](int c) {
+      mbar_arrive_expect_tx(&x_bar, 8192);
+      tma_load_tile(sb + sX, &tm_x, 0, hv, sq.bos + c * kC, &x_bar);
+    };
+    auto load_p = [&](int c) {
+      mbar_arrive_expect_tx(&p_bar, 16384);
+      bulk_load(sb + sP, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar);
     };
     // lane l handles tokens l and l + 32; the raw values of a chunk are requested two chunks ahead and wait in registers
     float pf_g[2] = {0.f, 0.f}, pf_b[2] = {0.f, 0.f}, pf_gl = 0.f;
@@ -183,28 +189,50 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       tma_prefetch_descriptor(&tm_k);
       tma_prefetch_descriptor(&tm_x);
       tma_prefetch_descriptor(&tm_v);
-      if (nt > 0) issue_loads(0);
+      if (nt > 0) {
+        load_qk(0);
+        load_v(0);
+        load_x(0);
+        load_p(0);
+      }
     }
     __syncwarp();
     load_scalars(0);
     make_factors(0);
     load_scalars(1);
     scan_sync();   // factors of chunk 0 are visible
+    uint32_t mphase = 0, ophase = 0;
     for (int c = 0; c < nt; ++c) {
-      scan_sync();                                          // sync 1: chunk c - 1 no longer reads the other buffers
-      if (lane == 0 && c + 1 < nt) issue_loads(c + 1);
+      const bool more = c + 1 < nt;
+      scan_sync();                                          // sync 1: chunk c - 1 no longer reads the other [q; k] buffer
+      if (lane == 0) {
+        if (more) load_qk(c + 1);
+        wait_or_mark(&mma_bar, mphase, dead, p.status);     // the first batch of products has read the v rows
+        if (more) load_v(c + 1);
+      }
       __syncwarp();
       make_factors(c + 1);                                  // read from sync 3 of this chunk on
       load_scalars(c + 2);
       scan_sync();                                          // sync 2
+      if (lane == 0) {
+        wait_or_mark(&mma_bar, mphase, dead, p.status);     // X has been read
+        if (more) load_x(c + 1);
+      }
+      __syncwarp();
       scan_sync();                                          // sync 3
+      if (lane == 0) {
+        wait_or_mark(&mma_bar, mphase, dead, p.status);
+        wait_or_mark(&o_bar, ophase, dead, p.status);       // the output product has read P
+        if (more) load_p(c + 1);
+      }
+      __syncwarp();
     }
     scan_sync();   // matches the epilogue warps' barrier before the TMEM is released
     return;
   }
 
   // ================================================================ epilogue warps
-  const ScanBars bars{&mma_bar, &o_bar, qk_bar, x_bar, p_bar, v_bar};
+  const ScanBars bars{&mma_bar, &o_bar, qk_bar, &x_bar, &p_bar, &v_bar};
   const int quad = warp & 3, half = warp >> 2;
   const int vrow = quad * 32 + lane;                       // my value channel inside the block = my TMEM lane
   const uint32_t tlane = tmem_addr(tbase, quad * 32, 0);
@@ -250,22 +278,9 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   };
   auto store_o = [&](int c) {
     const int rows = min(kC, sq.len - c * kC);
-    const int64_t tok0 = int64_t(sq.bos) + c * kC;
-    uint8_t* tile = smem + sO;
-    if (p.o_is_f32) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) *reinterpret_cast<float*>(tile + (t_lo + i) * 512 + vrow * 4) = ov[i];
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) *reinterpret_cast<bf16*>(tile + (t_lo + i) * 256 + vrow * 2) = __float2bfloat16_rn(ov[i]);
-    }
-    epi_sync();
-    if (p.o_is_f32)
-      copy_out_tile<512>(tile, reinterpret_cast<uint8_t*>(static_cast<float*>(p.o) + tok0 * p.o_st + hv * p.o_sh + vb * 128),
-                         p.o_st * 4, rows, tid);
-    else
-      copy_out_tile<256>(tile, reinterpret_cast<uint8_t*>(static_cast<bf16*>(p.o) + tok0 * p.o_st + hv * p.o_sh + vb * 128),
-                         p.o_st * 2, rows, tid);
+    const int64_t off = (int64_t(sq.bos) + c * kC) * p.o_st + hv * p.o_sh + vb * 128;
+    void* g = p.o_is_f32 ? static_cast<void*>(static_cast<float*>(p.o) + off) : static_cast<void*>(static_cast<bf16*>(p.o) + off);
+    store_rows_transposed(smem + sO, ov, g, p.o_st, p.o_is_f32 != 0, rows, half, vrow, tid);
   };
 
   for (int c = 0; c < nt; ++c) {
@@ -297,6 +312,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       tc_fence_after();
       form_o(c - 1);
     }
+    if (kSave && tid == 0) bulk_wait_read();       // the v_new image of chunk c - 1 has left the staging panels
     tc_fence_before();
     scan_sync();                                   // sync 1
     tc_fence_after();
@@ -304,16 +320,26 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     // ---- while [QS^T | KS^T] runs: output rows of chunk c - 1, saved state image
     if (c > 0) store_o(c - 1);
     if (kSave) {
-      uint8_t* img = reinterpret_cast<uint8_t*>(p.s_img + cidx * 32768);
+      // The state image: every thread copies its row of the operand just published (value, residual: 2 x 128 bytes)
+      // from tensor memory into the staging panels; one bulk copy then moves the 64 KB to global memory.  Stores made
+      // by the threads themselves would be 16-byte pieces 128 bytes apart: measured 0.4 ms per launch.
+      uint8_t* stg = smem + sG;
       uint32_t w[16];
 #pragma unroll
       for (int part = 0; part < 4; ++part) {             // my 64 key dims = one panel row = 8 pieces of 16 bytes; 16 columns per load
         tmem_ld16u(tlane + ((part < 2) ? tSAh : tSAl) + half * 32 + (part & 1) * 16, w);
         tmem_ld_wait();
-        uint8_t* dst = img + (part < 2 ? 0 : 32768) + half * 16384;
+        uint8_t* dst = stg + (part < 2 ? 0 : 32768) + half * 16384;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
           *reinterpret_cast<uint4*>(dst + panel_chunk_off(vrow, (part & 1) * 4 + ch)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+      }
+      fence_async_smem();
+      epi_sync();
+      if (tid == 0) {
+        bulk_store(p.s_img + cidx * 32768, sb + sG, 32768);
+        bulk_store(p.s_img + cidx * 32768 + 16384, sb + sG + 32768, 32768);
+        bulk_commit();
       }
     }
     wait_or_mark(&mma_bar, mphase, dead, p.status);
@@ -344,6 +370,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       }
       tmem_st_wait();
     }
+    if (kSave && tid == 0) bulk_wait_read();       // the state image has left the staging panels
     tc_fence_before();
     scan_sync();                                   // sync 2
     tc_fence_after();
@@ -364,12 +391,12 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
         split16(vn, hi, lo);
         tmem_st8u(tlane + tZAh + half * 16 + g * 8, hi);
         tmem_st8u(tlane + tZAl + half * 16 + g * 8, lo);
-        if (kSave) {
-          uint8_t* img = reinterpret_cast<uint8_t*>(p.vn_img + cidx * 16384);
+        if (kSave) {                                 // v_new image (value panel, residual panel) into the staging panels
+          uint8_t* stg = smem + sG;
 #pragma unroll
           for (int ch = 0; ch < 2; ++ch) {
-            *reinterpret_cast<uint4*>(img + panel_chunk_off(vrow, half * 4 + g * 2 + ch)) = make_uint4(hi[4 * ch], hi[4 * ch + 1], hi[4 * ch + 2], hi[4 * ch + 3]);
-            *reinterpret_cast<uint4*>(img + 16384 + panel_chunk_off(vrow, half * 4 + g * 2 + ch)) = make_uint4(lo[4 * ch], lo[4 * ch + 1], lo[4 * ch + 2], lo[4 * ch + 3]);
+            *reinterpret_cast<uint4*>(stg + panel_chunk_off(vrow, half * 4 + g * 2 + ch)) = make_uint4(hi[4 * ch], hi[4 * ch + 1], hi[4 * ch + 2], hi[4 * ch + 3]);
+            *reinterpret_cast<uint4*>(stg + 16384 + panel_chunk_off(vrow, half * 4 + g * 2 + ch)) = make_uint4(lo[4 * ch], lo[4 * ch + 1], lo[4 * ch + 2], lo[4 * ch + 3]);
           }
         }
 #pragma unroll
@@ -384,10 +411,17 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       }
       tmem_st_wait();
     }
+    if (kSave) fence_async_smem();
     tc_fence_before();
     scan_sync();                                   // sync 3
     tc_fence_after();
-    if (tid == 0) dead = scan_fwd_mma3(tbase, sb, c, bars, p.status, dead);
+    if (tid == 0) {
+      dead = scan_fwd_mma3(tbase, sb, c, bars, p.status, dead);
+      if (kSave) {
+        bulk_store(p.vn_img + cidx * 16384, sb + sG, 32768);
+        bulk_commit();
+      }
+    }
     wait_or_mark(&mma_bar, mphase, dead, p.status);    // the state update has completed (the output product may still run)
     tc_fence_after();
   }
@@ -398,6 +432,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     form_o(nt - 1);
     store_o(nt - 1);
   }
+  if (kSave && tid == 0) bulk_wait_all();            // every saved panel is in global memory before the CTA ends
   if (!dead && p.ht) {
     float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + k_lo) * p.V + vb * 128 + vrow;
 #pragma unroll

@@ -83,16 +83,40 @@ __device__ __forceinline__ void write_identity_panel(uint8_t* pan, int tid, int 
   }
 }
 
-// A [64 tokens][128 channels] tile staged in shared memory (row_bytes per token) leaves for global memory as 16-byte
-// pieces of rows; `rows` tokens are valid.  Two-byte stores scattered over tokens, which is what each thread's own
-// data would need, cost several thousand cycles per chunk.
-template <int kRowBytes>
+// A [kRows tokens][128 channels] tile staged in shared memory (kRowBytes per token) leaves for global memory as 16-byte
+// pieces of rows; the first `rows` tokens are valid.  Two-byte stores scattered over tokens, which is what each
+// thread's own data would need, cost several thousand cycles per chunk.
+template <int kRowBytes, int kRows>
 __device__ __forceinline__ void copy_out_tile(const uint8_t* tile, uint8_t* gbase, int64_t g_row_bytes, int rows, int tid) {
-  constexpr int kPerRow = kRowBytes / 16, kIters = kC * kPerRow / kScanEpiThreads;
+  constexpr int kPerRow = kRowBytes / 16, kIters = kRows * kPerRow / kScanEpiThreads;
 #pragma unroll
   for (int i = 0; i < kIters; ++i) {
     const int id = tid + i * kScanEpiThreads, r = id / kPerRow, c16 = id % kPerRow;
     if (r < rows) *reinterpret_cast<uint4*>(gbase + r * g_row_bytes + c16 * 16) = *reinterpret_cast<const uint4*>(tile + r * kRowBytes + c16 * 16);
+  }
+}
+
+// Each epilogue thread holds one channel (`vrow`) of 32 tokens (t_lo .. t_lo + 31) of a [64 tokens][128 channels] result.
+// The tile is transposed through a 16 KB shared-memory buffer: bf16 results in one pass, fp32 results in two (the 32
+// tokens of each half of the warps).  `g` points at the chunk's first token, channel 0 of this block.
+__device__ __forceinline__ void store_rows_transposed(uint8_t* tile, const float* ov, void* g, int64_t g_row_elems, bool f32, int rows,
+                                                      int half, int vrow, int tid) {
+  if (f32) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (half == h) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) *reinterpret_cast<float*>(tile + i * 512 + vrow * 4) = ov[i];
+      }
+      epi_sync();
+      copy_out_tile<512, 32>(tile, reinterpret_cast<uint8_t*>(static_cast<float*>(g) + h * 32 * g_row_elems), g_row_elems * 4, rows - h * 32, tid);
+      epi_sync();
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) *reinterpret_cast<bf16*>(tile + (half * 32 + i) * 256 + vrow * 2) = __float2bfloat16_rn(ov[i]);
+    epi_sync();
+    copy_out_tile<256, 64>(tile, static_cast<uint8_t*>(g), g_row_elems * 2, rows, tid);
   }
 }
 
