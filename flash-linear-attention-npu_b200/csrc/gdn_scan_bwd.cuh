@@ -312,9 +312,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     tc_fence_before();
     scan_sync();                                   // sync 1
     tc_fence_after();
-    if (tid == 0) dead = scan_bwd_mma1(tbase, sb, s, bars, p.status, dead);
+    if (tid == 0) {
+      dead = scan_bwd_mma1(tbase, sb, s, bars, p.status, dead);
+      bulk_wait_read();                            // the [dO^T | dZ^T] image of the previous step has left the staging panels
+    }
     // ---- while W1 / U1 run: the dS' image for the chunk-parallel kernel, through the staging panels and one bulk copy
     {
+      epi_sync();
       uint8_t* stg = smem + bG;
       uint32_t w[16];
 #pragma unroll
@@ -363,13 +367,16 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       }
       tmem_st_wait();
     }
-    if (tid == 0) bulk_wait_read();                // the dS' image has left the staging panels
     tc_fence_before();
     scan_sync();                                   // sync 2
     tc_fence_after();
-    if (tid == 0) dead = scan_bwd_mma2(tbase, sb, s, bars, p.status, dead);
+    if (tid == 0) {
+      dead = scan_bwd_mma2(tbase, sb, s, bars, p.status, dead);
+      bulk_wait_read();                            // the dS' image has left the staging panels
+    }
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
+    epi_sync();
 
     // ---- C: dZ^T -> dV rows, partial sums of dZ V, the [dO^T | dZ^T] image, the operand [scale e^gam dO^T | -beta e^gam dZ^T]
     {
@@ -433,7 +440,6 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     store_dv(c);                                   // while the state-gradient update runs
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
-    if (tid == 0) bulk_wait_read();                // the [dO^T | dZ^T] image has left the staging panels
   }
   if (tid == 0) bulk_wait_all();                   // every saved panel is in global memory before the CTA ends
 

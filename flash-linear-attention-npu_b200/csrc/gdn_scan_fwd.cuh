@@ -312,14 +312,17 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       tc_fence_after();
       form_o(c - 1);
     }
-    if (kSave && tid == 0) bulk_wait_read();       // the v_new image of chunk c - 1 has left the staging panels
     tc_fence_before();
     scan_sync();                                   // sync 1
     tc_fence_after();
-    if (tid == 0) dead = scan_fwd_mma1(tbase, sb, c, bars, p.status, dead);
+    if (tid == 0) {
+      dead = scan_fwd_mma1(tbase, sb, c, bars, p.status, dead);
+      if (kSave) bulk_wait_read();                 // the v_new image of chunk c - 1 has left the staging panels
+    }
     // ---- while [QS^T | KS^T] runs: output rows of chunk c - 1, saved state image
     if (c > 0) store_o(c - 1);
     if (kSave) {
+      epi_sync();                                  // ... and every thread knows it
       // The state image: every thread copies its row of the operand just published (value, residual: 2 x 128 bytes)
       // from tensor memory into the staging panels; one bulk copy then moves the 64 KB to global memory.  Stores made
       // by the threads themselves would be 16-byte pieces 128 bytes apart: measured 0.4 ms per launch.
@@ -370,13 +373,16 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       }
       tmem_st_wait();
     }
-    if (kSave && tid == 0) bulk_wait_read();       // the state image has left the staging panels
     tc_fence_before();
     scan_sync();                                   // sync 2
     tc_fence_after();
-    if (tid == 0) dead = scan_fwd_mma2(tbase, sb, c, bars, p.status, dead);
+    if (tid == 0) {
+      dead = scan_fwd_mma2(tbase, sb, c, bars, p.status, dead);
+      if (kSave) bulk_wait_read();                 // the state image has left the staging panels
+    }
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
+    if (kSave) epi_sync();
 
     // ---- E: v_new^T (rows past the end of the sequence are zero) and its decayed copy
     {
