@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       scan_sync();                                          // sync 1
       if (lane == 0) {
         if (more) load_qk(s + 1);
-        wait_or_mark(&mma_bar, mphase, dead, p.status);     // the first batch of products has read P
+        lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // the first batch of products has read P
         if (more) load_p(s + 1);
       }
       __syncwarp();
@@ -230,12 +230,12 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       load_scalars(s + 2);
       scan_sync();                                          // sync 2
       if (lane == 0) {
-        wait_or_mark(&mma_bar, mphase, dead, p.status);     // the second batch has read X and the dO, v rows
+        lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // the second batch has read X and the dO, v rows
         if (more) load_xvd(s + 1);
       }
       __syncwarp();
       scan_sync();                                          // sync 3
-      if (lane == 0) wait_or_mark(&mma_bar, mphase, dead, p.status);
+      if (lane == 0) lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);
       __syncwarp();
     }
     scan_sync();

@@ -42,45 +42,59 @@ constexpr uint32_t sO = 106496;              // 16 KB: the chunk's output rows o
 constexpr uint32_t sI = 122880;              // 8 KB: identity panel
 constexpr uint32_t sG = 131072;              // 64 KB: the saved panels of a chunk on their way out (state image, then v_new image)
 constexpr uint32_t kScanFwdSmem = 196608;
+constexpr uint32_t sX2 = sG, sP2 = sG + 8192, sV2 = sG + 24576;   // second buffers (forward without saving only)
 
 struct ScanBars {
-  uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;
+  uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;   // x / p / v: two barriers each (index = buffer)
+};
+// Where chunk c finds its X, P and v rows.  While saving for the backward the staging panels take the space of the
+// second buffers: there is one buffer, used by every chunk (barrier parity = chunk parity).  Otherwise there are two
+// (the second set lies in the staging area) and chunk c uses buffer c & 1 (parity (c >> 1) & 1).
+template <bool kSave>
+struct ScanBuf {
+  __device__ static int buf(int c) { return kSave ? 0 : (c & 1); }
+  __device__ static uint32_t par(int c) { return kSave ? uint32_t(c & 1) : uint32_t((c >> 1) & 1); }
 };
 // The three batches of products of one chunk, each issued by one thread.  Kept out of line: inlined into the epilogue
 // code their unrolled descriptor arithmetic costs registers the accumulator rows need.
+template <bool kSave>
 __device__ __noinline__ bool scan_fwd_mma1(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
-  const int b = c & 1;
-  const uint32_t ph = (c >> 1) & 1;
+  const int b = c & 1, xb = ScanBuf<kSave>::buf(c);
+  const uint32_t ph = (c >> 1) & 1, xph = ScanBuf<kSave>::par(c);
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.qk_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opKQ{sb + sQK + b * 32768, 16384, 0};
   mma_tile_ts(tbase + tKQ, tbase + tSAh, opKQ, 128, 8, false);
   mma_tile_ts(tbase + tKQ, tbase + tSAl, opKQ, 128, 8, true);
   // V^T into the columns the decayed v_new of this chunk will occupy later
-  if (!dead && !mbar_wait(bars.v_bar, c & 1, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opVt{sb + sV, 8192, 1}, opI{sb + sI, 8192, 0};
+  if (!dead && !mbar_wait(&bars.v_bar[xb], xph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opVt{sb + (xb ? sV2 : sV), 8192, 1}, opI{sb + sI, 8192, 0};
   mma_tile(tbase + tVAh, opVt, opI, 128, 64, 4, false);
   mma_commit(bars.mma_bar);
   return dead;
 }
+template <bool kSave>
 __device__ __noinline__ bool scan_fwd_mma2(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
+  const int xb = ScanBuf<kSave>::buf(c);
   tc_fence_after();
-  if (!dead && !mbar_wait(bars.x_bar, c & 1, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opX{sb + sX, 8192, 0};
+  if (!dead && !mbar_wait(&bars.x_bar[xb], ScanBuf<kSave>::par(c), status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opX{sb + (xb ? sX2 : sX), 8192, 0};
   mma_tile_ts(tbase + tVN, tbase + tZAh, opX, 64, 4, false);
   mma_tile_ts(tbase + tVN, tbase + tZAl, opX, 64, 4, true);
   mma_commit(bars.mma_bar);
   return dead;
 }
+template <bool kSave>
 __device__ __noinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
-  const int b = c & 1;
+  const int b = c & 1, xb = ScanBuf<kSave>::buf(c);
   tc_fence_after();
   const Operand opK{sb + sQK + b * 32768 + 8192, 16384, 1};   // k rows: reduction over tokens, N = 128 key dims over two panels
   mma_tile_ts(tbase + tST, tbase + tVAh, opK, 128, 4, true);
   mma_tile_ts(tbase + tST, tbase + tVAl, opK, 128, 4, true);
   mma_commit(bars.mma_bar);                                   // the state update: what the next chunk waits for
-  if (!dead && !mbar_wait(bars.p_bar, c & 1, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opPh{sb + sP, 8192, 0}, opPl{sb + sP + 8192, 8192, 0};
+  if (!dead && !mbar_wait(&bars.p_bar[xb], ScanBuf<kSave>::par(c), status, FLA_ERR_TIMEOUT)) dead = true;
+  const uint32_t pp = sb + (xb ? sP2 : sP);
+  const Operand opPh{pp, 8192, 0}, opPl{pp + 8192, 8192, 0};
   mma_tile_ts(tbase + tVN, tbase + tZAh, opPh, 64, 4, false);
   mma_tile_ts(tbase + tVN, tbase + tZAl, opPh, 64, 4, true);
   mma_tile_ts(tbase + tVN, tbase + tZAh, opPl, 64, 4, true);
@@ -97,7 +111,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ ScanFactors fac[3];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar, o_bar, qk_bar[2], x_bar, p_bar, v_bar;
+  __shared__ __align__(8) uint64_t mma_bar, o_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2];
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -113,11 +127,12 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
     mbar_init(&o_bar, 1);
-    mbar_init(&qk_bar[0], 1);
-    mbar_init(&qk_bar[1], 1);
-    mbar_init(&x_bar, 1);
-    mbar_init(&p_bar, 1);
-    mbar_init(&v_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qk_bar[i], 1);
+      mbar_init(&x_bar[i], 1);
+      mbar_init(&p_bar[i], 1);
+      mbar_init(&v_bar[i], 1);
+    }
     mbar_init_fence();
   }
   write_identity_panel(smem + sI, tid, kScanThreads);
@@ -140,18 +155,21 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       tma_load_tile(qk + 16384 + 8192, &tm_k, 64, hk, row0, &qk_bar[b]);
     };
     auto load_v = [&](int c) {
-      const int row0 = sq.bos + c * kC;
-      mbar_arrive_expect_tx(&v_bar, 16384);
-      tma_load_tile(sb + sV, &tm_v, vb * 128, hv, row0, &v_bar);
-      tma_load_tile(sb + sV + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar);
+      const int row0 = sq.bos + c * kC, xb = ScanBuf<kSave>::buf(c);
+      const uint32_t dst = sb + (xb ? sV2 : sV);
+      mbar_arrive_expect_tx(&v_bar[xb], 16384);
+      tma_load_tile(dst, &tm_v, vb * 128, hv, row0, &v_bar[xb]);
+      tma_load_tile(dst + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[xb]);
     };
     auto load_x = [&](int c) {
-      mbar_arrive_expect_tx(&x_bar, 8192);
-      tma_load_tile(sb + sX, &tm_x, 0, hv, sq.bos + c * kC, &x_bar);
+      const int xb = ScanBuf<kSave>::buf(c);
+      mbar_arrive_expect_tx(&x_bar[xb], 8192);
+      tma_load_tile(sb + (xb ? sX2 : sX), &tm_x, 0, hv, sq.bos + c * kC, &x_bar[xb]);
     };
     auto load_p = [&](int c) {
-      mbar_arrive_expect_tx(&p_bar, 16384);
-      bulk_load(sb + sP, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar);
+      const int xb = ScanBuf<kSave>::buf(c);
+      mbar_arrive_expect_tx(&p_bar[xb], 16384);
+      bulk_load(sb + (xb ? sP2 : sP), p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[xb]);
     };
     // lane l handles tokens l and l + 32; the raw values of a chunk are requested two chunks ahead and wait in registers
     float pf_g[2] = {0.f, 0.f}, pf_b[2] = {0.f, 0.f}, pf_gl = 0.f;
@@ -207,23 +225,34 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       scan_sync();                                          // sync 1: chunk c - 1 no longer reads the other [q; k] buffer
       if (lane == 0) {
         if (more) load_qk(c + 1);
-        wait_or_mark(&mma_bar, mphase, dead, p.status);     // the first batch of products has read the v rows
-        if (more) load_v(c + 1);
+        if (!kSave && more) {                               // two buffers: chunk c - 1, their last reader, has completed
+          load_v(c + 1);
+          load_x(c + 1);
+          load_p(c + 1);
+        }
+        if (kSave) {
+          lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // the first batch of products has read the v rows
+          if (more) load_v(c + 1);
+        }
       }
       __syncwarp();
       make_factors(c + 1);                                  // read from sync 3 of this chunk on
       load_scalars(c + 2);
       scan_sync();                                          // sync 2
       if (lane == 0) {
-        wait_or_mark(&mma_bar, mphase, dead, p.status);     // X has been read
-        if (more) load_x(c + 1);
+        if (kSave) {
+          lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // X has been read
+          if (more) load_x(c + 1);
+        }
       }
       __syncwarp();
       scan_sync();                                          // sync 3
       if (lane == 0) {
-        wait_or_mark(&mma_bar, mphase, dead, p.status);
-        wait_or_mark(&o_bar, ophase, dead, p.status);       // the output product has read P
-        if (more) load_p(c + 1);
+        if (kSave) {
+          lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);
+          lazy_wait_or_mark(&o_bar, ophase, dead, p.status);     // the output product has read P
+          if (more) load_p(c + 1);
+        }
       }
       __syncwarp();
     }
@@ -232,7 +261,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   }
 
   // ================================================================ epilogue warps
-  const ScanBars bars{&mma_bar, &o_bar, qk_bar, &x_bar, &p_bar, &v_bar};
+  const ScanBars bars{&mma_bar, &o_bar, qk_bar, x_bar, p_bar, v_bar};
   const int quad = warp & 3, half = warp >> 2;
   const int vrow = quad * 32 + lane;                       // my value channel inside the block = my TMEM lane
   const uint32_t tlane = tmem_addr(tbase, quad * 32, 0);
@@ -316,7 +345,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     scan_sync();                                   // sync 1
     tc_fence_after();
     if (tid == 0) {
-      dead = scan_fwd_mma1(tbase, sb, c, bars, p.status, dead);
+      dead = scan_fwd_mma1<kSave>(tbase, sb, c, bars, p.status, dead);
       if (kSave) bulk_wait_read();                 // the v_new image of chunk c - 1 has left the staging panels
     }
     // ---- while [QS^T | KS^T] runs: output rows of chunk c - 1, saved state image
@@ -377,7 +406,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     scan_sync();                                   // sync 2
     tc_fence_after();
     if (tid == 0) {
-      dead = scan_fwd_mma2(tbase, sb, c, bars, p.status, dead);
+      dead = scan_fwd_mma2<kSave>(tbase, sb, c, bars, p.status, dead);
       if (kSave) bulk_wait_read();                 // the state image has left the staging panels
     }
     wait_or_mark(&mma_bar, mphase, dead, p.status);
@@ -422,7 +451,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     scan_sync();                                   // sync 3
     tc_fence_after();
     if (tid == 0) {
-      dead = scan_fwd_mma3(tbase, sb, c, bars, p.status, dead);
+      dead = scan_fwd_mma3<kSave>(tbase, sb, c, bars, p.status, dead);
       if (kSave) {
         bulk_store(p.vn_img + cidx * 16384, sb + sG, 32768);
         bulk_commit();

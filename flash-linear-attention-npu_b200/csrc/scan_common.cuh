@@ -63,6 +63,22 @@ __device__ __forceinline__ void pack16(const float* x, uint32_t* w) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) w[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
 }
+// A wait for threads that are in no hurry (the helper warp waiting for a product to release a buffer): sleeps between polls
+// so that it does not compete for issue slots with the epilogue warps of its scheduler.
+__device__ __forceinline__ void lazy_wait_or_mark(uint64_t* bar, uint32_t& phase, bool& dead, int* status) {
+  if (!dead) {
+    bool ok = false;
+    for (uint32_t it = 0; it < (kSpinLimit >> 4) && !ok; ++it) {
+      ok = mbar_try_wait(bar, phase);
+      if (!ok) __nanosleep(64);
+    }
+    if (!ok) {
+      if (status) atomicExch(status, 8 /* FLA_ERR_TIMEOUT */);
+      dead = true;
+    }
+  }
+  phase ^= 1;
+}
 // the 8 epilogue warps + the helper warp
 __device__ __forceinline__ void scan_sync() { __syncthreads(); }
 // the 8 epilogue warps only
