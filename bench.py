@@ -682,9 +682,14 @@ def strong_scaling(bench, wl, K, W, n_streams, ms_full, ms_full_single):
     d = shard_inputs(wl, d_full, b0, b1, h0, h1)
     del d_full
     torch.cuda.empty_cache()
-    ms, ms1 = bench.device_timing(lambda: wl.step(d), K, W, n_streams)
+    # One batch row per GPU leaves the sequential scans with fewer chains than SMs (one CTA per (row, value head, 128
+    # channels of V)); independent steps in flight on more streams fill them, so the stream count follows the shard size.
+    chains = (b1 - b0) * (h1 - h0) * (wl.cfg["HV"] // wl.cfg["HK"]) * (wl.cfg["V"] // 128)
+    s_streams = n_streams if n_streams == 1 else max(n_streams, min(8, -(-296 // max(chains, 1))))
+    ms, ms1 = bench.device_timing(lambda: wl.step(d), K, W, s_streams)
     tokens = wl.tokens_per_step
-    out = {"scaling": "strong", "global_batch": wl.cfg["B"], "partition": how, "ms_per_step": ms,
+    out = {"scaling": "strong", "global_batch": wl.cfg["B"], "partition": how, "streams": s_streams,
+           "scan_chains_per_gpu": chains, "ms_per_step": ms,
            "value": tokens / (ms * 1e-3), "unit": "tokens/s", "speedup_vs_one_gpu": ms_full / ms,
            "efficiency": ms_full / ms / world}
     if ms1 is not None and ms_full_single is not None:

@@ -217,36 +217,52 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
-// A tile operand made of panels (rows x 64 columns each, `panel_stride` bytes apart).
+// A tile operand in shared memory.
+//   mn_major 0 / 1: 128-byte-swizzled panels (rows x 64 columns each, `panel_stride` bytes apart), read with the rows as
+//                   M / N and the columns as the reduction dim (0) or the other way round (1).
+//   mn_major 2:     the un-swizzled "strip" layout [M or N / 8][reduction rows][8 elements = 16 bytes]: the 8 x 16-byte core
+//                   matrices are 128 contiguous bytes, strips are `panel_stride` bytes apart.  A writer whose threads each own
+//                   one reduction row stores a strip piece as 16 bytes per thread at consecutive addresses (coalesced), which
+//                   the swizzled panels cannot offer (their rows are 128 bytes apart).
 struct Operand {
-  uint32_t saddr;         // shared address of panel 0
-  uint32_t panel_stride;  // bytes between panels (rows * 128)
-  int mn_major;           // 0: rows are M/N, columns are the reduction dim; 1: the transpose view
+  uint32_t saddr;         // shared address of the operand
+  uint32_t panel_stride;  // bytes between panels (mn_major 0 / 1) or between strips (2)
+  int mn_major;
 };
 __device__ __forceinline__ uint64_t operand_desc(const Operand& o, int kstep) {
   if (o.mn_major) return desc_mnmajor(o.saddr + kstep * 2048, o.panel_stride);
   return desc_kmajor(o.saddr + (kstep >> 2) * o.panel_stride + (kstep & 3) * 32);
 }
-// Upper 32 bits of every descriptor used here: stride byte offset 1024, descriptor version 1, SWIZZLE_128B.
+// Upper 32 bits of the swizzled descriptors: stride byte offset 1024, descriptor version 1, SWIZZLE_128B.
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
-// Lower 32 bits at k-step 0: start address, and the leading byte offset (panel stride) of MN-major views.
+// Upper 32 bits: swizzled, or (strips) stride byte offset = strip stride, version 1, no swizzle.
+__device__ __forceinline__ uint32_t operand_desc_hi(const Operand& o) {
+  return o.mn_major == 2 ? (((o.panel_stride >> 4) & 0x3FFFu) | (1u << 14)) : kDescHi;
+}
+// Lower 32 bits at k-step 0: start address and leading byte offset (panel stride of swizzled MN-major views; for strips
+// the 128 bytes between groups of 8 reduction rows).
 __device__ __forceinline__ uint32_t operand_desc_lo(const Operand& o) {
-  return ((o.saddr >> 4) & 0x3FFFu) | (o.mn_major ? ((o.panel_stride >> 4) & 0x3FFFu) << 16 : (1u << 16));
+  const uint32_t lbo = o.mn_major == 2 ? (128u >> 4) : (o.mn_major ? ((o.panel_stride >> 4) & 0x3FFFu) : 1u);
+  return ((o.saddr >> 4) & 0x3FFFu) | (lbo << 16);
+}
+// Start-address advance (in 16-byte units) of k-step `ks`
+__device__ __forceinline__ uint32_t operand_kstep(const Operand& o, int ks) {
+  if (o.mn_major == 2) return uint32_t(ks) * 16u;                       // 16 reduction rows of 16 bytes
+  if (o.mn_major == 1) return uint32_t(ks) * 128u;                      // 16 rows of 128 bytes
+  return uint32_t(ks >> 2) * (o.panel_stride >> 4) + uint32_t(ks & 3) * 2u;
 }
 // D (+)= A * B over `ksteps` MMAs of K = 16 each.  Single-thread call; call with a literal `ksteps` so the
 // loop unrolls.  Issue cost matters (one thread feeds the tensor core): per k-step only the start-address
 // field of each descriptor changes, by a constant, so each MMA costs two integer adds.
 __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N,
                                          int ksteps, bool accumulate) {
-  const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major, b.mn_major);
+  const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major != 0, b.mn_major != 0);
   const uint32_t alo = operand_desc_lo(a), blo = operand_desc_lo(b);
-  const uint32_t aps = a.panel_stride >> 4, bps = b.panel_stride >> 4;
+  const uint32_t ahi = operand_desc_hi(a), bhi = operand_desc_hi(b);
 #pragma unroll
   for (int ks = 0; ks < ksteps; ++ks) {
-    const uint32_t ao = a.mn_major ? uint32_t(ks) * 128u : uint32_t(ks >> 2) * aps + uint32_t(ks & 3) * 2u;
-    const uint32_t bo = b.mn_major ? uint32_t(ks) * 128u : uint32_t(ks >> 2) * bps + uint32_t(ks & 3) * 2u;
-    const uint64_t ad = (uint64_t(kDescHi) << 32) | uint64_t(alo + ao);
-    const uint64_t bd = (uint64_t(kDescHi) << 32) | uint64_t(blo + bo);
+    const uint64_t ad = (uint64_t(ahi) << 32) | uint64_t(alo + operand_kstep(a, ks));
+    const uint64_t bd = (uint64_t(bhi) << 32) | uint64_t(blo + operand_kstep(b, ks));
     mma_ss(d_tmem, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
@@ -254,13 +270,11 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, cons
 // D (+)= A * B over `ksteps` MMAs of K = 16 with A in tensor memory at columns [a_tmem, a_tmem + 8 * ksteps).
 __device__ __forceinline__ void mma_tile_ts(uint32_t d_tmem, uint32_t a_tmem, const Operand& b, int N, int ksteps,
                                             bool accumulate) {
-  const uint32_t idesc = make_idesc_bf16(128, N, 0, b.mn_major);
-  const uint32_t blo = operand_desc_lo(b);
-  const uint32_t bps = b.panel_stride >> 4;
+  const uint32_t idesc = make_idesc_bf16(128, N, 0, b.mn_major != 0);
+  const uint32_t blo = operand_desc_lo(b), bhi = operand_desc_hi(b);
 #pragma unroll
   for (int ks = 0; ks < ksteps; ++ks) {
-    const uint32_t bo = b.mn_major ? uint32_t(ks) * 128u : uint32_t(ks >> 2) * bps + uint32_t(ks & 3) * 2u;
-    const uint64_t bd = (uint64_t(kDescHi) << 32) | uint64_t(blo + bo);
+    const uint64_t bd = (uint64_t(bhi) << 32) | uint64_t(blo + operand_kstep(b, ks));
     mma_ts(d_tmem, a_tmem + uint32_t(ks) * 8u, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }

@@ -60,9 +60,9 @@ constexpr int64_t kDzImg = 8192;   // per (chunk, head, block): 64x64 dO + 64x64
 
 // ============================================================================================= par
 constexpr uint32_t rOffQK = 0, rQKPanel = 16384;
-constexpr uint32_t rOffAH = 32768;             // [dO ; dZ_hi] rows of one V block (128 rows)
-// 49152 .. 65535: 16 KB whose contents do not matter (rows 0-63 of the Vn-as-A operand, which starts 8 KB before rOffVNH)
-constexpr uint32_t rOffVNH = 65536, rOffVNL = 73728;
+constexpr uint32_t rOffAH = 49152;             // [dO^T | dZ^T] strips of one 64-channel step (16 KB); the 16 KB before them are unused
+constexpr uint32_t rOffVNH = 65536, rOffVNL = 73728;   // v_new^T value / residual strips; as an A operand with valid rows 64..127 the
+                                                       // view starts 8 KB earlier, inside the dZ^T strips (any finite contents do)
 constexpr uint32_t rOffSH = 81920, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 131072;
 constexpr uint32_t rOffPAH = 147456, rOffPAL = 163840;   // [dP ; dAt] hi / lo (128 rows x 64)
 constexpr uint32_t kParSmem = 180224;
@@ -116,25 +116,16 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     tmem_relinquish();
   }
   const uint32_t sb = smem_u32(smem);
-  // One thread: operands of one (value head, 64-channel slice of V) step.  The scans store their panels with value
-  // channels as rows (128 per block of V); a step takes the 64 rows of one half of every panel, which are contiguous.
+  // One thread: operands of one (value head, 64-channel half of a block of V) step.  The scans store every saved operand
+  // per half, so a step is four contiguous pieces.
   auto issue_loads = [&](int hv, int vb) {
     const int64_t blk = ((int64_t(sq.cbase) + c) * p.HV + hv) * (NVB / 2) + (vb >> 1);
-    const int64_t half = int64_t(vb & 1) * 4096;                         // elements: 64 rows x 64 columns
-    const bf16* dz = p.dz_img + blk * 16384 + half;                      // [dO^T | dZ^T] panels
-    const bf16* vn = p.vn_img + blk * 16384 + half;                      // [value | residual] panels
-    const bf16* sp = p.s_img + blk * 32768 + half;                       // [value | residual] x [key dims 0-63 | 64-127]
-    const bf16* dp = p.ds_img + blk * 32768 + half;
+    const int64_t hf = vb & 1;
     mbar_arrive_expect_tx(&load_bar, kStepBytes);
-    bulk_load(sb + rOffAH, dz, 8192, &load_bar);
-    bulk_load(sb + rOffAH + 8192, dz + 8192, 8192, &load_bar);
-    bulk_load(sb + rOffVNH, vn, 8192, &load_bar);
-    bulk_load(sb + rOffVNL, vn + 8192, 8192, &load_bar);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {                                         // panels in stored order: value kd 0-63, 64-127, residual ...
-      bulk_load(sb + rOffSH + i * 8192, sp + i * 8192, 8192, &load_bar);
-      bulk_load(sb + rOffDSH + i * 8192, dp + i * 8192, 8192, &load_bar);
-    }
+    bulk_load(sb + rOffAH, p.dz_img + blk * 16384 + hf * 8192, 16384, &load_bar);      // [dO^T | dZ^T] strips
+    bulk_load(sb + rOffVNH, p.vn_img + blk * 16384 + hf * 8192, 16384, &load_bar);     // [value | residual]
+    bulk_load(sb + rOffSH, p.s_img + blk * 32768 + hf * 16384, 32768, &load_bar);      // [value | residual], 16 strips each
+    bulk_load(sb + rOffDSH, p.ds_img + blk * 32768 + hf * 16384, 32768, &load_bar);
   };
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
@@ -171,12 +162,12 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   const Operand opKb{sb + rOffQK + 8192, rQKPanel, 0};               // k as B, N = 64 tokens
   const Operand opKn{sb + rOffQK + 8192, rQKPanel, 1};               // k as B, N = 128 key dims, reduction over tokens
   const Operand opQKn{sb + rOffQK, rQKPanel, 1};                     // [q; k] as B, N = 128 key dims, reduction over 128 rows
-  // operands of a step: every saved panel has value channels as rows, i.e. the reduction dim of these products runs over rows
-  const Operand opAH{sb + rOffAH, 8192, 1};                                               // [dO; dZ]: M = 128 tokens over two panels
-  const Operand opVNbH{sb + rOffVNH, 8192, 1}, opVNbL{sb + rOffVNL, 8192, 1};            // Vn as B (N = 64 tokens)
-  const Operand opVNaH{sb + rOffVNH - 8192, 8192, 1}, opVNaL{sb + rOffVNL - 8192, 8192, 1};  // Vn as A: accumulator rows 64..127 are valid
-  const Operand opSH{sb + rOffSH, 8192, 1}, opSL{sb + rOffSL, 8192, 1};                  // S block as B (N = 128 key dims over two panels)
-  const Operand opDSH{sb + rOffDSH, 8192, 1}, opDSL{sb + rOffDSL, 8192, 1};
+  // operands of a step: un-swizzled strips (sm100.cuh) whose 64 rows are value channels, the reduction dim of these products
+  const Operand opAH{sb + rOffAH, 1024, 2};                                               // [dO; dZ]: M = 128 tokens = 16 strips
+  const Operand opVNbH{sb + rOffVNH, 1024, 2}, opVNbL{sb + rOffVNL, 1024, 2};            // Vn as B (N = 64 tokens = 8 strips)
+  const Operand opVNaH{sb + rOffVNH - 8192, 1024, 2}, opVNaL{sb + rOffVNL - 8192, 1024, 2};  // Vn as A: accumulator rows 64..127 are valid
+  const Operand opSH{sb + rOffSH, 1024, 2}, opSL{sb + rOffSL, 1024, 2};                  // S block as B (N = 128 key dims = 16 strips)
+  const Operand opDSH{sb + rOffDSH, 1024, 2}, opDSL{sb + rOffDSL, 1024, 2};
   const Operand opPAH{sb + rOffPAH, 16384, 0}, opPAL{sb + rOffPAL, 16384, 0};            // [dP; dAt], reduction over j
   const Operand opPATh{sb + rOffPAH - 8192, 8192, 1}, opPATl{sb + rOffPAL - 8192, 8192, 1};  // its transpose, valid rows 64..127
 

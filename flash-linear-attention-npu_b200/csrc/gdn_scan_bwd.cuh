@@ -11,9 +11,10 @@
 //     dV     = beta dZ;   bz = sum_v dZ V  (partial sums per 32 value channels);   dR = -beta e^gam dZ
 //     dS^T   = e^{gam_L} dS'^T + [scale e^gam dO^T | dR^T] [Q; K]     N = 128 key dims, reduction over 128 rows
 // dO^T and V^T reach tensor memory through identity products.  For the chunk-parallel kernel the scan saves, per
-// (chunk, head, block), operand panels whose rows are value channels:
-//     ds_img  dS' as [value | residual] x [key dims 0-63 | 64-127] x 128 rows (v) x 64 columns   = 64 KB
-//     dz_img  [dO^T | dZ^T] x 128 rows (v) x 64 columns (tokens), one bf16 each                   = 32 KB
+// (chunk, head, block), operands in the un-swizzled strip layout (sm100.cuh) whose rows are value channels, stored by
+// the thread that owns the channel (coalesced):
+//     ds_img  dS' as [64-channel half][value | residual][16 strips of 8 key dims][64 rows x 16 bytes]   = 64 KB
+//     dz_img  [64-channel half][dO^T | dZ^T][8 strips of 8 tokens][64 rows x 16 bytes], one bf16 each    = 32 KB
 #pragma once
 #include "scan_common.cuh"
 
@@ -29,48 +30,47 @@ constexpr uint32_t uDVh = 384;     // dVn^T as A operand: 64 tokens in 32 column
 constexpr uint32_t uDVl = 416;
 constexpr uint32_t uVT = 448;      // V^T (fp32, 64 tokens)
 
-// shared memory: the [q; k] panels exist twice (step parity), every other load buffer once (reloaded as soon as the
-// product that reads it has completed)
+// shared memory: load buffers twice (step parity)
 constexpr uint32_t bQK = 0;                  // 2 x 32 KB
-constexpr uint32_t bX = 65536;               // 8 KB
-constexpr uint32_t bP = 73728;               // 16 KB (value, residual)
-constexpr uint32_t bV = 90112;               // 16 KB: v rows, two 64-column panels of 64 rows
-constexpr uint32_t bD = 106496;              // 16 KB: dO rows, same layout
-constexpr uint32_t bO = 122880;              // 16 KB: dV rows on their way out
-constexpr uint32_t bI = 139264;              // 8 KB: identity panel
-constexpr uint32_t bG = 147456;              // 64 KB: saved panels on their way out (dS' image, then the [dO^T | dZ^T] image)
-constexpr uint32_t kScanBwdSmem = 212992;
+constexpr uint32_t bX = 65536;               // 2 x 8 KB
+constexpr uint32_t bP = 81920;               // 2 x 16 KB (value, residual)
+constexpr uint32_t bV = 114688;              // 2 x 16 KB: v rows, two 64-column panels of 64 rows
+constexpr uint32_t bD = 147456;              // 2 x 16 KB: dO rows, same layout
+constexpr uint32_t bO = 180224;              // 16 KB: dV rows on their way out
+constexpr uint32_t bI = 196608;              // 8 KB: identity panel
+constexpr uint32_t kScanBwdSmem = 204800;
 
 struct ScanBwdBars {
   uint64_t *mma_bar, *qk_bar, *x_bar, *p_bar, *v_bar, *d_bar;
 };
 __device__ __noinline__ bool scan_bwd_mma1(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, int* status, bool dead) {
   const int b = s & 1;
-  const uint32_t ph = (s >> 1) & 1, ph1 = s & 1;
+  const uint32_t ph = (s >> 1) & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.qk_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opK{sb + bQK + b * 32768 + 8192, 16384, 0};          // k rows as B: N = 64 tokens, reduction over key dims
   mma_tile_ts(tbase + uW, tbase + uAh, opK, 64, 8, false);
   mma_tile_ts(tbase + uW, tbase + uAl, opK, 64, 8, true);
-  if (!dead && !mbar_wait(bars.d_bar, ph1, status, FLA_ERR_TIMEOUT)) dead = true;
-  if (!dead && !mbar_wait(bars.p_bar, ph1, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opDt{sb + bD, 8192, 1};                              // dO^T: M = 128 channels over two panels, reduction over tokens
-  const Operand opPh{sb + bP, 8192, 1}, opPl{sb + bP + 8192, 8192, 1};   // P with its rows as the reduction
+  if (!dead && !mbar_wait(&bars.d_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  if (!dead && !mbar_wait(&bars.p_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opDt{sb + bD + b * 16384, 8192, 1};                  // dO^T: M = 128 channels over two panels, reduction over tokens
+  const Operand opPh{sb + bP + b * 16384, 8192, 1}, opPl{sb + bP + b * 16384 + 8192, 8192, 1};   // P with its rows as the reduction
   mma_tile(tbase + uU, opDt, opPh, 128, 64, 4, false);
   mma_tile(tbase + uU, opDt, opPl, 128, 64, 4, true);
   mma_commit(bars.mma_bar);
   return dead;
 }
 __device__ __noinline__ bool scan_bwd_mma2(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, int* status, bool dead) {
-  const uint32_t ph1 = s & 1;
+  const int b = s & 1;
+  const uint32_t ph = (s >> 1) & 1;
   tc_fence_after();
-  if (!dead && !mbar_wait(bars.x_bar, ph1, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opX{sb + bX, 8192, 1};                               // X with its rows as the reduction: X^T dVn
+  if (!dead && !mbar_wait(&bars.x_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opX{sb + bX + b * 8192, 8192, 1};                    // X with its rows as the reduction: X^T dVn
   mma_tile_ts(tbase + uW, tbase + uDVh, opX, 64, 4, false);
   mma_tile_ts(tbase + uW, tbase + uDVl, opX, 64, 4, true);
-  if (!dead && !mbar_wait(bars.v_bar, ph1, status, FLA_ERR_TIMEOUT)) dead = true;
+  if (!dead && !mbar_wait(&bars.v_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opI{sb + bI, 8192, 0};
-  const Operand opDt{sb + bD, 8192, 1}, opVt{sb + bV, 8192, 1};
+  const Operand opDt{sb + bD + b * 16384, 8192, 1}, opVt{sb + bV + b * 16384, 8192, 1};
   mma_tile(tbase + uU, opDt, opI, 128, 64, 4, false);                // dO^T, exact
   mma_tile(tbase + uVT, opVt, opI, 128, 64, 4, false);               // V^T, exact
   mma_commit(bars.mma_bar);
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ ScanFactors fac[3];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar, qk_bar[2], x_bar, p_bar, v_bar, d_bar;
+  __shared__ __align__(8) uint64_t mma_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2], d_bar[2];
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -125,12 +125,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
   }
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
-    mbar_init(&qk_bar[0], 1);
-    mbar_init(&qk_bar[1], 1);
-    mbar_init(&x_bar, 1);
-    mbar_init(&p_bar, 1);
-    mbar_init(&v_bar, 1);
-    mbar_init(&d_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qk_bar[i], 1);
+      mbar_init(&x_bar[i], 1);
+      mbar_init(&p_bar[i], 1);
+      mbar_init(&v_bar[i], 1);
+      mbar_init(&d_bar[i], 1);
+    }
     mbar_init_fence();
   }
   write_identity_panel(smem + bI, tid, kScanThreads);
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
 
   if (warp == 8) {
     // ============================================================ helper warp: TMA loads and per-token factors
-    auto load_qk = [&](int s) {
+    auto issue_loads = [&](int s) {
       const int c = nt - 1 - s, b = s & 1, row0 = sq.bos + c * kC;
       const uint32_t qk = sb + bQK + b * 32768;
       mbar_arrive_expect_tx(&qk_bar[b], 32768);
@@ -152,22 +153,16 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       tma_load_tile(qk + 16384, &tm_q, 64, hk, row0, &qk_bar[b]);
       tma_load_tile(qk + 8192, &tm_k, 0, hk, row0, &qk_bar[b]);
       tma_load_tile(qk + 16384 + 8192, &tm_k, 64, hk, row0, &qk_bar[b]);
-    };
-    auto load_p = [&](int s) {
-      const int c = nt - 1 - s;
-      mbar_arrive_expect_tx(&p_bar, 16384);
-      bulk_load(sb + bP, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar);
-    };
-    auto load_xvd = [&](int s) {
-      const int c = nt - 1 - s, row0 = sq.bos + c * kC;
-      mbar_arrive_expect_tx(&d_bar, 16384);
-      tma_load_tile(sb + bD, &tm_d, vb * 128, hv, row0, &d_bar);
-      tma_load_tile(sb + bD + 8192, &tm_d, vb * 128 + 64, hv, row0, &d_bar);
-      mbar_arrive_expect_tx(&x_bar, 8192);
-      tma_load_tile(sb + bX, &tm_x, 0, hv, row0, &x_bar);
-      mbar_arrive_expect_tx(&v_bar, 16384);
-      tma_load_tile(sb + bV, &tm_v, vb * 128, hv, row0, &v_bar);
-      tma_load_tile(sb + bV + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar);
+      mbar_arrive_expect_tx(&d_bar[b], 16384);
+      tma_load_tile(sb + bD + b * 16384, &tm_d, vb * 128, hv, row0, &d_bar[b]);
+      tma_load_tile(sb + bD + b * 16384 + 8192, &tm_d, vb * 128 + 64, hv, row0, &d_bar[b]);
+      mbar_arrive_expect_tx(&p_bar[b], 16384);
+      bulk_load(sb + bP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
+      mbar_arrive_expect_tx(&x_bar[b], 8192);
+      tma_load_tile(sb + bX + b * 8192, &tm_x, 0, hv, row0, &x_bar[b]);
+      mbar_arrive_expect_tx(&v_bar[b], 16384);
+      tma_load_tile(sb + bV + b * 16384, &tm_v, vb * 128, hv, row0, &v_bar[b]);
+      tma_load_tile(sb + bV + b * 16384 + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[b]);
     };
     float pf_g[2] = {0.f, 0.f}, pf_b[2] = {0.f, 0.f}, pf_gl = 0.f;
     auto load_scalars = [&](int s) {
@@ -205,45 +200,28 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       tma_prefetch_descriptor(&tm_x);
       tma_prefetch_descriptor(&tm_v);
       tma_prefetch_descriptor(&tm_d);
-      if (nt > 0) {
-        load_qk(0);
-        load_p(0);
-        load_xvd(0);
-      }
+      if (nt > 0) issue_loads(0);
     }
     __syncwarp();
     load_scalars(0);
     make_factors(0);
     load_scalars(1);
     scan_sync();   // factors of the first step are visible
-    uint32_t mphase = 0;
     for (int s = 0; s < nt; ++s) {
-      const bool more = s + 1 < nt;
-      scan_sync();                                          // sync 1
-      if (lane == 0) {
-        if (more) load_qk(s + 1);
-        lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // the first batch of products has read P
-        if (more) load_p(s + 1);
-      }
+      scan_sync();                                          // sync 1: step s - 1 no longer reads the other buffers
+      if (lane == 0 && s + 1 < nt) issue_loads(s + 1);
       __syncwarp();
       make_factors(s + 1);
       load_scalars(s + 2);
       scan_sync();                                          // sync 2
-      if (lane == 0) {
-        lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // the second batch has read X and the dO, v rows
-        if (more) load_xvd(s + 1);
-      }
-      __syncwarp();
       scan_sync();                                          // sync 3
-      if (lane == 0) lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);
-      __syncwarp();
     }
     scan_sync();
     return;
   }
 
   // ================================================================ epilogue warps
-  const ScanBwdBars bars{&mma_bar, qk_bar, &x_bar, &p_bar, &v_bar, &d_bar};
+  const ScanBwdBars bars{&mma_bar, qk_bar, x_bar, p_bar, v_bar, d_bar};
   const int quad = warp & 3, half = warp >> 2;
   const int vrow = quad * 32 + lane;
   const uint32_t tlane = tmem_addr(tbase, quad * 32, 0);
@@ -266,7 +244,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
   // are zeroed in shared memory (every other operand meets a zero row of beta or of dVn there).
   if (nt > 0 && sq.len - (nt - 1) * kC < kC) {
     const int rows = sq.len - (nt - 1) * kC;
-    if (!mbar_wait(&d_bar, 0, p.status, FLA_ERR_TIMEOUT)) dead = true;
+    if (!mbar_wait(&d_bar[0], 0, p.status, FLA_ERR_TIMEOUT)) dead = true;
     for (int idx = tid; idx < (kC - rows) * 16; idx += kScanEpiThreads) {
       const int r = rows + idx / 16, pc = idx % 16;
       *reinterpret_cast<uint4*>(smem + bD + (pc >> 3) * 8192 + panel_chunk_off(r, pc & 7)) = make_uint4(0, 0, 0, 0);
@@ -293,6 +271,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     // ---- A: publish dS' (the gradient entering this chunk): bf16 value + residual as A operand, decayed copy as accumulator
     {
       const float dl = f.dl;
+      uint8_t* s_row = reinterpret_cast<uint8_t*>(p.ds_img + cidx * 32768) + (vrow >> 6) * 32768 + (vrow & 63) * 16;
 #pragma unroll
       for (int g4 = 0; g4 < 4; ++g4) {
         float s16[16];
@@ -302,6 +281,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
         split16(s16, hi, lo);
         tmem_st8u(tlane + uAh + half * 32 + g4 * 8, hi);
         tmem_st8u(tlane + uAl + half * 32 + g4 * 8, lo);
+        {   // the dS' image for the chunk-parallel kernel: strips half * 8 + g4 * 2 and the next one of my channel's row
+          uint8_t* dst = s_row + (half * 8 + g4 * 2) * 1024;
+          *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(dst + 1024) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+          *reinterpret_cast<uint4*>(dst + 16384) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4*>(dst + 16384 + 1024) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) s16[i] *= dl;
         tmem_st16(tlane + uDS + k_lo + g4 * 16, s16);
@@ -312,32 +298,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     tc_fence_before();
     scan_sync();                                   // sync 1
     tc_fence_after();
-    if (tid == 0) {
-      dead = scan_bwd_mma1(tbase, sb, s, bars, p.status, dead);
-      bulk_wait_read();                            // the [dO^T | dZ^T] image of the previous step has left the staging panels
-    }
-    // ---- while W1 / U1 run: the dS' image for the chunk-parallel kernel, through the staging panels and one bulk copy
-    {
-      epi_sync();
-      uint8_t* stg = smem + bG;
-      uint32_t w[16];
-#pragma unroll
-      for (int part = 0; part < 4; ++part) {
-        tmem_ld16u(tlane + ((part < 2) ? uAh : uAl) + half * 32 + (part & 1) * 16, w);
-        tmem_ld_wait();
-        uint8_t* dst = stg + (part < 2 ? 0 : 32768) + half * 16384;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(dst + panel_chunk_off(vrow, (part & 1) * 4 + ch)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
-      }
-      fence_async_smem();
-      epi_sync();
-      if (tid == 0) {
-        bulk_store(p.ds_img + cidx * 32768, sb + bG, 32768);
-        bulk_store(p.ds_img + cidx * 32768 + 16384, sb + bG + 32768, 32768);
-        bulk_commit();
-      }
-    }
+    if (tid == 0) dead = scan_bwd_mma1(tbase, sb, s, bars, p.status, dead);
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
 
@@ -370,17 +331,14 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     tc_fence_before();
     scan_sync();                                   // sync 2
     tc_fence_after();
-    if (tid == 0) {
-      dead = scan_bwd_mma2(tbase, sb, s, bars, p.status, dead);
-      bulk_wait_read();                            // the dS' image has left the staging panels
-    }
+    if (tid == 0) dead = scan_bwd_mma2(tbase, sb, s, bars, p.status, dead);
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
-    epi_sync();
 
     // ---- C: dZ^T -> dV rows, partial sums of dZ V, the [dO^T | dZ^T] image, the operand [scale e^gam dO^T | -beta e^gam dZ^T]
     {
-      uint8_t* img = smem + bG;                    // the [dO^T | dZ^T] image is assembled in the staging panels
+      // the [dO^T | dZ^T] image: my channel's row of strips half * 4 + g * 2 and the next one
+      uint8_t* img = reinterpret_cast<uint8_t*>(p.dz_img + cidx * 16384) + (vrow >> 6) * 16384 + (vrow & 63) * 16;
       float pr[32];
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
@@ -392,8 +350,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
         for (int i = 0; i < 16; ++i) pr[g * 16 + i] = dz[i] * t16[i];
         uint32_t w8[8];
         pack16(dz, w8);
-        *reinterpret_cast<uint4*>(img + 16384 + panel_chunk_off(vrow, half * 4 + g * 2)) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-        *reinterpret_cast<uint4*>(img + 16384 + panel_chunk_off(vrow, half * 4 + g * 2 + 1)) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+        *reinterpret_cast<uint4*>(img + 8192 + (half * 4 + g * 2) * 1024) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+        *reinterpret_cast<uint4*>(img + 8192 + (half * 4 + g * 2 + 1) * 1024) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
 #pragma unroll
         for (int i4 = 0; i4 < 16; i4 += 4) {
           const float4 b4 = *reinterpret_cast<const float4*>(&f.b[t_lo + g * 16 + i4]);
@@ -410,8 +368,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
         tmem_ld16(tlane + uU + t_lo + g * 16, t16);       // dO^T
         tmem_ld_wait();
         pack16(t16, w8);                                  // exact: these are the bf16 inputs
-        *reinterpret_cast<uint4*>(img + panel_chunk_off(vrow, half * 4 + g * 2)) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-        *reinterpret_cast<uint4*>(img + panel_chunk_off(vrow, half * 4 + g * 2 + 1)) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+        *reinterpret_cast<uint4*>(img + (half * 4 + g * 2) * 1024) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+        *reinterpret_cast<uint4*>(img + (half * 4 + g * 2 + 1) * 1024) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
 #pragma unroll
         for (int i4 = 0; i4 < 16; i4 += 4) {
           const float4 s4 = *reinterpret_cast<const float4*>(&f.se[t_lo + g * 16 + i4]);
@@ -428,20 +386,14 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       if (t_lo + lane < rows)
         p.bz[(int64_t(vb * 4 + quad) * p.total_tokens + int64_t(sq.bos) + c * kC + t_lo + lane) * p.HV + hv] = bzsum;
     }
-    fence_async_smem();
     tc_fence_before();
     scan_sync();                                   // sync 3
     tc_fence_after();
-    if (tid == 0) {
-      dead = scan_bwd_mma3(tbase, sb, s, bars, dead);
-      bulk_store(p.dz_img + cidx * 16384, sb + bG, 32768);
-      bulk_commit();
-    }
+    if (tid == 0) dead = scan_bwd_mma3(tbase, sb, s, bars, dead);
     store_dv(c);                                   // while the state-gradient update runs
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
   }
-  if (tid == 0) bulk_wait_all();                   // every saved panel is in global memory before the CTA ends
 
   if (!dead && p.dh0) {
     float* dst = p.dh0 + ((int64_t(n) * p.HV + hv) * kK + k_lo) * p.V + vb * 128 + vrow;

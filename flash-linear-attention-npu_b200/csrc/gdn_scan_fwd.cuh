@@ -11,10 +11,12 @@
 //     o^T     = scale (e^gam QS^T + v_new^T P^T)
 // Operands the result is sensitive to (state copy, Z, v_new, vhat, P) are a bf16 value plus a bf16 residual and enter
 // two or three products; q, k, v enter as the exact bf16 inputs; accumulation is fp32.
-// For the backward the kernel saves, per (chunk, head, block), the state and v_new as ready-made operand panels
-// whose rows are value channels:
-//     s_img   [value | residual] x [key dims 0-63 | 64-127] x 128 rows (v) x 64 columns   = 64 KB
-//     vn_img  [value | residual] x 128 rows (v) x 64 columns (tokens)                      = 32 KB
+// For the backward the kernel saves, per (chunk, head, block), the state and v_new as ready-made operands in the
+// un-swizzled strip layout (sm100.cuh), rows = value channels: a thread owns one channel, so the 16 bytes it stores for a
+// strip lie next to its neighbours' (512 contiguous bytes per warp store).  Swizzled panels, whose rows are 128 bytes
+// apart, had to be staged in shared memory and written by bulk copies: 0.83 ms per launch against 0.7x ms.
+//     s_img   [64-channel half][value | residual][16 strips of 8 key dims][64 rows x 16 bytes]   = 64 KB
+//     vn_img  [64-channel half][value | residual][8 strips of 8 tokens][64 rows x 16 bytes]      = 32 KB
 #pragma once
 #include "scan_common.cuh"
 
@@ -31,69 +33,54 @@ constexpr uint32_t tZAl = 416;
 constexpr uint32_t tVAh = 448;     // V^T (fp32, 64 columns) until Z is built, then the decayed v_new^T as A operand
 constexpr uint32_t tVAl = 480;
 
-// shared memory (offsets from a 1024-byte aligned base).  The [q; k] panels exist twice (chunk parity): k is read by the
-// last product of a chunk and q, k of the next chunk by the first one right after.  X, P and the v rows have one buffer
-// each: they are reloaded as soon as the product that reads them has completed, most of a chunk before their next use.
+// shared memory (offsets from a 1024-byte aligned base); the load buffers exist twice (chunk parity)
 constexpr uint32_t sQK = 0;                  // 2 x 32 KB: [q; k] rows, two 64-column panels of 128 rows
-constexpr uint32_t sX = 65536;               // 8 KB
-constexpr uint32_t sP = 73728;               // 16 KB (value, residual)
-constexpr uint32_t sV = 90112;               // 16 KB: v rows of the chunk, two 64-column panels of 64 rows
-constexpr uint32_t sO = 106496;              // 16 KB: the chunk's output rows on their way out
-constexpr uint32_t sI = 122880;              // 8 KB: identity panel
-constexpr uint32_t sG = 131072;              // 64 KB: the saved panels of a chunk on their way out (state image, then v_new image)
-constexpr uint32_t kScanFwdSmem = 196608;
-constexpr uint32_t sX2 = sG, sP2 = sG + 8192, sV2 = sG + 24576;   // second buffers (forward without saving only)
+constexpr uint32_t sX = 65536;               // 2 x 8 KB
+constexpr uint32_t sP = 81920;               // 2 x 16 KB (value, residual)
+constexpr uint32_t sV = 114688;              // 2 x 16 KB: v rows of the chunk, two 64-column panels of 64 rows
+constexpr uint32_t sO = 147456;              // 16 KB: the chunk's output rows on their way out
+constexpr uint32_t sI = 163840;              // 8 KB: identity panel
+constexpr uint32_t kScanFwdSmem = 172032;
 
 struct ScanBars {
-  uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;   // x / p / v: two barriers each (index = buffer)
-};
-// Where chunk c finds its X, P and v rows.  While saving for the backward the staging panels take the space of the
-// second buffers: there is one buffer, used by every chunk (barrier parity = chunk parity).  Otherwise there are two
-// (the second set lies in the staging area) and chunk c uses buffer c & 1 (parity (c >> 1) & 1).
-template <bool kSave>
-struct ScanBuf {
-  __device__ static int buf(int c) { return kSave ? 0 : (c & 1); }
-  __device__ static uint32_t par(int c) { return kSave ? uint32_t(c & 1) : uint32_t((c >> 1) & 1); }
+  uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;   // two barriers each (index = chunk parity) but the first two
 };
 // The three batches of products of one chunk, each issued by one thread.  Kept out of line: inlined into the epilogue
 // code their unrolled descriptor arithmetic costs registers the accumulator rows need.
-template <bool kSave>
 __device__ __noinline__ bool scan_fwd_mma1(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
-  const int b = c & 1, xb = ScanBuf<kSave>::buf(c);
-  const uint32_t ph = (c >> 1) & 1, xph = ScanBuf<kSave>::par(c);
+  const int b = c & 1;
+  const uint32_t ph = (c >> 1) & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.qk_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opKQ{sb + sQK + b * 32768, 16384, 0};
   mma_tile_ts(tbase + tKQ, tbase + tSAh, opKQ, 128, 8, false);
   mma_tile_ts(tbase + tKQ, tbase + tSAl, opKQ, 128, 8, true);
   // V^T into the columns the decayed v_new of this chunk will occupy later
-  if (!dead && !mbar_wait(&bars.v_bar[xb], xph, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opVt{sb + (xb ? sV2 : sV), 8192, 1}, opI{sb + sI, 8192, 0};
+  if (!dead && !mbar_wait(&bars.v_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opVt{sb + sV + b * 16384, 8192, 1}, opI{sb + sI, 8192, 0};
   mma_tile(tbase + tVAh, opVt, opI, 128, 64, 4, false);
   mma_commit(bars.mma_bar);
   return dead;
 }
-template <bool kSave>
 __device__ __noinline__ bool scan_fwd_mma2(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
-  const int xb = ScanBuf<kSave>::buf(c);
+  const int b = c & 1;
   tc_fence_after();
-  if (!dead && !mbar_wait(&bars.x_bar[xb], ScanBuf<kSave>::par(c), status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opX{sb + (xb ? sX2 : sX), 8192, 0};
+  if (!dead && !mbar_wait(&bars.x_bar[b], (c >> 1) & 1, status, FLA_ERR_TIMEOUT)) dead = true;
+  const Operand opX{sb + sX + b * 8192, 8192, 0};
   mma_tile_ts(tbase + tVN, tbase + tZAh, opX, 64, 4, false);
   mma_tile_ts(tbase + tVN, tbase + tZAl, opX, 64, 4, true);
   mma_commit(bars.mma_bar);
   return dead;
 }
-template <bool kSave>
 __device__ __noinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
-  const int b = c & 1, xb = ScanBuf<kSave>::buf(c);
+  const int b = c & 1;
   tc_fence_after();
   const Operand opK{sb + sQK + b * 32768 + 8192, 16384, 1};   // k rows: reduction over tokens, N = 128 key dims over two panels
   mma_tile_ts(tbase + tST, tbase + tVAh, opK, 128, 4, true);
   mma_tile_ts(tbase + tST, tbase + tVAl, opK, 128, 4, true);
   mma_commit(bars.mma_bar);                                   // the state update: what the next chunk waits for
-  if (!dead && !mbar_wait(&bars.p_bar[xb], ScanBuf<kSave>::par(c), status, FLA_ERR_TIMEOUT)) dead = true;
-  const uint32_t pp = sb + (xb ? sP2 : sP);
+  if (!dead && !mbar_wait(&bars.p_bar[b], (c >> 1) & 1, status, FLA_ERR_TIMEOUT)) dead = true;
+  const uint32_t pp = sb + sP + b * 16384;
   const Operand opPh{pp, 8192, 0}, opPl{pp + 8192, 8192, 0};
   mma_tile_ts(tbase + tVN, tbase + tZAh, opPh, 64, 4, false);
   mma_tile_ts(tbase + tVN, tbase + tZAl, opPh, 64, 4, true);
@@ -154,22 +141,15 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       tma_load_tile(qk + 8192, &tm_k, 0, hk, row0, &qk_bar[b]);
       tma_load_tile(qk + 16384 + 8192, &tm_k, 64, hk, row0, &qk_bar[b]);
     };
-    auto load_v = [&](int c) {
-      const int row0 = sq.bos + c * kC, xb = ScanBuf<kSave>::buf(c);
-      const uint32_t dst = sb + (xb ? sV2 : sV);
-      mbar_arrive_expect_tx(&v_bar[xb], 16384);
-      tma_load_tile(dst, &tm_v, vb * 128, hv, row0, &v_bar[xb]);
-      tma_load_tile(dst + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[xb]);
-    };
-    auto load_x = [&](int c) {
-      const int xb = ScanBuf<kSave>::buf(c);
-      mbar_arrive_expect_tx(&x_bar[xb], 8192);
-      tma_load_tile(sb + (xb ? sX2 : sX), &tm_x, 0, hv, sq.bos + c * kC, &x_bar[xb]);
-    };
-    auto load_p = [&](int c) {
-      const int xb = ScanBuf<kSave>::buf(c);
-      mbar_arrive_expect_tx(&p_bar[xb], 16384);
-      bulk_load(sb + (xb ? sP2 : sP), p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[xb]);
+    auto load_rest = [&](int c) {
+      const int b = c & 1, row0 = sq.bos + c * kC;
+      mbar_arrive_expect_tx(&v_bar[b], 16384);
+      tma_load_tile(sb + sV + b * 16384, &tm_v, vb * 128, hv, row0, &v_bar[b]);
+      tma_load_tile(sb + sV + b * 16384 + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[b]);
+      mbar_arrive_expect_tx(&x_bar[b], 8192);
+      tma_load_tile(sb + sX + b * 8192, &tm_x, 0, hv, row0, &x_bar[b]);
+      mbar_arrive_expect_tx(&p_bar[b], 16384);
+      bulk_load(sb + sP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
     };
     // lane l handles tokens l and l + 32; the raw values of a chunk are requested two chunks ahead and wait in registers
     float pf_g[2] = {0.f, 0.f}, pf_b[2] = {0.f, 0.f}, pf_gl = 0.f;
@@ -209,9 +189,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       tma_prefetch_descriptor(&tm_v);
       if (nt > 0) {
         load_qk(0);
-        load_v(0);
-        load_x(0);
-        load_p(0);
+        load_rest(0);
       }
     }
     __syncwarp();
@@ -219,42 +197,17 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     make_factors(0);
     load_scalars(1);
     scan_sync();   // factors of chunk 0 are visible
-    uint32_t mphase = 0, ophase = 0;
     for (int c = 0; c < nt; ++c) {
-      const bool more = c + 1 < nt;
-      scan_sync();                                          // sync 1: chunk c - 1 no longer reads the other [q; k] buffer
-      if (lane == 0) {
-        if (more) load_qk(c + 1);
-        if (!kSave && more) {                               // two buffers: chunk c - 1, their last reader, has completed
-          load_v(c + 1);
-          load_x(c + 1);
-          load_p(c + 1);
-        }
-        if (kSave) {
-          lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // the first batch of products has read the v rows
-          if (more) load_v(c + 1);
-        }
+      scan_sync();                                          // sync 1: chunk c - 1 no longer reads the other buffers
+      if (lane == 0 && c + 1 < nt) {
+        load_qk(c + 1);
+        load_rest(c + 1);
       }
       __syncwarp();
       make_factors(c + 1);                                  // read from sync 3 of this chunk on
       load_scalars(c + 2);
       scan_sync();                                          // sync 2
-      if (lane == 0) {
-        if (kSave) {
-          lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);   // X has been read
-          if (more) load_x(c + 1);
-        }
-      }
-      __syncwarp();
       scan_sync();                                          // sync 3
-      if (lane == 0) {
-        if (kSave) {
-          lazy_wait_or_mark(&mma_bar, mphase, dead, p.status);
-          lazy_wait_or_mark(&o_bar, ophase, dead, p.status);     // the output product has read P
-          if (more) load_p(c + 1);
-        }
-      }
-      __syncwarp();
     }
     scan_sync();   // matches the epilogue warps' barrier before the TMEM is released
     return;
@@ -317,9 +270,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     const int rows = min(kC, sq.len - c * kC);
     const int64_t cidx = ((int64_t(sq.cbase) + c) * p.HV + hv) * (p.V / 128) + vb;
 
-    // ---- A: publish the state at chunk start: bf16 value + residual as A operand, decayed fp32 copy as accumulator
+    // ---- A: publish the state at chunk start: bf16 value + residual as A operand (and as the saved image), decayed
+    //         fp32 copy as accumulator
     {
       const float dl = f.dl;
+      uint8_t* s_row = kSave ? reinterpret_cast<uint8_t*>(p.s_img + cidx * 32768) + (vrow >> 6) * 32768 + (vrow & 63) * 16 : nullptr;
 #pragma unroll
       for (int g4 = 0; g4 < 4; ++g4) {                   // 16 key dims at a time: 8 packed columns per operand store
         float s16[16];
@@ -329,6 +284,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
         split16(s16, hi, lo);
         tmem_st8u(tlane + tSAh + half * 32 + g4 * 8, hi);
         tmem_st8u(tlane + tSAl + half * 32 + g4 * 8, lo);
+        if (kSave) {   // strips half * 8 + g4 * 2 and the next one of my channel's row
+          uint8_t* dst = s_row + (half * 8 + g4 * 2) * 1024;
+          *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(dst + 1024) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+          *reinterpret_cast<uint4*>(dst + 16384) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4*>(dst + 16384 + 1024) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) s16[i] *= dl;
         tmem_st16(tlane + tST + k_lo + g4 * 16, s16);
@@ -344,36 +306,9 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     tc_fence_before();
     scan_sync();                                   // sync 1
     tc_fence_after();
-    if (tid == 0) {
-      dead = scan_fwd_mma1<kSave>(tbase, sb, c, bars, p.status, dead);
-      if (kSave) bulk_wait_read();                 // the v_new image of chunk c - 1 has left the staging panels
-    }
-    // ---- while [QS^T | KS^T] runs: output rows of chunk c - 1, saved state image
+    if (tid == 0) dead = scan_fwd_mma1(tbase, sb, c, bars, p.status, dead);
+    // ---- while [QS^T | KS^T] runs: output rows of chunk c - 1
     if (c > 0) store_o(c - 1);
-    if (kSave) {
-      epi_sync();                                  // ... and every thread knows it
-      // The state image: every thread copies its row of the operand just published (value, residual: 2 x 128 bytes)
-      // from tensor memory into the staging panels; one bulk copy then moves the 64 KB to global memory.  Stores made
-      // by the threads themselves would be 16-byte pieces 128 bytes apart: measured 0.4 ms per launch.
-      uint8_t* stg = smem + sG;
-      uint32_t w[16];
-#pragma unroll
-      for (int part = 0; part < 4; ++part) {             // my 64 key dims = one panel row = 8 pieces of 16 bytes; 16 columns per load
-        tmem_ld16u(tlane + ((part < 2) ? tSAh : tSAl) + half * 32 + (part & 1) * 16, w);
-        tmem_ld_wait();
-        uint8_t* dst = stg + (part < 2 ? 0 : 32768) + half * 16384;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(dst + panel_chunk_off(vrow, (part & 1) * 4 + ch)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
-      }
-      fence_async_smem();
-      epi_sync();
-      if (tid == 0) {
-        bulk_store(p.s_img + cidx * 32768, sb + sG, 32768);
-        bulk_store(p.s_img + cidx * 32768 + 16384, sb + sG + 32768, 32768);
-        bulk_commit();
-      }
-    }
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
 
@@ -405,13 +340,9 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     tc_fence_before();
     scan_sync();                                   // sync 2
     tc_fence_after();
-    if (tid == 0) {
-      dead = scan_fwd_mma2<kSave>(tbase, sb, c, bars, p.status, dead);
-      if (kSave) bulk_wait_read();                 // the state image has left the staging panels
-    }
+    if (tid == 0) dead = scan_fwd_mma2(tbase, sb, c, bars, p.status, dead);
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
-    if (kSave) epi_sync();
 
     // ---- E: v_new^T (rows past the end of the sequence are zero) and its decayed copy
     {
@@ -426,13 +357,12 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
         split16(vn, hi, lo);
         tmem_st8u(tlane + tZAh + half * 16 + g * 8, hi);
         tmem_st8u(tlane + tZAl + half * 16 + g * 8, lo);
-        if (kSave) {                                 // v_new image (value panel, residual panel) into the staging panels
-          uint8_t* stg = smem + sG;
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
-            *reinterpret_cast<uint4*>(stg + panel_chunk_off(vrow, half * 4 + g * 2 + ch)) = make_uint4(hi[4 * ch], hi[4 * ch + 1], hi[4 * ch + 2], hi[4 * ch + 3]);
-            *reinterpret_cast<uint4*>(stg + 16384 + panel_chunk_off(vrow, half * 4 + g * 2 + ch)) = make_uint4(lo[4 * ch], lo[4 * ch + 1], lo[4 * ch + 2], lo[4 * ch + 3]);
-          }
+        if (kSave) {                                 // v_new image: strips half * 4 + g * 2 and the next one
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.vn_img + cidx * 16384) + (vrow >> 6) * 16384 + (half * 4 + g * 2) * 1024 + (vrow & 63) * 16;
+          *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(dst + 1024) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+          *reinterpret_cast<uint4*>(dst + 8192) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4*>(dst + 8192 + 1024) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
         }
 #pragma unroll
         for (int i4 = 0; i4 < 16; i4 += 4) {
@@ -446,17 +376,10 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       }
       tmem_st_wait();
     }
-    if (kSave) fence_async_smem();
     tc_fence_before();
     scan_sync();                                   // sync 3
     tc_fence_after();
-    if (tid == 0) {
-      dead = scan_fwd_mma3<kSave>(tbase, sb, c, bars, p.status, dead);
-      if (kSave) {
-        bulk_store(p.vn_img + cidx * 16384, sb + sG, 32768);
-        bulk_commit();
-      }
-    }
+    if (tid == 0) dead = scan_fwd_mma3(tbase, sb, c, bars, p.status, dead);
     wait_or_mark(&mma_bar, mphase, dead, p.status);    // the state update has completed (the output product may still run)
     tc_fence_after();
   }
@@ -467,7 +390,6 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     form_o(nt - 1);
     store_o(nt - 1);
   }
-  if (kSave && tid == 0) bulk_wait_all();            // every saved panel is in global memory before the CTA ends
   if (!dead && p.ht) {
     float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + k_lo) * p.V + vb * 128 + vrow;
 #pragma unroll

@@ -153,6 +153,84 @@ __global__ void __launch_bounds__(128) selftest_mma_ts_kernel(SelftestParams p) 
   if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
+// B operand in the UN-swizzled "interleaved" layout [N / 8][K rows][8 elements = 16 bytes] (reduction dim along rows, 8 x 16-byte
+// core matrices of 128 contiguous bytes), A from tensor memory.  `variant` chooses which descriptor field carries which stride.
+__global__ void __launch_bounds__(128) selftest_mma_nosw_kernel(SelftestParams p, int variant) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t bar;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  // p.b is [K][N] row-major (b_mn layout of the other self-tests): element (k, n) -> group n / 8, row k
+  for (int idx = threadIdx.x; idx < p.K * p.N / 8; idx += blockDim.x) {
+    const int k = idx / (p.N / 8), j = idx % (p.N / 8);
+    *reinterpret_cast<uint4*>(smem + size_t(j) * p.K * 16 + k * 16) = *reinterpret_cast<const uint4*>(p.b + size_t(k) * p.N + j * 8);
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_base_s;
+  const uint32_t a_col = 256;
+  {
+    const __nv_bfloat16* arow = p.a + size_t(threadIdx.x) * p.K;
+    for (int c0 = 0; c0 < p.K / 2; c0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t lo = __bfloat16_as_ushort(arow[2 * (c0 + i)]), hi = __bfloat16_as_ushort(arow[2 * (c0 + i) + 1]);
+        v[i] = __uint_as_float(lo | (hi << 16));
+      }
+      tmem_st16(tmem_addr(tbase, warp * 32, a_col + c0), v);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (variant == 1) {   // A in strips as well: element (m, k) of the row-major [128][K] input -> strip m / 8, row k
+    for (int idx = threadIdx.x; idx < 128 * p.K; idx += blockDim.x) {
+      const int m = idx / p.K, k = idx % p.K;
+      *reinterpret_cast<__nv_bfloat16*>(smem + 32768 + size_t(m / 8) * p.K * 16 + k * 16 + (m % 8) * 2) = p.a[idx];
+    }
+    fence_async_smem();
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    tc_fence_after();
+    const Operand B{smem_u32(smem), uint32_t(p.K) * 16u, 2};
+    if (variant == 1) {
+      const Operand A{smem_u32(smem) + 32768, uint32_t(p.K) * 16u, 2};
+      mma_tile(tbase, A, B, 128, p.N, p.K / 16, false);
+    } else {
+      mma_tile_ts(tbase, tbase + a_col, B, p.N, p.K / 16, false);
+    }
+    mma_commit(&bar);
+  }
+  const bool ok = mbar_wait(&bar, 0, p.err, 1);
+  tc_fence_after();
+  if (ok) {
+    for (int c0 = 0; c0 < p.N; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem_addr(tbase, warp * 32, c0), v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) p.d[size_t(warp * 32 + lane) * p.N + c0 + i] = v[i];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
 // A CTA that holds TMEM and waits on an mbarrier nobody arrives at: the wait gives up after `spin_limit` polls, records
 // FLA_ERR_TIMEOUT in the status word, releases the TMEM and returns - the way every kernel of the library leaves a wait
 // that runs out.  Nothing traps and nothing spins without a bound.
@@ -199,6 +277,18 @@ extern "C" FLA_API int fla_b200_selftest_mma_ts(const void* a, const void* b, fl
   const int smem = 65536 + 1024;
   if (cudaFuncSetAttribute(selftest_mma_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FLA_ERR_CUDA;
   selftest_mma_ts_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+extern "C" FLA_API int fla_b200_selftest_mma_nosw(const void* a, const void* b, float* d, int N, int K, int variant, int* err_flag,
+                                                  void* stream) {
+  using namespace fla;
+  if (!a || !b || !d || !err_flag) return FLA_ERR_NULL;
+  if (N % 16 || N < 16 || N > 256 || K % 32 || K < 32 || K > 128 || N * K * 2 > 32768) return FLA_ERR_SHAPE;
+  SelftestParams p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, 128, N, K, 0, 1, 0, 0, err_flag};
+  const int smem = 65536 + 1024;
+  if (cudaFuncSetAttribute(selftest_mma_nosw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FLA_ERR_CUDA;
+  selftest_mma_nosw_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(p, variant);
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
 

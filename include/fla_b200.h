@@ -76,6 +76,11 @@ FLA_API int fla_b200_selftest_mma(const void* a, const void* b, float* d, int M,
  * into TMEM columns 256 + a_col_off .. by the kernel (two elements per 32-bit column), B as above, d[128][N] out. */
 FLA_API int fla_b200_selftest_mma_ts(const void* a, const void* b, float* d, int N, int K, int b_mn, int a_col_off,
                              int* err_flag, void* stream);
+/* The same check for operands in the un-swizzled strip layout ([M or N / 8][reduction rows][16 bytes]) in which the scan
+ * kernels save their per-chunk operands: b is [K][N] row-major; variant 0 reads A [128][K] from tensor memory, variant 1
+ * stages A in strips as well. */
+FLA_API int fla_b200_selftest_mma_nosw(const void* a, const void* b, float* d, int N, int K, int variant, int* err_flag,
+                               void* stream);
 
 /* Device-side failure reporting (the counterpart of the non-zero aclnnStatus the reference turns into a
  * RuntimeError, torch_custom/fla_npu/fla_npu/ops/ascendc/_runtime.py:410-411,427-428).  Launches are

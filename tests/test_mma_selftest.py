@@ -82,3 +82,25 @@ def test_tile_gemm_with_a_from_tensor_memory(lib, N, K, b_mn, a_col):
     ref = A.double() @ B.double().t()
     e = (d.cpu().double() - ref).abs().max().item()
     assert e < 1e-3 * max(1.0, ref.abs().max().item()), f"max err {e}"
+
+
+@pytest.mark.parametrize("N,K", [(64, 64), (128, 64), (128, 128), (64, 32)])
+@pytest.mark.parametrize("variant", [0, 1])
+def test_tile_gemm_with_strip_layout_operands(lib, N, K, variant):
+    """Operands in the un-swizzled strip layout ([N / 8][K rows][16 bytes], reduction dim along rows) that the scan kernels save
+    for the chunk-parallel backward: B always, A from tensor memory (variant 0) or in strips too (variant 1)."""
+    g = torch.Generator().manual_seed(300 + N + K)
+    A = torch.randn(128, K, generator=g).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    a_dev, b_dev = A.contiguous().cuda(), B.t().contiguous().cuda()
+    d = torch.full((128, N), float("nan"), device="cuda", dtype=torch.float32)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = lib.fla_b200_selftest_mma_nosw(ctypes.c_void_p(a_dev.data_ptr()), ctypes.c_void_p(b_dev.data_ptr()), ctypes.c_void_p(d.data_ptr()),
+                                        N, K, variant, ctypes.c_void_p(err.data_ptr()),
+                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0, f"status {st}"
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0, "device-side wait timed out"
+    ref = A.double() @ B.double().t()
+    e = (d.cpu().double() - ref).abs().max().item()
+    assert e < 1e-3 * max(1.0, ref.abs().max().item()), f"max err {e}"
