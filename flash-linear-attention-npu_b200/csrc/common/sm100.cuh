@@ -224,6 +224,8 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 //                   matrices are 128 contiguous bytes, strips are `panel_stride` bytes apart.  A writer whose threads each own
 //                   one reduction row stores a strip piece as 16 bytes per thread at consecutive addresses (coalesced), which
 //                   the swizzled panels cannot offer (their rows are 128 bytes apart).
+//   mn_major 3:     the same memory read the other way round: [reduction / 8][M or N rows][16 bytes], i.e. strips of 8
+//                   reduction elements and rows = M / N (what the swizzled panels do with one layout, strips do too).
 struct Operand {
   uint32_t saddr;         // shared address of the operand
   uint32_t panel_stride;  // bytes between panels (mn_major 0 / 1) or between strips (2)
@@ -237,16 +239,21 @@ __device__ __forceinline__ uint64_t operand_desc(const Operand& o, int kstep) {
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 // Upper 32 bits: swizzled, or (strips) stride byte offset = strip stride, version 1, no swizzle.
 __device__ __forceinline__ uint32_t operand_desc_hi(const Operand& o) {
-  return o.mn_major == 2 ? (((o.panel_stride >> 4) & 0x3FFFu) | (1u << 14)) : kDescHi;
+  if (o.mn_major == 2) return ((o.panel_stride >> 4) & 0x3FFFu) | (1u << 14);   // stride offset = next strip of 8 M / N elements
+  if (o.mn_major == 3) return (128u >> 4) | (1u << 14);                          // stride offset = next 8 rows (M / N)
+  return kDescHi;
 }
 // Lower 32 bits at k-step 0: start address and leading byte offset (panel stride of swizzled MN-major views; for strips
 // the 128 bytes between groups of 8 reduction rows).
 __device__ __forceinline__ uint32_t operand_desc_lo(const Operand& o) {
-  const uint32_t lbo = o.mn_major == 2 ? (128u >> 4) : (o.mn_major ? ((o.panel_stride >> 4) & 0x3FFFu) : 1u);
+  const uint32_t lbo = o.mn_major == 2 ? (128u >> 4)                               // next 8 reduction rows
+                       : o.mn_major == 3 ? ((o.panel_stride >> 4) & 0x3FFFu)       // next strip of 8 reduction elements
+                       : (o.mn_major ? ((o.panel_stride >> 4) & 0x3FFFu) : 1u);
   return ((o.saddr >> 4) & 0x3FFFu) | (lbo << 16);
 }
 // Start-address advance (in 16-byte units) of k-step `ks`
 __device__ __forceinline__ uint32_t operand_kstep(const Operand& o, int ks) {
+  if (o.mn_major == 3) return uint32_t(ks) * 2u * (o.panel_stride >> 4);  // two strips of 8 reduction elements
   if (o.mn_major == 2) return uint32_t(ks) * 16u;                       // 16 reduction rows of 16 bytes
   if (o.mn_major == 1) return uint32_t(ks) * 128u;                      // 16 rows of 128 bytes
   return uint32_t(ks >> 2) * (o.panel_stride >> 4) + uint32_t(ks & 3) * 2u;
@@ -256,7 +263,7 @@ __device__ __forceinline__ uint32_t operand_kstep(const Operand& o, int ks) {
 // field of each descriptor changes, by a constant, so each MMA costs two integer adds.
 __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N,
                                          int ksteps, bool accumulate) {
-  const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major != 0, b.mn_major != 0);
+  const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major == 1 || a.mn_major == 2, b.mn_major == 1 || b.mn_major == 2);
   const uint32_t alo = operand_desc_lo(a), blo = operand_desc_lo(b);
   const uint32_t ahi = operand_desc_hi(a), bhi = operand_desc_hi(b);
 #pragma unroll
@@ -270,7 +277,7 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, cons
 // D (+)= A * B over `ksteps` MMAs of K = 16 with A in tensor memory at columns [a_tmem, a_tmem + 8 * ksteps).
 __device__ __forceinline__ void mma_tile_ts(uint32_t d_tmem, uint32_t a_tmem, const Operand& b, int N, int ksteps,
                                             bool accumulate) {
-  const uint32_t idesc = make_idesc_bf16(128, N, 0, b.mn_major != 0);
+  const uint32_t idesc = make_idesc_bf16(128, N, 0, b.mn_major == 1 || b.mn_major == 2);
   const uint32_t blo = operand_desc_lo(b), bhi = operand_desc_hi(b);
 #pragma unroll
   for (int ks = 0; ks < ksteps; ++ks) {

@@ -490,8 +490,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
   if (gam.dtype != FLA_F32 || gam.ndim != 3 || gam.shape[0] != B || gam.shape[1] != T || gam.shape[2] != HV ||
       gam.stride[2] != 1 || gam.stride[1] != HV || (B > 1 && gam.stride[0] != T * HV))
     return FLA_ERR_SHAPE;
-  if (X.dtype != FLA_BF16 || X.ndim != 4 || X.shape[0] != B || X.shape[1] != T || X.shape[2] != HV || X.shape[3] != kC ||
-      X.stride[3] != 1 || X.stride[2] != kC || X.stride[1] != HV * kC || !aligned16(X.data))
+  if (X.dtype != FLA_BF16 || X.ndim != 1 || X.shape[0] != total_chunks * HV * 8192 || !aligned16(X.data))
     return FLA_ERR_SHAPE;
   if (a->p_img.dtype != FLA_BF16 || a->p_img.ndim != 1 || a->p_img.shape[0] != total_chunks * HV * 8192 || !aligned16(a->p_img.data))
     return FLA_ERR_SHAPE;
@@ -547,16 +546,15 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
     if (cudaFuncSetAttribute(gdn_bwd_par_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
-  CUtensorMap tm_q, tm_k, tm_x, tm_v, tm_d;
+  CUtensorMap tm_q, tm_k, tm_v, tm_d;
   if (make_row_tile_map(&tm_q, p.q, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.q_sh), uint64_t(p.q_st)) ||
       make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)) ||
-      make_row_tile_map(&tm_x, p.X, kC, uint64_t(HV), uint64_t(B * T), uint64_t(kC), uint64_t(HV) * kC) ||
       make_row_tile_map(&tm_v, p.v, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.v_sh), uint64_t(p.v_st)) ||
       make_row_tile_map(&tm_d, p.dO, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.do_sh), uint64_t(p.do_st)))
     return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_bwd_dhu", cs);
-    gdn_scan_bwd_kernel<<<dim3(unsigned(V / 128), unsigned(HV), N), kScanThreads, kScanBwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x, tm_v, tm_d);
+    gdn_scan_bwd_kernel<<<dim3(unsigned(V / 128), unsigned(HV), N), kScanThreads, kScanBwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_d);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   const int nt_max = (max_len + kC - 1) / kC;

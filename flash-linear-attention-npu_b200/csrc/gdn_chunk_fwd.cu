@@ -31,7 +31,7 @@ struct GdnFwdParams {
   const bf16* q; const bf16* k; const bf16* v;
   const void* g; const void* beta;
   float* gam;          // [tokens, HV]      chunk-local cumulative log decay (saved for backward)
-  bf16* X;             // [tokens, HV, 64]  row i of the chunk's (I + A)^-1 (saved for backward)
+  bf16* X;             // [chunks, HV, 2, 8 x 64 x 8]  the chunk's (I + A)^-1 as value + residual strips (saved for backward)
   float* at;           // [chunks, HV, 64, 64] scratch: A^T handed to the triangular-inverse kernel
   bf16* p_img;         // [chunks, HV, 2, 64x64] tril(Q K^T * decay) as hi / lo operand panels (scratch, reused by backward)
   const float* h0;     // [N, HV, K, V] or null
@@ -243,8 +243,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   if (gam.dtype != FLA_F32 || gam.ndim != 3 || gam.shape[0] != B || gam.shape[1] != T || gam.shape[2] != HV ||
       gam.stride[2] != 1 || gam.stride[1] != HV || (B > 1 && gam.stride[0] != T * HV))
     return FLA_ERR_SHAPE;
-  if (X.dtype != FLA_BF16 || X.ndim != 4 || X.shape[0] != B || X.shape[1] != T || X.shape[2] != HV || X.shape[3] != kC ||
-      X.stride[3] != 1 || X.stride[2] != kC || X.stride[1] != HV * kC || !aligned16(X.data))
+  if (X.dtype != FLA_BF16 || X.ndim != 1 || X.shape[0] != total_chunks * HV * 8192 || !aligned16(X.data))
     return FLA_ERR_SHAPE;
   for (const fla_tensor_t* s : {&a->initial_state, &a->final_state}) {
     if (!s->data) continue;
@@ -310,21 +309,20 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {
     KernelTimer kt("tri_inverse", cs);
-    TriInverseParams tp{p.at, p.X, nullptr, nullptr, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, 0};
+    TriInverseParams tp{p.at, nullptr, p.X, nullptr, nullptr, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, 0};
     if (launch_tri_inverse(tp, nt_max, N, cs)) return FLA_ERR_CUDA;
   }
-  CUtensorMap tm_q, tm_k, tm_x;
+  CUtensorMap tm_q, tm_k;
   if (make_row_tile_map(&tm_q, p.q, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.q_sh), uint64_t(p.q_st)) ||
-      make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)) ||
-      make_row_tile_map(&tm_x, p.X, kC, uint64_t(HV), uint64_t(B * T), uint64_t(kC), uint64_t(HV) * kC))
+      make_row_tile_map(&tm_k, p.k, kK, uint64_t(HK), uint64_t(B * T), uint64_t(p.k_sh), uint64_t(p.k_st)))
     return FLA_ERR_CUDA;
   CUtensorMap tm_v;
   if (make_row_tile_map(&tm_v, p.v, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.v_sh), uint64_t(p.v_st))) return FLA_ERR_CUDA;
   {
     KernelTimer kt("gdn_fwd", cs);
     const dim3 grid(unsigned(V / 128), unsigned(HV), N);
-    if (p.s_img) gdn_scan_fwd_kernel<true><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x, tm_v);
-    else gdn_scan_fwd_kernel<false><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_x, tm_v);
+    if (p.s_img) gdn_scan_fwd_kernel<true><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v);
+    else gdn_scan_fwd_kernel<false><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v);
   }
   return cuda_status(cudaGetLastError());
 }

@@ -32,13 +32,13 @@ constexpr uint32_t uVT = 448;      // V^T (fp32, 64 tokens)
 
 // shared memory: load buffers twice (step parity)
 constexpr uint32_t bQK = 0;                  // 2 x 32 KB
-constexpr uint32_t bX = 65536;               // 2 x 8 KB
-constexpr uint32_t bP = 81920;               // 2 x 16 KB (value, residual)
-constexpr uint32_t bV = 114688;              // 2 x 16 KB: v rows, two 64-column panels of 64 rows
-constexpr uint32_t bD = 147456;              // 2 x 16 KB: dO rows, same layout
-constexpr uint32_t bO = 180224;              // 16 KB: dV rows on their way out
-constexpr uint32_t bI = 196608;              // 8 KB: identity panel
-constexpr uint32_t kScanBwdSmem = 204800;
+constexpr uint32_t bX = 65536;               // 2 x 16 KB: the chunk's inverse as value + residual strips
+constexpr uint32_t bP = 98304;               // 2 x 16 KB (value, residual)
+constexpr uint32_t bV = 131072;              // 2 x 16 KB: v rows, two 64-column panels of 64 rows
+constexpr uint32_t bD = 163840;              // 2 x 16 KB: dO rows, same layout
+constexpr uint32_t bO = 196608;              // 16 KB: dV rows on their way out
+constexpr uint32_t bI = 212992;              // 8 KB: identity panel
+constexpr uint32_t kScanBwdSmem = 221184;
 
 struct ScanBwdBars {
   uint64_t *mma_bar, *qk_bar, *x_bar, *p_bar, *v_bar, *d_bar;
@@ -65,9 +65,11 @@ __device__ __noinline__ bool scan_bwd_mma2(uint32_t tbase, uint32_t sb, int s, S
   const uint32_t ph = (s >> 1) & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.x_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opX{sb + bX + b * 8192, 8192, 1};                    // X with its rows as the reduction: X^T dVn
-  mma_tile_ts(tbase + uW, tbase + uDVh, opX, 64, 4, false);
-  mma_tile_ts(tbase + uW, tbase + uDVl, opX, 64, 4, true);
+  // X in strips of 8 rows, read with its rows as the reduction dim: X^T dVn
+  const Operand opXh{sb + bX + b * 16384, 1024, 3}, opXl{sb + bX + b * 16384 + 8192, 1024, 3};
+  mma_tile_ts(tbase + uW, tbase + uDVh, opXh, 64, 4, false);
+  mma_tile_ts(tbase + uW, tbase + uDVl, opXh, 64, 4, true);
+  mma_tile_ts(tbase + uW, tbase + uDVh, opXl, 64, 4, true);
   if (!dead && !mbar_wait(&bars.v_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opI{sb + bI, 8192, 0};
   const Operand opDt{sb + bD + b * 16384, 8192, 1}, opVt{sb + bV + b * 16384, 8192, 1};
@@ -103,7 +105,6 @@ __device__ __forceinline__ float warp_transpose_reduce32(float* x, int lane) {
 
 __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                         const __grid_constant__ CUtensorMap tm_k,
-                                                                        const __grid_constant__ CUtensorMap tm_x,
                                                                         const __grid_constant__ CUtensorMap tm_v,
                                                                         const __grid_constant__ CUtensorMap tm_d) {
   extern __shared__ uint8_t smem_raw[];
@@ -158,8 +159,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       tma_load_tile(sb + bD + b * 16384 + 8192, &tm_d, vb * 128 + 64, hv, row0, &d_bar[b]);
       mbar_arrive_expect_tx(&p_bar[b], 16384);
       bulk_load(sb + bP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
-      mbar_arrive_expect_tx(&x_bar[b], 8192);
-      tma_load_tile(sb + bX + b * 8192, &tm_x, 0, hv, row0, &x_bar[b]);
+      mbar_arrive_expect_tx(&x_bar[b], 16384);
+      bulk_load(sb + bX + b * 16384, p.X + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &x_bar[b]);
       mbar_arrive_expect_tx(&v_bar[b], 16384);
       tma_load_tile(sb + bV + b * 16384, &tm_v, vb * 128, hv, row0, &v_bar[b]);
       tma_load_tile(sb + bV + b * 16384 + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[b]);
@@ -197,7 +198,6 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     if (lane == 0) {
       tma_prefetch_descriptor(&tm_q);
       tma_prefetch_descriptor(&tm_k);
-      tma_prefetch_descriptor(&tm_x);
       tma_prefetch_descriptor(&tm_v);
       tma_prefetch_descriptor(&tm_d);
       if (nt > 0) issue_loads(0);

@@ -3,10 +3,10 @@
 //
 // One CTA per (sequence, value head, 128-column block of V); the state lives transposed in tensor memory for the whole
 // sequence (scan_common.cuh).  Per chunk, with S the state at chunk start, gam the chunk-local cumulative log decay,
-// X = (I + A)^-1 and P = tril(Q K^T e^{gam_i-gam_j}) from the prep kernels:
+// X = (I + A)^-1 (bf16 value + residual) and P = tril(Q K^T e^{gam_i-gam_j}) from the prep kernels:
 //     [QS^T | KS^T] = S^T [Q; K]^T          N = 128 tokens of the [q; k] panel, reduction over the 128 key dims
 //     Z^T     = beta (V^T - e^gam KS^T)     epilogue; V^T arrives through an identity product
-//     v_new^T = Z^T X^T                     N = 64
+//     v_new^T = Z^T X^T                     N = 64; X is a value + a residual (a single bf16 X is what dominated the error)
 //     S^T    <- e^{gam_L} S^T + vhat^T K    N = 128 key dims, reduction over the 64 tokens, vhat = e^{gam_L-gam} v_new
 //     o^T     = scale (e^gam QS^T + v_new^T P^T)
 // Operands the result is sensitive to (state copy, Z, v_new, vhat, P) are a bf16 value plus a bf16 residual and enter
@@ -35,12 +35,12 @@ constexpr uint32_t tVAl = 480;
 
 // shared memory (offsets from a 1024-byte aligned base); the load buffers exist twice (chunk parity)
 constexpr uint32_t sQK = 0;                  // 2 x 32 KB: [q; k] rows, two 64-column panels of 128 rows
-constexpr uint32_t sX = 65536;               // 2 x 8 KB
-constexpr uint32_t sP = 81920;               // 2 x 16 KB (value, residual)
-constexpr uint32_t sV = 114688;              // 2 x 16 KB: v rows of the chunk, two 64-column panels of 64 rows
-constexpr uint32_t sO = 147456;              // 16 KB: the chunk's output rows on their way out
-constexpr uint32_t sI = 163840;              // 8 KB: identity panel
-constexpr uint32_t kScanFwdSmem = 172032;
+constexpr uint32_t sX = 65536;               // 2 x 16 KB: the chunk's inverse as value + residual strips
+constexpr uint32_t sP = 98304;               // 2 x 16 KB (value, residual)
+constexpr uint32_t sV = 131072;              // 2 x 16 KB: v rows of the chunk, two 64-column panels of 64 rows
+constexpr uint32_t sO = 163840;              // 16 KB: the chunk's output rows on their way out
+constexpr uint32_t sI = 180224;              // 8 KB: identity panel
+constexpr uint32_t kScanFwdSmem = 188416;
 
 struct ScanBars {
   uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;   // two barriers each (index = chunk parity) but the first two
@@ -66,9 +66,11 @@ __device__ __noinline__ bool scan_fwd_mma2(uint32_t tbase, uint32_t sb, int c, S
   const int b = c & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.x_bar[b], (c >> 1) & 1, status, FLA_ERR_TIMEOUT)) dead = true;
-  const Operand opX{sb + sX + b * 8192, 8192, 0};
-  mma_tile_ts(tbase + tVN, tbase + tZAh, opX, 64, 4, false);
-  mma_tile_ts(tbase + tVN, tbase + tZAl, opX, 64, 4, true);
+  // X in strips of 8 rows: rows of X are N here, its columns the reduction dim
+  const Operand opXh{sb + sX + b * 16384, 1024, 2}, opXl{sb + sX + b * 16384 + 8192, 1024, 2};
+  mma_tile_ts(tbase + tVN, tbase + tZAh, opXh, 64, 4, false);
+  mma_tile_ts(tbase + tVN, tbase + tZAl, opXh, 64, 4, true);
+  mma_tile_ts(tbase + tVN, tbase + tZAh, opXl, 64, 4, true);
   mma_commit(bars.mma_bar);
   return dead;
 }
@@ -92,7 +94,6 @@ __device__ __noinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c, S
 template <bool kSave>
 __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                         const __grid_constant__ CUtensorMap tm_k,
-                                                                        const __grid_constant__ CUtensorMap tm_x,
                                                                         const __grid_constant__ CUtensorMap tm_v) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -146,8 +147,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       mbar_arrive_expect_tx(&v_bar[b], 16384);
       tma_load_tile(sb + sV + b * 16384, &tm_v, vb * 128, hv, row0, &v_bar[b]);
       tma_load_tile(sb + sV + b * 16384 + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[b]);
-      mbar_arrive_expect_tx(&x_bar[b], 8192);
-      tma_load_tile(sb + sX + b * 8192, &tm_x, 0, hv, row0, &x_bar[b]);
+      mbar_arrive_expect_tx(&x_bar[b], 16384);
+      bulk_load(sb + sX + b * 16384, p.X + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &x_bar[b]);
       mbar_arrive_expect_tx(&p_bar[b], 16384);
       bulk_load(sb + sP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
     };
@@ -185,7 +186,6 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     if (lane == 0) {
       tma_prefetch_descriptor(&tm_q);
       tma_prefetch_descriptor(&tm_k);
-      tma_prefetch_descriptor(&tm_x);
       tma_prefetch_descriptor(&tm_v);
       if (nt > 0) {
         load_qk(0);

@@ -754,7 +754,7 @@ int fla::kda_launch_forward(const KdaParams& p, int nt_max, cudaStream_t cs) {
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {
     KernelTimer kt("tri_inverse", cs);
-    TriInverseParams tp{p.at, nullptr, p.x_img, p.x_img + kC * kC, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, int(kKdaXImg)};
+    TriInverseParams tp{p.at, nullptr, nullptr, p.x_img, p.x_img + kC * kC, p.cu_seqlens, p.chunk_offsets, p.T, p.HV, int(kKdaXImg)};
     if (launch_tri_inverse(tp, nt_max, p.N, cs)) return FLA_ERR_CUDA;
   }
   {

@@ -170,9 +170,13 @@ __global__ void __launch_bounds__(128) selftest_mma_nosw_kernel(SelftestParams p
     mbar_init_fence();
   }
   // p.b is [K][N] row-major (b_mn layout of the other self-tests): element (k, n) -> group n / 8, row k
-  for (int idx = threadIdx.x; idx < p.K * p.N / 8; idx += blockDim.x) {
-    const int k = idx / (p.N / 8), j = idx % (p.N / 8);
-    *reinterpret_cast<uint4*>(smem + size_t(j) * p.K * 16 + k * 16) = *reinterpret_cast<const uint4*>(p.b + size_t(k) * p.N + j * 8);
+  // (variant 2: p.b is [N][K] row-major and element (n, k) -> group k / 8, row n)
+  {
+    const int R = variant == 2 ? p.N : p.K, C = variant == 2 ? p.K : p.N;
+    for (int idx = threadIdx.x; idx < R * C / 8; idx += blockDim.x) {
+      const int r = idx / (C / 8), j = idx % (C / 8);
+      *reinterpret_cast<uint4*>(smem + size_t(j) * R * 16 + r * 16) = *reinterpret_cast<const uint4*>(p.b + size_t(r) * C + j * 8);
+    }
   }
   fence_async_smem();
   tc_fence_before();
@@ -206,7 +210,9 @@ __global__ void __launch_bounds__(128) selftest_mma_nosw_kernel(SelftestParams p
   }
   if (threadIdx.x == 0) {
     tc_fence_after();
-    const Operand B{smem_u32(smem), uint32_t(p.K) * 16u, 2};
+    // variant 2: the strips hold B^T, i.e. [K / 8][N rows][16 bytes] (strips along the reduction dim): the host passes b as
+    // [N][K] row-major for it, staged by the same loop with the roles of the two dims swapped
+    const Operand B = variant == 2 ? Operand{smem_u32(smem), uint32_t(p.N) * 16u, 3} : Operand{smem_u32(smem), uint32_t(p.K) * 16u, 2};
     if (variant == 1) {
       const Operand A{smem_u32(smem) + 32768, uint32_t(p.K) * 16u, 2};
       mma_tile(tbase, A, B, 128, p.N, p.K / 16, false);

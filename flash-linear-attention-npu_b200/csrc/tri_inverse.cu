@@ -60,6 +60,19 @@ __global__ void __launch_bounds__(64 * kTriTiles, 5) tri_inverse_kernel(TriInver
     for (int i = 0; i < kC; ++i)
       if (i < rows) xg[int64_t(i) * p.HV * kC] = __float2bfloat16_rn(x[i]);
   }
+  if (p.x_strips) {          // strips of 8 rows: column c stores its 8 entries of every strip as 16 bytes next to its neighbours'
+    uint8_t* img = reinterpret_cast<uint8_t*>(p.x_strips + cidx * 8192) + c * 16;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float xs[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xs[i] = (g * 8 + i < rows) ? x[g * 8 + i] : 0.f;
+      uint4 hi, lo;
+      split8(xs, hi, lo);
+      *reinterpret_cast<uint4*>(img + g * 1024) = hi;
+      *reinterpret_cast<uint4*>(img + 8192 + g * 1024) = lo;
+    }
+  }
   if (p.x_img) {             // swizzled 64x64 operand panel per (chunk, head); rows past the sequence end are zero
     const int64_t stride = p.img_stride ? p.img_stride : kC * kC;
     uint8_t* img = reinterpret_cast<uint8_t*>(p.x_img + cidx * stride);

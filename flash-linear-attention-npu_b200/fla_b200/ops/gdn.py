@@ -76,7 +76,7 @@ def gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     o = torch.empty((B, T, HV, V), dtype=output_dtype or q.dtype, device=dev)
     ht = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if output_final_state else None
     gam = torch.empty((B, T, HV), dtype=torch.float32, device=dev)
-    x_inv = torch.empty((B, T, HV, CHUNK), dtype=torch.bfloat16, device=dev)
+    x_inv = torch.empty(total_chunks * HV * 8192, dtype=torch.bfloat16, device=dev)   # (I + A)^-1 per chunk: value + residual strips
     s_img = vn_img = p_img = None
     if save_for_backward:
         s_img = torch.empty(total_chunks * HV * (V // 64) * 16384, dtype=torch.bfloat16, device=dev)

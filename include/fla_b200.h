@@ -78,7 +78,8 @@ FLA_API int fla_b200_selftest_mma_ts(const void* a, const void* b, float* d, int
                              int* err_flag, void* stream);
 /* The same check for operands in the un-swizzled strip layout ([M or N / 8][reduction rows][16 bytes]) in which the scan
  * kernels save their per-chunk operands: b is [K][N] row-major; variant 0 reads A [128][K] from tensor memory, variant 1
- * stages A in strips as well. */
+ * stages A in strips as well; variant 2 takes b as [N][K] row-major and stages it in strips along the reduction dim
+ * ([K / 8][N rows][16 bytes]). */
 FLA_API int fla_b200_selftest_mma_nosw(const void* a, const void* b, float* d, int N, int K, int variant, int* err_flag,
                                void* stream);
 
@@ -206,7 +207,8 @@ FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* a
  *   o [B, T, HV, V] bf16|f32
  *   initial_state / final_state [N, HV, 128(K), V] f32, optional
  *   gam   [B, T, HV] f32      out: chunk-local cumulative sum of g      (saved for backward)
- *   x_inv [B, T, HV, 64] bf16 out: rows of (I + strict_tril(beta_i exp(gam_i-gam_j) k_i.k_j))^-1 per chunk
+ *   x_inv [chunks * HV * 8192] bf16 out: X = (I + strict_tril(beta_i exp(gam_i-gam_j) k_i.k_j))^-1 per (chunk, head), as a bf16 value
+ *          and a bf16 residual (4096 elements each) in strips of 8 rows: element [r/8][c][r%8] = X[r][c]; rows past the chunk are zero
  *   s_img  [chunks * HV * (V/64) * 16384] bf16, optional out (for backward): per (chunk, head) the state at chunk start as
  *          V/64 (64-column blocks of V) x 2 (hi, lo = bf16 residual) swizzled 128x64 operand panels
  *   vn_img [chunks * HV * (V/64) * 8192] bf16, optional out (for backward): v_new, V/64 x 2 (hi, lo = bf16 residual) 64x64 panels

@@ -85,14 +85,15 @@ def test_tile_gemm_with_a_from_tensor_memory(lib, N, K, b_mn, a_col):
 
 
 @pytest.mark.parametrize("N,K", [(64, 64), (128, 64), (128, 128), (64, 32)])
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 def test_tile_gemm_with_strip_layout_operands(lib, N, K, variant):
     """Operands in the un-swizzled strip layout ([N / 8][K rows][16 bytes], reduction dim along rows) that the scan kernels save
-    for the chunk-parallel backward: B always, A from tensor memory (variant 0) or in strips too (variant 1)."""
+    for the chunk-parallel backward: B always, A from tensor memory (variant 0) or in strips too (variant 1).  Variant 2 reads
+    strips laid along the reduction dim ([K / 8][N rows][16 bytes]): how the reverse scan reads the chunk inverse transposed."""
     g = torch.Generator().manual_seed(300 + N + K)
     A = torch.randn(128, K, generator=g).to(torch.bfloat16)
     B = torch.randn(N, K, generator=g).to(torch.bfloat16)
-    a_dev, b_dev = A.contiguous().cuda(), B.t().contiguous().cuda()
+    a_dev, b_dev = A.contiguous().cuda(), (B.contiguous() if variant == 2 else B.t().contiguous()).cuda()
     d = torch.full((128, N), float("nan"), device="cuda", dtype=torch.float32)
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
     st = lib.fla_b200_selftest_mma_nosw(ctypes.c_void_p(a_dev.data_ptr()), ctypes.c_void_p(b_dev.data_ptr()), ctypes.c_void_p(d.data_ptr()),
