@@ -90,7 +90,7 @@ STAGE_BYTES = {
     _th(c, "HV", 128, 4),
     "prepare_wy_repr_bwd_group_sum": lambda c: _th(c, "HV", 128, 4) + _th(c, "HK", 128, 2),
 }
-KERNEL_SYMBOL = {"gdn_fwd": "gdn_fwd_kernel", "gdn_bwd_dhu": "gdn_bwd_dhu_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
+KERNEL_SYMBOL = {"gdn_fwd": "gdn_scan_fwd_kernel", "gdn_bwd_dhu": "gdn_scan_bwd_kernel", "gdn_bwd_par": "gdn_bwd_par_kernel",
                  "kda_fwd": "kda_fwd_kernel", "kda_prep": "kda_prep_kernel", "kda_bwd_dhu": "kda_bwd_dhu_kernel", "kda_bwd_par": "kda_bwd_par_kernel", "gdn_prep": "gdn_prep_kernel", "tri_inverse": "tri_inverse_kernel",
                  "recurrent_gdn": "recurrent_gdn_kernel", "causal_conv1d_fwd": "conv_fwd_kernel",
                  "causal_conv1d_update": "conv_update1_kernel", "causal_conv1d_bwd": "conv_bwd_kernel",
@@ -332,7 +332,7 @@ class Workload:
         """DRAM bytes (read + write) of one launch: the per-unit figure of one ncu capture of a small case of the
         same kernel (profiles/), scaled by the units this launch processes; None where no capture exists."""
         c = self.cfg
-        per_chunk_head = {"gdn_fwd": 312.98e6 / 2048, "gdn_bwd_dhu": 346.22e6 / 2048, "gdn_bwd_par": 469.55e6 / 2048,
+        per_chunk_head = {"gdn_fwd": 323.00e6 / 2048, "gdn_bwd_dhu": 361.24e6 / 2048, "gdn_bwd_par": 470.01e6 / 2048,
                           "kda_prep": 159.25e6 / 1024, "kda_fwd": 232.05e6 / 1024, "kda_bwd_dhu": 266.41e6 / 1024,
                           "kda_bwd_par": 396.41e6 / 1024, "recompute_w_u_fwd": 87.51e6 / 2048, "chunk_fwd_h": 144.66e6 / 2048,
                           "chunk_fwd_o": 151.88e6 / 2048}
@@ -340,8 +340,8 @@ class Workload:
             return None     # the capture is of the training forward (it also writes the saved images)
         if kname in per_chunk_head and "T" in c:
             return per_chunk_head[kname] * c["B"] * ((c["T"] + 63) // 64) * c["HV"]
-        if kname == "recurrent_gdn":       # 212.29 MB for 64 sequences x 32 heads
-            return 212.29e6 / 64 * c["N"] * c["HV"] / 32
+        if kname == "recurrent_gdn":       # 541.1 MB read + 480.2 MB written for 256 sequences x 32 heads (a 537 MB pool, > 4 x L2)
+            return 1021.4e6 / 256 * c["N"] * c["HV"] / 32
         if kname == "causal_conv1d_fwd":   # 229.92 MB for 2 x 4096 x 8192 elements
             return 229.92e6 / (2 * 4096 * 8192) * c["B"] * c["T"] * c["D"]
         if kname == "causal_conv1d_bwd":   # 391.52 MB for 2 x 4096 x 8192 elements

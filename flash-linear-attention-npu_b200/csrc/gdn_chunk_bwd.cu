@@ -1,13 +1,13 @@
 // Chunked gated-delta-rule backward (chunk = 64, K = V = 128) as two kernels.
 //
 // With per chunk  gam = cumsum(g),  P = tril(Q K^T * e^{gam_i-gam_j}),  X = (I + strict_tril(beta_i e^{gam_i-gam_j} k_i.k_j))^-1,
-// S = state at chunk start, Vn = v_new (both saved by the forward as split bf16 panel images) and dS' the state
+// S = state at chunk start, Vn = v_new (both saved by the forward as bf16 value + residual strip images) and dS' the state
 // gradient entering the chunk from the right:
 //
-//  gdn_bwd_dhu_kernel  (reverse-sequential over chunks, one CTA per (sequence, value head, 64-column block of V)):
+//  gdn_scan_bwd_kernel  (gdn_scan_bwd.cuh; reverse-sequential over chunks, one CTA per (sequence, value head, 128 channels of V)):
 //      dVn = scale P^T dO + e^{gam_L-gam} * (K dS')          dZ = X^T dVn          dV = beta * dZ
 //      dS  = e^{gam_L} dS' + (scale e^{gam} * Q)^T dO - K^T (beta e^{gam} * dZ)     dh0 = dS after the first chunk
-//      saves dS' and [dO; dZ] as panel images and the partial row sums  sum_v dZ*V  for the second kernel.
+//      saves dS' and [dO; dZ] as strip images and the partial row sums  sum_v dZ*V  for the second kernel.
 //      Replaces chunk_bwd_dv_local + chunk_gated_delta_rule_bwd_dhu of the reference
 //      (examples/flash_gated_delta_rule.py:930-960) and the dv / du parts of prepare_wy_repr_bwd_*.
 //  gdn_bwd_par_kernel  (parallel over chunks, one CTA per (chunk, q/k head), looping over the value heads of the group):

@@ -41,6 +41,25 @@ def _as_rows(t):
     return t
 
 
+def _fold_batch(t):
+    """A `[B,T,H,D]` view of head-first memory (`[B,H,T,D]` storage: batch stride = H x head stride) seen as one sequence of
+    B*H heads, `[1,T,B*H,D]`, on the same storage.  Every (batch row, head) pair is an independent recurrence, so the kernels
+    run head-first batches through this view without a copy.  None when the strides do not allow it."""
+    B, T, H, D = t.shape
+    if t.stride(3) != 1 or t.stride(0) != H * t.stride(2):
+        return None
+    return t.as_strided((1, T, B * H, D), (B * t.stride(0), t.stride(1), t.stride(2), 1))
+
+
+def _fold_plan(q, k, v, cu_seqlens):
+    """Whether a fixed-length batch whose rows do not sit back to back (head-first storage) can run as one sequence of
+    B*H heads instead of being copied: returns the folded (q, k, v) views or None."""
+    if cu_seqlens is not None or q.shape[0] == 1 or all(_as_rows(t) is t for t in (q, k, v)):
+        return None
+    folded = tuple(_fold_batch(t) for t in (q, k, v))
+    return None if any(f is None for f in folded) else folded
+
+
 def gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens=None, save_for_backward=False,
                   output_dtype=None):
     """Launch the forward kernels.  Returns (o, final_state, saved) where saved holds gam, X and, when
@@ -141,7 +160,16 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, output_dtype, qk_l2norm):
         need_grad = any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
-        q_, k_, v_, g_, b_ = (_as_rows(x.detach()) for x in (q, k, v, g, beta))
+        B, T, HK, HV = q.shape[0], q.shape[1], q.shape[2], v.shape[2]
+        h0 = None if initial_state is None else initial_state.detach()
+        folded = _fold_plan(q.detach(), k.detach(), v.detach(), cu_seqlens)
+        ctx.fold = (B, HK, HV) if folded is not None else None
+        if folded is not None:   # head-first storage: B*H heads of one sequence, gates re-laid to match (they are small)
+            q_, k_, v_ = folded
+            g_, b_ = (x.detach().permute(1, 0, 2).reshape(1, T, B * HV) for x in (g, beta))
+            h0 = None if h0 is None else h0.reshape(1, B * HV, *h0.shape[2:])
+        else:
+            q_, k_, v_, g_, b_ = (_as_rows(x.detach()) for x in (q, k, v, g, beta))
         ctx.qk_l2norm = qk_l2norm
         if qk_l2norm:
             # q, k <- x * rsqrt(sum x^2 + 1e-6), stored in the input dtype like the reference's l2norm_fwd
@@ -149,9 +177,11 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             from .l2norm import l2norm_fwd
             q_, q_rstd = l2norm_fwd(q_)
             k_, k_rstd = l2norm_fwd(k_)
-        o, ht, saved = gdn_chunk_fwd(q_, k_, v_, g_, b_, scale, None if initial_state is None else initial_state.detach(),
-                                     output_final_state, cu_seqlens, save_for_backward=need_grad,
+        o, ht, saved = gdn_chunk_fwd(q_, k_, v_, g_, b_, scale, h0, output_final_state, cu_seqlens, save_for_backward=need_grad,
                                      output_dtype=output_dtype)
+        if folded is not None:
+            o = o.view(T, B, HV, o.shape[-1]).permute(1, 0, 2, 3)
+            ht = None if ht is None else ht.view(B, HV, *ht.shape[2:])
         if need_grad:
             extra = (q_rstd, k_rstd) if qk_l2norm else ()
             ctx.save_for_backward(q_, k_, v_, b_, saved["gam"], saved["x_inv"], saved["s_img"], saved["vn_img"],
@@ -166,13 +196,23 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     def backward(ctx, do, dht):
         q, k, v, beta, gam, x_inv, s_img, vn_img, p_img = ctx.saved_tensors[:9]
         saved = dict(ctx.meta, gam=gam, x_inv=x_inv, s_img=s_img, vn_img=vn_img, p_img=p_img)
-        dq, dk, dv, dg, dbeta, dh0 = gdn_chunk_bwd(q, k, v, beta, saved, do.contiguous(), dht, ctx.scale, ctx.has_h0,
+        if ctx.fold is not None:
+            B, HK, HV = ctx.fold
+            T = do.shape[1]
+            do = do.permute(1, 0, 2, 3).reshape(1, T, B * HV, do.shape[-1])   # a view when do has the strides of o
+            dht = None if dht is None else dht.reshape(1, B * HV, *dht.shape[2:])
+        dq, dk, dv, dg, dbeta, dh0 = gdn_chunk_bwd(q, k, v, beta, saved, do, dht, ctx.scale, ctx.has_h0,
                                                    grad_dtype=torch.float32 if (ctx.in_dtypes[3] == torch.float32 or ctx.qk_l2norm) else None)
         if ctx.qk_l2norm:
             from .l2norm import l2norm_bwd
             q_rstd, k_rstd = ctx.saved_tensors[9:11]
             dq = l2norm_bwd(q, q_rstd, dq)
             dk = l2norm_bwd(k, k_rstd, dk)
+        if ctx.fold is not None:
+            dq, dk = (x.view(T, B, HK, x.shape[-1]).permute(1, 0, 2, 3) for x in (dq, dk))
+            dv = dv.view(T, B, HV, dv.shape[-1]).permute(1, 0, 2, 3)
+            dg, dbeta = (x.view(T, B, HV).permute(1, 0, 2) for x in (dg, dbeta))
+            dh0 = None if dh0 is None else dh0.view(B, HV, *dh0.shape[2:])
         dts = ctx.in_dtypes
         return (dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]), dg.to(dts[3]), dbeta.to(dts[4]), None, dh0, None, None, None,
                 None)

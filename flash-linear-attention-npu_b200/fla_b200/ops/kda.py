@@ -154,7 +154,9 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     per-chunk blocks Aqk and Akk (what `npu_chunk_kda_fwd` returns)."""
     op = "chunk_kda"
     if use_beta_sigmoid_in_kernel:
-        raise NotImplementedError(f"{op}: the beta sigmoid is only fused into the decode operator (recurrent_kda)")
+        # beta arrives as logits.  It is a [B,T,HV] tensor, 1/128 of the gate's bytes: the activation (and, through autograd,
+        # its gradient) is one elementwise pass in front of the kernels rather than a mode of them.
+        beta = torch.sigmoid(beta.float())
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != torch.bfloat16:
             raise TypeError(f"{op}: {name} must be bfloat16, got {t.dtype}")

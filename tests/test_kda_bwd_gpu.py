@@ -158,6 +158,27 @@ def test_kda_backward_through_the_gate_activation():
     assert_close("d_dt_bias", b_d.grad, b64.grad, TOL)
 
 
+def test_kda_beta_given_as_logits():
+    """`use_beta_sigmoid_in_kernel` (kda/chunk_kda_fwd/docs/api.md): beta holds logits; output and the gradient
+    with respect to the logits against fp64 autograd through sigmoid + recurrence."""
+    from fla_b200.ops import chunk_kda
+    B, T, HK, HV = 1, 128, 1, 2
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=79)
+    logits = torch.randn(B, T, HV, generator=torch.Generator().manual_seed(9))
+    l64 = logits.double().requires_grad_(True)
+    q64, k64 = inp["q"].double().repeat_interleave(HV // HK, 2), inp["k"].double().repeat_interleave(HV // HK, 2)
+    o_ref, _ = oracle.naive_recurrent_kda(q64, k64, inp["v"].double(), inp["g"].double(), torch.sigmoid(l64), scale=128 ** -0.5,
+                                          dtype=torch.float64)
+    (o_ref * inp["do"].double()).sum().backward()
+    d = {n: t.cuda() for n, t in inp.items() if t is not None}
+    l_d = logits.cuda().requires_grad_(True)
+    o, _ = chunk_kda(d["q"], d["k"], d["v"], d["g"], l_d, use_beta_sigmoid_in_kernel=True, output_dtype=torch.float32)
+    (o * d["do"].float()).sum().backward()
+    torch.cuda.synchronize()
+    assert_close("o", o, o_ref, TOL)
+    assert_close("d_beta_logits", l_d.grad, l64.grad, TOL)
+
+
 KDA_EMPTY_CASES = {
     "leading": ([0, 70, 71, 200], [0, 0, 70, 71, 200], [1, 2, 3], [0]),
     "interior": ([0, 70, 71, 200], [0, 70, 70, 71, 200], [0, 2, 3], [1]),
