@@ -211,9 +211,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       scan_sync();                                          // sync 1: step s - 1 no longer reads the other buffers
       if (lane == 0 && s + 1 < nt) issue_loads(s + 1);
       __syncwarp();
+      scan_sync();                                          // sync 2
+      // not before sync 2: the epilogue warps have just handed the 64 KB dS' image to the load/store unit, and this warp's
+      // shared-memory stores and global loads would queue behind it while the whole CTA waits at the barrier
       make_factors(s + 1);
       load_scalars(s + 2);
-      scan_sync();                                          // sync 2
       scan_sync();                                          // sync 3
     }
     scan_sync();
