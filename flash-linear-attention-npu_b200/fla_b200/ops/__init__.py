@@ -1,5 +1,7 @@
-"""Operator surface.  Every function launches hand-written sm_100a kernels through the C ABI;
-nothing here computes on the CPU or through PyTorch math."""
+"""Operator surface.  Every function launches hand-written sm_100a kernels through the C ABI; nothing here computes on
+the CPU.  Two small elementwise steps of `chunk_kda` run as PyTorch operations in front of the kernels when gradients are
+required: the gate activation of `use_gate_in_kernel` (without gradients it is a mode of the prep kernel) and the sigmoid
+of `use_beta_sigmoid_in_kernel`; layout glue (views, the re-laying of `[B,T,H]` gates) is PyTorch as well."""
 from .conv import (causal_conv1d, causal_conv1d_bwd, causal_conv1d_update, npu_causal_conv1d,  # noqa: F401
                    npu_causal_conv1d_bwd)
 from .gdn import (chunk_gated_delta_rule, chunk_gated_delta_rule_bwd, chunk_gated_delta_rule_fwd_bwd,  # noqa: F401
