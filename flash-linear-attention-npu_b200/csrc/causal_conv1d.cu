@@ -68,6 +68,8 @@ struct ConvFwdParams {
   const int32_t* cu_seqlens;  // varlen: [N+1] token offsets into the single batch row
   int64_t x_sb, x_st, y_sb, y_st, r_sb, r_st, w_sd, w_sw;
   int64_t i_sn, i_sd, i_sw, f_sn, f_sd, f_sw;
+  int64_t y_sh;       // head-first output [B, H, T, D/H]: stride between heads (0 with the [B, T, D] output)
+  int y_hd;           // channels per head of the output (D with the [B, T, D] output)
   int B, T, D, nseq, silu;
 };
 
@@ -107,7 +109,7 @@ __global__ void __launch_bounds__(kConvThreads, 4) conv_fwd_kernel(ConvFwdParams
   }
 
   const bf16* xb = p.x + b * p.x_sb + d0;
-  bf16* yb = p.y + b * p.y_sb + d0;
+  bf16* yb = p.y + b * p.y_sb + (d0 / p.y_hd) * p.y_sh + d0 % p.y_hd;   // a thread's 8 channels never straddle a head
   const bf16* rb = HAS_RES ? p.residual + b * p.r_sb + d0 : nullptr;
 
   // win[0 .. W-2] = the W-1 inputs before the group, win[W-1 + i] = input i of the group
@@ -338,12 +340,16 @@ extern "C" FLA_API int fla_b200_causal_conv1d_fwd(const fla_causal_conv1d_fwd_ar
   if (!a) return FLA_ERR_NULL;
   const fla_tensor_t &x = a->x, &y = a->y, &w = a->weight;
   if (!x.data || !y.data || !w.data) return FLA_ERR_NULL;
-  if (x.ndim != 3 || y.ndim != 3 || w.ndim != 2) return FLA_ERR_SHAPE;
+  if (x.ndim != 3 || (y.ndim != 3 && y.ndim != 4) || w.ndim != 2) return FLA_ERR_SHAPE;
   if (x.dtype != FLA_BF16 || y.dtype != FLA_BF16 || w.dtype != FLA_BF16) return FLA_ERR_DTYPE;
   const int64_t B = x.shape[0], T = x.shape[1], D = x.shape[2], W = w.shape[1];
   if (w.shape[0] != D || W < 2 || W > 4 || D % 8 || B <= 0 || T < 0) return FLA_ERR_SHAPE;
-  for (int i = 0; i < 3; ++i)
-    if (y.shape[i] != x.shape[i]) return FLA_ERR_SHAPE;
+  if (y.ndim == 3) {
+    for (int i = 0; i < 3; ++i)
+      if (y.shape[i] != x.shape[i]) return FLA_ERR_SHAPE;
+  } else if (y.shape[0] != B || y.shape[2] != T || y.shape[1] * y.shape[3] != D || y.shape[3] % 8) {
+    return FLA_ERR_SHAPE;   // head-first output [B, H, T, D / H]
+  }
   if (!vec_ok(x) || !vec_ok(y)) return FLA_ERR_LAYOUT;
   if (w.stride[0] == 1 && (!aligned16(w.data) || w.stride[1] % 8)) return FLA_ERR_LAYOUT;
   int nseq = int(B);
@@ -356,6 +362,8 @@ extern "C" FLA_API int fla_b200_causal_conv1d_fwd(const fla_causal_conv1d_fwd_ar
   p.x = static_cast<const bf16*>(x.data); p.y = static_cast<bf16*>(y.data);
   p.weight = static_cast<const bf16*>(w.data);
   p.x_sb = x.stride[0]; p.x_st = x.stride[1]; p.y_sb = y.stride[0]; p.y_st = y.stride[1];
+  p.y_hd = int(D);
+  if (y.ndim == 4) { p.y_sh = y.stride[1]; p.y_st = y.stride[2]; p.y_hd = int(y.shape[3]); }
   p.w_sd = w.stride[0]; p.w_sw = w.stride[1];
   if (a->residual.data) {
     const fla_tensor_t& r = a->residual;

@@ -86,7 +86,8 @@ def causal_conv1d(x, weight=None, bias=None, residual=None, initial_state=None, 
 
 
 def _causal_conv1d_fwd(x, weight=None, bias=None, residual=None, initial_state=None, output_final_state=False,
-                       activation=None, cu_seqlens=None):
+                       activation=None, cu_seqlens=None, head_num=0):
+    """`head_num` > 0: y comes out head-first, `[B, head_num, T, D // head_num]`, written in that layout by the kernel."""
     op = "causal_conv1d"
     if x.dim() != 3:
         raise RuntimeError(f"{op}: x must be [B,T,D], got {tuple(x.shape)}")
@@ -101,7 +102,13 @@ def _causal_conv1d_fwd(x, weight=None, bias=None, residual=None, initial_state=N
     if cu_seqlens is not None:
         cu = cu_seqlens.to(device=x.device, dtype=torch.int32)
         N = cu.numel() - 1
-    y = torch.empty_like(x)
+    head_num = int(head_num)
+    if head_num > 0:
+        if D % head_num or (D // head_num) % 8:
+            raise RuntimeError(f"{op}: head_num={head_num} must divide D={D} into heads of a multiple of 8 channels")
+        y = torch.empty((B, head_num, T, D // head_num), dtype=x.dtype, device=x.device)
+    else:
+        y = torch.empty_like(x)
     final = torch.empty((N, D, W - 1), dtype=x.dtype, device=x.device) if output_final_state else None
     a = CausalConv1dFwdArgs()
     a.x, a.weight, a.bias, a.residual = rt.desc(x), rt.desc(weight), rt.desc(bias), rt.desc(residual)
@@ -137,10 +144,12 @@ def npu_causal_conv1d(x, weight, bias=None, conv_states=None, *, query_start_loc
                       initial_state_mode=None, num_accepted_tokens=None, activation_mode=0, pad_slot_id=-1,
                       run_mode=0, head_num=0):
     """Reference low-level signature.  x `[B,T,D]` / `[T,D]` (varlen with query_start_loc) for run_mode 0,
-    `[N,D]` / `[N,T,D]` for run_mode 1; weight `[W,D]`; conv_states `[slots,S,D]` updated in place."""
+    `[N,D]` / `[N,T,D]` for run_mode 1; weight `[W,D]`; conv_states `[slots,S,D]` updated in place.
+    `head_num` > 0 (prefill only, …/_aclnn_ctypes.py:939-948): the output is `[B, head_num, T, D // head_num]`."""
     op = "npu_causal_conv1d"
-    if head_num:
-        raise NotImplementedError(f"{op}: head_num output re-layout is not provided; outputs keep the layout of x")
+    head_num = int(head_num)
+    if head_num and int(run_mode) == 1:
+        head_num = 0    # the reference re-lays the output only in prefill mode (_infer_causal_conv1d_y)
     w_dw = weight.transpose(0, 1)                                   # [D,W] view of the [W,D] tensor
     st = None if conv_states is None else conv_states.transpose(1, 2)  # [slots,D,S] view
     dev = x.device
@@ -170,7 +179,10 @@ def npu_causal_conv1d(x, weight, bias=None, conv_states=None, *, query_start_loc
             sel = st if idx is None else st[idx.long()]
             mode = as_i32(initial_state_mode).bool()
             init = torch.where(mode[:, None, None], sel, torch.zeros_like(sel))
-    y, final = causal_conv1d(x3, w_dw, bias, None, init, st is not None, int(activation_mode), cu)
+    if head_num:   # prefill output as [B, head_num, T, D / head_num] ([head_num, T, D / head_num] for packed input)
+        y, final = _causal_conv1d_fwd(x3, w_dw, bias, None, init, st is not None, int(activation_mode), cu, head_num=head_num)
+    else:
+        y, final = causal_conv1d(x3, w_dw, bias, None, init, st is not None, int(activation_mode), cu)
     if st is not None:
         if idx is None:
             st[:N].copy_(final)
@@ -178,7 +190,7 @@ def npu_causal_conv1d(x, weight, bias=None, conv_states=None, *, query_start_loc
             keep = idx != pad_slot_id
             st[idx[keep].long()] = final[keep]
         rt.mark_mutated(conv_states)
-    return y.squeeze(0) if varlen else y
+    return y.squeeze(0) if varlen else y   # packed input with head_num: [head_num, T, D / head_num]
 
 
 def npu_causal_conv1d_bwd(x, y, weight, dy, initial_state=None, dht=None, *, query_start_loc=None, activation=0,

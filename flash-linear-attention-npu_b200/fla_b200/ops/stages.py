@@ -144,12 +144,20 @@ def recompute_w_u_fwd(k, v, beta, A, chunk_size, *, g=None, gk=None, cu_seqlens=
 def chunk_gated_delta_rule_fwd_h(k, w, u, g=None, *, gk=None, initial_state=None, output_final_state=False, chunk_size=None,
                                  cu_seqlens=None, chunk_indices=None, state_v_first=False):
     """Sequential state pass: `h_c = S`, `v_new = u - w S`, `S <- e^{g_last} S + k^T (e^{g_last - g} v_new)`.
-    Returns (h `[B,HV,NT,K,V]`, v_new `[B,HV,T,V]`, final_state `[N,HV,K,V]` fp32 or None)."""
+    Returns (h `[B,HV,NT,K,V]`, v_new `[B,HV,T,V]`, final_state `[N,HV,K,V]` fp32 or None).
+    `state_v_first` (…/_aclnn_ctypes.py:564,581-586): initial_state, h and final_state have their last two dims swapped
+    (`[.., V, K]`); the kernel works K-first, so the states are transposed on the way in and out (a copy each)."""
     del chunk_indices
     if gk is not None or g is None:
         raise NotImplementedError("chunk_gated_delta_rule_fwd_h: scalar gates (g) only; gk belongs to the fused KDA operator")
     if state_v_first:
-        raise NotImplementedError("chunk_gated_delta_rule_fwd_h: state_v_first is not supported")
+        if initial_state is not None:
+            if initial_state.dim() != 4 or initial_state.shape[2:] != (u.shape[3], k.shape[3]):
+                raise RuntimeError("npu_chunk_gated_delta_rule_fwd_h: initial_state shape does not match state_v_first.")
+            initial_state = initial_state.transpose(-1, -2)
+        h, v_new, ht = chunk_gated_delta_rule_fwd_h(k, w, u, g, initial_state=initial_state, output_final_state=output_final_state,
+                                                    chunk_size=chunk_size, cu_seqlens=cu_seqlens)
+        return h.transpose(-1, -2).contiguous(), v_new, None if ht is None else ht.transpose(-1, -2).contiguous()
     chunk_size = CHUNK if chunk_size is None else int(chunk_size)
     B, HV, T, V = u.shape
     K = k.shape[3]

@@ -145,7 +145,8 @@ FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* args, void* wor
  * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:951-985) and the composed entry
  * causal_conv1d_ascendc (examples/flash_gated_delta_rule.py:422-443).
  *   y[t, d] = act(bias[d] + sum_{j<W} weight[d, j] * x[t - (W-1) + j, d]) (+ residual[t, d])
- *   x, y, residual [B, T, D] bf16, D contiguous and a multiple of 8
+ *   x, y, residual [B, T, D] bf16, D contiguous and a multiple of 8; y may instead be head-first, [B, H, T, D/H] with D/H a
+ *          multiple of 8 (the reference's head_num output, _aclnn_ctypes.py:939-948): channel d goes to head d / (D/H)
  *   weight [D, W] bf16 (any strides: pass the reference's [W, D] tensor as a transposed view), W in {2,3,4}
  *   bias [D] bf16, optional
  *   initial_state / final_state [N, D, W-1] bf16 (any strides), optional: the last W-1 inputs before /

@@ -153,3 +153,26 @@ def test_reference_known_answer_vectors():
     yu = npu_causal_conv1d(xu.cuda(), w_op.cuda(), bias.cuda(), conv_states, activation_mode=1, run_mode=1)
     assert_close("y_update", yu, ref_u, TOL, stored_bf16=True)
     assert torch.equal(conv_states.cpu().float(), st_ref.transpose(1, 2).float())
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_prefill_head_first_output(packed):
+    """`head_num` of the reference operator (_aclnn_ctypes.py:939-948): the prefill output is written head-first,
+    `[B, head_num, T, D // head_num]`; bit-identical to the `[B, T, D]` output re-laid on the host."""
+    from fla_b200.ops import npu_causal_conv1d
+    B, T, D, W, H = (1, 150, 512, 4, 4) if packed else (2, 70, 256, 3, 8)
+    inp = oracle.make_conv_inputs(B, T, D, W, seed=21)
+    x = inp["x"].cuda()
+    w_wd = inp["weight"].t().contiguous().cuda()
+    kw = dict(activation_mode=1)
+    if packed:
+        x = x[0]
+        kw["query_start_loc"] = [0, 40, 41, 150]
+    y_plain = npu_causal_conv1d(x, w_wd, inp["bias"].cuda(), **kw)
+    y_heads = npu_causal_conv1d(x, w_wd, inp["bias"].cuda(), head_num=H, **kw)
+    if packed:
+        assert y_heads.shape == (H, T, D // H)
+        assert torch.equal(y_heads, y_plain.view(T, H, D // H).permute(1, 0, 2))
+    else:
+        assert y_heads.shape == (B, H, T, D // H)
+        assert torch.equal(y_heads, y_plain.view(B, T, H, D // H).permute(0, 2, 1, 3))

@@ -155,6 +155,11 @@ def test_chunk_fwd_h(case):
     assert_close("ht", ht, d["ht"], TOL)
     h2, v2, none = chunk_gated_delta_rule_fwd_h(d["k"].cuda(), _bf(d["w"]).cuda(), _bf(d["u"]).cuda(), d["gam"].cuda(), cu_seqlens=cu)
     assert none is None and (h2[:, :, 0] == 0).all()
+    # state_v_first: the same states with their last two dims swapped
+    h3, v3, ht3 = chunk_gated_delta_rule_fwd_h(d["k"].cuda(), _bf(d["w"]).cuda(), _bf(d["u"]).cuda(), d["gam"].cuda(),
+                                               initial_state=d["h0"].transpose(-1, -2).contiguous().cuda(), output_final_state=True,
+                                               chunk_size=C, cu_seqlens=cu, state_v_first=True)
+    assert torch.equal(h3, h.transpose(-1, -2)) and torch.equal(ht3, ht.transpose(-1, -2)) and torch.equal(v3, v_new)
 
 
 def test_chunk_fwd_o(case):
