@@ -186,35 +186,56 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t panel_
 }
 
 // One tcgen05.mma (K = 16): D[tmem] (+)= A[smem] * B[smem].  Issued by a single thread.
+// `leader` != 0 in the thread that issues: callers inside a branch that only one thread takes pass 1 (the default); callers
+// whose whole warp runs the issuing code (so that descriptors stay warp-uniform values) pass elect_one().
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
+                                       uint32_t accumulate, uint32_t leader = 1u) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p, q;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " setp.ne.b32 q, %5, 0;\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+// One lane of the (converged) warp.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
   asm volatile(
       "{\n"
       " .reg .pred p;\n"
-      " setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
+      " elect.sync _|p, 0xffffffff;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred;
 }
 // The same with the A operand in tensor memory: row m of A is TMEM lane m (M = 128), its 16-bit elements are packed two
 // per 32-bit column (element 2c in the low half of column c), so one K = 16 step reads 8 columns starting at `a_tmem`.
 // A written with tcgen05.st needs tcgen05.wait::st + tcgen05.fence::before_thread_sync + a barrier before this is issued.
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
+                                       uint32_t accumulate, uint32_t leader = 1u) {
   asm volatile(
       "{\n"
-      " .reg .pred p;\n"
+      " .reg .pred p, q;\n"
       " setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      " setp.ne.b32 q, %5, 0;\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
       "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
       : "memory");
 }
 // Make the mbarrier observe completion of every MMA this thread issued so far.
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+__device__ __forceinline__ void mma_commit(uint64_t* bar, uint32_t leader = 1u) {
+  asm volatile(
+      "{\n"
+      " .reg .pred q;\n"
+      " setp.ne.b32 q, %1, 0;\n"
+      " @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(smem_u32(bar)), "r"(leader)
+      : "memory");
 }
 
 // A tile operand in shared memory.
@@ -262,7 +283,7 @@ __device__ __forceinline__ uint32_t operand_kstep(const Operand& o, int ks) {
 // loop unrolls.  Issue cost matters (one thread feeds the tensor core): per k-step only the start-address
 // field of each descriptor changes, by a constant, so each MMA costs two integer adds.
 __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N,
-                                         int ksteps, bool accumulate) {
+                                         int ksteps, bool accumulate, uint32_t leader = 1u) {
   const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major == 1 || a.mn_major == 2, b.mn_major == 1 || b.mn_major == 2);
   const uint32_t alo = operand_desc_lo(a), blo = operand_desc_lo(b);
   const uint32_t ahi = operand_desc_hi(a), bhi = operand_desc_hi(b);
@@ -270,19 +291,19 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, const Operand& a, cons
   for (int ks = 0; ks < ksteps; ++ks) {
     const uint64_t ad = (uint64_t(ahi) << 32) | uint64_t(alo + operand_kstep(a, ks));
     const uint64_t bd = (uint64_t(bhi) << 32) | uint64_t(blo + operand_kstep(b, ks));
-    mma_ss(d_tmem, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    mma_ss(d_tmem, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u, leader);
   }
 }
 
 // D (+)= A * B over `ksteps` MMAs of K = 16 with A in tensor memory at columns [a_tmem, a_tmem + 8 * ksteps).
 __device__ __forceinline__ void mma_tile_ts(uint32_t d_tmem, uint32_t a_tmem, const Operand& b, int N, int ksteps,
-                                            bool accumulate) {
+                                            bool accumulate, uint32_t leader = 1u) {
   const uint32_t idesc = make_idesc_bf16(128, N, 0, b.mn_major == 1 || b.mn_major == 2);
   const uint32_t blo = operand_desc_lo(b), bhi = operand_desc_hi(b);
 #pragma unroll
   for (int ks = 0; ks < ksteps; ++ks) {
     const uint64_t bd = (uint64_t(bhi) << 32) | uint64_t(blo + operand_kstep(b, ks));
-    mma_ts(d_tmem, a_tmem + uint32_t(ks) * 8u, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    mma_ts(d_tmem, a_tmem + uint32_t(ks) * 8u, bd, idesc, (accumulate || ks > 0) ? 1u : 0u, leader);
   }
 }
 

@@ -43,48 +43,48 @@ constexpr uint32_t kScanBwdSmem = 221184;
 struct ScanBwdBars {
   uint64_t *mma_bar, *qk_bar, *x_bar, *p_bar, *v_bar, *d_bar;
 };
-__device__ __noinline__ bool scan_bwd_mma1(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, int* status, bool dead) {
+__device__ __forceinline__ bool scan_bwd_mma1(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, int* status, bool dead, uint32_t lead) {
   const int b = s & 1;
   const uint32_t ph = (s >> 1) & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.qk_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opK{sb + bQK + b * 32768 + 8192, 16384, 0};          // k rows as B: N = 64 tokens, reduction over key dims
-  mma_tile_ts(tbase + uW, tbase + uAh, opK, 64, 8, false);
-  mma_tile_ts(tbase + uW, tbase + uAl, opK, 64, 8, true);
+  mma_tile_ts(tbase + uW, tbase + uAh, opK, 64, 8, false, lead);
+  mma_tile_ts(tbase + uW, tbase + uAl, opK, 64, 8, true, lead);
   if (!dead && !mbar_wait(&bars.d_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   if (!dead && !mbar_wait(&bars.p_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opDt{sb + bD + b * 16384, 8192, 1};                  // dO^T: M = 128 channels over two panels, reduction over tokens
   const Operand opPh{sb + bP + b * 16384, 8192, 1}, opPl{sb + bP + b * 16384 + 8192, 8192, 1};   // P with its rows as the reduction
-  mma_tile(tbase + uU, opDt, opPh, 128, 64, 4, false);
-  mma_tile(tbase + uU, opDt, opPl, 128, 64, 4, true);
-  mma_commit(bars.mma_bar);
+  mma_tile(tbase + uU, opDt, opPh, 128, 64, 4, false, lead);
+  mma_tile(tbase + uU, opDt, opPl, 128, 64, 4, true, lead);
+  mma_commit(bars.mma_bar, lead);
   return dead;
 }
-__device__ __noinline__ bool scan_bwd_mma2(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, int* status, bool dead) {
+__device__ __forceinline__ bool scan_bwd_mma2(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, int* status, bool dead, uint32_t lead) {
   const int b = s & 1;
   const uint32_t ph = (s >> 1) & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.x_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   // X in strips of 8 rows, read with its rows as the reduction dim: X^T dVn
   const Operand opXh{sb + bX + b * 16384, 1024, 3}, opXl{sb + bX + b * 16384 + 8192, 1024, 3};
-  mma_tile_ts(tbase + uW, tbase + uDVh, opXh, 64, 4, false);
-  mma_tile_ts(tbase + uW, tbase + uDVl, opXh, 64, 4, true);
-  mma_tile_ts(tbase + uW, tbase + uDVh, opXl, 64, 4, true);
+  mma_tile_ts(tbase + uW, tbase + uDVh, opXh, 64, 4, false, lead);
+  mma_tile_ts(tbase + uW, tbase + uDVl, opXh, 64, 4, true, lead);
+  mma_tile_ts(tbase + uW, tbase + uDVh, opXl, 64, 4, true, lead);
   if (!dead && !mbar_wait(&bars.v_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opI{sb + bI, 8192, 0};
   const Operand opDt{sb + bD + b * 16384, 8192, 1}, opVt{sb + bV + b * 16384, 8192, 1};
-  mma_tile(tbase + uU, opDt, opI, 128, 64, 4, false);                // dO^T, exact
-  mma_tile(tbase + uVT, opVt, opI, 128, 64, 4, false);               // V^T, exact
-  mma_commit(bars.mma_bar);
+  mma_tile(tbase + uU, opDt, opI, 128, 64, 4, false, lead);                // dO^T, exact
+  mma_tile(tbase + uVT, opVt, opI, 128, 64, 4, false, lead);               // V^T, exact
+  mma_commit(bars.mma_bar, lead);
   return dead;
 }
-__device__ __noinline__ bool scan_bwd_mma3(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, bool dead) {
+__device__ __forceinline__ bool scan_bwd_mma3(uint32_t tbase, uint32_t sb, int s, ScanBwdBars bars, bool dead, uint32_t lead) {
   const int b = s & 1;
   tc_fence_after();
   const Operand opQK{sb + bQK + b * 32768, 16384, 1};                // [q; k] rows as the reduction, N = 128 key dims
-  mma_tile_ts(tbase + uDS, tbase + uAh, opQK, 128, 8, true);
-  mma_tile_ts(tbase + uDS, tbase + uAl, opQK, 128, 8, true);
-  mma_commit(bars.mma_bar);
+  mma_tile_ts(tbase + uDS, tbase + uAh, opQK, 128, 8, true, lead);
+  mma_tile_ts(tbase + uDS, tbase + uAl, opQK, 128, 8, true, lead);
+  mma_commit(bars.mma_bar, lead);
   return dead;
 }
 
@@ -224,6 +224,9 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
 
   // ================================================================ epilogue warps
   const ScanBwdBars bars{&mma_bar, qk_bar, x_bar, p_bar, v_bar, d_bar};
+  // products: one elected lane of warp 0 in code the whole warp runs, so that the descriptors are warp-uniform values
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);
+  const uint32_t tbase_u = __shfl_sync(0xffffffffu, tbase, 0), sb_u = __shfl_sync(0xffffffffu, sb, 0);
   const int quad = warp & 3, half = warp >> 2;
   const int vrow = quad * 32 + lane;
   const uint32_t tlane = tmem_addr(tbase, quad * 32, 0);
@@ -300,7 +303,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     tc_fence_before();
     scan_sync();                                   // sync 1
     tc_fence_after();
-    if (tid == 0) dead = scan_bwd_mma1(tbase, sb, s, bars, p.status, dead);
+    if (warp_u == 0) dead = scan_bwd_mma1(tbase_u, sb_u, s, bars, p.status, dead, elect_one());
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
 
@@ -333,7 +336,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     tc_fence_before();
     scan_sync();                                   // sync 2
     tc_fence_after();
-    if (tid == 0) dead = scan_bwd_mma2(tbase, sb, s, bars, p.status, dead);
+    if (warp_u == 0) dead = scan_bwd_mma2(tbase_u, sb_u, s, bars, p.status, dead, elect_one());
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
 
@@ -391,7 +394,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     tc_fence_before();
     scan_sync();                                   // sync 3
     tc_fence_after();
-    if (tid == 0) dead = scan_bwd_mma3(tbase, sb, s, bars, dead);
+    if (warp_u == 0) dead = scan_bwd_mma3(tbase_u, sb_u, s, bars, dead, elect_one());
     store_dv(c);                                   // while the state-gradient update runs
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();

@@ -45,49 +45,50 @@ constexpr uint32_t kScanFwdSmem = 188416;
 struct ScanBars {
   uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;   // two barriers each (index = chunk parity) but the first two
 };
-// The three batches of products of one chunk, each issued by one thread.  Kept out of line: inlined into the epilogue
-// code their unrolled descriptor arithmetic costs registers the accumulator rows need.
-__device__ __noinline__ bool scan_fwd_mma1(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
+// The three batches of products of one chunk.  All of warp 0 runs them and the lane `lead` marks issues: built from
+// warp-uniform values in converged code a product costs a handful of instructions; out of line, or in a branch that one
+// thread takes, it cost some thirty and the tensor pipe waited for its issuer (0.65 -> 0.53 ms for the inference forward).
+__device__ __forceinline__ bool scan_fwd_mma1(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead, uint32_t lead) {
   const int b = c & 1;
   const uint32_t ph = (c >> 1) & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.qk_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opKQ{sb + sQK + b * 32768, 16384, 0};
-  mma_tile_ts(tbase + tKQ, tbase + tSAh, opKQ, 128, 8, false);
-  mma_tile_ts(tbase + tKQ, tbase + tSAl, opKQ, 128, 8, true);
+  mma_tile_ts(tbase + tKQ, tbase + tSAh, opKQ, 128, 8, false, lead);
+  mma_tile_ts(tbase + tKQ, tbase + tSAl, opKQ, 128, 8, true, lead);
   // V^T into the columns the decayed v_new of this chunk will occupy later
   if (!dead && !mbar_wait(&bars.v_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opVt{sb + sV + b * 16384, 8192, 1}, opI{sb + sI, 8192, 0};
-  mma_tile(tbase + tVAh, opVt, opI, 128, 64, 4, false);
-  mma_commit(bars.mma_bar);
+  mma_tile(tbase + tVAh, opVt, opI, 128, 64, 4, false, lead);
+  mma_commit(bars.mma_bar, lead);
   return dead;
 }
-__device__ __noinline__ bool scan_fwd_mma2(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
+__device__ __forceinline__ bool scan_fwd_mma2(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead, uint32_t lead) {
   const int b = c & 1;
   tc_fence_after();
   if (!dead && !mbar_wait(&bars.x_bar[b], (c >> 1) & 1, status, FLA_ERR_TIMEOUT)) dead = true;
   // X in strips of 8 rows: rows of X are N here, its columns the reduction dim
   const Operand opXh{sb + sX + b * 16384, 1024, 2}, opXl{sb + sX + b * 16384 + 8192, 1024, 2};
-  mma_tile_ts(tbase + tVN, tbase + tZAh, opXh, 64, 4, false);
-  mma_tile_ts(tbase + tVN, tbase + tZAl, opXh, 64, 4, true);
-  mma_tile_ts(tbase + tVN, tbase + tZAh, opXl, 64, 4, true);
-  mma_commit(bars.mma_bar);
+  mma_tile_ts(tbase + tVN, tbase + tZAh, opXh, 64, 4, false, lead);
+  mma_tile_ts(tbase + tVN, tbase + tZAl, opXh, 64, 4, true, lead);
+  mma_tile_ts(tbase + tVN, tbase + tZAh, opXl, 64, 4, true, lead);
+  mma_commit(bars.mma_bar, lead);
   return dead;
 }
-__device__ __noinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead) {
+__device__ __forceinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c, ScanBars bars, int* status, bool dead, uint32_t lead) {
   const int b = c & 1;
   tc_fence_after();
   const Operand opK{sb + sQK + b * 32768 + 8192, 16384, 1};   // k rows: reduction over tokens, N = 128 key dims over two panels
-  mma_tile_ts(tbase + tST, tbase + tVAh, opK, 128, 4, true);
-  mma_tile_ts(tbase + tST, tbase + tVAl, opK, 128, 4, true);
-  mma_commit(bars.mma_bar);                                   // the state update: what the next chunk waits for
+  mma_tile_ts(tbase + tST, tbase + tVAh, opK, 128, 4, true, lead);
+  mma_tile_ts(tbase + tST, tbase + tVAl, opK, 128, 4, true, lead);
+  mma_commit(bars.mma_bar, lead);                                   // the state update: what the next chunk waits for
   if (!dead && !mbar_wait(&bars.p_bar[b], (c >> 1) & 1, status, FLA_ERR_TIMEOUT)) dead = true;
   const uint32_t pp = sb + sP + b * 16384;
   const Operand opPh{pp, 8192, 0}, opPl{pp + 8192, 8192, 0};
-  mma_tile_ts(tbase + tVN, tbase + tZAh, opPh, 64, 4, false);
-  mma_tile_ts(tbase + tVN, tbase + tZAl, opPh, 64, 4, true);
-  mma_tile_ts(tbase + tVN, tbase + tZAh, opPl, 64, 4, true);
-  mma_commit(bars.o_bar);                                     // the output product: read when the next chunk's state is out
+  mma_tile_ts(tbase + tVN, tbase + tZAh, opPh, 64, 4, false, lead);
+  mma_tile_ts(tbase + tVN, tbase + tZAl, opPh, 64, 4, true, lead);
+  mma_tile_ts(tbase + tVN, tbase + tZAh, opPl, 64, 4, true, lead);
+  mma_commit(bars.o_bar, lead);                                     // the output product: read when the next chunk's state is out
   return dead;
 }
 
@@ -218,6 +219,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
 
   // ================================================================ epilogue warps
   const ScanBars bars{&mma_bar, &o_bar, qk_bar, x_bar, p_bar, v_bar};
+  // The products are issued by one elected lane of warp 0 inside code that the whole warp runs: descriptors built from
+  // warp-uniform values stay in uniform registers, which is what the instruction takes; built in a branch that a single
+  // thread takes they cost some thirty instructions per product to move there.
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);
+  const uint32_t tbase_u = __shfl_sync(0xffffffffu, tbase, 0), sb_u = __shfl_sync(0xffffffffu, sb, 0);
   const int quad = warp & 3, half = warp >> 2;
   const int vrow = quad * 32 + lane;                       // my value channel inside the block = my TMEM lane
   const uint32_t tlane = tmem_addr(tbase, quad * 32, 0);
@@ -278,7 +284,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     {
       const float dl = f.dl;
       uint8_t* s_row = kSave ? reinterpret_cast<uint8_t*>(p.s_img + cidx * 32768) + (vrow >> 6) * 32768 + (vrow & 63) * 16 : nullptr;
-#pragma unroll
+#pragma unroll 1
       for (int g4 = 0; g4 < 4; ++g4) {                   // 16 key dims at a time: 8 packed columns per operand store
         float s16[16];
         tmem_ld16(tlane + tST + k_lo + g4 * 16, s16);
@@ -309,7 +315,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     tc_fence_before();
     scan_sync();                                   // sync 1
     tc_fence_after();
-    if (tid == 0) dead = scan_fwd_mma1(tbase, sb, c, bars, p.status, dead);
+    if (warp_u == 0) dead = scan_fwd_mma1(tbase_u, sb_u, c, bars, p.status, dead, elect_one());
     // ---- while [QS^T | KS^T] runs: output rows of chunk c - 1
     if (c > 0) store_o(c - 1);
     wait_or_mark(&mma_bar, mphase, dead, p.status);
@@ -317,7 +323,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
 
     // ---- C: Z^T = beta (V^T - e^gam KS^T) for my 32 tokens
     {
-#pragma unroll
+#pragma unroll 1
       for (int g = 0; g < 2; ++g) {
         float ks[16], vt[16];
         tmem_ld16(tlane + tKQ + 64 + t_lo + g * 16, ks);
@@ -343,13 +349,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     tc_fence_before();
     scan_sync();                                   // sync 2
     tc_fence_after();
-    if (tid == 0) dead = scan_fwd_mma2(tbase, sb, c, bars, p.status, dead);
+    if (warp_u == 0) dead = scan_fwd_mma2(tbase_u, sb_u, c, bars, p.status, dead, elect_one());
     wait_or_mark(&mma_bar, mphase, dead, p.status);
     tc_fence_after();
 
     // ---- E: v_new^T (rows past the end of the sequence are zero) and its decayed copy
     {
-#pragma unroll
+#pragma unroll 1
       for (int g = 0; g < 2; ++g) {
         float vn[16];
         tmem_ld16(tlane + tVN + t_lo + g * 16, vn);
@@ -382,7 +388,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     tc_fence_before();
     scan_sync();                                   // sync 3
     tc_fence_after();
-    if (tid == 0) dead = scan_fwd_mma3(tbase, sb, c, bars, p.status, dead);
+    if (warp_u == 0) dead = scan_fwd_mma3(tbase_u, sb_u, c, bars, p.status, dead, elect_one());
     wait_or_mark(&mma_bar, mphase, dead, p.status);    // the state update has completed (the output product may still run)
     tc_fence_after();
   }
