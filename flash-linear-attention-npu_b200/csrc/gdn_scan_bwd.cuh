@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     {
       const float dl = f.dl;
       uint8_t* s_row = reinterpret_cast<uint8_t*>(p.ds_img + cidx * 32768) + (vrow >> 6) * 32768 + (vrow & 63) * 16;
-#pragma unroll
+#pragma unroll 1
       for (int g4 = 0; g4 < 4; ++g4) {
         float s16[16];
         tmem_ld16(tlane + uDS + k_lo + g4 * 16, s16);
@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
 
     // ---- B: dVn^T = scale U1^T + e^{gam_L-gam} W1^T (zero past the end of the sequence) for my 32 tokens
     {
-#pragma unroll
+#pragma unroll 1
       for (int g = 0; g < 2; ++g) {
         float w1[16], u1[16];
         tmem_ld16(tlane + uW + t_lo + g * 16, w1);
