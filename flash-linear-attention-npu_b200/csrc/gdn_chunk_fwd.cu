@@ -53,9 +53,13 @@ namespace fla {
 
 // --------------------------------------------------------------------------------------------- prep
 // One CTA per (chunk, q/k head).  One M = 128 product [q; k] k^T leaves Q K^T in TMEM lanes 0..63 and K K^T in
-// lanes 64..127; each thread keeps its row in registers and, per value head of the GVA group, the q-side
-// threads emit P = tril(Q K^T * e^{gam_i - gam_j}) as split operand panels and the k-side threads emit A^T.
-__global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
+// lanes 64..127.  Eight warps: warp w reads lane quadrant w % 4 and the half w / 4 of the 64 columns, so a thread keeps
+// half a row (32 values) in registers; per value head of the GVA group the q-side threads emit their half of
+// P = tril(Q K^T * e^{gam_i - gam_j}) as split operand panels and the k-side threads their half of A^T.  (With four warps
+// and whole rows per thread the kernel took 0.245 ms at the benchmark shape: it is a chain of latencies, and half the
+// work per thread at twice the warps per SM shortens it.)
+constexpr int kPrepThreads = 256;
+__global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* qk_pan = smem;                        // 2 panels x 128 rows: rows 0..63 q, rows 64..127 k
@@ -72,10 +76,10 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   const int rows = min(kC, sq.len - t0);
   const int64_t tok0 = int64_t(sq.bos) + t0;
   {
-    uint4 val[16];   // all loads in flight before the first one is consumed
+    uint4 val[8];   // all loads in flight before the first one is consumed
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int idx = tid + i * 128, r = (idx / 16) & 63, ch = idx % 16;
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * kPrepThreads, r = (idx / 16) & 63, ch = idx % 16;
       const bool isk = idx >= 1024;
       val[i] = make_uint4(0, 0, 0, 0);
       if (r < rows) {
@@ -84,8 +88,8 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
       }
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int idx = tid + i * 128, r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * kPrepThreads, r = ((idx / 16) & 63) + (idx >= 1024 ? 64 : 0), ch = idx % 16;
       *reinterpret_cast<uint4*>(qk_pan + (ch / 8) * 16384 + panel_chunk_off(r, ch % 8)) = val[i];
     }
   }
@@ -109,12 +113,18 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
     mma_commit(&bar);
   }
   const int G = p.HV / p.HK;
-  const bool kside = tid >= 64;
-  const int tok = tid & 63;
+  const int quad = warp & 3, half = warp >> 2;
+  const int row = quad * 32 + lane;                 // accumulator row == TMEM lane
+  const bool kside = row >= 64;
+  const int tok = row & 63;
+  const int j0 = half * 32;                         // my 32 columns
   const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
   tc_fence_after();
-  float sc[kC];   // my row of Q K^T (q side) or K K^T (k side)
-  if (ok) tmem_ld_row64(tmem_addr(tbase, warp * 32, 0), sc);
+  float sc[32];   // my half of row `tok` of Q K^T (q side) or K K^T (k side)
+  if (ok) {
+    tmem_ld32(tmem_addr(tbase, quad * 32, j0), sc);
+    tmem_ld_wait();
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 64);
@@ -123,9 +133,9 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
   for (int h = 0; h < G; ++h) {
     const int hv = hk * G + h;
     const int64_t cidx = (int64_t(sq.cbase) + blockIdx.x) * p.HV + hv;
-    // chunk-local cumulative sum of g (threads 0..63, two warps)
+    // chunk-local cumulative sum of g (warps 0 and 1: the q-side rows of the first column half)
     float gv = 0.f;
-    if (!kside) {
+    if (warp < 2) {
       gv = tok < rows ? ld_scalar(p.g, (tok0 + tok) * p.g_st + hv, p.g_is_f32) : 0.f;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -136,7 +146,7 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
     }
     const float bi = (kside && tok < rows) ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
     __syncthreads();
-    if (!kside) {
+    if (warp < 2) {
       if (warp == 1) gv += wsum_s[0];
       gam_s[tok] = gv;
       if (tok < rows) p.gam[(tok0 + tok) * p.HV + hv] = gv;
@@ -144,20 +154,20 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
     __syncthreads();
     const float gam_i = gam_s[tok];
     if (!kside) {
-      // P row as split bf16, written straight into the (swizzled) panel images
+      // my half of the P row as split bf16, written straight into the (swizzled) panel images
       uint8_t* img = reinterpret_cast<uint8_t*>(p.p_img + cidx * 8192);
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
         float t[8];
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
-          const int j = ch * 8 + jj;
+          const int j = j0 + ch * 8 + jj;
           const float e = __expf(fminf(gam_i - gam_s[j], 0.f));
-          t[jj] = sc[j] * ((j <= tok) ? e : 0.f);
+          t[jj] = sc[ch * 8 + jj] * ((j <= tok) ? e : 0.f);
         }
         uint4 hi, lo;
         split8(t, hi, lo);
-        const uint32_t off = panel_chunk_off(tok, ch);
+        const uint32_t off = panel_chunk_off(tok, half * 4 + ch);
         *reinterpret_cast<uint4*>(img + off) = hi;
         *reinterpret_cast<uint4*>(img + 8192 + off) = lo;
       }
@@ -165,8 +175,10 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnFwdParams p) {
       // A^T[j][i] = beta_i exp(gam_i - gam_j) (k_i . k_j) for j < i, written coalesced along i
       float* at = p.at + cidx * (kC * kC);
 #pragma unroll
-      for (int j = 0; j < kC - 1; ++j)
-        if (j < tok) at[j * kC + tok] = bi * __expf(gam_i - gam_s[j]) * sc[j];
+      for (int jl = 0; jl < 32; ++jl) {
+        const int j = j0 + jl;
+        if (j < tok) at[j * kC + tok] = bi * __expf(gam_i - gam_s[j]) * sc[jl];
+      }
     }
     __syncthreads();
   }
@@ -304,7 +316,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   const int nt_max = (max_len + kC - 1) / kC;
   {
     KernelTimer kt("gdn_prep", cs);
-    gdn_prep_kernel<<<dim3(nt_max, unsigned(HK), N), 128, prep_smem, cs>>>(p);
+    gdn_prep_kernel<<<dim3(nt_max, unsigned(HK), N), kPrepThreads, prep_smem, cs>>>(p);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {

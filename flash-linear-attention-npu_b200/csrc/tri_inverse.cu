@@ -29,9 +29,21 @@ __global__ void __launch_bounds__(64 * kTriTiles, 5) tri_inverse_kernel(TriInver
   const int64_t cidx = (int64_t(sq.cbase) + chunk) * p.HV + hv;
   float* AT = tri_smem + grp * kC * kTriStride;
   if (active) {
-    const float* src = p.at + cidx * (kC * kC);     // A^T row-major: src[j * 64 + i] = A[i][j]
-#pragma unroll 8
-    for (int j = 0; j < kC; ++j) AT[j * kTriStride + c] = src[j * kC + c];
+    // A^T row-major: src[j * 64 + i] = A[i][j].  16-byte pieces, all of a thread's sixteen requested before the first is
+    // stored (one round trip to memory instead of eight), and only the pieces that hold an entry below the diagonal
+    // (i > j): the others are neither written by the producer nor read by the solve.
+    const float4* src = reinterpret_cast<const float4*>(p.at + cidx * (kC * kC));
+    float4 v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = c + i * 64, j = idx >> 4, q4 = idx & 15;
+      if (4 * q4 + 3 > j) v[i] = src[idx];
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = c + i * 64, j = idx >> 4, q4 = idx & 15;
+      if (4 * q4 + 3 > j) *reinterpret_cast<float4*>(AT + j * kTriStride + 4 * q4) = v[i];
+    }
   }
   __syncthreads();
   if (!active) return;
