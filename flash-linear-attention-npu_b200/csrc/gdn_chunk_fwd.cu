@@ -154,7 +154,9 @@ __global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams 
     __syncthreads();
     const float gam_i = gam_s[tok];
     if (!kside) {
-      // my half of the P row as split bf16, written straight into the (swizzled) panel images
+      // my half of the P row as split bf16, in strips of 8 columns ([j / 8][row i][16 bytes], value then residual): the 16
+      // bytes a thread stores for a strip lie next to its neighbours' (512 contiguous bytes per warp store), and the scans
+      // read the image as an operand with the reduction along j (forward) or along i (reverse) by the descriptor alone
       uint8_t* img = reinterpret_cast<uint8_t*>(p.p_img + cidx * 8192);
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -167,7 +169,7 @@ __global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams 
         }
         uint4 hi, lo;
         split8(t, hi, lo);
-        const uint32_t off = panel_chunk_off(tok, half * 4 + ch);
+        const uint32_t off = uint32_t(half * 4 + ch) * 1024u + uint32_t(tok) * 16u;
         *reinterpret_cast<uint4*>(img + off) = hi;
         *reinterpret_cast<uint4*>(img + 8192 + off) = lo;
       }

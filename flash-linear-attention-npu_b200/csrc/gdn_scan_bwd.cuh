@@ -54,7 +54,7 @@ __device__ __forceinline__ bool scan_bwd_mma1(uint32_t tbase, uint32_t sb, int s
   if (!dead && !mbar_wait(&bars.d_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   if (!dead && !mbar_wait(&bars.p_bar[b], ph, status, FLA_ERR_TIMEOUT)) dead = true;
   const Operand opDt{sb + bD + b * 16384, 8192, 1};                  // dO^T: M = 128 channels over two panels, reduction over tokens
-  const Operand opPh{sb + bP + b * 16384, 8192, 1}, opPl{sb + bP + b * 16384 + 8192, 8192, 1};   // P with its rows as the reduction
+  const Operand opPh{sb + bP + b * 16384, 1024, 2}, opPl{sb + bP + b * 16384 + 8192, 1024, 2};   // P (strips of 8 columns j = N) with its rows as the reduction
   mma_tile(tbase + uU, opDt, opPh, 128, 64, 4, false, lead);
   mma_tile(tbase + uU, opDt, opPl, 128, 64, 4, true, lead);
   mma_commit(bars.mma_bar, lead);

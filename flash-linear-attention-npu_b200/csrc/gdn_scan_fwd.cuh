@@ -84,7 +84,7 @@ __device__ __forceinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c
   mma_commit(bars.mma_bar, lead);                                   // the state update: what the next chunk waits for
   if (!dead && !mbar_wait(&bars.p_bar[b], (c >> 1) & 1, status, FLA_ERR_TIMEOUT)) dead = true;
   const uint32_t pp = sb + sP + b * 16384;
-  const Operand opPh{pp, 8192, 0}, opPl{pp + 8192, 8192, 0};
+  const Operand opPh{pp, 1024, 3}, opPl{pp + 8192, 1024, 3};   // P in strips of 8 columns: N = rows i, reduction along j
   mma_tile_ts(tbase + tVN, tbase + tZAh, opPh, 64, 4, false, lead);
   mma_tile_ts(tbase + tVN, tbase + tZAl, opPh, 64, 4, true, lead);
   mma_tile_ts(tbase + tVN, tbase + tZAh, opPl, 64, 4, true, lead);

@@ -210,10 +210,13 @@ FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* a
  *   gam   [B, T, HV] f32      out: chunk-local cumulative sum of g      (saved for backward)
  *   x_inv [chunks * HV * 8192] bf16 out: X = (I + strict_tril(beta_i exp(gam_i-gam_j) k_i.k_j))^-1 per (chunk, head), as a bf16 value
  *          and a bf16 residual (4096 elements each) in strips of 8 rows: element [r/8][c][r%8] = X[r][c]; rows past the chunk are zero
- *   s_img  [chunks * HV * (V/64) * 16384] bf16, optional out (for backward): per (chunk, head) the state at chunk start as
- *          V/64 (64-column blocks of V) x 2 (hi, lo = bf16 residual) swizzled 128x64 operand panels
- *   vn_img [chunks * HV * (V/64) * 8192] bf16, optional out (for backward): v_new, V/64 x 2 (hi, lo = bf16 residual) 64x64 panels
- *   p_img  [chunks * HV * 8192] bf16, optional out (for backward): tril(Q K^T * decay), 2 (hi, lo) 64x64 panels;
+ *   s_img  [chunks * HV * (V/64) * 16384] bf16, optional out (for backward): per (chunk, head, 64-channel half of V) the state at
+ *          chunk start as a bf16 value and a bf16 residual, each 128 key dims x 64 channels in strips of 8 key dims
+ *          (element [k/8][channel][k%8])
+ *   vn_img [chunks * HV * (V/64) * 8192] bf16, optional out (for backward): v_new per half, value and residual, each 64 tokens x
+ *          64 channels in strips of 8 tokens (element [t/8][channel][t%8])
+ *   p_img  [chunks * HV * 8192] bf16, optional out (for backward): tril(Q K^T * decay) as a bf16 value and a bf16 residual,
+ *          each 64x64 in strips of 8 columns (element [j/8][i][j%8] = P[i][j]);
  *          when absent the forward keeps these panels in its workspace
  *          (s_img, vn_img, p_img are opaque to the caller: produced here, consumed by fla_b200_gdn_chunk_bwd)
  *   cu_seqlens int32 [N+1] device (requires B == 1) with chunk_offsets int32 [N+1] device (prefix sum of
