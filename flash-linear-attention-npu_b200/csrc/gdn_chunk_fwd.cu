@@ -118,6 +118,10 @@ __global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams 
   const bool kside = row >= 64;
   const int tok = row & 63;
   const int j0 = half * 32;                         // my 32 columns
+  // the gate / beta values of a head are requested one head ahead (and those of the first head before the product is waited for)
+  auto fetch_g = [&](int hv) { return (warp < 2 && tok < rows) ? ld_scalar(p.g, (tok0 + tok) * p.g_st + hv, p.g_is_f32) : 0.f; };
+  auto fetch_b = [&](int hv) { return (kside && tok < rows) ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f; };
+  float g_next = fetch_g(hk * G), b_next = fetch_b(hk * G);
   const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
   tc_fence_after();
   float sc[32];   // my half of row `tok` of Q K^T (q side) or K K^T (k side)
@@ -134,9 +138,13 @@ __global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams 
     const int hv = hk * G + h;
     const int64_t cidx = (int64_t(sq.cbase) + blockIdx.x) * p.HV + hv;
     // chunk-local cumulative sum of g (warps 0 and 1: the q-side rows of the first column half)
-    float gv = 0.f;
+    float gv = g_next;
+    const float bi = b_next;
+    if (h + 1 < G) {
+      g_next = fetch_g(hv + 1);
+      b_next = fetch_b(hv + 1);
+    }
     if (warp < 2) {
-      gv = tok < rows ? ld_scalar(p.g, (tok0 + tok) * p.g_st + hv, p.g_is_f32) : 0.f;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float up = __shfl_up_sync(0xffffffffu, gv, o);
@@ -144,7 +152,6 @@ __global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams 
       }
       if (lane == 31) wsum_s[warp] = gv;
     }
-    const float bi = (kside && tok < rows) ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
     __syncthreads();
     if (warp < 2) {
       if (warp == 1) gv += wsum_s[0];
