@@ -202,11 +202,13 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p, const __g
     mma_tile(tbase, aL, bH, 128, 64, 8, true);
     mma_commit(&bar);
   }
-  const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
-  tc_fence_after();
   // 5. q-side rows: P = tril(Aqk) written straight into its split panel image;
   //    k-side rows: Akk^T = (beta_i Kp Kn^T)^T for the inverse kernel (coalesced along i)
   const int quad = warp & 3, half = warp >> 2, row = quad * 32 + lane, tok = row & 63;
+  // requested before the product is waited for
+  const float bi = (quad >= 2 && tok < rows) ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
+  const bool ok = mbar_wait(&bar, 0, p.status, FLA_ERR_TIMEOUT);
+  tc_fence_after();
   if (ok) {
     float sc[32];
     tmem_ld32(tmem_addr(tbase, quad * 32, half * 32), sc);
@@ -224,7 +226,6 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaParams p, const __g
         *reinterpret_cast<uint4*>(img + 8192 + off) = lo;
       }
     } else {
-      const float bi = tok < rows ? ld_scalar(p.beta, (tok0 + tok) * p.beta_st + hv, p.beta_is_f32) : 0.f;
       float* at = p.at + cidx * (kC * kC);
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) {
