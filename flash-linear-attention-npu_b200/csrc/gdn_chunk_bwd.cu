@@ -46,6 +46,7 @@ struct GdnBwdParams {
   int64_t total_tokens;
   int N, T, HK, HV, beta_is_f32, grads_f32;
   int V, nvb;          // value head dim (128 or 256) and its number of 64-column blocks
+  int n0;              // first sequence of this launch (the backward may be launched as two halves of the batch)
   float scale;
   int* status;
 };
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   __shared__ __align__(8) uint64_t mma_bar, load_bar, qk_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int hk = blockIdx.y, n = blockIdx.z;
+  const int hk = blockIdx.y, n = blockIdx.z + p.n0;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   const int c = blockIdx.x;
   if (c >= sq.nt) return;
@@ -463,8 +464,48 @@ static int check_tok3(const fla_tensor_t& t, int64_t B, int64_t T, int64_t heads
   return FLA_OK;
 }
 
-extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, void* workspace, uint64_t workspace_bytes,
-                                              void* stream) {
+#include <mutex>
+namespace {
+// A second stream (high priority) with fork / join events for every caller stream that has used the backward, per device.
+struct AuxStream {
+  cudaStream_t user = nullptr, s = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  std::mutex mu;
+};
+constexpr int kAuxPerDevice = 8;
+std::mutex g_aux_mu;
+AuxStream g_aux[64][kAuxPerDevice];
+int g_aux_used[64] = {};
+int g_sm_count[64] = {};
+
+int sm_count(int dev) {
+  std::lock_guard<std::mutex> lk(g_aux_mu);
+  if (!g_sm_count[dev] && cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) g_sm_count[dev] = 1 << 30;
+  return g_sm_count[dev];
+}
+AuxStream* aux_stream_for(int dev, cudaStream_t user) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(user, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+  std::lock_guard<std::mutex> lk(g_aux_mu);
+  for (int i = 0; i < g_aux_used[dev]; ++i)
+    if (g_aux[dev][i].user == user) return g_aux[dev][i].s ? &g_aux[dev][i] : nullptr;
+  if (g_aux_used[dev] == kAuxPerDevice) return nullptr;
+  AuxStream& a = g_aux[dev][g_aux_used[dev]++];
+  a.user = user;
+  int lo = 0, hi = 0;
+  cudaDeviceGetStreamPriorityRange(&lo, &hi);
+  if (cudaStreamCreateWithPriority(&a.s, cudaStreamNonBlocking, hi) != cudaSuccess ||
+      cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&a.join, cudaEventDisableTiming) != cudaSuccess) {
+    a.s = nullptr;   // remembered as unavailable: the single-stream path is used
+    return nullptr;
+  }
+  return &a;
+}
+}  // namespace
+
+static int gdn_chunk_bwd_impl(const fla_gdn_chunk_bwd_args* a, void* workspace, uint64_t workspace_bytes, void* stream,
+                              bool allow_split) {
   if (!a) return FLA_ERR_NULL;
   int64_t total_chunks; int N, max_len;
   int st = bwd_geometry(a, &total_chunks, &N, &max_len);
@@ -552,18 +593,51 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, v
       make_row_tile_map(&tm_v, p.v, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.v_sh), uint64_t(p.v_st)) ||
       make_row_tile_map(&tm_d, p.dO, uint64_t(V), uint64_t(HV), uint64_t(B * T), uint64_t(p.do_sh), uint64_t(p.do_st)))
     return FLA_ERR_CUDA;
+  const int nt_max = (max_len + kC - 1) / kC;
+  auto launch_scan = [&](const GdnBwdParams& pp, int nseq, cudaStream_t st) {
+    gdn_scan_bwd_kernel<<<dim3(unsigned(V / 128), unsigned(HV), nseq), kScanThreads, kScanBwdSmem + 1024, st>>>(pp, tm_q, tm_k, tm_v, tm_d);
+  };
+  auto launch_par = [&](const GdnBwdParams& pp, int nseq, cudaStream_t st) {
+    if (nvb == 2) gdn_bwd_par_kernel<2><<<dim3(nt_max, unsigned(HK), nseq), 256, kParSmem + 1024, st>>>(pp, tm_q, tm_k);
+    else gdn_bwd_par_kernel<4><<<dim3(nt_max, unsigned(HK), nseq), 256, kParSmem + 1024, st>>>(pp, tm_q, tm_k);
+  };
+  // The reverse scan launches one CTA per (sequence, value head, 128 channels) and each needs a whole SM: when there are
+  // more chains than SMs the last round leaves SMs idle for the length of a chain.  The batch is then launched as two
+  // halves on two streams, so that the chunk-parallel kernel of the first half fills the SMs the second half's scan
+  // leaves free.  Not while per-kernel timing is on (its events bracket single launches), not during stream capture, not
+  // for the allocation-free entry (creating the second stream may allocate).
+  AuxStream* aux = nullptr;
+  if (allow_split && N >= 2 && int64_t(V / 128) * HV * N > sm_count(dev) && !kernel_timing_enabled()) aux = aux_stream_for(dev, cs);
+  if (aux) {
+    std::lock_guard<std::mutex> lk(aux->mu);   // the fork / join events are shared by the callers of this stream
+    const int n1 = N / 2;
+    GdnBwdParams p2 = p;
+    p2.n0 = n1;
+    bool okc = cudaEventRecord(aux->fork, cs) == cudaSuccess && cudaStreamWaitEvent(aux->s, aux->fork, 0) == cudaSuccess;
+    if (!okc) return FLA_ERR_CUDA;
+    launch_scan(p, n1, cs);
+    launch_scan(p2, N - n1, aux->s);
+    launch_par(p, n1, cs);
+    launch_par(p2, N - n1, aux->s);
+    okc = cudaEventRecord(aux->join, aux->s) == cudaSuccess && cudaStreamWaitEvent(cs, aux->join, 0) == cudaSuccess;
+    if (!okc) return FLA_ERR_CUDA;
+    return cuda_status(cudaGetLastError());
+  }
   {
     KernelTimer kt("gdn_bwd_dhu", cs);
-    gdn_scan_bwd_kernel<<<dim3(unsigned(V / 128), unsigned(HV), N), kScanThreads, kScanBwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v, tm_d);
+    launch_scan(p, N, cs);
   }
   if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
-  const int nt_max = (max_len + kC - 1) / kC;
   {
     KernelTimer kt("gdn_bwd_par", cs);
-    if (nvb == 2) gdn_bwd_par_kernel<2><<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p, tm_q, tm_k);
-    else gdn_bwd_par_kernel<4><<<dim3(nt_max, unsigned(HK), N), 256, kParSmem + 1024, cs>>>(p, tm_q, tm_k);
+    launch_par(p, N, cs);
   }
   return cuda_status(cudaGetLastError());
+}
+
+extern "C" FLA_API int fla_b200_gdn_chunk_bwd(const fla_gdn_chunk_bwd_args* a, void* workspace, uint64_t workspace_bytes,
+                                              void* stream) {
+  return gdn_chunk_bwd_impl(a, workspace, workspace_bytes, stream, true);
 }
 
 // ----------------------------------------------------------------------------- allocation-free variant
@@ -611,7 +685,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_bwd_noalloc(const fla_gdn_chunk_bwd_ar
   }
   // The regular entry point clears the status block at the head of the scratch on `stream` and overwrites
   // every other byte it later reads, so nothing else of the previous call's contents matters.
-  return fla_b200_gdn_chunk_bwd(a, scratch, kStaticScratchBytes, stream);
+  return gdn_chunk_bwd_impl(a, scratch, kStaticScratchBytes, stream, false);   // one stream: creating a second one may allocate
 }
 
 // The status word of the allocation-free entry lives at the head of the built-in array, which the caller cannot

@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
   __shared__ __align__(8) uint64_t mma_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2], d_bar[2];
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
+  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z + p.n0;
   const int hk = hv / (p.HV / p.HK);
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   const uint32_t sb = smem_u32(smem);
