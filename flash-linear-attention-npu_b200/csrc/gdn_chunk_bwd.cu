@@ -26,6 +26,7 @@
 #include "gdn_common.cuh"
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
+#include "aux_stream.h"
 #include "tensor_map.h"
 
 namespace fla {
@@ -464,45 +465,6 @@ static int check_tok3(const fla_tensor_t& t, int64_t B, int64_t T, int64_t heads
   return FLA_OK;
 }
 
-#include <mutex>
-namespace {
-// A second stream (high priority) with fork / join events for every caller stream that has used the backward, per device.
-struct AuxStream {
-  cudaStream_t user = nullptr, s = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr;
-  std::mutex mu;
-};
-constexpr int kAuxPerDevice = 8;
-std::mutex g_aux_mu;
-AuxStream g_aux[64][kAuxPerDevice];
-int g_aux_used[64] = {};
-int g_sm_count[64] = {};
-
-int sm_count(int dev) {
-  std::lock_guard<std::mutex> lk(g_aux_mu);
-  if (!g_sm_count[dev] && cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) g_sm_count[dev] = 1 << 30;
-  return g_sm_count[dev];
-}
-AuxStream* aux_stream_for(int dev, cudaStream_t user) {
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(user, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
-  std::lock_guard<std::mutex> lk(g_aux_mu);
-  for (int i = 0; i < g_aux_used[dev]; ++i)
-    if (g_aux[dev][i].user == user) return g_aux[dev][i].s ? &g_aux[dev][i] : nullptr;
-  if (g_aux_used[dev] == kAuxPerDevice) return nullptr;
-  AuxStream& a = g_aux[dev][g_aux_used[dev]++];
-  a.user = user;
-  int lo = 0, hi = 0;
-  cudaDeviceGetStreamPriorityRange(&lo, &hi);
-  if (cudaStreamCreateWithPriority(&a.s, cudaStreamNonBlocking, hi) != cudaSuccess ||
-      cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&a.join, cudaEventDisableTiming) != cudaSuccess) {
-    a.s = nullptr;   // remembered as unavailable: the single-stream path is used
-    return nullptr;
-  }
-  return &a;
-}
-}  // namespace
 
 static int gdn_chunk_bwd_impl(const fla_gdn_chunk_bwd_args* a, void* workspace, uint64_t workspace_bytes, void* stream,
                               bool allow_split) {

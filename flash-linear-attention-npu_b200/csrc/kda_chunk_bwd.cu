@@ -23,6 +23,7 @@
 #include "gdn_common.cuh"
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
+#include "aux_stream.h"
 #include "kda_common.cuh"
 #include "tensor_map.h"
 
@@ -43,6 +44,7 @@ struct KdaBwdParams {
   int64_t dq_st, dq_sh, dk_st, dk_sh, dv_st, dv_sh, dg_st, dg_sh;
   int64_t total_tokens;
   int N, T, HK, HV, beta_is_f32, grads_f32;
+  int n0;              // first sequence of this launch (the backward may be launched as two halves of the batch)
   int V, nvb;          // value head dim (128 or 256) and its number of 64-column blocks
   float scale;
   int* status;
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_dhu_kernel(KdaBwdParams p) {
   __shared__ __align__(8) uint64_t bar, pbar, qk_bar, kn_bar, x_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
+  const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z + p.n0;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   const int quad = warp & 3, half = warp >> 2;   // TMEM lane quadrant; which 32 of the tile's 64 columns
   const bool kside = quad >= 2;
@@ -409,7 +411,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
   __shared__ __align__(8) uint64_t mma_bar, load_bar, img_bar, gk_bar;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int hk = blockIdx.y, n = blockIdx.z;
+  const int hk = blockIdx.y, n = blockIdx.z + p.n0;
   const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
   const int c = blockIdx.x;
   if (c >= sq.nt) return;
@@ -914,17 +916,40 @@ extern "C" FLA_API int fla_b200_kda_chunk_bwd(const fla_kda_chunk_bwd_args* a, v
     if (cudaFuncSetAttribute(kda_bwd_par_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kKdaParSmem) + 1024) != cudaSuccess) return FLA_ERR_CUDA;
     attr_done_dev[dev] = true;
   }
-  {
-    KernelTimer kt("kda_bwd_dhu", cs);
-    kda_bwd_dhu_kernel<<<dim3(unsigned(nvb), unsigned(HV), N), 256, kKdaDhuSmem + 1024, cs>>>(p);
-  }
-  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   CUtensorMap tm_gk;
   if (make_row_tile_map_f32(&tm_gk, p.gk, kK, uint64_t(HV), uint64_t(B * T), uint64_t(kK), uint64_t(HV) * kK)) return FLA_ERR_CUDA;
+  auto launch_scan = [&](const KdaBwdParams& pp, int nseq, cudaStream_t st_) {
+    kda_bwd_dhu_kernel<<<dim3(unsigned(nvb), unsigned(HV), nseq), 256, kKdaDhuSmem + 1024, st_>>>(pp);
+  };
+  auto launch_par = [&](const KdaBwdParams& pp, int nseq, cudaStream_t st_) {
+    if (nvb == 2) kda_bwd_par_kernel<2><<<dim3(nt_max, unsigned(HK), nseq), 256, kKdaParSmem + 1024, st_>>>(pp, tm_gk);
+    else kda_bwd_par_kernel<4><<<dim3(nt_max, unsigned(HK), nseq), 256, kKdaParSmem + 1024, st_>>>(pp, tm_gk);
+  };
+  // more scan chains (one CTA per SM each) than SMs: two halves of the batch on two streams, so that the chunk-parallel
+  // kernel of the first half fills the SMs the second half's scan leaves idle (aux_stream.h)
+  AuxStream* aux = nullptr;
+  if (N >= 2 && int64_t(nvb) * HV * N > sm_count(dev) && !kernel_timing_enabled()) aux = aux_stream_for(dev, cs);
+  if (aux) {
+    std::lock_guard<std::mutex> lk(aux->mu);
+    const int n1 = N / 2;
+    KdaBwdParams p2 = p;
+    p2.n0 = n1;
+    if (cudaEventRecord(aux->fork, cs) != cudaSuccess || cudaStreamWaitEvent(aux->s, aux->fork, 0) != cudaSuccess) return FLA_ERR_CUDA;
+    launch_scan(p, n1, cs);
+    launch_scan(p2, N - n1, aux->s);
+    launch_par(p, n1, cs);
+    launch_par(p2, N - n1, aux->s);
+    if (cudaEventRecord(aux->join, aux->s) != cudaSuccess || cudaStreamWaitEvent(cs, aux->join, 0) != cudaSuccess) return FLA_ERR_CUDA;
+    return cuda_status(cudaGetLastError());
+  }
+  {
+    KernelTimer kt("kda_bwd_dhu", cs);
+    launch_scan(p, N, cs);
+  }
+  if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   {
     KernelTimer kt("kda_bwd_par", cs);
-    if (nvb == 2) kda_bwd_par_kernel<2><<<dim3(nt_max, unsigned(HK), N), 256, kKdaParSmem + 1024, cs>>>(p, tm_gk);
-    else kda_bwd_par_kernel<4><<<dim3(nt_max, unsigned(HK), N), 256, kKdaParSmem + 1024, cs>>>(p, tm_gk);
+    launch_par(p, N, cs);
   }
   return cuda_status(cudaGetLastError());
 }
