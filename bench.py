@@ -294,8 +294,15 @@ class Workload:
         return self.graph_out
 
     def launches_per_step(self):
-        return {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1, "conv_bwd": 2,
-                "gdn_stage_fwd": 6, "gdn_stage_fwd_bwd": 13}[self.name]
+        n = {"gdn_fwd_bwd": 5, "gdn_fwd_conv": 4, "kda_fwd": 3, "kda_fwd_bwd": 5, "decode": 2, "conv_prefill": 1, "conv_bwd": 2,
+             "gdn_stage_fwd": 6, "gdn_stage_fwd_bwd": 13}[self.name]
+        c = self.cfg
+        if self.name in ("gdn_fwd_bwd", "kda_fwd_bwd") and c["B"] >= 2:
+            # the backward launches its two kernels once per half of the batch when its scan has more chains than SMs
+            chains = c["B"] * c["HV"] * (c["V"] // (128 if self.name == "gdn_fwd_bwd" else 64))
+            if chains > torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count:
+                n += 2
+        return n
 
     def kernel_names(self):
         return {"gdn_fwd_bwd": ["gdn_prep", "tri_inverse", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par"],
