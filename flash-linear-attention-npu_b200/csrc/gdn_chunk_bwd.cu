@@ -69,6 +69,7 @@ constexpr uint32_t rOffSH = 81920, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 1
 constexpr uint32_t rOffPAH = 147456, rOffPAL = 163840;   // [dP ; dAt] hi / lo (128 rows x 64)
 constexpr uint32_t kParSmem = 180224;
 constexpr uint32_t rColQK = 0, rColDV = 64, rColTA = 128, rColTB = 256;
+constexpr uint32_t rColAcc = 384;   // running dq (q-side rows) / dk (k-side rows) over the value heads of the group: 128 columns
 constexpr uint32_t kStepBytes = 16384 + 16384 + 32768 + 32768;
 
 __device__ __forceinline__ void row_dot64(const uint8_t* pan0, uint32_t panel_stride, int row, int col0, const float* x,
@@ -173,9 +174,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   const Operand opPAH{sb + rOffPAH, 16384, 0}, opPAL{sb + rOffPAL, 16384, 0};            // [dP; dAt], reduction over j
   const Operand opPATh{sb + rOffPAH - 8192, 8192, 1}, opPATl{sb + rOffPAL - 8192, 8192, 1};  // its transpose, valid rows 64..127
 
-  float acc_out[64];  // running dq (q-side rows) or dk (k-side rows), this thread's 64 key-dim columns
-#pragma unroll
-  for (int i = 0; i < 64; ++i) acc_out[i] = 0.f;
+  // The running dq (q-side rows) / dk (k-side rows) of the group lives in the last 128 tensor-memory columns, this thread's
+  // 64 key-dim columns at rColAcc + half * 64: in registers it would leave none for the issuing code of warp 0.
 
   // dg / dbeta rows of one value head from its row reductions (threads 0..63 = the two warps that own the 64 rows).
   // dg = reverse chunk-local cumulative sum of dgam; the last row additionally carries
@@ -370,8 +370,26 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     }
     float xdx = 0.f;  // q.dq (q-side) or k.dk (k-side) over my columns
     row_dot64(smem + rOffQK, rQKPanel, row, half * 64, part, xdx);
+    if (h > 0) {
+      float t[64];
+      tmem_ld_row64(trow + rColAcc + half * 64, t);
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc_out[i] += part[i];
+      for (int i = 0; i < 64; ++i) part[i] += t[i];
+    }
+    if (h + 1 < G) tmem_st_row64(trow + rColAcc + half * 64, part);
+    else if (tok < rows) {   // the last head: the rows are complete
+      void* base = kside ? p.dk : p.dq;
+      const int64_t off = kside ? (tok0 + tok) * p.dk_st + hk * p.dk_sh + half * 64 : (tok0 + tok) * p.dq_st + hk * p.dq_sh + half * 64;
+      if (p.grads_f32) {
+        float* dst = static_cast<float*>(base) + off;
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(part[i], part[i + 1], part[i + 2], part[i + 3]);
+      } else {
+        bf16* dst = static_cast<bf16*>(base) + off;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(part + ch * 8);
+      }
+    }
     if (!kside) {
       red[0][half][tok] = xdx;
     } else {
@@ -386,19 +404,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   }
   if (__syncthreads_and(ok) && tid < kC) finish_head(hk * G + G - 1, (G - 1) & 1, bz_prev);
 
-  if (ok && tok < rows) {
-    void* base = kside ? p.dk : p.dq;
-    const int64_t off = kside ? (tok0 + tok) * p.dk_st + hk * p.dk_sh + half * 64 : (tok0 + tok) * p.dq_st + hk * p.dq_sh + half * 64;
-    if (p.grads_f32) {
-      float* dst = static_cast<float*>(base) + off;
-#pragma unroll
-      for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(acc_out[i], acc_out[i + 1], acc_out[i + 2], acc_out[i + 3]);
-    } else {
-      bf16* dst = static_cast<bf16*>(base) + off;
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(acc_out + ch * 8);
-    }
-  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 512);
