@@ -71,6 +71,11 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, u
                "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// Asks for a global range to be brought into L2 (no completion to wait for): a later bulk_load of it then pays the L2 latency
+// instead of the DRAM one.  For consumers that can only issue the load itself once their single buffer is free.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
                : "memory");

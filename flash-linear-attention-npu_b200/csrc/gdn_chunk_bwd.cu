@@ -130,6 +130,16 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     bulk_load(sb + rOffSH, p.s_img + blk * 32768 + hf * 16384, 32768, &load_bar);      // [value | residual], 16 strips each
     bulk_load(sb + rOffDSH, p.ds_img + blk * 32768 + hf * 16384, 32768, &load_bar);
   };
+  // the same four pieces asked into L2 one step ahead: the buffer they will land in is still being read, so the load itself
+  // cannot be issued yet, but the DRAM part of its latency can be spent meanwhile
+  auto prefetch_loads = [&](int hv, int vb) {
+    const int64_t blk = ((int64_t(sq.cbase) + c) * p.HV + hv) * (NVB / 2) + (vb >> 1);
+    const int64_t hf = vb & 1;
+    bulk_prefetch_l2(p.dz_img + blk * 16384 + hf * 8192, 16384);
+    bulk_prefetch_l2(p.vn_img + blk * 16384 + hf * 8192, 16384);
+    bulk_prefetch_l2(p.s_img + blk * 32768 + hf * 16384, 32768);
+    bulk_prefetch_l2(p.ds_img + blk * 32768 + hf * 16384, 32768);
+  };
   if (tid == 0) {
     mbar_init(&mma_bar, 1);
     mbar_init(&load_bar, 1);
@@ -258,6 +268,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
         mma_tile(tbase + rColTB, opVNaH, opDSL, 128, 128, 4, true);
         mma_tile(tbase + rColTB, opVNaL, opDSH, 128, 128, 4, true);
         mma_commit(&mma_bar);
+        if (vb + 1 < NVB) prefetch_loads(hv, vb + 1);
+        else if (h + 1 < G) prefetch_loads(hv + 1, 0);
       }
       if (h > 0 && vb == 0 && tid < kC) finish_head(hv - 1, hb ^ 1, bz_prev);   // while the MMAs run
       // <S, dS'> over this V block while the MMAs run (elementwise on the raw panel images)
