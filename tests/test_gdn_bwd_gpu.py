@@ -140,3 +140,44 @@ def test_empty_sequence_in_a_packed_batch(case):
     assert torch.equal(g_a[5], g_b[5][keep])
     for e in empty:
         assert torch.equal(ht_b[e].cpu(), h0[e]) and torch.equal(g_b[5][e].cpu(), dht[e])
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_two_half_launch_matches_single_launch(packed):
+    """With more scan chains than SMs the backward launches the batch as two halves on two streams; with per-kernel
+    timing on it launches it whole on one.  Same inputs, both ways: bit-identical gradients (odd number of sequences,
+    one of them empty in the packed case)."""
+    import fla_b200
+    from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
+    lib = fla_b200.load_library()
+    HK, HV = 16, 32
+    if packed:
+        cu = [0, 70, 71, 71, 200, 264, 330, 331]        # 7 sequences x 32 heads = 224 chains
+        inp = oracle.make_gdn_inputs(1, cu[-1], HK, HV, seed=31)
+        N = len(cu) - 1
+        gen = torch.Generator().manual_seed(32)
+        inp["h0"] = 0.1 * torch.randn(N, HV, 128, 128, generator=gen)
+        inp["dht"] = 0.1 * torch.randn(N, HV, 128, 128, generator=gen)
+        cu_t = torch.tensor(cu, dtype=torch.int32)
+    else:
+        inp = oracle.make_gdn_inputs(5, 200, HK, HV, seed=33)   # 5 x 32 = 160 chains
+        cu_t = None
+    assert torch.cuda.get_device_properties(0).multi_processor_count < 160
+    d = {n: t.cuda() for n, t in inp.items() if t is not None}
+
+    def run():
+        o, ht, gr = chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
+                                                   dht=d["dht"], cu_seqlens=cu_t, grad_dtype=torch.float32)
+        torch.cuda.synchronize()
+        return gr
+    split = run()
+    lib.fla_b200_kernel_timing_enable(1)
+    try:
+        whole = run()
+    finally:
+        lib.fla_b200_kernel_timing_enable(0)
+    for name, a, b in zip(NAMES + ("dh0",), split, whole):
+        assert torch.equal(a, b), name
+    again = run()
+    for name, a, b in zip(NAMES + ("dh0",), split, again):
+        assert torch.equal(a, b), name
