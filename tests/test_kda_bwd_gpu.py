@@ -241,3 +241,31 @@ def test_kda_qk_l2norm_in_kernel():
     assert_close("o", o, ref.detach(), TOL)
     assert_close("dq", qd.grad, qr.grad, TOL, stored_bf16=True)
     assert_close("dk", kd.grad, kr.grad, TOL, stored_bf16=True)
+
+
+@pytest.mark.parametrize("recompute", [True, False])
+def test_kda_two_half_launch_matches_single_launch(recompute):
+    """More scan chains than SMs: the KDA backward launches the batch as two halves on two streams; with per-kernel
+    timing on it launches it whole.  Bit-identical gradients either way (three sequences: halves of one and two)."""
+    import fla_b200
+    from fla_b200.ops import chunk_kda_fwd_bwd
+    lib = fla_b200.load_library()
+    B, T, H = 3, 200, 32          # 2 blocks of V x 32 heads x 3 sequences = 192 chains
+    assert torch.cuda.get_device_properties(0).multi_processor_count < 192
+    inp = oracle.make_kda_inputs(B, T, H, H, seed=41)
+    d = {n: t.cuda() for n, t in inp.items() if t is not None}
+
+    def run():
+        o, ht, gr = chunk_kda_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], grad_dtype=torch.float32,
+                                      disable_recompute=not recompute)
+        torch.cuda.synchronize()
+        return [t for t in gr if t is not None]
+    split = run()
+    lib.fla_b200_kernel_timing_enable(1)
+    try:
+        whole = run()
+    finally:
+        lib.fla_b200_kernel_timing_enable(0)
+    assert len(split) == len(whole) >= 5
+    for i, (a, b) in enumerate(zip(split, whole)):
+        assert torch.equal(a, b), i
