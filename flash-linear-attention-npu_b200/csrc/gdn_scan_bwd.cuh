@@ -206,17 +206,20 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     load_scalars(0);
     make_factors(0);
     load_scalars(1);
-    scan_sync();   // factors of the first step are visible
+    make_factors(1);
+    load_scalars(2);
+    scan_sync();   // factors of the first two steps are visible
     for (int s = 0; s < nt; ++s) {
       scan_sync();                                          // sync 1: step s - 1 no longer reads the other buffers
       if (lane == 0 && s + 1 < nt) issue_loads(s + 1);
       __syncwarp();
       scan_sync();                                          // sync 2
-      // not before sync 2: the epilogue warps have just handed the 64 KB dS' image to the load/store unit, and this warp's
-      // shared-memory stores and global loads would queue behind it while the whole CTA waits at the barrier
-      make_factors(s + 1);
-      load_scalars(s + 2);
       scan_sync();                                          // sync 3
+      // The factors are made two steps ahead and here, while the state-gradient update runs: the epilogue warps hand 64 KB
+      // (dS' image, before sync 1) and 32 KB ([dO | dZ] image, before sync 3) of stores to the load/store unit, and this
+      // warp's shared-memory stores and global loads queue behind them; anywhere else the whole CTA waits for it at a barrier.
+      make_factors(s + 2);                                  // buffer (s + 2) % 3 was last read by step s - 1
+      load_scalars(s + 3);
     }
     scan_sync();
     return;

@@ -197,7 +197,9 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     load_scalars(0);
     make_factors(0);
     load_scalars(1);
-    scan_sync();   // factors of chunk 0 are visible
+    make_factors(1);
+    load_scalars(2);
+    scan_sync();   // factors of chunks 0 and 1 are visible
     for (int c = 0; c < nt; ++c) {
       scan_sync();                                          // sync 1: chunk c - 1 no longer reads the other buffers
       if (lane == 0 && c + 1 < nt) {
@@ -206,12 +208,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       }
       __syncwarp();
       scan_sync();                                          // sync 2
-      // Not before sync 2: when the state image is saved, the epilogue warps have just handed 64 KB of stores to the
-      // load/store unit, and this warp's shared-memory stores and global loads would queue behind them while the
-      // whole CTA waits for it at the barrier (measured: 1.4 k cycles per chunk).
-      make_factors(c + 1);                                  // read from sync 3 of this chunk on
-      load_scalars(c + 2);
       scan_sync();                                          // sync 3
+      // The factors are made two chunks ahead and here, while the state update runs: when the images are saved the
+      // epilogue warps hand 64 KB (before sync 1) and 32 KB (before sync 3) of stores to the load/store unit, and this
+      // warp's shared-memory stores and global loads queue behind them; anywhere else the whole CTA waits for it at a
+      // barrier (measured: 1.4 k cycles per chunk when this sat between sync 1 and sync 2).
+      make_factors(c + 2);                                  // buffer (c + 2) % 3 was last read for chunk c - 1's output rows
+      load_scalars(c + 3);
     }
     scan_sync();   // matches the epilogue warps' barrier before the TMEM is released
     return;
