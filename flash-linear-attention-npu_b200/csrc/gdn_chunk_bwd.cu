@@ -512,7 +512,7 @@ static int gdn_chunk_bwd_impl(const fla_gdn_chunk_bwd_args* a, void* workspace, 
     return FLA_ERR_SHAPE;
   if (X.dtype != FLA_BF16 || X.ndim != 1 || X.shape[0] != total_chunks * HV * 8192 || !aligned16(X.data))
     return FLA_ERR_SHAPE;
-  if (a->p_img.dtype != FLA_BF16 || a->p_img.ndim != 1 || a->p_img.shape[0] != total_chunks * HV * 8192 || !aligned16(a->p_img.data))
+  if (a->p_img.dtype != FLA_BF16 || a->p_img.ndim != 1 || a->p_img.shape[0] != total_chunks * HV * kPImg || !aligned16(a->p_img.data))
     return FLA_ERR_SHAPE;
   if (a->s_img.dtype != FLA_BF16 || a->s_img.ndim != 1 || a->s_img.shape[0] != total_chunks * HV * nvb * kSImg || !aligned16(a->s_img.data))
     return FLA_ERR_SHAPE;

@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams 
       // my half of the P row as split bf16, in strips of 8 columns ([j / 8][row i][16 bytes], value then residual): the 16
       // bytes a thread stores for a strip lie next to its neighbours' (512 contiguous bytes per warp store), and the scans
       // read the image as an operand with the reduction along j (forward) or along i (reverse) by the descriptor alone
-      uint8_t* img = reinterpret_cast<uint8_t*>(p.p_img + cidx * 8192);
+      uint8_t* img = reinterpret_cast<uint8_t*>(p.p_img + cidx * kPImg);
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         float t[8];
@@ -181,6 +181,15 @@ __global__ void __launch_bounds__(kPrepThreads, 4) gdn_prep_kernel(GdnFwdParams 
         *reinterpret_cast<uint4*>(img + 8192 + off) = lo;
       }
     } else {
+      if (half == 0) {   // the chunk's per-token factors for the scans, behind the P tile (rows past the end: beta = 0, gam = gam_L)
+        ScanFactors* f = reinterpret_cast<ScanFactors*>(reinterpret_cast<uint8_t*>(p.p_img + cidx * kPImg) + kPTileBytes);
+        const float eg = __expf(gam_i), gl = gam_s[rows - 1];
+        f->b[tok] = bi;
+        f->bg[tok] = bi * eg;
+        f->se[tok] = p.scale * eg;
+        f->dk[tok] = __expf(gl - gam_i);
+        if (tok == 0) f->dl = __expf(gl);
+      }
       // A^T[j][i] = beta_i exp(gam_i - gam_j) (k_i . k_j) for j < i, written coalesced along i
       float* at = p.at + cidx * (kC * kC);
 #pragma unroll
@@ -222,7 +231,7 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd_workspace_size(const fla_gdn_chunk
   if (a->cu_seqlens.data) chunks = a->total_chunks;
   if (chunks <= 0) return FLA_ERR_VALUE;
   // status block + A^T scratch for the inverse + P panels (unless the caller keeps them for the backward)
-  *bytes = 256 + uint64_t(chunks) * a->v.shape[2] * (kC * kC * 4 + (a->p_img.data ? 0 : 8192 * 2));
+  *bytes = 256 + uint64_t(chunks) * a->v.shape[2] * (kC * kC * 4 + (a->p_img.data ? 0 : kPImgBytes));
   return FLA_OK;
 }
 
@@ -298,11 +307,11 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   p.status = static_cast<int*>(workspace);
   {
     const uint64_t per = uint64_t(total_chunks) * HV;
-    if (workspace_bytes < 256 + per * (kC * kC * 4 + (a->p_img.data ? 0 : 8192 * 2))) return FLA_ERR_WORKSPACE;
+    if (workspace_bytes < 256 + per * (kC * kC * 4 + (a->p_img.data ? 0 : kPImgBytes))) return FLA_ERR_WORKSPACE;
     p.at = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
     if (a->p_img.data) {
       const fla_tensor_t& pi = a->p_img;
-      if (pi.dtype != FLA_BF16 || pi.ndim != 1 || pi.shape[0] != int64_t(per) * 8192 || !aligned16(pi.data)) return FLA_ERR_SHAPE;
+      if (pi.dtype != FLA_BF16 || pi.ndim != 1 || pi.shape[0] != int64_t(per) * kPImg || !aligned16(pi.data)) return FLA_ERR_SHAPE;
       p.p_img = static_cast<bf16*>(pi.data);
     } else {
       p.p_img = reinterpret_cast<bf16*>(static_cast<uint8_t*>(workspace) + 256 + per * kC * kC * 4);

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ ScanFactors fac[3];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2], d_bar[2];
+  __shared__ __align__(8) uint64_t mma_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2], d_bar[2], f_bar[3];
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z + p.n0;
@@ -133,6 +133,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       mbar_init(&v_bar[i], 1);
       mbar_init(&d_bar[i], 1);
     }
+    for (int i = 0; i < 3; ++i) mbar_init(&f_bar[i], 1);
     mbar_init_fence();
   }
   write_identity_panel(smem + bI, tid, kScanThreads);
@@ -158,41 +159,20 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       tma_load_tile(sb + bD + b * 16384, &tm_d, vb * 128, hv, row0, &d_bar[b]);
       tma_load_tile(sb + bD + b * 16384 + 8192, &tm_d, vb * 128 + 64, hv, row0, &d_bar[b]);
       mbar_arrive_expect_tx(&p_bar[b], 16384);
-      bulk_load(sb + bP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
+      bulk_load(sb + bP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * kPImg, 16384, &p_bar[b]);
       mbar_arrive_expect_tx(&x_bar[b], 16384);
       bulk_load(sb + bX + b * 16384, p.X + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &x_bar[b]);
       mbar_arrive_expect_tx(&v_bar[b], 16384);
       tma_load_tile(sb + bV + b * 16384, &tm_v, vb * 128, hv, row0, &v_bar[b]);
       tma_load_tile(sb + bV + b * 16384 + 8192, &tm_v, vb * 128 + 64, hv, row0, &v_bar[b]);
     };
-    float pf_g[2] = {0.f, 0.f}, pf_b[2] = {0.f, 0.f}, pf_gl = 0.f;
-    auto load_scalars = [&](int s) {
+    // the per-token factors of step s (chunk nt - 1 - s; made by the prep kernel, behind the chunk's P tile) into buffer s % 3
+    auto load_factors = [&](int s) {
       if (s < nt) {
         const int c = nt - 1 - s;
-        const int rows = min(kC, sq.len - c * kC);
-        const int64_t tok0 = int64_t(sq.bos) + c * kC;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int t = lane + 32 * j;
-          pf_g[j] = p.gam[(tok0 + min(t, rows - 1)) * p.HV + hv];
-          pf_b[j] = t < rows ? ld_scalar(p.beta, (tok0 + t) * p.beta_st + hv, p.beta_is_f32) : 0.f;
-        }
-        pf_gl = p.gam[(tok0 + rows - 1) * p.HV + hv];
-      }
-    };
-    auto make_factors = [&](int s) {
-      if (s < nt) {
-        ScanFactors& f = fac[s % 3];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int t = lane + 32 * j;
-          const float eg = __expf(pf_g[j]);
-          f.b[t] = pf_b[j];
-          f.bg[t] = pf_b[j] * eg;
-          f.se[t] = p.scale * eg;
-          f.dk[t] = __expf(pf_gl - pf_g[j]);
-        }
-        if (lane == 0) f.dl = __expf(pf_gl);
+        mbar_arrive_expect_tx(&f_bar[s % 3], uint32_t(sizeof(ScanFactors)));
+        bulk_load(smem_u32(&fac[s % 3]), reinterpret_cast<const uint8_t*>(p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * kPImg) + kPTileBytes,
+                  uint32_t(sizeof(ScanFactors)), &f_bar[s % 3]);
       }
     };
     if (lane == 0) {
@@ -201,25 +181,20 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
       tma_prefetch_descriptor(&tm_v);
       tma_prefetch_descriptor(&tm_d);
       if (nt > 0) issue_loads(0);
+      load_factors(0);
+      load_factors(1);
     }
     __syncwarp();
-    load_scalars(0);
-    make_factors(0);
-    load_scalars(1);
-    make_factors(1);
-    load_scalars(2);
-    scan_sync();   // factors of the first two steps are visible
+    scan_sync();   // (pairs with the epilogue warps' barrier after they have loaded the final-state gradient)
     for (int s = 0; s < nt; ++s) {
       scan_sync();                                          // sync 1: step s - 1 no longer reads the other buffers
-      if (lane == 0 && s + 1 < nt) issue_loads(s + 1);
+      if (lane == 0) {
+        if (s + 1 < nt) issue_loads(s + 1);
+        load_factors(s + 2);                                // buffer (s + 2) % 3 was last read by step s - 1
+      }
       __syncwarp();
       scan_sync();                                          // sync 2
       scan_sync();                                          // sync 3
-      // The factors are made two steps ahead and here, while the state-gradient update runs: the epilogue warps hand 64 KB
-      // (dS' image, before sync 1) and 32 KB ([dO | dZ] image, before sync 3) of stores to the load/store unit, and this
-      // warp's shared-memory stores and global loads queue behind them; anywhere else the whole CTA waits for it at a barrier.
-      make_factors(s + 2);                                  // buffer (s + 2) % 3 was last read by step s - 1
-      load_scalars(s + 3);
     }
     scan_sync();
     return;
@@ -273,6 +248,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
   for (int s = 0; s < nt; ++s) {
     const int c = nt - 1 - s;
     const ScanFactors& f = fac[s % 3];
+    if (!dead && !mbar_wait(&f_bar[s % 3], (s / 3) & 1, p.status, FLA_ERR_TIMEOUT)) dead = true;   // requested two steps ago
     const int rows = min(kC, sq.len - c * kC);
     const int64_t cidx = ((int64_t(sq.cbase) + c) * p.HV + hv) * (p.V / 128) + vb;
 

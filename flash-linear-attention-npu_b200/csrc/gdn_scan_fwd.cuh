@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ ScanFactors fac[3];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) uint64_t mma_bar, o_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2];
+  __shared__ __align__(8) uint64_t mma_bar, o_bar, qk_bar[2], x_bar[2], p_bar[2], v_bar[2], f_bar[3];
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int vb = blockIdx.x, hv = blockIdx.y, n = blockIdx.z;
@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       mbar_init(&p_bar[i], 1);
       mbar_init(&v_bar[i], 1);
     }
+    for (int i = 0; i < 3; ++i) mbar_init(&f_bar[i], 1);
     mbar_init_fence();
   }
   write_identity_panel(smem + sI, tid, kScanThreads);
@@ -151,37 +152,14 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       mbar_arrive_expect_tx(&x_bar[b], 16384);
       bulk_load(sb + sX + b * 16384, p.X + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &x_bar[b]);
       mbar_arrive_expect_tx(&p_bar[b], 16384);
-      bulk_load(sb + sP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * 8192, 16384, &p_bar[b]);
+      bulk_load(sb + sP + b * 16384, p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * kPImg, 16384, &p_bar[b]);
     };
-    // lane l handles tokens l and l + 32; the raw values of a chunk are requested two chunks ahead and wait in registers
-    float pf_g[2] = {0.f, 0.f}, pf_b[2] = {0.f, 0.f}, pf_gl = 0.f;
-    auto load_scalars = [&](int c) {
+    // the per-token factors of chunk c (made by the prep kernel, behind the chunk's P tile) into buffer c % 3
+    auto load_factors = [&](int c) {
       if (c < nt) {
-        const int rows = min(kC, sq.len - c * kC);
-        const int64_t tok0 = int64_t(sq.bos) + c * kC;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int t = lane + 32 * j;
-          // rows past the end of the sequence carry the last valid cumulative decay so every exponent stays finite
-          pf_g[j] = p.gam[(tok0 + min(t, rows - 1)) * p.HV + hv];
-          pf_b[j] = t < rows ? ld_scalar(p.beta, (tok0 + t) * p.beta_st + hv, p.beta_is_f32) : 0.f;
-        }
-        pf_gl = p.gam[(tok0 + rows - 1) * p.HV + hv];
-      }
-    };
-    auto make_factors = [&](int c) {
-      if (c < nt) {
-        ScanFactors& f = fac[c % 3];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int t = lane + 32 * j;
-          const float eg = __expf(pf_g[j]);
-          f.b[t] = pf_b[j];
-          f.bg[t] = pf_b[j] * eg;
-          f.se[t] = p.scale * eg;
-          f.dk[t] = __expf(pf_gl - pf_g[j]);
-        }
-        if (lane == 0) f.dl = __expf(pf_gl);
+        mbar_arrive_expect_tx(&f_bar[c % 3], uint32_t(sizeof(ScanFactors)));
+        bulk_load(smem_u32(&fac[c % 3]), reinterpret_cast<const uint8_t*>(p.p_img + ((int64_t(sq.cbase) + c) * p.HV + hv) * kPImg) + kPTileBytes,
+                  uint32_t(sizeof(ScanFactors)), &f_bar[c % 3]);
       }
     };
     if (lane == 0) {
@@ -192,29 +170,23 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
         load_qk(0);
         load_rest(0);
       }
+      load_factors(0);
+      load_factors(1);
     }
     __syncwarp();
-    load_scalars(0);
-    make_factors(0);
-    load_scalars(1);
-    make_factors(1);
-    load_scalars(2);
-    scan_sync();   // factors of chunks 0 and 1 are visible
+    scan_sync();   // (pairs with the epilogue warps' barrier after they have loaded the initial state)
     for (int c = 0; c < nt; ++c) {
       scan_sync();                                          // sync 1: chunk c - 1 no longer reads the other buffers
-      if (lane == 0 && c + 1 < nt) {
-        load_qk(c + 1);
-        load_rest(c + 1);
+      if (lane == 0) {
+        if (c + 1 < nt) {
+          load_qk(c + 1);
+          load_rest(c + 1);
+        }
+        load_factors(c + 2);                                // buffer (c + 2) % 3 was last read for chunk c - 1's output rows
       }
       __syncwarp();
       scan_sync();                                          // sync 2
       scan_sync();                                          // sync 3
-      // The factors are made two chunks ahead and here, while the state update runs: when the images are saved the
-      // epilogue warps hand 64 KB (before sync 1) and 32 KB (before sync 3) of stores to the load/store unit, and this
-      // warp's shared-memory stores and global loads queue behind them; anywhere else the whole CTA waits for it at a
-      // barrier (measured: 1.4 k cycles per chunk when this sat between sync 1 and sync 2).
-      make_factors(c + 2);                                  // buffer (c + 2) % 3 was last read for chunk c - 1's output rows
-      load_scalars(c + 3);
     }
     scan_sync();   // matches the epilogue warps' barrier before the TMEM is released
     return;
@@ -279,6 +251,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
 
   for (int c = 0; c < nt; ++c) {
     const ScanFactors& f = fac[c % 3];
+    if (!dead && !mbar_wait(&f_bar[c % 3], (c / 3) & 1, p.status, FLA_ERR_TIMEOUT)) dead = true;   // requested two chunks ago
     const int rows = min(kC, sq.len - c * kC);
     const int64_t cidx = ((int64_t(sq.cbase) + c) * p.HV + hv) * (p.V / 128) + vb;
 

@@ -20,7 +20,13 @@ namespace fla {
 constexpr int kScanEpiThreads = 256;
 constexpr int kScanThreads = 288;
 
-struct __align__(16) ScanFactors {     // per-token factors of one chunk, written by the helper warp one chunk ahead
+// The prep kernel leaves, behind the P tile of every (chunk, value head), the chunk's per-token factors as one ScanFactors
+// record: both scans fetch it with a single bulk copy straight into shared memory (global loads issued by the helper warp
+// took it thousands of cycles per chunk, with the whole CTA waiting at its next barrier).
+constexpr int64_t kPTileBytes = 16384;                 // P: value + residual, 64 x 64 bf16 each
+constexpr int64_t kPImgBytes = kPTileBytes + 1152;     // + the factor record (1040 bytes used), 128-byte aligned stride
+constexpr int64_t kPImg = kPImgBytes / 2;              // in bf16 elements: the per-(chunk, head) stride of p_img
+struct __align__(16) ScanFactors {     // per-token factors of one chunk, made by the prep kernel
   float b[kC];           // beta_j
   float bg[kC];          // beta_j e^{gam_j}
   float dk[kC];          // e^{gam_L - gam_j}

@@ -100,7 +100,7 @@ def gdn_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     if save_for_backward:
         s_img = torch.empty(total_chunks * HV * (V // 64) * 16384, dtype=torch.bfloat16, device=dev)
         vn_img = torch.empty(total_chunks * HV * (V // 64) * 8192, dtype=torch.bfloat16, device=dev)
-        p_img = torch.empty(total_chunks * HV * 8192, dtype=torch.bfloat16, device=dev)
+        p_img = torch.empty(total_chunks * HV * 8768, dtype=torch.bfloat16, device=dev)   # P tile (16 KB) + the chunk's factor record
     a = GdnChunkFwdArgs()
     a.q, a.k, a.v, a.g, a.beta = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(g), rt.desc(beta)
     a.initial_state, a.o, a.final_state = rt.desc(initial_state), rt.desc(o), rt.desc(ht)

@@ -215,8 +215,9 @@ FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* a
  *          (element [k/8][channel][k%8])
  *   vn_img [chunks * HV * (V/64) * 8192] bf16, optional out (for backward): v_new per half, value and residual, each 64 tokens x
  *          64 channels in strips of 8 tokens (element [t/8][channel][t%8])
- *   p_img  [chunks * HV * 8192] bf16, optional out (for backward): tril(Q K^T * decay) as a bf16 value and a bf16 residual,
- *          each 64x64 in strips of 8 columns (element [j/8][i][j%8] = P[i][j]);
+ *   p_img  [chunks * HV * 8768] bf16, optional out (for backward): per (chunk, head) tril(Q K^T * decay) as a bf16 value and a
+ *          bf16 residual, each 64x64 in strips of 8 columns (element [j/8][i][j%8] = P[i][j]), followed by 1152 bytes that hold
+ *          the chunk's per-token factors (beta, beta e^gam, e^{gam_L-gam}, scale e^gam as 64 floats each, then e^{gam_L});
  *          when absent the forward keeps these panels in its workspace
  *          (s_img, vn_img, p_img are opaque to the caller: produced here, consumed by fla_b200_gdn_chunk_bwd)
  *   cu_seqlens int32 [N+1] device (requires B == 1) with chunk_offsets int32 [N+1] device (prefix sum of
