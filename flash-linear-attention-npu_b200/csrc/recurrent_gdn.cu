@@ -11,15 +11,16 @@
 // and recurrent_kda (fla/ops/ascendc/kda/recurrent_kda/docs/design.md:44-70: per-channel gate with optional in-kernel
 // gate activation and beta sigmoid).
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include "fla_b200_internal.h"
 #include "kernel_timer.h"
 
 namespace fla {
 
 struct RecurrentParams {
-  const __nv_bfloat16* q;  // [T, HK, K]
-  const __nv_bfloat16* k;  // [T, HK, K]
-  const __nv_bfloat16* v;  // [T, HV, V]
+  const void* q;           // [T, HK, K]  bf16, or fp16 when act_f16
+  const void* k;           // [T, HK, K]
+  const void* v;           // [T, HV, V]
   const void* g;           // [T, HV] or null
   const void* beta;        // [T, HV] or null
   const void* gk;          // [T, HV, K] per-channel log gate (raw when gate_mode != 0) or null
@@ -37,6 +38,7 @@ struct RecurrentParams {
   int HK, HV, tokens_per_seq, nblocks_in, nblocks_out;
   int64_t gk_stride_t, gk_stride_h;
   int g_is_f32, beta_is_f32, out_is_f32, l2norm, gk_is_f32, gate_mode, beta_mode;
+  int act_f16, out_is_f16;   // q, k, v are fp16 (read exactly: the arithmetic is fp32) / out is fp16
   float scale, lower_bound;
 };
 
@@ -53,8 +55,23 @@ __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
   const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
   return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
+template <>
+__device__ __forceinline__ float4 load4<__half>(const __half* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
 template <typename T>
 __device__ __forceinline__ void store4(T* p, float4 x);
+template <>
+__device__ __forceinline__ void store4<__half>(__half* p, float4 x) {
+  __half2 a = __floats2half2_rn(x.x, x.y), b = __floats2half2_rn(x.z, x.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
 template <>
 __device__ __forceinline__ void store4<float>(float* p, float4 x) {
   *reinterpret_cast<float4*>(p) = x;
@@ -68,6 +85,10 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 x
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
+// one activation element (q, k, v): bf16, or fp16 when f16
+__device__ __forceinline__ float load_act(const void* p, int64_t idx, int f16) {
+  return f16 ? __half2float(static_cast<const __half*>(p)[idx]) : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+}
 __device__ __forceinline__ float load_scalar(const void* p, int64_t idx, int is_f32) {
   return is_f32 ? static_cast<const float*>(p)[idx] : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
 }
@@ -127,9 +148,9 @@ __global__ void __launch_bounds__(kRecThreads, 3) recurrent_gdn_kernel(Recurrent
   for (int t = t0; t < t1; ++t) {
     __syncthreads();  // previous token's readers of k_s/q_s/red are done
     if (tid < K) {
-      k_s[tid] = __bfloat162float(p.k[t * p.k_stride_t + hk * p.k_stride_h + tid]);
+      k_s[tid] = load_act(p.k, t * p.k_stride_t + hk * p.k_stride_h + tid, p.act_f16);
     } else if (tid < 2 * K) {
-      q_s[tid - K] = __bfloat162float(p.q[t * p.q_stride_t + hk * p.q_stride_h + (tid - K)]);
+      q_s[tid - K] = load_act(p.q, t * p.q_stride_t + hk * p.q_stride_h + (tid - K), p.act_f16);
     }
     if (p.gk && tid < K) {   // per-channel decay of this token: exp(gate(gk))
       float gate = load_scalar(p.gk, t * p.gk_stride_t + hv * p.gk_stride_h + tid, p.gk_is_f32);
@@ -189,7 +210,9 @@ __global__ void __launch_bounds__(kRecThreads, 3) recurrent_gdn_kernel(Recurrent
         const float4 x = *reinterpret_cast<const float4*>(&red[r][c0]);
         dot.x += x.x; dot.y += x.y; dot.z += x.z; dot.w += x.w;
       }
-      const float4 vv = load4<__nv_bfloat16>(p.v + t * p.v_stride_t + hv * p.v_stride_h + v0 + c0);
+      const int64_t voff = t * p.v_stride_t + hv * p.v_stride_h + v0 + c0;
+      const float4 vv = p.act_f16 ? load4<__half>(static_cast<const __half*>(p.v) + voff)
+                                  : load4<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.v) + voff);
       float4 d;
       d.x = beta * (vv.x - decay * dot.x); d.y = beta * (vv.y - decay * dot.y);
       d.z = beta * (vv.z - decay * dot.z); d.w = beta * (vv.w - decay * dot.w);
@@ -213,6 +236,7 @@ __global__ void __launch_bounds__(kRecThreads, 3) recurrent_gdn_kernel(Recurrent
         }
         const int64_t off = t * p.out_stride_t + hv * p.out_stride_h + v0 + c0;
         if (p.out_is_f32) store4<float>(static_cast<float*>(p.out) + off, o);
+        else if (p.out_is_f16) store4<__half>(static_cast<__half*>(p.out) + off, o);
         else store4<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p.out) + off, o);
       }
     } else {
@@ -225,7 +249,7 @@ __global__ void __launch_bounds__(kRecThreads, 3) recurrent_gdn_kernel(Recurrent
         float dot = s[i].x * kk.x + s[i].y * kk.y + s[i].z * kk.z + s[i].w * kk.w;
 #pragma unroll
         for (int o = TPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float vv = __bfloat162float(p.v[t * p.v_stride_t + hv * p.v_stride_h + row]);
+        const float vv = load_act(p.v, t * p.v_stride_t + hv * p.v_stride_h + row, p.act_f16);
         const float d = beta * (vv - decay * dot);
         s[i].x = decay * s[i].x + d * kk.x; s[i].y = decay * s[i].y + d * kk.y;
         s[i].z = decay * s[i].z + d * kk.z; s[i].w = decay * s[i].w + d * kk.w;
@@ -235,6 +259,7 @@ __global__ void __launch_bounds__(kRecThreads, 3) recurrent_gdn_kernel(Recurrent
         if (tid % TPR == 0) {
           const int64_t off = t * p.out_stride_t + hv * p.out_stride_h + row;
           if (p.out_is_f32) static_cast<float*>(p.out)[off] = o;
+          else if (p.out_is_f16) static_cast<__half*>(p.out)[off] = __float2half_rn(o);
           else static_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(o);
         }
       }
@@ -283,9 +308,9 @@ extern "C" FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* a, v
   const fla_tensor_t &q = a->q, &k = a->k, &v = a->v, &si = a->state_in, &so = a->state_out, &o = a->out;
   if (!q.data || !k.data || !v.data || !si.data || !so.data || !o.data) return FLA_ERR_NULL;
   if (q.ndim != 3 || k.ndim != 3 || v.ndim != 3 || o.ndim != 3 || si.ndim != 4 || so.ndim != 4) return FLA_ERR_SHAPE;
-  if (q.dtype != FLA_BF16 || k.dtype != FLA_BF16 || v.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  if ((q.dtype != FLA_BF16 && q.dtype != FLA_F16) || k.dtype != q.dtype || v.dtype != q.dtype) return FLA_ERR_DTYPE;
   if (si.dtype != so.dtype || (si.dtype != FLA_F32 && si.dtype != FLA_BF16)) return FLA_ERR_DTYPE;
-  if (o.dtype != FLA_BF16 && o.dtype != FLA_F32) return FLA_ERR_DTYPE;
+  if (o.dtype != FLA_BF16 && o.dtype != FLA_F32 && o.dtype != FLA_F16) return FLA_ERR_DTYPE;
   const int64_t T = q.shape[0], HK = q.shape[1], K = q.shape[2], HV = v.shape[1], V = v.shape[2];
   if (T <= 0 || HK <= 0 || HV <= 0 || HV % HK) return FLA_ERR_SHAPE;
   for (int i = 0; i < 3; ++i)
@@ -338,9 +363,10 @@ extern "C" FLA_API int fla_b200_recurrent_gdn(const fla_recurrent_gdn_args* a, v
   }
 
   RecurrentParams p{};
-  p.q = static_cast<const __nv_bfloat16*>(q.data);
-  p.k = static_cast<const __nv_bfloat16*>(k.data);
-  p.v = static_cast<const __nv_bfloat16*>(v.data);
+  p.q = q.data;
+  p.k = k.data;
+  p.v = v.data;
+  p.act_f16 = q.dtype == FLA_F16; p.out_is_f16 = o.dtype == FLA_F16;
   p.g = a->g.data; p.beta = a->beta.data;
   p.state_in = si.data; p.state_out = so.data; p.out = o.data;
   p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);

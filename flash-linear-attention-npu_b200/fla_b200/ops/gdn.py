@@ -122,7 +122,8 @@ def gdn_chunk_bwd(q, k, v, beta, saved, do, dht, scale, want_dh0, grad_dtype=Non
     HV, V = v.shape[2], v.shape[3]
     dev = q.device
     if do.dtype != torch.bfloat16:
-        do = do.to(torch.bfloat16)
+        from ._convert import convert
+        do = convert(do, torch.bfloat16, op)
     do = _as_rows(do)
     if tuple(do.shape) != (B, T, HV, V):
         raise RuntimeError(f"{op}: do must be {(B, T, HV, V)}, got {tuple(do.shape)}")
@@ -249,6 +250,18 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     if int(chunk_size) not in (16, 32, 64, 128):
         raise NotImplementedError(f"{op}: chunk_size must be one of 16, 32, 64, 128, got {chunk_size}")
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
+    if torch.float16 in (q.dtype, k.dtype, v.dtype):
+        # fp16 tensors (the reference takes them, examples/flash_gated_delta_rule.py:1161-1162): the tensor-core products
+        # run on bf16 operands, so q, k, v are rounded to bf16 by the library's conversion kernel, fp16 gates become fp32,
+        # o is computed in fp32 and converted to fp16 once; the gradients come back through the same conversions
+        if not (q.dtype == k.dtype == v.dtype):
+            raise TypeError(f"{op}: q, k, v must share one dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
+        from ._convert import to_dtype
+        q, k, v = (to_dtype(x, torch.bfloat16, op) for x in (q, k, v))
+        g, beta = (to_dtype(x, torch.float32, op) if x.dtype == torch.float16 else x for x in (g, beta))
+        o, ht = ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
+                                                  torch.float32, bool(use_qk_l2norm_in_kernel))
+        return to_dtype(o, output_dtype or torch.float16, op), ht
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                                              output_dtype, bool(use_qk_l2norm_in_kernel))
 

@@ -68,7 +68,10 @@ def kda_chunk_bwd(q, k, v, g, beta, scale, initial_state, do, dht, meta, grad_dt
     dg = torch.empty((B, T, HV, K), dtype=gdt, device=dev)
     dbeta = torch.empty((B, T, HV), dtype=gdt, device=dev)
     dh0 = torch.empty((N, HV, K, V), dtype=torch.float32, device=dev) if initial_state is not None else None
-    do = _as_rows(do if do.dtype == torch.bfloat16 else do.to(torch.bfloat16))
+    if do.dtype != torch.bfloat16:
+        from ._convert import convert
+        do = convert(do, torch.bfloat16, "chunk_kda_bwd")
+    do = _as_rows(do)
     if dht is not None:
         dht = dht.float().contiguous()
     a = KdaChunkBwdArgs()
@@ -157,9 +160,26 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         # beta arrives as logits.  It is a [B,T,HV] tensor, 1/128 of the gate's bytes: the activation (and, through autograd,
         # its gradient) is one elementwise pass in front of the kernels rather than a mode of them.
         beta = torch.sigmoid(beta.float())
+    if torch.float16 in (q.dtype, k.dtype, v.dtype):
+        # fp16 tensors (the reference's published 4-stage case is fp16, fla/ops/ascendc/kda/KDA_FORWARD_VALIDATION_REPORT.md:133-146):
+        # q, k, v are rounded to the bf16 operands of the tensor-core products by the library's conversion kernel, fp16
+        # gates become fp32, o is computed in fp32 and converted to fp16 once; gradients return through the same conversions
+        if not (q.dtype == k.dtype == v.dtype):
+            raise TypeError(f"{op}: q, k, v must share one dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
+        from ._convert import to_dtype
+        q, k, v = (to_dtype(x, torch.bfloat16, op) for x in (q, k, v))
+        g, beta = (to_dtype(x, torch.float32, op) if x.dtype == torch.float16 else x for x in (g, beta))
+        if export_scores is not None and any(x.dtype == torch.float16 for x in export_scores):
+            raise NotImplementedError(f"{op}: export_scores takes bf16 or fp32 views")
+        res = chunk_kda(q, k, v, g, beta, scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+                        use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, use_gate_in_kernel=use_gate_in_kernel,
+                        use_beta_sigmoid_in_kernel=False, cu_seqlens=cu_seqlens, safe_gate=safe_gate, lower_bound=lower_bound,
+                        A_log=A_log, dt_bias=dt_bias, return_gate_cumsum=return_gate_cumsum, output_dtype=torch.float32,
+                        disable_recompute=disable_recompute, export_scores=export_scores)
+        return (to_dtype(res[0], output_dtype or torch.float16, op),) + tuple(res[1:])
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != torch.bfloat16:
-            raise TypeError(f"{op}: {name} must be bfloat16, got {t.dtype}")
+            raise TypeError(f"{op}: {name} must be bfloat16 or float16, got {t.dtype}")
     if q.dim() != 4 or q.shape != k.shape or v.dim() != 4 or v.shape[:2] != q.shape[:2]:
         raise RuntimeError(f"{op}: expected q,k [B,T,HK,K] and v [B,T,HV,V]")
     B, T, HK, K = q.shape

@@ -19,8 +19,18 @@ _OP = "recurrent_gdn"
 
 
 def _activation_ok(name, t):
-    if t.dtype != torch.bfloat16:
-        raise TypeError(f"{name} dtype must be torch.bfloat16, got {t.dtype}")
+    # fp16 activations are read exactly by the decode kernel (fp32 arithmetic on CUDA cores); q, k, v share one dtype
+    if t.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"{name} dtype must be torch.bfloat16 or torch.float16, got {t.dtype}")
+
+
+def _gate_f16_to_f32(t, op):
+    """fp16 gate tensors (g, beta, gk) as fp32, through the library's conversion kernel; others unchanged."""
+    if t is None or t.dtype != torch.float16:
+        return t
+    from ._convert import convert
+    shape = t.shape
+    return convert(t.reshape(-1, shape[-1]), torch.float32, op).view(shape)
 
 
 def fused_recurrent_gated_delta_rule(q, k, v, g=None, beta=None, scale=None, initial_state=None,
@@ -36,6 +46,9 @@ def fused_recurrent_gated_delta_rule(q, k, v, g=None, beta=None, scale=None, ini
     op = "fused_recurrent_gated_delta_rule"
     for n, t in (("q", q), ("k", k), ("v", v)):
         _activation_ok(f"{op}: {n}", t)
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError(f"{op}: q, k, v must share one dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
+    g, beta, gk = (_gate_f16_to_f32(x, op) for x in (g, beta, gk))
     if q.dim() != 4 or q.shape != k.shape or v.dim() != 4:
         raise RuntimeError(f"{op}: q/k must be [B,T,HK,K] and v [B,T,HV,V]")
     B, T, HK, K = q.shape
@@ -107,6 +120,9 @@ def recurrent_gated_delta_rule(query, key, value, state, *, beta, scale=1.0, act
                                   "the reference documents it as not supported yet as well")
     for n, t in (("query", query), ("key", key), ("value", value), ("beta", beta)):
         _activation_ok(f"{op}: {n}", t)
+    if not (query.dtype == key.dtype == value.dtype):
+        raise TypeError(f"{op}: query, key, value must share one dtype, got {query.dtype}, {key.dtype}, {value.dtype}")
+    beta, g = _gate_f16_to_f32(beta, op), _gate_f16_to_f32(g, op)
     if state.dtype not in (torch.bfloat16, torch.float32):
         raise TypeError(f"{op}: state dtype must be bfloat16 or float32, got {state.dtype}")
     if actual_seq_lengths.dtype != torch.int32 or ssm_state_indices.dtype != torch.int32:
@@ -165,6 +181,9 @@ def recurrent_kda(q, k, v, g, beta, initial_state=None, *, cu_seqlens=None, ssm_
         raise RuntimeError(f"{op}: q and k must have identical shape.")
     for n, t in (("q", q), ("k", k), ("v", v)):
         _activation_ok(f"{op}: {n}", t)
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError(f"{op}: q, k, v must share one dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
+    g, beta = _gate_f16_to_f32(g, op), _gate_f16_to_f32(beta, op)
     if tnd:
         q, k, v, g, beta = (x.unsqueeze(0) for x in (q, k, v, g, beta))
     B, T, H, K = q.shape

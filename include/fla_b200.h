@@ -62,7 +62,7 @@ FLA_API int fla_b200_version(void);
  * recorded events and returns the summed duration and the number of launches of `kernel_name`
  * (names: "gdn_prep", "tri_inverse", "kda_prep", "kda_fwd", "gdn_fwd", "gdn_bwd_dhu", "gdn_bwd_par", "recurrent_gdn", "causal_conv1d_fwd",
  * "causal_conv1d_update", "causal_conv1d_bwd", "kda_bwd_dhu", "kda_bwd_par", "chunk_local_cumsum", "chunk_scaled_dot_kkt",
- * "solve_tri", "recompute_w_u_fwd", "chunk_fwd_h", "chunk_fwd_o"). */
+ * "solve_tri", "recompute_w_u_fwd", "chunk_fwd_h", "chunk_fwd_o", "convert"). */
 FLA_API int fla_b200_kernel_timing_enable(int enable);
 FLA_API int fla_b200_kernel_timing_read(const char* kernel_name, float* total_ms, int* launches);
 
@@ -104,11 +104,12 @@ FLA_API int fla_b200_selftest_wait_timeout(uint32_t spin_limit, void* status_wor
  * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:654-846; kernel
  * fla/ops/ascendc/gdn/recurrent_gdn/recurrent_gated_delta_rule/op_kernel/recurrent_gated_delta_rule.h:159-199).
  * Per token: S <- exp(g) S; d = beta (v - S^T k); S <- S + k d^T; o = S^T (scale q).
- *   q, k   [T, HK, K] bf16          v   [T, HV, V] bf16        (HV % HK == 0, head hv reads q/k head hv / (HV/HK))
+ *   q, k   [T, HK, K] bf16|f16      v   [T, HV, V], the same dtype (HV % HK == 0, head hv reads q/k head hv / (HV/HK));
+ *          fp16 values are read exactly (the arithmetic is fp32 on CUDA cores)
  *   g      [T, HV] f32|bf16, optional (absent: no decay)        beta [T, HV] f32|bf16, optional (absent: 1)
  *   state_in / state_out [blocks, HV, K, V] (state_v_first = 0) or [blocks, HV, V, K] (= 1), f32|bf16,
  *          innermost two dims dense; the two may be the same tensor (in-place update)
- *   out    [T, HV, V] bf16|f32
+ *   out    [T, HV, V] bf16|f16|f32
  *   cu_seqlens          int32 [N+1] device, token offsets of the N sequences; absent: every sequence has
  *                       `tokens_per_seq` tokens
  *   state_indices       int32 [T] device: the state after token t is written to block state_indices[t], and a
@@ -374,6 +375,16 @@ typedef struct fla_fast_gelu_args {
 } fla_fast_gelu_args;
 FLA_API int fla_b200_fast_gelu(const fla_fast_gelu_args* args, void* stream);
 FLA_API int fla_b200_fast_gelu_bwd(const fla_fast_gelu_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Elementwise conversion between f32, bf16 and f16 tensors (round to nearest even) with re-layout.
+ * The chunk and decode operators multiply bf16 operands; the reference also accepts fp16 tensors
+ * (examples/flash_gated_delta_rule.py:1161-1162 rejects only fp32): the host wrappers route fp16 inputs and
+ * results through this kernel (inputs are rounded from 11 to 8 significant bits).
+ *   src, dst: the same shape, 1 to 4 dims, innermost dim contiguous, any other strides (a head-first view can be
+ *   made token-major in the same pass).  Rows of a multiple of 8 elements at 16-byte aligned addresses take the
+ *   vector path.  Single-phase (no workspace). */
+FLA_API int fla_b200_convert(const fla_tensor_t* src, const fla_tensor_t* dst, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Stand-alone stages of the chunked gated-delta-rule forward: one entry point per low-level reference operator,

@@ -1,0 +1,139 @@
+"""fp16 tensors through the operators that take them in the reference (examples/flash_gated_delta_rule.py:1161-1162 rejects
+only fp32; the published KDA 4-stage case is fp16, fla/ops/ascendc/kda/KDA_FORWARD_VALIDATION_REPORT.md:133-146).
+
+* the conversion kernel: bit-exact against `Tensor.to` for every pair of f32 / bf16 / f16, dense, strided and odd rows;
+* decode (`fused_recurrent_gated_delta_rule`, `recurrent_gated_delta_rule`, `recurrent_kda`): fp16 values are read exactly
+  and the arithmetic is fp32, so the fp32-oracle bar of the bf16 tests holds unchanged;
+* chunk operators: q, k, v are rounded to the bf16 operands of the tensor-core products.  Two comparisons, both with the
+  tolerance written here: against the fp64 oracle fed the SAME rounded operands at the plain 5e-3 bar (the kernels add
+  nothing beyond what they add for bf16 callers), and against the fp64 oracle fed the original fp16 tensors at
+  FP16_INPUT_TOL = 6e-2: rounding q, k, v, dO from 11 to 8 significant bits alone moves o, the final state and the
+  gradients by 1e-2..4e-2 of their RMS in the worst element (the same distance a bf16 caller's tensors are from their
+  fp32 originals), so fp16 callers get bf16-operand accuracy, not fp16-operand accuracy.
+"""
+import pytest
+import torch
+
+import oracle
+from _util import assert_close, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 5e-3
+FP16_INPUT_TOL = 6e-2
+DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+
+
+@pytest.mark.parametrize("src", DTYPES)
+@pytest.mark.parametrize("dst", DTYPES)
+def test_convert_matches_torch_bit_exact(src, dst):
+    from fla_b200.ops._convert import convert
+    gen = torch.Generator().manual_seed(7)
+    x = (torch.randn(3, 50, 4, 128, generator=gen) * torch.logspace(-6, 3, 128)).to(src).cuda()
+    assert torch.equal(convert(x, dst), x.to(dst))
+    xt = x.transpose(1, 2)                       # head-first view: strided rows, dense result
+    got = convert(xt, dst)
+    assert got.is_contiguous() and torch.equal(got, xt.to(dst))
+    odd = x[0, :, 0, :37]                        # rows of 37 elements at unaligned addresses: the scalar path
+    assert torch.equal(convert(odd, dst), odd.to(dst))
+    flat = x.reshape(-1)[: 8 * 1000]
+    assert torch.equal(convert(flat, dst), flat.to(dst))
+
+
+def test_convert_is_differentiable():
+    from fla_b200.ops._convert import to_dtype
+    x = torch.randn(2, 16, 2, 64, device="cuda", dtype=torch.float16, requires_grad=True)
+    y = to_dtype(x, torch.bfloat16)
+    assert y.dtype == torch.bfloat16 and to_dtype(y, torch.bfloat16) is y
+    y.float().sum().backward()
+    assert x.grad.dtype == torch.float16 and torch.equal(x.grad, torch.ones_like(x))
+
+
+def _bf16_rounded(inp):
+    return {n: (t.to(torch.bfloat16) if (t is not None and n in ("q", "k", "v", "do")) else t) for n, t in inp.items()}
+
+
+@pytest.mark.parametrize("B,T,HK,HV", [(1, 200, 1, 2), (2, 256, 2, 4)])
+def test_chunk_gated_delta_rule_fp16(B, T, HK, HV):
+    from fla_b200.ops import chunk_gated_delta_rule
+    inp = oracle.make_gdn_inputs(B, T, HK, HV, seed=900 + T, dtype=torch.float16)
+    refs = {}
+    for tag, src in (("exact", inp), ("rounded", _bf16_rounded(inp))):
+        refs[tag] = oracle.gdn_reference_fwd_bwd(src["q"], src["k"], src["v"], src["g"], src["beta"], initial_state=src["h0"],
+                                                 do=src["do"], dht=src["dht"], dtype=torch.float64)
+    d = {n: (t.cuda() if t is not None else None) for n, t in inp.items()}
+    leaves = [d[n].requires_grad_() for n in ("q", "k", "v", "g", "beta", "h0")]
+    o, ht = chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True)
+    assert o.dtype == torch.float16 and ht.dtype == torch.float32
+    torch.autograd.backward([o, ht], [d["do"], d["dht"]])
+    for t in leaves[:5]:
+        assert t.grad.dtype == torch.float16
+    got = dict(o=o, ht=ht, dq=d["q"].grad, dk=d["k"].grad, dv=d["v"].grad, dg=d["g"].grad, dbeta=d["beta"].grad, dh0=d["h0"].grad)
+    half_stored = {"o", "dq", "dk", "dv", "dg", "dbeta"}     # rounded to bf16 / fp16 on the way out: half-ulp allowance
+    for name, val in got.items():
+        assert_close(f"{name} vs oracle on the rounded operands", val, refs["rounded"][name], TOL, stored_bf16=name in half_stored)
+        assert_close(f"{name} vs oracle on the fp16 tensors", val, refs["exact"][name], FP16_INPUT_TOL,
+                     stored_bf16=name in half_stored)
+
+
+def test_flash_gated_delta_rule_fp16_head_first():
+    """The reference's composed entry with fp16 `[B,H,T,D]` tensors: same result as the bf16 call on the rounded tensors."""
+    from fla_b200.ops import flash_gated_delta_rule
+    inp = oracle.make_gdn_inputs(2, 192, 2, 2, seed=77, dtype=torch.float16, with_grad=False)
+    q, k, v = (inp[n].cuda().transpose(1, 2).contiguous() for n in ("q", "k", "v"))       # [B,H,T,D]
+    g, beta = inp["g"].cuda(), inp["beta"].cuda()
+    o16, ht16 = flash_gated_delta_rule(q, k, v, g, beta, output_final_state=True)
+    ob, htb = flash_gated_delta_rule(q.bfloat16(), k.bfloat16(), v.bfloat16(), g.float(), beta.float(), output_final_state=True)
+    assert o16.dtype == torch.float16 and o16.shape == ob.shape
+    assert torch.equal(ht16, htb)
+    # the same fp32 result stored once as fp16 and once as bf16: half an ulp of each apart at most
+    diff = (o16.double() - ob.double()).abs()
+    assert (diff <= ob.double().abs() * (2.0 ** -8 + 2.0 ** -11) + 2.0 ** -24).all()   # 2^-24: fp16 subnormal spacing, rel_err(o16, ob)
+
+
+@pytest.mark.parametrize("T", [128, 200])
+def test_chunk_kda_fp16(T):
+    from fla_b200.ops import chunk_kda
+    inp = oracle.make_kda_inputs(1, T, 2, 2, seed=300 + T, dtype=torch.float16)
+    refs = {}
+    for tag, src in (("exact", inp), ("rounded", _bf16_rounded(inp))):
+        refs[tag] = oracle.kda_reference_fwd_bwd(src["q"], src["k"], src["v"], src["g"], src["beta"], do=src["do"],
+                                                 dtype=torch.float64)
+    d = {n: (t.cuda() if t is not None else None) for n, t in inp.items()}
+    for n in ("q", "k", "v", "g", "beta"):
+        d[n].requires_grad_()
+    o, _ = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"])
+    assert o.dtype == torch.float16
+    o.backward(d["do"])
+    got = dict(o=o, dq=d["q"].grad, dk=d["k"].grad, dv=d["v"].grad, dg=d["g"].grad, dbeta=d["beta"].grad)
+    for name, val in got.items():
+        assert val.dtype == torch.float16
+        assert_close(f"{name} vs oracle on the rounded operands", val, refs["rounded"][name], TOL, stored_bf16=True)
+        assert_close(f"{name} vs oracle on the fp16 tensors", val, refs["exact"][name], FP16_INPUT_TOL, stored_bf16=True)
+
+
+def test_decode_reads_fp16_exactly():
+    from fla_b200.ops import fused_recurrent_gated_delta_rule
+    N, HK, HV = 6, 2, 4
+    inp = oracle.make_decode_inputs(N, HK, HV, seed=41, tokens_per_seq=3, dtype=torch.float16)
+    T = 3
+    q, k, v = (inp[n].view(N, T, *inp[n].shape[1:]) for n in ("q", "k", "v"))
+    g, beta = (inp[n].view(N, T, HV) for n in ("g", "beta"))
+    rep = HV // HK
+    ref_o, ref_s = oracle.naive_recurrent_gated_delta_rule(q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2), v, beta, g,
+                                                           scale=128 ** -0.5, initial_state=inp["state"], dtype=torch.float64)
+    o, s = fused_recurrent_gated_delta_rule(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), initial_state=inp["state"].cuda(),
+                                            output_final_state=True)
+    assert o.dtype == torch.float16
+    assert_close("final state", s, ref_s, 1e-5)
+    # the fp16 store may move a value by half an fp16 ulp (2^-11 |x|) on top of the fp32 bar
+    err = (o.double().cpu() - ref_o).abs()
+    rms = ref_o.pow(2).mean().sqrt()
+    assert (err <= 1e-5 * rms + ref_o.abs() * 2.0 ** -11).all(), (err.max() / rms).item()
+
+
+def test_decode_rejects_mixed_activation_dtypes():
+    from fla_b200.ops import fused_recurrent_gated_delta_rule
+    inp = oracle.make_decode_inputs(2, 1, 1, seed=5)
+    q, k, v = (inp[n].unsqueeze(1).cuda() for n in ("q", "k", "v"))
+    with pytest.raises(TypeError, match="share one dtype"):
+        fused_recurrent_gated_delta_rule(q.half(), k, v, inp["g"].unsqueeze(1).cuda(), inp["beta"].unsqueeze(1).cuda())
