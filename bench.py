@@ -339,7 +339,7 @@ class Workload:
         """DRAM bytes (read + write) of one launch: the per-unit figure of one ncu capture of a small case of the
         same kernel (profiles/), scaled by the units this launch processes; None where no capture exists."""
         c = self.cfg
-        per_chunk_head = {"gdn_fwd": 323.00e6 / 2048, "gdn_bwd_dhu": 361.24e6 / 2048, "gdn_bwd_par": 470.01e6 / 2048,
+        per_chunk_head = {"gdn_fwd": 323.56e6 / 2048, "gdn_bwd_dhu": 390.73e6 / 2048, "gdn_bwd_par": 500.59e6 / 2048,
                           "kda_prep": 159.25e6 / 1024, "kda_fwd": 232.05e6 / 1024, "kda_bwd_dhu": 266.41e6 / 1024,
                           "kda_bwd_par": 396.41e6 / 1024, "recompute_w_u_fwd": 87.51e6 / 2048, "chunk_fwd_h": 144.66e6 / 2048,
                           "chunk_fwd_o": 151.88e6 / 2048}

@@ -37,7 +37,7 @@ struct GdnBwdParams {
   const float* gam; const bf16* X;
   const bf16* s_img; const bf16* vn_img; const bf16* p_img;
   bf16* ds_img;        // [chunks, HV, V/64, 2, 128x64]  state gradient entering each chunk (hi, lo)
-  bf16* dz_img;        // [chunks, HV, V/64, 128x64: rows 0-63 dO, rows 64-127 dZ rounded to bf16]
+  bf16* dz_img;        // [chunks, HV, V/64, 192x64: rows 0-63 dO, rows 64-127 dZ rounded to bf16, rows 128-191 the residual of dZ]
   float* bz;           // [V/32, tokens, HV] partial sums of dZ * V over the 32-column slices of V
   const float* dht; float* dh0;
   void* dq; void* dk; void* dv; void* dg; void* dbeta;
@@ -58,11 +58,12 @@ namespace fla {
 
 constexpr int64_t kSImg = 16384;   // bf16 elements of the state images per (chunk, head, 64-column block of V): (hi, lo) x 128x64
 constexpr int64_t kVnImg = 8192;   // v_new images per (chunk, head, block): (hi, lo) x 64x64
-constexpr int64_t kDzImg = 8192;   // per (chunk, head, block): 64x64 dO + 64x64 dZ, single bf16
+constexpr int64_t kDzImg = kDzHalf;   // per (chunk, head, block): 64x64 dO, 64x64 dZ and the residual of dZ
 
 // ============================================================================================= par
 constexpr uint32_t rOffQK = 0, rQKPanel = 16384;
-constexpr uint32_t rOffAH = 49152;             // [dO^T | dZ^T] strips of one 64-channel step (16 KB); the 16 KB before them are unused
+constexpr uint32_t rOffAH = 49152;             // [dO^T | dZ^T] strips of one 64-channel step (16 KB)
+constexpr uint32_t rOffAL = 32768;             // [0 | residual of dZ^T]: 8 KB of zeros written once, then the step's 8 KB of strips
 constexpr uint32_t rOffVNH = 65536, rOffVNL = 73728;   // v_new^T value / residual strips; as an A operand with valid rows 64..127 the
                                                        // view starts 8 KB earlier, inside the dZ^T strips (any finite contents do)
 constexpr uint32_t rOffSH = 81920, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 131072;
@@ -70,7 +71,7 @@ constexpr uint32_t rOffPAH = 147456, rOffPAL = 163840;   // [dP ; dAt] hi / lo (
 constexpr uint32_t kParSmem = 180224;
 constexpr uint32_t rColQK = 0, rColDV = 64, rColTA = 128, rColTB = 256;
 constexpr uint32_t rColAcc = 384;   // running dq (q-side rows) / dk (k-side rows) over the value heads of the group: 128 columns
-constexpr uint32_t kStepBytes = 16384 + 16384 + 32768 + 32768;
+constexpr uint32_t kStepBytes = 16384 + 8192 + 16384 + 32768 + 32768;
 
 __device__ __forceinline__ void row_dot64(const uint8_t* pan0, uint32_t panel_stride, int row, int col0, const float* x,
                                           float& acc) {
@@ -125,7 +126,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     const int64_t blk = ((int64_t(sq.cbase) + c) * p.HV + hv) * (NVB / 2) + (vb >> 1);
     const int64_t hf = vb & 1;
     mbar_arrive_expect_tx(&load_bar, kStepBytes);
-    bulk_load(sb + rOffAH, p.dz_img + blk * 16384 + hf * 8192, 16384, &load_bar);      // [dO^T | dZ^T] strips
+    bulk_load(sb + rOffAH, p.dz_img + blk * (2 * kDzHalf) + hf * kDzHalf, 16384, &load_bar);      // [dO^T | dZ^T] strips
+    bulk_load(sb + rOffAL + 8192, p.dz_img + blk * (2 * kDzHalf) + hf * kDzHalf + 8192, 8192, &load_bar);   // residual of dZ^T
     bulk_load(sb + rOffVNH, p.vn_img + blk * 16384 + hf * 8192, 16384, &load_bar);     // [value | residual]
     bulk_load(sb + rOffSH, p.s_img + blk * 32768 + hf * 16384, 32768, &load_bar);      // [value | residual], 16 strips each
     bulk_load(sb + rOffDSH, p.ds_img + blk * 32768 + hf * 16384, 32768, &load_bar);
@@ -135,7 +137,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   auto prefetch_loads = [&](int hv, int vb) {
     const int64_t blk = ((int64_t(sq.cbase) + c) * p.HV + hv) * (NVB / 2) + (vb >> 1);
     const int64_t hf = vb & 1;
-    bulk_prefetch_l2(p.dz_img + blk * 16384 + hf * 8192, 16384);
+    bulk_prefetch_l2(p.dz_img + blk * (2 * kDzHalf) + hf * kDzHalf, 24576);
     bulk_prefetch_l2(p.vn_img + blk * 16384 + hf * 8192, 16384);
     bulk_prefetch_l2(p.s_img + blk * 32768 + hf * 16384, 32768);
     bulk_prefetch_l2(p.ds_img + blk * 32768 + hf * 16384, 32768);
@@ -164,6 +166,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     }
   };
   prefetch_scalars(hk * G);
+  reinterpret_cast<uint4*>(smem + rOffAL)[tid] = make_uint4(0, 0, 0, 0);          // the zero rows of [0 | residual of dZ^T]
+  reinterpret_cast<uint4*>(smem + rOffAL)[tid + 256] = make_uint4(0, 0, 0, 0);
   fence_async_smem();
   __syncthreads();
   const uint32_t tbase = tmem_base_s;
@@ -177,6 +181,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   const Operand opQKn{sb + rOffQK, rQKPanel, 1};                     // [q; k] as B, N = 128 key dims, reduction over 128 rows
   // operands of a step: un-swizzled strips (sm100.cuh) whose 64 rows are value channels, the reduction dim of these products
   const Operand opAH{sb + rOffAH, 1024, 2};                                               // [dO; dZ]: M = 128 tokens = 16 strips
+  const Operand opAL{sb + rOffAL, 1024, 2};                                               // [0; residual of dZ]: enters dA = -tril(dZ Vn^T) only
   const Operand opVNbH{sb + rOffVNH, 1024, 2}, opVNbL{sb + rOffVNL, 1024, 2};            // Vn as B (N = 64 tokens = 8 strips)
   const Operand opVNaH{sb + rOffVNH - 8192, 1024, 2}, opVNaL{sb + rOffVNL - 8192, 1024, 2};  // Vn as A: accumulator rows 64..127 are valid
   const Operand opSH{sb + rOffSH, 1024, 2}, opSL{sb + rOffSL, 1024, 2};                  // S block as B (N = 128 key dims = 16 strips)
@@ -262,6 +267,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
         const bool accf = vb > 0;
         mma_tile(tbase + rColDV, opAH, opVNbH, 128, 64, 4, accf);
         mma_tile(tbase + rColDV, opAH, opVNbL, 128, 64, 4, true);
+        mma_tile(tbase + rColDV, opAL, opVNbH, 128, 64, 4, true);
         mma_tile(tbase + rColTA, opAH, opSH, 128, 128, 4, accf);
         mma_tile(tbase + rColTA, opAH, opSL, 128, 128, 4, true);
         mma_tile(tbase + rColTB, opVNaH, opDSH, 128, 128, 4, accf);

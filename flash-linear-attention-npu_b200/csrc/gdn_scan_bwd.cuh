@@ -14,7 +14,7 @@
 // (chunk, head, block), operands in the un-swizzled strip layout (sm100.cuh) whose rows are value channels, stored by
 // the thread that owns the channel (coalesced):
 //     ds_img  dS' as [64-channel half][value | residual][16 strips of 8 key dims][64 rows x 16 bytes]   = 64 KB
-//     dz_img  [64-channel half][dO^T | dZ^T][8 strips of 8 tokens][64 rows x 16 bytes], one bf16 each    = 32 KB
+//     dz_img  [64-channel half][dO^T | dZ^T | residual of dZ^T][8 strips of 8 tokens][64 rows x 16 bytes] = 48 KB
 #pragma once
 #include "scan_common.cuh"
 
@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
     // ---- C: dZ^T -> dV rows, partial sums of dZ V, the [dO^T | dZ^T] image, the operand [scale e^gam dO^T | -beta e^gam dZ^T]
     {
       // the [dO^T | dZ^T] image: my channel's row of strips half * 4 + g * 2 and the next one
-      uint8_t* img = reinterpret_cast<uint8_t*>(p.dz_img + cidx * 16384) + (vrow >> 6) * 16384 + (vrow & 63) * 16;
+      uint8_t* img = reinterpret_cast<uint8_t*>(p.dz_img + cidx * (2 * kDzHalf)) + (vrow >> 6) * (2 * kDzHalf) + (vrow & 63) * 16;
       float pr[32];
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
@@ -333,9 +333,14 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_bwd_kernel(GdnBwdPar
 #pragma unroll
         for (int i = 0; i < 16; ++i) pr[g * 16 + i] = dz[i] * t16[i];
         uint32_t w8[8];
-        pack16(dz, w8);
-        *reinterpret_cast<uint4*>(img + 8192 + (half * 4 + g * 2) * 1024) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-        *reinterpret_cast<uint4*>(img + 8192 + (half * 4 + g * 2 + 1) * 1024) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+        {
+          uint32_t zl[8];
+          split16(dz, w8, zl);     // dZ as value + residual: dA = -tril(dZ Vn^T) feeds dk, dg, dbeta through cancelling sums
+          *reinterpret_cast<uint4*>(img + 8192 + (half * 4 + g * 2) * 1024) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+          *reinterpret_cast<uint4*>(img + 8192 + (half * 4 + g * 2 + 1) * 1024) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+          *reinterpret_cast<uint4*>(img + 16384 + (half * 4 + g * 2) * 1024) = make_uint4(zl[0], zl[1], zl[2], zl[3]);
+          *reinterpret_cast<uint4*>(img + 16384 + (half * 4 + g * 2 + 1) * 1024) = make_uint4(zl[4], zl[5], zl[6], zl[7]);
+        }
 #pragma unroll
         for (int i4 = 0; i4 < 16; i4 += 4) {
           const float4 b4 = *reinterpret_cast<const float4*>(&f.b[t_lo + g * 16 + i4]);

@@ -23,6 +23,8 @@ constexpr int kScanThreads = 288;
 // The prep kernel leaves, behind the P tile of every (chunk, value head), the chunk's per-token factors as one ScanFactors
 // record: both scans fetch it with a single bulk copy straight into shared memory (global loads issued by the helper warp
 // took it thousands of cycles per chunk, with the whole CTA waiting at its next barrier).
+// [dO^T | dZ^T | residual of dZ^T] strips of one 64-channel half of a (chunk, head): bf16 elements
+constexpr int64_t kDzHalf = 12288;
 constexpr int64_t kPTileBytes = 16384;                 // P: value + residual, 64 x 64 bf16 each
 constexpr int64_t kPImgBytes = kPTileBytes + 1152;     // + the factor record (1040 bytes used), 128-byte aligned stride
 constexpr int64_t kPImg = kPImgBytes / 2;              // in bf16 elements: the per-(chunk, head) stride of p_img
