@@ -181,3 +181,17 @@ def test_two_half_launch_matches_single_launch(packed):
     again = run()
     for name, a, b in zip(NAMES + ("dh0",), split, again):
         assert torch.equal(a, b), name
+
+
+@pytest.mark.parametrize("seed,T", [(2013, 1024), (2010, 2048), (2007, 768), (2002, 2048)])
+def test_gradient_margin_over_seeds(seed, T):
+    """Seeds and lengths at which dk / dg / dbeta came closest to (and once crossed) the bar while dZ travelled between the two
+    backward kernels as a single bf16; with its residual every tensor stays below half the bar."""
+    from fla_b200.ops import chunk_gated_delta_rule_fwd_bwd
+    ref, d = _ref_and_inputs(1, T, 4, 8, seed=seed)
+    o, ht, grads = chunk_gated_delta_rule_fwd_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], initial_state=d["h0"],
+                                                  dht=d["dht"], output_dtype=torch.float32, grad_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert_close("o", o, ref["o"], TOL / 2)
+    for name, got in zip(NAMES + ("dh0",), grads):
+        assert_close(name, got, ref[name], TOL / 2)
