@@ -64,9 +64,10 @@ constexpr int64_t kDzImg = kDzHalf;   // per (chunk, head, block): 64x64 dO, 64x
 constexpr uint32_t rOffQK = 0, rQKPanel = 16384;
 constexpr uint32_t rOffAH = 49152;             // [dO^T | dZ^T] strips of one 64-channel step (16 KB)
 constexpr uint32_t rOffAL = 32768;             // [0 | residual of dZ^T]: 8 KB of zeros written once, then the step's 8 KB of strips
-constexpr uint32_t rOffVNH = 65536, rOffVNL = 73728;   // v_new^T value / residual strips; as an A operand with valid rows 64..127 the
-                                                       // view starts 8 KB earlier, inside the dZ^T strips (any finite contents do)
-constexpr uint32_t rOffSH = 81920, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 131072;
+// v_new^T and S strips, value / residual, interleaved so that [Vn_lo | S_hi] and [Vn_hi | S_lo] are each one contiguous B operand
+// of 24 strips.  As an A operand with valid rows 64..127 the view of v_new^T starts 8 KB earlier, inside the dZ^T strips or the
+// S strips (any finite contents do).
+constexpr uint32_t rOffVNL = 65536, rOffSH = 73728, rOffVNH = 90112, rOffSL = 98304, rOffDSH = 114688, rOffDSL = 131072;
 constexpr uint32_t rOffPAH = 147456, rOffPAL = 163840;   // [dP ; dAt] hi / lo (128 rows x 64)
 constexpr uint32_t kParSmem = 180224;
 constexpr uint32_t rColQK = 0, rColDV = 64, rColTA = 128, rColTB = 256;
@@ -128,8 +129,10 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
     mbar_arrive_expect_tx(&load_bar, kStepBytes);
     bulk_load(sb + rOffAH, p.dz_img + blk * (2 * kDzHalf) + hf * kDzHalf, 16384, &load_bar);      // [dO^T | dZ^T] strips
     bulk_load(sb + rOffAL + 8192, p.dz_img + blk * (2 * kDzHalf) + hf * kDzHalf + 8192, 8192, &load_bar);   // residual of dZ^T
-    bulk_load(sb + rOffVNH, p.vn_img + blk * 16384 + hf * 8192, 16384, &load_bar);     // [value | residual]
-    bulk_load(sb + rOffSH, p.s_img + blk * 32768 + hf * 16384, 32768, &load_bar);      // [value | residual], 16 strips each
+    bulk_load(sb + rOffVNH, p.vn_img + blk * 16384 + hf * 8192, 8192, &load_bar);           // value
+    bulk_load(sb + rOffVNL, p.vn_img + blk * 16384 + hf * 8192 + 4096, 8192, &load_bar);    // residual
+    bulk_load(sb + rOffSH, p.s_img + blk * 32768 + hf * 16384, 16384, &load_bar);           // value, 16 strips
+    bulk_load(sb + rOffSL, p.s_img + blk * 32768 + hf * 16384 + 8192, 16384, &load_bar);    // residual
     bulk_load(sb + rOffDSH, p.ds_img + blk * 32768 + hf * 16384, 32768, &load_bar);
   };
   // the same four pieces asked into L2 one step ahead: the buffer they will land in is still being read, so the load itself
@@ -184,7 +187,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
   const Operand opAL{sb + rOffAL, 1024, 2};                                               // [0; residual of dZ]: enters dA = -tril(dZ Vn^T) only
   const Operand opVNbH{sb + rOffVNH, 1024, 2}, opVNbL{sb + rOffVNL, 1024, 2};            // Vn as B (N = 64 tokens = 8 strips)
   const Operand opVNaH{sb + rOffVNH - 8192, 1024, 2}, opVNaL{sb + rOffVNL - 8192, 1024, 2};  // Vn as A: accumulator rows 64..127 are valid
-  const Operand opSH{sb + rOffSH, 1024, 2}, opSL{sb + rOffSL, 1024, 2};                  // S block as B (N = 128 key dims = 16 strips)
+  // (the S block, N = 128 key dims = 16 strips, follows each Vn image: the B operands of the N = 192 products start at Vn)
   const Operand opDSH{sb + rOffDSH, 1024, 2}, opDSL{sb + rOffDSL, 1024, 2};
   const Operand opPAH{sb + rOffPAH, 16384, 0}, opPAL{sb + rOffPAL, 16384, 0};            // [dP; dAt], reduction over j
   const Operand opPATh{sb + rOffPAH - 8192, 8192, 1}, opPATl{sb + rOffPAL - 8192, 8192, 1};  // its transpose, valid rows 64..127
@@ -265,11 +268,11 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
         tc_fence_after();
         if (h == 0 && vb == 0) mma_tile(tbase + rColQK, opQK, opKb, 128, 64, 8, false);
         const bool accf = vb > 0;
-        mma_tile(tbase + rColDV, opAH, opVNbH, 128, 64, 4, accf);
-        mma_tile(tbase + rColDV, opAH, opVNbL, 128, 64, 4, true);
+        // [dO; dZ] . [Vn_lo | S_hi]^T and [dO; dZ] . [Vn_hi | S_lo]^T as N = 192 products (the images are neighbours in shared memory, their
+        // accumulators neighbours in tensor memory): the A operand is read once for both
+        mma_tile(tbase + rColDV, opAH, opVNbL, 128, 192, 4, accf);
+        mma_tile(tbase + rColDV, opAH, opVNbH, 128, 192, 4, true);     // [Vn_hi | S_lo]
         mma_tile(tbase + rColDV, opAL, opVNbH, 128, 64, 4, true);
-        mma_tile(tbase + rColTA, opAH, opSH, 128, 128, 4, accf);
-        mma_tile(tbase + rColTA, opAH, opSL, 128, 128, 4, true);
         mma_tile(tbase + rColTB, opVNaH, opDSH, 128, 128, 4, accf);
         mma_tile(tbase + rColTB, opVNaH, opDSL, 128, 128, 4, true);
         mma_tile(tbase + rColTB, opVNaL, opDSH, 128, 128, 4, true);
@@ -278,7 +281,9 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
         else if (h + 1 < G) prefetch_loads(hv + 1, 0);
       }
       if (h > 0 && vb == 0 && tid < kC) finish_head(hv - 1, hb ^ 1, bz_prev);   // while the MMAs run
-      // <S, dS'> over this V block while the MMAs run (elementwise on the raw panel images)
+      // <S, dS'> over this V block while the MMAs run (elementwise on the raw images).  Values and residuals: the terms
+      // have either sign, so the sum is no larger than its rounding noise would be with the values alone (ragged chunks,
+      // where this term dominates dg, then miss the bar by 10x).
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t off = (tid + i * 256) * 16;
