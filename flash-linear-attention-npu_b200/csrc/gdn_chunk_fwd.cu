@@ -33,7 +33,7 @@ struct GdnFwdParams {
   float* gam;          // [tokens, HV]      chunk-local cumulative log decay (saved for backward)
   bf16* X;             // [chunks, HV, 2, 8 x 64 x 8]  the chunk's (I + A)^-1 as value + residual strips (saved for backward)
   float* at;           // [chunks, HV, 64, 64] scratch: A^T handed to the triangular-inverse kernel
-  bf16* p_img;         // [chunks, HV, 2, 64x64] tril(Q K^T * decay) as hi / lo operand panels (scratch, reused by backward)
+  bf16* p_img;         // [chunks, HV, kPImg]: tril(Q K^T * decay) as value / residual strips, then the chunk's factor record (reused by backward)
   const float* h0;     // [N, HV, K, V] or null
   float* ht;           // [N, HV, K, V] or null
   void* o;             // [tokens, HV, V]

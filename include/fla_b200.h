@@ -226,7 +226,7 @@ FLA_API int fla_b200_causal_conv1d_update(const fla_causal_conv1d_update_args* a
  * Token tensors need a contiguous last dim, 16-byte aligned rows and batch rows laid out back to back.
  * Workspace: a 256-byte status block (first int32 becomes FLA_ERR_TIMEOUT if a device-side wait ran out)
  * followed by a 16 KB fp32 scratch tile per (chunk, value head) for the triangular inverse and, when p_img is
- * absent, 16 KB per (chunk, value head) for the score panels. */
+ * absent, 17,536 bytes per (chunk, value head) for the score tile and the chunk's factor record. */
 typedef struct fla_gdn_chunk_fwd_args {
   fla_tensor_t q, k, v, g, beta, initial_state;
   fla_tensor_t o, final_state, gam, x_inv, s_img, vn_img, p_img;
