@@ -270,6 +270,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_par_kernel(GdnBwdParams p, con
         const bool accf = vb > 0;
         // [dO; dZ] . [Vn_lo | S_hi]^T and [dO; dZ] . [Vn_hi | S_lo]^T as N = 192 products (the images are neighbours in shared memory, their
         // accumulators neighbours in tensor memory): the A operand is read once for both
+        static_assert(rOffVNL + 8192 == rOffSH && rOffVNH + 8192 == rOffSL && rColDV + 64 == rColTA, "the N = 192 products need these adjacent");
         mma_tile(tbase + rColDV, opAH, opVNbL, 128, 192, 4, accf);
         mma_tile(tbase + rColDV, opAH, opVNbH, 128, 192, 4, true);     // [Vn_hi | S_lo]
         mma_tile(tbase + rColDV, opAL, opVNbH, 128, 64, 4, true);

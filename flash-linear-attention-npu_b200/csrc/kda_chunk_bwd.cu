@@ -508,10 +508,12 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_par_kernel(KdaBwdParams p, con
           mma_tile(tbase + qColQK, opQKl, opKNbh, 128, 64, 8, true);
         }
         const bool accf = vb > 0;
-        mma_tile(tbase + qColDV, opAH, opVNbH, 128, 64, 4, accf);
-        mma_tile(tbase + qColDV, opAH, opVNbL, 128, 64, 4, true);
+        // [dO; dZ] . [Vn_lo | Sa_hi]^T as one N = 192 product: the two images are neighbours in shared memory and their
+        // accumulators neighbours in tensor memory, so the A operand is read once for both
+        static_assert(qOffVNL + 8192 == qOffSH && qColDV + 64 == qColTA, "the N = 192 product needs both pairs adjacent");
+        mma_tile(tbase + qColDV, opAH, opVNbL, 128, 192, 4, accf);
+        mma_tile(tbase + qColDV, opAH, opVNbH, 128, 64, 4, true);
         mma_tile(tbase + qColDV, opAL, opVNbH, 128, 64, 4, true);
-        mma_tile(tbase + qColTA, opAH, opSH, 128, 128, 4, accf);
         mma_tile(tbase + qColTA, opAH, opSL, 128, 128, 4, true);
         mma_tile(tbase + qColTA, opAL, opSH, 128, 128, 4, true);
         mma_tile(tbase + qColTB1, opVNaH, opDSH, 128, 128, 4, accf);
