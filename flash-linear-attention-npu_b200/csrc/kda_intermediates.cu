@@ -1,0 +1,245 @@
+// The head-major intermediates of the reference's low-level KDA forward, npu_chunk_kda_fwd with disable_recompute /
+// return_intermediate_states (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1066-1265, visibility rule
+// _kda_policy.py:15-37; definitions in the golden tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:447-492):
+//     qg = q 2^{gk}      kg = k 2^{gk_last - gk}      w = Akk (beta k 2^{gk})      u = Akk (beta v)
+//     v_new = u - w S    h  = S, the state at the start of each chunk
+// The fused forward never forms w and u and keeps S, v_new only as operand images of its `saved` buffer.  This kernel
+// runs after it, chunk-parallel on CUDA cores in fp32: w and u from the inverse image (value + residual panels), v_new
+// and h read back from the saved images (h = diag(e^-a) Sa undoes the per-channel anchor the forward applies), qg and kg
+// from q, k and the saved cumulative gate.  An export path: nothing of it runs unless a caller asks for these tensors.
+#include <cuda_fp16.h>
+#include <atomic>
+#include "gdn_common.cuh"
+#include "fla_b200_internal.h"
+#include "kernel_timer.h"
+#include "kda_common.cuh"
+
+namespace fla {
+namespace {
+
+struct OutView {
+  void* p; int dtype; int64_t sb, st, sh;
+};
+struct InView {
+  const bf16* p; int64_t sb, st, sh;
+};
+
+struct KdaInterParams {
+  InView q, k, v;
+  const void* beta; int beta_is_f32; int64_t beta_sb, beta_st, beta_sh;
+  const float* gk;        // [tokens, HV, K] chunk-local cumulative gate (natural log) of the saved buffer
+  const bf16* x_img;      // (I + Akk)^-1 per (chunk, head): value + residual panels
+  const float* vec;       // per (chunk, head): e^a, e^{gk_L - a}, a
+  const bf16* s_img;      // Sa = diag(e^a) S per (chunk, head, 64-column block of V): value + residual panels
+  const bf16* vn_img;     // v_new per (chunk, head, block): value + residual panels
+  OutView w, u, qg, kg, vn;
+  void* h; int h_dtype, h_vfirst;
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int T, HK, HV, V, nvb;
+};
+
+__device__ __forceinline__ void put(void* p, int dtype, int64_t idx, float x) {
+  if (dtype == FLA_F32) static_cast<float*>(p)[idx] = x;
+  else if (dtype == FLA_F16) static_cast<__half*>(p)[idx] = __float2half_rn(x);
+  else static_cast<bf16*>(p)[idx] = __float2bfloat16_rn(x);
+}
+__device__ __forceinline__ float panel_val(const uint8_t* hi, uint32_t lo_off, int row, int col) {
+  const uint32_t o = panel_off(row, col);
+  return __bfloat162float(*reinterpret_cast<const bf16*>(hi + o)) + __bfloat162float(*reinterpret_cast<const bf16*>(hi + lo_off + o));
+}
+
+constexpr int kInterSmem = (kC * kC + kC * 128) * 4;   // X^T and one 64 x 128 right-hand side, fp32
+
+// out[i][c] = sum_j X[i][j] rhs[j][c] for this thread's column c and 32 rows; X is lower triangular (zeros above it are stored)
+__device__ __forceinline__ void tri_apply(const float* xt, const float* rhs, int c, int ih, float* acc) {
+#pragma unroll
+  for (int r = 0; r < 32; ++r) acc[r] = 0.f;
+  for (int j = 0; j < kC; ++j) {
+    const float b = rhs[j * 128 + c];
+    const float4* xr = reinterpret_cast<const float4*>(xt + j * kC + ih * 32);
+#pragma unroll
+    for (int r4 = 0; r4 < 8; ++r4) {
+      const float4 x4 = xr[r4];
+      acc[4 * r4] += x4.x * b; acc[4 * r4 + 1] += x4.y * b; acc[4 * r4 + 2] += x4.z * b; acc[4 * r4 + 3] += x4.w * b;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) kda_intermediates_kernel(KdaInterParams p) {
+  extern __shared__ float inter_smem[];
+  float* xt = inter_smem;               // xt[j * 64 + i] = X[i][j]
+  float* rhs = inter_smem + kC * kC;    // rhs[j * 128 + c]
+  __shared__ float beta_s[kC], ea_s[kK];
+  const int tid = threadIdx.x;
+  const int n = blockIdx.z, hv = blockIdx.y, c = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (c >= sq.nt) return;
+  const int rows = min(kC, sq.len - c * kC);
+  const int hk = hv / (p.HV / p.HK);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + c * kC;      // first token of the chunk inside batch row b
+  const int64_t flat0 = b * p.T + t0;                           // the same in the saved buffer's flat token order
+  const int64_t chunk = int64_t(sq.cbase) + c;
+  const int64_t cidx = chunk * p.HV + hv;
+  const bool full = p.w.p || p.u.p || p.qg.p || p.kg.p;
+
+  if (full) {
+    const uint8_t* xi = reinterpret_cast<const uint8_t*>(p.x_img + cidx * kKdaXImg);
+    for (int idx = tid; idx < kC * kC; idx += 256) {
+      const int i = idx & 63, j = idx >> 6;
+      xt[j * kC + i] = (i < rows && j < rows) ? panel_val(xi, 8192, i, j) : 0.f;
+    }
+    if (tid < kC)
+      beta_s[tid] = tid < rows ? ld_scalar(p.beta, b * p.beta_sb + (t0 + tid) * p.beta_st + hv * p.beta_sh, p.beta_is_f32) : 0.f;
+  }
+  if (p.h && tid < kK) ea_s[tid] = expf(-p.vec[cidx * kKdaVecs * kK + 2 * kK + tid]);
+  __syncthreads();
+
+  const int col = tid & 127, ih = tid >> 7;
+  if (full) {
+    // qg, kg and the right-hand side beta k 2^{gk} of w
+    const float* gkc = p.gk + (flat0 * p.HV + hv) * kK + col;
+    const float g_last = gkc[int64_t(rows - 1) * p.HV * kK];
+    for (int s = 0; s < 32; ++s) {
+      const int t = ih + 2 * s;
+      float r = 0.f;
+      if (t < rows) {
+        const float g = gkc[int64_t(t) * p.HV * kK];
+        const float e = expf(g);
+        const float qv = __bfloat162float(p.q.p[b * p.q.sb + (t0 + t) * p.q.st + hk * p.q.sh + col]);
+        const float kv = __bfloat162float(p.k.p[b * p.k.sb + (t0 + t) * p.k.st + hk * p.k.sh + col]);
+        if (p.qg.p) put(p.qg.p, p.qg.dtype, b * p.qg.sb + (t0 + t) * p.qg.st + hv * p.qg.sh + col, qv * e);
+        if (p.kg.p) put(p.kg.p, p.kg.dtype, b * p.kg.sb + (t0 + t) * p.kg.st + hv * p.kg.sh + col, kv * expf(g_last - g));
+        r = beta_s[t] * kv * e;
+      }
+      rhs[t * 128 + col] = r;
+    }
+    __syncthreads();
+    float acc[32];
+    if (p.w.p) {
+      tri_apply(xt, rhs, col, ih, acc);
+#pragma unroll
+      for (int r = 0; r < 32; ++r)
+        if (ih * 32 + r < rows) put(p.w.p, p.w.dtype, b * p.w.sb + (t0 + ih * 32 + r) * p.w.st + hv * p.w.sh + col, acc[r]);
+    }
+    if (p.u.p) {
+      for (int vh = 0; vh < p.V / 128; ++vh) {   // u = Akk (beta v), 128 value channels at a time
+        __syncthreads();
+        for (int s = 0; s < 32; ++s) {
+          const int t = ih + 2 * s;
+          rhs[t * 128 + col] = t < rows ? beta_s[t] * __bfloat162float(p.v.p[b * p.v.sb + (t0 + t) * p.v.st + hv * p.v.sh + vh * 128 + col]) : 0.f;
+        }
+        __syncthreads();
+        tri_apply(xt, rhs, col, ih, acc);
+#pragma unroll
+        for (int r = 0; r < 32; ++r)
+          if (ih * 32 + r < rows)
+            put(p.u.p, p.u.dtype, b * p.u.sb + (t0 + ih * 32 + r) * p.u.st + hv * p.u.sh + vh * 128 + col, acc[r]);
+      }
+    }
+  }
+  // v_new and h straight from the saved images
+  for (int vb = 0; vb < p.nvb; ++vb) {
+    if (p.vn.p) {
+      const uint8_t* img = reinterpret_cast<const uint8_t*>(p.vn_img + (cidx * p.nvb + vb) * kKdaVnImg);
+      for (int idx = tid; idx < kC * 64; idx += 256) {
+        const int t = idx >> 6, ch = idx & 63;
+        if (t < rows) put(p.vn.p, p.vn.dtype, b * p.vn.sb + (t0 + t) * p.vn.st + hv * p.vn.sh + vb * 64 + ch, panel_val(img, 8192, t, ch));
+      }
+    }
+    if (p.h) {
+      const uint8_t* img = reinterpret_cast<const uint8_t*>(p.s_img + (cidx * p.nvb + vb) * kKdaSImg);
+      for (int idx = tid; idx < kK * 64; idx += 256) {
+        const int kd = idx >> 6, ch = idx & 63;
+        const float x = panel_val(img, 16384, kd, ch) * ea_s[kd];
+        const int64_t o = p.h_vfirst ? (cidx * p.V + vb * 64 + ch) * kK + kd : (cidx * kK + kd) * p.V + vb * 64 + ch;
+        put(p.h, p.h_dtype, o, x);
+      }
+    }
+  }
+}
+
+bool in_view(const fla_tensor_t& t, int64_t B, int64_t T, int64_t H, int64_t D, InView* v) {
+  if (!t.data || t.ndim != 4 || t.dtype != FLA_BF16 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != H || t.shape[3] != D ||
+      t.stride[3] != 1)
+    return false;
+  *v = InView{static_cast<const bf16*>(t.data), t.stride[0], t.stride[1], t.stride[2]};
+  return true;
+}
+int out_view(const fla_tensor_t& t, int64_t B, int64_t T, int64_t H, int64_t D, OutView* v) {
+  *v = OutView{nullptr, 0, 0, 0, 0};
+  if (!t.data) return FLA_OK;
+  if (t.ndim != 4 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != H || t.shape[3] != D || t.stride[3] != 1) return FLA_ERR_SHAPE;
+  if (t.dtype != FLA_BF16 && t.dtype != FLA_F16 && t.dtype != FLA_F32) return FLA_ERR_DTYPE;
+  *v = OutView{t.data, t.dtype, t.stride[0], t.stride[1], t.stride[2]};
+  return FLA_OK;
+}
+
+}  // namespace
+}  // namespace fla
+
+extern "C" FLA_API int fla_b200_kda_chunk_intermediates(const fla_kda_intermediates_args* a, void* stream) {
+  using namespace fla;
+  if (!a) return FLA_ERR_NULL;
+  if (!a->q.data || !a->k.data || !a->v.data || !a->beta.data || !a->saved.data) return FLA_ERR_NULL;
+  if (a->q.ndim != 4 || a->v.ndim != 4) return FLA_ERR_SHAPE;
+  const int64_t B = a->q.shape[0], T = a->q.shape[1], HK = a->q.shape[2], HV = a->v.shape[2], V = a->v.shape[3];
+  if (a->q.shape[3] != kK || (V != 128 && V != 256) || HK <= 0 || HV % HK) return FLA_ERR_SHAPE;
+  KdaInterParams p{};
+  if (!in_view(a->q, B, T, HK, kK, &p.q) || !in_view(a->k, B, T, HK, kK, &p.k) || !in_view(a->v, B, T, HV, V, &p.v)) return FLA_ERR_SHAPE;
+  const fla_tensor_t& be = a->beta;
+  if (be.ndim != 3 || be.shape[0] != B || be.shape[1] != T || be.shape[2] != HV) return FLA_ERR_SHAPE;
+  if (be.dtype != FLA_F32 && be.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  p.beta = be.data; p.beta_is_f32 = be.dtype == FLA_F32; p.beta_sb = be.stride[0]; p.beta_st = be.stride[1]; p.beta_sh = be.stride[2];
+  int N = int(B), max_len = int(T);
+  int64_t total_chunks = B * ((T + kC - 1) / kC);
+  if (a->cu_seqlens.data) {
+    if (B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    N = int(a->cu_seqlens.shape[0] - 1);
+    if (!a->chunk_offsets.data || a->chunk_offsets.dtype != FLA_I32 || a->chunk_offsets.shape[0] != N + 1) return FLA_ERR_SHAPE;
+    if (a->max_seqlen <= 0 || a->max_seqlen > T || a->total_chunks <= 0) return FLA_ERR_VALUE;
+    max_len = a->max_seqlen;
+    total_chunks = a->total_chunks;
+  }
+  const int64_t nvb = V / 64;
+  uint64_t soff[4], woff[6];
+  const uint64_t sbytes = kda_saved_layout(total_chunks, HV, nvb, B * T, soff);
+  kda_ws_layout(total_chunks, HV, woff);
+  if (a->saved.dtype != FLA_BF16 || a->saved.ndim != 1 || uint64_t(a->saved.shape[0]) * 2 < sbytes || !aligned16(a->saved.data))
+    return FLA_ERR_SHAPE;
+  const uint8_t* sv = static_cast<const uint8_t*>(a->saved.data);
+  p.x_img = reinterpret_cast<const bf16*>(sv + soff[0] + woff[3]);
+  p.vec = reinterpret_cast<const float*>(sv + soff[0] + woff[4]);
+  p.gk = reinterpret_cast<const float*>(sv + soff[1]);
+  p.s_img = reinterpret_cast<const bf16*>(sv + soff[2]);
+  p.vn_img = reinterpret_cast<const bf16*>(sv + soff[3]);
+  int st;
+  if ((st = out_view(a->w, B, T, HV, kK, &p.w)) || (st = out_view(a->u, B, T, HV, V, &p.u)) || (st = out_view(a->qg, B, T, HV, kK, &p.qg)) ||
+      (st = out_view(a->kg, B, T, HV, kK, &p.kg)) || (st = out_view(a->v_new, B, T, HV, V, &p.vn)))
+    return st;
+  if (a->h.data) {
+    const fla_tensor_t& h = a->h;
+    const int64_t r = a->state_v_first ? V : kK, cdim = a->state_v_first ? kK : V;
+    if (h.ndim != 4 || h.shape[0] != total_chunks || h.shape[1] != HV || h.shape[2] != r || h.shape[3] != cdim) return FLA_ERR_SHAPE;
+    if (h.stride[3] != 1 || h.stride[2] != cdim || h.stride[1] != r * cdim || h.stride[0] != HV * r * cdim) return FLA_ERR_LAYOUT;
+    if (h.dtype != FLA_BF16 && h.dtype != FLA_F16 && h.dtype != FLA_F32) return FLA_ERR_DTYPE;
+    p.h = h.data; p.h_dtype = h.dtype; p.h_vfirst = a->state_v_first != 0;
+  }
+  if (!p.w.p && !p.u.p && !p.qg.p && !p.kg.p && !p.vn.p && !p.h) return FLA_OK;
+  p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+  p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
+  p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.V = int(V); p.nvb = int(nvb);
+
+  static std::atomic<bool> attr_done_dev[64] = {};   // per device ordinal; setting the attribute twice is harmless
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (!attr_done_dev[dev]) {
+    if (cudaFuncSetAttribute(kda_intermediates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kInterSmem) != cudaSuccess) return FLA_ERR_CUDA;
+    attr_done_dev[dev] = true;
+  }
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const int nt_max = (max_len + kC - 1) / kC;
+  KernelTimer kt("kda_intermediates", cs);
+  kda_intermediates_kernel<<<dim3(nt_max, unsigned(HV), N), 256, kInterSmem, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}

@@ -58,6 +58,12 @@ class KdaChunkBwdArgs(ctypes.Structure):
         ("total_chunks", ctypes.c_int32)]
 
 
+class KdaIntermediatesArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "v", "beta", "saved", "cu_seqlens", "chunk_offsets", "w", "u", "qg", "kg",
+                                           "v_new", "h")] + [
+        ("max_seqlen", ctypes.c_int32), ("total_chunks", ctypes.c_int32), ("state_v_first", ctypes.c_int32)]
+
+
 class L2NormArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("x", "y", "rstd", "dy", "dx")] + [("eps", ctypes.c_float)]
 

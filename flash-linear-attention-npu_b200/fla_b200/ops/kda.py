@@ -151,10 +151,12 @@ def _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound):
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
               use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
               cu_seqlens=None, safe_gate=False, lower_bound=None, A_log=None, dt_bias=None,
-              return_gate_cumsum=False, output_dtype=None, disable_recompute=False, export_scores=None):
+              return_gate_cumsum=False, output_dtype=None, disable_recompute=False, export_scores=None,
+              _return_saved=False):
     """Returns ``(o [B,T,HV,V], final_state [N,HV,K,V] | None)`` (plus the cumulative gate `[B,T,HV,K]` fp32
     when ``return_gate_cumsum``).  ``export_scores`` (inference only): a pair of `[B,T,HV,64]` views that receive the
-    per-chunk blocks Aqk and Akk (what `npu_chunk_kda_fwd` returns)."""
+    per-chunk blocks Aqk and Akk (what `npu_chunk_kda_fwd` returns).  ``_return_saved`` (inference only, used by
+    `npu_chunk_kda_fwd`): also return the buffer of forward intermediates, the chunk metadata and the row-major inputs."""
     op = "chunk_kda"
     if use_beta_sigmoid_in_kernel:
         # beta arrives as logits.  It is a [B,T,HV] tensor, 1/128 of the gate's bytes: the activation (and, through autograd,
@@ -175,7 +177,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
                         use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, use_gate_in_kernel=use_gate_in_kernel,
                         use_beta_sigmoid_in_kernel=False, cu_seqlens=cu_seqlens, safe_gate=safe_gate, lower_bound=lower_bound,
                         A_log=A_log, dt_bias=dt_bias, return_gate_cumsum=return_gate_cumsum, output_dtype=torch.float32,
-                        disable_recompute=disable_recompute, export_scores=export_scores)
+                        disable_recompute=disable_recompute, export_scores=export_scores, _return_saved=_return_saved)
         return (to_dtype(res[0], output_dtype or torch.float16, op),) + tuple(res[1:])
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != torch.bfloat16:
@@ -199,7 +201,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
             raise RuntimeError(f"{op}: use_gate_in_kernel needs A_log")
         if safe_gate and lower_bound is None:
             raise RuntimeError(f"{op}: safe_gate needs lower_bound")
-        if needs_grad:
+        if needs_grad or _return_saved:   # the kernels keep their intermediates only for gates given as they are
             g = _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound)
         else:
             gate_mode = 2 if safe_gate else 1
@@ -229,11 +231,45 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     if use_qk_l2norm_in_kernel:   # x * rsqrt(sum x^2 + 1e-6), stored in the input dtype (the l2norm kernels)
         from .l2norm import l2norm_fwd
         q, k = l2norm_fwd(q)[0], l2norm_fwd(k)[0]
+    if _return_saved:
+        o, ht, saved = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, 0, None, None, None, meta,
+                                    False, output_dtype, keep_for_backward=True, scores=export_scores)
+        return o, ht, saved, meta, (q, k, v, beta)
     o, ht, gk = _kda_forward(q, k, v, g, beta, scale, initial_state, output_final_state, gate_mode, A_log, dt_bias,
                              lower_bound, meta, return_gate_cumsum, output_dtype, scores=export_scores)
     if return_gate_cumsum:
         return o, ht, gk
     return o, ht
+
+
+def kda_chunk_intermediates(q, k, v, beta, saved, meta, *, full, state_v_first=False, dtype=None):
+    """w, u, qg, kg, v_new `[B,HV,T,.]` (when ``full``) and h `[B*NT | chunks, HV, K, V]` from the buffer a forward with
+    ``keep_for_backward`` left (`fla_b200_kda_chunk_intermediates`): a chunk-parallel fp32 pass outside the hot path."""
+    from ._structs import KdaIntermediatesArgs
+    B, T, HK, K = q.shape
+    HV, V = v.shape[2], v.shape[3]
+    cu, co, N, max_len, total_chunks = meta
+    dev, dtype = q.device, dtype or q.dtype
+    outs = {}
+    if full:
+        for name, d in (("w", K), ("u", V), ("qg", K), ("kg", K), ("v_new", V)):
+            outs[name] = torch.zeros((B, HV, T, d), dtype=dtype, device=dev)
+    hshape = (total_chunks, HV, V, K) if state_v_first else (total_chunks, HV, K, V)
+    h = torch.empty(hshape, dtype=dtype, device=dev)
+    a = KdaIntermediatesArgs()
+    a.q, a.k, a.v, a.beta, a.saved = rt.desc(q), rt.desc(k), rt.desc(v), rt.desc(beta), rt.desc(saved)
+    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    for name, t in outs.items():
+        setattr(a, name, rt.desc(t.transpose(1, 2)))
+    a.h = rt.desc(h)
+    a.max_seqlen, a.total_chunks, a.state_v_first = int(max_len), int(total_chunks), int(bool(state_v_first))
+    lib = load_library()
+    rt._check_arch(dev, "kda_chunk_intermediates")
+    with torch.cuda.device(dev):
+        status = lib.fla_b200_kda_chunk_intermediates(ctypes.byref(a), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if status != 0:
+        raise RuntimeError(f"kda_chunk_intermediates failed with status={status}: {rt._STATUS_NAMES.get(status, '?')}")
+    return outs, h
 
 
 def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", initial_state=None, output_final_state=False,
@@ -242,9 +278,10 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     """The reference's low-level KDA forward (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1066-1265) with its
     12-value return `(attn_out, final_state, gk, Aqk, Akk, w, u, qg, kg, v_new, h, initial_state)` and the visibility rule of
     `_kda_policy.py:15-37`: final_state when asked for, gk (base-2 chunk-local cumulative gate, head-first fp32) unless the gate
-    is activated in the kernel, Aqk and Akk `[B,HV,T,64]` always.  The head-major intermediates w, u, qg, kg, v_new, h never exist
-    in the fused kernels, so `disable_recompute=True` and `return_intermediate_states=True` (which make them visible) are
-    refused.  `state_v_first=True` takes and returns the recurrent state as `[N,HV,V,K]`.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
+    is activated in the kernel, Aqk and Akk `[B,HV,T,64]` always.  The head-major intermediates never exist in the fused
+    kernels; `disable_recompute=True` (w, u, qg, kg, v_new, h and gk) and `return_intermediate_states=True` (h) run a
+    second, chunk-parallel pass over the forward's saved operand images that forms them (`kda_chunk_intermediates`), with
+    the gate activated in front of the kernels when `use_gate_in_kernel` is set.  `state_v_first=True` takes and returns the recurrent state as `[N,HV,V,K]`.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
     comes back in the input's layout."""
     del chunk_indices
     op = "npu_chunk_kda_fwd"
@@ -255,8 +292,8 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
         raise RuntimeError(f"{op}: chunk_size must be 64 or 128.")
     if int(chunk_size) != CHUNK:
         raise NotImplementedError(f"{op}: this build supports chunk_size = 64")
-    if disable_recompute or return_intermediate_states:
-        raise NotImplementedError(f"{op}: w, u, qg, kg, v_new and h are not materialised by the fused kernels")
+    want_full = bool(disable_recompute)
+    want_h = want_full or bool(return_intermediate_states)
     rank3 = layout in {"TND", "NTD"}
 
     def to_bsnd(t):
@@ -282,13 +319,22 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
         if initial_state.dim() != 4 or initial_state.shape[-2] != vb.shape[-1] or initial_state.shape[-1] != K:
             raise RuntimeError(f"{op}: initial_state shape does not match state_v_first.")
         h0 = initial_state.transpose(-1, -2)
+    inter, h = {}, None
     with torch.no_grad():
-        o, ht = chunk_kda(qb, kb, vb, gb, bb, scale=scale, initial_state=h0, output_final_state=output_final_state,
-                          cu_seqlens=cu_seqlens, export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), **gate_kw)
+        if want_h:
+            o, ht, saved, meta, rows_in = chunk_kda(qb, kb, vb, gb, bb, scale=scale, initial_state=h0,
+                                                    output_final_state=output_final_state, cu_seqlens=cu_seqlens,
+                                                    export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), _return_saved=True,
+                                                    **gate_kw)
+            inter, h = kda_chunk_intermediates(*rows_in, saved, meta, full=want_full, state_v_first=state_v_first, dtype=q.dtype)
+            h = h if rank3 else h.view(B, -1, *h.shape[1:])
+        else:
+            o, ht = chunk_kda(qb, kb, vb, gb, bb, scale=scale, initial_state=h0, output_final_state=output_final_state,
+                              cu_seqlens=cu_seqlens, export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), **gate_kw)
     gk_out = None
-    if not use_gate_in_kernel:
+    if not use_gate_in_kernel or want_full:
         from .stages import kda_gate_cumsum
-        gk_out = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens).permute(0, 2, 1, 3)       # [B,HV,T,K]
+        gk_out = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens, **{k_: v_ for k_, v_ in gate_kw.items()}).permute(0, 2, 1, 3)   # [B,HV,T,K]
     if state_v_first and ht is not None:
         ht = ht.transpose(-1, -2).contiguous()
     if layout in {"BNSD", "NTD"}:
@@ -296,5 +342,7 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     if rank3:
         o, aqk, akk = o.squeeze(0), aqk.squeeze(0), akk.squeeze(0)
         gk_out = None if gk_out is None else gk_out.squeeze(0)
-    return o, ht, gk_out, aqk, akk, None, None, None, None, None, None, initial_state
+        inter = {n: t.squeeze(0) for n, t in inter.items()}
+    return (o, ht, gk_out, aqk, akk, inter.get("w"), inter.get("u"), inter.get("qg"), inter.get("kg"), inter.get("v_new"), h,
+            initial_state)
 

@@ -323,6 +323,29 @@ FLA_API int fla_b200_kda_chunk_saved_size(const fla_kda_chunk_fwd_args* args, ui
 FLA_API int fla_b200_kda_chunk_fwd(const fla_kda_chunk_fwd_args* args, void* workspace, uint64_t workspace_bytes,
                                    void* stream);
 
+/* The head-major intermediates of the reference's low-level KDA forward: what npu_chunk_kda_fwd returns in addition under
+ * disable_recompute=True (w, u, qg, kg, v_new, h) or return_intermediate_states=True (h)
+ * (torch_custom/fla_npu/fla_npu/ops/ascendc/_aclnn_ctypes.py:1066-1265, visibility _kda_policy.py:15-37, definitions
+ * tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:447-492):
+ *     qg = q 2^{gk}    kg = k 2^{gk_last - gk}    w = Akk (beta k 2^{gk})    u = Akk (beta v)    v_new = u - w S    h = S
+ * with gk the chunk-local cumulative gate in base 2, Akk the chunk inverse and S the state at the start of each chunk.
+ * Runs after fla_b200_kda_chunk_fwd on the `saved` buffer that call filled (same q, k, v, beta, cu_seqlens, chunk_offsets,
+ * max_seqlen, total_chunks): a chunk-parallel fp32 pass on CUDA cores, outside the hot path.
+ *   w, qg, kg [B, T, HV, K], u, v_new [B, T, HV, V]: optional out, bf16|f16|f32, any strides with a contiguous last dim
+ *       (the reference's head-first [B, HV, T, .] tensors are passed as transposed views)
+ *   h [total_chunks, HV, K, V] ([.., V, K] with state_v_first), dense, bf16|f16|f32, optional out
+ * Single-phase (no workspace). */
+typedef struct fla_kda_intermediates_args {
+  fla_tensor_t q, k, v, beta;
+  fla_tensor_t saved;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  fla_tensor_t w, u, qg, kg, v_new, h;
+  int32_t max_seqlen;
+  int32_t total_chunks;
+  int32_t state_v_first;
+} fla_kda_intermediates_args;
+FLA_API int fla_b200_kda_chunk_intermediates(const fla_kda_intermediates_args* args, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Chunked Kimi Delta Attention, backward (gate_mode 0: g is the per-channel log decay).
  * The reference has only the intra-chunk piece (aclnnChunkKdaBwdIntra as bound by npu_chunk_kda_bwd_intra,

@@ -81,8 +81,10 @@ def test_visibility_and_refusals():
     A_log = torch.zeros(1).cuda()
     out = npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, use_gate_in_kernel=True, A_log=A_log)
     assert out[2] is None                                                      # gate activated in the kernel: gk hidden
-    with pytest.raises(NotImplementedError):
-        npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, disable_recompute=True)
+    out = npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, return_intermediate_states=True)
+    assert all(x is None for x in out[5:10]) and tuple(out[10].shape) == (1, 1, 1, 128, 128)   # h alone
+    out = npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, use_gate_in_kernel=True, A_log=A_log, disable_recompute=True)
+    assert out[2] is not None and all(x is not None for x in out[5:11])       # disable_recompute shows gk and all six
     with pytest.raises(RuntimeError, match="chunk_size must be 64 or 128"):
         npu_chunk_kda_fwd(*args, 128 ** -0.5, 32)
     with pytest.raises(RuntimeError, match="layout must be uppercase"):
@@ -107,3 +109,62 @@ def test_state_v_first_and_value_dim_256():
     assert_close("ht", a[1], ref["ht"], 5e-3)
     with pytest.raises(RuntimeError, match="state_v_first"):
         npu_chunk_kda_fwd(*args, scale, 64, initial_state=h0.cuda(), state_v_first=True)
+
+
+def test_intermediates_replay_the_reference_golden():
+    """disable_recompute=True: w, u, qg, kg, v_new, h against the fixture the reference's own chunked golden produced
+    (tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:447-492) on a packed GVA case with a ragged last chunk and an initial
+    state; the other outputs must not change when the intermediates are asked for."""
+    import numpy as np
+    from pathlib import Path
+    from fla_b200.ops import npu_chunk_kda_fwd
+    f = {n: torch.from_numpy(np.asarray(a)) for n, a in np.load(Path(__file__).parent / "golden" / "kda_chunk_fwd_golden.npz").items()}
+    cu = [int(x) for x in f["cu"]]
+    bf = lambda n: f[n].squeeze(0).bfloat16().cuda()  # noqa: E731   (the fixture's inputs are bf16-valued)
+    args = (bf("q"), bf("k"), bf("v"), bf("g"), bf("beta"), float(f["scale"]), 64)
+    kw = dict(layout="TND", initial_state=f["h0"].cuda(), output_final_state=True, cu_seqlens=cu)
+    plain = npu_chunk_kda_fwd(*args, **kw)
+    out = npu_chunk_kda_fwd(*args, disable_recompute=True, **kw)
+    for i in range(5):
+        assert torch.equal(out[i], plain[i])
+    names = ("w", "u", "qg", "kg", "v_new")
+    for name, got in zip(names, out[5:10]):
+        assert got.dtype == torch.bfloat16 and tuple(got.shape) == tuple(f[name].shape[1:])
+        assert_close(name, got.unsqueeze(0), f[name], 5e-3, stored_bf16=True)
+    assert tuple(out[10].shape) == tuple(f["h"].shape[1:])
+    assert_close("h", out[10].unsqueeze(0), f["h"], 5e-3, stored_bf16=True)
+    only_h = npu_chunk_kda_fwd(*args, return_intermediate_states=True, **kw)
+    assert all(x is None for x in only_h[5:10]) and torch.equal(only_h[10], out[10])
+
+
+@pytest.mark.parametrize("layout", ["BSND", "BNSD"])
+def test_intermediates_fixed_length_layouts_and_v_first(layout):
+    """Fixed-length batches in both rank-4 layouts, V = 256 and `state_v_first`: the intermediates satisfy the relations that
+    define them, v_new = u - w S and S_next = 2^{gk_last} S + kg^T v_new, checked in fp64 on what the call returned (every
+    returned tensor is rounded to bf16, and u - w S cancels: 5e-2 of the RMS covers that rounding, a wrong layout or a
+    missing factor misses it by orders of magnitude; the values themselves are pinned by the golden replay above)."""
+    from fla_b200.ops import npu_chunk_kda_fwd
+    B, T, HK, HV, V = 2, 192, 1, 2, 256
+    inp = oracle.make_kda_inputs(B, T, HK, HV, V=V, seed=53, with_grad=False)
+    h0 = 0.1 * torch.randn(B, HV, 128, V, generator=torch.Generator().manual_seed(6))
+
+    def lay(t):
+        return t.cuda().transpose(1, 2).contiguous() if layout == "BNSD" else t.cuda()
+
+    args = [lay(inp[n]) for n in ("q", "k", "v", "g", "beta")]
+    out = npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, layout=layout, initial_state=h0.cuda(), output_final_state=True,
+                            disable_recompute=True)
+    outv = npu_chunk_kda_fwd(*args, 128 ** -0.5, 64, layout=layout, initial_state=h0.transpose(-1, -2).contiguous().cuda(),
+                             output_final_state=True, disable_recompute=True, state_v_first=True)
+    gk, w, u, qg, kg, v_new, h = (out[i].double().cpu() for i in (2, 5, 6, 7, 8, 9, 10))
+    assert tuple(h.shape) == (B, T // 64, HV, 128, V) and tuple(w.shape) == (B, HV, T, 128) and tuple(u.shape) == (B, HV, T, V)
+    assert torch.equal(outv[10].transpose(-1, -2), out[10])
+    for c in range(T // 64):
+        sl = slice(c * 64, (c + 1) * 64)
+        S = h[:, c]                                                    # [B,HV,K,V]
+        assert_close(f"v_new chunk {c}", v_new[:, :, sl], u[:, :, sl] - w[:, :, sl] @ S, 5e-2)
+        nxt = h[:, c + 1] if c + 1 < T // 64 else out[1].double().cpu()
+        upd = torch.exp2(gk[:, :, sl][:, :, -1]).unsqueeze(-1) * S + kg[:, :, sl].transpose(-1, -2) @ v_new[:, :, sl]
+        assert_close(f"state after chunk {c}", nxt, upd, 5e-2)
+    q64 = inp["q"].double().repeat_interleave(HV // HK, 2).permute(0, 2, 1, 3)
+    assert_close("qg", qg, q64 * torch.exp2(gk), 5e-3, stored_bf16=True)
