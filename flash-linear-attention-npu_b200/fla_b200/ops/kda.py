@@ -307,7 +307,8 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     B, T, HK, K = qb.shape
     HV = vb.shape[2]
     dev = q.device
-    aqk = torch.zeros((B, HV, T, CHUNK), dtype=q.dtype, device=dev)
+    # fp16 callers: the score blocks leave the export kernel as fp32 and are converted once at the end
+    aqk = torch.zeros((B, HV, T, CHUNK), dtype=torch.float32 if q.dtype == torch.float16 else q.dtype, device=dev)
     akk = torch.zeros_like(aqk)
     gate_kw = {}
     if use_gate_in_kernel:
@@ -337,6 +338,9 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
         gk_out = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens, **{k_: v_ for k_, v_ in gate_kw.items()}).permute(0, 2, 1, 3)   # [B,HV,T,K]
     if state_v_first and ht is not None:
         ht = ht.transpose(-1, -2).contiguous()
+    if q.dtype == torch.float16:
+        from ._convert import convert
+        aqk, akk = convert(aqk, torch.float16, op), convert(akk, torch.float16, op)
     if layout in {"BNSD", "NTD"}:
         o = o.transpose(1, 2).contiguous()
     if rank3:

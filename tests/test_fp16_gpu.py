@@ -137,3 +137,19 @@ def test_decode_rejects_mixed_activation_dtypes():
     q, k, v = (inp[n].unsqueeze(1).cuda() for n in ("q", "k", "v"))
     with pytest.raises(TypeError, match="share one dtype"):
         fused_recurrent_gated_delta_rule(q.half(), k, v, inp["g"].unsqueeze(1).cuda(), inp["beta"].unsqueeze(1).cuda())
+
+
+def test_npu_chunk_kda_fwd_fp16():
+    """The reference's low-level KDA forward takes fp16 q, k, v (_aclnn_ctypes.py:1143-1144): all twelve values come back, the
+    fp16 ones equal to the bf16 call on the rounded tensors up to the two storage roundings."""
+    from fla_b200.ops import npu_chunk_kda_fwd
+    inp = oracle.make_kda_inputs(1, 130, 1, 2, seed=61, dtype=torch.float16, with_grad=False)
+    h, b = ([inp[n].cuda().to(dt) for n in ("q", "k", "v")] for dt in (torch.float16, torch.bfloat16))
+    g, beta = inp["g"].cuda().float(), inp["beta"].cuda().float()
+    o16 = npu_chunk_kda_fwd(*h, g, beta, 128 ** -0.5, 64, output_final_state=True, disable_recompute=True)
+    ob = npu_chunk_kda_fwd(*b, g, beta, 128 ** -0.5, 64, output_final_state=True, disable_recompute=True)
+    assert torch.equal(o16[1], ob[1]) and torch.equal(o16[2], ob[2])            # final state and gk are fp32 in both
+    for i in (0, 3, 4, 5, 6, 7, 8, 9, 10):
+        assert o16[i].dtype == torch.float16 and o16[i].shape == ob[i].shape
+        diff = (o16[i].double() - ob[i].double()).abs()
+        assert (diff <= ob[i].double().abs() * (2.0 ** -8 + 2.0 ** -11) + 2.0 ** -24).all(), i
