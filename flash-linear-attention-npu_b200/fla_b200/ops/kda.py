@@ -136,16 +136,59 @@ def chunk_kda_fwd_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=
     return o, ht, grads
 
 
+class _KdaGateFunction(torch.autograd.Function):
+    """The activated gate as a tensor (`fla_b200_kda_gate_fwd`) with its gradient w.r.t. g, A_log and dt_bias
+    (`fla_b200_kda_gate_bwd`): one pass each way."""
+
+    @staticmethod
+    def forward(ctx, g, A_log, dt_bias, mode, lower_bound):
+        from ._structs import KdaGateArgs
+        HV, K = g.shape[2], g.shape[3]
+        g_ = _as_rows(g.detach())
+        al = A_log.detach().float().reshape(HV).contiguous()
+        db = None if dt_bias is None else dt_bias.detach().float().reshape(HV, K).contiguous()
+        gate = torch.empty(g.shape, dtype=torch.float32, device=g.device)
+        a = KdaGateArgs()
+        a.g, a.a_log, a.dt_bias, a.gate = rt.desc(g_), rt.desc(al), rt.desc(db), rt.desc(gate)
+        a.gate_mode, a.lower_bound = int(mode), float(lower_bound or 0.0)
+        _single_phase("kda_gate_fwd", a, g.device)
+        ctx.save_for_backward(g_, al, db)
+        ctx.mode, ctx.lower_bound = int(mode), float(lower_bound or 0.0)
+        ctx.shapes = (A_log.shape, A_log.dtype, None if dt_bias is None else (dt_bias.shape, dt_bias.dtype), g.dtype)
+        return gate
+
+    @staticmethod
+    def backward(ctx, d_gate):
+        from ._structs import KdaGateArgs
+        g_, al, db = ctx.saved_tensors
+        a_shape, a_dtype, b_meta, g_dtype = ctx.shapes
+        HV, K = g_.shape[2], g_.shape[3]
+        d_gate = _as_rows(d_gate.float())
+        d_g = torch.empty(g_.shape, dtype=g_dtype, device=g_.device)
+        d_al = torch.empty(HV, dtype=torch.float32, device=g_.device)
+        d_db = None if db is None else torch.empty((HV, K), dtype=torch.float32, device=g_.device)
+        a = KdaGateArgs()
+        a.g, a.a_log, a.dt_bias = rt.desc(g_), rt.desc(al), rt.desc(db)
+        a.d_gate, a.d_g, a.d_a_log, a.d_dt_bias = rt.desc(d_gate), rt.desc(d_g), rt.desc(d_al), rt.desc(d_db)
+        a.gate_mode, a.lower_bound = ctx.mode, ctx.lower_bound
+        rt.call("kda_gate_bwd", a, [g_, al, db, d_gate, d_g, d_al, d_db])
+        return (d_g, d_al.reshape(a_shape).to(a_dtype), None if d_db is None else d_db.reshape(b_meta[0]).to(b_meta[1]), None, None)
+
+
+def _single_phase(fn_name, args, dev):
+    rt._check_arch(dev, fn_name)
+    with torch.cuda.device(dev):
+        status = getattr(load_library(), f"fla_b200_{fn_name}")(ctypes.byref(args),
+                                                               ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if status != 0:
+        raise RuntimeError(f"{fn_name} failed with status={status}: {rt._STATUS_NAMES.get(status, '?')}")
+
+
 def _gate_activation(g, A_log, dt_bias, safe_gate, lower_bound):
-    """The in-kernel gate activations in PyTorch (kda/chunk_kda_fwd/docs/api.md:103-115), for the differentiable path."""
-    HV, K = g.shape[2], g.shape[3]
-    raw = g.float()
-    if dt_bias is not None:
-        raw = raw + dt_bias.float().reshape(HV, K)
-    eig = A_log.float().exp().reshape(1, 1, HV, 1)
-    if safe_gate:
-        return float(lower_bound) * torch.sigmoid(eig * raw)
-    return -eig * torch.nn.functional.softplus(raw)
+    """The gate activations of kda/chunk_kda_fwd/docs/api.md:103-115 as a tensor, differentiable w.r.t. g, A_log and dt_bias:
+    the library's gate kernels, for the paths on which the activated gate has to exist (gradients required, or the forward's
+    intermediates kept).  fp32 `[B,T,HV,K]`."""
+    return _KdaGateFunction.apply(g, A_log, dt_bias, 2 if safe_gate else 1, lower_bound)
 
 
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,

@@ -346,6 +346,26 @@ typedef struct fla_kda_intermediates_args {
 } fla_kda_intermediates_args;
 FLA_API int fla_b200_kda_chunk_intermediates(const fla_kda_intermediates_args* args, void* stream);
 
+/* Gate activation of KDA as a tensor, and its gradient: what chunk_kda needs on its differentiable path when
+ * use_gate_in_kernel is set (fla/ops/ascendc/kda/chunk_kda_fwd/docs/api.md:103-115; the inference path activates the gate
+ * inside the forward kernels instead).
+ *   gate_mode 1: gate = -e^{A_log[h]} softplus(g + dt_bias[h, :]);  2: gate = lower_bound sigmoid(e^{A_log[h]} (g + dt_bias[h, :]))
+ *   g       [B, T, HV, K] f32|bf16|f16 (K = 128; batch rows back to back, contiguous channels)
+ *   a_log   [HV] f32        dt_bias [HV, K] f32, optional
+ *   fwd:  gate [B, T, HV, K] f32 dense, out
+ *   bwd:  d_gate [B, T, HV, K] f32 in;  d_g [B, T, HV, K] dense, f32|bf16|f16, out;  d_a_log [HV] f32 and d_dt_bias [HV, K] f32,
+ *         optional out (per-tile sums added in a fixed order: deterministic).  Workspace: the per-tile sums. */
+typedef struct fla_kda_gate_args {
+  fla_tensor_t g, a_log, dt_bias;
+  fla_tensor_t gate;
+  fla_tensor_t d_gate, d_g, d_a_log, d_dt_bias;
+  float lower_bound;
+  int32_t gate_mode;
+} fla_kda_gate_args;
+FLA_API int fla_b200_kda_gate_fwd(const fla_kda_gate_args* args, void* stream);
+FLA_API int fla_b200_kda_gate_bwd_workspace_size(const fla_kda_gate_args* args, uint64_t* bytes);
+FLA_API int fla_b200_kda_gate_bwd(const fla_kda_gate_args* args, void* workspace, uint64_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Chunked Kimi Delta Attention, backward (gate_mode 0: g is the per-channel log decay).
  * The reference has only the intra-chunk piece (aclnnChunkKdaBwdIntra as bound by npu_chunk_kda_bwd_intra,

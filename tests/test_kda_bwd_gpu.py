@@ -269,3 +269,58 @@ def test_kda_two_half_launch_matches_single_launch(recompute):
     assert len(split) == len(whole) >= 5
     for i, (a, b) in enumerate(zip(split, whole)):
         assert torch.equal(a, b), i
+
+
+@pytest.mark.parametrize("safe_gate", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_gate_kernels_match_autograd(safe_gate, dtype):
+    """The gate activation kernels (`fla_b200_kda_gate_fwd` / `_bwd`) against fp64 autograd of the documented formulas
+    (kda/chunk_kda_fwd/docs/api.md:103-115), with and without dt_bias, a token count that is not a multiple of the tile."""
+    from fla_b200.ops.kda import _gate_activation
+    B, T, HV, K = 2, 333, 3, 128
+    gen = torch.Generator().manual_seed(17)
+    g = (2.0 * torch.randn(B, T, HV, K, generator=gen)).to(dtype)
+    A_log = torch.randn(HV, generator=gen) * 0.5
+    d_gate = torch.randn(B, T, HV, K, generator=gen)
+    for bias in (torch.randn(HV * K, generator=gen) * 0.3, None):
+        g64, A64 = g.double().requires_grad_(True), A_log.double().requires_grad_(True)
+        b64 = None if bias is None else bias.double().requires_grad_(True)
+        raw = g64 if b64 is None else g64 + b64.reshape(HV, K)
+        eig = A64.exp().reshape(1, 1, HV, 1)
+        ref = -5.0 * torch.sigmoid(eig * raw) if safe_gate else -eig * F.softplus(raw)
+        ref.backward(d_gate.double())
+        gd, Ad = g.cuda().requires_grad_(True), A_log.cuda().requires_grad_(True)
+        bd = None if bias is None else bias.cuda().requires_grad_(True)
+        got = _gate_activation(gd, Ad, bd, safe_gate, -5.0)
+        got.backward(d_gate.cuda())
+        assert got.dtype == torch.float32 and gd.grad.dtype == dtype and Ad.grad.shape == A_log.shape
+        assert_close("gate", got, ref, 1e-5)
+        assert_close("dg", gd.grad, g64.grad, 1e-5 if dtype == torch.float32 else TOL, stored_bf16=dtype != torch.float32)
+        assert_close("dA_log", Ad.grad, A64.grad, 1e-4)
+        if bias is not None:
+            assert bd.grad.shape == bias.shape
+            assert_close("d_dt_bias", bd.grad, b64.grad, 1e-4)
+
+
+def test_kda_backward_through_the_safe_gate():
+    """chunk_kda with use_gate_in_kernel and safe_gate: output and every gradient against fp64 autograd."""
+    from fla_b200.ops import chunk_kda
+    B, T, HK, HV = 1, 128, 1, 2
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=81)
+    gen = torch.Generator().manual_seed(8)
+    raw = torch.randn(B, T, HV, 128, generator=gen).bfloat16()
+    A_log = torch.randn(HV, generator=gen) * 0.3
+    raw64, A64 = raw.double().requires_grad_(True), A_log.double().requires_grad_(True)
+    gate = -0.5 * torch.sigmoid(torch.exp(A64)[None, None, :, None] * raw64)
+    q64, k64 = inp["q"].double().repeat_interleave(HV // HK, 2), inp["k"].double().repeat_interleave(HV // HK, 2)
+    o_ref, _ = oracle.naive_recurrent_kda(q64, k64, inp["v"].double(), gate, inp["beta"].double(), scale=128 ** -0.5,
+                                          dtype=torch.float64)
+    (o_ref * inp["do"].double()).sum().backward()
+    d = {n: t.cuda() for n, t in inp.items() if t is not None}
+    raw_d, A_d = raw.cuda().requires_grad_(True), A_log.cuda().requires_grad_(True)
+    o, _ = chunk_kda(d["q"], d["k"], d["v"], raw_d, d["beta"], use_gate_in_kernel=True, safe_gate=True, lower_bound=-0.5, A_log=A_d,
+                     output_dtype=torch.float32)
+    (o * d["do"].float()).sum().backward()
+    assert_close("o", o, o_ref, TOL)
+    assert_close("d_raw_gate", raw_d.grad, raw64.grad, TOL, stored_bf16=True)
+    assert_close("dA_log", A_d.grad, A64.grad, TOL)
