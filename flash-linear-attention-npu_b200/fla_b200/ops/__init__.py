@@ -1,7 +1,8 @@
 """Operator surface.  Every function launches hand-written sm_100a kernels through the C ABI; nothing here computes on
-the CPU.  Two small elementwise steps of `chunk_kda` run as PyTorch operations in front of the kernels when gradients are
-required: the gate activation of `use_gate_in_kernel` (without gradients it is a mode of the prep kernel) and the sigmoid
-of `use_beta_sigmoid_in_kernel`; layout glue (views, the re-laying of `[B,T,H]` gates) is PyTorch as well."""
+the CPU.  The gate activation of `chunk_kda(use_gate_in_kernel=True)` is a mode of the prep kernel in inference and the
+library's gate kernels (`fla_b200_kda_gate_fwd` / `_bwd`) when gradients are required; fp16 tensors enter and leave through
+the library's conversion kernel.  What remains PyTorch: the sigmoid of `use_beta_sigmoid_in_kernel` on the `[B,T,HV]`
+logits, and layout glue (views, the re-laying of `[B,T,H]` gates)."""
 from .conv import (causal_conv1d, causal_conv1d_bwd, causal_conv1d_update, npu_causal_conv1d,  # noqa: F401
                    npu_causal_conv1d_bwd)
 from .gdn import (chunk_gated_delta_rule, chunk_gated_delta_rule_bwd, chunk_gated_delta_rule_fwd_bwd,  # noqa: F401
