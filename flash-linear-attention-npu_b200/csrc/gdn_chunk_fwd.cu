@@ -351,8 +351,8 @@ extern "C" FLA_API int fla_b200_gdn_chunk_fwd(const fla_gdn_chunk_fwd_args* a, v
   {
     KernelTimer kt("gdn_fwd", cs);
     const dim3 grid(unsigned(V / 128), unsigned(HV), N);
-    if (p.s_img) gdn_scan_fwd_kernel<true><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v);
-    else gdn_scan_fwd_kernel<false><<<grid, kScanThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v);
+    if (p.s_img) gdn_scan_fwd_kernel<true><<<grid, kFwdThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v);
+    else gdn_scan_fwd_kernel<false><<<grid, kFwdThreads, kScanFwdSmem + 1024, cs>>>(p, tm_q, tm_k, tm_v);
   }
   return cuda_status(cudaGetLastError());
 }

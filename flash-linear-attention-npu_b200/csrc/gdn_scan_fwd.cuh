@@ -42,6 +42,46 @@ constexpr uint32_t sO = 163840;              // 16 KB: the chunk's output rows o
 constexpr uint32_t sI = 180224;              // 8 KB: identity panel
 constexpr uint32_t kScanFwdSmem = 188416;
 
+// Epilogue warps of the forward scan: TMEM lane quadrant = warp % 4, warp / 4 selects which of the kFwdSplit column
+// ranges of a tile the warp owns (64 / kFwdSplit tokens, 128 / kFwdSplit key dims); the helper warp comes after them.
+// Sixteen warps with a quarter of the columns each against eight with a half: 0.577 -> 0.564 ms (training) and
+// 0.498 -> 0.485 ms (inference); the per-chunk chain is mostly hand-off latency, not epilogue issue.
+constexpr int kFwdSplit = 4;
+constexpr int kFwdEpiWarps = 4 * kFwdSplit, kFwdEpiThreads = 32 * kFwdEpiWarps, kFwdThreads = kFwdEpiThreads + 32;
+constexpr int kFwdTT = 64 / kFwdSplit, kFwdKT = 128 / kFwdSplit;     // tokens / key dims per thread
+__device__ __forceinline__ void fwd_epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kFwdEpiThreads) : "memory"); }
+template <int kRowBytes, int kRows>
+__device__ __forceinline__ void fwd_copy_out_tile(const uint8_t* tile, uint8_t* gbase, int64_t g_row_bytes, int rows, int tid) {
+  constexpr int kPerRow = kRowBytes / 16, kIters = kRows * kPerRow / kFwdEpiThreads;
+#pragma unroll
+  for (int i = 0; i < kIters; ++i) {
+    const int id = tid + i * kFwdEpiThreads, r = id / kPerRow, c16 = id % kPerRow;
+    if (r < rows) *reinterpret_cast<uint4*>(gbase + r * g_row_bytes + c16 * 16) = *reinterpret_cast<const uint4*>(tile + r * kRowBytes + c16 * 16);
+  }
+}
+// Each epilogue thread holds one channel (`vrow`) of kFwdTT tokens (cs * kFwdTT ..) of a [64 tokens][128 channels] result.
+// The tile is transposed through a 16 KB shared-memory buffer: bf16 results in one pass, fp32 results in two (32 tokens each).
+__device__ __forceinline__ void fwd_store_rows_transposed(uint8_t* tile, const float* ov, void* g, int64_t g_row_elems, bool f32, int rows,
+                                                          int cs, int vrow, int tid) {
+  if (f32) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if ((cs * kFwdTT) / 32 == h) {
+#pragma unroll
+        for (int i = 0; i < kFwdTT; ++i) *reinterpret_cast<float*>(tile + ((cs * kFwdTT) % 32 + i) * 512 + vrow * 4) = ov[i];
+      }
+      fwd_epi_sync();
+      fwd_copy_out_tile<512, 32>(tile, reinterpret_cast<uint8_t*>(static_cast<float*>(g) + h * 32 * g_row_elems), g_row_elems * 4, rows - h * 32, tid);
+      fwd_epi_sync();
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kFwdTT; ++i) *reinterpret_cast<bf16*>(tile + (cs * kFwdTT + i) * 256 + vrow * 2) = __float2bfloat16_rn(ov[i]);
+    fwd_epi_sync();
+    fwd_copy_out_tile<256, 64>(tile, static_cast<uint8_t*>(g), g_row_elems * 2, rows, tid);
+  }
+}
+
 struct ScanBars {
   uint64_t *mma_bar, *o_bar, *qk_bar, *x_bar, *p_bar, *v_bar;   // two barriers each (index = chunk parity) but the first two
 };
@@ -93,7 +133,7 @@ __device__ __forceinline__ bool scan_fwd_mma3(uint32_t tbase, uint32_t sb, int c
 }
 
 template <bool kSave>
-__global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdParams p, const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(kFwdThreads, 1) gdn_scan_fwd_kernel(GdnFwdParams p, const __grid_constant__ CUtensorMap tm_q,
                                                                         const __grid_constant__ CUtensorMap tm_k,
                                                                         const __grid_constant__ CUtensorMap tm_v) {
   extern __shared__ uint8_t smem_raw[];
@@ -125,7 +165,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     for (int i = 0; i < 3; ++i) mbar_init(&f_bar[i], 1);
     mbar_init_fence();
   }
-  write_identity_panel(smem + sI, tid, kScanThreads);
+  write_identity_panel(smem + sI, tid, kFwdThreads);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -133,7 +173,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   const uint32_t tbase = tmem_base_s;
   bool dead = false;
 
-  if (warp == 8) {
+  if (warp == kFwdEpiWarps) {
     // ============================================================ helper warp: TMA loads and per-token factors
     auto load_qk = [&](int c) {
       const int b = c & 1, row0 = sq.bos + c * kC;
@@ -199,18 +239,18 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   // thread takes they cost some thirty instructions per product to move there.
   const int warp_u = __shfl_sync(0xffffffffu, warp, 0);
   const uint32_t tbase_u = __shfl_sync(0xffffffffu, tbase, 0), sb_u = __shfl_sync(0xffffffffu, sb, 0);
-  const int quad = warp & 3, half = warp >> 2;
+  const int quad = warp & 3, cs = warp >> 2;
   const int vrow = quad * 32 + lane;                       // my value channel inside the block = my TMEM lane
   const uint32_t tlane = tmem_addr(tbase, quad * 32, 0);
-  const int t_lo = half * 32;                              // my 32 tokens of a token-indexed tile
-  const int k_lo = half * 64;                              // my 64 key dims of the state row
+  const int t_lo = cs * kFwdTT;                            // my tokens of a token-indexed tile
+  const int k_lo = cs * kFwdKT;                            // my key dims of the state row
   uint32_t mphase = 0, ophase = 0;
 
   // the initial state goes straight into the accumulator columns: every chunk starts by reading its state from there
   {
     const float* src = p.h0 ? p.h0 + ((int64_t(n) * p.HV + hv) * kK + k_lo) * p.V + vb * 128 + vrow : nullptr;
 #pragma unroll
-    for (int part = 0; part < 4; ++part) {
+    for (int part = 0; part < kFwdKT / 16; ++part) {
       float s16[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) s16[i] = src ? src[int64_t(part * 16 + i) * p.V] : 0.f;
@@ -222,11 +262,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
 
   // Output rows of chunk c: the values are formed before sync 1 of chunk c + 1 (the accumulators they come from are
   // overwritten by that chunk's first product) and leave for global memory while that product runs.
-  float ov[32];
+  float ov[kFwdTT];
   auto form_o = [&](int c) {
     const ScanFactors& f = fac[c % 3];
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
+    for (int g = 0; g < kFwdTT / 16; ++g) {
       float qs[16], pv[16];
       tmem_ld16(tlane + tKQ + t_lo + g * 16, qs);
       tmem_ld16(tlane + tVN + t_lo + g * 16, pv);
@@ -246,7 +286,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     const int rows = min(kC, sq.len - c * kC);
     const int64_t off = (int64_t(sq.bos) + c * kC) * p.o_st + hv * p.o_sh + vb * 128;
     void* g = p.o_is_f32 ? static_cast<void*>(static_cast<float*>(p.o) + off) : static_cast<void*>(static_cast<bf16*>(p.o) + off);
-    store_rows_transposed(smem + sO, ov, g, p.o_st, p.o_is_f32 != 0, rows, half, vrow, tid);
+    fwd_store_rows_transposed(smem + sO, ov, g, p.o_st, p.o_is_f32 != 0, rows, cs, vrow, tid);
   };
 
   for (int c = 0; c < nt; ++c) {
@@ -261,16 +301,16 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
       const float dl = f.dl;
       uint8_t* s_row = kSave ? reinterpret_cast<uint8_t*>(p.s_img + cidx * 32768) + (vrow >> 6) * 32768 + (vrow & 63) * 16 : nullptr;
 #pragma unroll 1
-      for (int g4 = 0; g4 < 4; ++g4) {                   // 16 key dims at a time: 8 packed columns per operand store
+      for (int g4 = 0; g4 < kFwdKT / 16; ++g4) {         // 16 key dims at a time: 8 packed columns per operand store
         float s16[16];
         tmem_ld16(tlane + tST + k_lo + g4 * 16, s16);
         tmem_ld_wait();
         uint32_t hi[8], lo[8];
         split16(s16, hi, lo);
-        tmem_st8u(tlane + tSAh + half * 32 + g4 * 8, hi);
-        tmem_st8u(tlane + tSAl + half * 32 + g4 * 8, lo);
-        if (kSave) {   // strips half * 8 + g4 * 2 and the next one of my channel's row
-          uint8_t* dst = s_row + (half * 8 + g4 * 2) * 1024;
+        tmem_st8u(tlane + tSAh + cs * (kFwdKT / 2) + g4 * 8, hi);
+        tmem_st8u(tlane + tSAl + cs * (kFwdKT / 2) + g4 * 8, lo);
+        if (kSave) {   // strips k_lo / 8 + g4 * 2 and the next one of my channel's row
+          uint8_t* dst = s_row + (cs * (kFwdKT / 8) + g4 * 2) * 1024;
           *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
           *reinterpret_cast<uint4*>(dst + 1024) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
           *reinterpret_cast<uint4*>(dst + 16384) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -300,7 +340,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     // ---- C: Z^T = beta (V^T - e^gam KS^T) for my 32 tokens
     {
 #pragma unroll 1
-      for (int g = 0; g < 2; ++g) {
+      for (int g = 0; g < kFwdTT / 16; ++g) {
         float ks[16], vt[16];
         tmem_ld16(tlane + tKQ + 64 + t_lo + g * 16, ks);
         tmem_ld16(tlane + tVAh + t_lo + g * 16, vt);
@@ -316,8 +356,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
         }
         uint32_t hi[8], lo[8];
         split16(ks, hi, lo);
-        tmem_st8u(tlane + tZAh + half * 16 + g * 8, hi);
-        tmem_st8u(tlane + tZAl + half * 16 + g * 8, lo);
+        tmem_st8u(tlane + tZAh + cs * (kFwdTT / 2) + g * 8, hi);
+        tmem_st8u(tlane + tZAl + cs * (kFwdTT / 2) + g * 8, lo);
         group_fence();
       }
       tmem_st_wait();
@@ -332,7 +372,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
     // ---- E: v_new^T (rows past the end of the sequence are zero) and its decayed copy
     {
 #pragma unroll 1
-      for (int g = 0; g < 2; ++g) {
+      for (int g = 0; g < kFwdTT / 16; ++g) {
         float vn[16];
         tmem_ld16(tlane + tVN + t_lo + g * 16, vn);
         tmem_ld_wait();
@@ -340,10 +380,10 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
         for (int i = 0; i < 16; ++i) vn[i] = (t_lo + g * 16 + i < rows) ? vn[i] : 0.f;
         uint32_t hi[8], lo[8];
         split16(vn, hi, lo);
-        tmem_st8u(tlane + tZAh + half * 16 + g * 8, hi);
-        tmem_st8u(tlane + tZAl + half * 16 + g * 8, lo);
-        if (kSave) {                                 // v_new image: strips half * 4 + g * 2 and the next one
-          uint8_t* dst = reinterpret_cast<uint8_t*>(p.vn_img + cidx * 16384) + (vrow >> 6) * 16384 + (half * 4 + g * 2) * 1024 + (vrow & 63) * 16;
+        tmem_st8u(tlane + tZAh + cs * (kFwdTT / 2) + g * 8, hi);
+        tmem_st8u(tlane + tZAl + cs * (kFwdTT / 2) + g * 8, lo);
+        if (kSave) {                                 // v_new image: strips t_lo / 8 + g * 2 and the next one
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.vn_img + cidx * 16384) + (vrow >> 6) * 16384 + (cs * (kFwdTT / 8) + g * 2) * 1024 + (vrow & 63) * 16;
           *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
           *reinterpret_cast<uint4*>(dst + 1024) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
           *reinterpret_cast<uint4*>(dst + 8192) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -355,8 +395,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
           vn[i4] *= d4.x; vn[i4 + 1] *= d4.y; vn[i4 + 2] *= d4.z; vn[i4 + 3] *= d4.w;
         }
         split16(vn, hi, lo);
-        tmem_st8u(tlane + tVAh + half * 16 + g * 8, hi);
-        tmem_st8u(tlane + tVAl + half * 16 + g * 8, lo);
+        tmem_st8u(tlane + tVAh + cs * (kFwdTT / 2) + g * 8, hi);
+        tmem_st8u(tlane + tVAl + cs * (kFwdTT / 2) + g * 8, lo);
         group_fence();
       }
       tmem_st_wait();
@@ -378,7 +418,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_scan_fwd_kernel(GdnFwdPar
   if (!dead && p.ht) {
     float* dst = p.ht + ((int64_t(n) * p.HV + hv) * kK + k_lo) * p.V + vb * 128 + vrow;
 #pragma unroll
-    for (int part = 0; part < 4; ++part) {
+    for (int part = 0; part < kFwdKT / 16; ++part) {
       float s16[16];
       tmem_ld16(tlane + tST + k_lo + part * 16, s16);
       tmem_ld_wait();

@@ -4,11 +4,11 @@
 // bf16 pairs and consumed by tcgen05.mma straight from tensor memory; only the inputs (which arrive by TMA in the panel
 // layout the descriptors want) are read from shared memory.
 //
-// Thread roles: warps 0-7 are epilogue warps (TMEM lane quadrant = warp % 4, warp / 4 selects the half of a tile's
-// columns they own); thread 0 issues every product right after the CTA barrier that publishes its operands (measured:
-// 0.64 ms against 0.75 ms with the products issued by a separate warp, which has to win an issue slot first); warp 8 is
-// a helper that issues the TMA loads a chunk ahead and turns the raw gate / beta values of a chunk into per-token factors
-// two chunks ahead, so that neither latency is ever waited for.  Epilogues walk their tokens in groups of 16 with a
+// Thread roles: the first warps are epilogue warps (TMEM lane quadrant = warp % 4, warp / 4 selects the part of a tile's
+// columns they own: eight warps with a half each in the reverse scan, sixteen with a quarter each in the forward scan); thread 0 issues every product right after the CTA barrier that publishes its operands (measured:
+// 0.64 ms against 0.75 ms with the products issued by a separate warp, which has to win an issue slot first); the last warp is
+// a helper that issues the TMA loads a chunk ahead and the bulk copy of the chunk's per-token factor record two chunks
+// ahead, so that neither latency is ever waited for.  Epilogues walk their tokens in groups of 16 with a
 // compiler fence between groups: without it the loads of all groups are hoisted and the 168 registers a thread gets at
 // 288 threads per CTA spill.
 #pragma once
@@ -87,9 +87,9 @@ __device__ __forceinline__ void lazy_wait_or_mark(uint64_t* bar, uint32_t& phase
   }
   phase ^= 1;
 }
-// the 8 epilogue warps + the helper warp
+// every warp of the CTA (epilogue warps + the helper warp)
 __device__ __forceinline__ void scan_sync() { __syncthreads(); }
-// the 8 epilogue warps only
+// the 8 epilogue warps of the reverse scan only
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // 64 x 64 identity panel: the B operand that copies a 64-token tile of rows into tensor memory TRANSPOSED
