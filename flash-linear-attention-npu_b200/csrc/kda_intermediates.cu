@@ -243,3 +243,214 @@ extern "C" FLA_API int fla_b200_kda_chunk_intermediates(const fla_kda_intermedia
   kda_intermediates_kernel<<<dim3(nt_max, unsigned(HV), N), 256, kInterSmem, cs>>>(p);
   return cuda_status(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Score blocks of 128-token chunks from those of the 64-token chunks the kernels work in (npu_chunk_kda_fwd takes
+// chunk_size 64 or 128, _aclnn_ctypes.py:1094-1096).  With A the first and B the second half of a 128-token chunk,
+// gk the 64-token cumulative gate and L = gk at the last token of A (per channel):
+//     gk128 = gk on A, gk + L on B
+//     Aqk128 = [[Aqk_A, 0], [scale qg_B kg_A^T, Aqk_B]]          qg = q e^{gk},  kg = k e^{L - gk}  (all exponents <= 0)
+//     Akk128 = [[X_A, 0], [-X_B M X_A, X_B]],  M = beta_B (k e^{gk})_B kg_A^T   (the inverse of a block-triangular matrix)
+// One CTA per (128-token chunk, head), fp32 on CUDA cores: an export path like the kernel above.
+namespace fla {
+namespace {
+
+struct KdaMergeParams {
+  InView q, k;
+  const void* beta; int beta_is_f32; int64_t beta_sb, beta_st, beta_sh;
+  const float* gk;                 // [tokens, HV, K] cumulative gate of the 64-token chunks, dense
+  float gk_unit;                   // 1 for a natural-log gate, ln 2 for a base-2 gate
+  const float* aqk64; const float* akk64; int64_t a_sb, a_st, a_sh;   // [B, T, HV, 64] views, fp32
+  OutView aqk, akk;                // [B, T, HV, 128] views
+  float* gk_out; int64_t g_sb, g_st, g_sh;   // [B, T, HV, K] view, fp32, base 2
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int T, HK, HV;
+  float scale;
+};
+
+constexpr int kMergeSmem = (3 * kC * kK + 4 * kC * kC) * 4;   // kgA, qgB, kqB rows; M, T, X_A, X_B tiles
+
+__global__ void __launch_bounds__(256) kda_merge_blocks_kernel(KdaMergeParams p) {
+  extern __shared__ float merge_smem[];
+  float* kga = merge_smem;                 // [64][128]
+  float* qgb = kga + kC * kK;
+  float* kqb = qgb + kC * kK;
+  float* m_kk = kqb + kC * kK;             // [64][64]  beta_i (k e^gk)_i . kg_j
+  float* tmp = m_kk + kC * kC;             // [64][64]  M X_A
+  float* xa = tmp + kC * kC;               // [64][64]
+  float* xb = xa + kC * kC;
+  __shared__ float beta_s[kC];
+  const int tid = threadIdx.x;
+  const int n = blockIdx.z, hv = blockIdx.y, c2 = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (2 * c2 >= sq.nt) return;
+  const int hk = hv / (p.HV / p.HK);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + int64_t(c2) * 128;   // first token of the 128-token chunk in batch row b
+  const int64_t flat0 = b * p.T + t0;
+  const int len = min(128, sq.len - c2 * 128);
+  const int ra = min(kC, len), rb = len - ra;                            // tokens in the two halves
+  const int col = tid & 127, par = tid >> 7;
+
+  // gk128, and the operands of the two products
+  const float* gkc = p.gk + (flat0 * p.HV + hv) * kK + col;
+  const float L = gkc[int64_t(ra - 1) * p.HV * kK] * p.gk_unit;
+  for (int s = 0; s < 64; ++s) {
+    const int t = par + 2 * s;            // 0..127
+    if (t >= len) break;
+    const float g = gkc[int64_t(t) * p.HV * kK] * p.gk_unit;
+    const float g128 = t < kC ? g : g + L;
+    if (p.gk_out) p.gk_out[b * p.g_sb + (t0 + t) * p.g_st + hv * p.g_sh + col] = g128 * 1.4426950408889634f;
+    const float kv = __bfloat162float(p.k.p[b * p.k.sb + (t0 + t) * p.k.st + hk * p.k.sh + col]);
+    if (t < kC) {
+      kga[t * kK + col] = kv * expf(L - g);
+    } else {
+      const float e = expf(g);
+      qgb[(t - kC) * kK + col] = __bfloat162float(p.q.p[b * p.q.sb + (t0 + t) * p.q.st + hk * p.q.sh + col]) * e;
+      kqb[(t - kC) * kK + col] = kv * e;
+    }
+  }
+  if (tid < kC) beta_s[tid] = tid < rb ? ld_scalar(p.beta, b * p.beta_sb + (t0 + kC + tid) * p.beta_st + hv * p.beta_sh, p.beta_is_f32) : 0.f;
+  // the 64-token blocks (zero outside the valid rows / columns)
+  for (int idx = tid; idx < kC * kC; idx += 256) {
+    const int i = idx >> 6, j = idx & 63;
+    xa[idx] = (i < ra && j < ra) ? p.akk64[b * p.a_sb + (t0 + i) * p.a_st + hv * p.a_sh + j] : 0.f;
+    xb[idx] = (i < rb && j < rb) ? p.akk64[b * p.a_sb + (t0 + kC + i) * p.a_st + hv * p.a_sh + j] : 0.f;
+  }
+  __syncthreads();
+
+  // rows of the first half: [block | 0]
+  for (int idx = tid; idx < kC * 128; idx += 256) {
+    const int i = idx >> 7, j = idx & 127;
+    if (i >= ra) continue;
+    const int64_t o = b * p.aqk.sb + (t0 + i) * p.aqk.st + hv * p.aqk.sh + j;
+    const int64_t o2 = b * p.akk.sb + (t0 + i) * p.akk.st + hv * p.akk.sh + j;
+    put(p.aqk.p, p.aqk.dtype, o, (j < ra) ? p.aqk64[b * p.a_sb + (t0 + i) * p.a_st + hv * p.a_sh + j] : 0.f);
+    put(p.akk.p, p.akk.dtype, o2, (j < ra) ? xa[i * kC + j] : 0.f);
+  }
+  if (rb <= 0) return;
+
+  // off-diagonal blocks: thread (j = tid & 63, rows i = (tid >> 6) * 16 .. + 16)
+  {
+    const int j = tid & 63, i0 = (tid >> 6) * 16;
+    float aq[16], ak[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) aq[r] = ak[r] = 0.f;
+    for (int k = 0; k < kK; ++k) {
+      const float kg = kga[j * kK + ((k + j) & 127)];     // rotated channel order: the 32 lanes read 32 different banks
+      const int kk = (k + j) & 127;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        aq[r] += qgb[(i0 + r) * kK + kk] * kg;
+        ak[r] += kqb[(i0 + r) * kK + kk] * kg;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const int i = i0 + r;
+      const bool live = i < rb && j < ra;
+      m_kk[i * kC + j] = live ? beta_s[i] * ak[r] : 0.f;
+      if (i < rb) put(p.aqk.p, p.aqk.dtype, b * p.aqk.sb + (t0 + kC + i) * p.aqk.st + hv * p.aqk.sh + j, live ? p.scale * aq[r] : 0.f);
+    }
+  }
+  __syncthreads();
+  // tmp = M X_A, then X_21 = -X_B tmp
+  {
+    const int j = tid & 63, i0 = (tid >> 6) * 16;
+    float acc[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) acc[r] = 0.f;
+    for (int k = 0; k < kC; ++k) {
+      const float x = xa[k * kC + j];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) acc[r] += m_kk[(i0 + r) * kC + k] * x;
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) tmp[(i0 + r) * kC + j] = acc[r];
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 16; ++r) acc[r] = 0.f;
+    for (int k = 0; k < kC; ++k) {
+      const float x = tmp[k * kC + j];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) acc[r] += xb[(i0 + r) * kC + k] * x;
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const int i = i0 + r;
+      if (i < rb) put(p.akk.p, p.akk.dtype, b * p.akk.sb + (t0 + kC + i) * p.akk.st + hv * p.akk.sh + j, j < ra ? -acc[r] : 0.f);
+    }
+  }
+  // rows of the second half, columns 64..127: the block of the second 64-token chunk
+  for (int idx = tid; idx < kC * kC; idx += 256) {
+    const int i = idx >> 6, j = idx & 63;
+    if (i >= rb) continue;
+    put(p.aqk.p, p.aqk.dtype, b * p.aqk.sb + (t0 + kC + i) * p.aqk.st + hv * p.aqk.sh + kC + j,
+        (j < rb) ? p.aqk64[b * p.a_sb + (t0 + kC + i) * p.a_st + hv * p.a_sh + j] : 0.f);
+    put(p.akk.p, p.akk.dtype, b * p.akk.sb + (t0 + kC + i) * p.akk.st + hv * p.akk.sh + kC + j, (j < rb) ? xb[i * kC + j] : 0.f);
+  }
+}
+
+}  // namespace
+}  // namespace fla
+
+extern "C" FLA_API int fla_b200_kda_merge_score_blocks(const fla_kda_merge_blocks_args* a, void* stream) {
+  using namespace fla;
+  if (!a) return FLA_ERR_NULL;
+  if (!a->q.data || !a->k.data || !a->beta.data || !a->gk.data || !a->aqk64.data || !a->akk64.data || !a->aqk.data || !a->akk.data)
+    return FLA_ERR_NULL;
+  if (a->q.ndim != 4 || a->gk.ndim != 4) return FLA_ERR_SHAPE;
+  const int64_t B = a->q.shape[0], T = a->q.shape[1], HK = a->q.shape[2], HV = a->gk.shape[2];
+  if (a->q.shape[3] != kK || HK <= 0 || HV % HK) return FLA_ERR_SHAPE;
+  KdaMergeParams p{};
+  if (!in_view(a->q, B, T, HK, kK, &p.q) || !in_view(a->k, B, T, HK, kK, &p.k)) return FLA_ERR_SHAPE;
+  const fla_tensor_t& be = a->beta;
+  if (be.ndim != 3 || be.shape[0] != B || be.shape[1] != T || be.shape[2] != HV) return FLA_ERR_SHAPE;
+  if (be.dtype != FLA_F32 && be.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  p.beta = be.data; p.beta_is_f32 = be.dtype == FLA_F32; p.beta_sb = be.stride[0]; p.beta_st = be.stride[1]; p.beta_sh = be.stride[2];
+  const fla_tensor_t& gk = a->gk;
+  if (gk.dtype != FLA_F32 || gk.shape[0] != B || gk.shape[1] != T || gk.shape[3] != kK || gk.stride[3] != 1 || gk.stride[2] != kK ||
+      gk.stride[1] != HV * kK || (B > 1 && gk.stride[0] != T * HV * kK))
+    return FLA_ERR_SHAPE;
+  p.gk = static_cast<const float*>(gk.data);
+  p.gk_unit = a->gk_base2 ? 0.6931471805599453f : 1.f;
+  for (const fla_tensor_t* t : {&a->aqk64, &a->akk64}) {
+    if (t->dtype != FLA_F32 || t->ndim != 4 || t->shape[0] != B || t->shape[1] != T || t->shape[2] != HV || t->shape[3] != kC || t->stride[3] != 1)
+      return FLA_ERR_SHAPE;
+  }
+  if (a->aqk64.stride[0] != a->akk64.stride[0] || a->aqk64.stride[1] != a->akk64.stride[1] || a->aqk64.stride[2] != a->akk64.stride[2])
+    return FLA_ERR_LAYOUT;
+  p.aqk64 = static_cast<const float*>(a->aqk64.data); p.akk64 = static_cast<const float*>(a->akk64.data);
+  p.a_sb = a->aqk64.stride[0]; p.a_st = a->aqk64.stride[1]; p.a_sh = a->aqk64.stride[2];
+  int st;
+  if ((st = out_view(a->aqk, B, T, HV, 128, &p.aqk)) || (st = out_view(a->akk, B, T, HV, 128, &p.akk))) return st;
+  if (a->gk_out.data) {
+    const fla_tensor_t& g = a->gk_out;
+    if (g.dtype != FLA_F32 || g.ndim != 4 || g.shape[0] != B || g.shape[1] != T || g.shape[2] != HV || g.shape[3] != kK || g.stride[3] != 1)
+      return FLA_ERR_SHAPE;
+    p.gk_out = static_cast<float*>(g.data); p.g_sb = g.stride[0]; p.g_st = g.stride[1]; p.g_sh = g.stride[2];
+  }
+  int N = int(B), max_len = int(T);
+  if (a->cu_seqlens.data) {
+    if (B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    N = int(a->cu_seqlens.shape[0] - 1);
+    if (!a->chunk_offsets.data || a->chunk_offsets.dtype != FLA_I32 || a->chunk_offsets.shape[0] != N + 1) return FLA_ERR_SHAPE;
+    if (a->max_seqlen <= 0 || a->max_seqlen > T) return FLA_ERR_VALUE;
+    max_len = a->max_seqlen;
+  }
+  p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+  p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
+  p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.scale = a->scale;
+  static std::atomic<bool> attr_done_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (!attr_done_dev[dev]) {
+    if (cudaFuncSetAttribute(kda_merge_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeSmem) != cudaSuccess) return FLA_ERR_CUDA;
+    attr_done_dev[dev] = true;
+  }
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const int nt128 = (max_len + 127) / 128;
+  KernelTimer kt("kda_merge_score_blocks", cs);
+  kda_merge_blocks_kernel<<<dim3(nt128, unsigned(HV), N), 256, kMergeSmem, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}

@@ -64,6 +64,11 @@ class KdaIntermediatesArgs(ctypes.Structure):
         ("max_seqlen", ctypes.c_int32), ("total_chunks", ctypes.c_int32), ("state_v_first", ctypes.c_int32)]
 
 
+class KdaMergeBlocksArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("q", "k", "beta", "gk", "aqk64", "akk64", "cu_seqlens", "chunk_offsets", "aqk", "akk",
+                                           "gk_out")] + [("scale", ctypes.c_float), ("max_seqlen", ctypes.c_int32), ("gk_base2", ctypes.c_int32)]
+
+
 class KdaGateArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("g", "a_log", "dt_bias", "gate", "d_gate", "d_g", "d_a_log", "d_dt_bias")] + [
         ("lower_bound", ctypes.c_float), ("gate_mode", ctypes.c_int32)]

@@ -315,6 +315,34 @@ def kda_chunk_intermediates(q, k, v, beta, saved, meta, *, full, state_v_first=F
     return outs, h
 
 
+def _merge_score_blocks(q, k, beta, gk64, aqk64, akk64, scale, cu_seqlens, dtype, want_gk):
+    """Aqk, Akk `[B,HV,T,128]` and gk `[B,HV,T,K]` of 128-token chunks from the 64-token blocks (`fla_b200_kda_merge_score_blocks`).
+    q, k `[B,T,HK,K]`, beta `[B,T,HV]`, gk64 `[B,T,HV,K]` fp32 base 2, aqk64 / akk64 `[B,HV,T,64]` fp32."""
+    from ._structs import KdaMergeBlocksArgs
+    B, T, HK, K = q.shape
+    HV = beta.shape[2]
+    dev = q.device
+    q, k, beta = _as_rows(q), _as_rows(k), _as_rows(beta)
+    if beta.dtype not in (torch.float32, torch.bfloat16):
+        beta = beta.float()
+    cu = co = None
+    max_len = T
+    if cu_seqlens is not None:
+        cu, co, max_len, _, _, _ = _varlen_meta(cu_seqlens, dev)
+    aqk = torch.zeros((B, HV, T, 128), dtype=dtype, device=dev)
+    akk = torch.zeros_like(aqk)
+    gk = torch.empty((B, HV, T, K), dtype=torch.float32, device=dev) if want_gk else None
+    a = KdaMergeBlocksArgs()
+    a.q, a.k, a.beta, a.gk = rt.desc(q), rt.desc(k), rt.desc(beta), rt.desc(gk64.contiguous())
+    a.aqk64, a.akk64 = rt.desc(aqk64.transpose(1, 2)), rt.desc(akk64.transpose(1, 2))
+    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    a.aqk, a.akk = rt.desc(aqk.transpose(1, 2)), rt.desc(akk.transpose(1, 2))
+    a.gk_out = rt.desc(None if gk is None else gk.transpose(1, 2))
+    a.scale, a.max_seqlen, a.gk_base2 = float(scale), int(max_len), 1
+    _single_phase("kda_merge_score_blocks", a, dev)
+    return aqk, akk, gk
+
+
 def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", initial_state=None, output_final_state=False,
                       cu_seqlens=None, chunk_indices=None, safe_gate=False, lower_bound=None, use_gate_in_kernel=False,
                       A_log=None, dt_bias=None, disable_recompute=False, return_intermediate_states=False, state_v_first=False):
@@ -324,7 +352,9 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     is activated in the kernel, Aqk and Akk `[B,HV,T,64]` always.  The head-major intermediates never exist in the fused
     kernels; `disable_recompute=True` (w, u, qg, kg, v_new, h and gk) and `return_intermediate_states=True` (h) run a
     second, chunk-parallel pass over the forward's saved operand images that forms them (`kda_chunk_intermediates`), with
-    the gate activated in front of the kernels when `use_gate_in_kernel` is set.  `state_v_first=True` takes and returns the recurrent state as `[N,HV,V,K]`.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
+    the gate activated in front of the kernels when `use_gate_in_kernel` is set.  `chunk_size=128`: o and the states do not
+    depend on the blocking; gk, Aqk, Akk `[B,HV,T,128]` are merged from the 64-token blocks (`fla_b200_kda_merge_score_blocks`)
+    and h keeps every second state; w, u, qg, kg, v_new exist for chunk_size 64 only.  `state_v_first=True` takes and returns the recurrent state as `[N,HV,V,K]`.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
     comes back in the input's layout."""
     del chunk_indices
     op = "npu_chunk_kda_fwd"
@@ -333,10 +363,12 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
         raise RuntimeError(f"{op}: layout must be uppercase and one of BSND, BNSD, TND, NTD.")
     if int(chunk_size) not in {64, 128}:
         raise RuntimeError(f"{op}: chunk_size must be 64 or 128.")
-    if int(chunk_size) != CHUNK:
-        raise NotImplementedError(f"{op}: this build supports chunk_size = 64")
+    big = int(chunk_size) == 128     # the kernels tile by 64 tokens: o and the states do not depend on the blocking, the score
+    #                                  blocks and gk of 128-token chunks are merged from those of their two halves afterwards
     want_full = bool(disable_recompute)
     want_h = want_full or bool(return_intermediate_states)
+    if big and want_full:
+        raise NotImplementedError(f"{op}: w, u, qg, kg, v_new are formed for chunk_size = 64 only")
     rank3 = layout in {"TND", "NTD"}
 
     def to_bsnd(t):
@@ -351,7 +383,7 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     HV = vb.shape[2]
     dev = q.device
     # fp16 callers: the score blocks leave the export kernel as fp32 and are converted once at the end
-    aqk = torch.zeros((B, HV, T, CHUNK), dtype=torch.float32 if q.dtype == torch.float16 else q.dtype, device=dev)
+    aqk = torch.zeros((B, HV, T, CHUNK), dtype=torch.float32 if (big or q.dtype == torch.float16) else q.dtype, device=dev)
     akk = torch.zeros_like(aqk)
     gate_kw = {}
     if use_gate_in_kernel:
@@ -371,17 +403,30 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
                                                     export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), _return_saved=True,
                                                     **gate_kw)
             inter, h = kda_chunk_intermediates(*rows_in, saved, meta, full=want_full, state_v_first=state_v_first, dtype=q.dtype)
+            if big:   # the states at the starts of the 128-token chunks: every second 64-token chunk of each sequence
+                bounds = [0, T] if cu_seqlens is None else [int(x) for x in cu_seqlens]
+                first, idx = 0, []
+                for _ in range(B if cu_seqlens is None else 1):
+                    for bos, eos in zip(bounds[:-1], bounds[1:]):
+                        n64 = (eos - bos + CHUNK - 1) // CHUNK
+                        idx += list(range(first, first + n64, 2))
+                        first += n64
+                h = h.index_select(0, torch.tensor(idx, dtype=torch.int64, device=dev))
             h = h if rank3 else h.view(B, -1, *h.shape[1:])
         else:
             o, ht = chunk_kda(qb, kb, vb, gb, bb, scale=scale, initial_state=h0, output_final_state=output_final_state,
                               cu_seqlens=cu_seqlens, export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), **gate_kw)
     gk_out = None
-    if not use_gate_in_kernel or want_full:
+    if not use_gate_in_kernel or want_full or big:
         from .stages import kda_gate_cumsum
-        gk_out = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens, **{k_: v_ for k_, v_ in gate_kw.items()}).permute(0, 2, 1, 3)   # [B,HV,T,K]
+        gk64 = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens, **{k_: v_ for k_, v_ in gate_kw.items()})          # [B,T,HV,K], base 2
+        gk_out = gk64.permute(0, 2, 1, 3)                                                                             # [B,HV,T,K]
+    if big:
+        aqk, akk, gk_out = _merge_score_blocks(qb, kb, bb, gk64, aqk, akk, scale, cu_seqlens, q.dtype,
+                                               want_gk=not use_gate_in_kernel or want_full)
     if state_v_first and ht is not None:
         ht = ht.transpose(-1, -2).contiguous()
-    if q.dtype == torch.float16:
+    if q.dtype == torch.float16 and not big:
         from ._convert import convert
         aqk, akk = convert(aqk, torch.float16, op), convert(akk, torch.float16, op)
     if layout in {"BNSD", "NTD"}:

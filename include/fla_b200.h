@@ -346,6 +346,24 @@ typedef struct fla_kda_intermediates_args {
 } fla_kda_intermediates_args;
 FLA_API int fla_b200_kda_chunk_intermediates(const fla_kda_intermediates_args* args, void* stream);
 
+/* Score blocks of 128-token chunks (npu_chunk_kda_fwd takes chunk_size 64 or 128, _aclnn_ctypes.py:1094-1096) merged from
+ * those of the 64-token chunks the kernels work in.  With A / B the halves of a 128-token chunk and L = gk at the end of A:
+ *     gk128 = gk on A, gk + L on B;   Aqk128 = [[Aqk_A, 0], [scale (q e^{gk})_B (k e^{L-gk})_A^T, Aqk_B]];
+ *     Akk128 = [[X_A, 0], [-X_B M X_A, X_B]],  M = beta_B (k e^{gk})_B (k e^{L-gk})_A^T
+ *   q, k [B,T,HK,K] bf16, beta [B,T,HV] f32|bf16, gk [B,T,HV,K] f32 dense (cumulative gate of the 64-token chunks: natural log, the
+ *   `gk` output of fla_b200_kda_chunk_fwd, or base 2 with gk_base2), aqk64 / akk64 [B,T,HV,64] f32 views (the forward's exports)
+ *   aqk, akk [B,T,HV,128] out, bf16|f16|f32 views;  gk_out [B,T,HV,K] f32 view, optional out (base 2).
+ * A chunk-parallel fp32 pass on CUDA cores, outside the hot path.  Single-phase (no workspace). */
+typedef struct fla_kda_merge_blocks_args {
+  fla_tensor_t q, k, beta, gk, aqk64, akk64;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  fla_tensor_t aqk, akk, gk_out;
+  float scale;
+  int32_t max_seqlen;
+  int32_t gk_base2;   /* gk is given in base 2 (the output of fla_b200_chunk_local_cumsum with scale 1/ln 2) instead of natural log */
+} fla_kda_merge_blocks_args;
+FLA_API int fla_b200_kda_merge_score_blocks(const fla_kda_merge_blocks_args* args, void* stream);
+
 /* Gate activation of KDA as a tensor, and its gradient: what chunk_kda needs on its differentiable path when
  * use_gate_in_kernel is set (fla/ops/ascendc/kda/chunk_kda_fwd/docs/api.md:103-115; the inference path activates the gate
  * inside the forward kernels instead).

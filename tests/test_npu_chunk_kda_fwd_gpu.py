@@ -168,3 +168,48 @@ def test_intermediates_fixed_length_layouts_and_v_first(layout):
         assert_close(f"state after chunk {c}", nxt, upd, 5e-2)
     q64 = inp["q"].double().repeat_interleave(HV // HK, 2).permute(0, 2, 1, 3)
     assert_close("qg", qg, q64 * torch.exp2(gk), 5e-3, stored_bf16=True)
+
+
+@pytest.mark.parametrize("layout,cu", [("BSND", None), ("TND", [0, 70, 71, 200, 392]), ("BNSD", None)])
+def test_chunk_size_128(layout, cu):
+    """chunk_size = 128 (two of the reference's four published KDA cases, KDA_FORWARD_VALIDATION_REPORT.md:83-84): gk, Aqk and Akk
+    of 128-token chunks against the oracle's restatement of the reference golden run with that chunk size (ragged chunks with
+    fewer than 65 and with 65..127 tokens included); o and the final state do not depend on the blocking; h holds the state at
+    the start of every 128-token chunk."""
+    from fla_b200.ops import npu_chunk_kda_fwd
+    B, T, HK, HV = (1, 392, 1, 2) if cu else (2, 330, 2, 4)
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=47, with_grad=False)
+    scale = 128 ** -0.5
+    aqk_r, akk_r, gk_r = oracle.kda_chunk_score_blocks_ref(inp["q"], inp["k"], inp["g"], inp["beta"], scale, cu, 128)
+
+    def lay(t):
+        t = t.cuda()
+        if layout == "BNSD":
+            return t.transpose(1, 2).contiguous()
+        return t.squeeze(0).contiguous() if layout == "TND" else t
+
+    args = [lay(inp[n]) for n in ("q", "k", "v", "g", "beta")]
+    ref64 = npu_chunk_kda_fwd(*args, scale, 64, layout=layout, output_final_state=True, cu_seqlens=cu, return_intermediate_states=True)
+    out = npu_chunk_kda_fwd(*args, scale, 128, layout=layout, output_final_state=True, cu_seqlens=cu, return_intermediate_states=True)
+    assert torch.equal(out[0], ref64[0]) and torch.equal(out[1], ref64[1])
+    gk, aqk, akk, h = out[2], out[3], out[4], out[10]
+    if layout == "TND":
+        gk, aqk, akk = gk.unsqueeze(0), aqk.unsqueeze(0), akk.unsqueeze(0)
+    assert tuple(aqk.shape) == (B, HV, T, 128) and aqk.dtype == torch.bfloat16
+    assert_close("gk", gk, gk_r, 1e-5)
+    assert_close("Aqk", aqk, aqk_r, 5e-3, stored_bf16=True)
+    assert_close("Akk", akk, akk_r, 5e-3, stored_bf16=True)
+    # h: every second 64-token state of each sequence
+    h64 = ref64[10]
+    if cu is None:
+        n64 = (T + 63) // 64
+        assert torch.equal(h, h64[:, 0:n64:2])
+    else:
+        starts, first = [], 0
+        for bos, eos in zip(cu[:-1], cu[1:]):
+            n64 = (eos - bos + 63) // 64
+            starts += list(range(first, first + n64, 2))
+            first += n64
+        assert torch.equal(h, h64[starts])
+    with pytest.raises(NotImplementedError):
+        npu_chunk_kda_fwd(*args, scale, 128, layout=layout, cu_seqlens=cu, disable_recompute=True)
