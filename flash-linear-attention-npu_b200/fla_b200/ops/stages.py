@@ -182,7 +182,11 @@ def chunk_gated_delta_rule_fwd_h(k, w, u, g=None, *, gk=None, initial_state=None
 def chunk_fwd_o(q, k, v, h, scale, *, g=None, g_gamma=None, cu_seqlens=None, chunk_indices=None, chunk_size=None,
                 transpose_state_layout=False):
     """`o = scale (e^{g_i} q h_c + tril(q k^T e^{g_i - g_j}) v)` per chunk; v is the `v_new` of the state pass."""
-    del g_gamma, transpose_state_layout, chunk_indices
+    del chunk_indices
+    if g_gamma is not None:   # reserved in the reference too (chunk_gdn_fwd/chunk_fwd_o/README.md:177: not used, pass None)
+        raise RuntimeError("chunk_fwd_o: g_gamma is a reserved input and must be None")
+    if transpose_state_layout:
+        raise NotImplementedError("chunk_fwd_o: transpose_state_layout is not supported")
     if g is None:
         raise NotImplementedError("chunk_fwd_o: g is required")
     chunk_size = CHUNK if chunk_size is None else int(chunk_size)
@@ -194,7 +198,9 @@ def chunk_fwd_o(q, k, v, h, scale, *, g=None, g_gamma=None, cu_seqlens=None, chu
 def chunk_bwd_dv_local(q, k, d_o, g, scale, chunk_size, *, g_gamma=None, A=None, cu_seqlens=None, chunk_indices=None):
     """Intra-chunk part of dv: `dv_j = sum_{i >= j} scale (k_j.q_i) e^{g_i - g_j} d_o_i`.  q, k `[B,HK,T,K]`, d_o `[B,HV,T,V]`,
     g `[B,HV,T]` (chunk-local cumulative gate)."""
-    del g_gamma, A, chunk_indices
+    del chunk_indices
+    if g_gamma is not None or A is not None:   # reserved in the reference too (chunk_gdn_bwd/chunk_bwd_dv_local/README.md:84-85)
+        raise RuntimeError("chunk_bwd_dv_local: g_gamma and A are reserved inputs and must be None")
     dv = torch.empty_like(d_o)
     _stage_call("chunk_bwd_dv_local", dict(q=q, k=k, v=d_o, g=g, out0=dv), [q, k, d_o, g, dv], d_o, cu_seqlens, chunk_size, scale=scale)
     return dv
