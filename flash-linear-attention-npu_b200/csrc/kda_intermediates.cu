@@ -454,3 +454,200 @@ extern "C" FLA_API int fla_b200_kda_merge_score_blocks(const fla_kda_merge_block
   kda_merge_blocks_kernel<<<dim3(nt128, unsigned(HV), N), 256, kMergeSmem, cs>>>(p);
   return cuda_status(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// w, u, qg, kg of 128-token chunks from those of their 64-token halves A, B (same notation as above, XM = X_B M):
+//     qg128 = qg on A, qg e^L on B                 kg128 = kg e^{gk_B,last} on A, kg on B
+//     w128  = w on A,  w e^L - XM w_A on B          u128  = u on A,  u - XM u_A on B
+// (row block B of Akk128 is [-X_B M X_A, X_B], and X_A applied to the right-hand sides of A is w_A, u_A.)
+// v_new does not depend on the blocking and h keeps every second state, so neither passes through here.
+namespace fla {
+namespace {
+
+struct F32View {
+  const float* p; int64_t sb, st, sh;
+};
+struct KdaMergeInterParams {
+  InView k;
+  const void* beta; int beta_is_f32; int64_t beta_sb, beta_st, beta_sh;
+  const float* gk; float gk_unit;
+  F32View akk64, w64, u64, qg64, kg64;
+  OutView w, u, qg, kg;
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int T, HK, HV, V;
+};
+
+constexpr int kMergeInterSmem = (2 * kC * kK + 3 * kC * kC) * 4;   // a 64 x 128 tile twice; M, X_B, XM
+
+__global__ void __launch_bounds__(256) kda_merge_intermediates_kernel(KdaMergeInterParams p) {
+  extern __shared__ float mi_smem[];
+  float* ta = mi_smem;                  // [64][128]: kg_A, then the right-hand sides w_A / u_A
+  float* tb = ta + kC * kK;             // [64][128]: (k e^{gk})_B
+  float* m_kk = tb + kC * kK;           // [64][64]
+  float* xb = m_kk + kC * kC;
+  float* xm = xb + kC * kC;
+  __shared__ float beta_s[kC], el_s[kK], eb_s[kK];
+  const int tid = threadIdx.x;
+  const int n = blockIdx.z, hv = blockIdx.y, c2 = blockIdx.x;
+  const SeqInfo sq = seq_info(p.cu_seqlens, p.chunk_offsets, n, p.T);
+  if (2 * c2 >= sq.nt) return;
+  const int hk = hv / (p.HV / p.HK);
+  const int64_t b = p.cu_seqlens ? 0 : n;
+  const int64_t t0 = (p.cu_seqlens ? sq.bos : 0) + int64_t(c2) * 128;
+  const int64_t flat0 = b * p.T + t0;
+  const int len = min(128, sq.len - c2 * 128);
+  const int ra = min(kC, len), rb = len - ra;
+  const int col = tid & 127, par = tid >> 7;
+  auto at = [&](const F32View& v, int t, int c) { return v.p[b * v.sb + (t0 + t) * v.st + hv * v.sh + c]; };
+  auto to = [&](const OutView& v, int t, int c, float x) { put(v.p, v.dtype, b * v.sb + (t0 + t) * v.st + hv * v.sh + c, x); };
+
+  const float* gkc = p.gk + (flat0 * p.HV + hv) * kK + col;
+  if (tid < kK) {
+    el_s[tid] = expf(gkc[int64_t(ra - 1) * p.HV * kK] * p.gk_unit);
+    eb_s[tid] = rb > 0 ? expf(gkc[int64_t(len - 1) * p.HV * kK] * p.gk_unit) : 1.f;
+  }
+  if (tid < kC) beta_s[tid] = tid < rb ? ld_scalar(p.beta, b * p.beta_sb + (t0 + kC + tid) * p.beta_st + hv * p.beta_sh, p.beta_is_f32) : 0.f;
+  for (int s = 0; s < 64; ++s) {
+    const int t = par + 2 * s;
+    if (t >= len) break;
+    if (t < kC) {
+      ta[t * kK + col] = at(p.kg64, t, col);
+    } else {
+      const float g = gkc[int64_t(t) * p.HV * kK] * p.gk_unit;
+      tb[(t - kC) * kK + col] = __bfloat162float(p.k.p[b * p.k.sb + (t0 + t) * p.k.st + hk * p.k.sh + col]) * expf(g);
+    }
+  }
+  for (int idx = tid; idx < kC * kC; idx += 256) {
+    const int i = idx >> 6, j = idx & 63;
+    xb[idx] = (i < rb && j < rb) ? at(p.akk64, kC + i, j) : 0.f;
+  }
+  __syncthreads();
+  // the elementwise parts and the rows of A
+  for (int s = 0; s < 64; ++s) {
+    const int t = par + 2 * s;
+    if (t >= len) break;
+    if (p.qg.p) to(p.qg, t, col, at(p.qg64, t, col) * (t < kC ? 1.f : el_s[col]));
+    if (p.kg.p) to(p.kg, t, col, at(p.kg64, t, col) * (t < kC ? eb_s[col] : 1.f));
+    if (t < kC) {
+      if (p.w.p) to(p.w, t, col, at(p.w64, t, col));
+      if (p.u.p)
+        for (int vh = 0; vh < p.V / 128; ++vh) to(p.u, t, vh * 128 + col, at(p.u64, t, vh * 128 + col));
+    }
+  }
+  if (rb <= 0 || (!p.w.p && !p.u.p)) return;
+  // M = beta_B (k e^gk)_B kg_A^T, then XM = X_B M
+  {
+    const int j = tid & 63, i0 = (tid >> 6) * 16;
+    float ak[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) ak[r] = 0.f;
+    for (int k = 0; k < kK; ++k) {
+      const int kk = (k + j) & 127;
+      const float kg = ta[j * kK + kk];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) ak[r] += tb[(i0 + r) * kK + kk] * kg;
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) m_kk[(i0 + r) * kC + j] = (i0 + r < rb && j < ra) ? beta_s[i0 + r] * ak[r] : 0.f;
+    __syncthreads();
+    float acc[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) acc[r] = 0.f;
+    for (int k = 0; k < kC; ++k) {
+      const float x = m_kk[k * kC + j];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) acc[r] += xb[(i0 + r) * kC + k] * x;
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) xm[(i0 + r) * kC + j] = acc[r];
+  }
+  // rows of B: out = own - XM rhs_A, 128 columns at a time (w first, then u)
+  const int passes = (p.w.p ? 1 : 0) + (p.u.p ? p.V / 128 : 0);
+  for (int ps = 0; ps < passes; ++ps) {
+    const bool is_w = p.w.p && ps == 0;
+    const int vh = ps - (p.w.p ? 1 : 0);
+    __syncthreads();     // XM complete / the previous pass has read `ta`
+    for (int s = 0; s < 32; ++s) {
+      const int t = par + 2 * s;
+      ta[t * kK + col] = t < ra ? (is_w ? at(p.w64, t, col) : at(p.u64, t, vh * 128 + col)) : 0.f;
+    }
+    __syncthreads();
+    float acc[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) acc[r] = 0.f;
+    for (int j = 0; j < kC; ++j) {
+      const float rj = ta[j * kK + col];
+#pragma unroll
+      for (int r = 0; r < 32; ++r) acc[r] += xm[(par * 32 + r) * kC + j] * rj;
+    }
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      const int i = par * 32 + r;
+      if (i >= rb) continue;
+      if (is_w) to(p.w, kC + i, col, at(p.w64, kC + i, col) * el_s[col] - acc[r]);
+      else to(p.u, kC + i, vh * 128 + col, at(p.u64, kC + i, vh * 128 + col) - acc[r]);
+    }
+  }
+}
+
+bool f32_view(const fla_tensor_t& t, int64_t B, int64_t T, int64_t H, int64_t D, F32View* v) {
+  if (!t.data || t.dtype != FLA_F32 || t.ndim != 4 || t.shape[0] != B || t.shape[1] != T || t.shape[2] != H || t.shape[3] != D || t.stride[3] != 1)
+    return false;
+  *v = F32View{static_cast<const float*>(t.data), t.stride[0], t.stride[1], t.stride[2]};
+  return true;
+}
+
+}  // namespace
+}  // namespace fla
+
+extern "C" FLA_API int fla_b200_kda_merge_intermediates(const fla_kda_merge_inter_args* a, void* stream) {
+  using namespace fla;
+  if (!a) return FLA_ERR_NULL;
+  if (!a->k.data || !a->beta.data || !a->gk.data || !a->akk64.data || !a->w64.data || !a->u64.data || !a->qg64.data || !a->kg64.data)
+    return FLA_ERR_NULL;
+  if (a->k.ndim != 4 || a->gk.ndim != 4 || a->u64.ndim != 4) return FLA_ERR_SHAPE;
+  const int64_t B = a->k.shape[0], T = a->k.shape[1], HK = a->k.shape[2], HV = a->gk.shape[2], V = a->u64.shape[3];
+  if (a->k.shape[3] != kK || HK <= 0 || HV % HK || (V != 128 && V != 256)) return FLA_ERR_SHAPE;
+  KdaMergeInterParams p{};
+  if (!in_view(a->k, B, T, HK, kK, &p.k)) return FLA_ERR_SHAPE;
+  const fla_tensor_t& be = a->beta;
+  if (be.ndim != 3 || be.shape[0] != B || be.shape[1] != T || be.shape[2] != HV) return FLA_ERR_SHAPE;
+  if (be.dtype != FLA_F32 && be.dtype != FLA_BF16) return FLA_ERR_DTYPE;
+  p.beta = be.data; p.beta_is_f32 = be.dtype == FLA_F32; p.beta_sb = be.stride[0]; p.beta_st = be.stride[1]; p.beta_sh = be.stride[2];
+  const fla_tensor_t& gk = a->gk;
+  if (gk.dtype != FLA_F32 || gk.shape[0] != B || gk.shape[1] != T || gk.shape[3] != kK || gk.stride[3] != 1 || gk.stride[2] != kK ||
+      gk.stride[1] != HV * kK || (B > 1 && gk.stride[0] != T * HV * kK))
+    return FLA_ERR_SHAPE;
+  p.gk = static_cast<const float*>(gk.data);
+  p.gk_unit = a->gk_base2 ? 0.6931471805599453f : 1.f;
+  if (!f32_view(a->akk64, B, T, HV, kC, &p.akk64) || !f32_view(a->w64, B, T, HV, kK, &p.w64) || !f32_view(a->u64, B, T, HV, V, &p.u64) ||
+      !f32_view(a->qg64, B, T, HV, kK, &p.qg64) || !f32_view(a->kg64, B, T, HV, kK, &p.kg64))
+    return FLA_ERR_SHAPE;
+  int st;
+  if ((st = out_view(a->w, B, T, HV, kK, &p.w)) || (st = out_view(a->u, B, T, HV, V, &p.u)) || (st = out_view(a->qg, B, T, HV, kK, &p.qg)) ||
+      (st = out_view(a->kg, B, T, HV, kK, &p.kg)))
+    return st;
+  int N = int(B), max_len = int(T);
+  if (a->cu_seqlens.data) {
+    if (B != 1 || a->cu_seqlens.dtype != FLA_I32 || a->cu_seqlens.ndim != 1 || a->cu_seqlens.shape[0] < 2) return FLA_ERR_SHAPE;
+    N = int(a->cu_seqlens.shape[0] - 1);
+    if (!a->chunk_offsets.data || a->chunk_offsets.dtype != FLA_I32 || a->chunk_offsets.shape[0] != N + 1) return FLA_ERR_SHAPE;
+    if (a->max_seqlen <= 0 || a->max_seqlen > T) return FLA_ERR_VALUE;
+    max_len = a->max_seqlen;
+  }
+  p.cu_seqlens = static_cast<const int32_t*>(a->cu_seqlens.data);
+  p.chunk_offsets = static_cast<const int32_t*>(a->chunk_offsets.data);
+  p.T = int(T); p.HK = int(HK); p.HV = int(HV); p.V = int(V);
+  static std::atomic<bool> attr_done_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (!attr_done_dev[dev]) {
+    if (cudaFuncSetAttribute(kda_merge_intermediates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeInterSmem) != cudaSuccess)
+      return FLA_ERR_CUDA;
+    attr_done_dev[dev] = true;
+  }
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  KernelTimer kt("kda_merge_intermediates", cs);
+  kda_merge_intermediates_kernel<<<dim3((max_len + 127) / 128, unsigned(HV), N), 256, kMergeInterSmem, cs>>>(p);
+  return cuda_status(cudaGetLastError());
+}

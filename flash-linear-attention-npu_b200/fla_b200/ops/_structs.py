@@ -69,6 +69,11 @@ class KdaMergeBlocksArgs(ctypes.Structure):
                                            "gk_out")] + [("scale", ctypes.c_float), ("max_seqlen", ctypes.c_int32), ("gk_base2", ctypes.c_int32)]
 
 
+class KdaMergeInterArgs(ctypes.Structure):
+    _fields_ = [(n, TensorDesc) for n in ("k", "beta", "gk", "akk64", "w64", "u64", "qg64", "kg64", "cu_seqlens", "chunk_offsets",
+                                           "w", "u", "qg", "kg")] + [("max_seqlen", ctypes.c_int32), ("gk_base2", ctypes.c_int32)]
+
+
 class KdaGateArgs(ctypes.Structure):
     _fields_ = [(n, TensorDesc) for n in ("g", "a_log", "dt_bias", "gate", "d_gate", "d_g", "d_a_log", "d_dt_bias")] + [
         ("lower_bound", ctypes.c_float), ("gate_mode", ctypes.c_int32)]

@@ -343,6 +343,30 @@ def _merge_score_blocks(q, k, beta, gk64, aqk64, akk64, scale, cu_seqlens, dtype
     return aqk, akk, gk
 
 
+def _merge_intermediates(k, beta, gk64, akk64, inter64, cu_seqlens, dtype):
+    """w, u, qg, kg `[B,HV,T,.]` of 128-token chunks from the fp32 ones of the 64-token chunks (`fla_b200_kda_merge_intermediates`).
+    k `[B,T,HK,K]`, beta `[B,T,HV]` (row-major), gk64 `[B,T,HV,K]` fp32 base 2, akk64 `[B,HV,T,64]` fp32."""
+    from ._structs import KdaMergeInterArgs
+    B, T, HK, K = k.shape
+    HV = beta.shape[2]
+    dev = k.device
+    if beta.dtype not in (torch.float32, torch.bfloat16):
+        beta = beta.float()
+    cu = co = None
+    max_len = T
+    if cu_seqlens is not None:
+        cu, co, max_len, _, _, _ = _varlen_meta(cu_seqlens, dev)
+    out = {n: torch.zeros(inter64[n].shape, dtype=dtype, device=dev) for n in ("w", "u", "qg", "kg")}
+    a = KdaMergeInterArgs()
+    a.k, a.beta, a.gk, a.akk64 = rt.desc(k), rt.desc(beta), rt.desc(gk64.contiguous()), rt.desc(akk64.transpose(1, 2))
+    a.w64, a.u64, a.qg64, a.kg64 = (rt.desc(inter64[n].transpose(1, 2)) for n in ("w", "u", "qg", "kg"))
+    a.cu_seqlens, a.chunk_offsets = rt.desc(cu), rt.desc(co)
+    a.w, a.u, a.qg, a.kg = (rt.desc(out[n].transpose(1, 2)) for n in ("w", "u", "qg", "kg"))
+    a.max_seqlen, a.gk_base2 = int(max_len), 1
+    _single_phase("kda_merge_intermediates", a, dev)
+    return out
+
+
 def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", initial_state=None, output_final_state=False,
                       cu_seqlens=None, chunk_indices=None, safe_gate=False, lower_bound=None, use_gate_in_kernel=False,
                       A_log=None, dt_bias=None, disable_recompute=False, return_intermediate_states=False, state_v_first=False):
@@ -354,7 +378,8 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     second, chunk-parallel pass over the forward's saved operand images that forms them (`kda_chunk_intermediates`), with
     the gate activated in front of the kernels when `use_gate_in_kernel` is set.  `chunk_size=128`: o and the states do not
     depend on the blocking; gk, Aqk, Akk `[B,HV,T,128]` are merged from the 64-token blocks (`fla_b200_kda_merge_score_blocks`)
-    and h keeps every second state; w, u, qg, kg, v_new exist for chunk_size 64 only.  `state_v_first=True` takes and returns the recurrent state as `[N,HV,V,K]`.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
+    h keeps every second state, and w, u, qg, kg are merged from the fp32 ones of the halves (`fla_b200_kda_merge_intermediates`).
+    `state_v_first=True` takes and returns the recurrent state as `[N,HV,V,K]`.  Layouts: "BSND" `[B,T,H,D]`, "BNSD" `[B,H,T,D]`, "TND" / "NTD" (3-D, packed, with `cu_seqlens`); `attn_out`
     comes back in the input's layout."""
     del chunk_indices
     op = "npu_chunk_kda_fwd"
@@ -367,8 +392,6 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
     #                                  blocks and gk of 128-token chunks are merged from those of their two halves afterwards
     want_full = bool(disable_recompute)
     want_h = want_full or bool(return_intermediate_states)
-    if big and want_full:
-        raise NotImplementedError(f"{op}: w, u, qg, kg, v_new are formed for chunk_size = 64 only")
     rank3 = layout in {"TND", "NTD"}
 
     def to_bsnd(t):
@@ -402,7 +425,8 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
                                                     output_final_state=output_final_state, cu_seqlens=cu_seqlens,
                                                     export_scores=(aqk.transpose(1, 2), akk.transpose(1, 2)), _return_saved=True,
                                                     **gate_kw)
-            inter, h = kda_chunk_intermediates(*rows_in, saved, meta, full=want_full, state_v_first=state_v_first, dtype=q.dtype)
+            inter, h = kda_chunk_intermediates(*rows_in, saved, meta, full=want_full, state_v_first=state_v_first,
+                                               dtype=torch.float32 if (big and want_full) else q.dtype)
             if big:   # the states at the starts of the 128-token chunks: every second 64-token chunk of each sequence
                 bounds = [0, T] if cu_seqlens is None else [int(x) for x in cu_seqlens]
                 first, idx = 0, []
@@ -422,6 +446,12 @@ def npu_chunk_kda_fwd(q, k, v, g, beta, scale, chunk_size=64, *, layout="BSND", 
         gk64 = kda_gate_cumsum(gb, CHUNK, cu_seqlens=cu_seqlens, **{k_: v_ for k_, v_ in gate_kw.items()})          # [B,T,HV,K], base 2
         gk_out = gk64.permute(0, 2, 1, 3)                                                                             # [B,HV,T,K]
     if big:
+        if want_full:   # w, u, qg, kg of the 128-token chunks from the fp32 ones of their halves; v_new and h only change dtype
+            from ._convert import convert
+            merged = _merge_intermediates(rows_in[1], rows_in[3], gk64, akk, inter, cu_seqlens, q.dtype)
+            merged["v_new"] = convert(inter["v_new"], q.dtype, op)
+            inter = merged
+            h = convert(h.reshape(-1, *h.shape[-2:]), q.dtype, op).view(h.shape)
         aqk, akk, gk_out = _merge_score_blocks(qb, kb, bb, gk64, aqk, akk, scale, cu_seqlens, q.dtype,
                                                want_gk=not use_gate_in_kernel or want_full)
     if state_v_first and ht is not None:

@@ -364,6 +364,21 @@ typedef struct fla_kda_merge_blocks_args {
 } fla_kda_merge_blocks_args;
 FLA_API int fla_b200_kda_merge_score_blocks(const fla_kda_merge_blocks_args* args, void* stream);
 
+/* w, u, qg, kg of 128-token chunks from those of their 64-token halves A, B (fla_b200_kda_chunk_intermediates with f32 outputs):
+ *     qg128 = qg on A, qg e^L on B;   kg128 = kg e^{gk_B,last} on A, kg on B;
+ *     w128 = w on A, w e^L - (X_B M) w_A on B;   u128 = u on A, u - (X_B M) u_A on B      (M as in the score-block merge)
+ *   k [B,T,HK,K] bf16, beta [B,T,HV], gk [B,T,HV,K] f32 dense (natural log, or base 2 with gk_base2), akk64 [B,T,HV,64] f32 view,
+ *   w64, qg64, kg64 [B,T,HV,K] and u64 [B,T,HV,V] f32 views;  w, u, qg, kg: out views of the same shapes, bf16|f16|f32, optional.
+ * v_new does not depend on the blocking and h keeps every second state.  Single-phase (no workspace). */
+typedef struct fla_kda_merge_inter_args {
+  fla_tensor_t k, beta, gk, akk64, w64, u64, qg64, kg64;
+  fla_tensor_t cu_seqlens, chunk_offsets;
+  fla_tensor_t w, u, qg, kg;
+  int32_t max_seqlen;
+  int32_t gk_base2;
+} fla_kda_merge_inter_args;
+FLA_API int fla_b200_kda_merge_intermediates(const fla_kda_merge_inter_args* args, void* stream);
+
 /* Gate activation of KDA as a tensor, and its gradient: what chunk_kda needs on its differentiable path when
  * use_gate_in_kernel is set (fla/ops/ascendc/kda/chunk_kda_fwd/docs/api.md:103-115; the inference path activates the gate
  * inside the forward kernels instead).

@@ -10,7 +10,7 @@ reference tree by tests/golden/make_golden.py) on seeded inputs; the resulting v
 committed fixtures under tests/golden/, and tests/test_oracle_golden.py replays them.
 """
 from .gdn import naive_recurrent_gated_delta_rule, gdn_reference_fwd_bwd, chunk_gated_delta_rule_restated  # noqa: F401
-from .kda import (chunk_kda_bwd_intra_ref, kda_chunk_score_blocks_ref, kda_reference_fwd_bwd,  # noqa: F401
+from .kda import (chunk_kda_bwd_intra_ref, kda_chunk_intermediates_ref, kda_chunk_score_blocks_ref, kda_reference_fwd_bwd,  # noqa: F401
                   naive_recurrent_kda)
 from .recurrent import recurrent_gated_delta_rule_golden  # noqa: F401
 from .conv import (causal_conv1d_bwd_ref, causal_conv1d_ref, causal_conv1d_update_ref,  # noqa: F401

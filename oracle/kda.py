@@ -94,6 +94,51 @@ def kda_chunk_score_blocks_ref(q, k, g, beta, scale, cu_seqlens=None, chunk_size
     return aqk, akk, gk
 
 
+def kda_chunk_intermediates_ref(q, k, v, g, beta, scale, initial_state=None, cu_seqlens=None, chunk_size=64):
+    """The chunked KDA forward with every intermediate in fp64, `[B,T,H,.]` inputs (g = log decay per channel), head-first results:
+        gk (base 2), qg = q 2^{gk}, kg = k 2^{gk_last - gk}, w = Akk (beta k 2^{gk}), u = Akk (beta v)       [B,HV,T,.]
+        v_new = u - w S, S <- 2^{gk_last} S + kg^T v_new, o = scale qg S + Aqk v_new;  h = S at the start of every chunk  [chunks,HV,K,V]
+    Restates the chunk loop of the reference's chunked golden (tests/atk/chunk_kda_fwd/executor_chunk_kda_fwd.py:447-492)
+    on top of `kda_chunk_score_blocks_ref` (its score blocks), for any chunk size."""
+    C = chunk_size
+    B, T, HK, K = q.shape
+    HV, V = v.shape[2], v.shape[3]
+    G = HV // HK
+    aqk, akk, gk = kda_chunk_score_blocks_ref(q, k, g, beta, scale, cu_seqlens, C)
+    qq = q.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
+    kk = k.double().repeat_interleave(G, dim=2).permute(0, 2, 1, 3)
+    vv = v.double().permute(0, 2, 1, 3)
+    bb = beta.double().permute(0, 2, 1)
+    out = {n: torch.zeros(B, HV, T, d, dtype=torch.float64) for n, d in (("w", K), ("u", V), ("qg", K), ("kg", K), ("v_new", V), ("o", V))}
+    bounds = [0, T] if cu_seqlens is None else [int(x) for x in cu_seqlens]
+    nseq = len(bounds) - 1
+    N = B if cu_seqlens is None else nseq
+    state = torch.zeros(N, HV, K, V, dtype=torch.float64) if initial_state is None else initial_state.double().clone()
+    hs = []
+    for b in range(B):
+        for si, (bos, eos) in enumerate(zip(bounds[:-1], bounds[1:])):
+            n_idx = b if cu_seqlens is None else si
+            for s in range(bos, eos, C):
+                e = min(s + C, eos)
+                n = e - s
+                gc = gk[b, :, s:e]                                               # [HV, n, K], base 2
+                eg = torch.exp2(gc)
+                qg = qq[b, :, s:e] * eg
+                kg = kk[b, :, s:e] * torch.exp2(gc[:, -1:, :] - gc)
+                A = akk[b, :, s:e, :n]
+                w = A @ (kk[b, :, s:e] * bb[b, :, s:e, None] * eg)
+                u = A @ (vv[b, :, s:e] * bb[b, :, s:e, None])
+                S = state[n_idx]
+                hs.append(S.clone())
+                vn = u - w @ S
+                out["o"][b, :, s:e] = scale * (qg @ S) + aqk[b, :, s:e, :n] @ vn
+                state[n_idx] = torch.exp2(gc[:, -1, :]).unsqueeze(-1) * S + kg.transpose(1, 2) @ vn
+                for name, val in (("w", w), ("u", u), ("qg", qg), ("kg", kg), ("v_new", vn)):
+                    out[name][b, :, s:e] = val
+    out.update(gk=gk, aqk=aqk, akk=akk, h=torch.stack(hs), final_state=state)
+    return out
+
+
 def chunk_kda_bwd_intra_ref(q, k, gk, beta, d_aqk, d_akk, dq, dk, db, dg, chunk_size=64, cu_seqlens=None):
     """Intra-chunk KDA backward accumulated onto dq, dk, db, dg (returns new tensors), fp64, `[B,T,H,.]` layout.
     Restates torch_custom/fla_npu/test/test_npu_chunk_kda_bwd_intra.py:7-91 without its 16-row anchoring (exact in fp64):

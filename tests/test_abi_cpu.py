@@ -61,6 +61,7 @@ def _c_struct_fields(name):
                                           ("fla_kda_intermediates_args", "KdaIntermediatesArgs"),
                                           ("fla_kda_gate_args", "KdaGateArgs"),
                                           ("fla_kda_merge_blocks_args", "KdaMergeBlocksArgs"),
+                                          ("fla_kda_merge_inter_args", "KdaMergeInterArgs"),
                                           ("fla_l2norm_args", "L2NormArgs"),
                                           ("fla_fast_gelu_args", "FastGeluArgs"),
                                           ("fla_chunk_stage_args", "ChunkStageArgs"),

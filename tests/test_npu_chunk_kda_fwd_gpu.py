@@ -211,5 +211,14 @@ def test_chunk_size_128(layout, cu):
             starts += list(range(first, first + n64, 2))
             first += n64
         assert torch.equal(h, h64[starts])
-    with pytest.raises(NotImplementedError):
-        npu_chunk_kda_fwd(*args, scale, 128, layout=layout, cu_seqlens=cu, disable_recompute=True)
+    # disable_recompute at chunk size 128: every intermediate against the oracle's restatement of the reference's chunk loop
+    # (pinned to the reference fixture at chunk size 64 by tests/test_oracle_golden.py) run with chunk size 128
+    full = npu_chunk_kda_fwd(*args, scale, 128, layout=layout, output_final_state=True, cu_seqlens=cu, disable_recompute=True)
+    ref = oracle.kda_chunk_intermediates_ref(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], scale, cu_seqlens=cu, chunk_size=128)
+    assert torch.equal(full[0], out[0]) and torch.equal(full[3], out[3]) and torch.equal(full[4], out[4])
+    for name, got in zip(("w", "u", "qg", "kg", "v_new"), full[5:10]):
+        got = got.unsqueeze(0) if layout == "TND" else got
+        assert got.dtype == torch.bfloat16
+        assert_close(name, got, ref[name], 5e-3, stored_bf16=True)
+    hh = full[10] if layout == "TND" else full[10].reshape(-1, *full[10].shape[2:])
+    assert_close("h", hh, ref["h"], 5e-3, stored_bf16=True)

@@ -135,3 +135,20 @@ def test_kda_chunked_forward_golden_pins_the_score_blocks_and_the_recurrence():
         for name, got, ref in (("o", o, f["o"][:, bos:eos]), ("ht", ht, f["final_state"][i:i + 1])):
             err = (got - ref.double()).abs().max().item() / ref.double().pow(2).mean().sqrt().item()
             assert err < 2e-6, (name, i, err)
+
+
+def test_kda_chunked_forward_golden_pins_the_intermediates():
+    """w, u, qg, kg, v_new, h, o and the final state of the reference's chunked golden (the same fixture, chunk size 64) pin the
+    oracle's restatement of its chunk loop, which the GPU tests then run at chunk size 128 as well."""
+    f = _load("kda_chunk_fwd_golden.npz")
+    cu = [int(x) for x in f["cu"]]
+    got = oracle.kda_chunk_intermediates_ref(f["q"], f["k"], f["v"], f["g"], f["beta"], float(f["scale"]), initial_state=f["h0"],
+                                             cu_seqlens=cu, chunk_size=64)
+    for name in ("w", "u", "qg", "kg", "v_new", "final_state"):
+        ref = f[name].double()
+        err = (got[name] - ref).abs().max().item() / ref.pow(2).mean().sqrt().item()
+        assert err < 2e-6, (name, err)
+    ref = f["h"].double().squeeze(0)
+    assert (got["h"] - ref).abs().max().item() / ref.pow(2).mean().sqrt().item() < 2e-6
+    ref = f["o"].double().permute(0, 2, 1, 3)
+    assert (got["o"] - ref).abs().max().item() / ref.pow(2).mean().sqrt().item() < 2e-6
