@@ -322,6 +322,9 @@ def _merge_score_blocks(q, k, beta, gk64, aqk64, akk64, scale, cu_seqlens, dtype
     B, T, HK, K = q.shape
     HV = beta.shape[2]
     dev = q.device
+    if q.dtype == torch.float16:   # the same rounded operands the forward kernels saw
+        from ._convert import convert
+        q, k = convert(q, torch.bfloat16), convert(k, torch.bfloat16)
     q, k, beta = _as_rows(q), _as_rows(k), _as_rows(beta)
     if beta.dtype not in (torch.float32, torch.bfloat16):
         beta = beta.float()

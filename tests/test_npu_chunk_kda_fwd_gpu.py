@@ -222,3 +222,29 @@ def test_chunk_size_128(layout, cu):
         assert_close(name, got, ref[name], 5e-3, stored_bf16=True)
     hh = full[10] if layout == "TND" else full[10].reshape(-1, *full[10].shape[2:])
     assert_close("h", hh, ref["h"], 5e-3, stored_bf16=True)
+
+
+@pytest.mark.parametrize("chunk", [64, 128])
+def test_intermediates_edge_cases(chunk):
+    """A packed batch with an empty sequence, a one-token sequence and ragged chunks, V = 256, GVA, fp16 tensors and an initial
+    state: every one of the twelve values against the oracle's chunk loop on the bf16-rounded tensors, at both chunk sizes."""
+    from fla_b200.ops import npu_chunk_kda_fwd
+    cu = [0, 0, 1, 130, 131, 330]
+    T, HK, HV, V = 330, 1, 2, 256
+    inp = oracle.make_kda_inputs(1, T, HK, HV, V=V, seed=71, dtype=torch.float16, with_grad=False)
+    h0 = 0.1 * torch.randn(len(cu) - 1, HV, 128, V, generator=torch.Generator().manual_seed(12))
+    scale = 128 ** -0.5
+    rq, rk, rv = (inp[n].bfloat16() for n in ("q", "k", "v"))
+    ref = oracle.kda_chunk_intermediates_ref(rq, rk, rv, inp["g"], inp["beta"], scale, initial_state=h0, cu_seqlens=cu, chunk_size=chunk)
+    args = [inp[n].squeeze(0).cuda() for n in ("q", "k", "v")] + [inp["g"].squeeze(0).cuda().float(), inp["beta"].squeeze(0).cuda().float()]
+    out = npu_chunk_kda_fwd(*args, scale, chunk, layout="TND", initial_state=h0.cuda(), output_final_state=True, cu_seqlens=cu,
+                            disable_recompute=True)
+    names = ("o", "final_state", "gk", "aqk", "akk", "w", "u", "qg", "kg", "v_new", "h")
+    for name, got in zip(names, out[:11]):
+        r = ref[name]
+        if name == "o":
+            r = r.permute(0, 2, 1, 3)
+        if name not in ("final_state", "h"):
+            got = got.unsqueeze(0)
+        assert got.dtype == (torch.float32 if name in ("final_state", "gk") else torch.float16), name
+        assert_close(name, got, r, 1e-5 if name == "gk" else 5e-3, stored_bf16=name not in ("final_state", "gk"))
