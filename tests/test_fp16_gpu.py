@@ -153,3 +153,70 @@ def test_npu_chunk_kda_fwd_fp16():
         assert o16[i].dtype == torch.float16 and o16[i].shape == ob[i].shape
         diff = (o16[i].double() - ob[i].double()).abs()
         assert (diff <= ob[i].double().abs() * (2.0 ** -8 + 2.0 ** -11) + 2.0 ** -24).all(), i
+
+
+def _bf16_valued_half(t):
+    """fp16 tensor holding values that are exactly representable in bf16 as well (so both dtypes carry the same numbers)."""
+    return t.bfloat16().half()
+
+
+def test_decode_surfaces_fp16_equal_bf16_on_shared_values():
+    """recurrent_gated_delta_rule and recurrent_kda with fp16 tensors whose values are bf16-representable: the kernel's
+    arithmetic is fp32 on the same numbers, so the updated state pools are bit-identical to the bf16 calls."""
+    from fla_b200.ops import recurrent_gated_delta_rule, recurrent_kda
+    torch.manual_seed(3)
+    bs, mtp, nk, nv, dk, dv = 3, 2, 2, 4, 128, 128
+    asl = torch.cat([torch.tensor([1], dtype=torch.int32), torch.full((bs,), mtp, dtype=torch.int32)])
+    t = int(asl.sum())
+    state = torch.rand((t, nv, dv, dk))
+    q = _bf16_valued_half(torch.nn.functional.normalize(torch.rand((t, nk, dk)), p=2, dim=-1)).cuda()
+    k = _bf16_valued_half(torch.nn.functional.normalize(torch.rand((t, nk, dk)), p=2, dim=-1)).cuda()
+    v = _bf16_valued_half(torch.rand((t, nv, dv))).cuda()
+    beta = _bf16_valued_half(torch.rand((t, nv))).cuda()
+    g = (-torch.rand((t, nv))).cuda()
+    ssm = torch.randperm(t).to(torch.int32).cuda()
+    pools, outs = [], []
+    for dt in (torch.float16, torch.bfloat16):
+        pool = state.clone().cuda()
+        outs.append(recurrent_gated_delta_rule(q.to(dt), k.to(dt), v.to(dt), pool, beta=beta.to(dt), scale=dk ** -0.5,
+                                               actual_seq_lengths=asl.cuda(), ssm_state_indices=ssm, g=g))
+        pools.append(pool)
+    assert outs[0].dtype == torch.float16 and torch.equal(pools[0], pools[1])
+    a16, ab = outs[0][1:].double(), outs[1][1:].double()          # token 0 is the skipped prefix: its output row is never written
+    assert ((a16 - ab).abs() <= ab.abs() * (2.0 ** -8 + 2.0 ** -11) + 2.0 ** -24).all()
+
+    B, T, H, HV = 2, 3, 2, 4
+    gen = torch.Generator().manual_seed(5)
+    qk = [_bf16_valued_half(torch.nn.functional.normalize(torch.randn(B, T, H, 128, generator=gen), dim=-1)).cuda() for _ in range(2)]
+    vv = _bf16_valued_half(torch.randn(B, T, HV, 128, generator=gen)).cuda()
+    gg = _bf16_valued_half(torch.nn.functional.logsigmoid(torch.randn(B, T, HV, 128, generator=gen)) / 4).cuda()
+    bb = _bf16_valued_half(torch.sigmoid(torch.randn(B, T, HV, generator=gen))).cuda()
+    st = (0.1 * torch.randn(B, HV, 128, 128, generator=gen))
+    res = []
+    for dt in (torch.float16, torch.bfloat16):
+        pool = st.clone().cuda()
+        o, ht = recurrent_kda(qk[0].to(dt), qk[1].to(dt), vv.to(dt), gg.to(dt), bb.to(dt), pool, output_final_state=True,
+                              inplace_final_state=True)
+        res.append((o, pool))
+    assert res[0][0].dtype == torch.float16 and torch.equal(res[0][1], res[1][1])
+
+
+def test_flash_gated_delta_rule_fp16_varlen_backward():
+    """The composed entry with fp16 head-first tensors, packed sequences and in-kernel l2norm, forward and backward: equal to
+    the bf16 call on the rounded tensors up to the storage roundings of o and of the gradients."""
+    from fla_b200.ops import flash_gated_delta_rule
+    cu = torch.tensor([0, 70, 71, 200], dtype=torch.int32)
+    inp = oracle.make_gdn_inputs(1, 200, 2, 4, seed=83, dtype=torch.float16)
+    res = {}
+    for dt in (torch.float16, torch.bfloat16):
+        q, k, v = (inp[n].cuda().to(dt).transpose(1, 2).contiguous().requires_grad_() for n in ("q", "k", "v"))   # [B,H,T,D]
+        g, beta = inp["g"].cuda().float().requires_grad_(), inp["beta"].cuda().float().requires_grad_()
+        o, ht = flash_gated_delta_rule(q, k, v, g, beta, output_final_state=True, cu_seqlens=cu.cuda(), use_qk_l2norm_in_kernel=True)
+        (o.float() * inp["do"].cuda().to(dt).float()).sum().backward()
+        res[dt] = (o, ht, q.grad, k.grad, v.grad, g.grad, beta.grad)
+    a, b = res[torch.float16], res[torch.bfloat16]
+    assert a[0].dtype == torch.float16 and a[2].dtype == torch.float16 and a[4].dtype == torch.float16
+    assert torch.equal(a[1], b[1])
+    for i, name in ((0, "o"), (2, "dq"), (3, "dk"), (4, "dv"), (5, "dg"), (6, "dbeta")):
+        x, y = a[i].double(), b[i].double()                                # the same fp32 values behind two storage roundings
+        assert ((x - y).abs() <= y.abs() * (2.0 ** -8 + 2.0 ** -11) + 2.0 ** -24).all(), (name, rel_err(a[i], b[i]))
