@@ -220,3 +220,27 @@ def test_flash_gated_delta_rule_fp16_varlen_backward():
     for i, name in ((0, "o"), (2, "dq"), (3, "dk"), (4, "dv"), (5, "dg"), (6, "dbeta")):
         x, y = a[i].double(), b[i].double()                                # the same fp32 values behind two storage roundings
         assert ((x - y).abs() <= y.abs() * (2.0 ** -8 + 2.0 ** -11) + 2.0 ** -24).all(), (name, rel_err(a[i], b[i]))
+
+
+def test_chunk_kda_fp16_with_gate_in_kernel_backward():
+    """fp16 q, k, v and an fp16 raw gate with `use_gate_in_kernel`: same result and gradients (incl. A_log, dt_bias) as the bf16 /
+    fp32 call on the rounded tensors, up to the storage roundings."""
+    from fla_b200.ops import chunk_kda
+    B, T, HK, HV = 1, 130, 1, 2
+    inp = oracle.make_kda_inputs(B, T, HK, HV, seed=91, dtype=torch.float16)
+    gen = torch.Generator().manual_seed(2)
+    raw = torch.randn(B, T, HV, 128, generator=gen).half()
+    A_log, dt_bias = torch.randn(HV, generator=gen) * 0.3 - 2.0, torch.randn(HV, 128, generator=gen) * 0.1
+    res = {}
+    for dt in (torch.float16, torch.bfloat16):
+        q, k, v = (inp[n].cuda().to(dt).requires_grad_() for n in ("q", "k", "v"))
+        g = (raw.cuda() if dt == torch.float16 else raw.cuda().float()).requires_grad_()
+        A, b = A_log.cuda().requires_grad_(), dt_bias.cuda().requires_grad_()
+        o, _ = chunk_kda(q, k, v, g, inp["beta"].cuda().float(), use_gate_in_kernel=True, A_log=A, dt_bias=b)
+        (o.float() * inp["do"].cuda().to(dt).float()).sum().backward()
+        res[dt] = (o, q.grad, k.grad, v.grad, g.grad, A.grad, b.grad)
+    a, c = res[torch.float16], res[torch.bfloat16]
+    assert a[0].dtype == torch.float16 and a[4].dtype == torch.float16
+    assert torch.allclose(a[5], c[5], rtol=1e-5, atol=1e-7) and torch.allclose(a[6], c[6], rtol=1e-5, atol=1e-7)
+    for i, name in ((0, "o"), (1, "dq"), (2, "dk"), (3, "dv"), (4, "dg")):
+        assert rel_err(a[i], c[i]) < 3e-2, (name, rel_err(a[i], c[i]))
